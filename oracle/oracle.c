@@ -1,0 +1,599 @@
+/* TEST INFRASTRUCTURE ONLY -- see oracle.h. Compile with -ffp-contract=off (the reference's
+ * build has no FMA contraction and the Q4_K scale search is sensitive to it). */
+#include "oracle.h"
+
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+/* ---------------------------------------------------------------- f16 <-> f32
+ * IEEE binary16, round-to-nearest-even: what GGML_FP32_TO_FP16 / GGML_FP16_TO_FP32 compute
+ * (vendor/ggml/src/ggml-impl.h:407-431). */
+uint16_t orc_f32_to_f16(float f) {
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    uint32_t sign = (u >> 16) & 0x8000u;
+    uint32_t mag = u & 0x7fffffffu;
+    if (mag > 0x7f800000u) return (uint16_t)(sign | 0x7e00u); /* NaN */
+    if (mag >= 0x47800000u) {                                  /* >= 65536: inf (65520.. rounds up below) */
+        return (uint16_t)(sign | 0x7c00u);
+    }
+    if (mag < 0x38800000u) { /* result is subnormal or zero: value * 2^24 rounded to an integer */
+        if (mag < 0x33000000u) return (uint16_t)sign; /* < 2^-25 rounds to zero */
+        int e = (int)(mag >> 23);
+        uint32_t m = (mag & 0x7fffffu) | 0x800000u;
+        int shift = 126 - e; /* m * 2^(e-150) * 2^24 = m >> (126 - e) */
+        uint32_t q = m >> shift;
+        uint32_t rem = m & ((1u << shift) - 1u);
+        uint32_t half = 1u << (shift - 1);
+        if (rem > half || (rem == half && (q & 1u))) q++;
+        return (uint16_t)(sign | q);
+    }
+    uint32_t e = (mag >> 23) - 112u;
+    uint32_t m = mag & 0x7fffffu;
+    uint32_t h = (e << 10) | (m >> 13);
+    uint32_t rem = m & 0x1fffu;
+    if (rem > 0x1000u || (rem == 0x1000u && (h & 1u))) h++; /* carries into the exponent correctly */
+    return (uint16_t)(sign | h);
+}
+
+float orc_f16_to_f32(uint16_t h) {
+    uint32_t sign = ((uint32_t)h & 0x8000u) << 16;
+    uint32_t e = (h >> 10) & 0x1fu;
+    uint32_t m = h & 0x3ffu;
+    uint32_t u;
+    if (e == 0) {
+        if (m == 0) {
+            u = sign;
+        } else {
+            int s = 0;
+            while (!(m & 0x400u)) { m <<= 1; s++; }
+            m &= 0x3ffu;
+            u = sign | ((uint32_t)(113 - s) << 23) | (m << 13);
+        }
+    } else if (e == 31) {
+        u = sign | 0x7f800000u | (m << 13);
+    } else {
+        u = sign | ((e + 112u) << 23) | (m << 13);
+    }
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+/* ---------------------------------------------------------------- block layouts
+ * vendor/ggml/src/ggml-common.h:194-199 (q4_0), :251-256 (q8_0), :327-338 (q4_K), :371-375 (q8_K) */
+#pragma pack(push, 1)
+typedef struct { uint16_t d; uint8_t qs[16]; } blk_q4_0;                       /* 18 B / 32  */
+typedef struct { uint16_t d; int8_t qs[32]; } blk_q8_0;                        /* 34 B / 32  */
+typedef struct { uint16_t d, dmin; uint8_t scales[12]; uint8_t qs[128]; } blk_q4_K; /* 144 B / 256 */
+typedef struct { float d; int8_t qs[256]; int16_t bsums[16]; } blk_q8_K;       /* 292 B / 256 */
+#pragma pack(pop)
+
+int64_t orc_row_size(int type, int64_t ne0) {
+    switch (type) {
+        case ORC_F32: return ne0 * 4;
+        case ORC_F16: return ne0 * 2;
+        case ORC_Q4_0: return ne0 / 32 * 18;
+        case ORC_Q8_0: return ne0 / 32 * 34;
+        case ORC_Q4_K: return ne0 / 256 * 144;
+        default: return -1;
+    }
+}
+
+/* ggml-quants.c:621-626: round to nearest (ties to even) through the 1.5*2^23 magic constant */
+static int near_int(float v) {
+    float t = v + 12582912.f;
+    int32_t i;
+    memcpy(&i, &t, 4);
+    return (i & 0x007fffff) - 0x00400000;
+}
+
+/* ggml-quants.c:276-299 */
+void orc_quantize_row_q8_0(const float *x, void *vy, int64_t k) {
+    blk_q8_0 *y = (blk_q8_0 *)vy;
+    for (int64_t b = 0; b < k / 32; b++) {
+        const float *xb = x + b * 32;
+        float amax = 0.0f;
+        for (int j = 0; j < 32; j++) {
+            float a = fabsf(xb[j]);
+            if (a > amax) amax = a;
+        }
+        const float d = amax / 127;
+        const float id = d ? 1.0f / d : 0.0f;
+        y[b].d = orc_f32_to_f16(d);
+        for (int j = 0; j < 32; j++) y[b].qs[j] = (int8_t)roundf(xb[j] * id);
+    }
+}
+
+/* ggml-quants.c:113-148 */
+void orc_quantize_row_q4_0(const float *x, void *vy, int64_t k) {
+    blk_q4_0 *y = (blk_q4_0 *)vy;
+    for (int64_t b = 0; b < k / 32; b++) {
+        const float *xb = x + b * 32;
+        float amax = 0.0f, max = 0.0f;
+        for (int j = 0; j < 32; j++) {
+            if (amax < fabsf(xb[j])) { amax = fabsf(xb[j]); max = xb[j]; }
+        }
+        const float d = max / -8;
+        const float id = d ? 1.0f / d : 0.0f;
+        y[b].d = orc_f32_to_f16(d);
+        for (int j = 0; j < 16; j++) {
+            const float x0 = xb[j] * id, x1 = xb[16 + j] * id;
+            int a = (int8_t)(x0 + 8.5f), c = (int8_t)(x1 + 8.5f);
+            uint8_t lo = (uint8_t)(a > 15 ? 15 : a), hi = (uint8_t)(c > 15 ? 15 : c);
+            y[b].qs[j] = (uint8_t)(lo | (hi << 4));
+        }
+    }
+}
+
+/* ggml-quants.c:799-878, called with n=32, nmax=15, rmin=-1, rdelta=0.1, nstep=20, use_mad=false */
+static float search_scale_min(const float *x, const float *w, uint8_t *L, float *the_min, uint8_t *Laux) {
+    const int n = 32, nmax = 15, nstep = 20;
+    const float rmin = -1.f, rdelta = 0.1f;
+    float min = x[0], max = x[0];
+    float sum_w = w[0];
+    float sum_x = sum_w * x[0];
+    for (int i = 1; i < n; i++) {
+        if (x[i] < min) min = x[i];
+        if (x[i] > max) max = x[i];
+        sum_w += w[i];
+        sum_x += w[i] * x[i];
+    }
+    if (min > 0) min = 0;
+    if (max == min) {
+        for (int i = 0; i < n; i++) L[i] = 0;
+        *the_min = -min;
+        return 0.f;
+    }
+    float iscale = nmax / (max - min);
+    float scale = 1 / iscale;
+    float best = 0;
+    for (int i = 0; i < n; i++) {
+        int l = near_int(iscale * (x[i] - min));
+        l = l < 0 ? 0 : (l > nmax ? nmax : l);
+        L[i] = (uint8_t)l;
+        float diff = scale * L[i] + min - x[i];
+        diff = diff * diff;
+        best += w[i] * diff;
+    }
+    for (int is = 0; is <= nstep; is++) {
+        iscale = (rmin + rdelta * is + nmax) / (max - min);
+        float sum_l = 0, sum_l2 = 0, sum_xl = 0;
+        for (int i = 0; i < n; i++) {
+            int l = near_int(iscale * (x[i] - min));
+            l = l < 0 ? 0 : (l > nmax ? nmax : l);
+            Laux[i] = (uint8_t)l;
+            sum_l += w[i] * l;
+            sum_l2 += w[i] * l * l;
+            sum_xl += w[i] * l * x[i];
+        }
+        float D = sum_w * sum_l2 - sum_l * sum_l;
+        if (D > 0) {
+            float this_scale = (sum_w * sum_xl - sum_x * sum_l) / D;
+            float this_min = (sum_l2 * sum_x - sum_l * sum_xl) / D;
+            if (this_min > 0) {
+                this_min = 0;
+                this_scale = sum_xl / sum_l2;
+            }
+            float err = 0;
+            for (int i = 0; i < n; i++) {
+                float diff = this_scale * Laux[i] + this_min - x[i];
+                diff = diff * diff;
+                err += w[i] * diff;
+            }
+            if (err < best) {
+                memcpy(L, Laux, n);
+                best = err;
+                scale = this_scale;
+                min = this_min;
+            }
+        }
+    }
+    *the_min = -min;
+    return scale;
+}
+
+/* ggml-quants.c:880-887 */
+static void scale_min_k4(int j, const uint8_t *q, uint8_t *d, uint8_t *m) {
+    if (j < 4) {
+        *d = q[j] & 63;
+        *m = q[j + 4] & 63;
+    } else {
+        *d = (uint8_t)((q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4));
+        *m = (uint8_t)((q[j + 4] >> 4) | ((q[j] >> 6) << 4));
+    }
+}
+
+/* ggml-quants.c:1457-1527 */
+void orc_quantize_row_q4_K(const float *x, void *vy, int64_t k) {
+    blk_q4_K *y = (blk_q4_K *)vy;
+    uint8_t L[256], Laux[32];
+    float weights[32], mins[8], scales[8];
+    for (int64_t b = 0; b < k / 256; b++, x += 256) {
+        float max_scale = 0, max_min = 0;
+        for (int j = 0; j < 8; j++) {
+            const float *xs = x + 32 * j;
+            float sum_x2 = 0;
+            for (int l = 0; l < 32; l++) sum_x2 += xs[l] * xs[l];
+            float av_x = sqrtf(sum_x2 / 32);
+            for (int l = 0; l < 32; l++) weights[l] = av_x + fabsf(xs[l]);
+            scales[j] = search_scale_min(xs, weights, L + 32 * j, &mins[j], Laux);
+            if (scales[j] > max_scale) max_scale = scales[j];
+            if (mins[j] > max_min) max_min = mins[j];
+        }
+        float inv_scale = max_scale > 0 ? 63.f / max_scale : 0.f;
+        float inv_min = max_min > 0 ? 63.f / max_min : 0.f;
+        memset(y[b].scales, 0, 12);
+        for (int j = 0; j < 8; j++) {
+            uint8_t ls = (uint8_t)near_int(inv_scale * scales[j]);
+            uint8_t lm = (uint8_t)near_int(inv_min * mins[j]);
+            if (ls > 63) ls = 63;
+            if (lm > 63) lm = 63;
+            if (j < 4) {
+                y[b].scales[j] = ls;
+                y[b].scales[j + 4] = lm;
+            } else {
+                y[b].scales[j + 4] = (uint8_t)((ls & 0xF) | ((lm & 0xF) << 4));
+                y[b].scales[j - 4] |= (uint8_t)((ls >> 4) << 6);
+                y[b].scales[j] |= (uint8_t)((lm >> 4) << 6);
+            }
+        }
+        y[b].d = orc_f32_to_f16(max_scale / 63.f);
+        y[b].dmin = orc_f32_to_f16(max_min / 63.f);
+        for (int j = 0; j < 8; j++) {
+            uint8_t sc, m;
+            scale_min_k4(j, y[b].scales, &sc, &m);
+            const float d = orc_f16_to_f32(y[b].d) * sc;
+            if (!d) continue;
+            const float dm = orc_f16_to_f32(y[b].dmin) * m;
+            for (int i = 0; i < 32; i++) {
+                int l = near_int((x[32 * j + i] + dm) / d);
+                l = l < 0 ? 0 : (l > 15 ? 15 : l);
+                L[32 * j + i] = (uint8_t)l;
+            }
+        }
+        uint8_t *q = y[b].qs;
+        for (int j = 0; j < 256; j += 64, q += 32)
+            for (int l = 0; l < 32; l++) q[l] = (uint8_t)(L[j + l] | (L[j + l + 32] << 4));
+    }
+}
+
+/* ggml-quants.c:2768-2805 */
+void orc_quantize_row_q8_K(const float *x, void *vy, int64_t k) {
+    blk_q8_K *y = (blk_q8_K *)vy;
+    for (int64_t b = 0; b < k / 256; b++, x += 256) {
+        float max = 0, amax = 0;
+        for (int j = 0; j < 256; j++) {
+            float ax = fabsf(x[j]);
+            if (ax > amax) { amax = ax; max = x[j]; }
+        }
+        if (!amax) {
+            memset(&y[b], 0, sizeof(blk_q8_K)); /* the reference leaves bsums untouched; see note */
+            continue;
+        }
+        const float iscale = -127.f / max;
+        for (int j = 0; j < 256; j++) {
+            int v = near_int(iscale * x[j]);
+            y[b].qs[j] = (int8_t)(v > 127 ? 127 : v);
+        }
+        for (int j = 0; j < 16; j++) {
+            int sum = 0;
+            for (int i = 0; i < 16; i++) sum += y[b].qs[j * 16 + i];
+            y[b].bsums[j] = (int16_t)sum;
+        }
+        y[b].d = 1 / iscale;
+    }
+}
+/* note on the all-zero block: the reference sets d = 0 and qs = 0 and does not write bsums
+ * (ggml-quants.c:2782-2787); with d = 0 the block contributes 0*bsums to every dot product, so the
+ * result only differs if the stale bsums*0 were NaN/inf, which int16 cannot be. Byte comparisons
+ * of Q8_K in tests exclude the bsums of such blocks. */
+
+int orc_quantize_rows(int type, const float *src, int64_t nrows, int64_t n, void *dst) {
+    int64_t rs = orc_row_size(type, n);
+    if (rs < 0) return -1;
+    for (int64_t r = 0; r < nrows; r++) {
+        void *o = (char *)dst + r * rs;
+        const float *s = src + r * n;
+        switch (type) {
+            case ORC_Q8_0: orc_quantize_row_q8_0(s, o, n); break;
+            case ORC_Q4_0: orc_quantize_row_q4_0(s, o, n); break;
+            case ORC_Q4_K: orc_quantize_row_q4_K(s, o, n); break;
+            case ORC_F16: for (int64_t i = 0; i < n; i++) ((uint16_t *)o)[i] = orc_f32_to_f16(s[i]); break;
+            case ORC_F32: memcpy(o, s, (size_t)n * 4); break;
+            default: return -1;
+        }
+    }
+    return 0;
+}
+
+/* ggml-quants.c dequantize_row_q8_0 / _q4_0 / _q4_K (:1529-1551) */
+int orc_dequantize_row(int type, const void *src, float *y, int64_t k) {
+    switch (type) {
+        case ORC_F32: memcpy(y, src, (size_t)k * 4); return 0;
+        case ORC_F16: for (int64_t i = 0; i < k; i++) y[i] = orc_f16_to_f32(((const uint16_t *)src)[i]); return 0;
+        case ORC_Q8_0: {
+            const blk_q8_0 *x = (const blk_q8_0 *)src;
+            for (int64_t b = 0; b < k / 32; b++) {
+                const float d = orc_f16_to_f32(x[b].d);
+                for (int j = 0; j < 32; j++) y[b * 32 + j] = x[b].qs[j] * d;
+            }
+            return 0;
+        }
+        case ORC_Q4_0: {
+            const blk_q4_0 *x = (const blk_q4_0 *)src;
+            for (int64_t b = 0; b < k / 32; b++) {
+                const float d = orc_f16_to_f32(x[b].d);
+                for (int j = 0; j < 16; j++) {
+                    y[b * 32 + j] = ((x[b].qs[j] & 0x0F) - 8) * d;
+                    y[b * 32 + j + 16] = ((x[b].qs[j] >> 4) - 8) * d;
+                }
+            }
+            return 0;
+        }
+        case ORC_Q4_K: {
+            const blk_q4_K *x = (const blk_q4_K *)src;
+            for (int64_t b = 0; b < k / 256; b++) {
+                const float d = orc_f16_to_f32(x[b].d), mn = orc_f16_to_f32(x[b].dmin);
+                const uint8_t *q = x[b].qs;
+                for (int j = 0; j < 4; j++, q += 32) {
+                    uint8_t sc, m;
+                    scale_min_k4(2 * j, x[b].scales, &sc, &m);
+                    const float d1 = d * sc, m1 = mn * m;
+                    scale_min_k4(2 * j + 1, x[b].scales, &sc, &m);
+                    const float d2 = d * sc, m2 = mn * m;
+                    for (int l = 0; l < 32; l++) *y++ = d1 * (q[l] & 0xF) - m1;
+                    for (int l = 0; l < 32; l++) *y++ = d2 * (q[l] >> 4) - m2;
+                }
+            }
+            return 0;
+        }
+        default: return -1;
+    }
+}
+
+/* ---------------------------------------------------------------- dot products
+ * generic (non-SIMD) versions: the ones the reference's -O3 build without -march runs */
+
+/* ggml-cpu/quants.c:451-479 */
+static float dot_q8_0_q8_0(int64_t n, const blk_q8_0 *x, const blk_q8_0 *y) {
+    float sumf = 0;
+    for (int64_t b = 0; b < n / 32; b++) {
+        int sumi = 0;
+        for (int j = 0; j < 32; j++) sumi += x[b].qs[j] * y[b].qs[j];
+        sumf += sumi * (orc_f16_to_f32(x[b].d) * orc_f16_to_f32(y[b].d));
+    }
+    return sumf;
+}
+
+/* ggml-cpu/quants.c:225-260 */
+static float dot_q4_0_q8_0(int64_t n, const blk_q4_0 *x, const blk_q8_0 *y) {
+    float sumf = 0;
+    for (int64_t b = 0; b < n / 32; b++) {
+        int s0 = 0, s1 = 0;
+        for (int j = 0; j < 16; j++) {
+            const int v0 = (x[b].qs[j] & 0x0F) - 8, v1 = (x[b].qs[j] >> 4) - 8;
+            s0 += v0 * y[b].qs[j];
+            s1 += v1 * y[b].qs[j + 16];
+        }
+        int sumi = s0 + s1;
+        sumf += sumi * orc_f16_to_f32(x[b].d) * orc_f16_to_f32(y[b].d);
+    }
+    return sumf;
+}
+
+/* ggml-cpu/quants.c:696-770 */
+static float dot_q4_K_q8_K(int64_t n, const blk_q4_K *x, const blk_q8_K *y) {
+    float sums[8] = {0};
+    float sumf = 0;
+    for (int64_t b = 0; b < n / 256; b++) {
+        int8_t a[256];
+        const uint8_t *q4 = x[b].qs;
+        for (int j = 0; j < 4; j++, q4 += 32) {
+            for (int l = 0; l < 32; l++) a[64 * j + l] = (int8_t)(q4[l] & 0xF);
+            for (int l = 0; l < 32; l++) a[64 * j + 32 + l] = (int8_t)(q4[l] >> 4);
+        }
+        int32_t aux32[8] = {0};
+        int sumi = 0;
+        for (int j = 0; j < 8; j++) {
+            uint8_t sc, m;
+            scale_min_k4(j, x[b].scales, &sc, &m);
+            sumi += (y[b].bsums[2 * j] + y[b].bsums[2 * j + 1]) * m;
+            for (int g = 0; g < 4; g++)
+                for (int l = 0; l < 8; l++) {
+                    int i = 32 * j + 8 * g + l;
+                    aux32[l] += (int32_t)sc * (int16_t)(y[b].qs[i] * a[i]);
+                }
+        }
+        const float d = orc_f16_to_f32(x[b].d) * y[b].d;
+        for (int l = 0; l < 8; l++) sums[l] += d * aux32[l];
+        const float dmin = orc_f16_to_f32(x[b].dmin) * y[b].d;
+        sumf -= dmin * sumi;
+    }
+    for (int l = 0; l < 8; l++) sumf += sums[l];
+    return sumf;
+}
+
+/* ggml-cpu.c:1272-1357: src1 rows are converted with the weight type's vec_dot_type quantizer,
+ * then every output is one vec_dot over the whole row. */
+int orc_mul_mat(int type, const void *W, int64_t K, int64_t M, const float *x, int64_t N, float *y) {
+    const int64_t wrow = orc_row_size(type, K);
+    if (wrow < 0) return -1;
+    if (type == ORC_F32 || type == ORC_F16) {
+        float *row = (float *)malloc((size_t)K * 4);
+        for (int64_t m = 0; m < M; m++) {
+            orc_dequantize_row(type, (const char *)W + m * wrow, row, K);
+            for (int64_t n = 0; n < N; n++) {
+                double s = 0;
+                for (int64_t k = 0; k < K; k++) s += (double)row[k] * (double)x[n * K + k];
+                y[n * M + m] = (float)s;
+            }
+        }
+        free(row);
+        return 0;
+    }
+    const int kq = type == ORC_Q4_K;
+    const int64_t arow = kq ? K / 256 * (int64_t)sizeof(blk_q8_K) : K / 32 * (int64_t)sizeof(blk_q8_0);
+    char *act = (char *)malloc((size_t)(arow * N));
+    for (int64_t n = 0; n < N; n++) {
+        if (kq) orc_quantize_row_q8_K(x + n * K, act + n * arow, K);
+        else orc_quantize_row_q8_0(x + n * K, act + n * arow, K);
+    }
+    for (int64_t n = 0; n < N; n++)
+        for (int64_t m = 0; m < M; m++) {
+            const void *w = (const char *)W + m * wrow;
+            const void *a = act + n * arow;
+            float r;
+            if (type == ORC_Q8_0) r = dot_q8_0_q8_0(K, (const blk_q8_0 *)w, (const blk_q8_0 *)a);
+            else if (type == ORC_Q4_0) r = dot_q4_0_q8_0(K, (const blk_q4_0 *)w, (const blk_q8_0 *)a);
+            else r = dot_q4_K_q8_K(K, (const blk_q4_K *)w, (const blk_q8_K *)a);
+            y[n * M + m] = r;
+        }
+    free(act);
+    return 0;
+}
+
+int orc_mul_mat_dequant(int type, const void *W, int64_t K, int64_t M, const float *x, int64_t N, float *y) {
+    const int64_t wrow = orc_row_size(type, K);
+    if (wrow < 0) return -1;
+    float *row = (float *)malloc((size_t)K * 4);
+    for (int64_t m = 0; m < M; m++) {
+        if (orc_dequantize_row(type, (const char *)W + m * wrow, row, K)) { free(row); return -1; }
+        for (int64_t n = 0; n < N; n++) {
+            double s = 0;
+            for (int64_t k = 0; k < K; k++) s += (double)row[k] * (double)x[n * K + k];
+            y[n * M + m] = (float)s;
+        }
+    }
+    free(row);
+    return 0;
+}
+
+/* ---------------------------------------------------------------- row ops */
+
+/* ops.cpp:3794-3860: sum of squares in double, mean and scale in float */
+void orc_rms_norm(const float *x, int64_t n, int64_t rows, float eps, const float *w, float *y) {
+    for (int64_t r = 0; r < rows; r++) {
+        const float *xr = x + r * n;
+        double sum = 0.0;
+        for (int64_t i = 0; i < n; i++) sum += (double)(xr[i] * xr[i]);
+        const float mean = (float)(sum / n);
+        const float scale = 1.0f / sqrtf(mean + eps);
+        for (int64_t i = 0; i < n; i++) y[r * n + i] = w ? xr[i] * scale * w[i] : xr[i] * scale;
+    }
+}
+
+void orc_silu_mul(const float *g, const float *u, int64_t n, float *y) {
+    for (int64_t i = 0; i < n; i++) y[i] = (g[i] / (1.0f + expf(-g[i]))) * u[i];
+}
+
+/* ops.cpp:5846-5860 (cache: theta multiplied up sequentially), :5935-5949 (pair rotation),
+ * :6085-6093 (dims past n_dims copied). ext_factor = 0, no frequency factors. */
+void orc_rope(const float *x, int64_t ne0, int64_t heads, int64_t tokens, const int32_t *pos, int n_dims,
+              int mode, float freq_base, float freq_scale, float attn_factor, float *y) {
+    const float theta_scale = powf(freq_base, -2.0f / n_dims);
+    float *cache = (float *)malloc((size_t)ne0 * 4);
+    for (int64_t t = 0; t < tokens; t++) {
+        float theta = (float)pos[t];
+        for (int64_t i0 = 0; i0 < ne0; i0 += 2) {
+            const float th = freq_scale * theta;
+            cache[i0] = cosf(th) * attn_factor;
+            cache[i0 + 1] = sinf(th) * attn_factor;
+            theta *= theta_scale;
+        }
+        for (int64_t h = 0; h < heads; h++) {
+            const float *s = x + (t * heads + h) * ne0;
+            float *d = y + (t * heads + h) * ne0;
+            const int64_t off = mode == 0 ? 1 : n_dims / 2;
+            for (int64_t i0 = 0; i0 < n_dims; i0 += 2) {
+                const int64_t ic = mode == 0 ? i0 : i0 / 2;
+                const float c = cache[i0], sn = cache[i0 + 1];
+                const float x0 = s[ic], x1 = s[ic + off];
+                d[ic] = x0 * c - x1 * sn;
+                d[ic + off] = x0 * sn + x1 * c;
+            }
+            for (int64_t i0 = n_dims; i0 < ne0; i0++) d[i0] = s[i0];
+        }
+    }
+    free(cache);
+}
+
+/* ops.cpp:5517-5554 with no mask: y = exp(x*scale - max) / sum (sum in double) */
+void orc_soft_max(const float *x, int64_t n, int64_t rows, float scale, float *y) {
+    for (int64_t r = 0; r < rows; r++) {
+        const float *xr = x + r * n;
+        float *yr = y + r * n;
+        float mx = -INFINITY;
+        for (int64_t i = 0; i < n; i++) {
+            yr[i] = xr[i] * scale;
+            if (yr[i] > mx) mx = yr[i];
+        }
+        double sum = 0.0;
+        for (int64_t i = 0; i < n; i++) {
+            yr[i] = expf(yr[i] - mx);
+            sum += (double)yr[i];
+        }
+        const float inv = (float)(1.0 / sum);
+        for (int64_t i = 0; i < n; i++) yr[i] *= inv;
+    }
+}
+
+int orc_get_rows(int type, const void *table, int64_t ne0, const int32_t *ids, int64_t n_ids, float *y) {
+    const int64_t rs = orc_row_size(type, ne0);
+    if (rs < 0) return -1;
+    for (int64_t i = 0; i < n_ids; i++)
+        if (orc_dequantize_row(type, (const char *)table + (int64_t)ids[i] * rs, y + i * ne0, ne0)) return -1;
+    return 0;
+}
+
+void orc_argmax(const float *x, int64_t n, int64_t rows, int32_t *out) {
+    for (int64_t r = 0; r < rows; r++) {
+        float mx = -INFINITY;
+        int32_t idx = 0;
+        for (int64_t i = 0; i < n; i++) {
+            if (x[r * n + i] > mx) mx = x[r * n + i];
+            if (mx == x[r * n + i]) idx = (int32_t)i;
+        }
+        out[r] = idx;
+    }
+}
+
+void orc_attention_decode(const uint16_t *q, const uint16_t *const *k, const uint16_t *const *v,
+                          const int32_t *ctx, int seqs, int heads, int kv_heads, int hs, float scale,
+                          uint16_t *out, float *out_f32) {
+    const int group = heads / kv_heads;
+    for (int s = 0; s < seqs; s++) {
+        const int n = ctx[s];
+        float *logit = (float *)malloc((size_t)(n > 0 ? n : 1) * 4);
+        double *acc = (double *)malloc((size_t)hs * 8);
+        for (int h = 0; h < heads; h++) {
+            const int kvh = h / group;
+            const uint16_t *qv = q + ((int64_t)s * heads + h) * hs;
+            float mx = -INFINITY;
+            for (int t = 0; t < n; t++) {
+                const uint16_t *kr = k[s] + ((int64_t)t * kv_heads + kvh) * hs;
+                double d = 0;
+                for (int i = 0; i < hs; i++) d += (double)orc_f16_to_f32(qv[i]) * (double)orc_f16_to_f32(kr[i]);
+                logit[t] = (float)d * scale;
+                if (logit[t] > mx) mx = logit[t];
+            }
+            double sum = 0;
+            for (int i = 0; i < hs; i++) acc[i] = 0;
+            for (int t = 0; t < n; t++) {
+                const double p = exp((double)logit[t] - (double)mx);
+                sum += p;
+                const uint16_t *vr = v[s] + ((int64_t)t * kv_heads + kvh) * hs;
+                for (int i = 0; i < hs; i++) acc[i] += p * (double)orc_f16_to_f32(vr[i]);
+            }
+            for (int i = 0; i < hs; i++) {
+                const float o = n > 0 ? (float)(acc[i] / sum) : 0.0f;
+                const int64_t at = ((int64_t)s * heads + h) * hs + i;
+                if (out) out[at] = orc_f32_to_f16(o);
+                if (out_f32) out_f32[at] = o;
+            }
+        }
+        free(logit);
+        free(acc);
+    }
+}
