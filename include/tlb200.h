@@ -1,0 +1,174 @@
+/* tlb200 -- C ABI of the B200-native executor for tensorlisp's Device::Native path.
+ *
+ * The reference reaches its native CUDA executor through Rust types
+ * (crates/tensorlisp/src/native_cuda.rs:28-168 over crates/kernels/src/cuda/exec.rs:20-240); there
+ * is no C ABI at that seam. This header is the seam restated as plain C so a Rust shim with the
+ * same eleven methods as native_cuda.rs can bind it (the stub is shown in INTEGRATION.md).
+ * Every entry point names the reference item it replaces.
+ *
+ * Conventions
+ *  - every function returns a tlb_status; TLB_OK is 0. No entry point aborts, throws or exits.
+ *  - tlb_last_error() returns the message of the last failing call on the calling thread.
+ *  - handles may be used from any thread; callers run one program at a time per device, as the
+ *    reference does under its per-model mutex (crates/tensorlisp/src/model.rs:96,802).
+ *  - the library never computes on the CPU: without a usable GPU, tlb_device_open fails with
+ *    TLB_NO_DEVICE and nothing else can be called.
+ */
+#ifndef TLB200_H
+#define TLB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* crates/kernels/src/lib.rs:43-60 (enum Error) */
+typedef enum tlb_status {
+    TLB_OK = 0,
+    TLB_NO_DEVICE = 1,   /* Error::NoDevice     */
+    TLB_COMPILE = 2,     /* Error::Compile      */
+    TLB_PIPELINE = 3,    /* Error::Pipeline     */
+    TLB_ALLOC = 4,       /* Error::Alloc        */
+    TLB_EXECUTION = 5,   /* Error::Execution    */
+    TLB_INVALID = 6,     /* Error::Invalid      */
+    TLB_UNSUPPORTED = 7  /* Error::Unsupported  */
+} tlb_status;
+
+typedef struct tlb_device tlb_device;
+typedef struct tlb_buffer tlb_buffer;
+typedef struct tlb_program tlb_program;
+
+/* ggml's enum ggml_type numbering (crates/kernels/src/graph.rs:12-27) */
+enum {
+    TLB_TYPE_F32 = 0, TLB_TYPE_F16 = 1, TLB_TYPE_Q4_0 = 2, TLB_TYPE_Q4_1 = 3, TLB_TYPE_Q5_0 = 6,
+    TLB_TYPE_Q5_1 = 7, TLB_TYPE_Q8_0 = 8, TLB_TYPE_Q2_K = 10, TLB_TYPE_Q3_K = 11, TLB_TYPE_Q4_K = 12,
+    TLB_TYPE_Q5_K = 13, TLB_TYPE_Q6_K = 14, TLB_TYPE_I8 = 24, TLB_TYPE_I16 = 25, TLB_TYPE_I32 = 26,
+    TLB_TYPE_I64 = 27, TLB_TYPE_BF16 = 30
+};
+
+/* crates/kernels/src/graph.rs:70-81 (enum Storage) */
+enum { TLB_STORAGE_WEIGHT = 0, TLB_STORAGE_STATE = 1, TLB_STORAGE_INPUT = 2, TLB_STORAGE_TEMP = 3 };
+
+/* crates/kernels/src/graph.rs:83-101 (struct Tensor); filled the way
+ * crates/tensorlisp/src/native_ir.rs:66-95 fills it from a ggml_tensor. */
+typedef struct tlb_tensor {
+    uint32_t ty;            /* ggml type id                                              */
+    int64_t  ne[4];         /* elements per dimension, innermost first                   */
+    uint64_t nb[4];         /* byte strides                                              */
+    char     op[32];        /* ggml op name ("MUL_MAT", "NONE" for leaves, ...)          */
+    int32_t  op_params[16]; /* copied verbatim from ggml                                 */
+    int32_t  src[10];       /* tensor ids, -1 = absent                                   */
+    int32_t  view_src;      /* root tensor this one aliases, -1 = none                   */
+    uint64_t view_offs;     /* byte offset into view_src                                 */
+    uint32_t storage_kind;  /* TLB_STORAGE_*; meaningful for roots                       */
+    uint32_t storage_index; /* weight / state / input index                              */
+    char     name[64];
+} tlb_tensor;
+
+/* crates/kernels/src/graph.rs:204-209 (struct Graph: tensors, nodes, keep) */
+typedef struct tlb_graph {
+    const tlb_tensor *tensors;
+    uint32_t          n_tensors;
+    const int32_t    *nodes;    /* execution order; view ops included (they launch nothing) */
+    uint32_t          n_nodes;
+    const int32_t    *keep;     /* outputs and taps: valid after the last node              */
+    uint32_t          n_keep;
+} tlb_graph;
+
+/* crates/kernels/src/plan.rs:42-47 (struct Leaves) */
+typedef struct tlb_leaves {
+    const uint32_t *weight_buffer; /* per weight: index into the buffers given to tlb_program_run */
+    const uint64_t *weight_offset; /* per weight: byte offset in that buffer (256-byte aligned)    */
+    uint32_t        n_weights;
+    const uint64_t *state_offset;  /* per state tensor: byte offset in the state block             */
+    uint32_t        n_states;
+} tlb_leaves;
+
+/* ------------------------------------------------------------------ device
+ * Device::system_default (crates/kernels/src/cuda/mod.rs:244-277): primary context of one GPU and
+ * one non-blocking stream. Fails with TLB_NO_DEVICE instead of aborting when there is no GPU. */
+tlb_status tlb_device_open(int ordinal, tlb_device **dev);
+void       tlb_device_close(tlb_device *dev);
+/* "native <gpu name>" -- Native::device_name (crates/tensorlisp/src/native_cuda.rs:124-126) */
+tlb_status tlb_device_name(tlb_device *dev, char *out, size_t n);
+/* Device::sync (cuda/mod.rs): waits for everything enqueued on the device's stream. */
+tlb_status tlb_device_sync(tlb_device *dev);
+/* The cudaStream_t every launch of this device goes to, so callers can record events on it
+ * (the reference keeps its stream private; cuda/mod.rs:258). */
+void      *tlb_device_stream(tlb_device *dev);
+int        tlb_device_sm_count(tlb_device *dev);
+const char *tlb_last_error(void);
+
+/* ------------------------------------------------------------------ buffers
+ * Weights: Native::load puts every tensor of the file into one allocation at 256-byte aligned
+ * offsets and copies each from host memory (native_cuda.rs:48-70). */
+tlb_status tlb_weights_create(tlb_device *dev, uint64_t total_bytes, tlb_buffer **w);
+/* State blocks: alloc_states / new_state_block (zeroed), fork_block, reset_block
+ * (native_cuda.rs:85-122). One block per session. */
+tlb_status tlb_state_create(tlb_device *dev, uint64_t bytes, tlb_buffer **s);
+tlb_status tlb_state_zero(tlb_buffer *s);
+tlb_status tlb_state_fork(tlb_buffer *src, tlb_buffer **copy);
+/* Buffer::write_at / read_range (cuda/mod.rs:79-120): bounds-checked blocking copies. */
+tlb_status tlb_buffer_write(tlb_buffer *b, uint64_t offset, const void *host, uint64_t n);
+tlb_status tlb_buffer_read(tlb_buffer *b, uint64_t offset, void *host, uint64_t n);
+uint64_t   tlb_buffer_size(tlb_buffer *b);
+void      *tlb_buffer_device_ptr(tlb_buffer *b);
+void       tlb_buffer_free(tlb_buffer *b);
+
+/* ------------------------------------------------------------------ programs
+ * Executor::compile (crates/kernels/src/cuda/exec.rs:27-62): plans every tensor into one arena
+ * (crates/kernels/src/plan.rs:56-189), lowers every node by ggml op name
+ * (crates/kernels/src/cuda/lower.rs:177-213) and records the launches. Every node is lowered before
+ * failing; the error then reads
+ *   "native CUDA: not implemented: OP xN (e.g. node: why); ..."        (exec.rs:48-58)
+ * View ops and tensors without elements launch nothing (lower.rs:179-181).
+ * `err` (may be NULL) receives the message as well. */
+tlb_status tlb_program_compile(tlb_device *dev, const tlb_graph *graph, const tlb_leaves *leaves,
+                               tlb_program **prog, char *err, size_t errlen);
+void       tlb_program_free(tlb_program *prog);
+/* Program::set_input (exec.rs:91-98): n must equal the input tensor's byte size, else
+ * "input i takes N bytes, got M". Blocking host-to-device copy into the program's io buffer. */
+tlb_status tlb_program_set_input(tlb_program *prog, uint32_t i, const void *bytes, uint64_t n);
+/* Program::run (exec.rs:186-225): enqueues every launch and waits. `weights` are the buffers the
+ * leaves' weight_buffer indices refer to; `state` may be NULL when the graph has no state. */
+tlb_status tlb_program_run(tlb_program *prog, tlb_buffer *const *weights, uint32_t n_weights, tlb_buffer *state);
+/* Program::run_n (exec.rs:176-183) without the final wait: enqueue only, for timing with events on
+ * tlb_device_stream. */
+tlb_status tlb_program_enqueue(tlb_program *prog, tlb_buffer *const *weights, uint32_t n_weights, tlb_buffer *state);
+/* Program::read (exec.rs:228-239): bytes of a tensor that lives in the arena or the io buffer. */
+tlb_status tlb_program_read(tlb_program *prog, uint32_t tensor_id, uint64_t bytes, void *out);
+/* Program::dispatch_count / labels (exec.rs:81-88) */
+uint32_t   tlb_program_dispatch_count(tlb_program *prog);
+const char *tlb_program_label(tlb_program *prog, uint32_t i);
+/* Device address and size of an input / kept tensor, so a caller that already has data in HBM can
+ * write inputs and read results without the host (no counterpart: the reference only has the
+ * blocking host copies). Returns NULL for tensors outside the io buffer and the arena. */
+void      *tlb_program_tensor_ptr(tlb_program *prog, uint32_t tensor_id, uint64_t *bytes);
+/* Layout figures of the plan (plan.rs Layout: arena_size, io_size). */
+uint64_t   tlb_program_arena_bytes(tlb_program *prog);
+
+/* ------------------------------------------------------------------ quantizers
+ * DType::from_f32 (crates/tensorlisp/src/dtype.rs:98-124) -> ggml_quantize_chunk: f32 rows to
+ * Q8_0 / Q4_0 / Q4_K blocks (also F16), bit-exact with the reference's build. Host pointers; the
+ * rows are quantized on the GPU. n_per_row must be a multiple of the block size (32 / 256). */
+tlb_status tlb_quantize_rows(tlb_device *dev, uint32_t type, const float *src, int64_t rows, int64_t n_per_row, void *out);
+/* Same on device-resident data (src and out are device pointers), enqueued on the device stream. */
+tlb_status tlb_quantize_rows_device(tlb_device *dev, uint32_t type, const void *src, int64_t rows, int64_t n_per_row, void *out);
+/* Type table of crates/kernels/src/graph.rs:30-50: bytes of a row of ne0 elements, 0 if unknown. */
+uint64_t   tlb_row_size(uint32_t type, int64_t ne0);
+
+/* ------------------------------------------------------------------ tensor parallelism
+ * No counterpart in the reference (single device: model.rs:415-422). A communicator joins the
+ * ranks of one box; programs compiled on a device with a communicator may contain the pseudo-op
+ * "ALLREDUCE" (sum over ranks of an f32 tensor, in place of its source), which the sharding pass
+ * inserts after each row-parallel MUL_MAT. */
+tlb_status tlb_comm_unique_id(void *out128);
+tlb_status tlb_comm_init(tlb_device *dev, int n_ranks, int rank, const void *id128);
+tlb_status tlb_comm_destroy(tlb_device *dev);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TLB200_H */

@@ -1,0 +1,700 @@
+// C ABI of include/tlb200.h: device, buffers, graph IR, arena planner and program replay.
+// Reference counterparts: crates/kernels/src/cuda/mod.rs (Device/Buffer), graph.rs (IR),
+// plan.rs (planner), cuda/exec.rs (Executor::compile, Program::run/read).
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <mutex>
+
+#include "kernels.h"
+#include "tlb_internal.h"
+
+namespace tlb {
+
+static thread_local std::string g_last_error;
+void set_error(const std::string &msg) { g_last_error = msg; }
+tlb_status fail(tlb_status st, const std::string &msg) {
+    g_last_error = msg;
+    return st;
+}
+std::string cuda_msg(cudaError_t e) { return std::string(cudaGetErrorName(e)) + ": " + cudaGetErrorString(e); }
+
+// ---------------------------------------------------------------------------- type table
+// crates/kernels/src/graph.rs:30-50
+const TypeTraits *type_traits(uint32_t ty) {
+    static const TypeTraits f32{"f32", 1, 4}, f16{"f16", 1, 2}, q4_0{"q4_0", 32, 18}, q4_1{"q4_1", 32, 20},
+        q5_0{"q5_0", 32, 22}, q5_1{"q5_1", 32, 24}, q8_0{"q8_0", 32, 34}, q2_K{"q2_K", 256, 84}, q3_K{"q3_K", 256, 110},
+        q4_K{"q4_K", 256, 144}, q5_K{"q5_K", 256, 176}, q6_K{"q6_K", 256, 210}, i8{"i8", 1, 1}, i16{"i16", 1, 2},
+        i32{"i32", 1, 4}, i64{"i64", 1, 8}, bf16{"bf16", 1, 2};
+    switch (ty) {
+        case 0: return &f32;
+        case 1: return &f16;
+        case 2: return &q4_0;
+        case 3: return &q4_1;
+        case 6: return &q5_0;
+        case 7: return &q5_1;
+        case 8: return &q8_0;
+        case 10: return &q2_K;
+        case 11: return &q3_K;
+        case 12: return &q4_K;
+        case 13: return &q5_K;
+        case 14: return &q6_K;
+        case 24: return &i8;
+        case 25: return &i16;
+        case 26: return &i32;
+        case 27: return &i64;
+        case 30: return &bf16;
+        default: return nullptr;
+    }
+}
+
+// ggml_nbytes (graph.rs:112-129)
+uint64_t Tensor::nbytes() const {
+    if (opaque_bytes) return opaque_bytes;
+    for (int i = 0; i < 4; i++)
+        if (ne[i] == 0) return 0;
+    const TypeTraits *tr = type_traits(ty);
+    if (!tr) return 0;
+    uint64_t n;
+    if (tr->blck == 1) {
+        n = tr->size + (uint64_t)(ne[0] - 1) * nb[0];
+    } else {
+        n = (uint64_t)ne[0] * nb[0] / (uint64_t)tr->blck;
+    }
+    for (int i = 1; i < 4; i++) n += (uint64_t)(ne[i] - 1) * nb[i];
+    return n;
+}
+uint64_t Tensor::row_size() const {
+    const TypeTraits *tr = type_traits(ty);
+    return tr ? tr->size * (uint64_t)ne[0] / (uint64_t)tr->blck : 0;
+}
+bool Tensor::is_contiguous_rows() const {
+    const TypeTraits *tr = type_traits(ty);
+    return tr && nb[0] == tr->size;
+}
+// ggml_is_contiguous_n (graph.rs:147-171)
+bool Tensor::is_contiguous_n(int n) const {
+    for (int i = 0; i < 4; i++)
+        if (ne[i] == 0) return true;
+    const TypeTraits *tr = type_traits(ty);
+    if (!tr) return false;
+    if (ne[0] != tr->blck && nb[0] != tr->size) return false;
+    uint64_t next = tr->size * (uint64_t)ne[0] / (uint64_t)tr->blck;
+    for (int i = 1; i < 4; i++) {
+        if (ne[i] != 1) {
+            if (i > n) {
+                if (nb[i] != next) return false;
+                next *= (uint64_t)ne[i];
+            } else {
+                next = (uint64_t)ne[i] * nb[i];
+            }
+        }
+    }
+    return true;
+}
+
+// ---------------------------------------------------------------------------- planner
+// crates/kernels/src/plan.rs:56-189: liveness of arena roots in node positions, first-fit by start
+// time over the lowest free offset, one short-lived scratch block per node that asks for one,
+// inputs in their own io buffer, views resolved through their root.
+Layout plan(const Graph &g, const Leaves &leaves, const std::function<uint64_t(int32_t)> &scratch_bytes) {
+    const size_t n = g.nodes.size(), nt = g.tensors.size();
+    std::vector<size_t> first(nt, SIZE_MAX), last(nt, 0);
+    auto touch = [&](int32_t root, size_t pos) {
+        first[root] = std::min(first[root], pos);
+        last[root] = std::max(last[root], pos);
+    };
+    for (size_t pos = 0; pos < n; pos++) {
+        const Tensor &t = g.tensors[g.nodes[pos]];
+        touch(g.root(g.nodes[pos]), pos);
+        for (int s : t.src)
+            if (s >= 0) touch(g.root(s), pos);
+    }
+    for (int32_t id : g.keep) last[g.root(id)] = n;
+
+    struct Block {
+        int32_t id;
+        size_t first, last;
+        uint64_t size;
+        bool scratch;
+        size_t pos;
+    };
+    std::vector<Block> blocks;
+    for (size_t id = 0; id < nt; id++) {
+        const Tensor &t = g.tensors[id];
+        if (t.view_src < 0 && t.storage_kind == TEMP && first[id] != SIZE_MAX)
+            blocks.push_back({(int32_t)id, first[id], last[id], align_up(std::max<uint64_t>(t.nbytes(), 1)), false, 0});
+    }
+    for (size_t pos = 0; pos < n; pos++) {
+        const uint64_t bytes = scratch_bytes(g.nodes[pos]);
+        if (bytes > 0) blocks.push_back({g.nodes[pos], pos, pos, align_up(bytes), true, pos});
+    }
+    std::stable_sort(blocks.begin(), blocks.end(), [](const Block &a, const Block &b) {
+        if (a.first != b.first) return a.first < b.first;
+        return a.scratch < b.scratch;
+    });
+
+    struct Live {
+        uint64_t off, size;
+        size_t last;
+    };
+    std::vector<Live> live;
+    Layout L;
+    std::vector<uint64_t> offsets(nt, 0);
+    L.scratch.assign(n, -1);
+    for (const Block &b : blocks) {
+        live.erase(std::remove_if(live.begin(), live.end(), [&](const Live &l) { return l.last < b.first; }), live.end());
+        std::sort(live.begin(), live.end(), [](const Live &x, const Live &y) { return x.off < y.off; });
+        uint64_t off = 0;
+        for (const Live &l : live) {
+            if (l.off >= off + b.size) break;
+            off = std::max(off, l.off + l.size);
+        }
+        live.push_back({off, b.size, b.last});
+        L.arena_size = std::max(L.arena_size, off + b.size);
+        if (b.scratch) L.scratch[b.pos] = (int64_t)off;
+        else offsets[b.id] = off;
+    }
+
+    for (const Tensor &t : g.tensors) {
+        if (t.view_src < 0 && t.storage_kind == INPUT) {
+            if (L.inputs.size() <= t.storage_index) L.inputs.resize(t.storage_index + 1, {0, 0});
+        }
+    }
+    // io offsets in input-index order so set_input(i) is independent of tensor order
+    std::vector<uint64_t> in_bytes(L.inputs.size(), 0);
+    for (const Tensor &t : g.tensors)
+        if (t.view_src < 0 && t.storage_kind == INPUT) in_bytes[t.storage_index] = t.nbytes();
+    for (size_t i = 0; i < L.inputs.size(); i++) {
+        L.inputs[i] = {L.io_size, in_bytes[i]};
+        L.io_size += align_up(std::max<uint64_t>(in_bytes[i], 1));
+    }
+
+    L.place.resize(nt);
+    for (size_t id = 0; id < nt; id++) {
+        uint64_t extra = 0;
+        const int32_t root = g.root((int32_t)id, &extra);
+        const Tensor &t = g.tensors[root];
+        Place p;
+        switch (t.storage_kind) {
+            case WEIGHT:
+                p.buf = BUF_WEIGHTS;
+                p.index = leaves.weights[t.storage_index].first;
+                p.off = leaves.weights[t.storage_index].second;
+                break;
+            case STATE:
+                p.buf = BUF_STATE;
+                p.off = leaves.states[t.storage_index];
+                break;
+            case INPUT:
+                p.buf = BUF_IO;
+                p.off = L.inputs[t.storage_index].first;
+                break;
+            default:
+                p.buf = BUF_ARENA;
+                p.off = offsets[root];
+        }
+        p.off += extra;
+        L.place[id] = p;
+    }
+    return L;
+}
+
+static std::once_flag g_configure_once;
+
+}  // namespace tlb
+
+using namespace tlb;
+
+#define TLB_TRY_CUDA(expr, st)                                          \
+    do {                                                                \
+        cudaError_t e__ = (expr);                                       \
+        if (e__ != cudaSuccess) return fail(st, std::string(#expr) + " failed: " + cuda_msg(e__)); \
+    } while (0)
+
+extern "C" {
+
+const char *tlb_last_error(void) { return g_last_error.c_str(); }
+
+uint64_t tlb_row_size(uint32_t type, int64_t ne0) {
+    const TypeTraits *tr = type_traits(type);
+    if (!tr || ne0 < 0 || ne0 % tr->blck != 0) return 0;
+    return tr->size * (uint64_t)ne0 / (uint64_t)tr->blck;
+}
+
+// ------------------------------------------------------------------ device
+tlb_status tlb_device_open(int ordinal, tlb_device **dev) {
+    if (!dev) return fail(TLB_INVALID, "tlb_device_open: null output");
+    *dev = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        return fail(TLB_NO_DEVICE, "no GPU device available");
+    }
+    if (ordinal < 0 || ordinal >= count) return fail(TLB_NO_DEVICE, "no GPU device with ordinal " + std::to_string(ordinal));
+    TLB_TRY_CUDA(cudaSetDevice(ordinal), TLB_NO_DEVICE);
+    tlb_device *d = new tlb_device;
+    d->ordinal = ordinal;
+    e = cudaGetDeviceProperties(&d->prop, ordinal);
+    if (e != cudaSuccess) {
+        delete d;
+        return fail(TLB_NO_DEVICE, "cudaGetDeviceProperties: " + cuda_msg(e));
+    }
+    if (d->prop.major != 10) {
+        const std::string m = "this library is built for sm_100a only; device " + std::string(d->prop.name) + " is sm_" +
+                              std::to_string(d->prop.major) + std::to_string(d->prop.minor);
+        delete d;
+        return fail(TLB_NO_DEVICE, m);
+    }
+    e = cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) {
+        delete d;
+        return fail(TLB_NO_DEVICE, "cudaStreamCreate: " + cuda_msg(e));
+    }
+    d->name = std::string("native ") + d->prop.name;
+    std::call_once(g_configure_once, [] {
+        gemv_configure();
+        attn_configure();
+    });
+    *dev = d;
+    return TLB_OK;
+}
+
+void tlb_device_close(tlb_device *dev) {
+    if (!dev) return;
+    tlb_comm_destroy(dev);
+    cudaSetDevice(dev->ordinal);
+    if (dev->stream) cudaStreamDestroy(dev->stream);
+    delete dev;
+}
+
+tlb_status tlb_device_name(tlb_device *dev, char *out, size_t n) {
+    if (!dev || !out || n == 0) return fail(TLB_INVALID, "tlb_device_name: bad arguments");
+    snprintf(out, n, "%s", dev->name.c_str());
+    return TLB_OK;
+}
+
+tlb_status tlb_device_sync(tlb_device *dev) {
+    if (!dev) return fail(TLB_INVALID, "null device");
+    cudaSetDevice(dev->ordinal);
+    TLB_TRY_CUDA(cudaStreamSynchronize(dev->stream), TLB_EXECUTION);
+    return TLB_OK;
+}
+
+void *tlb_device_stream(tlb_device *dev) { return dev ? (void *)dev->stream : nullptr; }
+int tlb_device_sm_count(tlb_device *dev) { return dev ? dev->prop.multiProcessorCount : 0; }
+
+// ------------------------------------------------------------------ buffers
+static tlb_status buffer_create(tlb_device *dev, uint64_t bytes, bool zero, tlb_buffer **out) {
+    if (!dev || !out) return fail(TLB_INVALID, "buffer create: bad arguments");
+    *out = nullptr;
+    cudaSetDevice(dev->ordinal);
+    void *p = nullptr;
+    const uint64_t n = std::max<uint64_t>(bytes, 1);
+    cudaError_t e = cudaMalloc(&p, n);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(TLB_ALLOC, "buffer allocation of " + std::to_string(n) + " bytes failed");
+    }
+    if (zero) {
+        e = cudaMemsetAsync(p, 0, n, dev->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(dev->stream);
+        if (e != cudaSuccess) {
+            cudaFree(p);
+            return fail(TLB_EXECUTION, "zeroing a buffer failed: " + cuda_msg(e));
+        }
+    }
+    tlb_buffer *b = new tlb_buffer;
+    b->dev = dev;
+    b->ptr = p;
+    b->size = n;
+    *out = b;
+    return TLB_OK;
+}
+
+tlb_status tlb_weights_create(tlb_device *dev, uint64_t total_bytes, tlb_buffer **w) { return buffer_create(dev, total_bytes, false, w); }
+tlb_status tlb_state_create(tlb_device *dev, uint64_t bytes, tlb_buffer **s) { return buffer_create(dev, bytes, true, s); }
+
+tlb_status tlb_state_zero(tlb_buffer *s) {
+    if (!s) return fail(TLB_INVALID, "null buffer");
+    cudaSetDevice(s->dev->ordinal);
+    TLB_TRY_CUDA(cudaMemsetAsync(s->ptr, 0, s->size, s->dev->stream), TLB_EXECUTION);
+    TLB_TRY_CUDA(cudaStreamSynchronize(s->dev->stream), TLB_EXECUTION);
+    return TLB_OK;
+}
+
+tlb_status tlb_state_fork(tlb_buffer *src, tlb_buffer **copy) {
+    if (!src || !copy) return fail(TLB_INVALID, "tlb_state_fork: bad arguments");
+    tlb_status st = buffer_create(src->dev, src->size, false, copy);
+    if (st != TLB_OK) return st;
+    cudaError_t e = cudaMemcpyAsync((*copy)->ptr, src->ptr, src->size, cudaMemcpyDeviceToDevice, src->dev->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(src->dev->stream);
+    if (e != cudaSuccess) {
+        tlb_buffer_free(*copy);
+        *copy = nullptr;
+        return fail(TLB_EXECUTION, "copying a state block failed: " + cuda_msg(e));
+    }
+    return TLB_OK;
+}
+
+tlb_status tlb_buffer_write(tlb_buffer *b, uint64_t offset, const void *host, uint64_t n) {
+    if (!b || (!host && n)) return fail(TLB_INVALID, "tlb_buffer_write: bad arguments");
+    if (offset > b->size || n > b->size - offset)
+        return fail(TLB_INVALID, "write of " + std::to_string(n) + " bytes at " + std::to_string(offset) + " past a buffer of " + std::to_string(b->size));
+    if (n == 0) return TLB_OK;
+    cudaSetDevice(b->dev->ordinal);
+    TLB_TRY_CUDA(cudaMemcpyAsync((char *)b->ptr + offset, host, n, cudaMemcpyHostToDevice, b->dev->stream), TLB_EXECUTION);
+    TLB_TRY_CUDA(cudaStreamSynchronize(b->dev->stream), TLB_EXECUTION);
+    return TLB_OK;
+}
+
+tlb_status tlb_buffer_read(tlb_buffer *b, uint64_t offset, void *host, uint64_t n) {
+    if (!b || (!host && n)) return fail(TLB_INVALID, "tlb_buffer_read: bad arguments");
+    if (offset > b->size || n > b->size - offset)
+        return fail(TLB_INVALID, "read of " + std::to_string(n) + " bytes at " + std::to_string(offset) + " past a buffer of " + std::to_string(b->size));
+    if (n == 0) return TLB_OK;
+    cudaSetDevice(b->dev->ordinal);
+    TLB_TRY_CUDA(cudaMemcpyAsync(host, (char *)b->ptr + offset, n, cudaMemcpyDeviceToHost, b->dev->stream), TLB_EXECUTION);
+    TLB_TRY_CUDA(cudaStreamSynchronize(b->dev->stream), TLB_EXECUTION);
+    return TLB_OK;
+}
+
+uint64_t tlb_buffer_size(tlb_buffer *b) { return b ? b->size : 0; }
+void *tlb_buffer_device_ptr(tlb_buffer *b) { return b ? b->ptr : nullptr; }
+void tlb_buffer_free(tlb_buffer *b) {
+    if (!b) return;
+    cudaSetDevice(b->dev->ordinal);
+    cudaFree(b->ptr);
+    delete b;
+}
+
+// ------------------------------------------------------------------ programs
+static void copy_err(const std::string &m, char *err, size_t errlen) {
+    if (err && errlen) snprintf(err, errlen, "%s", m.c_str());
+}
+
+tlb_status tlb_program_compile(tlb_device *dev, const tlb_graph *graph, const tlb_leaves *leaves, tlb_program **prog,
+                               char *err, size_t errlen) {
+    if (err && errlen) err[0] = 0;
+    auto bad = [&](tlb_status st, const std::string &m) {
+        copy_err(m, err, errlen);
+        return fail(st, m);
+    };
+    if (!dev || !graph || !prog) return bad(TLB_INVALID, "tlb_program_compile: bad arguments");
+    *prog = nullptr;
+    // ---- copy and validate the IR
+    Graph g;
+    g.tensors.resize(graph->n_tensors);
+    const int32_t nt = (int32_t)graph->n_tensors;
+    for (int32_t i = 0; i < nt; i++) {
+        const tlb_tensor &s = graph->tensors[i];
+        Tensor &t = g.tensors[i];
+        t.ty = s.ty;
+        for (int k = 0; k < 4; k++) {
+            t.ne[k] = s.ne[k];
+            t.nb[k] = s.nb[k];
+            if (s.ne[k] < 0) return bad(TLB_INVALID, "tensor " + std::to_string(i) + " has a negative dimension");
+        }
+        t.op.assign(s.op, strnlen(s.op, sizeof(s.op)));
+        std::memcpy(t.op_params, s.op_params, sizeof(t.op_params));
+        for (int k = 0; k < 10; k++) {
+            t.src[k] = s.src[k];
+            if (s.src[k] >= nt || s.src[k] < -1) return bad(TLB_INVALID, "tensor " + std::to_string(i) + " has a source out of range");
+        }
+        t.view_src = s.view_src;
+        if (s.view_src >= nt || s.view_src < -1) return bad(TLB_INVALID, "tensor " + std::to_string(i) + " has a view source out of range");
+        t.view_offs = s.view_offs;
+        t.storage_kind = s.storage_kind;
+        t.storage_index = s.storage_index;
+        t.name.assign(s.name, strnlen(s.name, sizeof(s.name)));
+        if (!type_traits(t.ty)) return bad(TLB_INVALID, "tensor `" + t.name + "` has unknown ggml type " + std::to_string(t.ty));
+        if (t.storage_kind > TEMP) return bad(TLB_INVALID, "tensor `" + t.name + "` has an unknown storage kind");
+    }
+    for (int32_t i = 0; i < nt; i++) {
+        const Tensor &t = g.tensors[i];
+        if (t.view_src >= 0 && g.tensors[t.view_src].view_src >= 0)
+            return bad(TLB_INVALID, "tensor `" + t.name + "`: view_src must be a root");
+        if (t.view_src < 0) {
+            if (t.storage_kind == WEIGHT && (!leaves || t.storage_index >= leaves->n_weights))
+                return bad(TLB_INVALID, "tensor `" + t.name + "` names weight " + std::to_string(t.storage_index) + ", which the leaves do not have");
+            if (t.storage_kind == STATE && (!leaves || t.storage_index >= leaves->n_states))
+                return bad(TLB_INVALID, "tensor `" + t.name + "` names state " + std::to_string(t.storage_index) + ", which the leaves do not have");
+        }
+    }
+    for (uint32_t i = 0; i < graph->n_nodes; i++) {
+        if (graph->nodes[i] < 0 || graph->nodes[i] >= nt) return bad(TLB_INVALID, "node id out of range");
+        g.nodes.push_back(graph->nodes[i]);
+    }
+    for (uint32_t i = 0; i < graph->n_keep; i++) {
+        if (graph->keep[i] < 0 || graph->keep[i] >= nt) return bad(TLB_INVALID, "kept tensor id out of range");
+        g.keep.push_back(graph->keep[i]);
+    }
+    Leaves lv;
+    if (leaves) {
+        for (uint32_t i = 0; i < leaves->n_weights; i++) lv.weights.push_back({leaves->weight_buffer[i], leaves->weight_offset[i]});
+        for (uint32_t i = 0; i < leaves->n_states; i++) lv.states.push_back(leaves->state_offset[i]);
+    }
+
+    tlb_program *p = new tlb_program;
+    p->dev = dev;
+    p->n_user_tensors = graph->n_tensors;
+    p->graph = std::move(g);
+    if (!getenv("TL_NATIVE_NOFUSE") || std::string(getenv("TL_NATIVE_NOFUSE")) != "1") rewrite_graph(p->graph);
+    const int sm = dev->prop.multiProcessorCount;
+    const Graph &G = p->graph;
+    p->layout = plan(G, lv, [&](int32_t id) { return node_scratch_bytes(G, id, sm); });
+
+    // ---- lower every node before failing, so one compile reports every missing op (exec.rs:39-58)
+    struct Missing {
+        std::string op;
+        int count;
+        std::string detail;
+    };
+    std::vector<Missing> missing;
+    LowerCtx lc{dev, &p->graph, &p->layout};
+    for (size_t pos = 0; pos < G.nodes.size(); pos++) {
+        try {
+            lower_node(lc, G.nodes[pos], (int)pos, p->dispatches);
+        } catch (const Unsupported &u) {
+            bool found = false;
+            for (Missing &m : missing)
+                if (m.op == u.op) {
+                    m.count++;
+                    found = true;
+                }
+            if (!found) missing.push_back({u.op, 1, u.node + ": " + u.why});
+        } catch (const std::string &m) {
+            delete p;
+            return bad(TLB_INVALID, m);
+        }
+    }
+    if (!missing.empty()) {
+        std::string m = "native CUDA: not implemented: ";
+        for (size_t i = 0; i < missing.size(); i++) {
+            if (i) m += "; ";
+            m += missing[i].op + " x" + std::to_string(missing[i].count) + " (e.g. " + missing[i].detail + ")";
+        }
+        delete p;
+        return bad(TLB_UNSUPPORTED, m);
+    }
+    cudaSetDevice(dev->ordinal);
+    cudaError_t e = cudaMalloc(&p->arena, std::max<uint64_t>(p->layout.arena_size, 1) + 256);
+    if (e == cudaSuccess) e = cudaMalloc(&p->io, std::max<uint64_t>(p->layout.io_size, 1));
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        const uint64_t want = p->layout.arena_size + p->layout.io_size;
+        tlb_program_free(p);
+        return bad(TLB_ALLOC, "buffer allocation of " + std::to_string(want) + " bytes failed");
+    }
+    // the last 256 bytes of the arena allocation hold the device error word of bounded waits
+    cudaMemsetAsync((char *)p->arena + std::max<uint64_t>(p->layout.arena_size, 1), 0, 256, dev->stream);
+    cudaStreamSynchronize(dev->stream);
+    const char *ng = getenv("TLB_NO_CUDA_GRAPH");
+    p->use_graph = !(ng && ng[0] == '1');
+    *prog = p;
+    return TLB_OK;
+}
+
+void tlb_program_free(tlb_program *prog) {
+    if (!prog) return;
+    cudaSetDevice(prog->dev->ordinal);
+    for (auto &c : prog->captured)
+        if (c.exec) cudaGraphExecDestroy(c.exec);
+    if (prog->arena) cudaFree(prog->arena);
+    if (prog->io) cudaFree(prog->io);
+    delete prog;
+}
+
+tlb_status tlb_program_set_input(tlb_program *prog, uint32_t i, const void *bytes, uint64_t n) {
+    if (!prog) return fail(TLB_INVALID, "null program");
+    if (i >= prog->layout.inputs.size()) return fail(TLB_INVALID, "no graph input " + std::to_string(i));
+    const auto in = prog->layout.inputs[i];
+    if (n != in.second) return fail(TLB_INVALID, "input " + std::to_string(i) + " takes " + std::to_string(in.second) + " bytes, got " + std::to_string(n));
+    if (n == 0) return TLB_OK;
+    if (!bytes) return fail(TLB_INVALID, "null input data");
+    cudaSetDevice(prog->dev->ordinal);
+    TLB_TRY_CUDA(cudaMemcpyAsync((char *)prog->io + in.first, bytes, n, cudaMemcpyHostToDevice, prog->dev->stream), TLB_EXECUTION);
+    TLB_TRY_CUDA(cudaStreamSynchronize(prog->dev->stream), TLB_EXECUTION);
+    return TLB_OK;
+}
+
+static tlb_status make_ctx(tlb_program *prog, tlb_buffer *const *weights, uint32_t n_weights, tlb_buffer *state, RunCtx &rc) {
+    uint32_t need_w = 0;
+    bool need_state = false;
+    for (const Place &pl : prog->layout.place) {
+        if (pl.buf == BUF_WEIGHTS) need_w = std::max(need_w, pl.index + 1);
+        if (pl.buf == BUF_STATE) need_state = true;
+    }
+    if (need_w > n_weights) return fail(TLB_INVALID, "the program reads weight buffer " + std::to_string(need_w - 1) + " but only " + std::to_string(n_weights) + " were given");
+    if (need_state && !state) return fail(TLB_INVALID, "the program reads state tensors but no state block was given");
+    for (uint32_t i = 0; i < n_weights; i++) {
+        if (!weights[i]) return fail(TLB_INVALID, "null weight buffer");
+        rc.weights.push_back((char *)weights[i]->ptr);
+    }
+    rc.state = state ? (char *)state->ptr : nullptr;
+    rc.io = (char *)prog->io;
+    rc.arena = (char *)prog->arena;
+    rc.stream = prog->dev->stream;
+    rc.dev = prog->dev;
+    rc.err = (int *)((char *)prog->arena + std::max<uint64_t>(prog->layout.arena_size, 1));
+    return TLB_OK;
+}
+
+static tlb_status launch_all(tlb_program *prog, const RunCtx &rc, bool profile) {
+    for (const Dispatch &d : prog->dispatches) {
+        cudaError_t e = d.fn(rc);
+        if (e == cudaSuccess && profile) e = cudaStreamSynchronize(rc.stream);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return fail(TLB_EXECUTION, "launching `" + d.label + "`: " + cuda_msg(e));
+        }
+    }
+    return TLB_OK;
+}
+
+tlb_status tlb_program_enqueue(tlb_program *prog, tlb_buffer *const *weights, uint32_t n_weights, tlb_buffer *state) {
+    if (!prog) return fail(TLB_INVALID, "null program");
+    cudaSetDevice(prog->dev->ordinal);
+    RunCtx rc;
+    tlb_status st = make_ctx(prog, weights, n_weights, state, rc);
+    if (st != TLB_OK) return st;
+    const bool profile = getenv("TL_NATIVE_PROFILE") != nullptr;
+    if (!prog->use_graph || profile || prog->dispatches.size() < 2) return launch_all(prog, rc, profile);
+    // replay a captured CUDA graph, one per set of buffer addresses (sessions switch state blocks)
+    std::vector<void *> key;
+    for (char *w : rc.weights) key.push_back(w);
+    key.push_back(rc.state);
+    for (auto &c : prog->captured)
+        if (c.key == key) {
+            TLB_TRY_CUDA(cudaGraphLaunch(c.exec, rc.stream), TLB_EXECUTION);
+            return TLB_OK;
+        }
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamBeginCapture(rc.stream, cudaStreamCaptureModeThreadLocal);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return launch_all(prog, rc, false);
+    }
+    st = launch_all(prog, rc, false);
+    e = cudaStreamEndCapture(rc.stream, &graph);
+    if (st != TLB_OK || e != cudaSuccess || !graph) {
+        cudaGetLastError();
+        if (graph) cudaGraphDestroy(graph);
+        if (st != TLB_OK) return st;
+        prog->use_graph = false;
+        return launch_all(prog, rc, false);
+    }
+    cudaGraphExec_t exec = nullptr;
+    e = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        prog->use_graph = false;
+        return launch_all(prog, rc, false);
+    }
+    if (prog->captured.size() >= 8) {
+        cudaGraphExecDestroy(prog->captured.front().exec);
+        prog->captured.erase(prog->captured.begin());
+    }
+    prog->captured.push_back({key, exec});
+    TLB_TRY_CUDA(cudaGraphLaunch(exec, rc.stream), TLB_EXECUTION);
+    return TLB_OK;
+}
+
+tlb_status tlb_program_run(tlb_program *prog, tlb_buffer *const *weights, uint32_t n_weights, tlb_buffer *state) {
+    tlb_status st = tlb_program_enqueue(prog, weights, n_weights, state);
+    if (st != TLB_OK) return st;
+    cudaError_t e = cudaStreamSynchronize(prog->dev->stream);
+    if (e != cudaSuccess)
+        return fail(TLB_EXECUTION, cuda_msg(e) + " (graph of " + std::to_string(prog->dispatches.size()) + " dispatches)");
+    // bounded waits inside kernels report through the error word behind the arena
+    int flag = 0;
+    e = cudaMemcpy(&flag, (char *)prog->arena + std::max<uint64_t>(prog->layout.arena_size, 1), 4, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail(TLB_EXECUTION, cuda_msg(e));
+    if (flag != 0) {
+        cudaMemset((char *)prog->arena + std::max<uint64_t>(prog->layout.arena_size, 1), 0, 4);
+        return fail(TLB_EXECUTION, "a kernel gave up waiting for its own copies (device error word " + std::to_string(flag) + ")");
+    }
+    return TLB_OK;
+}
+
+tlb_status tlb_program_read(tlb_program *prog, uint32_t tensor_id, uint64_t bytes, void *out) {
+    if (!prog || (!out && bytes)) return fail(TLB_INVALID, "tlb_program_read: bad arguments");
+    if (tensor_id >= prog->n_user_tensors) return fail(TLB_INVALID, "no tensor " + std::to_string(tensor_id));
+    const Place pl = prog->layout.place[tensor_id];
+    char *base;
+    uint64_t size;
+    if (pl.buf == BUF_ARENA) {
+        base = (char *)prog->arena;
+        size = prog->layout.arena_size;
+    } else if (pl.buf == BUF_IO) {
+        base = (char *)prog->io;
+        size = prog->layout.io_size;
+    } else {
+        return fail(TLB_INVALID, "tensor " + std::to_string(tensor_id) + " lives in " + (pl.buf == BUF_STATE ? "State" : "Weights") + ", which Program cannot read");
+    }
+    if (pl.off + bytes > size) return fail(TLB_INVALID, "tensor " + std::to_string(tensor_id) + " reads past its buffer");
+    if (bytes == 0) return TLB_OK;
+    cudaSetDevice(prog->dev->ordinal);
+    TLB_TRY_CUDA(cudaMemcpyAsync(out, base + pl.off, bytes, cudaMemcpyDeviceToHost, prog->dev->stream), TLB_EXECUTION);
+    TLB_TRY_CUDA(cudaStreamSynchronize(prog->dev->stream), TLB_EXECUTION);
+    return TLB_OK;
+}
+
+uint32_t tlb_program_dispatch_count(tlb_program *prog) { return prog ? (uint32_t)prog->dispatches.size() : 0; }
+const char *tlb_program_label(tlb_program *prog, uint32_t i) {
+    return prog && i < prog->dispatches.size() ? prog->dispatches[i].label.c_str() : "";
+}
+uint64_t tlb_program_arena_bytes(tlb_program *prog) { return prog ? prog->layout.arena_size : 0; }
+
+void *tlb_program_tensor_ptr(tlb_program *prog, uint32_t tensor_id, uint64_t *bytes) {
+    if (!prog || tensor_id >= prog->n_user_tensors) return nullptr;
+    const Place pl = prog->layout.place[tensor_id];
+    if (bytes) *bytes = prog->graph.tensors[tensor_id].nbytes();
+    if (pl.buf == BUF_ARENA) return (char *)prog->arena + pl.off;
+    if (pl.buf == BUF_IO) return (char *)prog->io + pl.off;
+    return nullptr;
+}
+
+// ------------------------------------------------------------------ quantizers
+tlb_status tlb_quantize_rows_device(tlb_device *dev, uint32_t type, const void *src, int64_t rows, int64_t n_per_row, void *out) {
+    if (!dev) return fail(TLB_INVALID, "null device");
+    const TypeTraits *tr = type_traits(type);
+    if (!tr || !(type == TLB_TYPE_Q8_0 || type == TLB_TYPE_Q4_0 || type == TLB_TYPE_Q4_K || type == TLB_TYPE_F16))
+        return fail(TLB_UNSUPPORTED, std::string("quantizing to ggml type ") + (tr ? tr->name : "?") + " is not implemented");
+    if (rows < 0 || n_per_row < 0 || n_per_row % tr->blck != 0)
+        return fail(TLB_INVALID, "row length " + std::to_string(n_per_row) + " is not a multiple of the block size " + std::to_string(tr->blck));
+    cudaSetDevice(dev->ordinal);
+    TLB_TRY_CUDA(launch_quantize_rows(type, (const float *)src, rows, n_per_row, out, dev->stream), TLB_EXECUTION);
+    return TLB_OK;
+}
+
+tlb_status tlb_quantize_rows(tlb_device *dev, uint32_t type, const float *src, int64_t rows, int64_t n_per_row, void *out) {
+    if (!dev || (!src && rows * n_per_row) || (!out && rows * n_per_row)) return fail(TLB_INVALID, "tlb_quantize_rows: bad arguments");
+    const uint64_t rs = tlb_row_size(type, n_per_row);
+    if (rows * n_per_row == 0) return tlb_quantize_rows_device(dev, type, nullptr, rows, n_per_row, nullptr);
+    if (rs == 0) return tlb_quantize_rows_device(dev, type, nullptr, rows, n_per_row, nullptr);  // reports the reason
+    cudaSetDevice(dev->ordinal);
+    const uint64_t in_bytes = (uint64_t)rows * n_per_row * 4, out_bytes = (uint64_t)rows * rs;
+    void *din = nullptr, *dout = nullptr;
+    if (cudaMalloc(&din, in_bytes) != cudaSuccess || cudaMalloc(&dout, out_bytes) != cudaSuccess) {
+        cudaGetLastError();
+        if (din) cudaFree(din);
+        return fail(TLB_ALLOC, "buffer allocation of " + std::to_string(in_bytes + out_bytes) + " bytes failed");
+    }
+    tlb_status st = TLB_OK;
+    cudaError_t e = cudaMemcpyAsync(din, src, in_bytes, cudaMemcpyHostToDevice, dev->stream);
+    if (e == cudaSuccess) {
+        st = tlb_quantize_rows_device(dev, type, din, rows, n_per_row, dout);
+        if (st == TLB_OK) e = cudaMemcpyAsync(out, dout, out_bytes, cudaMemcpyDeviceToHost, dev->stream);
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(dev->stream);
+    cudaFree(din);
+    cudaFree(dout);
+    if (st != TLB_OK) return st;
+    if (e != cudaSuccess) return fail(TLB_EXECUTION, "tlb_quantize_rows: " + cuda_msg(e));
+    return TLB_OK;
+}
+
+}  // extern "C"

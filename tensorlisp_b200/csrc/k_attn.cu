@@ -1,0 +1,406 @@
+// Paged-attention decode and its cache write (reference: the CUSTOM nodes lowered by
+// crates/kernels/src/cuda/lower.rs:660-759 onto the vendored vLLM kernels in
+// crates/kernels/src/cuda/shaders/, launcher maths in cuda/paged_attn.rs).
+//
+// The KV pools are only ever written by the cache-write node and read by the attention node
+// (scheme/core.ss:218-220), so their layout is the executor's own: f16
+// [block][kv_head][slot][head_size] for keys and for values -- every (block, kv_head) page is one
+// contiguous run of block_size rows, and a row is head_size*2 bytes.
+//
+// k_paged_attn: grid (context chunk, kv head x query-head group, sequence). A CTA serves ALL query
+// heads that share one KV head (GQA), so each K/V byte is read from HBM once. Each warp streams
+// 16-token tiles of K and V through its own cp.async ring in shared memory (XOR-swizzled rows,
+// conflict-free ldmatrix), computes S = Q K^T and O += P V on the f16 tensor cores
+// (mma.sync.m16n8k16, f32 accumulate; the query heads of the group are the M rows) with an online
+// softmax in base 2, and the warps' (max, sum, O) are merged at the end. With more than one chunk the
+// CTA writes an f32 partial (max, sum, O) and k_paged_reduce merges the chunks (split-K).
+#include <cuda_fp16.h>
+#include <math_constants.h>
+
+#include "kernels.h"
+
+namespace tlb {
+
+constexpr int PA_WARPS = 4;
+constexpr int PA_STAGES = 3;
+constexpr int PA_TILE = 16;  // tokens per tile
+
+__device__ __forceinline__ uint32_t s_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
+
+struct PagedParams {
+    const __half *q;       // [seqs][heads][HS]
+    const __half *kpool;   // [block][kv_heads][block_size][HS]
+    const __half *vpool;
+    const int32_t *tables; // [seqs][max_blocks]
+    const int32_t *lens;   // [seqs]
+    __half *out;           // [seqs][heads][HS]
+    float *partial;        // [seqs][heads][n_chunks][HS + 2]  (max, sum, O) when n_chunks > 1
+    int heads, kv_heads, group, groups_per_kv, block_size, max_blocks, chunk_tokens, n_chunks;
+    float scale_log2;      // softmax scale * log2(e)
+};
+
+template <int HS>
+__global__ void __launch_bounds__(PA_WARPS * 32) k_paged_attn(PagedParams p) {
+    constexpr int ROW_BYTES = HS * 2;
+    constexpr int CHUNKS = ROW_BYTES / 16;             // 16-byte chunks per row
+    constexpr int TILE_BYTES = PA_TILE * ROW_BYTES;    // one of K / V
+    constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+    constexpr int KS = HS / 16;                        // k-steps of Q K^T
+    constexpr int ND = HS / 8;                         // n-tiles of P V
+    constexpr int CP_PER_LANE = 2 * PA_TILE * CHUNKS / 32;
+    extern __shared__ __align__(128) uint8_t smem[];
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int chunk = blockIdx.x, seq = blockIdx.z;
+    const int kvh = blockIdx.y / p.groups_per_kv, grp = blockIdx.y % p.groups_per_kv;
+    const int ctx = p.lens[seq];
+    const int c_begin = chunk * p.chunk_tokens;
+    if (c_begin >= ctx && !(chunk == 0)) return;  // nothing to do; the reduce skips this chunk
+    const int c_end = min(ctx, c_begin + p.chunk_tokens);
+    const int head0 = kvh * p.group + grp * 16;               // first query head of this CTA
+    const int nrows = min(16, p.group - grp * 16);            // query heads served here
+    const int n_tiles = c_end > c_begin ? (c_end - c_begin + PA_TILE - 1) / PA_TILE : 0;
+
+    // ---- Q fragments (A operand, rows = query heads of the group, zero beyond nrows)
+    uint32_t qa[KS][4];
+    {
+        const __half *q0 = p.q + ((size_t)seq * p.heads + head0) * HS;
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++) {
+            const int c0 = ks * 16 + 2 * t;
+            qa[ks][0] = g < nrows ? *reinterpret_cast<const uint32_t *>(q0 + (size_t)g * HS + c0) : 0u;
+            qa[ks][1] = g + 8 < nrows ? *reinterpret_cast<const uint32_t *>(q0 + (size_t)(g + 8) * HS + c0) : 0u;
+            qa[ks][2] = g < nrows ? *reinterpret_cast<const uint32_t *>(q0 + (size_t)g * HS + c0 + 8) : 0u;
+            qa[ks][3] = g + 8 < nrows ? *reinterpret_cast<const uint32_t *>(q0 + (size_t)(g + 8) * HS + c0 + 8) : 0u;
+        }
+    }
+
+    uint8_t *ring = smem + (size_t)warp * PA_STAGES * STAGE_BYTES;
+    const int32_t *table = p.tables + (size_t)seq * p.max_blocks;
+    const size_t page_stride = (size_t)p.block_size * HS;  // elements per (block, kv_head)
+
+    // issue the cp.asyncs of this warp's tile `i` (tile index within the warp's sequence)
+    auto issue = [&](int i) {
+        const int tile = warp + i * PA_WARPS;
+        if (tile < n_tiles) {
+            uint8_t *st = ring + (size_t)(i % PA_STAGES) * STAGE_BYTES;
+            const int tok0 = c_begin + tile * PA_TILE;
+#pragma unroll
+            for (int it = 0; it < CP_PER_LANE; it++) {
+                const int qd = it * 32 + lane;
+                const int kv = qd / (PA_TILE * CHUNKS);
+                const int row = (qd % (PA_TILE * CHUNKS)) / CHUNKS;
+                const int col = qd % CHUNKS;
+                const int tok = tok0 + row;
+                const bool live = tok < c_end;
+                const __half *src = kv ? p.vpool : p.kpool;
+                if (live) {
+                    const int blk = table[tok / p.block_size];
+                    src += ((size_t)blk * p.kv_heads + kvh) * page_stride + (size_t)(tok % p.block_size) * HS + col * 8;
+                }
+                const uint32_t dst = s_u32(st + kv * TILE_BYTES + row * ROW_BYTES + ((col ^ (row & 7)) * 16));
+                cp_async16(dst, src, live ? 16 : 0);  // rows past the context are zero-filled
+            }
+        }
+        cp_commit();
+    };
+
+    float o[ND][4];
+#pragma unroll
+    for (int n = 0; n < ND; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F}, l_run[2] = {0.f, 0.f};
+
+    const int my_tiles = n_tiles > warp ? (n_tiles - warp + PA_WARPS - 1) / PA_WARPS : 0;
+#pragma unroll
+    for (int i = 0; i < PA_STAGES - 1; i++) issue(i);
+
+    for (int i = 0; i < my_tiles; i++) {
+        issue(i + PA_STAGES - 1);
+        cp_wait<PA_STAGES - 1>();
+        __syncwarp();
+        const uint8_t *st = ring + (size_t)(i % PA_STAGES) * STAGE_BYTES;
+        const uint32_t kbase = s_u32(st), vbase = kbase + TILE_BYTES;
+        const int tok0 = c_begin + (warp + i * PA_WARPS) * PA_TILE;
+
+        // ---- S = Q K^T for 16 tokens (two n-tiles of 8)
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        {
+            const int mi = lane >> 3, r = lane & 7;
+            const int row = (mi >> 1) * 8 + r;
+#pragma unroll
+            for (int ks = 0; ks < KS; ks++) {
+                const int col = ks * 2 + (mi & 1);
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4(kbase + row * ROW_BYTES + ((col ^ (row & 7)) * 16), b0, b1, b2, b3);
+                mma16816(s[0], qa[ks], b0, b1);
+                mma16816(s[1], qa[ks], b2, b3);
+            }
+        }
+        // ---- online softmax (base 2); rows g and g+8
+        float rmax[2] = {-CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+        for (int j = 0; j < 2; j++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int tok = tok0 + j * 8 + 2 * t + (e & 1);
+                const float v = tok < c_end ? s[j][e] * p.scale_log2 : -CUDART_INF_F;
+                s[j][e] = v;
+                rmax[e >> 1] = fmaxf(rmax[e >> 1], v);
+            }
+        float corr[2], m_use[2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            rmax[h] = fmaxf(rmax[h], __shfl_xor_sync(0xffffffffu, rmax[h], 1));
+            rmax[h] = fmaxf(rmax[h], __shfl_xor_sync(0xffffffffu, rmax[h], 2));
+            const float m_new = fmaxf(m_run[h], rmax[h]);
+            m_use[h] = m_new == -CUDART_INF_F ? 0.f : m_new;
+            corr[h] = exp2f(m_run[h] - m_use[h]);
+            m_run[h] = m_new;
+            l_run[h] *= corr[h];
+        }
+        uint32_t pa[4];
+        {
+            float pv[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; j++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    pv[j][e] = exp2f(s[j][e] - m_use[e >> 1]);
+                    l_run[e >> 1] += pv[j][e];
+                }
+            pa[0] = pack_h2(pv[0][0], pv[0][1]);
+            pa[1] = pack_h2(pv[0][2], pv[0][3]);
+            pa[2] = pack_h2(pv[1][0], pv[1][1]);
+            pa[3] = pack_h2(pv[1][2], pv[1][3]);
+        }
+        // ---- O = O * corr + P V
+        {
+            const int mi = lane >> 3, r = lane & 7;
+            const int row = (mi & 1) * 8 + r;
+#pragma unroll
+            for (int nd = 0; nd < ND; nd += 2) {
+                o[nd][0] *= corr[0]; o[nd][1] *= corr[0]; o[nd][2] *= corr[1]; o[nd][3] *= corr[1];
+                o[nd + 1][0] *= corr[0]; o[nd + 1][1] *= corr[0]; o[nd + 1][2] *= corr[1]; o[nd + 1][3] *= corr[1];
+                const int col = nd + (mi >> 1);
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4_t(vbase + row * ROW_BYTES + ((col ^ (row & 7)) * 16), b0, b1, b2, b3);
+                mma16816(o[nd], pa, b0, b1);
+                mma16816(o[nd + 1], pa, b2, b3);
+            }
+        }
+    }
+    cp_wait<0>();
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+    }
+    __syncthreads();  // every warp's ring is drained: shared memory is reused for the merge
+
+    // ---- merge the warps: ml[w][row] = (m, l), acc[w][row][HS]
+    float *ml = reinterpret_cast<float *>(smem);                   // [PA_WARPS][16][2]
+    float *acc = ml + PA_WARPS * 16 * 2;                           // [PA_WARPS][16][HS]
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const int row = g + 8 * h;
+        if (row < nrows) {
+            if (t == 0) {
+                ml[(warp * 16 + row) * 2] = m_run[h];
+                ml[(warp * 16 + row) * 2 + 1] = l_run[h];
+            }
+#pragma unroll
+            for (int nd = 0; nd < ND; nd++) {
+                float2 v = make_float2(o[nd][2 * h], o[nd][2 * h + 1]);
+                *reinterpret_cast<float2 *>(&acc[((size_t)warp * 16 + row) * HS + nd * 8 + 2 * t]) = v;
+            }
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nrows * HS; idx += PA_WARPS * 32) {
+        const int row = idx / HS, d = idx % HS;
+        float m = -CUDART_INF_F;
+#pragma unroll
+        for (int w = 0; w < PA_WARPS; w++) m = fmaxf(m, ml[(w * 16 + row) * 2]);
+        const float mu = m == -CUDART_INF_F ? 0.f : m;
+        float l = 0.f, a = 0.f;
+#pragma unroll
+        for (int w = 0; w < PA_WARPS; w++) {
+            const float f = exp2f(ml[(w * 16 + row) * 2] - mu);
+            l += ml[(w * 16 + row) * 2 + 1] * f;
+            a += acc[((size_t)w * 16 + row) * HS + d] * f;
+        }
+        const int head = head0 + row;
+        if (p.n_chunks == 1) {
+            p.out[((size_t)seq * p.heads + head) * HS + d] = __float2half_rn(l > 0.f ? a / l : 0.f);
+        } else {
+            float *pp = p.partial + (((size_t)seq * p.heads + head) * p.n_chunks + chunk) * (HS + 2);
+            pp[2 + d] = a;
+            if (d == 0) { pp[0] = m; pp[1] = l; }
+        }
+    }
+}
+
+template <int HS>
+__global__ void __launch_bounds__(128) k_paged_reduce(PagedParams p) {
+    const int head = blockIdx.x, seq = blockIdx.y;
+    const int ctx = p.lens[seq];
+    const int valid = ctx > 0 ? min(p.n_chunks, (ctx + p.chunk_tokens - 1) / p.chunk_tokens) : 0;
+    const float *pp = p.partial + ((size_t)seq * p.heads + head) * p.n_chunks * (HS + 2);
+    float m = -CUDART_INF_F;
+    for (int c = 0; c < valid; c++) m = fmaxf(m, pp[(size_t)c * (HS + 2)]);
+    const float mu = m == -CUDART_INF_F ? 0.f : m;
+    for (int d = threadIdx.x; d < HS; d += blockDim.x) {
+        float l = 0.f, a = 0.f;
+        for (int c = 0; c < valid; c++) {
+            const float f = exp2f(pp[(size_t)c * (HS + 2)] - mu);
+            l += pp[(size_t)c * (HS + 2) + 1] * f;
+            a += pp[(size_t)c * (HS + 2) + 2 + d] * f;
+        }
+        p.out[((size_t)seq * p.heads + head) * HS + d] = __float2half_rn(l > 0.f ? a / l : 0.f);
+    }
+}
+
+// ---------------------------------------------------------------- host side
+static size_t pa_smem(int hs) {
+    const size_t ring = (size_t)PA_WARPS * PA_STAGES * 2 * PA_TILE * hs * 2;
+    const size_t merge = (size_t)PA_WARPS * 16 * (2 + hs) * 4;
+    return ring > merge ? ring : merge;
+}
+
+void attn_configure() {
+    cudaFuncSetAttribute(k_paged_attn<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pa_smem(64));
+    cudaFuncSetAttribute(k_paged_attn<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pa_smem(128));
+    cudaFuncSetAttribute(k_paged_attn<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pa_smem(256));
+}
+
+bool paged_supported(const PagedGeom &g) {
+    if (!(g.hs == 64 || g.hs == 128 || g.hs == 256)) return false;
+    if (g.kv_heads < 1 || g.heads % g.kv_heads != 0) return false;
+    if (g.block_size < 1 || g.max_blocks < 1) return false;
+    return true;
+}
+
+void paged_plan(PagedGeom &g, int sm_count) {
+    const int group = g.heads / g.kv_heads;
+    const int64_t base = (int64_t)g.seqs * g.kv_heads * ((group + 15) / 16);
+    const int64_t target = (int64_t)sm_count * 8;
+    int64_t ct = ((int64_t)g.max_ctx * base + target - 1) / target;
+    ct = (ct + 63) / 64 * 64;
+    if (ct < 64) ct = 64;
+    if (ct > 512) ct = 512;
+    g.chunk_tokens = (int)ct;
+    g.n_chunks = (int)((g.max_ctx + ct - 1) / ct);
+    if (g.n_chunks < 1) g.n_chunks = 1;
+}
+
+uint64_t paged_scratch_bytes(const PagedGeom &g) {
+    if (g.n_chunks <= 1) return 0;
+    return (uint64_t)g.seqs * g.heads * g.n_chunks * (g.hs + 2) * 4;
+}
+
+template <int HS>
+static cudaError_t launch_pa(const PagedGeom &g, const PagedParams &p, cudaStream_t st) {
+    dim3 grid((unsigned)g.n_chunks, (unsigned)(g.kv_heads * p.groups_per_kv), (unsigned)g.seqs);
+    k_paged_attn<HS><<<grid, PA_WARPS * 32, pa_smem(HS), st>>>(p);
+    if (g.n_chunks > 1) k_paged_reduce<HS><<<dim3((unsigned)g.heads, (unsigned)g.seqs), 128, 0, st>>>(p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_paged_attention(const PagedGeom &g, const void *q, const void *kpool, const void *vpool,
+                                   const int32_t *tables, const int32_t *lens, void *out, void *scratch,
+                                   cudaStream_t st) {
+    if (g.seqs == 0 || g.heads == 0) return cudaSuccess;
+    PagedParams p;
+    p.q = (const __half *)q;
+    p.kpool = (const __half *)kpool;
+    p.vpool = (const __half *)vpool;
+    p.tables = tables;
+    p.lens = lens;
+    p.out = (__half *)out;
+    p.partial = (float *)scratch;
+    p.heads = g.heads;
+    p.kv_heads = g.kv_heads;
+    p.group = g.heads / g.kv_heads;
+    p.groups_per_kv = (p.group + 15) / 16;
+    p.block_size = g.block_size;
+    p.max_blocks = g.max_blocks;
+    p.chunk_tokens = g.chunk_tokens;
+    p.n_chunks = g.n_chunks;
+    p.scale_log2 = g.scale * 1.4426950408889634f;
+    switch (g.hs) {
+        case 64: return launch_pa<64>(g, p, st);
+        case 128: return launch_pa<128>(g, p, st);
+        case 256: return launch_pa<256>(g, p, st);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+// cache write: key/value f16 [kv_heads*hs, tokens] -> pools at slot = block*block_size + offset
+// (reshape_and_cache of the reference; a negative slot skips the token)
+__global__ void k_cache_write(int kv_heads, int hs, int block_size, const uint4 *key, const uint4 *value, uint4 *kpool,
+                              uint4 *vpool, const int64_t *slots) {
+    const int tok = blockIdx.x;
+    const int64_t slot = slots[tok];
+    if (slot < 0) return;
+    const int64_t blk = slot / block_size, off = slot % block_size;
+    const int cpr = hs / 8;  // 16-byte chunks per head row
+    for (int i = threadIdx.x; i < kv_heads * cpr; i += blockDim.x) {
+        const int h = i / cpr, c = i % cpr;
+        const size_t dst = (((size_t)blk * kv_heads + h) * block_size + off) * cpr + c;
+        const size_t src = (size_t)tok * kv_heads * cpr + i;
+        kpool[dst] = key[src];
+        vpool[dst] = value[src];
+    }
+}
+cudaError_t launch_cache_write(int tokens, int kv_heads, int hs, int block_size, const void *key, const void *value,
+                               void *kpool, void *vpool, const int64_t *slots, cudaStream_t st) {
+    if (tokens == 0) return cudaSuccess;
+    k_cache_write<<<tokens, 128, 0, st>>>(kv_heads, hs, block_size, (const uint4 *)key, (const uint4 *)value, (uint4 *)kpool,
+                                          (uint4 *)vpool, slots);
+    return cudaGetLastError();
+}
+
+// pool -> dense [ctx, kv_heads, hs] per sequence (gather_kv_cache of the reference)
+__global__ void k_paged_gather(int kv_heads, int hs, int block_size, int max_blocks, const uint4 *pool, const int32_t *tables,
+                               const int32_t *lens, const int64_t *seq_offsets, uint4 *out) {
+    const int seq = blockIdx.y, tok = blockIdx.x;
+    if (tok >= lens[seq]) return;
+    const int blk = tables[(size_t)seq * max_blocks + tok / block_size], off = tok % block_size;
+    const int cpr = hs / 8;
+    for (int i = threadIdx.x; i < kv_heads * cpr; i += blockDim.x) {
+        const int h = i / cpr, c = i % cpr;
+        out[(size_t)(seq_offsets[seq] + tok) * kv_heads * cpr + i] = pool[(((size_t)blk * kv_heads + h) * block_size + off) * cpr + c];
+    }
+}
+cudaError_t launch_paged_gather(int seqs, int kv_heads, int hs, int block_size, int max_blocks, const void *pool,
+                                const int32_t *tables, const int32_t *lens, const int64_t *seq_offsets, void *out,
+                                int max_ctx, cudaStream_t st) {
+    if (seqs == 0 || max_ctx == 0) return cudaSuccess;
+    k_paged_gather<<<dim3((unsigned)max_ctx, (unsigned)seqs), 128, 0, st>>>(kv_heads, hs, block_size, max_blocks, (const uint4 *)pool,
+                                                                            tables, lens, seq_offsets, (uint4 *)out);
+    return cudaGetLastError();
+}
+
+}  // namespace tlb

@@ -1,0 +1,559 @@
+// Elementwise, row and gather/scatter kernels of a decoder graph (reference:
+// crates/kernels/src/cuda/native/core.cu; op semantics are ggml's CPU backend,
+// vendor/ggml/src/ggml-cpu/ops.cpp). All of these are HBM-bound: rows are read with 128-bit
+// loads where the layout allows it, and the fusions that matter for a decode step (norm*weight,
+// act(gate)*up, rope+cast) are single passes.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <math_constants.h>
+
+#include "kernels.h"
+
+namespace tlb {
+
+// ---------------------------------------------------------------- typed element access
+__device__ __forceinline__ float ld_elem(const uint8_t *p, uint32_t ty) {
+    switch (ty) {
+        case TLB_TYPE_F32: return *reinterpret_cast<const float *>(p);
+        case TLB_TYPE_F16: return __half2float(*reinterpret_cast<const __half *>(p));
+        case TLB_TYPE_BF16: return __bfloat162float(*reinterpret_cast<const __nv_bfloat16 *>(p));
+        case TLB_TYPE_I32: return (float)*reinterpret_cast<const int32_t *>(p);
+        case TLB_TYPE_I64: return (float)*reinterpret_cast<const int64_t *>(p);
+        default: return 0.f;
+    }
+}
+__device__ __forceinline__ void st_elem(uint8_t *p, uint32_t ty, float v) {
+    switch (ty) {
+        case TLB_TYPE_F32: *reinterpret_cast<float *>(p) = v; break;
+        case TLB_TYPE_F16: *reinterpret_cast<__half *>(p) = __float2half_rn(v); break;
+        case TLB_TYPE_BF16: *reinterpret_cast<__nv_bfloat16 *>(p) = __float2bfloat16_rn(v); break;
+        case TLB_TYPE_I32: *reinterpret_cast<int32_t *>(p) = (int32_t)v; break;
+        case TLB_TYPE_I64: *reinterpret_cast<int64_t *>(p) = (int64_t)v; break;
+        default: break;
+    }
+}
+
+// element `i0` of a row of block-quantized data (ggml-quants.c dequantize_row_*)
+__device__ __forceinline__ float dq_elem(const uint8_t *row, uint32_t ty, int64_t i0) {
+    switch (ty) {
+        case TLB_TYPE_Q8_0: {
+            const uint8_t *b = row + (i0 >> 5) * 34;
+            const float d = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(b)));
+            return (float)reinterpret_cast<const int8_t *>(b + 2)[i0 & 31] * d;
+        }
+        case TLB_TYPE_Q4_0: {
+            const uint8_t *b = row + (i0 >> 5) * 18;
+            const float d = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(b)));
+            const int j = (int)(i0 & 31);
+            const int q = j < 16 ? (b[2 + j] & 0x0F) : (b[2 + j - 16] >> 4);
+            return (float)(q - 8) * d;
+        }
+        case TLB_TYPE_Q4_K: {
+            const uint8_t *b = row + (i0 >> 8) * 144;
+            const float d = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(b)));
+            const float dmin = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(b + 2)));
+            const int e = (int)(i0 & 255), j = e >> 5, l = e & 31;
+            const uint8_t *s = b + 4;
+            int sc, mn;
+            if (j < 4) {
+                sc = s[j] & 63;
+                mn = s[j + 4] & 63;
+            } else {
+                sc = (s[j + 4] & 0xF) | ((s[j - 4] >> 6) << 4);
+                mn = (s[j + 4] >> 4) | ((s[j] >> 6) << 4);
+            }
+            const int q = (b[16 + (j >> 1) * 32 + l] >> ((j & 1) * 4)) & 0xF;
+            return d * (float)sc * (float)q - dmin * (float)mn;
+        }
+        default: return ld_elem(row + i0 * (ty == TLB_TYPE_F32 || ty == TLB_TYPE_I32 ? 4 : (ty == TLB_TYPE_I64 ? 8 : 2)), ty);
+    }
+}
+
+__device__ __forceinline__ bool is_quant(uint32_t ty) { return ty == TLB_TYPE_Q8_0 || ty == TLB_TYPE_Q4_0 || ty == TLB_TYPE_Q4_K; }
+
+__device__ __forceinline__ void decomp(int64_t i, const int64_t *ne, int64_t &i0, int64_t &i1, int64_t &i2, int64_t &i3) {
+    i0 = i % ne[0]; i /= ne[0];
+    i1 = i % ne[1]; i /= ne[1];
+    i2 = i % ne[2];
+    i3 = i / ne[2];
+}
+__device__ __forceinline__ int64_t offs(const TView &t, int64_t i0, int64_t i1, int64_t i2, int64_t i3) {
+    return i0 * t.nb[0] + i1 * t.nb[1] + i2 * t.nb[2] + i3 * t.nb[3];
+}
+
+__device__ __forceinline__ float block_sum(float v, float *sh) {
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) v += __shfl_xor_sync(0xffffffffu, v, s);
+    const int w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) sh[w] = v;
+    __syncthreads();
+    float r = 0.f;
+    for (int i = 0; i < nw; i++) r += sh[i];
+    return r;
+}
+__device__ __forceinline__ float block_max(float v, float *sh) {
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, s));
+    const int w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) sh[w] = v;
+    __syncthreads();
+    float r = -CUDART_INF_F;
+    for (int i = 0; i < nw; i++) r = fmaxf(r, sh[i]);
+    return r;
+}
+
+static inline unsigned nblocks(int64_t n, int per) { return (unsigned)((n + per - 1) / per > 0 ? (n + per - 1) / per : 1); }
+static inline int row_threads(int64_t n) {
+    int t = 32;
+    while (t < 256 && t < n) t <<= 1;
+    return t;
+}
+
+// ---------------------------------------------------------------- ADD/SUB/MUL/DIV (f32, ggml broadcast)
+__device__ __forceinline__ float bin_op(int op, float a, float b) {
+    return op == 0 ? a + b : op == 1 ? a - b : op == 2 ? a * b : a / b;
+}
+__global__ void k_bin(BinArgs p, const uint8_t *a, const uint8_t *b, uint8_t *d, int64_t n) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t i0, i1, i2, i3;
+        decomp(i, p.d.ne, i0, i1, i2, i3);
+        const float x = *reinterpret_cast<const float *>(a + offs(p.a, i0, i1, i2, i3));
+        const float y = *reinterpret_cast<const float *>(b + offs(p.b, i0 % p.b.ne[0], i1 % p.b.ne[1], i2 % p.b.ne[2], i3 % p.b.ne[3]));
+        *reinterpret_cast<float *>(d + offs(p.d, i0, i1, i2, i3)) = bin_op(p.op, x, y);
+    }
+}
+// contiguous a and d, b either the same shape or one row repeated: 128-bit accesses
+__global__ void k_bin_vec(int op, const float4 *a, const float4 *b, float4 *d, int64_t n4, int64_t bn4) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+        const float4 x = a[i], y = b[i % bn4];
+        d[i] = make_float4(bin_op(op, x.x, y.x), bin_op(op, x.y, y.y), bin_op(op, x.z, y.z), bin_op(op, x.w, y.w));
+    }
+}
+static bool contiguous_f32(const TView &t) {
+    int64_t s = 4;
+    for (int i = 0; i < 4; i++) {
+        if (t.ne[i] != 1 && t.nb[i] != s) return false;
+        s *= t.ne[i];
+    }
+    return true;
+}
+cudaError_t launch_bin(const BinArgs &p, const void *a, const void *b, void *d, cudaStream_t st) {
+    const int64_t n = p.d.ne[0] * p.d.ne[1] * p.d.ne[2] * p.d.ne[3];
+    if (n == 0) return cudaSuccess;
+    const int64_t bn = p.b.ne[0] * p.b.ne[1] * p.b.ne[2] * p.b.ne[3];
+    const bool same = p.b.ne[0] == p.d.ne[0] && p.b.ne[1] == p.d.ne[1] && p.b.ne[2] == p.d.ne[2] && p.b.ne[3] == p.d.ne[3];
+    const bool row = p.b.ne[0] == p.d.ne[0] && bn == p.b.ne[0];
+    if (contiguous_f32(p.a) && contiguous_f32(p.d) && contiguous_f32(p.b) && (same || row) && p.d.ne[0] % 4 == 0 &&
+        ((uintptr_t)a % 16 == 0) && ((uintptr_t)b % 16 == 0) && ((uintptr_t)d % 16 == 0)) {
+        k_bin_vec<<<nblocks(n / 4, 256), 256, 0, st>>>(p.op, (const float4 *)a, (const float4 *)b, (float4 *)d, n / 4, bn / 4);
+    } else {
+        k_bin<<<nblocks(n, 256), 256, 0, st>>>(p, (const uint8_t *)a, (const uint8_t *)b, (uint8_t *)d, n);
+    }
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- UNARY / SCALE / CLAMP / ...
+// codes 0..21 are ggml's enum ggml_unary_op; 100.. are the other single-source ops
+// (crates/kernels/src/cuda/lower.rs:252-290 uses the same numbering).
+__device__ __forceinline__ float unary_op(int code, float x, float p0, float p1) {
+    switch (code) {
+        case 0: return fabsf(x);
+        case 1: return x > 0.f ? 1.f : (x < 0.f ? -1.f : 0.f);
+        case 2: return -x;
+        case 3: return x > 0.f ? 1.f : 0.f;
+        case 4: return tanhf(x);
+        case 5: return x > 0.f ? x : expm1f(x);
+        case 6: return x > 0.f ? x : 0.f;
+        case 7: return 1.f / (1.f + expf(-x));
+        case 8: return 0.5f * x * (1.f + tanhf(0.79788456080286535587989211986876f * x * (1.f + 0.044715f * x * x)));
+        case 9: return x * (1.f / (1.f + expf(-1.702f * x)));
+        case 10: return x / (1.f + expf(-x));
+        case 11: return x * fminf(1.f, fmaxf(0.f, (x + 3.f) / 6.f));
+        case 12: return fminf(1.f, fmaxf(0.f, (x + 3.f) / 6.f));
+        case 13: return expf(x);
+        case 14: return expm1f(x);
+        case 15: return x > 20.f ? x : logf(1.f + expf(x));
+        case 16: return 0.5f * x * (1.f + erff(x * 0.70710678118654752440f));
+        case 18: return floorf(x);
+        case 19: return ceilf(x);
+        case 20: return roundf(x);
+        case 21: return truncf(x);
+        case 100: return x * p0 + p1;
+        case 101: return p0;
+        case 102: return fminf(fmaxf(x, p0), p1);
+        case 103: return x > 0.f ? x : x * p0;
+        case 104: return x * x;
+        case 105: return sqrtf(x);
+        case 106: return sinf(x);
+        case 107: return cosf(x);
+        case 108: return logf(x);
+        default: return x;
+    }
+}
+__global__ void k_unary(UnaryArgs p, const uint8_t *a, uint8_t *d, int64_t n) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t i0, i1, i2, i3;
+        decomp(i, p.d.ne, i0, i1, i2, i3);
+        const float x = ld_elem(a + offs(p.a, i0, i1, i2, i3), p.aty);
+        st_elem(d + offs(p.d, i0, i1, i2, i3), p.dty, unary_op(p.code, x, p.p0, p.p1));
+    }
+}
+cudaError_t launch_unary(const UnaryArgs &p, const void *a, void *d, cudaStream_t st) {
+    const int64_t n = p.d.ne[0] * p.d.ne[1] * p.d.ne[2] * p.d.ne[3];
+    if (n == 0) return cudaSuccess;
+    k_unary<<<nblocks(n, 256), 256, 0, st>>>(p, (const uint8_t *)a, (uint8_t *)d, n);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- GLU: d = act(a) * b
+__device__ __forceinline__ float glu_act(int op, float x) {
+    switch (op) {
+        case 0: return x > 0.f ? x : 0.f;
+        case 1: return unary_op(8, x, 0, 0);
+        case 2: return x / (1.f + expf(-x));
+        case 4: return unary_op(16, x, 0, 0);
+        case 5: return unary_op(9, x, 0, 0);
+        default: return x;
+    }
+}
+__global__ void k_glu(GluArgs p, const float *a, const float *b, float *d) {
+    const int64_t total = p.n * p.rows;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / p.n, c = i % p.n;
+        d[i] = glu_act(p.glu_op, a[r * p.lda + c]) * b[r * p.ldb + c];
+    }
+}
+cudaError_t launch_glu(const GluArgs &p, const float *a, const float *b, float *d, cudaStream_t st) {
+    if (p.n * p.rows == 0) return cudaSuccess;
+    k_glu<<<nblocks(p.n * p.rows, 256), 256, 0, st>>>(p, a, b, d);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- NORM / RMS_NORM (* weight)
+// One CTA per row, the row stays in registers between the reduction and the scaling pass
+// (up to 16 values per thread; longer rows are re-read from L2).
+__global__ void k_norm(NormArgs p, const uint8_t *a, const uint8_t *w, uint8_t *d) {
+    __shared__ float sh[32];
+    const int64_t row = blockIdx.x;
+    const int64_t i1 = row % p.a.ne[1], i2 = (row / p.a.ne[1]) % p.a.ne[2], i3 = row / (p.a.ne[1] * p.a.ne[2]);
+    const float *x = reinterpret_cast<const float *>(a + i1 * p.a.nb[1] + i2 * p.a.nb[2] + i3 * p.a.nb[3]);
+    float *y = reinterpret_cast<float *>(d + i1 * p.d.nb[1] + i2 * p.d.nb[2] + i3 * p.d.nb[3]);
+    const int64_t n = p.a.ne[0];
+    const float *wr = nullptr;
+    if (p.has_w)
+        wr = reinterpret_cast<const float *>(w + (i1 % p.w.ne[1]) * p.w.nb[1] + (i2 % p.w.ne[2]) * p.w.nb[2] + (i3 % p.w.ne[3]) * p.w.nb[3]);
+    const int64_t wn = p.has_w ? p.w.ne[0] : 1;
+    float v[16];
+    const bool cached = n <= (int64_t)blockDim.x * 16;
+    float s = 0.f, s1 = 0.f;
+    int c = 0;
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x, c++) {
+        const float t = x[i];
+        if (cached) v[c & 15] = t;
+        s += t * t;
+        s1 += t;
+    }
+    float mean = 0.f, scale;
+    if (p.rms) {
+        s = block_sum(s, sh);
+        scale = 1.0f / sqrtf(s / (float)n + p.eps);
+    } else {
+        mean = block_sum(s1, sh) / (float)n;
+        float var = 0.f;
+        c = 0;
+        for (int64_t i = threadIdx.x; i < n; i += blockDim.x, c++) {
+            const float t = (cached ? v[c & 15] : x[i]) - mean;
+            var += t * t;
+        }
+        var = block_sum(var, sh) / (float)n;
+        scale = 1.0f / sqrtf(var + p.eps);
+    }
+    c = 0;
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x, c++) {
+        float t = ((cached ? v[c & 15] : x[i]) - mean) * scale;
+        if (wr) t *= wr[i % wn];
+        y[i] = t;
+    }
+}
+cudaError_t launch_norm(const NormArgs &p, const void *a, const void *w, void *d, cudaStream_t st) {
+    const int64_t rows = p.a.ne[1] * p.a.ne[2] * p.a.ne[3];
+    if (rows == 0 || p.a.ne[0] == 0) return cudaSuccess;
+    k_norm<<<(unsigned)rows, row_threads(p.a.ne[0]), 0, st>>>(p, (const uint8_t *)a, (const uint8_t *)w, (uint8_t *)d);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- ROPE (normal and neox pairs, YaRN ramp)
+// theta is built the way the CPU backend builds its cache (ops.cpp:5846-5860): multiplied up
+// sequentially in f32, not powf, so long positions agree.
+__global__ void k_rope(RopeArgs p, const uint8_t *a, const int32_t *pos, const float *ff, uint8_t *d, int64_t npairs) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= npairs) return;
+    const int64_t half = p.a.ne[0] / 2;
+    const int64_t pr = i % half;
+    int64_t r = i / half;
+    const int64_t i1 = r % p.a.ne[1]; r /= p.a.ne[1];
+    const int64_t i2 = r % p.a.ne[2];
+    const int64_t i3 = r / p.a.ne[2];
+    const uint8_t *src = a + i1 * p.a.nb[1] + i2 * p.a.nb[2] + i3 * p.a.nb[3];
+    uint8_t *dst = d + i1 * p.d.nb[1] + i2 * p.d.nb[2] + i3 * p.d.nb[3];
+    const int64_t i0 = 2 * pr;
+    if (i0 >= p.n_dims) {  // dims past n_dims are copied through
+        st_elem(dst + i0 * p.d.nb[0], p.dty, ld_elem(src + i0 * p.a.nb[0], p.aty));
+        st_elem(dst + (i0 + 1) * p.d.nb[0], p.dty, ld_elem(src + (i0 + 1) * p.a.nb[0], p.aty));
+        return;
+    }
+    float theta = (float)pos[i2];
+    for (int64_t k = 0; k < pr; k++) theta *= p.theta_scale;
+    const float fq = p.has_ff ? ff[pr] : 1.0f;
+    const float theta_extrap = theta / fq;
+    const float theta_interp = p.freq_scale * theta_extrap;
+    float th = theta_interp, mscale = p.attn_factor;
+    if (p.ext_factor != 0.0f) {
+        const float yv = ((float)(i0 / 2) - p.corr0) / fmaxf(0.001f, p.corr1 - p.corr0);
+        const float ramp_mix = (1.f - fminf(1.f, fmaxf(0.f, yv))) * p.ext_factor;
+        th = theta_interp * (1.f - ramp_mix) + theta_extrap * ramp_mix;
+        mscale *= 1.0f + 0.1f * logf(1.0f / p.freq_scale);
+    }
+    const float cs = cosf(th) * mscale, sn = sinf(th) * mscale;
+    const int64_t ic = p.mode == 0 ? i0 : pr;
+    const int64_t off = p.mode == 0 ? 1 : p.n_dims / 2;
+    const float x0 = ld_elem(src + ic * p.a.nb[0], p.aty), x1 = ld_elem(src + (ic + off) * p.a.nb[0], p.aty);
+    st_elem(dst + ic * p.d.nb[0], p.dty, x0 * cs - x1 * sn);
+    st_elem(dst + (ic + off) * p.d.nb[0], p.dty, x0 * sn + x1 * cs);
+}
+cudaError_t launch_rope(const RopeArgs &p, const void *a, const int32_t *pos, const float *ff, void *d, cudaStream_t st) {
+    const int64_t n = p.a.ne[0] / 2 * p.a.ne[1] * p.a.ne[2] * p.a.ne[3];
+    if (n == 0) return cudaSuccess;
+    k_rope<<<nblocks(n, 256), 256, 0, st>>>(p, (const uint8_t *)a, pos, ff, (uint8_t *)d, n);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- SOFT_MAX (scale, mask, ALiBi)
+__global__ void k_soft_max(SoftmaxArgs p, const uint8_t *a, const uint8_t *m, uint8_t *d) {
+    __shared__ float sh[32];
+    const int64_t row = blockIdx.x;
+    const int64_t i1 = row % p.a.ne[1], i2 = (row / p.a.ne[1]) % p.a.ne[2], i3 = row / (p.a.ne[1] * p.a.ne[2]);
+    const float *x = reinterpret_cast<const float *>(a + i1 * p.a.nb[1] + i2 * p.a.nb[2] + i3 * p.a.nb[3]);
+    float *y = reinterpret_cast<float *>(d + i1 * p.d.nb[1] + i2 * p.d.nb[2] + i3 * p.d.nb[3]);
+    const int64_t n = p.a.ne[0];
+    const uint8_t *mr = nullptr;
+    if (p.has_mask) mr = m + i1 * p.m.nb[1] + (i2 % p.m.ne[2]) * p.m.nb[2] + (i3 % p.m.ne[3]) * p.m.nb[3];
+    float slope = 1.0f;
+    if (p.max_bias > 0.0f) {
+        const int h = (int)i2;
+        slope = h < p.n_head_log2 ? powf(p.m0, (float)(h + 1)) : powf(p.m1, (float)(2 * (h - p.n_head_log2) + 1));
+    }
+    float mx = -CUDART_INF_F;
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
+        float v = x[i] * p.scale;
+        if (mr) v += slope * ld_elem(mr + i * p.m.nb[0], p.mty);
+        mx = fmaxf(mx, v);
+    }
+    mx = block_max(mx, sh);
+    float sum = 0.f;
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
+        float v = x[i] * p.scale;
+        if (mr) v += slope * ld_elem(mr + i * p.m.nb[0], p.mty);
+        const float e = expf(v - mx);
+        y[i] = e;
+        sum += e;
+    }
+    sum = block_sum(sum, sh);
+    const float inv = 1.0f / sum;
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) y[i] *= inv;
+}
+cudaError_t launch_soft_max(const SoftmaxArgs &p, const void *a, const void *m, void *d, cudaStream_t st) {
+    const int64_t rows = p.a.ne[1] * p.a.ne[2] * p.a.ne[3];
+    if (rows == 0 || p.a.ne[0] == 0) return cudaSuccess;
+    k_soft_max<<<(unsigned)rows, row_threads(p.a.ne[0]), 0, st>>>(p, (const uint8_t *)a, (const uint8_t *)m, (uint8_t *)d);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- GET_ROWS / SET_ROWS
+__device__ __forceinline__ int64_t ld_index(const uint8_t *p, uint32_t ty) {
+    return ty == TLB_TYPE_I64 ? *reinterpret_cast<const int64_t *>(p) : (int64_t)*reinterpret_cast<const int32_t *>(p);
+}
+// d[:, i10, i11, i12] = a[:, ids[i10, i11, i12], i11, i12]
+__global__ void k_get_rows(RowsArgs p, const uint8_t *a, const uint8_t *ids, uint8_t *d) {
+    const int64_t r = blockIdx.x;
+    const int64_t i10 = r % p.ids.ne[0], i11 = (r / p.ids.ne[0]) % p.ids.ne[1], i12 = r / (p.ids.ne[0] * p.ids.ne[1]);
+    const int64_t row = ld_index(ids + i10 * p.ids.nb[0] + i11 * p.ids.nb[1] + i12 * p.ids.nb[2], p.idty);
+    const uint8_t *src = a + row * p.a.nb[1] + i11 * p.a.nb[2] + i12 * p.a.nb[3];
+    uint8_t *dst = d + i10 * p.d.nb[1] + i11 * p.d.nb[2] + i12 * p.d.nb[3];
+    const bool q = is_quant(p.aty);
+    for (int64_t i = threadIdx.x; i < p.d.ne[0]; i += blockDim.x) {
+        const float v = q ? dq_elem(src, p.aty, i) : ld_elem(src + i * p.a.nb[0], p.aty);
+        st_elem(dst + i * p.d.nb[0], p.dty, v);
+    }
+}
+cudaError_t launch_get_rows(const RowsArgs &p, const void *a, const void *ids, void *d, cudaStream_t st) {
+    const int64_t rows = p.ids.ne[0] * p.ids.ne[1] * p.ids.ne[2];
+    if (rows == 0 || p.d.ne[0] == 0) return cudaSuccess;
+    k_get_rows<<<(unsigned)rows, 256, 0, st>>>(p, (const uint8_t *)a, (const uint8_t *)ids, (uint8_t *)d);
+    return cudaGetLastError();
+}
+// d[:, ids[i1, i2 % ne11, i3 % ne12], i2, i3] = rows[:, i1, i2, i3]   (ggml_set_rows)
+__global__ void k_set_rows(RowsArgs p, const uint8_t *a, const uint8_t *ids, uint8_t *d) {
+    const int64_t r = blockIdx.x;
+    const int64_t i1 = r % p.a.ne[1], i2 = (r / p.a.ne[1]) % p.a.ne[2], i3 = r / (p.a.ne[1] * p.a.ne[2]);
+    const int64_t row = ld_index(ids + i1 * p.ids.nb[0] + (i2 % p.ids.ne[1]) * p.ids.nb[1] + (i3 % p.ids.ne[2]) * p.ids.nb[2], p.idty);
+    if (row < 0 || row >= p.d.ne[1]) return;
+    const uint8_t *src = a + i1 * p.a.nb[1] + i2 * p.a.nb[2] + i3 * p.a.nb[3];
+    uint8_t *dst = d + row * p.d.nb[1] + i2 * p.d.nb[2] + i3 * p.d.nb[3];
+    for (int64_t i = threadIdx.x; i < p.a.ne[0]; i += blockDim.x)
+        st_elem(dst + i * p.d.nb[0], p.dty, ld_elem(src + i * p.a.nb[0], p.aty));
+}
+cudaError_t launch_set_rows(const RowsArgs &p, const void *rows, const void *ids, void *d, cudaStream_t st) {
+    const int64_t n = p.a.ne[1] * p.a.ne[2] * p.a.ne[3];
+    if (n == 0 || p.a.ne[0] == 0) return cudaSuccess;
+    k_set_rows<<<(unsigned)n, 256, 0, st>>>(p, (const uint8_t *)rows, (const uint8_t *)ids, (uint8_t *)d);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- DUP / CPY / CONT (casts, dequantizing reads)
+// Element i of the source (in its own index order) goes to element i of the destination.
+__global__ void k_cpy(CpyArgs p, const uint8_t *a, uint8_t *d, int64_t n) {
+    const bool q = is_quant(p.aty);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t a0, a1, a2, a3, d0, d1, d2, d3;
+        decomp(i, p.a.ne, a0, a1, a2, a3);
+        decomp(i, p.d.ne, d0, d1, d2, d3);
+        float v;
+        if (q) v = dq_elem(a + a1 * p.a.nb[1] + a2 * p.a.nb[2] + a3 * p.a.nb[3], p.aty, a0);
+        else v = ld_elem(a + offs(p.a, a0, a1, a2, a3), p.aty);
+        st_elem(d + offs(p.d, d0, d1, d2, d3), p.dty, v);
+    }
+}
+// same-type contiguous copy and f32 -> f16 contiguous cast: 128-bit reads
+__global__ void k_cpy_f32_f16(const float4 *a, uint2 *d, int64_t n4) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+        const float4 v = a[i];
+        const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+        d[i] = make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
+    }
+}
+static bool contiguous_ty(const TView &t, int64_t es) {
+    int64_t s = es;
+    for (int i = 0; i < 4; i++) {
+        if (t.ne[i] != 1 && t.nb[i] != s) return false;
+        s *= t.ne[i];
+    }
+    return true;
+}
+cudaError_t launch_cpy(const CpyArgs &p, const void *a, void *d, cudaStream_t st) {
+    const int64_t n = p.a.ne[0] * p.a.ne[1] * p.a.ne[2] * p.a.ne[3];
+    if (n == 0) return cudaSuccess;
+    if (p.aty == TLB_TYPE_F32 && p.dty == TLB_TYPE_F16 && contiguous_ty(p.a, 4) && contiguous_ty(p.d, 2) && n % 4 == 0 &&
+        (uintptr_t)a % 16 == 0 && (uintptr_t)d % 8 == 0) {
+        k_cpy_f32_f16<<<nblocks(n / 4, 256), 256, 0, st>>>((const float4 *)a, (uint2 *)d, n / 4);
+        return cudaGetLastError();
+    }
+    if (p.aty == p.dty && !(p.aty == TLB_TYPE_Q8_0 || p.aty == TLB_TYPE_Q4_0 || p.aty == TLB_TYPE_Q4_K)) {
+        const int64_t es = p.aty == TLB_TYPE_F32 || p.aty == TLB_TYPE_I32 ? 4 : (p.aty == TLB_TYPE_I64 ? 8 : 2);
+        if (contiguous_ty(p.a, es) && contiguous_ty(p.d, es))
+            return cudaMemcpyAsync(d, a, (size_t)(n * es), cudaMemcpyDeviceToDevice, st);
+    }
+    k_cpy<<<nblocks(n, 256), 256, 0, st>>>(p, (const uint8_t *)a, (uint8_t *)d, n);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- ARGMAX (last index among ties, as the CPU)
+__global__ void k_argmax(TView a, const uint8_t *x, int32_t *out) {
+    __shared__ float smax[32];
+    __shared__ int sidx[32];
+    const int64_t row = blockIdx.x;
+    const float *xr = reinterpret_cast<const float *>(x + row * a.nb[1]);
+    float mx = -CUDART_INF_F;
+    int idx = 0;
+    for (int64_t i = threadIdx.x; i < a.ne[0]; i += blockDim.x) {
+        const float v = xr[i];
+        if (v >= mx) { mx = v; idx = (int)i; }
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) {
+        const float om = __shfl_xor_sync(0xffffffffu, mx, s);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, s);
+        if (om > mx || (om == mx && oi > idx)) { mx = om; idx = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { smax[threadIdx.x >> 5] = mx; sidx[threadIdx.x >> 5] = idx; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); w++)
+            if (smax[w] > mx || (smax[w] == mx && sidx[w] > idx)) { mx = smax[w]; idx = sidx[w]; }
+        out[row] = idx;
+    }
+}
+cudaError_t launch_argmax(const TView &a, const void *x, int32_t *out, cudaStream_t st) {
+    const int64_t rows = a.ne[1] * a.ne[2] * a.ne[3];
+    if (rows == 0) return cudaSuccess;
+    k_argmax<<<(unsigned)rows, 256, 0, st>>>(a, (const uint8_t *)x, out);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- CONCAT / REPEAT / SUM_ROWS / ARANGE (f32)
+__global__ void k_concat(SimpleArgs p, const uint8_t *a, const uint8_t *b, uint8_t *d, int64_t n) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t ix[4];
+        decomp(i, p.d.ne, ix[0], ix[1], ix[2], ix[3]);
+        const int dim = (int)p.i0;
+        float v;
+        if (ix[dim] < p.a.ne[dim]) {
+            v = *reinterpret_cast<const float *>(a + offs(p.a, ix[0], ix[1], ix[2], ix[3]));
+        } else {
+            int64_t jx[4] = {ix[0], ix[1], ix[2], ix[3]};
+            jx[dim] -= p.a.ne[dim];
+            v = *reinterpret_cast<const float *>(b + offs(p.b, jx[0], jx[1], jx[2], jx[3]));
+        }
+        *reinterpret_cast<float *>(d + offs(p.d, ix[0], ix[1], ix[2], ix[3])) = v;
+    }
+}
+cudaError_t launch_concat(const SimpleArgs &p, const void *a, const void *b, void *d, cudaStream_t st) {
+    const int64_t n = p.d.ne[0] * p.d.ne[1] * p.d.ne[2] * p.d.ne[3];
+    if (n == 0) return cudaSuccess;
+    k_concat<<<nblocks(n, 256), 256, 0, st>>>(p, (const uint8_t *)a, (const uint8_t *)b, (uint8_t *)d, n);
+    return cudaGetLastError();
+}
+__global__ void k_repeat(SimpleArgs p, const uint8_t *a, uint8_t *d, int64_t n) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t i0, i1, i2, i3;
+        decomp(i, p.d.ne, i0, i1, i2, i3);
+        *reinterpret_cast<float *>(d + offs(p.d, i0, i1, i2, i3)) =
+            *reinterpret_cast<const float *>(a + offs(p.a, i0 % p.a.ne[0], i1 % p.a.ne[1], i2 % p.a.ne[2], i3 % p.a.ne[3]));
+    }
+}
+cudaError_t launch_repeat(const SimpleArgs &p, const void *a, void *d, cudaStream_t st) {
+    const int64_t n = p.d.ne[0] * p.d.ne[1] * p.d.ne[2] * p.d.ne[3];
+    if (n == 0) return cudaSuccess;
+    k_repeat<<<nblocks(n, 256), 256, 0, st>>>(p, (const uint8_t *)a, (uint8_t *)d, n);
+    return cudaGetLastError();
+}
+__global__ void k_sum_rows(SimpleArgs p, const uint8_t *a, uint8_t *d) {
+    __shared__ float sh[32];
+    const int64_t row = blockIdx.x;
+    const int64_t i1 = row % p.a.ne[1], i2 = (row / p.a.ne[1]) % p.a.ne[2], i3 = row / (p.a.ne[1] * p.a.ne[2]);
+    const float *x = reinterpret_cast<const float *>(a + i1 * p.a.nb[1] + i2 * p.a.nb[2] + i3 * p.a.nb[3]);
+    float s = 0.f;
+    for (int64_t i = threadIdx.x; i < p.a.ne[0]; i += blockDim.x) s += x[i];
+    s = block_sum(s, sh);
+    if (threadIdx.x == 0)
+        *reinterpret_cast<float *>(d + i1 * p.d.nb[1] + i2 * p.d.nb[2] + i3 * p.d.nb[3]) = p.i0 ? s / (float)p.a.ne[0] : s;
+}
+cudaError_t launch_sum_rows(const SimpleArgs &p, const void *a, void *d, cudaStream_t st) {
+    const int64_t rows = p.a.ne[1] * p.a.ne[2] * p.a.ne[3];
+    if (rows == 0) return cudaSuccess;
+    k_sum_rows<<<(unsigned)rows, row_threads(p.a.ne[0]), 0, st>>>(p, (const uint8_t *)a, (uint8_t *)d);
+    return cudaGetLastError();
+}
+__global__ void k_arange(float start, float step, float *d, int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) d[i] = start + step * (float)i;
+}
+cudaError_t launch_arange(const SimpleArgs &p, void *d, cudaStream_t st) {
+    if (p.d.ne[0] == 0) return cudaSuccess;
+    k_arange<<<nblocks(p.d.ne[0], 256), 256, 0, st>>>(p.f0, p.f1, (float *)d, p.d.ne[0]);
+    return cudaGetLastError();
+}
+
+}  // namespace tlb

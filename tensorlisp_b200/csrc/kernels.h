@@ -1,0 +1,102 @@
+// Launch helpers exported by the kernel files (k_*.cu) to the lowering code.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "../../include/tlb200.h"
+
+namespace tlb {
+
+// A strided view of up to four dimensions, in bytes, as ggml describes tensors.
+struct TView {
+    int64_t ne[4];
+    int64_t nb[4];
+};
+
+// ---------------------------------------------------------------- k_quant.cu
+enum { ACT_Q8_0 = 0, ACT_Q8_K = 1 };
+struct ActLayout {
+    int kind;
+    int64_t K, N;
+    uint64_t qs_off, d_off, bsum_off, bytes;
+};
+ActLayout act_layout(int kind, int64_t K, int64_t N);
+cudaError_t launch_quantize_rows(uint32_t type, const float *x, int64_t rows, int64_t n_per_row, void *y, cudaStream_t st);
+cudaError_t launch_act_quantize(const ActLayout &a, const float *x, int64_t ldx, void *out, cudaStream_t st);
+
+// ---------------------------------------------------------------- k_mm.cu
+// y[n*ldy + m] = dot(W row m, quantized activation column n), contiguous W rows of K elements.
+// Returns cudaErrorNotSupported when the shape cannot use the pipelined kernel (caller falls back).
+bool gemv_supported(uint32_t type, int64_t K, int64_t M, int64_t N);
+cudaError_t launch_gemv(uint32_t type, const void *W, int64_t K, int64_t M, const ActLayout &a, const void *act,
+                        float *y, int64_t ldy, int sm_count, int *err_flag, cudaStream_t st);
+// Generic strided / batched product (any supported weight type, f32 activations or a quantized
+// activation block per (i2,i3) batch). dst f32.
+struct MMGeneric {
+    uint32_t wtype;
+    TView w, x, y;       // x: f32 activations (used for plain weight types)
+    int64_t r2, r3;      // broadcast ratios
+    const void *act;     // quantized activations of the whole x (N = ne1*ne2*ne3 columns), or null
+    ActLayout a;
+};
+cudaError_t launch_mm_generic(const MMGeneric &p, const void *W, const void *X, void *Y, cudaStream_t st);
+void gemv_configure();  // sets the dynamic shared-memory attributes once per process
+
+// ---------------------------------------------------------------- k_core.cu
+struct BinArgs { TView a, b, d; int op; };  // 0 add 1 sub 2 mul 3 div; all f32
+cudaError_t launch_bin(const BinArgs &p, const void *a, const void *b, void *d, cudaStream_t st);
+struct UnaryArgs { TView a, d; int code; float p0, p1; uint32_t aty, dty; };
+cudaError_t launch_unary(const UnaryArgs &p, const void *a, void *d, cudaStream_t st);
+// GLU: d = act(a) * b over contiguous rows; glu_op as ggml (0 reglu, 1 geglu, 2 swiglu, 4 geglu_erf, 5 geglu_quick)
+struct GluArgs { int64_t n, rows; int64_t lda, ldb; int glu_op; };
+cudaError_t launch_glu(const GluArgs &p, const float *a, const float *b, float *d, cudaStream_t st);
+// (RMS_)NORM over rows of n f32 values, optional multiply by a broadcast weight row of wn values.
+struct NormArgs { TView a, d; int rms; float eps; int has_w; TView w; };
+cudaError_t launch_norm(const NormArgs &p, const void *a, const void *w, void *d, cudaStream_t st);
+struct RopeArgs {
+    TView a, d;
+    uint32_t aty, dty;
+    int n_dims, mode;
+    float freq_scale, ext_factor, attn_factor, theta_scale, corr0, corr1;
+    int has_ff;
+};
+cudaError_t launch_rope(const RopeArgs &p, const void *a, const int32_t *pos, const float *ff, void *d, cudaStream_t st);
+struct SoftmaxArgs { TView a, m, d; float scale, max_bias, m0, m1; int n_head_log2; int has_mask; uint32_t mty; };
+cudaError_t launch_soft_max(const SoftmaxArgs &p, const void *a, const void *m, void *d, cudaStream_t st);
+struct RowsArgs { TView a, ids, d; uint32_t aty, idty, dty; };
+cudaError_t launch_get_rows(const RowsArgs &p, const void *a, const void *ids, void *d, cudaStream_t st);
+cudaError_t launch_set_rows(const RowsArgs &p, const void *rows, const void *ids, void *d, cudaStream_t st);
+struct CpyArgs { TView a, d; uint32_t aty, dty; };
+cudaError_t launch_cpy(const CpyArgs &p, const void *a, void *d, cudaStream_t st);
+cudaError_t launch_argmax(const TView &a, const void *x, int32_t *out, cudaStream_t st);
+struct SimpleArgs { TView a, b, d; int64_t i0; float f0, f1; };
+cudaError_t launch_concat(const SimpleArgs &p, const void *a, const void *b, void *d, cudaStream_t st);
+cudaError_t launch_repeat(const SimpleArgs &p, const void *a, void *d, cudaStream_t st);
+cudaError_t launch_sum_rows(const SimpleArgs &p, const void *a, void *d, cudaStream_t st);  // i0: 1 = mean
+cudaError_t launch_arange(const SimpleArgs &p, void *d, cudaStream_t st);
+
+// ---------------------------------------------------------------- k_attn.cu
+// KV pools are private to the executor (only the two paged nodes touch them): f16
+// [block][kv_head][slot][head_size] for both keys and values.
+struct PagedGeom {
+    int seqs, heads, kv_heads, hs, block_size, max_ctx, max_blocks;
+    float scale;
+    int chunk_tokens, n_chunks;  // split of the context (filled by paged_plan)
+};
+void paged_plan(PagedGeom &g, int sm_count);
+uint64_t paged_scratch_bytes(const PagedGeom &g);
+bool paged_supported(const PagedGeom &g);
+cudaError_t launch_paged_attention(const PagedGeom &g, const void *q, const void *kpool, const void *vpool,
+                                   const int32_t *tables, const int32_t *lens, void *out, void *scratch,
+                                   cudaStream_t st);
+cudaError_t launch_cache_write(int tokens, int kv_heads, int hs, int block_size, const void *key, const void *value,
+                               void *kpool, void *vpool, const int64_t *slots, cudaStream_t st);
+// paged pool -> dense f16 [ctx, kv_heads, hs] per sequence, concatenated in sequence order
+cudaError_t launch_paged_gather(int seqs, int kv_heads, int hs, int block_size, int max_blocks, const void *pool,
+                                const int32_t *tables, const int32_t *lens, const int64_t *seq_offsets, void *out,
+                                int max_ctx, cudaStream_t st);
+void attn_configure();
+
+}  // namespace tlb

@@ -1,0 +1,620 @@
+// Lowers graph nodes to launches, by ggml op name (reference: crates/kernels/src/cuda/lower.rs:177-213),
+// after a few IR rewrites that form the fused ops of a decoder step (reference: the fusion rules of
+// crates/kernels/src/vulkan/fuse.rs:56-152, which its CUDA executor does not apply).
+#include <cmath>
+#include <cstdlib>
+#include <map>
+
+#include "kernels.h"
+#include "tlb_internal.h"
+
+namespace tlb {
+
+namespace {
+
+[[noreturn]] void unsupported(const Tensor &t, const std::string &why) { throw Unsupported{t.op, t.name, why}; }
+
+bool plain(uint32_t ty) { return ty == 0 || ty == 1 || ty == 30 || ty == 26 || ty == 27; }
+bool gemv_type(uint32_t ty) { return ty == TLB_TYPE_Q8_0 || ty == TLB_TYPE_Q4_0 || ty == TLB_TYPE_Q4_K; }
+bool mm_weight_ok(uint32_t ty) { return ty == 0 || ty == 1 || ty == 30 || gemv_type(ty); }
+
+TView view_of(const Tensor &t) {
+    TView v;
+    for (int i = 0; i < 4; i++) {
+        v.ne[i] = t.ne[i];
+        v.nb[i] = (int64_t)t.nb[i];
+    }
+    return v;
+}
+
+int act_kind_for(uint32_t wty) { return wty == TLB_TYPE_Q4_K ? ACT_Q8_K : ACT_Q8_0; }
+
+struct L {
+    const LowerCtx &c;
+    int32_t id;
+    int pos;
+    std::vector<Dispatch> &out;
+    const Tensor &t() const { return c.g->tensors[id]; }
+    const Tensor &T(int32_t i) const { return c.g->tensors[i]; }
+    Place place(int32_t i) const { return c.layout->place[i]; }
+    int32_t src(int i) const {
+        const int32_t s = t().src[i];
+        if (s < 0) throw std::string(t().op + " `" + t().name + "` is missing source " + std::to_string(i));
+        return s;
+    }
+    void push(std::function<cudaError_t(const RunCtx &)> fn) { out.push_back({t().op + " " + t().name, std::move(fn)}); }
+    void need_plain(std::initializer_list<int32_t> ids) const {
+        for (int32_t s : ids)
+            if (!plain(T(s).ty)) unsupported(t(), "quantized operand");
+    }
+    void need_f32(std::initializer_list<int32_t> ids) const {
+        for (int32_t s : ids)
+            if (T(s).ty != TLB_TYPE_F32) unsupported(t(), "operands must be f32");
+    }
+};
+
+void lower_bin(L &l) {
+    const int32_t a = l.src(0), b = l.src(1);
+    l.need_f32({a, b, l.id});
+    BinArgs p{view_of(l.T(a)), view_of(l.T(b)), view_of(l.t()), 0};
+    const std::string &op = l.t().op;
+    p.op = op == "ADD" ? 0 : op == "SUB" ? 1 : op == "MUL" ? 2 : 3;
+    for (int i = 0; i < 4; i++)
+        if (p.b.ne[i] == 0 || p.d.ne[i] % p.b.ne[i] != 0) unsupported(l.t(), "the second operand does not broadcast into the first");
+    const Place pa = l.place(a), pb = l.place(b), pd = l.place(l.id);
+    l.push([=](const RunCtx &r) { return launch_bin(p, r.at(pa), r.at(pb), r.at(pd), r.stream); });
+}
+
+void lower_unary(L &l) {
+    const int32_t a = l.src(0);
+    const Tensor &t = l.t();
+    l.need_plain({a, l.id});
+    UnaryArgs p{view_of(l.T(a)), view_of(t), 0, 0.f, 0.f, l.T(a).ty, t.ty};
+    const std::string &op = t.op;
+    if (op == "SCALE") { p.code = 100; p.p0 = t.param_f32(0); p.p1 = t.param_f32(1); }
+    else if (op == "FILL") { p.code = 101; p.p0 = t.param_f32(0); }
+    else if (op == "CLAMP") { p.code = 102; p.p0 = t.param_f32(0); p.p1 = t.param_f32(1); }
+    else if (op == "LEAKY_RELU") { p.code = 103; p.p0 = t.param_f32(0); }
+    else if (op == "SQR") p.code = 104;
+    else if (op == "SQRT") p.code = 105;
+    else if (op == "SIN") p.code = 106;
+    else if (op == "COS") p.code = 107;
+    else if (op == "LOG") p.code = 108;
+    else {
+        const int n = t.op_params[0];
+        if (n == 17) unsupported(t, "xielu");
+        if (n < 0 || n > 21) unsupported(t, "unary op " + std::to_string(n));
+        p.code = n;
+    }
+    if (l.T(a).nelements() != t.nelements()) unsupported(t, "source and destination differ in size");
+    const Place pa = l.place(a), pd = l.place(l.id);
+    l.push([=](const RunCtx &r) { return launch_unary(p, r.at(pa), r.at(pd), r.stream); });
+}
+
+void lower_glu(L &l) {
+    const Tensor &t = l.t();
+    const int32_t a = l.src(0);
+    const int32_t b = t.src[1];
+    const int glu_op = t.op_params[0];
+    const bool swapped = t.op_params[1] != 0;
+    if (!(glu_op == 0 || glu_op == 1 || glu_op == 2 || glu_op == 4 || glu_op == 5)) unsupported(t, "glu op " + std::to_string(glu_op));
+    l.need_f32({a, l.id});
+    const Tensor &ta = l.T(a);
+    if (ta.nb[0] != 4 || !t.is_contiguous()) unsupported(t, "needs dense rows");
+    GluArgs p;
+    p.n = t.ne[0];
+    p.rows = t.nrows();
+    p.glu_op = glu_op;
+    if (!ta.is_contiguous_n(1) && ta.nrows() != ta.ne[1]) unsupported(t, "needs uniformly strided rows");
+    p.lda = (int64_t)ta.nb[1] / 4;
+    int64_t a_off = 0, b_off = 0;
+    Place pb;
+    if (b >= 0) {
+        const Tensor &tb = l.T(b);
+        l.need_f32({b});
+        if (tb.nb[0] != 4 || tb.ne[0] != t.ne[0] || tb.nrows() != t.nrows()) unsupported(t, "operands differ in shape");
+        p.ldb = (int64_t)tb.nb[1] / 4;
+        pb = l.place(b);
+    } else {
+        if (ta.ne[0] != 2 * t.ne[0]) unsupported(t, "unsplit glu takes a source twice as wide");
+        p.ldb = p.lda;
+        pb = l.place(a);
+        a_off = swapped ? t.ne[0] * 4 : 0;
+        b_off = swapped ? 0 : t.ne[0] * 4;
+    }
+    if (ta.nrows() > 1 && (ta.ne[2] > 1 || ta.ne[3] > 1) && !ta.is_contiguous_n(1)) unsupported(t, "needs uniformly strided rows");
+    const Place pa = l.place(a), pd = l.place(l.id);
+    l.push([=](const RunCtx &r) {
+        return launch_glu(p, (const float *)(r.at(pa) + a_off), (const float *)(r.at(pb) + b_off), (float *)r.at(pd), r.stream);
+    });
+}
+
+void lower_norm(L &l, bool fused_mul) {
+    const Tensor &t = l.t();
+    const int32_t a = l.src(0);
+    l.need_f32({a, l.id});
+    if (l.T(a).nb[0] != 4 || t.nb[0] != 4) unsupported(t, "needs dense rows");
+    NormArgs p;
+    p.a = view_of(l.T(a));
+    p.d = view_of(t);
+    p.rms = (t.op == "RMS_NORM" || t.op == "RMS_NORM_MUL") ? 1 : 0;
+    p.eps = t.param_f32(fused_mul ? 15 : 0);
+    p.has_w = fused_mul ? 1 : 0;
+    Place pw;
+    if (fused_mul) {
+        const int32_t w = l.src(1);
+        p.w = view_of(l.T(w));
+        pw = l.place(w);
+    } else {
+        p.w = p.a;
+    }
+    const Place pa = l.place(a), pd = l.place(l.id);
+    l.push([=](const RunCtx &r) { return launch_norm(p, r.at(pa), fused_mul ? r.at(pw) : nullptr, r.at(pd), r.stream); });
+}
+
+void lower_rope(L &l) {
+    const Tensor &t = l.t();
+    const int32_t a = l.src(0), pos = l.src(1);
+    const int32_t ff = t.src[2];
+    const int mode = t.op_params[2];
+    if (mode != 0 && mode != 2) unsupported(t, "only normal and neox rope (mrope/vision are not supported)");
+    if (l.T(pos).ty != TLB_TYPE_I32 || l.T(pos).ne[0] != l.T(a).ne[2]) unsupported(t, "needs one i32 position per token");
+    if (ff >= 0 && (l.T(ff).ty != TLB_TYPE_F32 || l.T(ff).nb[0] != 4)) unsupported(t, "frequency factors must be f32");
+    const uint32_t aty = l.T(a).ty, dty = t.ty;
+    if (!(aty == 0 || aty == 1) || !(dty == 0 || dty == 1)) unsupported(t, "rope takes f32 or f16");
+    RopeArgs p;
+    p.a = view_of(l.T(a));
+    p.d = view_of(t);
+    p.aty = aty;
+    p.dty = dty;
+    p.n_dims = t.op_params[1];
+    p.mode = mode;
+    const float freq_base = t.param_f32(5);
+    p.freq_scale = t.param_f32(6);
+    p.ext_factor = t.param_f32(7);
+    p.attn_factor = t.param_f32(8);
+    const float beta_fast = t.param_f32(9), beta_slow = t.param_f32(10);
+    const float n_ctx_orig = (float)t.op_params[4];
+    if (p.n_dims <= 0 || p.n_dims > t.ne[0] || p.n_dims % 2) unsupported(t, "bad n_dims");
+    p.theta_scale = powf(freq_base, -2.0f / (float)p.n_dims);
+    // ggml_rope_yarn_corr_dims (ggml.c:4369-4381)
+    auto corr = [&](float beta) { return (float)p.n_dims * logf(n_ctx_orig / (beta * 2.0f * (float)M_PI)) / (2.0f * logf(freq_base)); };
+    p.corr0 = fmaxf(0.f, floorf(corr(beta_fast)));
+    p.corr1 = fminf((float)p.n_dims - 1.f, ceilf(corr(beta_slow)));
+    p.has_ff = ff >= 0;
+    const Place pa = l.place(a), pp = l.place(pos), pd = l.place(l.id);
+    Place pf;
+    if (ff >= 0) pf = l.place(ff);
+    const bool hf = ff >= 0;
+    l.push([=](const RunCtx &r) {
+        return launch_rope(p, r.at(pa), (const int32_t *)r.at(pp), hf ? (const float *)r.at(pf) : nullptr, r.at(pd), r.stream);
+    });
+}
+
+void lower_soft_max(L &l) {
+    const Tensor &t = l.t();
+    const int32_t a = l.src(0);
+    if (t.src[2] >= 0) unsupported(t, "sinks are not supported by the soft_max lowering");
+    l.need_f32({a, l.id});
+    const int32_t m = t.src[1];
+    if (m >= 0 && !(l.T(m).ty == 0 || l.T(m).ty == 1)) unsupported(t, "mask must be f16 or f32");
+    if (l.T(a).nb[0] != 4 || t.nb[0] != 4) unsupported(t, "needs dense rows");
+    SoftmaxArgs p;
+    p.a = view_of(l.T(a));
+    p.d = view_of(t);
+    p.has_mask = m >= 0;
+    p.m = m >= 0 ? view_of(l.T(m)) : p.a;
+    p.mty = m >= 0 ? l.T(m).ty : 0;
+    p.scale = t.param_f32(0);
+    p.max_bias = t.param_f32(1);
+    p.n_head_log2 = 1 << (int)floorf(log2f((float)l.T(a).ne[2]));
+    p.m0 = powf(2.0f, -p.max_bias / (float)p.n_head_log2);
+    p.m1 = powf(2.0f, -(p.max_bias / 2.0f) / (float)p.n_head_log2);
+    const Place pa = l.place(a), pd = l.place(l.id);
+    Place pm;
+    if (m >= 0) pm = l.place(m);
+    const bool hm = m >= 0;
+    l.push([=](const RunCtx &r) { return launch_soft_max(p, r.at(pa), hm ? r.at(pm) : nullptr, r.at(pd), r.stream); });
+}
+
+void lower_get_rows(L &l) {
+    const Tensor &t = l.t();
+    const int32_t a = l.src(0), ids = l.src(1);
+    const uint32_t aty = l.T(a).ty;
+    if (!(plain(aty) || gemv_type(aty))) unsupported(t, std::string("rows of ggml type ") + type_traits(aty)->name);
+    if (!(l.T(ids).ty == 26 || l.T(ids).ty == 27)) unsupported(t, "row indices must be i32 or i64");
+    if (!plain(t.ty)) unsupported(t, "operand type");
+    RowsArgs p{view_of(l.T(a)), view_of(l.T(ids)), view_of(t), aty, l.T(ids).ty, t.ty};
+    const Place pa = l.place(a), pi = l.place(ids), pd = l.place(l.id);
+    l.push([=](const RunCtx &r) { return launch_get_rows(p, r.at(pa), r.at(pi), r.at(pd), r.stream); });
+}
+
+void lower_set_rows(L &l) {
+    // ggml_set_rows(a = destination, b = rows, c = ids): the node is a view of a with src[0] = b, src[1] = c
+    const Tensor &t = l.t();
+    const int32_t rows = l.src(0), ids = l.src(1);
+    l.need_plain({rows, l.id});
+    if (!(l.T(ids).ty == 26 || l.T(ids).ty == 27)) unsupported(t, "row indices must be i32 or i64");
+    if (l.T(rows).ne[0] != t.ne[0]) unsupported(t, "rows and destination differ in width");
+    RowsArgs p{view_of(l.T(rows)), view_of(l.T(ids)), view_of(t), l.T(rows).ty, l.T(ids).ty, t.ty};
+    const Place pa = l.place(rows), pi = l.place(ids), pd = l.place(l.id);
+    l.push([=](const RunCtx &r) { return launch_set_rows(p, r.at(pa), r.at(pi), r.at(pd), r.stream); });
+}
+
+void lower_cpy(L &l) {
+    const Tensor &t = l.t();
+    const int32_t a = l.src(0);
+    const Tensor &ta = l.T(a);
+    if (ta.nelements() != t.nelements()) unsupported(t, "source and destination differ in size");
+    if (!(plain(ta.ty) || gemv_type(ta.ty))) unsupported(t, "operand type");
+    if (!plain(t.ty)) unsupported(t, "operand type");
+    CpyArgs p{view_of(ta), view_of(t), ta.ty, t.ty};
+    const Place pa = l.place(a), pd = l.place(l.id);
+    l.push([=](const RunCtx &r) { return launch_cpy(p, r.at(pa), r.at(pd), r.stream); });
+}
+
+void lower_argmax(L &l) {
+    const Tensor &t = l.t();
+    const int32_t a = l.src(0);
+    l.need_f32({a});
+    if (t.ty != TLB_TYPE_I32) unsupported(t, "argmax writes i32");
+    if (l.T(a).nb[0] != 4) unsupported(t, "needs dense rows");
+    if (!l.T(a).is_contiguous_n(1) ) unsupported(t, "needs uniformly strided rows");
+    const TView v = view_of(l.T(a));
+    const Place pa = l.place(a), pd = l.place(l.id);
+    l.push([=](const RunCtx &r) { return launch_argmax(v, r.at(pa), (int32_t *)r.at(pd), r.stream); });
+}
+
+void lower_simple(L &l) {
+    const Tensor &t = l.t();
+    SimpleArgs p{};
+    p.d = view_of(t);
+    const Place pd = l.place(l.id);
+    if (t.op == "ARANGE") {
+        if (t.ty != 0) unsupported(t, "arange writes f32");
+        p.f0 = t.param_f32(0);
+        p.f1 = t.param_f32(2);
+        l.push([=](const RunCtx &r) { return launch_arange(p, r.at(pd), r.stream); });
+        return;
+    }
+    const int32_t a = l.src(0);
+    l.need_f32({a, l.id});
+    p.a = view_of(l.T(a));
+    const Place pa = l.place(a);
+    if (t.op == "CONCAT") {
+        const int32_t b = l.src(1);
+        l.need_f32({b});
+        p.b = view_of(l.T(b));
+        p.i0 = t.op_params[0];
+        if (p.i0 < 0 || p.i0 > 3) unsupported(t, "bad concat dimension");
+        const Place pb = l.place(b);
+        l.push([=](const RunCtx &r) { return launch_concat(p, r.at(pa), r.at(pb), r.at(pd), r.stream); });
+    } else if (t.op == "REPEAT") {
+        l.push([=](const RunCtx &r) { return launch_repeat(p, r.at(pa), r.at(pd), r.stream); });
+    } else {  // SUM_ROWS / MEAN
+        if (l.T(a).nb[0] != 4) unsupported(t, "needs dense rows");
+        p.i0 = t.op == "MEAN";
+        l.push([=](const RunCtx &r) { return launch_sum_rows(p, r.at(pa), r.at(pd), r.stream); });
+    }
+}
+
+// ---- MUL_MAT (lower.rs:543-571). Quantized weights take int8 activations quantized once per
+// distinct activation tensor by a QUANT_ACT node that rewrite_graph put in src[2].
+void lower_mul_mat(L &l) {
+    const Tensor &t = l.t();
+    const int32_t w = l.src(0), x = l.src(1);
+    const Tensor &tw = l.T(w), &tx = l.T(x);
+    if (!mm_weight_ok(tw.ty)) unsupported(t, std::string("weights of ggml type ") + type_traits(tw.ty)->name);
+    if (tx.ty != TLB_TYPE_F32) unsupported(t, "activations must be f32");
+    if (t.ty != TLB_TYPE_F32) unsupported(t, "the result must be f32");
+    if (tw.ne[0] != tx.ne[0] || t.ne[0] != tw.ne[1] || t.ne[1] != tx.ne[1] || tw.ne[2] == 0 || tw.ne[3] == 0 ||
+        t.ne[2] != tx.ne[2] || t.ne[3] != tx.ne[3] || t.ne[2] % tw.ne[2] != 0 || t.ne[3] % tw.ne[3] != 0)
+        unsupported(t, "inconsistent shapes");
+    if (tw.nb[0] != type_traits(tw.ty)->size) unsupported(t, "weight rows must be dense");
+    const Place pw = l.place(w), px = l.place(x), pd = l.place(l.id);
+    const int64_t K = tw.ne[0], M = tw.ne[1], N = tx.ne[1];
+    const int sm = l.c.dev->prop.multiProcessorCount;
+    MMGeneric g{};
+    g.wtype = tw.ty;
+    g.w = view_of(tw);
+    g.x = view_of(tx);
+    g.y = view_of(t);
+    g.r2 = t.ne[2] / tw.ne[2];
+    g.r3 = t.ne[3] / tw.ne[3];
+    if (!gemv_type(tw.ty)) {
+        l.push([=](const RunCtx &r) { return launch_mm_generic(g, r.at(pw), r.at(px), r.at(pd), r.stream); });
+        return;
+    }
+    const int32_t qa = t.src[2];
+    if (qa < 0 || l.T(qa).op != "QUANT_ACT") unsupported(t, "activations could not be quantized (rows must be dense f32 with uniformly strided columns and a length that is a multiple of the block size)");
+    const Place pq = l.place(qa);
+    const ActLayout a = act_layout(act_kind_for(tw.ty), K, tx.nrows());
+    const bool batched = tw.ne[2] * tw.ne[3] * t.ne[2] * t.ne[3] != 1;
+    const bool dense_w = tw.nb[1] == tw.row_size();
+    const bool dense_y = t.is_contiguous();
+    if (!batched && dense_w && dense_y && gemv_supported(tw.ty, K, M, N) && !getenv("TLB_MM_GENERIC")) {
+        const uint32_t wty = tw.ty;
+        l.push([=](const RunCtx &r) {
+            return launch_gemv(wty, r.at(pw), K, M, a, r.at(pq), (float *)r.at(pd), M, sm, r.err, r.stream);
+        });
+        return;
+    }
+    g.a = a;
+    l.push([=](const RunCtx &r) {
+        MMGeneric gg = g;
+        gg.act = r.at(pq);
+        return launch_mm_generic(gg, r.at(pw), r.at(px), r.at(pd), r.stream);
+    });
+}
+
+void lower_quant_act(L &l) {
+    const Tensor &t = l.t();
+    const int32_t x = l.src(0);
+    const Tensor &tx = l.T(x);
+    const ActLayout a = act_layout(t.op_params[0], tx.ne[0], tx.nrows());
+    const int64_t ldx = tx.nrows() > 1 ? (int64_t)tx.nb[1] / 4 : tx.ne[0];
+    const Place px = l.place(x), pd = l.place(l.id);
+    l.push([=](const RunCtx &r) { return launch_act_quantize(a, (const float *)r.at(px), ldx, r.at(pd), r.stream); });
+}
+
+// ---- CUSTOM: the paged nodes (lower.rs:660-759). userdata, low to high bits: kind (4), kv heads (4),
+// block size (8), max context length (16), scale (f32).
+struct PagedUd {
+    int kind, kv_heads, block_size, max_ctx;
+    float scale;
+};
+PagedUd paged_ud(const Tensor &t) {
+    const uint64_t ud = (uint64_t)(uint32_t)t.op_params[4] | ((uint64_t)(uint32_t)t.op_params[5] << 32);
+    PagedUd u;
+    u.kind = (int)(ud & 15);
+    u.kv_heads = (int)((ud >> 4) & 15);
+    u.block_size = (int)((ud >> 8) & 255);
+    u.max_ctx = (int)((ud >> 16) & 0xffff);
+    const uint32_t bits = (uint32_t)(ud >> 32);
+    std::memcpy(&u.scale, &bits, 4);
+    return u;
+}
+
+bool paged_geom(const Graph &g, const Tensor &t, int sm, PagedGeom &pg) {
+    const PagedUd u = paged_ud(t);
+    if (u.kind != 1 || t.src[0] < 0 || t.src[3] < 0) return false;
+    const Tensor &q = g.tensors[t.src[0]];
+    pg.hs = (int)q.ne[0];
+    pg.heads = (int)q.ne[1];
+    pg.seqs = (int)q.ne[2];
+    pg.kv_heads = u.kv_heads;
+    pg.block_size = u.block_size;
+    pg.max_ctx = u.max_ctx;
+    pg.max_blocks = (int)g.tensors[t.src[3]].ne[0];
+    pg.scale = u.scale;
+    if (!paged_supported(pg)) return false;
+    paged_plan(pg, sm);
+    return true;
+}
+
+void lower_custom(L &l) {
+    const Tensor &t = l.t();
+    const PagedUd u = paged_ud(t);
+    auto f16 = [&](int32_t s) { return l.T(s).ty == TLB_TYPE_F16; };
+    if (u.kind == 1) {
+        const int32_t q = l.src(0), kc = l.src(1), vc = l.src(2), tables = l.src(3), lens = l.src(4);
+        const Tensor &tq = l.T(q);
+        if (!(f16(q) && f16(kc) && f16(vc) && t.ty == TLB_TYPE_F16)) unsupported(t, "paged attention takes f16 q, caches and output");
+        const uint64_t hs = (uint64_t)tq.ne[0], heads = (uint64_t)tq.ne[1];
+        if (tq.nb[0] != 2 || tq.nb[1] != hs * 2 || tq.nb[2] != hs * heads * 2 || t.ne[0] != tq.ne[0] || t.ne[1] != tq.ne[1] || t.ne[2] != tq.ne[2] || !t.is_contiguous())
+            unsupported(t, "paged attention takes a contiguous q and an output of its shape");
+        if (l.T(tables).ty != TLB_TYPE_I32 || l.T(lens).ty != TLB_TYPE_I32 || !l.T(tables).is_contiguous() || !l.T(lens).is_contiguous())
+            unsupported(t, "block tables and context lengths must be contiguous i32");
+        if (l.T(tables).ne[1] != tq.ne[2] || l.T(lens).ne[0] != tq.ne[2]) unsupported(t, "one block-table row and one length per sequence");
+        PagedGeom pg{};
+        if (!paged_geom(*l.c.g, t, l.c.dev->prop.multiProcessorCount, pg))
+            unsupported(t, "head size must be 64, 128 or 256 and the query heads a multiple of the kv heads");
+        if ((int64_t)pg.max_blocks * pg.block_size < pg.max_ctx) unsupported(t, "block tables are shorter than the maximum context");
+        const int64_t sc = l.c.layout->scratch[l.pos];
+        if (paged_scratch_bytes(pg) > 0 && sc < 0) throw std::string("paged attention scratch was not planned");
+        Place ps;
+        ps.buf = BUF_ARENA;
+        ps.off = sc < 0 ? 0 : (uint64_t)sc;
+        const Place pq = l.place(q), pk = l.place(kc), pv = l.place(vc), pt = l.place(tables), pl = l.place(lens), pd = l.place(l.id);
+        l.push([=](const RunCtx &r) {
+            return launch_paged_attention(pg, r.at(pq), r.at(pk), r.at(pv), (const int32_t *)r.at(pt), (const int32_t *)r.at(pl),
+                                          r.at(pd), r.at(ps), r.stream);
+        });
+    } else if (u.kind == 2) {
+        const int32_t key = l.src(0), value = l.src(1), kc = l.src(2), vc = l.src(3), slots = l.src(4);
+        const Tensor &tk = l.T(key);
+        if (!(f16(key) && f16(value) && f16(kc) && f16(vc))) unsupported(t, "the cache write takes f16 keys, values and caches");
+        const int tokens = (int)tk.nrows();
+        if (l.T(slots).nelements() != 2 * (int64_t)tokens || tk.nb[1] != (uint64_t)tk.ne[0] * 2 || !tk.is_contiguous() || !l.T(value).is_contiguous() ||
+            l.T(value).nelements() != tk.nelements())
+            unsupported(t, "the cache write takes contiguous keys and one i64 slot per token");
+        if (u.kv_heads < 1 || tk.ne[0] % u.kv_heads != 0 || (tk.ne[0] / u.kv_heads) % 8 != 0) unsupported(t, "head size must be a multiple of 8");
+        const int hs = (int)(tk.ne[0] / u.kv_heads);
+        const Place pk = l.place(key), pv = l.place(value), pkc = l.place(kc), pvc = l.place(vc), psl = l.place(slots);
+        const int kvh = u.kv_heads, bs = u.block_size;
+        l.push([=](const RunCtx &r) {
+            return launch_cache_write(tokens, kvh, hs, bs, r.at(pk), r.at(pv), r.at(pkc), r.at(pvc), (const int64_t *)r.at(psl), r.stream);
+        });
+    } else {
+        unsupported(t, "unknown custom op");
+    }
+}
+
+}  // namespace
+
+uint64_t node_scratch_bytes(const Graph &g, int32_t id, int sm_count) {
+    const Tensor &t = g.tensors[id];
+    if (t.op == "CUSTOM") {
+        PagedGeom pg{};
+        if (paged_geom(g, t, sm_count, pg)) return paged_scratch_bytes(pg);
+    }
+    return 0;
+}
+
+void lower_node(const LowerCtx &c, int32_t id, int pos, std::vector<Dispatch> &out) {
+    const Tensor &t = c.g->tensors[id];
+    if (t.is_view_op() || t.nelements() == 0) return;
+    L l{c, id, pos, out};
+    const std::string &op = t.op;
+    if (op == "QUANT_ACT") return lower_quant_act(l);
+    for (int s : t.src)
+        if (s >= 0) {
+            const uint32_t ty = c.g->tensors[s].ty;
+            if (!(plain(ty) || gemv_type(ty)) && c.g->tensors[s].op != "QUANT_ACT") unsupported(t, "operand type");
+        }
+    if (!plain(t.ty)) unsupported(t, "operand type");
+    if (op == "ADD" || op == "SUB" || op == "MUL" || op == "DIV") return lower_bin(l);
+    if (op == "SCALE" || op == "FILL" || op == "CLAMP" || op == "LEAKY_RELU" || op == "SQR" || op == "SQRT" || op == "SIN" ||
+        op == "COS" || op == "LOG" || op == "UNARY")
+        return lower_unary(l);
+    if (op == "GLU") return lower_glu(l);
+    if (op == "NORM" || op == "RMS_NORM") return lower_norm(l, false);
+    if (op == "RMS_NORM_MUL") return lower_norm(l, true);
+    if (op == "ROPE") return lower_rope(l);
+    if (op == "SOFT_MAX") return lower_soft_max(l);
+    if (op == "GET_ROWS") return lower_get_rows(l);
+    if (op == "SET_ROWS") return lower_set_rows(l);
+    if (op == "DUP" || op == "CPY" || op == "CONT") return lower_cpy(l);
+    if (op == "ARGMAX") return lower_argmax(l);
+    if (op == "CONCAT" || op == "REPEAT" || op == "SUM_ROWS" || op == "MEAN" || op == "ARANGE") return lower_simple(l);
+    if (op == "MUL_MAT") return lower_mul_mat(l);
+    if (op == "CUSTOM") return lower_custom(l);
+    unsupported(t, "op not implemented in the native CUDA backend");
+}
+
+// ---------------------------------------------------------------------------- IR rewrites
+// Readers of every root (views of a tensor count for the root), as fuse.rs:56-63 requires.
+void rewrite_graph(Graph &g) {
+    const size_t nt0 = g.tensors.size();
+    auto readers_of = [&](std::vector<int> &readers) {
+        readers.assign(g.tensors.size(), 0);
+        for (int32_t n : g.nodes) {
+            const Tensor &t = g.tensors[n];
+            for (int s : t.src)
+                if (s >= 0) readers[g.root(s)]++;
+        }
+        for (int32_t k : g.keep) readers[g.root(k)] += 2;  // kept tensors never fuse away
+    };
+    std::vector<int> readers;
+    readers_of(readers);
+    std::vector<int> pos_of(nt0, -1);
+    for (size_t i = 0; i < g.nodes.size(); i++) pos_of[g.nodes[i]] = (int)i;
+    std::vector<char> dead(g.nodes.size(), 0);
+    const char *nf = getenv("TL_NATIVE_NOFUSE");
+    const std::string nofuse = nf ? nf : "";
+    auto enabled = [&](const char *name) { return nofuse.find(name) == std::string::npos; };
+
+    for (size_t i = 0; i < g.nodes.size(); i++) {
+        const int32_t id = g.nodes[i];
+        Tensor &t = g.tensors[id];
+        if (t.op != "MUL" || t.view_src >= 0) continue;
+        // RMS_NORM + MUL -> RMS_NORM_MUL (fuse.rs:88-113)
+        for (int side = 0; side < 2 && enabled("RMS_NORM_MUL"); side++) {
+            const int32_t a = t.src[side], w = t.src[1 - side];
+            if (a < 0 || w < 0) continue;
+            Tensor &n = g.tensors[a];
+            if (n.op != "RMS_NORM" || n.view_src >= 0 || readers[a] != 1 || pos_of[a] < 0 || dead[pos_of[a]]) continue;
+            const Tensor &tw = g.tensors[w];
+            if (t.ty != 0 || n.ty != 0 || tw.ty != 0 || !t.is_contiguous() || tw.nb[0] != 4) continue;
+            bool same = true;
+            for (int k = 0; k < 4; k++) same = same && t.ne[k] == n.ne[k];
+            if (!same || tw.ne[0] == 0 || n.ne[0] % tw.ne[0] != 0) continue;
+            bool bc = true;
+            for (int k = 1; k < 4; k++) bc = bc && tw.ne[k] != 0 && t.ne[k] % tw.ne[k] == 0;
+            if (!bc || n.src[0] < 0 || g.tensors[n.src[0]].nb[0] != 4) continue;
+            t.op = "RMS_NORM_MUL";
+            t.op_params[15] = n.op_params[0];  // eps moves to slot 15
+            t.src[0] = n.src[0];
+            t.src[1] = w;
+            dead[pos_of[a]] = 1;
+            break;
+        }
+        if (t.op != "MUL") continue;
+        // act(g) * u -> GLU (the gated MLP of stdlib/nn.ss; FUSED_GU of fuse_tree.rs without the matmuls)
+        for (int side = 0; side < 2 && enabled("GLU"); side++) {
+            const int32_t a = t.src[side], u = t.src[1 - side];
+            if (a < 0 || u < 0) continue;
+            const Tensor &n = g.tensors[a];
+            if (n.op != "UNARY" || n.view_src >= 0 || readers[a] != 1 || pos_of[a] < 0 || dead[pos_of[a]]) continue;
+            int glu = -1;
+            switch (n.op_params[0]) {
+                case 6: glu = 0; break;   // RELU  -> REGLU
+                case 8: glu = 1; break;   // GELU  -> GEGLU
+                case 10: glu = 2; break;  // SILU  -> SWIGLU
+                case 16: glu = 4; break;  // GELU_ERF
+                case 9: glu = 5; break;   // GELU_QUICK
+            }
+            const int32_t gsrc = n.src[0];
+            if (glu < 0 || gsrc < 0) continue;
+            const Tensor &tg = g.tensors[gsrc], &tu = g.tensors[u];
+            if (t.ty != 0 || tg.ty != 0 || tu.ty != 0 || !t.is_contiguous() || !tg.is_contiguous() || !tu.is_contiguous()) continue;
+            bool same = true;
+            for (int k = 0; k < 4; k++) same = same && t.ne[k] == tg.ne[k] && t.ne[k] == tu.ne[k];
+            if (!same) continue;
+            t.op = "GLU";
+            for (int k = 0; k < 16; k++) t.op_params[k] = 0;
+            t.op_params[0] = glu;
+            t.src[0] = gsrc;
+            t.src[1] = u;
+            dead[pos_of[a]] = 1;
+            break;
+        }
+    }
+
+    // Quantize each distinct activation once: a QUANT_ACT node in front of the first quantized
+    // MUL_MAT that reads it, shared by later ones until something writes its storage again.
+    std::vector<int32_t> nodes;
+    std::map<std::pair<int32_t, int>, int32_t> cache;  // (activation tensor, kind) -> QUANT_ACT tensor
+    for (size_t i = 0; i < g.nodes.size(); i++) {
+        if (dead[i]) continue;
+        const int32_t id = g.nodes[i];
+        {
+            // a node that writes into storage an activation lives in invalidates its quantized copy
+            const int32_t root = g.root(id);
+            for (auto it = cache.begin(); it != cache.end();) {
+                if (g.root(it->first.first) == root && !g.tensors[id].is_view_op()) it = cache.erase(it);
+                else ++it;
+            }
+        }
+        Tensor &t = g.tensors[id];
+        if (t.op == "MUL_MAT" && t.src[0] >= 0 && t.src[1] >= 0 && gemv_type(g.tensors[t.src[0]].ty)) {
+            const Tensor &tw = g.tensors[t.src[0]];
+            const int32_t x = t.src[1];
+            const Tensor tx = g.tensors[x];
+            const int kind = act_kind_for(tw.ty);
+            const int64_t blk = kind == ACT_Q8_K ? 256 : 32;
+            bool ok = tx.ty == 0 && tx.nb[0] == 4 && tx.ne[0] % blk == 0 && tx.nelements() > 0 && tx.nb[1] % 16 == 0;
+            // columns must be uniformly strided
+            if (ok && tx.ne[2] > 1) ok = tx.nb[2] == tx.nb[1] * (uint64_t)tx.ne[1];
+            if (ok && tx.ne[3] > 1) ok = tx.nb[3] == tx.nb[1] * (uint64_t)tx.ne[1] * (uint64_t)tx.ne[2];
+            if (ok) {
+                auto key = std::make_pair(x, kind);
+                auto it = cache.find(key);
+                int32_t qa;
+                if (it != cache.end()) {
+                    qa = it->second;
+                } else {
+                    Tensor q;
+                    q.ty = TLB_TYPE_I8;
+                    q.op = "QUANT_ACT";
+                    q.op_params[0] = kind;
+                    q.src[0] = x;
+                    q.opaque_bytes = act_layout(kind, tx.ne[0], tx.nrows()).bytes;
+                    q.ne[0] = (int64_t)q.opaque_bytes;
+                    q.nb[0] = 1;
+                    q.nb[1] = q.nb[2] = q.nb[3] = q.opaque_bytes;
+                    q.name = tx.name + ".q8";
+                    qa = (int32_t)g.tensors.size();
+                    g.tensors.push_back(q);
+                    nodes.push_back(qa);
+                    cache[key] = qa;
+                }
+                g.tensors[id].src[2] = qa;
+            }
+        }
+        nodes.push_back(id);
+    }
+    g.nodes.swap(nodes);
+}
+
+}  // namespace tlb

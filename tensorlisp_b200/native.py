@@ -1,0 +1,249 @@
+"""Host-side mirror of the reference's native glue (crates/tensorlisp/src/native_cuda.rs:28-168):
+``Native`` (device, one weight buffer, the model's state block), ``StateBlock`` (one session's
+state) and ``NativeProgram`` (a compiled graph), with the same method names and error behaviour,
+forwarding to the C ABI of include/tlb200.h. Nothing here computes; every number comes from the
+CUDA library.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import TlbError, check
+from .graph import Graph, TYPE_TRAITS, align256
+
+__all__ = ["Native", "NativeProgram", "StateBlock", "TlbError", "quantize_rows", "row_size"]
+
+_NP_OF = {0: np.float32, 1: np.float16, 26: np.int32, 27: np.int64, 24: np.int8, 25: np.int16}
+
+
+def row_size(ty: int, ne0: int) -> int:
+    return int(_lib.lib().tlb_row_size(ty, ne0))
+
+
+class StateBlock:
+    """One session's state tensors, laid out like the model's own (native_cuda.rs:29-30)."""
+
+    def __init__(self, handle: C.c_void_p) -> None:
+        self.h = handle
+
+    def free(self) -> None:
+        if self.h:
+            _lib.lib().tlb_buffer_free(self.h)
+            self.h = None
+
+    def __del__(self) -> None:
+        try:
+            self.free()
+        except Exception:
+            pass
+
+    def write(self, offset: int, data: np.ndarray) -> None:
+        data = np.ascontiguousarray(data)
+        check(_lib.lib().tlb_buffer_write(self.h, offset, data.ctypes.data_as(C.c_void_p), data.nbytes))
+
+    def read(self, offset: int, nbytes: int) -> np.ndarray:
+        out = np.empty(nbytes, np.uint8)
+        check(_lib.lib().tlb_buffer_read(self.h, offset, out.ctypes.data_as(C.c_void_p), nbytes))
+        return out
+
+    @property
+    def size(self) -> int:
+        return int(_lib.lib().tlb_buffer_size(self.h))
+
+    @property
+    def device_ptr(self) -> int:
+        return int(_lib.lib().tlb_buffer_device_ptr(self.h) or 0)
+
+
+class Native:
+    """Weights, states and the device of one model (native_cuda.rs:32-127)."""
+
+    def __init__(self, ordinal: int = 0) -> None:
+        self.L = _lib.lib()
+        h = C.c_void_p()
+        check(self.L.tlb_device_open(ordinal, C.byref(h)))
+        self.dev = h
+        self.weights: StateBlock | None = None
+        self.weight_loc: list[tuple[int, int]] = []   # weight index -> (buffer index, byte offset)
+        self.state: StateBlock | None = None
+        self.state_offsets: list[int] = []
+
+    # Native::load (native_cuda.rs:44-82): one buffer, each tensor at a 256-byte aligned offset
+    @classmethod
+    def load(cls, weights: list[np.ndarray], ordinal: int = 0) -> "Native":
+        n = cls(ordinal)
+        total = 0
+        for w in weights:
+            n.weight_loc.append((0, total))
+            total += align256(max(int(w.nbytes), 1))
+        h = C.c_void_p()
+        check(n.L.tlb_weights_create(n.dev, max(total, 1), C.byref(h)))
+        n.weights = StateBlock(h)
+        for w, (_, off) in zip(weights, n.weight_loc):
+            w = np.ascontiguousarray(w)
+            check(n.L.tlb_buffer_write(h, off, w.ctypes.data_as(C.c_void_p), w.nbytes))
+        return n
+
+    # alloc_states (native_cuda.rs:85-98): one zeroed buffer for all state tensors
+    def alloc_states(self, nbytes_per_state: list[int]) -> None:
+        total = 0
+        self.state_offsets = []
+        for b in nbytes_per_state:
+            self.state_offsets.append(total)
+            total += align256(b)
+        self.state = self._zeroed(max(total, 1))
+
+    def _zeroed(self, nbytes: int) -> StateBlock:
+        h = C.c_void_p()
+        check(self.L.tlb_state_create(self.dev, nbytes, C.byref(h)))
+        return StateBlock(h)
+
+    def reset_state(self) -> None:
+        check(self.L.tlb_state_zero(self.state.h))
+
+    def new_state_block(self) -> StateBlock:
+        return self._zeroed(self.state.size if self.state else 1)
+
+    def fork_block(self, block: StateBlock) -> StateBlock:
+        h = C.c_void_p()
+        check(self.L.tlb_state_fork(block.h, C.byref(h)))
+        return StateBlock(h)
+
+    def reset_block(self, block: StateBlock) -> None:
+        check(self.L.tlb_state_zero(block.h))
+
+    def device_name(self) -> str:
+        buf = C.create_string_buffer(256)
+        check(self.L.tlb_device_name(self.dev, buf, 256))
+        return buf.value.decode()
+
+    def sm_count(self) -> int:
+        return int(self.L.tlb_device_sm_count(self.dev))
+
+    def stream(self) -> int:
+        return int(self.L.tlb_device_stream(self.dev) or 0)
+
+    def sync(self) -> None:
+        check(self.L.tlb_device_sync(self.dev))
+
+    def comm_init(self, n_ranks: int, rank: int, unique_id: bytes | None) -> None:
+        buf = C.create_string_buffer(unique_id, 128) if unique_id is not None else None
+        check(self.L.tlb_comm_init(self.dev, n_ranks, rank, buf))
+
+    @staticmethod
+    def comm_unique_id() -> bytes:
+        buf = C.create_string_buffer(128)
+        check(_lib.lib().tlb_comm_unique_id(buf))
+        return buf.raw
+
+    def close(self) -> None:
+        for b in (self.weights, self.state):
+            if b:
+                b.free()
+        self.weights = self.state = None
+        if self.dev:
+            self.L.tlb_device_close(self.dev)
+            self.dev = None
+
+
+class NativeProgram:
+    """A compiled graph with what is needed to feed and read it (native_cuda.rs:129-168)."""
+
+    def __init__(self, native: Native, handle: C.c_void_p, graph: Graph, outputs: list[tuple[str, int]]) -> None:
+        self.native = native
+        self.h = handle
+        self.graph = graph
+        self._outputs = outputs
+
+    @classmethod
+    def compile(cls, native: Native, graph: Graph, outputs: list[tuple[str, int]] | None = None) -> "NativeProgram":
+        outputs = outputs if outputs is not None else [(graph.tensors[t].name, t) for t in graph.keep]
+        for _, t in outputs:
+            if t not in graph.keep:
+                graph.keep.append(t)
+        g, keep = graph.to_c()
+        nw, ns = len(native.weight_loc), len(native.state_offsets)
+        wb = (C.c_uint32 * max(nw, 1))(*[b for b, _ in native.weight_loc])
+        wo = (C.c_uint64 * max(nw, 1))(*[o for _, o in native.weight_loc])
+        so = (C.c_uint64 * max(ns, 1))(*native.state_offsets)
+        leaves = _lib.tlb_leaves(wb, wo, nw, so, ns)
+        h = C.c_void_p()
+        err = C.create_string_buffer(4096)
+        st = native.L.tlb_program_compile(native.dev, C.byref(g), C.byref(leaves), C.byref(h), err, 4096)
+        del keep
+        if st != 0:
+            raise TlbError(st, err.value.decode(errors="replace"))
+        return cls(native, h, graph, outputs)
+
+    def set_input(self, i: int, data: np.ndarray | bytes) -> None:
+        if isinstance(data, (bytes, bytearray)):
+            data = np.frombuffer(data, np.uint8)
+        data = np.ascontiguousarray(data)
+        check(self.native.L.tlb_program_set_input(self.h, i, data.ctypes.data_as(C.c_void_p), data.nbytes))
+
+    def _buffers(self, state: StateBlock | None):
+        st = state if state is not None else self.native.state
+        w = self.native.weights
+        arr = (C.c_void_p * 1)(w.h if w else None)
+        return arr, (1 if w else 0), (st.h if st else None)
+
+    def run(self, state: StateBlock | None = None) -> None:
+        arr, n, st = self._buffers(state)
+        check(self.native.L.tlb_program_run(self.h, arr, n, st))
+
+    def enqueue(self, state: StateBlock | None = None) -> None:
+        arr, n, st = self._buffers(state)
+        check(self.native.L.tlb_program_enqueue(self.h, arr, n, st))
+
+    def read(self, tensor: int, dtype=None) -> np.ndarray:
+        """The tensor's bytes as an array of its own element type, in ndarray (outermost first) order."""
+        T = self.graph.tensors[tensor]
+        n = T.nbytes()
+        out = np.empty(n, np.uint8)
+        check(self.native.L.tlb_program_read(self.h, tensor, n, out.ctypes.data_as(C.c_void_p)))
+        dt = dtype or _NP_OF.get(T.ty)
+        if dt is None:
+            return out
+        return out.view(dt).reshape([d for d in reversed(T.ne)])
+
+    def outputs(self) -> list[tuple[str, np.ndarray]]:
+        return [(name, self.read(t)) for name, t in self._outputs]
+
+    def dispatch_count(self) -> int:
+        return int(self.native.L.tlb_program_dispatch_count(self.h))
+
+    def labels(self) -> list[str]:
+        return [self.native.L.tlb_program_label(self.h, i).decode() for i in range(self.dispatch_count())]
+
+    def tensor_ptr(self, tensor: int) -> tuple[int, int]:
+        n = C.c_uint64()
+        p = self.native.L.tlb_program_tensor_ptr(self.h, tensor, C.byref(n))
+        return int(p or 0), int(n.value)
+
+    def arena_bytes(self) -> int:
+        return int(self.native.L.tlb_program_arena_bytes(self.h))
+
+    def free(self) -> None:
+        if self.h:
+            self.native.L.tlb_program_free(self.h)
+            self.h = None
+
+    def __del__(self) -> None:
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+def quantize_rows(native: Native, ty: int, x: np.ndarray) -> np.ndarray:
+    """DType::from_f32 (crates/tensorlisp/src/dtype.rs:98-124): f32 [rows, n] -> blocks [rows, row bytes]."""
+    x = np.ascontiguousarray(x, np.float32)
+    rows, n = x.shape
+    name, blck, size = TYPE_TRAITS[ty]
+    out = np.zeros((rows, size * n // blck if n % blck == 0 else 0), np.uint8)
+    check(native.L.tlb_quantize_rows(native.dev, ty, x.ctypes.data_as(C.c_void_p), rows, n,
+                                     out.ctypes.data_as(C.c_void_p)))
+    return out

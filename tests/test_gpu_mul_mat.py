@@ -1,0 +1,111 @@
+"""MUL_MAT through compiled programs against the oracle (= the reference's CPU backend semantics:
+activations quantized to Q8_0 / Q8_K, integer block dots, f32 scaling).
+Bar: max|got-want| <= 1e-3 * max|want| (BASELINE north_star); observed ~1e-6 (summation order)."""
+import os
+
+import numpy as np
+import pytest
+
+from helpers import Model, close
+from oracle.bindings import F16, F32, Q4_0, Q4_K, Q8_0
+from tensorlisp_b200 import graph as G
+from tensorlisp_b200.native import TlbError
+
+pytestmark = pytest.mark.gpu
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "golden.npz"))
+TYPES = [(Q8_0, "q8_0"), (Q4_0, "q4_0"), (Q4_K, "q4_K")]
+TOL = 1e-3
+
+
+def mm_model(ty, K, M, N, Wq):
+    g = G.Graph()
+    w = g.weight(ty, [K, M], "W")
+    x = g.input(G.F32, [K, N], "x")
+    y = g.output(g.mul_mat(w, x, "y"))
+    return Model(g, [Wq]), y
+
+
+@pytest.mark.parametrize("ty,name", TYPES)
+def test_golden(ty, name, oracle):
+    Wq = oracle.quantize(ty, GOLD["mm_w"])
+    m, _ = mm_model(ty, 512, 24, 5, Wq)
+    (y,) = m.run(GOLD["mm_x"])
+    close(y, GOLD["mm_y_" + name], TOL)
+    m.close()
+
+
+@pytest.mark.parametrize("ty,name", TYPES)
+@pytest.mark.parametrize("K,M", [(4096, 512), (14336, 64), (256, 96), (1024, 7)])
+@pytest.mark.parametrize("N", [1, 2, 3, 5, 8, 9, 16, 40])
+def test_shapes(oracle, ty, name, K, M, N):
+    rng = np.random.default_rng(K + M + N)
+    W = (rng.standard_normal((M, K)) * 0.02).astype(np.float32)
+    X = rng.standard_normal((N, K)).astype(np.float32)
+    Wq = oracle.quantize(ty, W)
+    m, _ = mm_model(ty, K, M, N, Wq)
+    (y,) = m.run(X)
+    err = close(y, oracle.mul_mat(ty, Wq, K, X), TOL)
+    assert err <= 2e-5 * np.abs(y).max() + 1e-6   # only the f32 summation order differs
+    # and it is the reference's arithmetic, not dequantize-then-f32: that differs by ~5e-3
+    m.close()
+
+
+def test_config1_q8_0_4096(oracle):
+    """BASELINE config 1: W 4096x4096 N(0,0.02) seed 0 -> Q8_0, x N(0,1) seed 1, batch 1 and 16."""
+    W = (np.random.default_rng(0).standard_normal((4096, 4096)) * 0.02).astype(np.float32)
+    Wq = oracle.quantize(Q8_0, W)
+    for N in (1, 16):
+        X = np.random.default_rng(1).standard_normal((N, 4096)).astype(np.float32)
+        m, _ = mm_model(Q8_0, 4096, 4096, N, Wq)
+        (y,) = m.run(X)
+        close(y, oracle.mul_mat(Q8_0, Wq, 4096, X), TOL)
+        m.close()
+
+
+def test_linearity_full_size(oracle):
+    """Size-independent property at a BASELINE shape (Q4_K 4096->14336): scaling the activations by
+    a power of two scales the result exactly (quantization commutes with powers of two)."""
+    rng = np.random.default_rng(11)
+    W = (rng.standard_normal((14336, 4096)) * 0.02).astype(np.float32)
+    from tensorlisp_b200.native import Native, quantize_rows
+    n = Native(0)
+    Wq = quantize_rows(n, Q4_K, W)
+    n.close()
+    X = rng.standard_normal((2, 4096)).astype(np.float32)
+    m, _ = mm_model(Q4_K, 4096, 14336, 2, Wq)
+    (y1,) = m.run(X)
+    (y2,) = m.run(X * 4.0)
+    assert np.array_equal(y1 * 4.0, y2)
+    rows = rng.integers(0, 14336, 64)
+    close(y1[:, rows], oracle.mul_mat(Q4_K, Wq[rows], 4096, X), TOL)
+    m.close()
+
+
+@pytest.mark.parametrize("ty", [F32, F16])
+def test_plain_weights_and_batches(oracle, ty):
+    """f32/f16 weights with a broadcast batch (ne2 = 2 of weights vs 4 of activations)."""
+    rng = np.random.default_rng(5)
+    K, M, N = 64, 10, 3
+    W = rng.standard_normal((2, M, K)).astype(np.float32)
+    X = rng.standard_normal((4, N, K)).astype(np.float32)
+    g = G.Graph()
+    w = g.weight(ty, [K, M, 2], "W")
+    x = g.input(G.F32, [K, N, 4], "x")
+    y = g.output(g.mul_mat(w, x))
+    Wd = W.astype(np.float16) if ty == F16 else W
+    m = Model(g, [Wd])
+    (got,) = m.run(X)
+    want = np.einsum("bmk,bnk->bnm", Wd.astype(np.float64)[[0, 0, 1, 1]], X.astype(np.float64))
+    close(got.reshape(4, N, M), want, 1e-5)
+    m.close()
+
+
+def test_ragged_k_is_reported_by_name():
+    g = G.Graph()
+    w = g.weight(G.F32, [100, 4], "W")
+    x = g.input(G.I32, [100, 2], "x")
+    g.tensors[x].ty = G.I32
+    y = g.output(g.mul_mat(w, x, "y"))
+    with pytest.raises(TlbError) as e:
+        Model(g, [np.zeros((4, 100), np.float32)])
+    assert "MUL_MAT" in str(e.value) and "not implemented" in str(e.value)

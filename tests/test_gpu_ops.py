@@ -1,0 +1,244 @@
+"""Row / elementwise / gather ops of a decoder graph through compiled programs, against the oracle
+and the golden vectors (reference test model: crates/tensorlisp/tests/native.rs, tolerances
+:108-153 norms 1e-4, :251-278 rope/argmax 1e-5)."""
+import os
+
+import numpy as np
+import pytest
+
+from helpers import Model, close
+from oracle.bindings import Q8_0
+from tensorlisp_b200 import graph as G
+from tensorlisp_b200.native import TlbError
+
+pytestmark = pytest.mark.gpu
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "golden.npz"))
+
+
+def test_rms_norm_mul_fused_and_unfused(oracle, monkeypatch):
+    x, w = GOLD["row_x"], GOLD["row_w"]
+    for nofuse in ("", "1"):
+        if nofuse:
+            monkeypatch.setenv("TL_NATIVE_NOFUSE", nofuse)
+        g = G.Graph()
+        tx = g.input(G.F32, [384, 6], "x")
+        tw = g.weight(G.F32, [384], "w")
+        y = g.output(g.mul(g.rms_norm(tx, 1e-5), tw, "y"))
+        n = g.output(g.rms_norm(tx, 1e-6, "n"))
+        m = Model(g, [w])
+        labels = m.program.labels()
+        assert len(labels) == (3 if nofuse else 2), labels
+        got_y, got_n = m.run(x)
+        close(got_y, GOLD["row_rms_mul"], 1e-5)
+        close(got_n, GOLD["row_rms"], 1e-5)
+        m.close()
+
+
+def test_norm_second_reader_blocks_fusion():
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((4, 64)).astype(np.float32)
+    w = rng.standard_normal(64).astype(np.float32)
+    g = G.Graph()
+    tx = g.input(G.F32, [64, 4])
+    tw = g.weight(G.F32, [64])
+    n = g.rms_norm(tx, 1e-5)
+    y = g.output(g.mul(n, tw))
+    z = g.output(g.add(n, tx))
+    m = Model(g, [w])
+    assert len(m.program.labels()) == 3
+    gy, gz = m.run(x)
+    nn = x / np.sqrt((x.astype(np.float64) ** 2).mean(axis=1, keepdims=True) + 1e-5)
+    close(gy, nn * w, 1e-5)
+    close(gz, nn + x, 1e-5)
+    m.close()
+
+
+def test_narrow_weight_repeats_across_the_row():
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((3, 128)).astype(np.float32)
+    w = rng.standard_normal(32).astype(np.float32)
+    g = G.Graph()
+    tx = g.input(G.F32, [128, 3])
+    tw = g.weight(G.F32, [32])
+    y = g.output(g.mul(g.rms_norm(tx, 1e-5), tw))
+    m = Model(g, [w])
+    (gy,) = m.run(x)
+    nn = x / np.sqrt((x.astype(np.float64) ** 2).mean(axis=1, keepdims=True) + 1e-5)
+    close(gy, nn * np.tile(w, 4), 1e-5)
+    m.close()
+
+
+@pytest.mark.parametrize("style", ["unary_mul", "glu_split", "glu_packed"])
+def test_silu_gate(oracle, style):
+    x, u = GOLD["row_x"], GOLD["row_u"]
+    g = G.Graph()
+    if style == "glu_packed":
+        t = g.input(G.F32, [768, 6], "xu")
+        y = g.output(g.glu(t, "swiglu"))
+        m = Model(g)
+        (got,) = m.run(np.concatenate([x, u], axis=1))
+    else:
+        tx = g.input(G.F32, [384, 6], "x")
+        tu = g.input(G.F32, [384, 6], "u")
+        y = g.output(g.mul(g.silu(tx), tu) if style == "unary_mul" else g.glu(tx, "swiglu", b=tu))
+        m = Model(g)
+        if style == "unary_mul":
+            assert len(m.program.labels()) == 1  # SiLU and the product are one launch
+        (got,) = m.run(x, u)
+    close(got, GOLD["row_silu_mul"], 1e-5)
+    m.close()
+
+
+@pytest.mark.parametrize("mode,name,nd,base", [(2, "rope_neox", 128, 500000.0), (0, "rope_normal", 128, 500000.0), (2, "rope_neox_partial", 64, 10000.0)])
+def test_rope(mode, name, nd, base):
+    x, pos = GOLD["rope_x"], GOLD["rope_pos"]
+    g = G.Graph()
+    tx = g.input(G.F32, [128, 3, 5], "x")
+    tp = g.input(G.I32, [5], "pos")
+    y = g.output(g.rope_ext(tx, tp, None, nd, mode, 0, base, 1.0, 0.0, 1.0, 32.0, 1.0))
+    m = Model(g)
+    (got,) = m.run(x, pos)
+    close(got.reshape(5, 3, 128), GOLD[name], 1e-5)
+    m.close()
+
+
+def test_soft_max_scale_argmax_add():
+    x = GOLD["row_x"]
+    g = G.Graph()
+    tx = g.input(G.F32, [384, 6], "x")
+    sm = g.output(g.soft_max_ext(tx, None, 0.25))
+    am = g.output(g.argmax(tx))
+    sc = g.output(g.scale(tx, 0.5, 0.25))
+    ad = g.output(g.add(tx, sc))
+    m = Model(g)
+    gsm, gam, gsc, gad = m.run(x)
+    close(gsm, GOLD["row_softmax"], 1e-5)
+    assert np.array_equal(gam, GOLD["row_argmax"])
+    close(gsc, x * 0.5 + 0.25, 1e-6)
+    close(gad, x + (x * 0.5 + 0.25), 1e-6)
+    m.close()
+
+
+def test_argmax_ties_pick_the_last_index():
+    g = G.Graph()
+    tx = g.input(G.F32, [40, 3])
+    am = g.output(g.argmax(tx))
+    m = Model(g)
+    (got,) = m.run(GOLD["ties_x"])
+    assert np.array_equal(got, GOLD["ties_argmax"])
+    m.close()
+
+
+def test_masked_soft_max():
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((2, 5, 64)).astype(np.float32)       # [heads, rows, n]
+    mask = np.where(rng.random((5, 64)) < 0.3, -np.inf, 0).astype(np.float16)
+    mask[:, 0] = 0
+    g = G.Graph()
+    tx = g.input(G.F32, [64, 5, 2])
+    tm = g.input(G.F16, [64, 5])
+    y = g.output(g.soft_max_ext(tx, tm, 0.5))
+    m = Model(g)
+    (got,) = m.run(x, mask)
+    z = x.astype(np.float64) * 0.5 + mask.astype(np.float64)
+    e = np.exp(z - z.max(axis=-1, keepdims=True))
+    close(got, e / e.sum(axis=-1, keepdims=True), 1e-5)
+    m.close()
+
+
+def test_get_rows_q8_0_table(oracle):
+    tab = oracle.quantize(Q8_0, GOLD["emb_table"])
+    g = G.Graph()
+    tt = g.weight(G.Q8_0, [256, 50], "emb")
+    ti = g.input(G.I32, [5], "ids")
+    y = g.output(g.get_rows(tt, ti))
+    m = Model(g, [tab])
+    (got,) = m.run(GOLD["emb_ids"])
+    assert np.array_equal(got, GOLD["emb_rows"])
+    m.close()
+
+
+def test_casts_and_permuted_copy():
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal((3, 4, 8)).astype(np.float32)
+    g = G.Graph()
+    tx = g.input(G.F32, [8, 4, 3])
+    h = g.cast(tx, G.F16)
+    back = g.output(g.cast(h, G.F32))
+    pc = g.output(g.cont(g.permute(tx, 0, 2, 1, 3)))
+    m = Model(g)
+    gb, gp = m.run(x)
+    assert np.array_equal(gb, x.astype(np.float16).astype(np.float32))
+    assert np.array_equal(gp, x.transpose(1, 0, 2))
+    m.close()
+
+
+def test_state_persists_and_sessions_are_separate():
+    """SET_ROWS into a state tensor survives runs; reset_state / new_state_block / fork_block behave
+    like the reference's sessions (crates/tensorlisp/tests/native.rs:436-468)."""
+    g = G.Graph()
+    cache = g.state(G.F16, [16, 8], "cache")
+    rows = g.input(G.F32, [16, 2], "rows")
+    ids = g.input(G.I64, [2], "ids")
+    wr = g.set_rows(cache, rows, ids)
+    out = g.output(g.cast(wr, G.F32))
+    m = Model(g, state_bytes=[16 * 8 * 2])
+    r1 = np.arange(32, dtype=np.float32).reshape(2, 16)
+    (a,) = m.run(r1, np.array([1, 5], np.int64))
+    assert np.array_equal(a[1], r1[0]) and np.array_equal(a[5], r1[1]) and not a[0].any()
+    (b,) = m.run(r1 + 100, np.array([0, 7], np.int64))
+    assert np.array_equal(b[1], r1[0]) and np.array_equal(b[0], r1[0] + 100)   # first write still there
+    other = m.native.new_state_block()
+    (c,) = m.run(r1, np.array([2, 3], np.int64), state=other)
+    assert not c[1].any() and np.array_equal(c[2], r1[0])                        # a fresh session is zeroed
+    fork = m.native.fork_block(other)
+    (d,) = m.run(r1 + 1, np.array([4, 6], np.int64), state=fork)
+    assert np.array_equal(d[2], r1[0]) and np.array_equal(d[4], r1[0] + 1)
+    m.native.reset_state()
+    (e,) = m.run(r1, np.array([-1, 7], np.int64))
+    assert not e[:7].any() and np.array_equal(e[7], r1[1])                       # negative row ids are skipped
+    m.close()
+
+
+def test_unsupported_op_is_reported_by_name():
+    """crates/tensorlisp/tests/native.rs:240-249: CUMSUM + "not implemented"."""
+    g = G.Graph()
+    tx = g.input(G.F32, [8, 2])
+    a = g.cumsum(tx, "c1")
+    b = g.cumsum(a, "c2")
+    y = g.output(g.add(b, tx))
+    with pytest.raises(TlbError) as e:
+        Model(g)
+    msg = str(e.value)
+    assert msg.startswith("native CUDA: not implemented: CUMSUM x2 (e.g. c1:"), msg
+    assert e.value.kind == "Unsupported"
+
+
+def test_input_size_is_checked():
+    g = G.Graph()
+    tx = g.input(G.F32, [8, 2])
+    y = g.output(g.scale(tx, 2.0))
+    m = Model(g)
+    with pytest.raises(TlbError) as e:
+        m.program.set_input(0, np.zeros(15, np.float32))
+    assert str(e.value) == "input 0 takes 64 bytes, got 60"
+    with pytest.raises(TlbError):
+        m.program.set_input(3, np.zeros(16, np.float32))
+    m.close()
+
+
+def test_empty_tensors_launch_nothing():
+    g = G.Graph()
+    tx = g.input(G.F32, [8, 0])
+    y = g.output(g.scale(tx, 2.0))
+    m = Model(g)
+    assert m.program.dispatch_count() == 0
+    m.program.run()
+    m.close()
+
+
+def test_device_name():
+    from tensorlisp_b200.native import Native
+    n = Native(0)
+    assert n.device_name().startswith("native ")
+    n.close()

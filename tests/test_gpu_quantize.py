@@ -1,0 +1,61 @@
+"""GPU row quantizers through the C ABI (tlb_quantize_rows) against the oracle and the golden
+vectors: bit-exact bytes (reference: crates/tensorlisp/src/dtype.rs:98-124 -> ggml_quantize_chunk)."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle.bindings import Q4_0, Q4_K, Q8_0
+from tensorlisp_b200.native import TlbError, quantize_rows
+
+pytestmark = pytest.mark.gpu
+G = np.load(os.path.join(os.path.dirname(__file__), "golden", "golden.npz"))
+TYPES = [(Q8_0, "q8_0"), (Q4_0, "q4_0"), (Q4_K, "q4_K")]
+
+
+@pytest.mark.parametrize("ty,name", TYPES)
+def test_golden_bytes(native, ty, name):
+    got = quantize_rows(native, ty, G["quant_x"])
+    assert np.array_equal(got, G["quant_" + name])
+
+
+@pytest.mark.parametrize("ty,name", TYPES)
+@pytest.mark.parametrize("shape,scale,seed", [((64, 4096), 0.02, 0), ((8, 14336), 0.02, 3), ((33, 256), 1.0, 4), ((5, 1024), 50.0, 5)])
+def test_against_oracle(native, oracle, ty, name, shape, scale, seed):
+    rng = np.random.default_rng(seed)
+    x = (rng.standard_normal(shape) * scale).astype(np.float32)
+    x[0, :256] = 0.0          # an all-zero super-block
+    x[-1, :32] = 0.25         # a constant block
+    assert np.array_equal(quantize_rows(native, ty, x), oracle.quantize(ty, x))
+
+
+def test_config1_matrix_q8_0_bit_exact(native, oracle):
+    """BASELINE config 1: 4096x4096 N(0, 0.02) seed 0 -> Q8_0."""
+    x = (np.random.default_rng(0).standard_normal((4096, 4096)) * 0.02).astype(np.float32)
+    got = quantize_rows(native, Q8_0, x)
+    assert got.shape == (4096, 4352)
+    assert np.array_equal(got, oracle.quantize(Q8_0, x))
+
+
+def test_q4_K_full_rows_and_idempotence(native, oracle):
+    """Size-independent properties at full row lengths: quantizing the dequantized output again
+    reproduces the same codes' values (dequant is a fixed point of quantize o dequant for Q8_0)."""
+    x = (np.random.default_rng(7).standard_normal((512, 14336)) * 0.02).astype(np.float32)
+    q = quantize_rows(native, Q4_K, x)
+    assert np.array_equal(q, oracle.quantize(Q4_K, x))
+    q8 = quantize_rows(native, Q8_0, x)
+    d8 = oracle.dequantize(Q8_0, q8, 14336)
+    assert np.array_equal(oracle.dequantize(Q8_0, quantize_rows(native, Q8_0, d8), 14336), d8)
+    # the reconstruction error stays within half a quantization step of each block
+    step = np.abs(x).reshape(512, -1, 32).max(axis=2) / 127
+    assert np.all(np.abs(d8 - x).reshape(512, -1, 32).max(axis=2) <= step * 0.5 + 1e-6)
+
+
+def test_empty_and_bad_rows(native):
+    assert quantize_rows(native, Q8_0, np.zeros((0, 64), np.float32)).shape == (0, 68)
+    with pytest.raises(TlbError) as e:
+        quantize_rows(native, Q4_K, np.zeros((2, 100), np.float32))
+    assert "multiple of the block size" in str(e.value)
+    with pytest.raises(TlbError) as e:
+        quantize_rows(native, 14, np.zeros((2, 256), np.float32))  # q6_K is not implemented
+    assert "not implemented" in str(e.value)

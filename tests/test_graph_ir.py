@@ -1,0 +1,140 @@
+"""The product's graph builder against ggml's own constructors (reference:
+crates/tensorlisp/src/native_ir.rs:66-95 copies exactly these fields from a ggml_tensor)."""
+import numpy as np
+import pytest
+
+from tensorlisp_b200 import graph as G
+
+
+def build_both(ref, prog):
+    """prog(b) drives a small recorder that issues each call to both builders."""
+    g = G.Graph()
+    rg = ref.graph(64 << 20, 1)
+    pairs = []
+
+    class B:
+        def leaf(self, kind, ty, ne, name):
+            a = getattr(g, kind)(ty, ne, name)
+            b = rg.tensor(ty, ne, name)
+            pairs.append((a, b))
+            return (a, b)
+
+        def op(self, ours, theirs, srcs, ours_args=(), ints=(), floats=(), **kw):
+            a = getattr(g, ours)(*[s[0] if s is not None else None for s in srcs], *ours_args, **kw)
+            b = rg.op(theirs, [s[1] if s is not None else None for s in srcs], ints, floats)
+            pairs.append((a, b))
+            return (a, b)
+
+    prog(B())
+    return g, rg, pairs
+
+
+def compare(g, rg, pairs):
+    back = {b: a for a, b in pairs}
+    for a, b in pairs:
+        T, info = g.tensors[a], rg.info(b)
+        assert T.ty == info["ty"], (T.name, "type")
+        assert list(T.ne) == info["ne"], (T.op, T.name, "ne", T.ne, info["ne"])
+        assert list(T.nb) == info["nb"], (T.op, T.name, "nb", T.nb, info["nb"])
+        assert T.op == info["op"], (T.name, T.op, info["op"])
+        if T.op == "CUSTOM":  # slots 0,1 hold a function pointer (NULL), 4,5 the userdata
+            assert T.op_params[2] == info["op_params"][2] and T.op_params[4:6] == info["op_params"][4:6]
+        else:
+            assert list(T.op_params) == info["op_params"], (T.op, T.name, T.op_params, info["op_params"])
+        theirs_src = [back.get(s, -1) if s >= 0 else -1 for s in info["src"]]
+        assert list(T.src) == theirs_src, (T.op, T.name, T.src, theirs_src)
+        assert T.view_src == (back[info["view_src"]] if info["view_src"] >= 0 else -1), (T.op, T.name, "view_src")
+        assert T.view_offs == info["view_offs"], (T.op, T.name, "view_offs")
+
+
+def test_decoder_layer_ir_matches_ggml(ref):
+    d, heads, kvh, hd, ffn, T = 256, 4, 2, 64, 512, 3
+
+    def prog(b):
+        x = b.leaf("input", G.F32, [d, T], "x")
+        pos = b.leaf("input", G.I32, [T], "pos")
+        wn = b.leaf("weight", G.F32, [d], "attn_norm")
+        wq = b.leaf("weight", G.Q4_K, [d, heads * hd], "wq")
+        wk = b.leaf("weight", G.Q8_0, [d, kvh * hd], "wk")
+        wo = b.leaf("weight", G.Q4_0, [heads * hd, d], "wo")
+        wg = b.leaf("weight", G.Q4_K, [d, ffn], "wg")
+        wu = b.leaf("weight", G.Q4_K, [d, ffn], "wu")
+        wd = b.leaf("weight", G.Q4_K, [ffn, d], "wd")
+        n = b.op("rms_norm", "rms_norm", [x], (1e-5,), floats=[1e-5])
+        h = b.op("mul", "mul", [n, wn])
+        q = b.op("mul_mat", "mul_mat", [wq, h])
+        k = b.op("mul_mat", "mul_mat", [wk, h])
+        q3 = b.op("reshape", "reshape", [q], ([hd, heads, T],), ints=[hd, heads, T, 1])
+        k3 = b.op("reshape", "reshape", [k], ([hd, kvh, T],), ints=[hd, kvh, T, 1])
+        rope_o = (None, hd, 2, 0, 500000.0, 1.0, 0.0, 1.0, 32.0, 1.0)
+        qr = b.op("rope_ext", "rope_ext", [q3, pos], rope_o, ints=[hd, 2, 0], floats=[500000.0, 1.0, 0.0, 1.0, 32.0, 1.0])
+        kr = b.op("rope_ext", "rope_ext", [k3, pos], rope_o, ints=[hd, 2, 0], floats=[500000.0, 1.0, 0.0, 1.0, 32.0, 1.0])
+        qh = b.op("cast", "cast", [qr], (G.F16,), ints=[G.F16])
+        kh = b.op("cast", "cast", [kr], (G.F16,), ints=[G.F16])
+        qp = b.op("permute", "permute", [qr], (0, 2, 1, 3), ints=[0, 2, 1, 3])
+        kp = b.op("permute", "permute", [kr], (0, 2, 1, 3), ints=[0, 2, 1, 3])
+        kc = b.op("cont", "cont", [kp])
+        tr = b.op("transpose", "transpose", [x])
+        trc = b.op("cont", "cont", [tr])
+        a2 = b.op("reshape", "reshape", [qr], ([hd * heads, T],), ints=[hd * heads, T, 1, 1])
+        o = b.op("mul_mat", "mul_mat", [wo, a2])
+        x2 = b.op("add", "add", [x, o])
+        gt = b.op("mul_mat", "mul_mat", [wg, x2])
+        up = b.op("mul_mat", "mul_mat", [wu, x2])
+        s = b.op("unary", "unary", [gt], ("silu",), ints=[10])
+        m = b.op("mul", "mul", [s, up])
+        g2 = b.op("glu", "glu_split", [gt, up], ints=[2], op="swiglu", b=None) if False else None
+        dn = b.op("mul_mat", "mul_mat", [wd, m])
+        x3 = b.op("add", "add", [x2, dn])
+        sc = b.op("scale", "scale", [x3], (0.5, 0.25), floats=[0.5, 0.25])
+        sm = b.op("soft_max_ext", "soft_max_ext", [sc, None], (0.125, 0.0), floats=[0.125, 0.0])
+        am = b.op("argmax", "argmax", [sm])
+        v = b.op("view", "view", [x3], ([d // 2, T], d * 4, 0, 0, d * 2), ints=[d // 2, T, 1, 1, d * 4, d * 4 * T, d * 4 * T, d * 2])
+
+    g, rg, pairs = build_both(ref, prog)
+    compare(g, rg, pairs)
+
+
+def test_embedding_and_cache_ops_ir(ref):
+    def prog(b):
+        emb = b.leaf("weight", G.Q8_0, [256, 1000], "emb")
+        ids = b.leaf("input", G.I32, [5], "ids")
+        cache = b.leaf("state", G.F16, [64, 128], "cache")
+        rows = b.leaf("input", G.F32, [64, 5], "rows")
+        idx = b.leaf("input", G.I64, [5], "idx")
+        e = b.op("get_rows", "get_rows", [emb, ids])
+        s = b.op("set_rows", "set_rows", [cache, rows, idx])
+        c = b.op("cpy", "cpy", [rows, b.op("view", "view", [cache], ([64, 5], 128, 0, 0, 0), ints=[64, 5, 1, 1, 128, 640, 640, 0])])
+
+    g, rg, pairs = build_both(ref, prog)
+    compare(g, rg, pairs)
+
+
+def test_glu_and_paged_nodes_ir(ref):
+    scale = 1.0 / np.sqrt(128.0)
+
+    def prog(b):
+        a = b.leaf("input", G.F32, [512, 4], "a")
+        u = b.leaf("input", G.F32, [512, 4], "u")
+        q = b.leaf("input", G.F16, [128, 8, 3], "q")
+        kc = b.leaf("state", G.F16, [128 * 2 * 16, 10], "kc")
+        vc = b.leaf("state", G.F16, [128 * 2 * 16, 10], "vc")
+        tables = b.leaf("input", G.I32, [4, 3], "tables")
+        lens = b.leaf("input", G.I32, [3], "lens")
+        key = b.leaf("input", G.F16, [256, 3], "key")
+        val = b.leaf("input", G.F16, [256, 3], "val")
+        slots = b.leaf("input", G.I32, [6], "slots")
+        g1 = b.op("glu", "glu", [a], ("swiglu", False), ints=[2, 0])
+        g2 = b.op("glu", "glu", [a], ("geglu", True), ints=[1, 1])
+        ud1 = G.Graph.paged_userdata(1, 2, 16, 64, scale)
+        ud2 = G.Graph.paged_userdata(2, 2, 16, 1, 1.0)
+        p = b.op("paged_attention", "custom", [q, kc, vc, tables, lens], (16, 64, scale, 2), ints=[G.F16, 128, 8, 3, 1, ud1])
+        w = b.op("paged_cache_write", "custom", [key, val, kc, vc, slots], (16, 2), ints=[G.F16, 1, 1, 1, 1, ud2])
+
+    g, rg, pairs = build_both(ref, prog)
+    compare(g, rg, pairs)
+    g2 = G.Graph()
+    a = g2.input(G.F32, [512, 4], "a")
+    u = g2.input(G.F32, [512, 4], "u")
+    t = g2.glu(a, "swiglu", b=u)
+    assert g2.tensors[t].ne == [512, 4, 1, 1] and g2.tensors[t].src[:2] == [a, u]
