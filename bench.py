@@ -1,0 +1,412 @@
+"""Headline benchmark: batch-32 decode step of a random-init Llama-3-8B-shaped decoder with Q4_K
+weights (embeddings/output Q8_0) over a paged f16 KV cache at context 2048 (BASELINE config 4),
+through the C ABI of include/tlb200.h.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+N > 1 is launched by torchrun (one rank per GPU) and runs the tensor-parallel shard of the same
+step: column/row-parallel mul_mat, KV heads partitioned, one NCCL all-reduce after each
+row-parallel projection. Rank 0 prints ONE JSON line.
+
+`--impl reference` times the reference's own ggml CPU backend (oracle/_ref, built from the reference
+checkout) on the host cores on a bounded sample of the same workload; see cpu_reference_step().
+Synthetic data throughout: weights N(0, 0.02) quantized on the GPU, KV pages N(0, 1), token ids
+uniform over the vocabulary.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+BATCH = 32
+CONTEXT = 2048
+METRIC = "decode tok/s (8B-shape Q4_K, batch 32)"
+
+
+def measured_peaks() -> tuple[float, str]:
+    """HBM GB/s roofline denominator: the driver-measured copy bandwidth when present."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        self.index = index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self) -> None:
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------- our arm
+def build_model(rank: int, world: int, local_rank: int):
+    """Random-init 8B-shape decoder resident in HBM: weights drawn and quantized on the GPU into the
+    weight buffer, KV pools filled with N(0,1) f16 pages, one compiled decode-step program."""
+    import torch
+
+    from tensorlisp_b200.graph import F32, align256
+    from tensorlisp_b200.native import Native, NativeProgram, StateBlock
+    from tensorlisp_b200.programs import DecoderConfig, decoder_step
+    from tensorlisp_b200._lib import check
+
+    torch.cuda.set_device(local_rank)
+    cfg = DecoderConfig()
+    max_blocks = CONTEXT // cfg.block_size
+    pool_blocks = BATCH * max_blocks
+    dg = decoder_step(cfg, BATCH, CONTEXT, pool_blocks, tp=world)
+    native = Native(local_rank)
+    # ---- weights: one buffer, 256-byte aligned offsets (Native::load's layout)
+    total = 0
+    for s in dg.weights:
+        native.weight_loc.append((0, total))
+        total += align256(s.nbytes())
+    h = C.c_void_p()
+    check(native.L.tlb_weights_create(native.dev, total, C.byref(h)))
+    native.weights = StateBlock(h)
+    base = native.weights.device_ptr
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1234 + rank)
+    for s, (_, off) in zip(dg.weights, native.weight_loc):
+        if len(s.ne) == 1:
+            w = (1 + 0.1 * torch.randn(s.ne[0], generator=gen, device="cuda", dtype=torch.float32)).contiguous()
+            native.weights.copy_device(off, w.data_ptr(), w.numel() * 4)
+        else:
+            rows_left, done = s.ne[1], 0
+            row_bytes = s.nbytes() // s.ne[1]
+            while rows_left:
+                r = min(rows_left, 16384)
+                w = torch.randn((r, s.ne[0]), generator=gen, device="cuda", dtype=torch.float32) * 0.02
+                torch.cuda.synchronize()
+                check(native.L.tlb_quantize_rows_device(native.dev, s.ty, C.c_void_p(w.data_ptr()), r, s.ne[0],
+                                                        C.c_void_p(base + off + done * row_bytes)))
+                native.sync()
+                done += r
+                rows_left -= r
+    # ---- KV pools
+    native.alloc_states(dg.state_bytes)
+    for off, nbytes in zip(native.state_offsets, dg.state_bytes):
+        kv = torch.randn(nbytes // 2, generator=gen, device="cuda", dtype=torch.float16)
+        native.state.copy_device(off, kv.data_ptr(), nbytes)
+    del kv, w
+    torch.cuda.empty_cache()
+    prog = NativeProgram.compile(native, dg.graph)
+    return cfg, dg, native, prog, total
+
+
+def step_inputs(cfg, step: int, rng) -> list[np.ndarray]:
+    """Token ids uniform over the vocabulary; every sequence sits at position CONTEXT-1, so the step
+    attends over CONTEXT tokens. Block tables are a fixed random permutation of the pool."""
+    max_blocks = CONTEXT // cfg.block_size
+    ids = rng.integers(0, cfg.vocab, BATCH).astype(np.int32)
+    pos = np.full(BATCH, CONTEXT - 1, np.int32)
+    tables = np.random.default_rng(7).permutation(BATCH * max_blocks).astype(np.int32).reshape(BATCH, max_blocks)
+    lens = np.full(BATCH, CONTEXT, np.int32)
+    slots = (tables[:, (CONTEXT - 1) // cfg.block_size].astype(np.int64) * cfg.block_size
+             + (CONTEXT - 1) % cfg.block_size)
+    return [ids, pos, tables, lens, slots.view(np.int32)]
+
+
+def algorithmic_bytes(cfg, world: int) -> dict:
+    """Bytes one rank must move per step (SURVEY 8d figures, divided by the ranks)."""
+    from tensorlisp_b200.programs import decoder_weights
+    specs = decoder_weights(cfg, world)
+    w_layers = sum(s.nbytes() for s in specs if s.name.startswith("blk.") and len(s.ne) == 2)
+    w_head = [s for s in specs if s.name == "output"][0].nbytes()
+    kv = cfg.n_layers * BATCH * CONTEXT * (cfg.n_kv_heads // world) * cfg.head_dim * 2 * 2
+    return {"weights": w_layers + w_head, "w_layers": w_layers, "w_head": w_head, "kv": kv}
+
+
+def run_ours(args) -> dict:
+    import torch
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world)
+    cfg, dg, native, prog, weight_bytes = build_model(rank, world, local_rank)
+    if world > 1:
+        from tensorlisp_b200.native import Native
+        box = [Native.comm_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        native.comm_init(world, rank, box[0])
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        native.sync()
+
+    stream = torch.cuda.ExternalStream(native.stream())
+    rng = np.random.default_rng(100 + rank if world == 1 else 100)  # all ranks feed the same tokens
+    # pinned host copies of every step's inputs (the e2e leg copies them inside the timed region)
+    n_prepared = args.warmup + args.steps
+    pinned = []
+    for s in range(n_prepared):
+        arrs = step_inputs(cfg, s, rng)
+        pinned.append([torch.from_numpy(a.copy()).pin_memory() for a in arrs])
+    h2d = sum(t.numel() * t.element_size() for t in pinned[0])
+    tok_out = torch.empty(BATCH, dtype=torch.float32).pin_memory()
+    L = native.L
+
+    def feed(s):
+        for i, t in enumerate(pinned[s]):
+            prog.native.L.tlb_program_set_input(prog.h, i, C.c_void_p(t.data_ptr()), t.numel() * t.element_size())
+
+    # ---- device-resident leg: inputs already in HBM, K enqueued steps between two events
+    feed(0)
+    for _ in range(args.warmup):
+        prog.run()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        prog.enqueue()
+    e1.record(stream)
+    native.sync()
+    barrier()
+    ms_dev = e0.elapsed_time(e1) / args.steps
+    # ---- end-to-end leg: host inputs in, token ids out, every step
+    for s in range(args.warmup):
+        feed(s)
+        prog.run()
+    barrier()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record(stream)
+    for s in range(args.warmup, args.warmup + args.steps):
+        feed(s)
+        prog.run()
+        L.tlb_program_read(prog.h, dg.token, BATCH * 4, C.c_void_p(tok_out.data_ptr()))
+    e3.record(stream)
+    native.sync()
+    barrier()
+    clocks = sampler.stop()
+    ms_e2e = e2.elapsed_time(e3) / args.steps
+    # ---- per-launch device times of one step (CUDA events between launches, same stream)
+    prof = prog.profile()
+    barrier()
+    if dist is not None:
+        t = torch.tensor([ms_dev, ms_e2e], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_dev, ms_e2e = float(t[0]), float(t[1])
+
+    by_kind: dict[str, list] = {}
+    for label, ms in prof:
+        op = label.split(" ")[0]
+        if op == "MUL_MAT":
+            op = "MUL_MAT(output)" if label.endswith(" logits") else "MUL_MAT(layers)"
+        elif op == "CUSTOM":
+            op = "CUSTOM(paged_attention)" if label.endswith("attn") else "CUSTOM(cache_write)"
+        by_kind.setdefault(op, [0.0, 0])
+        by_kind[op][0] += ms
+        by_kind[op][1] += 1
+    total_prof = sum(v[0] for v in by_kind.values())
+    ab = algorithmic_bytes(cfg, world)
+    peak, peak_src = measured_peaks()
+    kinds = {"CUSTOM(paged_attention)": ab["kv"], "MUL_MAT(layers)": ab["w_layers"], "MUL_MAT(output)": ab["w_head"]}
+    dominant = max(kinds, key=lambda k: by_kind.get(k, [0.0, 0])[0])
+    dom_ms, dom_n = by_kind[dominant]
+    achieved = kinds[dominant] / (dom_ms * 1e-3) / 1e9 if dom_ms > 0 else 0.0
+    result = {
+        "metric": METRIC, "value": BATCH / (ms_dev * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_dev, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "int8 dot / f16 mma, f32 accumulate", "data": "synthetic",
+        "config": {"workload": "BASELINE config 4: Llama-3-8B shape, 32 layers, Q4_K weights (Q8_0 embed/output), "
+                               "batch 32 decode step at context 2048, paged f16 KV (16-token pages)",
+                   "parallelism": "tp%d" % world, "l2": "inputs larger than L2: %.2f GB weights + %.2f GB KV read per step per GPU"
+                                                        % (ab["weights"] / 1e9, ab["kv"] / 1e9)},
+        "e2e": {"value": BATCH / (ms_e2e * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": BATCH * 4,
+                "ms_per_step": ms_e2e},
+        "gpu_launches": prog.dispatch_count() * args.steps * 2,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "of": peak_src, "traffic": None, "launches_per_step": dom_n,
+                     "ms_per_step": dom_ms,
+                     "step_frac": (ab["weights"] + ab["kv"]) / (ms_dev * 1e-3) / 1e9 / peak},
+        "launch_share": {k: {"ms": round(v[0], 4), "launches": v[1], "share": round(v[0] / total_prof, 4)} for k, v in
+                         sorted(by_kind.items(), key=lambda kv: -kv[1][0])},
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        try:
+            result["cpu_baseline"] = cpu_reference_step(cfg, budget_s=20.0)
+        except Exception as e:  # the checker is optional equipment for a bench line
+            result["cpu_baseline"] = {"value": None, "unit": "tok/s", "cores": 0, "kind": "reference", "sample": "failed: %s" % e}
+    prog.free()
+    native.close()
+    if dist is not None:
+        dist.destroy_process_group()
+    return result if rank == 0 else {}
+
+
+# ---------------------------------------------------------------------------------- reference arm (CPU)
+def cpu_reference_step(cfg, budget_s: float = 20.0, steps: int = 1, warmup: int = 0) -> dict:
+    """The reference's own ggml CPU backend (the build of oracle/_ref that fits this host's CPU) on a
+    bounded sample of the decode step: ONE decoder layer at batch 32 / context 2048 (dense f16 K/V,
+    because ggml has no CPU paged attention; FLASH_ATTN_EXT reads the same bytes) plus the output
+    projection, all host threads. The full step is 32 x layer + output + small ops, so
+    tok/s = 32 / (32 * t_layer + t_output). Weight VALUES do not affect CPU time: 256 quantized rows
+    are tiled to the full row count instead of quantizing 8e9 values on the host."""
+    from oracle.bindings import F16, F32, I32, Q4_K, Q8_0, Ref, best_ref_variant
+
+    variant = best_ref_variant()
+    if variant is None:
+        raise RuntimeError("oracle/_ref is not built")
+    ref = Ref(variant)
+    threads = os.cpu_count() or 1
+    rng = np.random.default_rng(0)
+    d, hd, heads, kvh, ffn = cfg.d_model, cfg.head_dim, cfg.n_heads, cfg.n_kv_heads, cfg.d_ffn
+
+    def tiled(ty, k, rows):
+        base = ref.quantize(ty, (rng.standard_normal((256, k)) * 0.02).astype(np.float32))
+        return np.tile(base, ((rows + 255) // 256, 1))[:rows]
+
+    def layer_graph():
+        g = ref.graph(int(2.5e9), threads)
+        x = g.tensor(F32, [d, BATCH], data=rng.standard_normal((BATCH, d)).astype(np.float32))
+        pos = g.tensor(I32, [BATCH], data=np.full(BATCH, CONTEXT - 1, np.int32))
+        wn = g.tensor(F32, [d], data=np.ones(d, np.float32))
+        W = {n: g.tensor(Q4_K, [k, m], data=tiled(Q4_K, k, m)) for n, k, m in
+             (("wq", d, heads * hd), ("wk", d, kvh * hd), ("wv", d, kvh * hd), ("wo", heads * hd, d),
+              ("gate", d, ffn), ("up", d, ffn), ("down", ffn, d))}
+        K = g.tensor(F16, [hd, CONTEXT, kvh, BATCH], data=rng.standard_normal((BATCH, kvh, CONTEXT, hd)).astype(np.float16))
+        V = g.tensor(F16, [hd, CONTEXT, kvh, BATCH], data=rng.standard_normal((BATCH, kvh, CONTEXT, hd)).astype(np.float16))
+        h = g.op("mul", [g.op("rms_norm", [x], floats=[cfg.eps]), wn])
+        q = g.op("mul_mat", [W["wq"], h])
+        k = g.op("mul_mat", [W["wk"], h])
+        v = g.op("mul_mat", [W["wv"], h])
+        rp = dict(ints=[hd, 2, 0], floats=[cfg.rope_theta, 1.0, 0.0, 1.0, 32.0, 1.0])
+        q = g.op("rope_ext", [g.op("reshape", [q], ints=[hd, heads, BATCH, 1]), pos, None], **rp)
+        k = g.op("rope_ext", [g.op("reshape", [k], ints=[hd, kvh, BATCH, 1]), pos, None], **rp)
+        q4 = g.op("reshape", [q], ints=[hd, 1, heads, BATCH])      # one query per sequence
+        a = g.op("flash_attn_ext", [q4, K, V, None], floats=[1.0 / float(np.sqrt(hd)), 0.0, 0.0])
+        a = g.op("reshape", [a], ints=[hd * heads, BATCH, 1, 1])
+        x1 = g.op("add", [x, g.op("mul_mat", [W["wo"], a])])
+        h2 = g.op("mul", [g.op("rms_norm", [x1], floats=[cfg.eps]), wn])
+        m = g.op("mul", [g.op("unary", [g.op("mul_mat", [W["gate"], h2])], ints=[10]), g.op("mul_mat", [W["up"], h2])])
+        out = g.op("add", [x1, g.op("mul_mat", [W["down"], m])])
+        return g, [out, k, v]
+
+    def head_graph():
+        g = ref.graph(int(1.2e9), threads)
+        x = g.tensor(F32, [d, BATCH], data=rng.standard_normal((BATCH, d)).astype(np.float32))
+        w = g.tensor(Q8_0, [d, cfg.vocab], data=tiled(Q8_0, d, cfg.vocab))
+        y = g.op("mul_mat", [w, x])
+        return g, [g.op("argmax", [y])]
+
+    t0 = time.time()
+    gl, outs_l = layer_graph()
+    gh, outs_h = head_graph()
+    for _ in range(max(warmup, 1)):
+        gl.compute(outs_l)
+        gh.compute(outs_h)
+    t_layer, t_head, n = [], [], 0
+    while n < max(steps, 1) or (time.time() - t0 < budget_s and n < 5):
+        t_layer.append(gl.compute(outs_l))
+        t_head.append(gh.compute(outs_h))
+        n += 1
+    tl, th = float(np.median(t_layer)), float(np.median(t_head))
+    ms_step = cfg.n_layers * tl + th
+    gl.close()
+    gh.close()
+    return {"value": BATCH / (ms_step * 1e-3), "unit": "tok/s", "cores": threads, "kind": "reference",
+            "ms_per_step": ms_step, "build": "ggml CPU backend of the reference, flags %s" % ref.build_flags(),
+            "sample": "1 of 32 layers (%.1f ms) + output projection (%.1f ms), batch 32, context 2048, dense f16 K/V; "
+                      "step time = 32*layer + output; %d timed repeats" % (tl, th, n)}
+
+
+def run_reference(args) -> dict:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return {}
+    from tensorlisp_b200.programs import DecoderConfig
+    cfg = DecoderConfig()
+    try:
+        cb = cpu_reference_step(cfg, budget_s=0.0, steps=args.steps, warmup=min(args.warmup, 1))
+    except Exception as e:
+        return {"impl": "reference", "unavailable": "the reference's ggml CPU build is missing or failed: %s" % e}
+    return {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "tok/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["ms_per_step"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "int8 dot, f32 accumulate (ggml CPU)", "data": "synthetic",
+            "config": {"workload": "BASELINE config 4 (bounded sample, see cpu_baseline.sample)", "parallelism": "cpu"},
+            "cpu_baseline": cb, "gpu_launches": 0,
+            "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if out:
+        print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

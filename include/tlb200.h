@@ -115,6 +115,9 @@ tlb_status tlb_buffer_write(tlb_buffer *b, uint64_t offset, const void *host, ui
 tlb_status tlb_buffer_read(tlb_buffer *b, uint64_t offset, void *host, uint64_t n);
 uint64_t   tlb_buffer_size(tlb_buffer *b);
 void      *tlb_buffer_device_ptr(tlb_buffer *b);
+/* Device-to-device copy into a buffer, enqueued on the device stream and waited for (no counterpart:
+ * the reference only writes buffers from host memory). For callers whose data is already in HBM. */
+tlb_status tlb_buffer_copy_device(tlb_buffer *b, uint64_t offset, const void *device_src, uint64_t n);
 void       tlb_buffer_free(tlb_buffer *b);
 
 /* ------------------------------------------------------------------ programs
@@ -148,6 +151,11 @@ const char *tlb_program_label(tlb_program *prog, uint32_t i);
 void      *tlb_program_tensor_ptr(tlb_program *prog, uint32_t tensor_id, uint64_t *bytes);
 /* Layout figures of the plan (plan.rs Layout: arena_size, io_size). */
 uint64_t   tlb_program_arena_bytes(tlb_program *prog);
+/* TL_NATIVE_PROFILE of the reference (exec.rs:187-223) as a call: runs the program once, launch by
+ * launch (no CUDA graph), with a CUDA event between launches on the device stream, and writes the
+ * device time of each launch in milliseconds to ms[0..n) (n = tlb_program_dispatch_count). */
+tlb_status tlb_program_profile(tlb_program *prog, tlb_buffer *const *weights, uint32_t n_weights, tlb_buffer *state,
+                               float *ms, uint32_t n);
 
 /* ------------------------------------------------------------------ quantizers
  * DType::from_f32 (crates/tensorlisp/src/dtype.rs:98-124) -> ggml_quantize_chunk: f32 rows to

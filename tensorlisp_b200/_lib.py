@@ -80,6 +80,7 @@ SYMBOLS = {
     "tlb_buffer_read": (C.c_int, [_P, C.c_uint64, _P, C.c_uint64]),
     "tlb_buffer_size": (C.c_uint64, [_P]),
     "tlb_buffer_device_ptr": (_P, [_P]),
+    "tlb_buffer_copy_device": (C.c_int, [_P, C.c_uint64, _P, C.c_uint64]),
     "tlb_buffer_free": (None, [_P]),
     "tlb_program_compile": (C.c_int, [_P, C.POINTER(tlb_graph), C.POINTER(tlb_leaves), C.POINTER(_P), C.c_char_p, C.c_size_t]),
     "tlb_program_free": (None, [_P]),
@@ -91,6 +92,7 @@ SYMBOLS = {
     "tlb_program_label": (C.c_char_p, [_P, C.c_uint32]),
     "tlb_program_tensor_ptr": (_P, [_P, C.c_uint32, C.POINTER(C.c_uint64)]),
     "tlb_program_arena_bytes": (C.c_uint64, [_P]),
+    "tlb_program_profile": (C.c_int, [_P, C.POINTER(_P), C.c_uint32, _P, C.POINTER(C.c_float), C.c_uint32]),
     "tlb_quantize_rows": (C.c_int, [_P, C.c_uint32, _P, C.c_int64, C.c_int64, _P]),
     "tlb_quantize_rows_device": (C.c_int, [_P, C.c_uint32, _P, C.c_int64, C.c_int64, _P]),
     "tlb_row_size": (C.c_uint64, [C.c_uint32, C.c_int64]),

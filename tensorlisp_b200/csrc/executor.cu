@@ -307,6 +307,7 @@ static tlb_status buffer_create(tlb_device *dev, uint64_t bytes, bool zero, tlb_
     }
     tlb_buffer *b = new tlb_buffer;
     b->dev = dev;
+    b->ordinal = dev->ordinal;
     b->ptr = p;
     b->size = n;
     *out = b;
@@ -360,11 +361,22 @@ tlb_status tlb_buffer_read(tlb_buffer *b, uint64_t offset, void *host, uint64_t 
     return TLB_OK;
 }
 
+tlb_status tlb_buffer_copy_device(tlb_buffer *b, uint64_t offset, const void *device_src, uint64_t n) {
+    if (!b || (!device_src && n)) return fail(TLB_INVALID, "tlb_buffer_copy_device: bad arguments");
+    if (offset > b->size || n > b->size - offset)
+        return fail(TLB_INVALID, "write of " + std::to_string(n) + " bytes at " + std::to_string(offset) + " past a buffer of " + std::to_string(b->size));
+    if (n == 0) return TLB_OK;
+    cudaSetDevice(b->dev->ordinal);
+    TLB_TRY_CUDA(cudaMemcpyAsync((char *)b->ptr + offset, device_src, n, cudaMemcpyDeviceToDevice, b->dev->stream), TLB_EXECUTION);
+    TLB_TRY_CUDA(cudaStreamSynchronize(b->dev->stream), TLB_EXECUTION);
+    return TLB_OK;
+}
+
 uint64_t tlb_buffer_size(tlb_buffer *b) { return b ? b->size : 0; }
 void *tlb_buffer_device_ptr(tlb_buffer *b) { return b ? b->ptr : nullptr; }
 void tlb_buffer_free(tlb_buffer *b) {
     if (!b) return;
-    cudaSetDevice(b->dev->ordinal);
+    cudaSetDevice(b->ordinal);
     cudaFree(b->ptr);
     delete b;
 }
@@ -438,6 +450,7 @@ tlb_status tlb_program_compile(tlb_device *dev, const tlb_graph *graph, const tl
 
     tlb_program *p = new tlb_program;
     p->dev = dev;
+    p->ordinal = dev->ordinal;
     p->n_user_tensors = graph->n_tensors;
     p->graph = std::move(g);
     if (!getenv("TL_NATIVE_NOFUSE") || std::string(getenv("TL_NATIVE_NOFUSE")) != "1") rewrite_graph(p->graph);
@@ -498,7 +511,7 @@ tlb_status tlb_program_compile(tlb_device *dev, const tlb_graph *graph, const tl
 
 void tlb_program_free(tlb_program *prog) {
     if (!prog) return;
-    cudaSetDevice(prog->dev->ordinal);
+    cudaSetDevice(prog->ordinal);
     for (auto &c : prog->captured)
         if (c.exec) cudaGraphExecDestroy(c.exec);
     if (prog->arena) cudaFree(prog->arena);
@@ -556,6 +569,7 @@ static tlb_status launch_all(tlb_program *prog, const RunCtx &rc, bool profile) 
 tlb_status tlb_program_enqueue(tlb_program *prog, tlb_buffer *const *weights, uint32_t n_weights, tlb_buffer *state) {
     if (!prog) return fail(TLB_INVALID, "null program");
     cudaSetDevice(prog->dev->ordinal);
+    cudaGetLastError();  // a stale error of an unrelated earlier call must not be blamed on a launch
     RunCtx rc;
     tlb_status st = make_ctx(prog, weights, n_weights, state, rc);
     if (st != TLB_OK) return st;
@@ -599,6 +613,34 @@ tlb_status tlb_program_enqueue(tlb_program *prog, tlb_buffer *const *weights, ui
     }
     prog->captured.push_back({key, exec});
     TLB_TRY_CUDA(cudaGraphLaunch(exec, rc.stream), TLB_EXECUTION);
+    return TLB_OK;
+}
+
+tlb_status tlb_program_profile(tlb_program *prog, tlb_buffer *const *weights, uint32_t n_weights, tlb_buffer *state,
+                               float *ms, uint32_t n) {
+    if (!prog || (!ms && n)) return fail(TLB_INVALID, "tlb_program_profile: bad arguments");
+    if (n != prog->dispatches.size()) return fail(TLB_INVALID, "the program has " + std::to_string(prog->dispatches.size()) + " launches, room for " + std::to_string(n));
+    cudaSetDevice(prog->dev->ordinal);
+    cudaGetLastError();
+    RunCtx rc;
+    tlb_status st = make_ctx(prog, weights, n_weights, state, rc);
+    if (st != TLB_OK) return st;
+    std::vector<cudaEvent_t> ev(n + 1);
+    for (auto &e : ev) TLB_TRY_CUDA(cudaEventCreate(&e), TLB_EXECUTION);
+    cudaError_t e = cudaEventRecord(ev[0], rc.stream);
+    std::string where;
+    for (uint32_t i = 0; i < n && e == cudaSuccess; i++) {
+        e = prog->dispatches[i].fn(rc);
+        if (e == cudaSuccess) e = cudaEventRecord(ev[i + 1], rc.stream);
+        else where = prog->dispatches[i].label;
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(rc.stream);
+    for (uint32_t i = 0; i < n && e == cudaSuccess; i++) e = cudaEventElapsedTime(&ms[i], ev[i], ev[i + 1]);
+    for (auto &x : ev) cudaEventDestroy(x);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(TLB_EXECUTION, (where.empty() ? std::string("profiling: ") : "launching `" + where + "`: ") + cuda_msg(e));
+    }
     return TLB_OK;
 }
 

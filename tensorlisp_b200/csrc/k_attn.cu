@@ -180,20 +180,27 @@ __global__ void __launch_bounds__(PA_WARPS * 32) k_paged_attn(PagedParams p) {
             m_run[h] = m_new;
             l_run[h] *= corr[h];
         }
-        uint32_t pa[4];
+        // P as two f16 terms (value and rounding residual): the product with V is then accurate to
+        // ~2^-22, which matters because the next MUL_MAT re-quantizes this output to int8
+        uint32_t pa[4], pr[4];
         {
-            float pv[2][4];
+            float pv[2][4], rs[2][4];
 #pragma unroll
             for (int j = 0; j < 2; j++)
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
                     pv[j][e] = exp2f(s[j][e] - m_use[e >> 1]);
                     l_run[e >> 1] += pv[j][e];
+                    rs[j][e] = pv[j][e] - __half2float(__float2half_rn(pv[j][e]));
                 }
             pa[0] = pack_h2(pv[0][0], pv[0][1]);
             pa[1] = pack_h2(pv[0][2], pv[0][3]);
             pa[2] = pack_h2(pv[1][0], pv[1][1]);
             pa[3] = pack_h2(pv[1][2], pv[1][3]);
+            pr[0] = pack_h2(rs[0][0], rs[0][1]);
+            pr[1] = pack_h2(rs[0][2], rs[0][3]);
+            pr[2] = pack_h2(rs[1][0], rs[1][1]);
+            pr[3] = pack_h2(rs[1][2], rs[1][3]);
         }
         // ---- O = O * corr + P V
         {
@@ -207,7 +214,9 @@ __global__ void __launch_bounds__(PA_WARPS * 32) k_paged_attn(PagedParams p) {
                 uint32_t b0, b1, b2, b3;
                 ldsm_x4_t(vbase + row * ROW_BYTES + ((col ^ (row & 7)) * 16), b0, b1, b2, b3);
                 mma16816(o[nd], pa, b0, b1);
+                mma16816(o[nd], pr, b0, b1);
                 mma16816(o[nd + 1], pa, b2, b3);
+                mma16816(o[nd + 1], pr, b2, b3);
             }
         }
     }

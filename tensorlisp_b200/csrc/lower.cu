@@ -440,6 +440,18 @@ void lower_custom(L &l) {
     }
 }
 
+// ---- ALLREDUCE (tensor parallelism; no reference counterpart): the node is a view of its source
+void lower_allreduce(L &l) {
+    const Tensor &t = l.t();
+    const int32_t a = l.src(0);
+    if (t.ty != TLB_TYPE_F32 || !t.is_contiguous()) unsupported(t, "allreduce takes a contiguous f32 tensor");
+    if (l.c.g->root(l.id) != l.c.g->root(a)) unsupported(t, "allreduce works in place on its source");
+    const Place pd = l.place(l.id);
+    const size_t n = (size_t)t.nelements();
+    tlb_device *dev = l.c.dev;
+    l.push([=](const RunCtx &r) { return comm_allreduce_f32(dev, (float *)r.at(pd), n, r.stream); });
+}
+
 }  // namespace
 
 uint64_t node_scratch_bytes(const Graph &g, int32_t id, int sm_count) {
@@ -479,6 +491,7 @@ void lower_node(const LowerCtx &c, int32_t id, int pos, std::vector<Dispatch> &o
     if (op == "CONCAT" || op == "REPEAT" || op == "SUM_ROWS" || op == "MEAN" || op == "ARANGE") return lower_simple(l);
     if (op == "MUL_MAT") return lower_mul_mat(l);
     if (op == "CUSTOM") return lower_custom(l);
+    if (op == "ALLREDUCE") return lower_allreduce(l);
     unsupported(t, "op not implemented in the native CUDA backend");
 }
 

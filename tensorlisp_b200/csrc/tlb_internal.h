@@ -122,6 +122,7 @@ struct tlb_device {
 
 struct tlb_buffer {
     tlb_device *dev = nullptr;
+    int ordinal = 0;  // kept so a buffer can still be freed after its device handle was closed
     void *ptr = nullptr;
     uint64_t size = 0;
 };
@@ -160,6 +161,9 @@ struct LowerCtx {
 };
 void lower_node(const LowerCtx &c, int32_t id, int pos, std::vector<Dispatch> &out);
 uint64_t node_scratch_bytes(const Graph &g, int32_t id, int sm_count);
+// comm.cu: sum over the ranks of the device's communicator, in place (no-op without one)
+cudaError_t comm_allreduce_f32(tlb_device *dev, float *buf, size_t n, cudaStream_t st);
+int comm_ranks(tlb_device *dev);
 // IR rewrites before planning (fusion, shared activation quantization); fuse.cpp
 void rewrite_graph(Graph &g);
 
@@ -167,6 +171,7 @@ void rewrite_graph(Graph &g);
 
 struct tlb_program {
     tlb_device *dev = nullptr;
+    int ordinal = 0;
     tlb::Graph graph;
     tlb::Layout layout;
     std::vector<tlb::Dispatch> dispatches;

@@ -49,6 +49,10 @@ class StateBlock:
         check(_lib.lib().tlb_buffer_read(self.h, offset, out.ctypes.data_as(C.c_void_p), nbytes))
         return out
 
+    def copy_device(self, offset: int, device_ptr: int, nbytes: int) -> None:
+        """Device-to-device copy into the buffer (for data that is already in HBM)."""
+        check(_lib.lib().tlb_buffer_copy_device(self.h, offset, C.c_void_p(device_ptr), nbytes))
+
     @property
     def size(self) -> int:
         return int(_lib.lib().tlb_buffer_size(self.h))
@@ -198,6 +202,14 @@ class NativeProgram:
         arr, n, st = self._buffers(state)
         check(self.native.L.tlb_program_enqueue(self.h, arr, n, st))
 
+    def profile(self, state: StateBlock | None = None) -> list[tuple[str, float]]:
+        """Runs once launch by launch; returns (label, device milliseconds) per launch."""
+        arr, n, st = self._buffers(state)
+        k = self.dispatch_count()
+        ms = (C.c_float * max(k, 1))()
+        check(self.native.L.tlb_program_profile(self.h, arr, n, st, ms, k))
+        return list(zip(self.labels(), [float(v) for v in ms[:k]]))
+
     def read(self, tensor: int, dtype=None) -> np.ndarray:
         """The tensor's bytes as an array of its own element type, in ndarray (outermost first) order."""
         T = self.graph.tensors[tensor]
@@ -207,7 +219,10 @@ class NativeProgram:
         dt = dtype or _NP_OF.get(T.ty)
         if dt is None:
             return out
-        return out.view(dt).reshape([d for d in reversed(T.ne)])
+        shape = [d for d in reversed(T.ne)]
+        while len(shape) > 1 and shape[0] == 1:
+            shape.pop(0)
+        return out.view(dt).reshape(shape)
 
     def outputs(self) -> list[tuple[str, np.ndarray]]:
         return [(name, self.read(t)) for name, t in self._outputs]

@@ -1,0 +1,146 @@
+"""The graphs of the BASELINE configurations, written against ``Graph`` the way the reference's
+Scheme programs are written against the generated ``(ggml-*)`` ops: each helper is the stdlib form
+it restates (crates/tensorlisp/src/scheme/stdlib/nn.ss, attn.ss; ports/gemma4/concurrency.ss for
+the paged decode loop). Weights are declared in a fixed order so a caller can lay the weight buffer
+out once and compile any number of shapes against it.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from .graph import F16, F32, I32, Q4_K, Q8_0, Graph, row_size
+
+
+@dataclass
+class DecoderConfig:
+    """Llama-style decoder. Defaults are the Llama-3-8B shape of BASELINE config 4."""
+    n_layers: int = 32
+    d_model: int = 4096
+    n_heads: int = 32
+    n_kv_heads: int = 8
+    head_dim: int = 128
+    d_ffn: int = 14336
+    vocab: int = 128256
+    eps: float = 1e-5
+    rope_theta: float = 500000.0
+    block_size: int = 16
+    wtype: int = Q4_K        # projections and FFN matrices
+    etype: int = Q8_0        # token_embd and output
+
+
+@dataclass
+class WeightSpec:
+    name: str
+    ty: int
+    ne: list   # ggml order: [K (row length), M (rows)]
+
+    def nbytes(self) -> int:
+        n = row_size(self.ty, self.ne[0])
+        for d in self.ne[1:]:
+            n *= d
+        return n
+
+
+def rms_norm_w(g: Graph, x: int, w: int, eps: float, name: str = "") -> int:
+    """nn:rms-norm (stdlib/nn.ss:38-43) = ggml_mul(ggml_rms_norm(x, eps), w)."""
+    return g.mul(g.rms_norm(x, eps), w, name)
+
+
+def swiglu_ffn(g: Graph, x: int, norm_w: int, gate: int, up: int, down: int, eps: float) -> int:
+    """BASELINE config 2: RMSNorm -> gate/up -> SiLU(gate)*up -> down (gated MLP of ports/gemma4/gemma4.ss:62-64)."""
+    h = rms_norm_w(g, x, norm_w, eps, "ffn_norm")
+    a = g.mul_mat(gate, h, "ffn_gate")
+    b = g.mul_mat(up, h, "ffn_up")
+    m = g.mul(g.silu(a), b, "ffn_act")
+    return g.mul_mat(down, m, "ffn_down")
+
+
+def rope_neox(g: Graph, x: int, pos: int, head_dim: int, theta: float) -> int:
+    """attn:rope (stdlib/attn.ss:95-101): ggml_rope_ext(x, pos, NULL, dims, 2, 0, base, 1, 0, 1, 32, 1)."""
+    return g.rope_ext(x, pos, None, head_dim, 2, 0, theta, 1.0, 0.0, 1.0, 32.0, 1.0)
+
+
+@dataclass
+class DecoderGraph:
+    graph: Graph
+    weights: list            # WeightSpec, in weight-index order
+    state_bytes: list        # per state tensor
+    inputs: dict             # name -> input index
+    logits: int
+    token: int
+    cfg: DecoderConfig = None
+    tp: int = 1
+    extras: dict = field(default_factory=dict)
+
+
+def decoder_weights(cfg: DecoderConfig, tp: int = 1) -> list:
+    """Weight list of one rank. Column-parallel matrices (wq, wk, wv, gate, up, output) keep K and split
+    their rows; row-parallel ones (wo, down) split K (on 256-element boundaries) and keep their rows."""
+    d, hd = cfg.d_model, cfg.head_dim
+    qd, kvd = cfg.n_heads * hd // tp, cfg.n_kv_heads * hd // tp
+    ffn = cfg.d_ffn // tp
+    assert cfg.n_kv_heads % tp == 0 and cfg.d_ffn % (tp * 256) == 0 and (cfg.n_heads * hd // tp) % 256 == 0
+    ws = [WeightSpec("token_embd", cfg.etype, [d, cfg.vocab])]
+    for i in range(cfg.n_layers):
+        p = "blk.%d." % i
+        ws += [WeightSpec(p + "attn_norm", F32, [d]), WeightSpec(p + "wq", cfg.wtype, [d, qd]),
+               WeightSpec(p + "wk", cfg.wtype, [d, kvd]), WeightSpec(p + "wv", cfg.wtype, [d, kvd]),
+               WeightSpec(p + "wo", cfg.wtype, [qd, d]), WeightSpec(p + "ffn_norm", F32, [d]),
+               WeightSpec(p + "ffn_gate", cfg.wtype, [d, ffn]), WeightSpec(p + "ffn_up", cfg.wtype, [d, ffn]),
+               WeightSpec(p + "ffn_down", cfg.wtype, [ffn, d])]
+    assert cfg.vocab % tp == 0
+    ws += [WeightSpec("output_norm", F32, [d]), WeightSpec("output", cfg.etype, [d, cfg.vocab // tp])]
+    return ws
+
+
+def decoder_step(cfg: DecoderConfig, batch: int, max_ctx: int, pool_blocks: int, tp: int = 1,
+                 with_argmax: bool = True) -> DecoderGraph:
+    """One batched decode step over a paged f16 KV pool (the loop body of ports/gemma4/concurrency.ss:120-158):
+    inputs are the token ids, their positions, the block tables, the context lengths (after this
+    token) and the cache slots of the new tokens. With tp > 1 this is one rank's shard: attention over
+    its own KV heads, an ALLREDUCE after each row-parallel projection, logits for its vocabulary slice."""
+    g = Graph()
+    d, hd = cfg.d_model, cfg.head_dim
+    heads, kvh = cfg.n_heads // tp, cfg.n_kv_heads // tp
+    specs = decoder_weights(cfg, tp)
+    wid = {s.name: g.weight(s.ty, s.ne, s.name) for s in specs}
+    max_blocks = (max_ctx + cfg.block_size - 1) // cfg.block_size
+    pool_elems = pool_blocks * kvh * cfg.block_size * hd
+    pools = [(g.state(F16, [pool_elems], "k_pool.%d" % i), g.state(F16, [pool_elems], "v_pool.%d" % i))
+             for i in range(cfg.n_layers)]
+    ids = g.input(I32, [batch], "ids")
+    pos = g.input(I32, [batch], "pos")
+    tables = g.input(I32, [max_blocks, batch], "tables")
+    lens = g.input(I32, [batch], "lens")
+    slots = g.input(I32, [2 * batch], "slots")
+    scale = 1.0 / float(np.sqrt(hd))
+
+    x = g.get_rows(wid["token_embd"], ids, "embd")
+    for i in range(cfg.n_layers):
+        p = "blk.%d." % i
+        h = rms_norm_w(g, x, wid[p + "attn_norm"], cfg.eps, p + "attn_in")
+        q = g.mul_mat(wid[p + "wq"], h, p + "q")
+        k = g.mul_mat(wid[p + "wk"], h, p + "k")
+        v = g.mul_mat(wid[p + "wv"], h, p + "v")
+        q = rope_neox(g, g.reshape(q, [hd, heads, batch]), pos, hd, cfg.rope_theta)
+        k = rope_neox(g, g.reshape(k, [hd, kvh, batch]), pos, hd, cfg.rope_theta)
+        kc, vc = pools[i]
+        g.paged_cache_write(g.cast(g.reshape(k, [hd * kvh, batch]), F16), g.cast(v, F16), kc, vc, slots,
+                            cfg.block_size, kvh, p + "cache_write")
+        a = g.paged_attention(g.cast(q, F16), kc, vc, tables, lens, cfg.block_size, max_ctx, scale, kvh, p + "attn")
+        a = g.reshape(g.cast(a, F32), [hd * heads, batch])
+        o = g.mul_mat(wid[p + "wo"], a, p + "attn_out")
+        if tp > 1:
+            o = g.allreduce(o, p + "attn_out_sum")
+        x = g.add(x, o, p + "res1")
+        f = swiglu_ffn(g, x, wid[p + "ffn_norm"], wid[p + "ffn_gate"], wid[p + "ffn_up"], wid[p + "ffn_down"], cfg.eps)
+        if tp > 1:
+            f = g.allreduce(f, p + "ffn_down_sum")
+        x = g.add(x, f, p + "res2")
+    x = rms_norm_w(g, x, wid["output_norm"], cfg.eps, "final_norm")
+    logits = g.output(g.mul_mat(wid["output"], x, "logits"))
+    token = g.output(g.cast(g.argmax(logits, "argmax"), F32, "token")) if with_argmax else -1
+    return DecoderGraph(g, specs, [pool_elems * 2] * (2 * cfg.n_layers),
+                        dict(ids=0, pos=1, tables=2, lens=3, slots=4), logits, token, cfg, tp)

@@ -10,6 +10,8 @@ def close(got, want, tol):
     max|got-want| <= tol * max|want| + 1e-6."""
     got = np.asarray(got, np.float64)
     want = np.asarray(want, np.float64)
+    if got.size == want.size:  # reads drop leading dimensions of extent 1
+        got = got.reshape(want.shape)
     assert got.shape == want.shape, (got.shape, want.shape)
     err = np.abs(got - want).max() if got.size else 0.0
     bound = tol * (np.abs(want).max() if want.size else 0.0) + 1e-6
@@ -36,3 +38,50 @@ class Model:
     def close(self):
         self.program.free()
         self.native.close()
+
+
+# ------------------------------------------------------------------ oracle-side decoder step
+def make_decoder_weights(oracle, specs, seed=0):
+    """N(0, 0.02) f32 matrices quantized with the oracle (bit-exact with the reference), norm weights N(1, 0.1)."""
+    rng = np.random.default_rng(seed)
+    out = []
+    for s in specs:
+        if len(s.ne) == 1:
+            out.append((1 + 0.1 * rng.standard_normal(s.ne[0])).astype(np.float32))
+        else:
+            w = (rng.standard_normal((s.ne[1], s.ne[0])) * 0.02).astype(np.float32)
+            out.append(oracle.quantize(s.ty, w))
+    return out
+
+
+def oracle_decoder_step(oracle, cfg, specs, weights, ids, pos, ks, vs):
+    """The decode step of tensorlisp_b200.programs.decoder_step restated with oracle calls only.
+    ks[l][s], vs[l][s]: f16 [ctx_s, kv_heads, hd] INCLUDING the new token's slot (filled here).
+    Returns logits f32 [batch, vocab]."""
+    W = {s.name: (s, w) for s, w in zip(specs, weights)}
+    B = len(ids)
+    hd, heads, kvh = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
+
+    def lin(name, x):
+        s, w = W[name]
+        return oracle.mul_mat(s.ty, w, s.ne[0], x)
+
+    s, w = W["token_embd"]
+    x = oracle.get_rows(s.ty, w, cfg.d_model, ids)
+    for l in range(cfg.n_layers):
+        p = "blk.%d." % l
+        h = oracle.rms_norm(x, cfg.eps, W[p + "attn_norm"][1])
+        q, k, v = lin(p + "wq", h), lin(p + "wk", h), lin(p + "wv", h)
+        q = oracle.rope(q.reshape(B, heads, hd), pos, hd, 2, cfg.rope_theta)
+        k = oracle.rope(k.reshape(B, kvh, hd), pos, hd, 2, cfg.rope_theta)
+        for b in range(B):
+            ks[l][b][pos[b]] = k[b].astype(np.float16)
+            vs[l][b][pos[b]] = v[b].reshape(kvh, hd).astype(np.float16)
+        a16, _ = oracle.attention_decode(q.astype(np.float16), ks[l], vs[l], kvh, 1.0 / np.sqrt(hd))
+        o = lin(p + "wo", a16.astype(np.float32).reshape(B, heads * hd))
+        x = x + o
+        h = oracle.rms_norm(x, cfg.eps, W[p + "ffn_norm"][1])
+        m = oracle.silu_mul(lin(p + "ffn_gate", h), lin(p + "ffn_up", h))
+        x = x + lin(p + "ffn_down", m)
+    x = oracle.rms_norm(x, cfg.eps, W["output_norm"][1])
+    return lin("output", x)

@@ -46,9 +46,10 @@ def test_q4_K_full_rows_and_idempotence(native, oracle):
     q8 = quantize_rows(native, Q8_0, x)
     d8 = oracle.dequantize(Q8_0, q8, 14336)
     assert np.array_equal(oracle.dequantize(Q8_0, quantize_rows(native, Q8_0, d8), 14336), d8)
-    # the reconstruction error stays within half a quantization step of each block
+    # the reconstruction error stays within half a quantization step of each block, plus the f16
+    # rounding of the block scale (127 codes * 2^-11 relative)
     step = np.abs(x).reshape(512, -1, 32).max(axis=2) / 127
-    assert np.all(np.abs(d8 - x).reshape(512, -1, 32).max(axis=2) <= step * 0.5 + 1e-6)
+    assert np.all(np.abs(d8 - x).reshape(512, -1, 32).max(axis=2) <= step * (0.5 + 127 / 2048) + 1e-7)
 
 
 def test_empty_and_bad_rows(native):
