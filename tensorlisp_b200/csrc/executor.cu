@@ -256,6 +256,7 @@ tlb_status tlb_device_open(int ordinal, tlb_device **dev) {
     std::call_once(g_configure_once, [] {
         gemv_configure();
         attn_configure();
+        mmq_tc_configure();
     });
     *dev = d;
     return TLB_OK;

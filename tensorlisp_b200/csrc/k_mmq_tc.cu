@@ -1,0 +1,480 @@
+// Batched MUL_MAT (9..64 activation columns) with Q4_K weights on the 5th-generation tensor cores.
+//
+// Arithmetic (same integers as the reference's ggml-cpu path, vendor/ggml/src/ggml-cpu/quants.c:696-770):
+// the activations are the Q8_K codes q8 (k_quant.cu), the weights the 4-bit codes q with their 6-bit
+// sub-block scales sc and mins m. Per 256-element super-block and output (row r, column c)
+//     S = sum_k (sc*q)[r,k] * q8[k,c]          T = sum_j m[r,j] * bsum[j,c]
+//     y += yd[c] * (d[r] * S - dmin[r] * T)
+// Both sums are products of small integers: sc*q <= 945 and |q8| <= 127 are exact in f16, so
+// tcgen05.mma kind::f16 with f32 accumulation in tensor memory reproduces the integer sums to 2^-24,
+// and the per-sub-block scale costs nothing (it is folded into the f16 weight operand).
+//
+// Data movement: TMA brings a 128-row x 144-byte box of raw super-blocks (2-D tensor map over the
+// weight matrix as bytes) and one packed activation blob per super-block into shared memory; all
+// warps expand the nibbles into the K-major core-matrix layout (8 rows x 16 bytes, no swizzle) the
+// MMA reads; one thread issues 16 MMAs (M=128, N=columns, K=16) plus one for T per super-block into a
+// double-buffered TMEM accumulator; four warps drain it with tcgen05.ld and apply the f32 scales
+// while the next super-block is being expanded and multiplied. K is split across CTAs; partial sums
+// go to scratch and k_mmq_reduce adds them in a fixed order (deterministic).
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include "kernels.h"
+
+namespace tlb {
+
+namespace tc {
+
+constexpr int ROWS = 128;          // rows per CTA tile (UMMA M)
+constexpr int THREADS = 256;
+constexpr int RAW_BYTES = ROWS * 144;
+constexpr int A_HALF_BYTES = ROWS * 128 * 2;   // 128 rows x 128 k of f16
+constexpr int AMIN_BYTES = ROWS * 16 * 2;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+__device__ __forceinline__ uint32_t su32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(su32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(su32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(su32(bar)) : "memory");
+}
+// Bounded wait. Once any wait of the CTA has given up, every later wait returns at once so the
+// kernel runs to its end (with a wrong result and the error word set) instead of hanging.
+__device__ __forceinline__ void mbar_wait(uint64_t *bar, uint32_t parity, volatile int *fail) {
+    if (*fail) return;
+    const uint32_t a = su32(bar);
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(a), "r"(parity)
+            : "memory");
+        if (ok) return;
+        if ((i & 1023) == 1023 && *fail) return;
+    }
+    *fail = 1;
+}
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(su32(dst)),
+                 "l"(src), "r"(bytes), "r"(su32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tma_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(su32(dst)),
+                 "l"(map), "r"(x), "r"(y), "r"(su32(bar))
+                 : "memory");
+}
+
+// ---- tcgen05 wrappers
+__device__ __forceinline__ void tmem_alloc(uint32_t *dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(su32(dst_smem)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(su32(bar)) : "memory");
+}
+// 32 lanes x 16 consecutive 32-bit columns: thread t of the warp gets lane (warp%4)*32 + t
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                   "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+#pragma unroll
+    for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, no swizzle: a core matrix is 8 rows x 16 bytes stored contiguously (128 bytes);
+// `lbo` = byte distance between the two 16-byte K chunks of one MMA, `sbo` = between 8-row groups.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3fff);
+    d |= (uint64_t)((lbo >> 4) & 0x3fff) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3fff) << 32;
+    d |= (uint64_t)1 << 46;  // descriptor version of sm_100
+    return d;
+}
+
+}  // namespace tc
+
+// Bytes of one packed activation blob (one super-block of NPAD columns):
+//   B    f16 [NPAD x 256]  core-matrix layout, sbo 4096, lbo 128       NPAD*512
+//   Bmin f16 [NPAD x 16]   core-matrix layout, sbo 256,  lbo 128       NPAD*32
+//   yd   f32 [NPAD]                                                    NPAD*4
+static inline __host__ __device__ int tc_blob_bytes(int npad) { return (npad * 548 + 127) / 128 * 128; }
+
+// ---------------------------------------------------------------- activation packer
+// From the Q8_K activation block (qs int8 [N][K], d f32 [N][K/256], bsums int16 [N][K/16]) to the
+// per-super-block blobs the MMA reads. Element order inside a 16-byte K chunk follows the order in
+// which the weight nibbles come out of a 32-bit word: (0, 2, 1, 3, 4, 6, 5, 7).
+__global__ void __launch_bounds__(256) k_act_pack_tc(const int8_t *__restrict__ qs, const float *__restrict__ ds,
+                                                      const int16_t *__restrict__ bsums, int64_t K, int N, int npad,
+                                                      uint8_t *__restrict__ out) {
+    const int sb = blockIdx.x;
+    const int blob = tc_blob_bytes(npad);
+    uint8_t *o = out + (size_t)sb * blob;
+    // B tile: one 16-byte chunk per (n, kc)
+    for (int u = threadIdx.x; u < npad * 32; u += blockDim.x) {
+        const int n = u / 32, kc = u % 32;
+        __half h[8];
+        if (n < N) {
+            const int8_t *src = qs + (size_t)n * K + (size_t)sb * 256 + kc * 8;
+            const int perm[8] = {0, 2, 1, 3, 4, 6, 5, 7};
+#pragma unroll
+            for (int e = 0; e < 8; e++) h[e] = __int2half_rn((int)src[perm[e]]);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; e++) h[e] = __float2half_rn(0.f);
+        }
+        *reinterpret_cast<uint4 *>(o + (size_t)(n / 8) * 4096 + kc * 128 + (n % 8) * 16) = *reinterpret_cast<const uint4 *>(h);
+    }
+    uint8_t *omin = o + (size_t)npad * 512;
+    for (int u = threadIdx.x; u < npad * 2; u += blockDim.x) {
+        const int n = u / 2, kc = u % 2;
+        __half h[8];
+#pragma unroll
+        for (int e = 0; e < 8; e++)
+            h[e] = n < N ? __int2half_rn((int)bsums[(size_t)n * (K / 16) + (size_t)sb * 16 + kc * 8 + e]) : __float2half_rn(0.f);
+        *reinterpret_cast<uint4 *>(omin + (size_t)(n / 8) * 256 + kc * 128 + (n % 8) * 16) = *reinterpret_cast<const uint4 *>(h);
+    }
+    float *oyd = reinterpret_cast<float *>(o + (size_t)npad * 544);
+    for (int n = threadIdx.x; n < npad; n += blockDim.x) oyd[n] = n < N ? ds[(size_t)n * (K / 256) + sb] : 0.f;
+}
+
+// ---------------------------------------------------------------- the GEMM
+struct TcParams {
+    const uint8_t *act;   // packed blobs, one per super-block
+    float *out;           // y (n_split == 1) or partial sums [split][N][M]
+    int64_t M;
+    int N, npad, nsb, sb_per_split, n_split;
+    int64_t ldy;          // elements between output columns
+    int *err;
+};
+
+template <int NPAD, int RAW_STAGES, int ACT_STAGES>
+__global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_constant__ CUtensorMap wmap, TcParams p) {
+    using namespace tc;
+    constexpr int BLOB = (NPAD * 548 + 127) / 128 * 128;
+    constexpr uint32_t TMEM_COLS = NPAD * 4 <= 32 ? 32 : (NPAD * 4 <= 64 ? 64 : (NPAD * 4 <= 128 ? 128 : (NPAD * 4 <= 256 ? 256 : 512)));
+    constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(NPAD >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);  // f16 x f16 -> f32, K-major A and B
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = smem_raw + ((1024u - (tc::su32(smem_raw) & 1023u)) & 1023u);   // 1 KB of slack is allocated for this
+    uint8_t *raw = smem;                                   // RAW_STAGES x RAW_BYTES
+    uint8_t *actb = raw + RAW_STAGES * RAW_BYTES;          // ACT_STAGES x BLOB
+    uint8_t *abuf = actb + ACT_STAGES * BLOB;              // 2 x A_HALF_BYTES
+    uint8_t *amin = abuf + 2 * A_HALF_BYTES;               // 2 x AMIN_BYTES (by super-block parity)
+    float2 *dd = reinterpret_cast<float2 *>(amin + 2 * AMIN_BYTES);  // [2][ROWS] (d, dmin) by super-block parity
+    __shared__ uint64_t bar_raw[RAW_STAGES], bar_act[ACT_STAGES], bar_half[2], bar_mma[2], bar_epi[2];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int s_fail;
+    volatile int *fail = &s_fail;
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int row_tile = blockIdx.x, split = blockIdx.y;
+    const int sb0 = split * p.sb_per_split;
+    const int nsb = min(p.sb_per_split, p.nsb - sb0);      // super-blocks of this CTA (>= 1 by construction)
+    if (tid == 0) {
+        for (int i = 0; i < RAW_STAGES; i++) mbar_init(&bar_raw[i], 1);
+        for (int i = 0; i < ACT_STAGES; i++) mbar_init(&bar_act[i], 1);
+        for (int i = 0; i < 2; i++) {
+            mbar_init(&bar_half[i], 1);
+            mbar_init(&bar_mma[i], 1);
+            mbar_init(&bar_epi[i], 128);
+        }
+        s_fail = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) tmem_alloc(&tmem_base_s, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+
+    auto load_raw = [&](int i) {   // super-block i of this CTA -> raw stage i % RAW_STAGES
+        const int s = i % RAW_STAGES;
+        mbar_expect_tx(&bar_raw[s], RAW_BYTES);
+        tma_2d(raw + s * RAW_BYTES, &wmap, (sb0 + i) * 144, row_tile * ROWS, &bar_raw[s]);
+    };
+    auto load_act = [&](int i) {
+        const int s = i % ACT_STAGES;
+        mbar_expect_tx(&bar_act[s], BLOB);
+        bulk_g2s(actb + s * BLOB, p.act + (size_t)(sb0 + i) * BLOB, BLOB, &bar_act[s]);
+    };
+    if (tid == 0) {
+        for (int i = 0; i < nsb && i < RAW_STAGES; i++) load_raw(i);
+        for (int i = 0; i < nsb && i < ACT_STAGES; i++) load_act(i);
+    }
+
+    float yacc[NPAD];
+#pragma unroll
+    for (int c = 0; c < NPAD; c++) yacc[c] = 0.f;
+
+    // the epilogue of super-block i: warps 0..3, one row per thread
+    auto epilogue = [&](int i) {
+        const int b = i & 1;
+        mbar_wait(&bar_mma[b], (uint32_t)((i >> 1) & 1), fail);
+        tc_fence_after();
+        const float2 sc = dd[b * ROWS + tid];
+        const float *yd = reinterpret_cast<const float *>(actb + (i % ACT_STAGES) * BLOB + NPAD * 544);
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(b * 2 * NPAD);
+#pragma unroll
+        for (int c0 = 0; c0 < NPAD; c0 += 16) {
+            float S[16], T[16];
+            tmem_ld16(lane_addr + c0, S);
+            tmem_ld16(lane_addr + NPAD + c0, T);
+            tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 16; c++) yacc[c0 + c] += yd[c0 + c] * (sc.x * S[c] - sc.y * T[c]);
+        }
+        tc_fence_before();
+        mbar_arrive(&bar_epi[b]);   // TMEM buffer b, activation stage and dd[b] may be reused
+    };
+
+    const int r = tid & 127, hsel = tid >> 7;   // dequant role: row and which half of each 128-k half
+    for (int i = 0; i < nsb; i++) {
+        const int rs = i % RAW_STAGES;
+        mbar_wait(&bar_raw[rs], (uint32_t)((i / RAW_STAGES) & 1), fail);
+        const uint8_t *rrow = raw + rs * RAW_BYTES + r * 144;
+        const uint4 hdr = *reinterpret_cast<const uint4 *>(rrow);
+        // 6-bit scales and mins of the eight sub-blocks (get_scale_min_k4, ggml-quants.c:880-887)
+        uint32_t sc8[2], mn8[2];   // four bytes each
+        sc8[0] = hdr.y & 0x3f3f3f3fu;
+        mn8[0] = hdr.z & 0x3f3f3f3fu;
+        sc8[1] = (hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u);
+        mn8[1] = ((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u);
+        if (hsel == 0) {
+            // (d, dmin) for the epilogue and the mins as the f16 operand of the T product
+            if (i >= 2) mbar_wait(&bar_epi[i & 1], (uint32_t)(((i - 2) >> 1) & 1), fail);  // dd / amin of i-2 consumed
+            dd[(i & 1) * ROWS + r] = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
+            uint8_t *am = amin + (i & 1) * AMIN_BYTES + (r >> 3) * 256 + (r & 7) * 16;
+#pragma unroll
+            for (int kc = 0; kc < 2; kc++) {
+                __half2 h[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float m = (float)((mn8[kc] >> (8 * e)) & 0xffu);
+                    h[e] = __floats2half2_rn(m, m);
+                }
+                *reinterpret_cast<uint4 *>(am + kc * 128) = *reinterpret_cast<const uint4 *>(h);
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            // A buffer h is free once the MMAs that read it (previous super-block) have completed
+            if (i >= 1) mbar_wait(&bar_half[h], (uint32_t)((i - 1) & 1), fail);
+            uint8_t *arow = abuf + h * A_HALF_BYTES + (r >> 3) * 2048 + (r & 7) * 16;
+            // half h holds sub-blocks 4h..4h+3 = qs chunks 2h, 2h+1; this thread expands chunk 2h+hsel:
+            // low nibbles -> sub-block jl = 2*(2h+hsel), high nibbles -> jl+1
+            const int ch = 2 * h + hsel;
+            const uint32_t scw = sc8[ch >> 1] >> ((ch & 1) * 16);
+            const float s_lo = (float)(scw & 0xffu), s_hi = (float)((scw >> 8) & 0xffu);
+            const __half2 mlo = __floats2half2_rn(s_lo, s_lo), blo = __floats2half2_rn(-1024.f * s_lo, -1024.f * s_lo);
+            const __half2 mhi = __floats2half2_rn(s_hi, s_hi), bhi = __floats2half2_rn(-64.f * s_hi, -64.f * s_hi);
+            const uint8_t *q = rrow + 16 + ch * 32;
+            const int kc_lo = (2 * hsel) * 4, kc_hi = (2 * hsel + 1) * 4;   // K chunk (of 16 in this half) of piece 0
+#pragma unroll
+            for (int pc = 0; pc < 4; pc++) {
+                const uint2 w = *reinterpret_cast<const uint2 *>(q + pc * 8);
+                const uint32_t ws[2] = {w.x, w.y};
+                __half2 lo[4], hi[4];
+#pragma unroll
+                for (int k = 0; k < 2; k++) {
+                    const uint32_t a = ws[k], b = ws[k] >> 8;
+                    uint32_t t0 = (a & 0x000f000fu) | 0x64006400u, t1 = (b & 0x000f000fu) | 0x64006400u;
+                    uint32_t u0 = (a & 0x00f000f0u) | 0x54005400u, u1 = (b & 0x00f000f0u) | 0x54005400u;
+                    lo[2 * k] = __hfma2(*reinterpret_cast<__half2 *>(&t0), mlo, blo);       // (1024+q)*sc - 1024*sc, exact
+                    lo[2 * k + 1] = __hfma2(*reinterpret_cast<__half2 *>(&t1), mlo, blo);
+                    hi[2 * k] = __hfma2(*reinterpret_cast<__half2 *>(&u0), mhi, bhi);       // (64+q)*sc - 64*sc, exact
+                    hi[2 * k + 1] = __hfma2(*reinterpret_cast<__half2 *>(&u1), mhi, bhi);
+                }
+                *reinterpret_cast<uint4 *>(arow + (kc_lo + pc) * 128) = *reinterpret_cast<const uint4 *>(lo);
+                *reinterpret_cast<uint4 *>(arow + (kc_hi + pc) * 128) = *reinterpret_cast<const uint4 *>(hi);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> async-proxy (MMA) reads
+            __syncthreads();
+            if (tid == 0) {
+                const int as = i % ACT_STAGES, b = i & 1;
+                if (h == 0) {
+                    mbar_wait(&bar_act[as], (uint32_t)((i / ACT_STAGES) & 1), fail);
+                    if (i >= 2) mbar_wait(&bar_epi[b], (uint32_t)(((i - 2) >> 1) & 1), fail);   // TMEM buffer b drained
+                }
+                tc_fence_after();
+                const uint32_t d_S = tmem_base + (uint32_t)(b * 2 * NPAD), d_T = d_S + NPAD;
+                const uint32_t a_base = su32(abuf + h * A_HALF_BYTES);
+                const uint32_t b_base = su32(actb + as * BLOB) + (uint32_t)(h * 16) * 128;
+#pragma unroll
+                for (int ks = 0; ks < 8; ks++)
+                    umma_f16(d_S, smem_desc(a_base + ks * 256, 128, 2048), smem_desc(b_base + ks * 256, 128, 4096), IDESC,
+                             (h | ks) ? 1u : 0u);
+                if (h == 0)
+                    umma_f16(d_T, smem_desc(su32(amin + b * AMIN_BYTES), 128, 256),
+                             smem_desc(su32(actb + as * BLOB + NPAD * 512), 128, 256), IDESC, 0u);
+                umma_commit(&bar_half[h]);
+                if (h == 1) umma_commit(&bar_mma[b]);
+            }
+        }
+        // every thread has passed the barrier after its last read of this raw stage
+        if (tid == 0 && i + RAW_STAGES < nsb) load_raw(i + RAW_STAGES);
+        if (i >= 1) {
+            if (warp < 4) epilogue(i - 1);
+            if (tid == 0 && i - 1 + ACT_STAGES < nsb) {
+                mbar_wait(&bar_epi[(i - 1) & 1], (uint32_t)(((i - 1) >> 1) & 1), fail);   // all 128 rows read yd of stage
+                load_act(i - 1 + ACT_STAGES);
+            }
+        }
+    }
+    if (warp < 4) {
+        epilogue(nsb - 1);
+        const int64_t row = (int64_t)row_tile * ROWS + tid;
+        if (row < p.M) {
+            float *o = p.out + (size_t)split * p.N * p.ldy + row;
+#pragma unroll
+            for (int c = 0; c < NPAD; c++)
+                if (c < p.N) o[(size_t)c * p.ldy] = yacc[c];
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, TMEM_COLS);
+    if (tid == 0 && s_fail) atomicExch(p.err, 2);
+}
+
+// y[n][m] = sum over the K splits, in split order
+__global__ void k_mmq_reduce(const float *__restrict__ part, float *__restrict__ y, int64_t total, int n_split) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    float s = 0.f;
+    for (int k = 0; k < n_split; k++) s += part[(size_t)k * total + i];
+    y[i] = s;
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
+        return (EncodeTiledFn)p;
+    }();
+    return fn;
+}
+
+template <int NPAD, int RS, int AS>
+static size_t tc_smem() {
+    return (size_t)RS * tc::RAW_BYTES + (size_t)AS * tc_blob_bytes(NPAD) + 2 * tc::A_HALF_BYTES + 2 * tc::AMIN_BYTES +
+           2 * tc::ROWS * sizeof(float2) + 1024;
+}
+
+void mmq_tc_configure() {
+    cudaFuncSetAttribute(k_mmq_tc_q4k<16, 4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem<16, 4, 4>());
+    cudaFuncSetAttribute(k_mmq_tc_q4k<32, 4, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem<32, 4, 3>());
+    cudaFuncSetAttribute(k_mmq_tc_q4k<64, 3, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem<64, 3, 2>());
+}
+
+bool mmq_tc_supported(uint32_t type, int64_t K, int64_t M, int64_t N) {
+    return type == TLB_TYPE_Q4_K && K % 256 == 0 && K >= 256 && M >= 1 && N > 4 && N <= 64 && encode_tiled() != nullptr;
+}
+
+TcPlan mmq_tc_plan(int64_t K, int64_t M, int64_t N, int sm_count) {
+    TcPlan t;
+    t.npad = N <= 16 ? 16 : (N <= 32 ? 32 : 64);
+    t.nsb = (int)(K / 256);
+    const int64_t tiles = (M + tc::ROWS - 1) / tc::ROWS;
+    // K split: fill the SMs in whole waves, at least two super-blocks per CTA, small penalty per split
+    int best = 1;
+    double best_score = -1.0;
+    for (int s = 1; s <= t.nsb && s <= 16; s++) {
+        const int per = (t.nsb + s - 1) / s;
+        if (s > 1 && per < 2) break;
+        const int splits = (t.nsb + per - 1) / per;
+        if (splits != s) continue;
+        const int64_t units = tiles * splits;
+        const int64_t waves = (units + sm_count - 1) / sm_count;
+        const double score = (double)units / (double)(waves * sm_count) - 0.015 * splits;
+        if (score > best_score) { best_score = score; best = splits; }
+    }
+    t.n_split = best;
+    t.sb_per_split = (t.nsb + best - 1) / best;
+    t.blob_bytes = (uint64_t)t.nsb * tc_blob_bytes(t.npad);
+    t.partial_bytes = best > 1 ? (uint64_t)best * N * M * 4 : 0;
+    return t;
+}
+
+cudaError_t launch_act_pack_tc(const ActLayout &a, const void *act, int npad, void *blobs, cudaStream_t st) {
+    const char *ab = (const char *)act;
+    k_act_pack_tc<<<(unsigned)(a.K / 256), 256, 0, st>>>((const int8_t *)(ab + a.qs_off), (const float *)(ab + a.d_off),
+                                                        (const int16_t *)(ab + a.bsum_off), a.K, (int)a.N, npad, (uint8_t *)blobs);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_mmq_tc(const TcPlan &t, const void *W, int64_t K, int64_t M, int64_t N, const void *blobs, float *y,
+                          int64_t ldy, void *partial, int *err, cudaStream_t st) {
+    CUtensorMap map;
+    const cuuint64_t row_bytes = (cuuint64_t)(K / 256 * 144);
+    const cuuint64_t gdim[2] = {row_bytes, (cuuint64_t)M};
+    const cuuint64_t gstride[1] = {row_bytes};
+    const cuuint32_t box[2] = {144, (cuuint32_t)tc::ROWS};
+    const cuuint32_t estr[2] = {1, 1};
+    if (encode_tiled()(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(W), gdim, gstride, box, estr,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return cudaErrorInvalidValue;
+    TcParams p;
+    p.act = (const uint8_t *)blobs;
+    p.M = M;
+    p.N = (int)N;
+    p.npad = t.npad;
+    p.nsb = t.nsb;
+    p.sb_per_split = t.sb_per_split;
+    p.n_split = t.n_split;
+    p.err = err;
+    if (t.n_split > 1) {
+        p.out = (float *)partial;
+        p.ldy = M;
+    } else {
+        p.out = y;
+        p.ldy = ldy;
+    }
+    dim3 grid((unsigned)((M + tc::ROWS - 1) / tc::ROWS), (unsigned)t.n_split);
+    switch (t.npad) {
+        case 16: k_mmq_tc_q4k<16, 4, 4><<<grid, tc::THREADS, tc_smem<16, 4, 4>(), st>>>(map, p); break;
+        case 32: k_mmq_tc_q4k<32, 4, 3><<<grid, tc::THREADS, tc_smem<32, 4, 3>(), st>>>(map, p); break;
+        default: k_mmq_tc_q4k<64, 3, 2><<<grid, tc::THREADS, tc_smem<64, 3, 2>(), st>>>(map, p); break;
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    if (t.n_split > 1) {
+        if (ldy != M) return cudaErrorInvalidValue;   // the reduce writes dense columns
+        const int64_t total = N * M;
+        k_mmq_reduce<<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const float *)partial, y, total, t.n_split);
+        e = cudaGetLastError();
+    }
+    return e;
+}
+
+}  // namespace tlb

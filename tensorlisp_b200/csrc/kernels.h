@@ -44,6 +44,20 @@ struct MMGeneric {
 cudaError_t launch_mm_generic(const MMGeneric &p, const void *W, const void *X, void *Y, cudaStream_t st);
 void gemv_configure();  // sets the dynamic shared-memory attributes once per process
 
+// ---------------------------------------------------------------- k_mmq_tc.cu
+// Q4_K weights x 5..64 activation columns on tcgen05 (f16 operands built from the integer codes).
+struct TcPlan {
+    int npad, nsb, n_split, sb_per_split;
+    uint64_t blob_bytes;     // packed activation blobs, all super-blocks
+    uint64_t partial_bytes;  // scratch for the K-split partial sums (0 when not split)
+};
+bool mmq_tc_supported(uint32_t type, int64_t K, int64_t M, int64_t N);
+TcPlan mmq_tc_plan(int64_t K, int64_t M, int64_t N, int sm_count);
+cudaError_t launch_act_pack_tc(const ActLayout &a, const void *act, int npad, void *blobs, cudaStream_t st);
+cudaError_t launch_mmq_tc(const TcPlan &t, const void *W, int64_t K, int64_t M, int64_t N, const void *blobs, float *y,
+                          int64_t ldy, void *partial, int *err, cudaStream_t st);
+void mmq_tc_configure();
+
 // ---------------------------------------------------------------- k_core.cu
 struct BinArgs { TView a, b, d; int op; };  // 0 add 1 sub 2 mul 3 div; all f32
 cudaError_t launch_bin(const BinArgs &p, const void *a, const void *b, void *d, cudaStream_t st);

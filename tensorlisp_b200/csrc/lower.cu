@@ -332,6 +332,22 @@ void lower_mul_mat(L &l) {
     const bool batched = tw.ne[2] * tw.ne[3] * t.ne[2] * t.ne[3] != 1;
     const bool dense_w = tw.nb[1] == tw.row_size();
     const bool dense_y = t.is_contiguous();
+    if (!batched && dense_w && dense_y && l.T(qa).op_params[1] > 0 && mmq_tc_supported(tw.ty, K, M, N) && !getenv("TLB_MM_GENERIC") &&
+        !getenv("TLB_NO_TC")) {
+        // tensor-core path: the QUANT_ACT node also packed the activations into per-super-block blobs
+        const TcPlan tp = mmq_tc_plan(K, M, N, sm);
+        if (tp.npad != l.T(qa).op_params[1]) throw std::string("activation blobs were packed for another column count");
+        const int64_t sc = l.c.layout->scratch[l.pos];
+        if (tp.partial_bytes > 0 && sc < 0) throw std::string("split-K scratch was not planned");
+        Place ps;
+        ps.buf = BUF_ARENA;
+        ps.off = sc < 0 ? 0 : (uint64_t)sc;
+        const uint64_t blob_off = a.bytes;
+        l.push([=](const RunCtx &r) {
+            return launch_mmq_tc(tp, r.at(pw), K, M, N, r.at(pq) + blob_off, (float *)r.at(pd), M, r.at(ps), r.err, r.stream);
+        });
+        return;
+    }
     if (!batched && dense_w && dense_y && gemv_supported(tw.ty, K, M, N) && !getenv("TLB_MM_GENERIC")) {
         const uint32_t wty = tw.ty;
         l.push([=](const RunCtx &r) {
@@ -354,7 +370,12 @@ void lower_quant_act(L &l) {
     const ActLayout a = act_layout(t.op_params[0], tx.ne[0], tx.nrows());
     const int64_t ldx = tx.nrows() > 1 ? (int64_t)tx.nb[1] / 4 : tx.ne[0];
     const Place px = l.place(x), pd = l.place(l.id);
-    l.push([=](const RunCtx &r) { return launch_act_quantize(a, (const float *)r.at(px), ldx, r.at(pd), r.stream); });
+    const int npad = t.op_params[1];   // > 0: also pack the blobs of the tensor-core path behind the Q8_K block
+    l.push([=](const RunCtx &r) {
+        cudaError_t e = launch_act_quantize(a, (const float *)r.at(px), ldx, r.at(pd), r.stream);
+        if (e == cudaSuccess && npad > 0) e = launch_act_pack_tc(a, r.at(pd), npad, r.at(pd) + a.bytes, r.stream);
+        return e;
+    });
 }
 
 // ---- CUSTOM: the paged nodes (lower.rs:660-759). userdata, low to high bits: kind (4), kv heads (4),
@@ -459,6 +480,13 @@ uint64_t node_scratch_bytes(const Graph &g, int32_t id, int sm_count) {
     if (t.op == "CUSTOM") {
         PagedGeom pg{};
         if (paged_geom(g, t, sm_count, pg)) return paged_scratch_bytes(pg);
+    }
+    if (t.op == "MUL_MAT" && t.src[0] >= 0 && t.src[1] >= 0 && t.src[2] >= 0 && g.tensors[t.src[2]].op == "QUANT_ACT" &&
+        g.tensors[t.src[2]].op_params[1] > 0) {
+        // split-K partial sums of the tensor-core path
+        const Tensor &tw = g.tensors[t.src[0]], &tx = g.tensors[t.src[1]];
+        if (tw.ne[2] * tw.ne[3] * t.ne[2] * t.ne[3] == 1 && mmq_tc_supported(tw.ty, tw.ne[0], tw.ne[1], tx.ne[1]))
+            return mmq_tc_plan(tw.ne[0], tw.ne[1], tx.ne[1], sm_count).partial_bytes;
     }
     return 0;
 }
@@ -591,7 +619,7 @@ void rewrite_graph(Graph &g) {
         }
         Tensor &t = g.tensors[id];
         if (t.op == "MUL_MAT" && t.src[0] >= 0 && t.src[1] >= 0 && gemv_type(g.tensors[t.src[0]].ty)) {
-            const Tensor &tw = g.tensors[t.src[0]];
+            const Tensor tw = g.tensors[t.src[0]];   // by value: the tensor vector grows below
             const int32_t x = t.src[1];
             const Tensor tx = g.tensors[x];
             const int kind = act_kind_for(tw.ty);
@@ -623,6 +651,17 @@ void rewrite_graph(Graph &g) {
                     cache[key] = qa;
                 }
                 g.tensors[id].src[2] = qa;
+                // a consumer that takes the tensor-core path also needs the packed blobs behind the Q8_K block
+                const Tensor &mm = g.tensors[id];
+                const bool plain2d = tw.ne[2] * tw.ne[3] * mm.ne[2] * mm.ne[3] == 1 && tw.nb[1] == tw.row_size();
+                if (plain2d && mmq_tc_supported(tw.ty, tx.ne[0], tw.ne[1], tx.ne[1]) && !getenv("TLB_NO_TC")) {
+                    const TcPlan tp = mmq_tc_plan(tx.ne[0], tw.ne[1], tx.ne[1], 148);
+                    Tensor &q = g.tensors[qa];
+                    q.op_params[1] = tp.npad;
+                    q.opaque_bytes = act_layout(kind, tx.ne[0], tx.nrows()).bytes + tp.blob_bytes;
+                    q.ne[0] = (int64_t)q.opaque_bytes;
+                    q.nb[1] = q.nb[2] = q.nb[3] = q.opaque_bytes;
+                }
             }
         }
         nodes.push_back(id);

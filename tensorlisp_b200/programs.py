@@ -48,13 +48,13 @@ def rms_norm_w(g: Graph, x: int, w: int, eps: float, name: str = "") -> int:
     return g.mul(g.rms_norm(x, eps), w, name)
 
 
-def swiglu_ffn(g: Graph, x: int, norm_w: int, gate: int, up: int, down: int, eps: float) -> int:
+def swiglu_ffn(g: Graph, x: int, norm_w: int, gate: int, up: int, down: int, eps: float, p: str = "") -> int:
     """BASELINE config 2: RMSNorm -> gate/up -> SiLU(gate)*up -> down (gated MLP of ports/gemma4/gemma4.ss:62-64)."""
-    h = rms_norm_w(g, x, norm_w, eps, "ffn_norm")
-    a = g.mul_mat(gate, h, "ffn_gate")
-    b = g.mul_mat(up, h, "ffn_up")
-    m = g.mul(g.silu(a), b, "ffn_act")
-    return g.mul_mat(down, m, "ffn_down")
+    h = rms_norm_w(g, x, norm_w, eps, p + "ffn_in")
+    a = g.mul_mat(gate, h, p + "ffn_gate_out")
+    b = g.mul_mat(up, h, p + "ffn_up_out")
+    m = g.mul(g.silu(a), b, p + "ffn_act")
+    return g.mul_mat(down, m, p + "ffn_down_out")
 
 
 def rope_neox(g: Graph, x: int, pos: int, head_dim: int, theta: float) -> int:
@@ -96,7 +96,7 @@ def decoder_weights(cfg: DecoderConfig, tp: int = 1) -> list:
 
 
 def decoder_step(cfg: DecoderConfig, batch: int, max_ctx: int, pool_blocks: int, tp: int = 1,
-                 with_argmax: bool = True) -> DecoderGraph:
+                 with_argmax: bool = True, taps: bool = False) -> DecoderGraph:
     """One batched decode step over a paged f16 KV pool (the loop body of ports/gemma4/concurrency.ss:120-158):
     inputs are the token ids, their positions, the block tables, the context lengths (after this
     token) and the cache slots of the new tokens. With tp > 1 this is one rank's shard: attention over
@@ -117,15 +117,15 @@ def decoder_step(cfg: DecoderConfig, batch: int, max_ctx: int, pool_blocks: int,
     slots = g.input(I32, [2 * batch], "slots")
     scale = 1.0 / float(np.sqrt(hd))
 
-    x = g.get_rows(wid["token_embd"], ids, "embd")
+    x = x0 = g.get_rows(wid["token_embd"], ids, "embd")
     for i in range(cfg.n_layers):
         p = "blk.%d." % i
         h = rms_norm_w(g, x, wid[p + "attn_norm"], cfg.eps, p + "attn_in")
         q = g.mul_mat(wid[p + "wq"], h, p + "q")
         k = g.mul_mat(wid[p + "wk"], h, p + "k")
         v = g.mul_mat(wid[p + "wv"], h, p + "v")
-        q = rope_neox(g, g.reshape(q, [hd, heads, batch]), pos, hd, cfg.rope_theta)
-        k = rope_neox(g, g.reshape(k, [hd, kvh, batch]), pos, hd, cfg.rope_theta)
+        q = g.set_name(rope_neox(g, g.reshape(q, [hd, heads, batch]), pos, hd, cfg.rope_theta), p + "q_rope")
+        k = g.set_name(rope_neox(g, g.reshape(k, [hd, kvh, batch]), pos, hd, cfg.rope_theta), p + "k_rope")
         kc, vc = pools[i]
         g.paged_cache_write(g.cast(g.reshape(k, [hd * kvh, batch]), F16), g.cast(v, F16), kc, vc, slots,
                             cfg.block_size, kvh, p + "cache_write")
@@ -135,12 +135,26 @@ def decoder_step(cfg: DecoderConfig, batch: int, max_ctx: int, pool_blocks: int,
         if tp > 1:
             o = g.allreduce(o, p + "attn_out_sum")
         x = g.add(x, o, p + "res1")
-        f = swiglu_ffn(g, x, wid[p + "ffn_norm"], wid[p + "ffn_gate"], wid[p + "ffn_up"], wid[p + "ffn_down"], cfg.eps)
+        f = swiglu_ffn(g, x, wid[p + "ffn_norm"], wid[p + "ffn_gate"], wid[p + "ffn_up"], wid[p + "ffn_down"], cfg.eps, p)
         if tp > 1:
             f = g.allreduce(f, p + "ffn_down_sum")
         x = g.add(x, f, p + "res2")
     x = rms_norm_w(g, x, wid["output_norm"], cfg.eps, "final_norm")
     logits = g.output(g.mul_mat(wid["output"], x, "logits"))
     token = g.output(g.cast(g.argmax(logits, "argmax"), F32, "token")) if with_argmax else -1
+    extras = {}
+    if taps:
+        # every named intermediate stays readable after the run (the reference's `taps`, native_ir.rs:117-132)
+        names = ("attn_in", "q", "k", "v", "q_rope", "k_rope", "attn", "attn_out", "res1", "ffn_in", "ffn_gate_out",
+                 "ffn_up_out", "ffn_act", "ffn_down_out", "res2")
+        tap = {"embd": x0, "final_norm": x}
+        for t in g.nodes:
+            nm = g.tensors[t].name
+            if nm.startswith("blk.") and nm.split(".", 2)[2] in names:
+                tap[nm] = t
+        for t in tap.values():
+            if t not in g.keep:
+                g.keep.append(t)
+        extras["taps"] = tap
     return DecoderGraph(g, specs, [pool_elems * 2] * (2 * cfg.n_layers),
-                        dict(ids=0, pos=1, tables=2, lens=3, slots=4), logits, token, cfg, tp)
+                        dict(ids=0, pos=1, tables=2, lens=3, slots=4), logits, token, cfg, tp, extras)
