@@ -23,7 +23,7 @@ LIB = HERE / "libtlb200.so"
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", 
           "-Xcompiler", "-Wall", "--expt-relaxed-constexpr", "-DTLB_BUILDING"]
-PER_FILE = {"k_quant.cu": ["-fmad=false"]}
+PER_FILE = {"k_quant.cu": ["-fmad=false"], "k_fused.cu": ["-fmad=false"]}
 
 
 def _nvcc() -> str:

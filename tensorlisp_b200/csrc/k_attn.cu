@@ -56,7 +56,7 @@ struct PagedParams {
     const int32_t *lens;   // [seqs]
     __half *out;           // [seqs][heads][HS]
     float *partial;        // [seqs][heads][n_chunks][HS + 2]  (max, sum, O) when n_chunks > 1
-    int heads, kv_heads, group, groups_per_kv, block_size, max_blocks, chunk_tokens, n_chunks;
+    int heads, kv_heads, group, groups_per_kv, block_size, block_shift, max_blocks, chunk_tokens, n_chunks;
     float scale_log2;      // softmax scale * log2(e)
 };
 
@@ -68,7 +68,6 @@ __global__ void __launch_bounds__(PA_WARPS * 32) k_paged_attn(PagedParams p) {
     constexpr int STAGE_BYTES = 2 * TILE_BYTES;
     constexpr int KS = HS / 16;                        // k-steps of Q K^T
     constexpr int ND = HS / 8;                         // n-tiles of P V
-    constexpr int CP_PER_LANE = 2 * PA_TILE * CHUNKS / 32;
     extern __shared__ __align__(128) uint8_t smem[];
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -107,21 +106,23 @@ __global__ void __launch_bounds__(PA_WARPS * 32) k_paged_attn(PagedParams p) {
         if (tile < n_tiles) {
             uint8_t *st = ring + (size_t)(i % PA_STAGES) * STAGE_BYTES;
             const int tok0 = c_begin + tile * PA_TILE;
+            // K and V rows of a token sit at the same offset of their pools: one table lookup and one
+            // address per (lane, row), shifts instead of divisions (block sizes are powers of two)
+            constexpr int ROWS_PER_IT = 32 / CHUNKS, N_IT = PA_TILE / ROWS_PER_IT;
+            const int col = lane % CHUNKS, row0 = lane / CHUNKS;
 #pragma unroll
-            for (int it = 0; it < CP_PER_LANE; it++) {
-                const int qd = it * 32 + lane;
-                const int kv = qd / (PA_TILE * CHUNKS);
-                const int row = (qd % (PA_TILE * CHUNKS)) / CHUNKS;
-                const int col = qd % CHUNKS;
+            for (int it = 0; it < N_IT; it++) {
+                const int row = it * ROWS_PER_IT + row0;
                 const int tok = tok0 + row;
                 const bool live = tok < c_end;
-                const __half *src = kv ? p.vpool : p.kpool;
+                size_t off = 0;
                 if (live) {
-                    const int blk = table[tok / p.block_size];
-                    src += ((size_t)blk * p.kv_heads + kvh) * page_stride + (size_t)(tok % p.block_size) * HS + col * 8;
+                    const int blk = table[tok >> p.block_shift];
+                    off = ((size_t)blk * p.kv_heads + kvh) * page_stride + (size_t)(tok & (p.block_size - 1)) * HS + col * 8;
                 }
-                const uint32_t dst = s_u32(st + kv * TILE_BYTES + row * ROW_BYTES + ((col ^ (row & 7)) * 16));
-                cp_async16(dst, src, live ? 16 : 0);  // rows past the context are zero-filled
+                const uint32_t dst = s_u32(st + row * ROW_BYTES + ((col ^ (row & 7)) * 16));
+                cp_async16(dst, p.kpool + off, live ? 16 : 0);   // rows past the context are zero-filled
+                cp_async16(dst + TILE_BYTES, p.vpool + off, live ? 16 : 0);
             }
         }
         cp_commit();
@@ -307,7 +308,7 @@ void attn_configure() {
 bool paged_supported(const PagedGeom &g) {
     if (!(g.hs == 64 || g.hs == 128 || g.hs == 256)) return false;
     if (g.kv_heads < 1 || g.heads % g.kv_heads != 0) return false;
-    if (g.block_size < 1 || g.max_blocks < 1) return false;
+    if (g.block_size < 1 || g.max_blocks < 1 || (g.block_size & (g.block_size - 1)) != 0) return false;
     return true;
 }
 
@@ -354,6 +355,8 @@ cudaError_t launch_paged_attention(const PagedGeom &g, const void *q, const void
     p.group = g.heads / g.kv_heads;
     p.groups_per_kv = (p.group + 15) / 16;
     p.block_size = g.block_size;
+    p.block_shift = 0;
+    while ((1 << p.block_shift) < g.block_size) p.block_shift++;
     p.max_blocks = g.max_blocks;
     p.chunk_tokens = g.chunk_tokens;
     p.n_chunks = g.n_chunks;

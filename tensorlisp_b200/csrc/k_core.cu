@@ -273,7 +273,7 @@ __global__ void k_norm(NormArgs p, const uint8_t *a, const uint8_t *w, uint8_t *
     c = 0;
     for (int64_t i = threadIdx.x; i < n; i += blockDim.x, c++) {
         float t = ((cached ? v[c & 15] : x[i]) - mean) * scale;
-        if (wr) t *= wr[i % wn];
+        if (wr) t *= wr[wn == n ? i : (int64_t)((uint32_t)i % (uint32_t)wn)];
         y[i] = t;
     }
 }

@@ -23,10 +23,24 @@
 
 namespace tlb {
 
+#ifdef TC_DEBUG
+__device__ unsigned long long g_tc_dbg[256];
+#define TC_STAMP(slot)                                                                         \
+    do {                                                                                       \
+        if (blockIdx.x == 0 && blockIdx.y == 0) {                                              \
+            unsigned long long t__;                                                            \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));                              \
+            g_tc_dbg[slot] = t__;                                                              \
+        }                                                                                      \
+    } while (0)
+#else
+#define TC_STAMP(slot) do {} while (0)
+#endif
+
 namespace tc {
 
 constexpr int ROWS = 128;          // rows per CTA tile (UMMA M)
-constexpr int THREADS = 256;
+constexpr int THREADS = 416;          // 1 issue warp + 4 epilogue warps + 8 expanding warps
 constexpr int RAW_BYTES = ROWS * 144;
 constexpr int A_HALF_BYTES = ROWS * 128 * 2;   // 128 rows x 128 k of f16
 constexpr int AMIN_BYTES = ROWS * 16 * 2;
@@ -186,12 +200,13 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
     uint8_t *abuf = actb + ACT_STAGES * BLOB;              // 2 x A_HALF_BYTES
     uint8_t *amin = abuf + 2 * A_HALF_BYTES;               // 2 x AMIN_BYTES (by super-block parity)
     float2 *dd = reinterpret_cast<float2 *>(amin + 2 * AMIN_BYTES);  // [2][ROWS] (d, dmin) by super-block parity
-    __shared__ uint64_t bar_raw[RAW_STAGES], bar_act[ACT_STAGES], bar_half[2], bar_mma[2], bar_epi[2];
+    __shared__ uint64_t bar_raw[RAW_STAGES], bar_act[ACT_STAGES], bar_half[2], bar_mma[2], bar_epi[2], bar_aready[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ int s_fail;
     volatile int *fail = &s_fail;
 
     const int tid = threadIdx.x, warp = tid >> 5;
+    if (tid == 0) TC_STAMP(0);
     const int row_tile = blockIdx.x, split = blockIdx.y;
     const int sb0 = split * p.sb_per_split;
     const int nsb = min(p.sb_per_split, p.nsb - sb0);      // super-blocks of this CTA (>= 1 by construction)
@@ -202,6 +217,7 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
             mbar_init(&bar_half[i], 1);
             mbar_init(&bar_mma[i], 1);
             mbar_init(&bar_epi[i], 128);
+            mbar_init(&bar_aready[i], 256);
         }
         s_fail = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -211,6 +227,7 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
+    if (tid == 0) TC_STAMP(1);
 
     auto load_raw = [&](int i) {   // super-block i of this CTA -> raw stage i % RAW_STAGES
         const int s = i % RAW_STAGES;
@@ -227,137 +244,153 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
         for (int i = 0; i < nsb && i < ACT_STAGES; i++) load_act(i);
     }
 
-    float yacc[NPAD];
-#pragma unroll
-    for (int c = 0; c < NPAD; c++) yacc[c] = 0.f;
-
-    // the epilogue of super-block i: warps 0..3, one row per thread
-    auto epilogue = [&](int i) {
-        const int b = i & 1;
-        mbar_wait(&bar_mma[b], (uint32_t)((i >> 1) & 1), fail);
-        tc_fence_after();
-        const float2 sc = dd[b * ROWS + tid];
-        const float *yd = reinterpret_cast<const float *>(actb + (i % ACT_STAGES) * BLOB + NPAD * 544);
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(b * 2 * NPAD);
-#pragma unroll
-        for (int c0 = 0; c0 < NPAD; c0 += 16) {
-            float S[16], T[16];
-            tmem_ld16(lane_addr + c0, S);
-            tmem_ld16(lane_addr + NPAD + c0, T);
-            tmem_ld_wait();
-#pragma unroll
-            for (int c = 0; c < 16; c++) yacc[c0 + c] += yd[c0 + c] * (sc.x * S[c] - sc.y * T[c]);
-        }
-        tc_fence_before();
-        mbar_arrive(&bar_epi[b]);   // TMEM buffer b, activation stage and dd[b] may be reused
-    };
-
-    const int r = tid & 127, hsel = tid >> 7;   // dequant role: row and which half of each 128-k half
-    for (int i = 0; i < nsb; i++) {
-        const int rs = i % RAW_STAGES;
-        mbar_wait(&bar_raw[rs], (uint32_t)((i / RAW_STAGES) & 1), fail);
-        const uint8_t *rrow = raw + rs * RAW_BYTES + r * 144;
-        const uint4 hdr = *reinterpret_cast<const uint4 *>(rrow);
-        // 6-bit scales and mins of the eight sub-blocks (get_scale_min_k4, ggml-quants.c:880-887)
-        uint32_t sc8[2], mn8[2];   // four bytes each
-        sc8[0] = hdr.y & 0x3f3f3f3fu;
-        mn8[0] = hdr.z & 0x3f3f3f3fu;
-        sc8[1] = (hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u);
-        mn8[1] = ((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u);
-        if (hsel == 0) {
-            // (d, dmin) for the epilogue and the mins as the f16 operand of the T product
-            if (i >= 2) mbar_wait(&bar_epi[i & 1], (uint32_t)(((i - 2) >> 1) & 1), fail);  // dd / amin of i-2 consumed
-            dd[(i & 1) * ROWS + r] = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
-            uint8_t *am = amin + (i & 1) * AMIN_BYTES + (r >> 3) * 256 + (r & 7) * 16;
-#pragma unroll
-            for (int kc = 0; kc < 2; kc++) {
-                __half2 h[4];
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const float m = (float)((mn8[kc] >> (8 * e)) & 0xffu);
-                    h[e] = __floats2half2_rn(m, m);
-                }
-                *reinterpret_cast<uint4 *>(am + kc * 128) = *reinterpret_cast<const uint4 *>(h);
-            }
-        }
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            // A buffer h is free once the MMAs that read it (previous super-block) have completed
-            if (i >= 1) mbar_wait(&bar_half[h], (uint32_t)((i - 1) & 1), fail);
-            uint8_t *arow = abuf + h * A_HALF_BYTES + (r >> 3) * 2048 + (r & 7) * 16;
-            // half h holds sub-blocks 4h..4h+3 = qs chunks 2h, 2h+1; this thread expands chunk 2h+hsel:
-            // low nibbles -> sub-block jl = 2*(2h+hsel), high nibbles -> jl+1
-            const int ch = 2 * h + hsel;
-            const uint32_t scw = sc8[ch >> 1] >> ((ch & 1) * 16);
-            const float s_lo = (float)(scw & 0xffu), s_hi = (float)((scw >> 8) & 0xffu);
-            const __half2 mlo = __floats2half2_rn(s_lo, s_lo), blo = __floats2half2_rn(-1024.f * s_lo, -1024.f * s_lo);
-            const __half2 mhi = __floats2half2_rn(s_hi, s_hi), bhi = __floats2half2_rn(-64.f * s_hi, -64.f * s_hi);
-            const uint8_t *q = rrow + 16 + ch * 32;
-            const int kc_lo = (2 * hsel) * 4, kc_hi = (2 * hsel + 1) * 4;   // K chunk (of 16 in this half) of piece 0
-#pragma unroll
-            for (int pc = 0; pc < 4; pc++) {
-                const uint2 w = *reinterpret_cast<const uint2 *>(q + pc * 8);
-                const uint32_t ws[2] = {w.x, w.y};
-                __half2 lo[4], hi[4];
-#pragma unroll
-                for (int k = 0; k < 2; k++) {
-                    const uint32_t a = ws[k], b = ws[k] >> 8;
-                    uint32_t t0 = (a & 0x000f000fu) | 0x64006400u, t1 = (b & 0x000f000fu) | 0x64006400u;
-                    uint32_t u0 = (a & 0x00f000f0u) | 0x54005400u, u1 = (b & 0x00f000f0u) | 0x54005400u;
-                    lo[2 * k] = __hfma2(*reinterpret_cast<__half2 *>(&t0), mlo, blo);       // (1024+q)*sc - 1024*sc, exact
-                    lo[2 * k + 1] = __hfma2(*reinterpret_cast<__half2 *>(&t1), mlo, blo);
-                    hi[2 * k] = __hfma2(*reinterpret_cast<__half2 *>(&u0), mhi, bhi);       // (64+q)*sc - 64*sc, exact
-                    hi[2 * k + 1] = __hfma2(*reinterpret_cast<__half2 *>(&u1), mhi, bhi);
-                }
-                *reinterpret_cast<uint4 *>(arow + (kc_lo + pc) * 128) = *reinterpret_cast<const uint4 *>(lo);
-                *reinterpret_cast<uint4 *>(arow + (kc_hi + pc) * 128) = *reinterpret_cast<const uint4 *>(hi);
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> async-proxy (MMA) reads
-            __syncthreads();
-            if (tid == 0) {
+    // ---- warp roles: no CTA-wide barrier inside the loop, the roles meet only through mbarriers
+    //   warp 0, lane 0      issues the TMA copies and the MMAs
+    //   warps 1..4          epilogue: TMEM -> registers, f32 scaling, final store (lane quadrant = warp % 4)
+    //   warps 5..12         expand the raw nibbles into the f16 operand
+    const int lane = tid & 31;
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < nsb; i++) {
                 const int as = i % ACT_STAGES, b = i & 1;
-                if (h == 0) {
-                    mbar_wait(&bar_act[as], (uint32_t)((i / ACT_STAGES) & 1), fail);
-                    if (i >= 2) mbar_wait(&bar_epi[b], (uint32_t)(((i - 2) >> 1) & 1), fail);   // TMEM buffer b drained
-                }
-                tc_fence_after();
                 const uint32_t d_S = tmem_base + (uint32_t)(b * 2 * NPAD), d_T = d_S + NPAD;
-                const uint32_t a_base = su32(abuf + h * A_HALF_BYTES);
-                const uint32_t b_base = su32(actb + as * BLOB) + (uint32_t)(h * 16) * 128;
 #pragma unroll
-                for (int ks = 0; ks < 8; ks++)
-                    umma_f16(d_S, smem_desc(a_base + ks * 256, 128, 2048), smem_desc(b_base + ks * 256, 128, 4096), IDESC,
-                             (h | ks) ? 1u : 0u);
-                if (h == 0)
-                    umma_f16(d_T, smem_desc(su32(amin + b * AMIN_BYTES), 128, 256),
-                             smem_desc(su32(actb + as * BLOB + NPAD * 512), 128, 256), IDESC, 0u);
-                umma_commit(&bar_half[h]);
-                if (h == 1) umma_commit(&bar_mma[b]);
+                for (int h = 0; h < 2; h++) {
+                    mbar_wait(&bar_aready[h], (uint32_t)(i & 1), fail);
+                    TC_STAMP(16 + 4 * i + 2 * h);
+                    if (h == 0) {
+                        mbar_wait(&bar_act[as], (uint32_t)((i / ACT_STAGES) & 1), fail);
+                        if (i >= 2) mbar_wait(&bar_epi[b], (uint32_t)(((i - 2) >> 1) & 1), fail);   // TMEM buffer b drained
+                    }
+                    tc_fence_after();
+                    const uint32_t a_base = su32(abuf + h * A_HALF_BYTES);
+                    const uint32_t b_base = su32(actb + as * BLOB) + (uint32_t)(h * 16) * 128;
+#pragma unroll
+                    for (int ks = 0; ks < 8; ks++)
+                        umma_f16(d_S, smem_desc(a_base + ks * 256, 128, 2048), smem_desc(b_base + ks * 256, 128, 4096), IDESC,
+                                 (h | ks) ? 1u : 0u);
+                    if (h == 0)
+                        umma_f16(d_T, smem_desc(su32(amin + b * AMIN_BYTES), 128, 256),
+                                 smem_desc(su32(actb + as * BLOB + NPAD * 512), 128, 256), IDESC, 0u);
+                    umma_commit(&bar_half[h]);
+                    if (h == 1) umma_commit(&bar_mma[b]);
+                    TC_STAMP(16 + 4 * i + 2 * h + 1);
+                }
+                // all expanding threads arrived on bar_aready[1] after their last read of this raw stage
+                if (i + RAW_STAGES < nsb) load_raw(i + RAW_STAGES);
+                if (i >= 1 && i - 1 + ACT_STAGES < nsb) {
+                    mbar_wait(&bar_epi[(i - 1) & 1], (uint32_t)(((i - 1) >> 1) & 1), fail);   // yd of that stage consumed
+                    load_act(i - 1 + ACT_STAGES);
+                }
             }
         }
-        // every thread has passed the barrier after its last read of this raw stage
-        if (tid == 0 && i + RAW_STAGES < nsb) load_raw(i + RAW_STAGES);
-        if (i >= 1) {
-            if (warp < 4) epilogue(i - 1);
-            if (tid == 0 && i - 1 + ACT_STAGES < nsb) {
-                mbar_wait(&bar_epi[(i - 1) & 1], (uint32_t)(((i - 1) >> 1) & 1), fail);   // all 128 rows read yd of stage
-                load_act(i - 1 + ACT_STAGES);
+    } else if (warp <= 4) {
+        const int q = warp & 3;                 // TMEM lane quadrant this warp may read
+        const int row_in_tile = q * 32 + lane;
+        float yacc[NPAD];
+#pragma unroll
+        for (int c = 0; c < NPAD; c++) yacc[c] = 0.f;
+        for (int i = 0; i < nsb; i++) {
+            const int b = i & 1;
+            mbar_wait(&bar_mma[b], (uint32_t)((i >> 1) & 1), fail);
+            if (warp == 1 && lane == 0) TC_STAMP(96 + 2 * i);
+            tc_fence_after();
+            const float2 sc = dd[b * ROWS + row_in_tile];
+            const float *yd = reinterpret_cast<const float *>(actb + (i % ACT_STAGES) * BLOB + NPAD * 544);
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * 2 * NPAD);
+#pragma unroll
+            for (int c0 = 0; c0 < NPAD; c0 += 16) {
+                float S[16], T[16];
+                tmem_ld16(lane_addr + c0, S);
+                tmem_ld16(lane_addr + NPAD + c0, T);
+                tmem_ld_wait();
+#pragma unroll
+                for (int c = 0; c < 16; c++) yacc[c0 + c] += yd[c0 + c] * (sc.x * S[c] - sc.y * T[c]);
             }
+            tc_fence_before();
+            mbar_arrive(&bar_epi[b]);   // TMEM buffer b, the activation stage, dd[b] and amin[b] may be reused
+            if (warp == 1 && lane == 0) TC_STAMP(96 + 2 * i + 1);
         }
-    }
-    if (warp < 4) {
-        epilogue(nsb - 1);
-        const int64_t row = (int64_t)row_tile * ROWS + tid;
+        const int64_t row = (int64_t)row_tile * ROWS + row_in_tile;
         if (row < p.M) {
             float *o = p.out + (size_t)split * p.N * p.ldy + row;
 #pragma unroll
             for (int c = 0; c < NPAD; c++)
                 if (c < p.N) o[(size_t)c * p.ldy] = yacc[c];
         }
+    } else {
+        const int dt = tid - 160;
+        const int r = dt & 127, hsel = dt >> 7;   // row, and which qs chunk of each 128-k half
+        for (int i = 0; i < nsb; i++) {
+            const int rs = i % RAW_STAGES;
+            mbar_wait(&bar_raw[rs], (uint32_t)((i / RAW_STAGES) & 1), fail);
+            if (dt == 0) TC_STAMP(160 + 4 * i);
+            const uint8_t *rrow = raw + rs * RAW_BYTES + r * 144;
+            const uint4 hdr = *reinterpret_cast<const uint4 *>(rrow);
+            // 6-bit scales and mins of the eight sub-blocks (get_scale_min_k4, ggml-quants.c:880-887)
+            uint32_t sc8[2], mn8[2];   // four bytes each
+            sc8[0] = hdr.y & 0x3f3f3f3fu;
+            mn8[0] = hdr.z & 0x3f3f3f3fu;
+            sc8[1] = (hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u);
+            mn8[1] = ((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u);
+            if (hsel == 0) {
+                // (d, dmin) for the epilogue and the mins as the f16 operand of the T product
+                if (i >= 2) mbar_wait(&bar_epi[i & 1], (uint32_t)(((i - 2) >> 1) & 1), fail);   // those of i-2 consumed
+                dd[(i & 1) * ROWS + r] = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
+                uint8_t *am = amin + (i & 1) * AMIN_BYTES + (r >> 3) * 256 + (r & 7) * 16;
+#pragma unroll
+                for (int kc = 0; kc < 2; kc++) {
+                    __half2 hm[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const float m = (float)((mn8[kc] >> (8 * e)) & 0xffu);
+                        hm[e] = __floats2half2_rn(m, m);
+                    }
+                    *reinterpret_cast<uint4 *>(am + kc * 128) = *reinterpret_cast<const uint4 *>(hm);
+                }
+            }
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                // A buffer h is free once the MMAs that read it (previous super-block) have completed
+                if (i >= 1) mbar_wait(&bar_half[h], (uint32_t)((i - 1) & 1), fail);
+                uint8_t *arow = abuf + h * A_HALF_BYTES + (r >> 3) * 2048 + (r & 7) * 16;
+                // half h holds sub-blocks 4h..4h+3 = qs chunks 2h, 2h+1; this thread expands chunk 2h+hsel:
+                // low nibbles -> sub-block 2*(2h+hsel), high nibbles -> the next one
+                const int ch = 2 * h + hsel;
+                const uint32_t scw = sc8[ch >> 1] >> ((ch & 1) * 16);
+                const float s_lo = (float)(scw & 0xffu), s_hi = (float)((scw >> 8) & 0xffu);
+                const __half2 mlo = __floats2half2_rn(s_lo, s_lo), blo = __floats2half2_rn(-1024.f * s_lo, -1024.f * s_lo);
+                const __half2 mhi = __floats2half2_rn(s_hi, s_hi), bhi = __floats2half2_rn(-64.f * s_hi, -64.f * s_hi);
+                const uint8_t *qq = rrow + 16 + ch * 32;
+                const int kc_lo = (2 * hsel) * 4, kc_hi = (2 * hsel + 1) * 4;   // K chunk (of 16 in this half) of piece 0
+#pragma unroll
+                for (int pc = 0; pc < 4; pc++) {
+                    const uint2 w = *reinterpret_cast<const uint2 *>(qq + pc * 8);
+                    const uint32_t ws[2] = {w.x, w.y};
+                    __half2 lo[4], hi[4];
+#pragma unroll
+                    for (int k = 0; k < 2; k++) {
+                        const uint32_t a = ws[k], bb = ws[k] >> 8;
+                        uint32_t t0 = (a & 0x000f000fu) | 0x64006400u, t1 = (bb & 0x000f000fu) | 0x64006400u;
+                        uint32_t u0 = (a & 0x00f000f0u) | 0x54005400u, u1 = (bb & 0x00f000f0u) | 0x54005400u;
+                        lo[2 * k] = __hfma2(*reinterpret_cast<__half2 *>(&t0), mlo, blo);       // (1024+q)*sc - 1024*sc, exact
+                        lo[2 * k + 1] = __hfma2(*reinterpret_cast<__half2 *>(&t1), mlo, blo);
+                        hi[2 * k] = __hfma2(*reinterpret_cast<__half2 *>(&u0), mhi, bhi);       // (64+q)*sc - 64*sc, exact
+                        hi[2 * k + 1] = __hfma2(*reinterpret_cast<__half2 *>(&u1), mhi, bhi);
+                    }
+                    *reinterpret_cast<uint4 *>(arow + (kc_lo + pc) * 128) = *reinterpret_cast<const uint4 *>(lo);
+                    *reinterpret_cast<uint4 *>(arow + (kc_hi + pc) * 128) = *reinterpret_cast<const uint4 *>(hi);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> async-proxy (MMA) reads
+                mbar_arrive(&bar_aready[h]);
+                if (dt == 0) TC_STAMP(160 + 4 * i + 1 + h);
+            }
+        }
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem_base, TMEM_COLS);
+    if (tid == 0) TC_STAMP(2);
     if (tid == 0 && s_fail) atomicExch(p.err, 2);
 }
 
@@ -392,7 +425,7 @@ static size_t tc_smem() {
 
 void mmq_tc_configure() {
     cudaFuncSetAttribute(k_mmq_tc_q4k<16, 4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem<16, 4, 4>());
-    cudaFuncSetAttribute(k_mmq_tc_q4k<32, 4, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem<32, 4, 3>());
+    cudaFuncSetAttribute(k_mmq_tc_q4k<32, 4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem<32, 4, 4>());
     cudaFuncSetAttribute(k_mmq_tc_q4k<64, 3, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem<64, 3, 2>());
 }
 
@@ -463,7 +496,7 @@ cudaError_t launch_mmq_tc(const TcPlan &t, const void *W, int64_t K, int64_t M, 
     dim3 grid((unsigned)((M + tc::ROWS - 1) / tc::ROWS), (unsigned)t.n_split);
     switch (t.npad) {
         case 16: k_mmq_tc_q4k<16, 4, 4><<<grid, tc::THREADS, tc_smem<16, 4, 4>(), st>>>(map, p); break;
-        case 32: k_mmq_tc_q4k<32, 4, 3><<<grid, tc::THREADS, tc_smem<32, 4, 3>(), st>>>(map, p); break;
+        case 32: k_mmq_tc_q4k<32, 4, 4><<<grid, tc::THREADS, tc_smem<32, 4, 4>(), st>>>(map, p); break;
         default: k_mmq_tc_q4k<64, 3, 2><<<grid, tc::THREADS, tc_smem<64, 3, 2>(), st>>>(map, p); break;
     }
     cudaError_t e = cudaGetLastError();

@@ -58,6 +58,32 @@ cudaError_t launch_mmq_tc(const TcPlan &t, const void *W, int64_t K, int64_t M, 
                           int64_t ldy, void *partial, int *err, cudaStream_t st);
 void mmq_tc_configure();
 
+// ---------------------------------------------------------------- k_fused.cu
+// One row (= activation column n) per CTA: produce the f32 row, quantize it to Q8_K into an ActLayout
+// block at `out`, optionally also pack the tensor-core blobs behind it.
+enum { RQ_PLAIN = 0, RQ_NORM = 1, RQ_GLU = 2, RQ_F16 = 3 };
+struct RowQuantArgs {
+    int mode;
+    int64_t K, N;
+    const float *a;      // PLAIN/NORM: the row source; GLU: gate; F16: half values (cast pointer)
+    int64_t lda;
+    const float *b;      // PLAIN/NORM: optional addend (residual add), GLU: up
+    int64_t ldb;
+    float *sum_out;      // a + b written back (new residual stream), may be null
+    int64_t ld_sum;
+    const float *w;      // NORM: weight row of wn values
+    int64_t wn;
+    float eps;
+    float *y_out;        // optional f32 copy of the produced row
+    int64_t ld_y;
+    void *out;           // ActLayout block (ACT_Q8_K) for N columns
+    uint64_t qs_off, d_off, bsum_off;
+    int npad;            // > 0: also pack blobs of npad columns at out + blob_off
+    uint64_t blob_off, blob_bytes;
+};
+bool row_quant_supported(int64_t K);
+cudaError_t launch_row_quant(const RowQuantArgs &p, cudaStream_t st);
+
 // ---------------------------------------------------------------- k_core.cu
 struct BinArgs { TView a, b, d; int op; };  // 0 add 1 sub 2 mul 3 div; all f32
 cudaError_t launch_bin(const BinArgs &p, const void *a, const void *b, void *d, cudaStream_t st);

@@ -28,6 +28,7 @@ TView view_of(const Tensor &t) {
 }
 
 int act_kind_for(uint32_t wty) { return wty == TLB_TYPE_Q4_K ? ACT_Q8_K : ACT_Q8_0; }
+bool is_qact(const std::string &op) { return op == "QUANT_ACT" || op == "ROW_QUANT"; }
 
 struct L {
     const LowerCtx &c;
@@ -326,7 +327,7 @@ void lower_mul_mat(L &l) {
         return;
     }
     const int32_t qa = t.src[2];
-    if (qa < 0 || l.T(qa).op != "QUANT_ACT") unsupported(t, "activations could not be quantized (rows must be dense f32 with uniformly strided columns and a length that is a multiple of the block size)");
+    if (qa < 0 || !is_qact(l.T(qa).op)) unsupported(t, "activations could not be quantized (rows must be dense f32 with uniformly strided columns and a length that is a multiple of the block size)");
     const Place pq = l.place(qa);
     const ActLayout a = act_layout(act_kind_for(tw.ty), K, tx.nrows());
     const bool batched = tw.ne[2] * tw.ne[3] * t.ne[2] * t.ne[3] != 1;
@@ -375,6 +376,46 @@ void lower_quant_act(L &l) {
         cudaError_t e = launch_act_quantize(a, (const float *)r.at(px), ldx, r.at(pd), r.stream);
         if (e == cudaSuccess && npad > 0) e = launch_act_pack_tc(a, r.at(pd), npad, r.at(pd) + a.bytes, r.stream);
         return e;
+    });
+}
+
+// ---- ROW_QUANT: a QUANT_ACT node that absorbed its producer (fuse_row_producers)
+void lower_row_quant(L &l) {
+    const Tensor &t = l.t();
+    const int mode = t.op_params[2];
+    const int32_t a = l.src(0);
+    const Tensor &shape = mode == RQ_F16 ? l.T(l.src(5)) : l.T(a);
+    RowQuantArgs p{};
+    p.mode = mode;
+    p.K = shape.ne[0];
+    p.N = shape.nrows();
+    const ActLayout al = act_layout(ACT_Q8_K, p.K, p.N);
+    p.qs_off = al.qs_off;
+    p.d_off = al.d_off;
+    p.bsum_off = al.bsum_off;
+    p.npad = t.op_params[1];
+    p.blob_off = al.bytes;
+    p.blob_bytes = p.npad > 0 ? mmq_tc_plan(p.K, 128, p.N, 148).blob_bytes / (uint64_t)(p.K / 256) : 0;
+    p.eps = t.param_f32(15);
+    p.lda = mode == RQ_F16 ? p.K : (p.N > 1 ? (int64_t)l.T(a).nb[1] / 4 : p.K);
+    const int32_t b = t.src[1], w = t.src[3], sum = t.src[4];
+    if (b >= 0) p.ldb = p.N > 1 ? (int64_t)l.T(b).nb[1] / 4 : p.K;
+    if (w >= 0) p.wn = l.T(w).ne[0];
+    if (sum >= 0) p.ld_sum = p.K;
+    const Place pa = l.place(a), pd = l.place(l.id);
+    Place pb, pw, ps;
+    if (b >= 0) pb = l.place(b);
+    if (w >= 0) pw = l.place(w);
+    if (sum >= 0) ps = l.place(sum);
+    l.push([=](const RunCtx &r) {
+        RowQuantArgs q = p;
+        q.a = (const float *)r.at(pa);
+        q.b = b >= 0 ? (const float *)r.at(pb) : nullptr;
+        q.w = w >= 0 ? (const float *)r.at(pw) : nullptr;
+        q.sum_out = sum >= 0 ? (float *)r.at(ps) : nullptr;
+        q.y_out = nullptr;
+        q.out = r.at(pd);
+        return launch_row_quant(q, r.stream);
     });
 }
 
@@ -481,7 +522,7 @@ uint64_t node_scratch_bytes(const Graph &g, int32_t id, int sm_count) {
         PagedGeom pg{};
         if (paged_geom(g, t, sm_count, pg)) return paged_scratch_bytes(pg);
     }
-    if (t.op == "MUL_MAT" && t.src[0] >= 0 && t.src[1] >= 0 && t.src[2] >= 0 && g.tensors[t.src[2]].op == "QUANT_ACT" &&
+    if (t.op == "MUL_MAT" && t.src[0] >= 0 && t.src[1] >= 0 && t.src[2] >= 0 && is_qact(g.tensors[t.src[2]].op) &&
         g.tensors[t.src[2]].op_params[1] > 0) {
         // split-K partial sums of the tensor-core path
         const Tensor &tw = g.tensors[t.src[0]], &tx = g.tensors[t.src[1]];
@@ -497,10 +538,11 @@ void lower_node(const LowerCtx &c, int32_t id, int pos, std::vector<Dispatch> &o
     L l{c, id, pos, out};
     const std::string &op = t.op;
     if (op == "QUANT_ACT") return lower_quant_act(l);
+    if (op == "ROW_QUANT") return lower_row_quant(l);
     for (int s : t.src)
         if (s >= 0) {
             const uint32_t ty = c.g->tensors[s].ty;
-            if (!(plain(ty) || gemv_type(ty)) && c.g->tensors[s].op != "QUANT_ACT") unsupported(t, "operand type");
+            if (!(plain(ty) || gemv_type(ty)) && !is_qact(c.g->tensors[s].op)) unsupported(t, "operand type");
         }
     if (!plain(t.ty)) unsupported(t, "operand type");
     if (op == "ADD" || op == "SUB" || op == "MUL" || op == "DIV") return lower_bin(l);
@@ -524,6 +566,7 @@ void lower_node(const LowerCtx &c, int32_t id, int pos, std::vector<Dispatch> &o
 }
 
 // ---------------------------------------------------------------------------- IR rewrites
+void fuse_row_producers(Graph &g);
 // Readers of every root (views of a tensor count for the root), as fuse.rs:56-63 requires.
 void rewrite_graph(Graph &g) {
     const size_t nt0 = g.tensors.size();
@@ -667,6 +710,110 @@ void rewrite_graph(Graph &g) {
         nodes.push_back(id);
     }
     g.nodes.swap(nodes);
+    if (enabled("ROW_QUANT")) fuse_row_producers(g);
+}
+
+// Fold the producer of a quantized activation into its QUANT_ACT node (k_fused.cu): RMS_NORM_MUL
+// (optionally with the residual ADD in front of it), GLU(swiglu) and the f16 -> f32 cast of the
+// attention output. Legality follows vulkan/fuse.rs:56-63: the folded intermediates have no other
+// reader, are not kept, and nothing between the folded nodes and the fused one touches them.
+void fuse_row_producers(Graph &g) {
+    const size_t nn = g.nodes.size();
+    std::vector<int> pos_of(g.tensors.size(), -1);
+    for (size_t i = 0; i < nn; i++) pos_of[g.nodes[i]] = (int)i;
+    std::vector<char> kept(g.tensors.size(), 0);
+    for (int32_t k : g.keep) kept[g.root(k)] = 1;
+    // a MUL_MAT that carries a QUANT_ACT of its activation never reads the f32 activation itself
+    auto really_reads = [&](const Tensor &t, int slot) {
+        return !(t.op == "MUL_MAT" && slot == 1 && t.src[2] >= 0 && is_qact(g.tensors[t.src[2]].op) &&
+                 gemv_type(g.tensors[t.src[0]].ty));
+    };
+    // readers of a root among the nodes, by position
+    auto readers = [&](int32_t root, std::vector<int> &out) {
+        out.clear();
+        for (size_t i = 0; i < nn; i++) {
+            const Tensor &t = g.tensors[g.nodes[i]];
+            for (int s = 0; s < 10; s++)
+                if (t.src[s] >= 0 && g.root(t.src[s]) == root && really_reads(t, s)) out.push_back((int)i);
+        }
+    };
+    auto dense_rows = [&](const Tensor &t, int64_t es) {
+        if (t.nb[0] != (uint64_t)es) return false;
+        if (t.ne[2] > 1 && t.nb[2] != t.nb[1] * (uint64_t)t.ne[1]) return false;
+        if (t.ne[3] > 1 && t.nb[3] != t.nb[1] * (uint64_t)t.ne[1] * (uint64_t)t.ne[2]) return false;
+        return t.nb[1] % 16 == 0;
+    };
+    std::vector<char> dead(nn, 0);
+    std::vector<int> rd;
+    for (size_t qi = 0; qi < nn; qi++) {
+        const int32_t qid = g.nodes[qi];
+        if (g.tensors[qid].op != "QUANT_ACT" || g.tensors[qid].op_params[0] != ACT_Q8_K) continue;
+        const int32_t x = g.tensors[qid].src[0];
+        const Tensor X = g.tensors[x];
+        if (X.ty != 0 || !row_quant_supported(X.ne[0]) || !dense_rows(X, 4)) continue;
+        const int32_t xroot = g.root(x);
+        if (kept[xroot]) continue;
+        const int xp = pos_of[xroot];
+        if (xp < 0 || dead[xp]) continue;
+        const Tensor P = g.tensors[xroot];   // producer of the storage X views
+        // every reader of the producer's storage must be this QUANT_ACT (views of it launch nothing)
+        readers(xroot, rd);
+        bool only_q = true;
+        for (int r : rd) only_q = only_q && (r == (int)qi || g.tensors[g.nodes[r]].is_view_op());
+        if (!only_q) continue;
+        Tensor &Q = g.tensors[qid];
+        if (P.op == "RMS_NORM_MUL" && xroot == x) {
+            const int32_t a = P.src[0], w = P.src[1];
+            const Tensor &A = g.tensors[a], &W = g.tensors[w];
+            if (A.ty != 0 || W.ty != 0 || W.nb[0] != 4 || W.ne[1] * W.ne[2] * W.ne[3] != 1 || !dense_rows(A, 4)) continue;
+            Q.op = "ROW_QUANT";
+            Q.op_params[2] = RQ_NORM;
+            Q.op_params[15] = P.op_params[15];
+            Q.src[0] = a;
+            Q.src[1] = -1;
+            Q.src[3] = w;
+            dead[xp] = 1;
+            // residual ADD in front of the norm: computed (and written back) by the same launch
+            const int32_t aroot = g.root(a);
+            const int ap = pos_of[aroot];
+            if (a == aroot && ap >= 0 && !dead[ap] && g.tensors[a].op == "ADD") {
+                const Tensor R = g.tensors[a];
+                const int32_t s0 = R.src[0], s1 = R.src[1];
+                bool ok = s0 >= 0 && s1 >= 0 && g.tensors[s0].ty == 0 && g.tensors[s1].ty == 0 && R.is_contiguous() &&
+                          dense_rows(g.tensors[s0], 4) && dense_rows(g.tensors[s1], 4);
+                for (int k = 0; ok && k < 4; k++) ok = g.tensors[s0].ne[k] == R.ne[k] && g.tensors[s1].ne[k] == R.ne[k];
+                // nobody may read the sum between the ADD's old position and the fused node
+                readers(aroot, rd);
+                for (int r : rd) ok = ok && (r >= (int)qi || r == xp);
+                if (ok) {
+                    Q.src[0] = s0;
+                    Q.src[1] = s1;
+                    Q.src[4] = a;   // the sum is written into the ADD's own tensor
+                    dead[ap] = 1;
+                }
+            }
+        } else if (P.op == "GLU" && xroot == x && P.op_params[0] == 2 && P.src[0] >= 0 && P.src[1] >= 0) {
+            const Tensor &G0 = g.tensors[P.src[0]], &U0 = g.tensors[P.src[1]];
+            if (G0.ty != 0 || U0.ty != 0 || !dense_rows(G0, 4) || !dense_rows(U0, 4)) continue;
+            Q.op = "ROW_QUANT";
+            Q.op_params[2] = RQ_GLU;
+            Q.src[0] = P.src[0];
+            Q.src[1] = P.src[1];
+            dead[xp] = 1;
+        } else if (P.op == "CPY" && P.src[0] >= 0 && g.tensors[P.src[0]].ty == TLB_TYPE_F16 && P.is_contiguous() &&
+                   g.tensors[P.src[0]].is_contiguous() && P.view_src < 0) {
+            Q.op = "ROW_QUANT";
+            Q.op_params[2] = RQ_F16;
+            Q.src[0] = P.src[0];
+            Q.src[1] = -1;
+            Q.src[5] = x;   // keeps the shape of the activation matrix (a view of the folded cast)
+            dead[xp] = 1;
+        }
+    }
+    std::vector<int32_t> out;
+    for (size_t i = 0; i < nn; i++)
+        if (!dead[i]) out.push_back(g.nodes[i]);
+    g.nodes.swap(out);
 }
 
 }  // namespace tlb
