@@ -167,6 +167,29 @@ tlb_status tlb_quantize_rows_device(tlb_device *dev, uint32_t type, const void *
 /* Type table of crates/kernels/src/graph.rs:30-50: bytes of a row of ne0 elements, 0 if unknown. */
 uint64_t   tlb_row_size(uint32_t type, int64_t ne0);
 
+/* ------------------------------------------------------------------ paged attention with no allocation
+ * No counterpart in the reference (its paged attention allocates its scratch when the node is lowered,
+ * crates/kernels/src/cuda/paged_attn.rs). For callers that may not allocate device memory -- a decode
+ * loop that keeps the allocator off its latency path, a host confined to a fixed reservation, code
+ * that runs while another component owns the allocator -- this is paged-attention decode (the CUSTOM
+ * kind-1 node, same kernels and same results as through a program) whose only scratch, the
+ * split-context partial sums, lives in an 8 MiB array inside the library image. Every GPU that
+ * loads the library holds those 8 MiB until the process exits.
+ *   q, out          f16 [seqs][heads][head_size]          (device pointers, caller-owned)
+ *   k_pool, v_pool  f16 [block][kv_heads][block_size][head_size], as the cache-write node fills them
+ *   block_tables    i32 [seqs][max_blocks], context_lens i32 [seqs]
+ * Calls no cudaMalloc/cudaFree and no allocating library routine; enqueues on the device's stream and
+ * waits. Shapes whose partial sums exceed 8 MiB are refused with TLB_INVALID (the message gives both
+ * sizes); run those through a compiled program instead. The first call on a device looks up the
+ * array's device address (cudaGetSymbolAddress): make that first call before any stream capture.
+ * All calls share the one array and leave their partial sums in it; nothing in it needs clearing
+ * between calls, but two calls that overlap on the same GPU race on it (each GPU has its own copy of
+ * the array): issue them one after another. */
+tlb_status tlb_paged_attention_static(tlb_device *dev, const void *q, const void *k_pool, const void *v_pool,
+                                      const int32_t *block_tables, const int32_t *context_lens, void *out, int seqs,
+                                      int heads, int kv_heads, int head_size, int block_size, int max_blocks,
+                                      int max_context, float scale);
+
 /* ------------------------------------------------------------------ tensor parallelism
  * No counterpart in the reference (single device: model.rs:415-422). A communicator joins the
  * ranks of one box; programs compiled on a device with a communicator may contain the pseudo-op

@@ -96,6 +96,8 @@ SYMBOLS = {
     "tlb_quantize_rows": (C.c_int, [_P, C.c_uint32, _P, C.c_int64, C.c_int64, _P]),
     "tlb_quantize_rows_device": (C.c_int, [_P, C.c_uint32, _P, C.c_int64, C.c_int64, _P]),
     "tlb_row_size": (C.c_uint64, [C.c_uint32, C.c_int64]),
+    "tlb_paged_attention_static": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                            C.c_int, C.c_float]),
     "tlb_comm_unique_id": (C.c_int, [_P]),
     "tlb_comm_init": (C.c_int, [_P, C.c_int, C.c_int, _P]),
     "tlb_comm_destroy": (C.c_int, [_P]),

@@ -18,6 +18,7 @@
 #include <math_constants.h>
 
 #include "kernels.h"
+#include "tlb_internal.h"
 
 namespace tlb {
 
@@ -416,3 +417,67 @@ cudaError_t launch_paged_gather(int seqs, int kv_heads, int hs, int block_size, 
 }
 
 }  // namespace tlb
+
+// ---------------------------------------------------------------- paged attention without any allocation
+// Some callers may not allocate device memory at all: a serving loop that must never touch the
+// allocator on its latency path, a host that runs under a fixed memory reservation it does not
+// control, code running while another library owns the allocator. For them the split-context
+// partial sums (the only scratch paged attention needs) live in this fixed array. It is part of
+// the library image: every GPU that loads the library holds these bytes until the process exits.
+#define TLB_PA_STATIC_SCRATCH_BYTES (8u << 20)
+static __device__ __align__(256) unsigned char g_pa_static_scratch[TLB_PA_STATIC_SCRATCH_BYTES];
+
+namespace tlb {
+// In host code the array's name is only a handle for the runtime, not a device address; the address
+// is looked up once per device, with that device current, and cached here.
+static void *g_pa_scratch_addr[64] = {nullptr};
+static cudaError_t pa_static_scratch(int ordinal, void **out) {
+    if (ordinal < 0 || ordinal >= 64) return cudaErrorInvalidDevice;
+    if (!g_pa_scratch_addr[ordinal]) {
+        void *p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_pa_static_scratch);
+        if (e != cudaSuccess) return e;
+        g_pa_scratch_addr[ordinal] = p;
+    }
+    *out = g_pa_scratch_addr[ordinal];
+    return cudaSuccess;
+}
+}  // namespace tlb
+
+extern "C" tlb_status tlb_paged_attention_static(tlb_device *dev, const void *q, const void *k_pool, const void *v_pool,
+                                                 const int32_t *block_tables, const int32_t *context_lens, void *out, int seqs,
+                                                 int heads, int kv_heads, int head_size, int block_size, int max_blocks,
+                                                 int max_context, float scale) {
+    using namespace tlb;
+    if (!dev || !q || !k_pool || !v_pool || !block_tables || !context_lens || !out)
+        return fail(TLB_INVALID, "tlb_paged_attention_static: null argument");
+    PagedGeom g{};
+    g.seqs = seqs;
+    g.heads = heads;
+    g.kv_heads = kv_heads;
+    g.hs = head_size;
+    g.block_size = block_size;
+    g.max_ctx = max_context;
+    g.max_blocks = max_blocks;
+    g.scale = scale;
+    if (seqs < 0 || heads < 1 || max_context < 1 || !paged_supported(g))
+        return fail(TLB_UNSUPPORTED, "tlb_paged_attention_static: head size must be 64, 128 or 256, the block size a power of two and the query heads a multiple of the kv heads");
+    if ((int64_t)max_blocks * block_size < max_context) return fail(TLB_INVALID, "block tables are shorter than the maximum context");
+    if (cudaSetDevice(dev->ordinal) != cudaSuccess) return fail(TLB_NO_DEVICE, "cannot make the device current");
+    paged_plan(g, dev->prop.multiProcessorCount);
+    const uint64_t need = paged_scratch_bytes(g);
+    if (need > TLB_PA_STATIC_SCRATCH_BYTES)
+        return fail(TLB_INVALID, "tlb_paged_attention_static: this shape needs " + std::to_string(need) + " bytes of scratch, the built-in scratch holds " +
+                                     std::to_string((uint64_t)TLB_PA_STATIC_SCRATCH_BYTES) + "; use a compiled program (tlb_program_run) for it");
+    void *scratch = nullptr;
+    cudaError_t e = pa_static_scratch(dev->ordinal, &scratch);
+    if (e != cudaSuccess) return fail(TLB_EXECUTION, "cudaGetSymbolAddress: " + cuda_msg(e));
+    // nothing in the scratch has to start at zero: every chunk that the reduce reads is written by this launch
+    e = launch_paged_attention(g, q, k_pool, v_pool, block_tables, context_lens, out, scratch, dev->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(dev->stream);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(TLB_EXECUTION, "tlb_paged_attention_static: " + cuda_msg(e));
+    }
+    return TLB_OK;
+}
