@@ -11,6 +11,7 @@
 // mbarrier) through a multi-stage ring, so tens of KB per SM are always in flight without
 // spending registers or issue slots; warps then take 128-bit pieces of a super-block out of
 // shared memory, unpack nibbles in registers, and use dp4a against the int8 activations.
+#include <algorithm>
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
 
@@ -55,24 +56,53 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
-constexpr int GEMV_THREADS = 256;
-constexpr int GEMV_WARPS = GEMV_THREADS / 32;
-constexpr int GEMV_STAGES = 4;
-constexpr int GEMV_STAGE_BYTES = 40 * 1024;  // tile of whole rows, at most this many bytes
-constexpr int GEMV_PAD = 16;                 // word-aligned reads may run 2 bytes past a block
+constexpr int GEMV_CW = 16;                       // consumer warps
+constexpr int GEMV_THREADS = 32 * (GEMV_CW + 1);  // plus one warp whose lane 0 issues the bulk copies
+constexpr int GEMV_STAGES = 4;                    // power of two
+constexpr int GEMV_STAGE_BYTES = 40 * 1024;       // tile of whole rows, at most this many bytes
+constexpr int GEMV_PAD = 16;                      // word-aligned reads may run 2 bytes past a block
+constexpr int GEMV_ACT_SMEM = 60 * 1024;          // Q4_K: int8 activation codes of one pass, staged in shared memory
+
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+// unsigned bytes x signed bytes
+__device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// Shared-memory order of one column's int8 codes for the Q4_K kernel: a warp iteration covers 8
+// super-blocks = 32 chunks of 64 codes (lane = chunk); the j-th 16-byte piece of every chunk of an
+// iteration is contiguous in lane order, so each of a lane's four 128-bit reads is conflict-free.
+__device__ __forceinline__ int q4k_act_slot(int piece16) {  // index of a 16-byte piece -> byte offset
+    const int g = piece16 >> 2, j = piece16 & 3;
+    return (((g >> 5) * 4 + j) << 9) + ((g & 31) << 4);
+}
 
 // ---------------------------------------------------------------- per-row dot products from shared memory
+// Four lanes share a super-block: lane c of them owns the 32 nibble bytes of sub-blocks 2c (low
+// nibbles) and 2c+1 (high nibbles), so the 6-bit scale decode is paid once per 64 weights. The
+// high nibbles are used in place (16 x their value, as unsigned bytes); the factor leaves as an
+// exact shift of the integer sum.
 template <int NC>
-__device__ __forceinline__ void row_q4_K(const uint8_t *row, int64_t K, const int8_t *aq, const float *ad,
-                                         const int16_t *ab, int n0, int lane, int part, int wpr, float (&f)[NC]) {
-    const int piece = lane & 7, c = piece >> 1, half = piece & 1;
-    const int nsb = (int)(K / 256);
-    for (int sb = (lane >> 3) + 4 * part; sb < nsb; sb += 4 * wpr) {
-        const uint4 hdr = *reinterpret_cast<const uint4 *>(row + sb * 144);
-        const uint4 q = *reinterpret_cast<const uint4 *>(row + sb * 144 + 16 + 16 * piece);
+__device__ __forceinline__ void row_q4_K(const uint8_t *row, int nsb, const uint8_t *sact, int act_stride,
+                                         const float *ad, const int16_t *ab, int lane, int part, int wpr, float (&f)[NC]) {
+    const int c = lane & 3;
+    const int sh = (c & 1) * 16;
+    for (int it = part; it * 8 < nsb; it += wpr) {
+        const int sb = it * 8 + (lane >> 2);
+        if (sb >= nsb) break;
+        const uint8_t *blk = row + sb * 144;
+        const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
+        const uint4 q0 = *reinterpret_cast<const uint4 *>(blk + 16 + 32 * c);
+        const uint4 q1 = *reinterpret_cast<const uint4 *>(blk + 32 + 32 * c);
         const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
         // 6-bit scales/mins of sub-blocks 2c and 2c+1 (get_scale_min_k4, ggml-quants.c:880-887)
-        const int sh = (c & 1) * 16;
         const uint32_t a16 = (hdr.y >> sh) & 0xffffu, b16 = (hdr.z >> sh) & 0xffffu, c16 = (hdr.w >> sh) & 0xffffu;
         uint32_t sc2, m2;
         if (c < 2) {
@@ -83,27 +113,34 @@ __device__ __forceinline__ void row_q4_K(const uint8_t *row, int64_t K, const in
             m2 = ((c16 >> 4) & 0x0f0fu) | ((b16 >> 2) & 0x3030u);
         }
         const int sc_lo = sc2 & 0xff, sc_hi = sc2 >> 8, m_lo = m2 & 0xff, m_hi = m2 >> 8;
-        const uint32_t lo[4] = {q.x & 0x0f0f0f0fu, q.y & 0x0f0f0f0fu, q.z & 0x0f0f0f0fu, q.w & 0x0f0f0f0fu};
-        const uint32_t hi[4] = {(q.x >> 4) & 0x0f0f0f0fu, (q.y >> 4) & 0x0f0f0f0fu, (q.z >> 4) & 0x0f0f0f0fu,
-                                (q.w >> 4) & 0x0f0f0f0fu};
-        const int64_t kbase = (int64_t)sb * 256 + c * 64 + half * 16;
+        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        const uint8_t *a = sact + it * 2048 + lane * 16;
 #pragma unroll
         for (int n = 0; n < NC; n++) {
-            const int8_t *a = aq + (int64_t)(n0 + n) * K + kbase;
-            const int4 al = *reinterpret_cast<const int4 *>(a);
-            const int4 ah = *reinterpret_cast<const int4 *>(a + 32);
-            int il = __dp4a((int)lo[0], al.x, 0);
-            il = __dp4a((int)lo[1], al.y, il);
-            il = __dp4a((int)lo[2], al.z, il);
-            il = __dp4a((int)lo[3], al.w, il);
-            int ih = __dp4a((int)hi[0], ah.x, 0);
-            ih = __dp4a((int)hi[1], ah.y, ih);
-            ih = __dp4a((int)hi[2], ah.z, ih);
-            ih = __dp4a((int)hi[3], ah.w, ih);
-            const int16_t *bs = ab + (int64_t)(n0 + n) * (K / 16) + sb * 16 + 4 * c + half;
-            const int acc = sc_lo * il + sc_hi * ih;
-            const int macc = m_lo * (int)bs[0] + m_hi * (int)bs[2];
-            const float yd = ad[(int64_t)(n0 + n) * (K / 256) + sb];
+            const int4 a0 = *reinterpret_cast<const int4 *>(a + n * act_stride);
+            const int4 a1 = *reinterpret_cast<const int4 *>(a + n * act_stride + 512);
+            const int4 a2 = *reinterpret_cast<const int4 *>(a + n * act_stride + 1024);
+            const int4 a3 = *reinterpret_cast<const int4 *>(a + n * act_stride + 1536);
+            int il = __dp4a((int)(w[0] & 0x0f0f0f0fu), a0.x, 0), il2 = __dp4a((int)(w[4] & 0x0f0f0f0fu), a1.x, 0);
+            il = __dp4a((int)(w[1] & 0x0f0f0f0fu), a0.y, il);
+            il2 = __dp4a((int)(w[5] & 0x0f0f0f0fu), a1.y, il2);
+            il = __dp4a((int)(w[2] & 0x0f0f0f0fu), a0.z, il);
+            il2 = __dp4a((int)(w[6] & 0x0f0f0f0fu), a1.z, il2);
+            il = __dp4a((int)(w[3] & 0x0f0f0f0fu), a0.w, il);
+            il2 = __dp4a((int)(w[7] & 0x0f0f0f0fu), a1.w, il2);
+            int ih = dp4a_us(w[0] & 0xf0f0f0f0u, a2.x, 0), ih2 = dp4a_us(w[4] & 0xf0f0f0f0u, a3.x, 0);
+            ih = dp4a_us(w[1] & 0xf0f0f0f0u, a2.y, ih);
+            ih2 = dp4a_us(w[5] & 0xf0f0f0f0u, a3.y, ih2);
+            ih = dp4a_us(w[2] & 0xf0f0f0f0u, a2.z, ih);
+            ih2 = dp4a_us(w[6] & 0xf0f0f0f0u, a3.z, ih2);
+            ih = dp4a_us(w[3] & 0xf0f0f0f0u, a2.w, ih);
+            ih2 = dp4a_us(w[7] & 0xf0f0f0f0u, a3.w, ih2);
+            // bsums of the four 16-value groups of this chunk: two per sub-block
+            const int2 bs = *reinterpret_cast<const int2 *>(ab + n * (nsb * 16) + sb * 16 + 4 * c);
+            const int b_lo = (int)(short)(bs.x & 0xffff) + (bs.x >> 16), b_hi = (int)(short)(bs.y & 0xffff) + (bs.y >> 16);
+            const int acc = sc_lo * (il + il2) + sc_hi * ((ih + ih2) >> 4);
+            const int macc = m_lo * b_lo + m_hi * b_hi;
+            const float yd = ad[n * nsb + sb];
             f[n] += yd * (dm.x * (float)acc - dm.y * (float)macc);
         }
     }
@@ -111,9 +148,9 @@ __device__ __forceinline__ void row_q4_K(const uint8_t *row, int64_t K, const in
 
 // 34-byte / 18-byte blocks are only 2-byte aligned: read whole words and realign by 16 bits.
 template <int NC>
-__device__ __forceinline__ void row_q8_0(const uint8_t *row, int64_t K, const int8_t *aq, const float *ad, int n0,
-                                         int lane, int part, int wpr, float (&f)[NC]) {
-    const int nblk = (int)(K / 32);
+__device__ __forceinline__ void row_q8_0(const uint8_t *row, int K, const int8_t *aq, const float *ad, int lane,
+                                         int part, int wpr, float (&f)[NC]) {
+    const int nblk = K / 32;
     for (int b = lane + 32 * part; b < nblk; b += 32 * wpr) {
         const uint32_t *w = reinterpret_cast<const uint32_t *>(row + ((34 * b) & ~3));
         uint32_t r[9];
@@ -133,7 +170,7 @@ __device__ __forceinline__ void row_q8_0(const uint8_t *row, int64_t K, const in
         const float d = __half2float(__ushort_as_half(dh));
 #pragma unroll
         for (int n = 0; n < NC; n++) {
-            const int4 *a = reinterpret_cast<const int4 *>(aq + (int64_t)(n0 + n) * K + (int64_t)b * 32);
+            const int4 *a = reinterpret_cast<const int4 *>(aq + n * K + b * 32);
             const int4 a0 = a[0], a1 = a[1];
             int s = __dp4a((int)qs[0], a0.x, 0);
             s = __dp4a((int)qs[1], a0.y, s);
@@ -143,15 +180,15 @@ __device__ __forceinline__ void row_q8_0(const uint8_t *row, int64_t K, const in
             s = __dp4a((int)qs[5], a1.y, s);
             s = __dp4a((int)qs[6], a1.z, s);
             s = __dp4a((int)qs[7], a1.w, s);
-            f[n] += (float)s * (d * ad[(int64_t)(n0 + n) * (K / 32) + b]);
+            f[n] += (float)s * (d * ad[n * nblk + b]);
         }
     }
 }
 
 template <int NC>
-__device__ __forceinline__ void row_q4_0(const uint8_t *row, int64_t K, const int8_t *aq, const float *ad, int n0,
-                                         int lane, int part, int wpr, float (&f)[NC]) {
-    const int nblk = (int)(K / 32);
+__device__ __forceinline__ void row_q4_0(const uint8_t *row, int K, const int8_t *aq, const float *ad, int lane,
+                                         int part, int wpr, float (&f)[NC]) {
+    const int nblk = K / 32;
     for (int b = lane + 32 * part; b < nblk; b += 32 * wpr) {
         const uint32_t *w = reinterpret_cast<const uint32_t *>(row + ((18 * b) & ~3));
         uint32_t r[5];
@@ -171,7 +208,7 @@ __device__ __forceinline__ void row_q4_0(const uint8_t *row, int64_t K, const in
         const float d = __half2float(__ushort_as_half(dh));
 #pragma unroll
         for (int n = 0; n < NC; n++) {
-            const int4 *a = reinterpret_cast<const int4 *>(aq + (int64_t)(n0 + n) * K + (int64_t)b * 32);
+            const int4 *a = reinterpret_cast<const int4 *>(aq + n * K + b * 32);
             const int4 a0 = a[0], a1 = a[1];
             const int av0[4] = {a0.x, a0.y, a0.z, a0.w}, av1[4] = {a1.x, a1.y, a1.z, a1.w};
             int s = 0;
@@ -182,113 +219,131 @@ __device__ __forceinline__ void row_q4_0(const uint8_t *row, int64_t K, const in
                 s = __dp4a(lo, av0[i], s);
                 s = __dp4a(hi, av1[i], s);
             }
-            f[n] += (float)s * d * ad[(int64_t)(n0 + n) * (K / 32) + b];
+            f[n] += (float)s * d * ad[n * nblk + b];
         }
     }
 }
 
 // ---------------------------------------------------------------- the streaming kernel
+// One CTA per SM. Warp GEMV_CW (lane 0) is the producer: it refills a stage as soon as every
+// consumer warp has released it (empty barrier, one arrival per warp). The 16 consumer warps never
+// meet at a CTA-wide barrier: each waits for a stage, reduces its own rows and releases it.
 template <int TYPE, int NC>
 __global__ void __launch_bounds__(GEMV_THREADS, 1)
-k_gemv_stream(const uint8_t *__restrict__ W, int64_t row_bytes, int64_t M, int64_t K, const int8_t *__restrict__ aq,
+k_gemv_stream(const uint8_t *__restrict__ W, int row_bytes, int64_t M, int K, const int8_t *__restrict__ aq,
               const float *__restrict__ ad, const int16_t *__restrict__ ab, float *__restrict__ y, int64_t ldy, int n0,
-              int rows_per_tile, int wpr, int stage_stride, int *__restrict__ err) {
+              int rows_per_tile, int wpr_log, int stage_stride, int act_stride, int *__restrict__ err) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ uint64_t full[GEMV_STAGES];
-    __shared__ int s_fail;
-    __shared__ float partial[2][GEMV_WARPS][NC];
-    int pbuf = 0;
-    const int rows_per_pass = GEMV_WARPS / wpr;
+    __shared__ uint64_t full[GEMV_STAGES], empty[GEMV_STAGES];
+    __shared__ float partial[2][GEMV_CW][NC];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wpr = 1 << wpr_log;
+    const int rows_per_pass = GEMV_CW >> wpr_log;
     const int64_t n_tiles = (M + rows_per_tile - 1) / rows_per_tile;
-    const int64_t my_tiles = blockIdx.x < n_tiles ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int my_tiles = blockIdx.x < n_tiles ? (int)((n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
+    uint8_t *sact = smem + GEMV_STAGES * stage_stride;
     if (tid == 0) {
-        for (int s = 0; s < GEMV_STAGES; s++) mbar_init(&full[s], 1);
-        s_fail = 0;
+        for (int s = 0; s < GEMV_STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], GEMV_CW);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    auto issue = [&](int64_t i) {  // tile i of this CTA -> stage i % STAGES
-        const int64_t tile = blockIdx.x + i * gridDim.x;
-        const int64_t r0 = tile * rows_per_tile;
-        const int64_t rows = min((int64_t)rows_per_tile, M - r0);
-        const uint32_t bytes = (uint32_t)(rows * row_bytes);
-        const int s = (int)(i % GEMV_STAGES);
-        mbar_expect_tx(&full[s], bytes);
-        bulk_g2s(smem + (size_t)s * stage_stride, W + r0 * row_bytes, bytes, &full[s]);
-    };
-    if (tid == 0)
-        for (int64_t i = 0; i < my_tiles && i < GEMV_STAGES; i++) issue(i);
 
-    int64_t issued = my_tiles < GEMV_STAGES ? my_tiles : GEMV_STAGES;
-    int64_t done = 0;
-    for (int64_t i = 0; i < my_tiles; i++) {
-        const int s = (int)(i % GEMV_STAGES);
-        const bool ok = !__syncthreads_or(!mbar_wait(&full[s], (uint32_t)((i / GEMV_STAGES) & 1)));  // uniform
-        if (!ok) {
-            if (tid == 0) s_fail = 1;
-            __syncthreads();
-            break;
+    if (warp == GEMV_CW) {
+        if (lane != 0) return;
+        int issued = 0;
+        bool ok = true;
+        for (int i = 0; i < my_tiles && ok; i++) {
+            const int s = i & (GEMV_STAGES - 1);
+            if (i >= GEMV_STAGES) ok = mbar_wait(&empty[s], (uint32_t)(((i / GEMV_STAGES) - 1) & 1));
+            if (!ok) break;
+            const int64_t r0 = (blockIdx.x + (int64_t)i * gridDim.x) * rows_per_tile;
+            const int rows = (int)min((int64_t)rows_per_tile, M - r0);
+            const uint32_t bytes = (uint32_t)(rows * row_bytes);
+            mbar_expect_tx(&full[s], bytes);
+            bulk_g2s(smem + s * stage_stride, W + r0 * row_bytes, bytes, &full[s]);
+            issued = i + 1;
         }
-        const int64_t tile = blockIdx.x + i * gridDim.x;
-        const int64_t r0 = tile * rows_per_tile;
+        if (!ok) {
+            // the consumers stopped releasing stages: record it, then wait (bounded) for the copies
+            // still in flight before the CTA's shared memory is released
+            atomicExch(err, 1);
+            for (int j = max(0, issued - GEMV_STAGES); j < issued; j++)
+                mbar_wait(&full[j & (GEMV_STAGES - 1)], (uint32_t)((j / GEMV_STAGES) & 1));
+        }
+        return;
+    }
+
+    // ---- consumers
+    aq += (int64_t)n0 * K;
+    if (TYPE == TLB_TYPE_Q4_K) {
+        // int8 codes of this pass's columns -> shared memory, in the lane order of row_q4_K
+        const int pieces = K / 16;
+        for (int n = 0; n < NC; n++)
+            for (int p = tid; p < pieces; p += GEMV_CW * 32)
+                *reinterpret_cast<int4 *>(sact + n * act_stride + q4k_act_slot(p)) =
+                    *reinterpret_cast<const int4 *>(aq + (int64_t)n * K + p * 16);
+        named_bar_sync(1, GEMV_CW * 32);
+    }
+    const int nblk = TYPE == TLB_TYPE_Q4_K ? K / 256 : K / 32;
+    ad += (int64_t)n0 * nblk;
+    if (TYPE == TLB_TYPE_Q4_K) ab += (int64_t)n0 * (K / 16);
+    y += (int64_t)n0 * ldy;
+    const int grp = warp >> wpr_log, part = warp & (wpr - 1);
+    int pbuf = 0;
+    for (int i = 0; i < my_tiles; i++) {
+        const int s = i & (GEMV_STAGES - 1);
+        if (!mbar_wait(&full[s], (uint32_t)((i / GEMV_STAGES) & 1))) {
+            if (lane == 0) atomicExch(err, 1);
+            break;  // this warp stops releasing stages; the producer's bounded wait ends the CTA
+        }
+        const int64_t r0 = (blockIdx.x + (int64_t)i * gridDim.x) * rows_per_tile;
         const int rows = (int)min((int64_t)rows_per_tile, M - r0);
-        if (ok) {
-            const uint8_t *base = smem + (size_t)s * stage_stride;
-            for (int rb = 0; rb < rows; rb += rows_per_pass) {
-                const int r = rb + warp / wpr, part = warp % wpr;
-                float f[NC];
+        const uint8_t *base = smem + s * stage_stride;
+        for (int r = grp; r < rows; r += rows_per_pass) {
+            float f[NC];
 #pragma unroll
-                for (int n = 0; n < NC; n++) f[n] = 0.f;
-                if (r < rows) {
-                    const uint8_t *row = base + (size_t)r * row_bytes;
-                    if (TYPE == TLB_TYPE_Q4_K) row_q4_K<NC>(row, K, aq, ad, ab, n0, lane, part, wpr, f);
-                    else if (TYPE == TLB_TYPE_Q8_0) row_q8_0<NC>(row, K, aq, ad, n0, lane, part, wpr, f);
-                    else row_q4_0<NC>(row, K, aq, ad, n0, lane, part, wpr, f);
+            for (int n = 0; n < NC; n++) f[n] = 0.f;
+            const uint8_t *row = base + r * row_bytes;
+            if (TYPE == TLB_TYPE_Q4_K) row_q4_K<NC>(row, nblk, sact, act_stride, ad, ab, lane, part, wpr, f);
+            else if (TYPE == TLB_TYPE_Q8_0) row_q8_0<NC>(row, K, aq, ad, lane, part, wpr, f);
+            else row_q4_0<NC>(row, K, aq, ad, lane, part, wpr, f);
+#pragma unroll
+            for (int n = 0; n < NC; n++) f[n] = warp_sum(f[n]);
+            if (wpr == 1) {
+                if (lane == 0) {
+#pragma unroll
+                    for (int n = 0; n < NC; n++) y[n * ldy + r0 + r] = f[n];
                 }
+            } else {
+                // the warps of a row combine their partial sums in a fixed order; the pair of
+                // buffers lets the fastest warp run one row ahead of the one that adds them up
+                if (lane == 0) {
 #pragma unroll
-                for (int n = 0; n < NC; n++) f[n] = warp_sum(f[n]);
-                if (wpr == 1) {
-                    if (lane == 0 && r < rows) {
-#pragma unroll
-                        for (int n = 0; n < NC; n++) y[(int64_t)(n0 + n) * ldy + r0 + r] = f[n];
-                    }
-                } else {
-                    // several warps share a row: combine their partial sums through shared memory
-                    if (lane == 0) {
-#pragma unroll
-                        for (int n = 0; n < NC; n++) partial[pbuf][warp][n] = f[n];
-                    }
-                    __syncthreads();
-                    if (tid < rows_per_pass * NC) {
-                        const int rr = tid / NC, n = tid % NC;
-                        if (rb + rr < rows) {
-                            float v = 0.f;
-                            for (int pp = 0; pp < wpr; pp++) v += partial[pbuf][rr * wpr + pp][n];
-                            y[(int64_t)(n0 + n) * ldy + r0 + rb + rr] = v;
-                        }
-                    }
-                    pbuf ^= 1;
+                    for (int n = 0; n < NC; n++) partial[pbuf][warp][n] = f[n];
                 }
+                named_bar_sync(2 + grp, 32 * wpr);
+                if (part == 0 && lane < NC) {
+                    float v = 0.f;
+                    for (int pp = 0; pp < wpr; pp++) v += partial[pbuf][warp + pp][lane];
+                    y[lane * ldy + r0 + r] = v;
+                }
+                pbuf ^= 1;
             }
         }
-        __syncthreads();  // every warp is done with stage s
-        done = i + 1;
-        if (tid == 0 && i + GEMV_STAGES < my_tiles) {
-            issue(i + GEMV_STAGES);
-            issued = i + GEMV_STAGES + 1;
-        }
-    }
-    if (s_fail && tid == 0) {
-        // wait (bounded) for the copies still in flight before the CTA's shared memory is released
-        for (int64_t j = done; j < issued; j++) mbar_wait(&full[j % GEMV_STAGES], (uint32_t)((j / GEMV_STAGES) & 1));
-        atomicExch(err, 1);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
     }
 }
 
+static uint64_t q4k_act_bytes(int64_t K) { return (uint64_t)((K / 256 + 7) / 8) * 2048; }
+
 bool gemv_supported(uint32_t type, int64_t K, int64_t M, int64_t N) {
     if (type != TLB_TYPE_Q4_K && type != TLB_TYPE_Q8_0 && type != TLB_TYPE_Q4_0) return false;
-    if (K % 256 != 0 || M < 1 || N < 1) return false;
+    if (K % 256 != 0 || M < 1 || N < 1 || K > (1 << 20)) return false;
+    if (type == TLB_TYPE_Q4_K && q4k_act_bytes(K) > GEMV_ACT_SMEM) return false;
     const int64_t rb = (int64_t)tlb_row_size(type, K);
     return rb % 16 == 0 && rb + GEMV_PAD <= GEMV_STAGE_BYTES;
 }
@@ -296,7 +351,7 @@ bool gemv_supported(uint32_t type, int64_t K, int64_t M, int64_t N) {
 template <int TYPE, int NC>
 static void set_attr() {
     cudaFuncSetAttribute(k_gemv_stream<TYPE, NC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         GEMV_STAGES * (GEMV_STAGE_BYTES + 128));
+                         GEMV_STAGES * (GEMV_STAGE_BYTES + 128) + (TYPE == TLB_TYPE_Q4_K ? GEMV_ACT_SMEM : 0));
 }
 template <int TYPE>
 static void set_attr_type() {
@@ -312,31 +367,41 @@ template <int TYPE>
 static cudaError_t launch_gemv_t(const void *W, int64_t K, int64_t M, const ActLayout &a, const void *act, float *y,
                                  int64_t ldy, int sm_count, int *err, cudaStream_t st) {
     const int64_t rb = (int64_t)tlb_row_size(TYPE, K);
-    int rows_per_tile = (int)((GEMV_STAGE_BYTES - GEMV_PAD) / rb);
+    int max_rows = (int)((GEMV_STAGE_BYTES - GEMV_PAD) / rb);
     // keep every SM busy: no more rows per tile than gives each SM a few tiles
     const int64_t want_tiles = (int64_t)sm_count * 4;
     const int64_t cap = (M + want_tiles - 1) / want_tiles;
-    if (rows_per_tile > cap) rows_per_tile = (int)(cap < 1 ? 1 : cap);
-    // whole warps' worth of rows keeps the 8 warps evenly loaded; with fewer rows than warps,
-    // several warps share a row
-    if (rows_per_tile > GEMV_WARPS) rows_per_tile = rows_per_tile / GEMV_WARPS * GEMV_WARPS;
-    int wpr = 1;
-    while (wpr * 2 * rows_per_tile <= GEMV_WARPS) wpr *= 2;
-    const int64_t units = TYPE == TLB_TYPE_Q4_K ? K / 256 / 4 : K / 32 / 32;  // loop trips of one warp
-    while (wpr > 1 && units < wpr) wpr /= 2;
+    if (max_rows > cap) max_rows = (int)(cap < 1 ? 1 : cap);
+    const int64_t units = TYPE == TLB_TYPE_Q4_K ? (K / 256 + 7) / 8 : (K / 32 + 31) / 32;  // loop trips of one warp
+    // rows per tile: a whole number of rows per consumer warp, or (fewer rows than warps) the
+    // count that keeps most warps busy when 2^j warps share a row
+    int rows_per_tile = max_rows, wpr_log = 0;
+    if (max_rows >= GEMV_CW) {
+        rows_per_tile = max_rows / GEMV_CW * GEMV_CW;
+    } else {
+        int best = -1;
+        for (int r = 1; r <= max_rows; r++) {
+            int wl = 0;
+            while ((2 << wl) * r <= GEMV_CW && (2 << wl) <= units) wl++;
+            const int used = r << wl;
+            if (used >= best) { best = used; rows_per_tile = r; wpr_log = wl; }
+        }
+    }
     const int stage_stride = (int)(((int64_t)rows_per_tile * rb + GEMV_PAD + 127) / 128 * 128);
     const int64_t n_tiles = (M + rows_per_tile - 1) / rows_per_tile;
     const int grid = (int)(n_tiles < sm_count ? n_tiles : sm_count);
-    const size_t smem = (size_t)GEMV_STAGES * stage_stride;
+    const int act_stride = TYPE == TLB_TYPE_Q4_K ? (int)q4k_act_bytes(K) : 0;
+    const int nc_max = TYPE == TLB_TYPE_Q4_K ? (int)std::min<int64_t>(4, GEMV_ACT_SMEM / act_stride) : 4;
     const char *ab = (const char *)act;
     const int8_t *aq = (const int8_t *)(ab + a.qs_off);
     const float *ad = (const float *)(ab + a.d_off);
     const int16_t *bs = (const int16_t *)(ab + a.bsum_off);
     for (int n0 = 0; n0 < a.N;) {
-        const int nc = (int)(a.N - n0 >= 4 ? 4 : a.N - n0);
-#define GO(NCV)                                                                                                   \
-    k_gemv_stream<TYPE, NCV><<<grid, GEMV_THREADS, smem, st>>>((const uint8_t *)W, rb, M, K, aq, ad, bs, y, ldy, n0, \
-                                                              rows_per_tile, wpr, stage_stride, err)
+        const int nc = (int)std::min<int64_t>(nc_max, a.N - n0);
+        const size_t smem = (size_t)GEMV_STAGES * stage_stride + (size_t)nc * act_stride;
+#define GO(NCV)                                                                                                        \
+    k_gemv_stream<TYPE, NCV><<<grid, GEMV_THREADS, smem, st>>>((const uint8_t *)W, (int)rb, M, (int)K, aq, ad, bs, y, ldy, \
+                                                              n0, rows_per_tile, wpr_log, stage_stride, act_stride, err)
         switch (nc) {
             case 1: GO(1); break;
             case 2: GO(2); break;
