@@ -300,6 +300,97 @@ def run_ours(args) -> dict:
     return result if rank == 0 else {}
 
 
+
+# ---------------------------------------------------------------------------------- single-kernel runs
+def run_kernel(args) -> dict:
+    """`--kernel mul_mat:TYPE:K:M:N` or `--kernel paged_attention:SEQS:CTX` replays a program holding
+    only that op (several independent copies, so every replay reads more bytes than L2 holds) and
+    prints the launch time and the algorithmic bytes it moved. The commands under profiles/ use it
+    to give the profiler one kernel on a small, bounded case."""
+    import torch
+
+    from tensorlisp_b200 import graph as G
+    from tensorlisp_b200._lib import check
+    from tensorlisp_b200.native import Native, NativeProgram, StateBlock
+    from tensorlisp_b200.programs import DecoderConfig
+
+    spec = args.kernel.split(":")
+    rng = np.random.default_rng(0)
+    g = G.Graph()
+    if spec[0] == "mul_mat":
+        n = Native(0)
+        ty = {"q4_K": G.Q4_K, "q8_0": G.Q8_0, "q4_0": G.Q4_0}[spec[1]]
+        K, M, N = int(spec[2]), int(spec[3]), int(spec[4])
+        rs = G.row_size(ty, K)
+        copies = args.copies or max(2, int(300e6 // (rs * M)))
+        ws = [g.weight(ty, [K, M], "W%d" % i) for i in range(copies)]
+        x = g.input(G.F32, [K, N], "x")
+        for i, w in enumerate(ws):
+            g.output(g.mul_mat(w, x, "y%d" % i))
+        per = G.align256(rs * M)
+        h = C.c_void_p()
+        check(n.L.tlb_weights_create(n.dev, per * copies, C.byref(h)))
+        n.weights = StateBlock(h)
+        for i in range(copies):
+            n.weight_loc.append((0, per * i))
+            w = torch.randn((M, K), device="cuda") * 0.02
+            torch.cuda.synchronize()
+            check(n.L.tlb_quantize_rows_device(n.dev, ty, C.c_void_p(w.data_ptr()), M, K,
+                                               C.c_void_p(n.weights.device_ptr + per * i)))
+            n.sync()
+        n.alloc_states([])
+        prog = NativeProgram.compile(n, g)
+        prog.set_input(0, rng.standard_normal((N, K)).astype(np.float32))
+        bytes_per_launch = rs * M
+        what = "%s weights [%d x %d], %d activation column(s)" % (spec[1], M, K, N)
+    elif spec[0] == "paged_attention":
+        cfg = DecoderConfig()
+        seqs, ctx = int(spec[1]), int(spec[2])
+        copies = args.copies or 2
+        bs, kvh, hs, heads = cfg.block_size, cfg.n_kv_heads, cfg.head_dim, cfg.n_heads
+        max_blocks = (ctx + bs - 1) // bs
+        pool = seqs * max_blocks * kvh * bs * hs
+        pools = [(g.state(G.F16, [pool]), g.state(G.F16, [pool])) for _ in range(copies)]
+        q = g.input(G.F32, [hs, heads, seqs])
+        tt = g.input(G.I32, [max_blocks, seqs])
+        tl = g.input(G.I32, [seqs])
+        qh = g.cast(q, G.F16)
+        for kc, vc in pools:
+            g.output(g.paged_attention(qh, kc, vc, tt, tl, bs, ctx, 1.0 / np.sqrt(hs), kvh))
+        n = Native.load([])
+        n.alloc_states([pool * 2] * (2 * copies))
+        for off in n.state_offsets:
+            kv = torch.randn(pool, device="cuda", dtype=torch.float16)
+            n.state.copy_device(off, kv.data_ptr(), pool * 2)
+        prog = NativeProgram.compile(n, g)
+        prog.set_input(0, rng.standard_normal((seqs, heads, hs)).astype(np.float32))
+        prog.set_input(1, rng.permutation(seqs * max_blocks).astype(np.int32).reshape(seqs, max_blocks))
+        prog.set_input(2, np.full(seqs, ctx, np.int32))
+        bytes_per_launch = seqs * ctx * kvh * hs * 2 * 2
+        what = "%d sequences x %d tokens, %d/%d heads of %d, f16 pages of %d tokens" % (seqs, ctx, heads, kvh, hs, bs)
+    else:
+        raise SystemExit("unknown --kernel " + args.kernel)
+    for _ in range(max(args.warmup, 1)):
+        prog.run()
+    stream = torch.cuda.ExternalStream(n.stream())
+    ts = []
+    for _ in range(args.steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        prog.enqueue()
+        e1.record(stream)
+        n.sync()
+        ts.append(e0.elapsed_time(e1) / copies)
+    ms = float(np.median(ts))
+    peak, src = measured_peaks()
+    out = {"kernel": args.kernel, "what": what, "copies_per_replay": copies, "us_per_launch": ms * 1e3,
+           "algorithmic_bytes_per_launch": bytes_per_launch, "achieved_GBps": bytes_per_launch / ms / 1e6,
+           "peak_GBps": peak, "frac": bytes_per_launch / ms / 1e6 / peak, "of": src, "launches": prog.labels()}
+    prog.free()
+    n.close()
+    return out
+
+
 # ---------------------------------------------------------------------------------- reference arm (CPU)
 def cpu_reference_step(cfg, budget_s: float = 20.0, steps: int = 1, warmup: int = 0) -> dict:
     """The reference's own ggml CPU backend (the build of oracle/_ref that fits this host's CPU) on a
@@ -401,7 +492,13 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel", default="", help="time one kernel instead of the decode step, e.g. mul_mat:q4_K:4096:14336:1 "
+                                                 "or paged_attention:32:2048")
+    ap.add_argument("--copies", type=int, default=0, help="--kernel: independent copies of the op per replay")
     args = ap.parse_args()
+    if args.kernel:
+        print(json.dumps(run_kernel(args)), flush=True)
+        return
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     out = run_reference(args) if args.impl == "reference" else run_ours(args)
     if out:

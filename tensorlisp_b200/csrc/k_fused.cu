@@ -20,162 +20,156 @@ __device__ __forceinline__ int nearest_int_f(float v) {
 }
 
 constexpr int RQ_THREADS = 256;
-constexpr int RQ_MAXB = 8;   // 256-element blocks per warp held in registers: rows up to 16384 elements
+constexpr int RQ_WARPS = RQ_THREADS / 32;
 
+// The f32 value at (column n, element k) before any normalisation: a, a + b, act(a) * b or f16 a.
+__device__ __forceinline__ void rq_load8(const RowQuantArgs &p, int n, int64_t k0, float (&x)[8]) {
+    if (p.mode == RQ_GLU) {
+        const float4 g0 = *reinterpret_cast<const float4 *>(p.a + n * p.lda + k0), g1 = *reinterpret_cast<const float4 *>(p.a + n * p.lda + k0 + 4);
+        const float4 u0 = *reinterpret_cast<const float4 *>(p.b + n * p.ldb + k0), u1 = *reinterpret_cast<const float4 *>(p.b + n * p.ldb + k0 + 4);
+        const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w}, u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+        for (int e = 0; e < 8; e++) x[e] = __fmul_rn(__fdiv_rn(g[e], __fadd_rn(1.0f, expf(-g[e]))), u[e]);   // SiLU(g)*u
+    } else if (p.mode == RQ_F16) {
+        const uint4 h = *reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(p.a) + n * p.lda + k0);
+        const __half2 *h2 = reinterpret_cast<const __half2 *>(&h);
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const float2 f = __half22float2(h2[e]);
+            x[2 * e] = f.x;
+            x[2 * e + 1] = f.y;
+        }
+    } else {
+        const float4 a0 = *reinterpret_cast<const float4 *>(p.a + n * p.lda + k0), a1 = *reinterpret_cast<const float4 *>(p.a + n * p.lda + k0 + 4);
+        x[0] = a0.x; x[1] = a0.y; x[2] = a0.z; x[3] = a0.w; x[4] = a1.x; x[5] = a1.y; x[6] = a1.z; x[7] = a1.w;
+        if (p.b) {   // residual add: x = a + b
+            const float4 b0 = *reinterpret_cast<const float4 *>(p.b + n * p.ldb + k0), b1 = *reinterpret_cast<const float4 *>(p.b + n * p.ldb + k0 + 4);
+            x[0] = __fadd_rn(x[0], b0.x); x[1] = __fadd_rn(x[1], b0.y); x[2] = __fadd_rn(x[2], b0.z); x[3] = __fadd_rn(x[3], b0.w);
+            x[4] = __fadd_rn(x[4], b1.x); x[5] = __fadd_rn(x[5], b1.y); x[6] = __fadd_rn(x[6], b1.z); x[7] = __fadd_rn(x[7], b1.w);
+        }
+    }
+}
+
+// Grid (column, slice of 8 blocks): every warp owns ONE 256-element block, so a row of 4096 (14336)
+// elements is spread over 2 (7) CTAs instead of one warp walking several blocks in turn. With a
+// normalisation, every CTA of a row first adds up the squares of the whole row in the same order
+// (the row is a few KB and sits in L2), so all of them use the same scale.
 __global__ void __launch_bounds__(RQ_THREADS) k_row_quant_q8k(RowQuantArgs p) {
-    __shared__ float red[RQ_THREADS / 32];
+    __shared__ float red[RQ_WARPS];
     const int n = blockIdx.x;          // activation column (= token)
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t K = p.K;
     const int nblk = (int)(K / 256);
+    const int sb = blockIdx.y * RQ_WARPS + warp;
     char *ob = (char *)p.out;
     if (n >= p.N) {
         // padding columns of the tensor-core blobs are zero
-        if (p.npad > 0) {
-            for (int sb = warp; sb < nblk; sb += RQ_THREADS / 32) {
-                uint8_t *o = (uint8_t *)ob + p.blob_off + (size_t)sb * p.blob_bytes;
-                *reinterpret_cast<uint4 *>(o + (size_t)(n / 8) * 4096 + lane * 128 + (n % 8) * 16) = make_uint4(0, 0, 0, 0);
-                if ((lane & 1) == 0)
-                    *reinterpret_cast<__half *>(o + (size_t)p.npad * 512 + (size_t)(n / 8) * 256 + (lane >> 4) * 128 + (n % 8) * 16 + ((lane >> 1) & 7) * 2) = __float2half_rn(0.f);
-                if (lane == 0) reinterpret_cast<float *>(o + (size_t)p.npad * 544)[n] = 0.f;
-            }
+        if (p.npad > 0 && sb < nblk) {
+            uint8_t *o = (uint8_t *)ob + p.blob_off + (size_t)sb * p.blob_bytes;
+            *reinterpret_cast<uint4 *>(o + (size_t)(n / 8) * 4096 + lane * 128 + (n % 8) * 16) = make_uint4(0, 0, 0, 0);
+            if ((lane & 1) == 0)
+                *reinterpret_cast<__half *>(o + (size_t)p.npad * 512 + (size_t)(n / 8) * 256 + (lane >> 4) * 128 + (n % 8) * 16 + ((lane >> 1) & 7) * 2) = __float2half_rn(0.f);
+            if (lane == 0) reinterpret_cast<float *>(o + (size_t)p.npad * 544)[n] = 0.f;
         }
         return;
     }
-    // ---- produce the f32 row: this lane's 8 consecutive values of every block its warp owns
-    float v[RQ_MAXB][8];
-    float ss = 0.f;
-#pragma unroll
-    for (int b = 0; b < RQ_MAXB; b++) {
-        const int sb = warp + b * (RQ_THREADS / 32);
-        if (sb < nblk) {
-            const int64_t k0 = (int64_t)sb * 256 + lane * 8;
-            float x[8];
-            if (p.mode == RQ_GLU) {
-                const float4 g0 = *reinterpret_cast<const float4 *>(p.a + n * p.lda + k0), g1 = *reinterpret_cast<const float4 *>(p.a + n * p.lda + k0 + 4);
-                const float4 u0 = *reinterpret_cast<const float4 *>(p.b + n * p.ldb + k0), u1 = *reinterpret_cast<const float4 *>(p.b + n * p.ldb + k0 + 4);
-                const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w}, u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
-#pragma unroll
-                for (int e = 0; e < 8; e++) x[e] = __fmul_rn(__fdiv_rn(g[e], __fadd_rn(1.0f, expf(-g[e]))), u[e]);   // SiLU(g)*u
-            } else if (p.mode == RQ_F16) {
-                const uint4 h = *reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(p.a) + n * p.lda + k0);
-                const __half2 *h2 = reinterpret_cast<const __half2 *>(&h);
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const float2 f = __half22float2(h2[e]);
-                    x[2 * e] = f.x;
-                    x[2 * e + 1] = f.y;
-                }
-            } else {
-                const float4 a0 = *reinterpret_cast<const float4 *>(p.a + n * p.lda + k0), a1 = *reinterpret_cast<const float4 *>(p.a + n * p.lda + k0 + 4);
-                x[0] = a0.x; x[1] = a0.y; x[2] = a0.z; x[3] = a0.w; x[4] = a1.x; x[5] = a1.y; x[6] = a1.z; x[7] = a1.w;
-                if (p.b) {   // residual add: x = a + b, written back as the new residual stream
-                    const float4 b0 = *reinterpret_cast<const float4 *>(p.b + n * p.ldb + k0), b1 = *reinterpret_cast<const float4 *>(p.b + n * p.ldb + k0 + 4);
-                    x[0] = __fadd_rn(x[0], b0.x); x[1] = __fadd_rn(x[1], b0.y); x[2] = __fadd_rn(x[2], b0.z); x[3] = __fadd_rn(x[3], b0.w);
-                    x[4] = __fadd_rn(x[4], b1.x); x[5] = __fadd_rn(x[5], b1.y); x[6] = __fadd_rn(x[6], b1.z); x[7] = __fadd_rn(x[7], b1.w);
-                    if (p.sum_out) {
-                        *reinterpret_cast<float4 *>(p.sum_out + n * p.ld_sum + k0) = make_float4(x[0], x[1], x[2], x[3]);
-                        *reinterpret_cast<float4 *>(p.sum_out + n * p.ld_sum + k0 + 4) = make_float4(x[4], x[5], x[6], x[7]);
-                    }
-                }
-            }
-#pragma unroll
-            for (int e = 0; e < 8; e++) {
-                v[b][e] = x[e];
-                ss = __fadd_rn(ss, __fmul_rn(x[e], x[e]));
-            }
-        }
-    }
+    float scale = 1.f;
     if (p.mode == RQ_NORM) {
+        float ss = 0.f;
+        for (int64_t k0 = (int64_t)threadIdx.x * 8; k0 < K; k0 += RQ_THREADS * 8) {
+            float x[8];
+            rq_load8(p, n, k0, x);
+#pragma unroll
+            for (int e = 0; e < 8; e++) ss = __fadd_rn(ss, __fmul_rn(x[e], x[e]));
+        }
 #pragma unroll
         for (int s = 16; s > 0; s >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, s));
         if (lane == 0) red[warp] = ss;
         __syncthreads();
         float tot = 0.f;
 #pragma unroll
-        for (int i = 0; i < RQ_THREADS / 32; i++) tot = __fadd_rn(tot, red[i]);
-        const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)K), p.eps)));
+        for (int i = 0; i < RQ_WARPS; i++) tot = __fadd_rn(tot, red[i]);
+        scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)K), p.eps)));
+    }
+    if (sb >= nblk) return;
+    // ---- this warp's block: lane holds 8 consecutive values
+    const int64_t k0 = (int64_t)sb * 256 + lane * 8;
+    float v[8];
+    rq_load8(p, n, k0, v);
+    if (p.mode != RQ_GLU && p.mode != RQ_F16 && p.b && p.sum_out) {   // the sum is the new residual stream
+        *reinterpret_cast<float4 *>(p.sum_out + n * p.ld_sum + k0) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4 *>(p.sum_out + n * p.ld_sum + k0 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+    if (p.mode == RQ_NORM) {
 #pragma unroll
-        for (int b = 0; b < RQ_MAXB; b++) {
-            const int sb = warp + b * (RQ_THREADS / 32);
-            if (sb < nblk) {
-                const int64_t k0 = (int64_t)sb * 256 + lane * 8;
-#pragma unroll
-                for (int e = 0; e < 8; e++) {
-                    const int wi = p.wn == K ? (int)(k0 + e) : (int)((uint32_t)(k0 + e) % (uint32_t)p.wn);
-                    v[b][e] = __fmul_rn(__fmul_rn(v[b][e], scale), p.w[wi]);
-                }
-            }
+        for (int e = 0; e < 8; e++) {
+            const int wi = p.wn == K ? (int)(k0 + e) : (int)((uint32_t)(k0 + e) % (uint32_t)p.wn);
+            v[e] = __fmul_rn(__fmul_rn(v[e], scale), p.w[wi]);
         }
     }
-    // ---- optional f32 copy of the row, then Q8_K per 256-element block
+    // ---- optional f32 copy of the row, then Q8_K of the block
     int8_t *qs = (int8_t *)(ob + p.qs_off);
     float *ds = (float *)(ob + p.d_off);
     int16_t *bsums = (int16_t *)(ob + p.bsum_off);
+    if (p.y_out) {
+        *reinterpret_cast<float4 *>(p.y_out + n * p.ld_y + k0) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4 *>(p.y_out + n * p.ld_y + k0 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+    float amax = 0.f, mx = 0.f;
+    int idx = 512;
 #pragma unroll
-    for (int b = 0; b < RQ_MAXB; b++) {
-        const int sb = warp + b * (RQ_THREADS / 32);
-        if (sb >= nblk) continue;
-        const int64_t k0 = (int64_t)sb * 256 + lane * 8;
-        if (p.y_out) {
-            *reinterpret_cast<float4 *>(p.y_out + n * p.ld_y + k0) = make_float4(v[b][0], v[b][1], v[b][2], v[b][3]);
-            *reinterpret_cast<float4 *>(p.y_out + n * p.ld_y + k0 + 4) = make_float4(v[b][4], v[b][5], v[b][6], v[b][7]);
-        }
-        float amax = 0.f, mx = 0.f;
-        int idx = 512;
+    for (int e = 0; e < 8; e++)
+        if (fabsf(v[e]) > amax) { amax = fabsf(v[e]); mx = v[e]; idx = lane * 8 + e; }
 #pragma unroll
-        for (int e = 0; e < 8; e++)
-            if (fabsf(v[b][e]) > amax) { amax = fabsf(v[b][e]); mx = v[b][e]; idx = lane * 8 + e; }
+    for (int s = 1; s < 32; s <<= 1) {
+        const float oa = __shfl_xor_sync(0xffffffffu, amax, s), om = __shfl_xor_sync(0xffffffffu, mx, s);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, s);
+        if (oa > amax || (oa == amax && oi < idx)) { amax = oa; mx = om; idx = oi; }
+    }
+    int q[8];
+    float d = 0.f;
+    if (amax == 0.f) {
 #pragma unroll
-        for (int s = 1; s < 32; s <<= 1) {
-            const float oa = __shfl_xor_sync(0xffffffffu, amax, s), om = __shfl_xor_sync(0xffffffffu, mx, s);
-            const int oi = __shfl_xor_sync(0xffffffffu, idx, s);
-            if (oa > amax || (oa == amax && oi < idx)) { amax = oa; mx = om; idx = oi; }
-        }
-        int q[8];
-        float d = 0.f;
-        if (amax == 0.f) {
+        for (int e = 0; e < 8; e++) q[e] = 0;
+    } else {
+        const float iscale = __fdiv_rn(-127.f, mx);
 #pragma unroll
-            for (int e = 0; e < 8; e++) q[e] = 0;
-        } else {
-            const float iscale = __fdiv_rn(-127.f, mx);
+        for (int e = 0; e < 8; e++) q[e] = min(127, nearest_int_f(__fmul_rn(iscale, v[e])));
+        d = __fdiv_rn(1.f, iscale);
+    }
+    int s8 = 0;
 #pragma unroll
-            for (int e = 0; e < 8; e++) q[e] = min(127, nearest_int_f(__fmul_rn(iscale, v[b][e])));
-            d = __fdiv_rn(1.f, iscale);
-        }
-        int s8 = 0;
-#pragma unroll
-        for (int e = 0; e < 8; e++) s8 += q[e];
-        const int s16 = s8 + __shfl_xor_sync(0xffffffffu, s8, 1);
-        uint2 packed;
-        packed.x = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[1] & 0xff) << 8) | ((uint32_t)(q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
-        packed.y = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
-        *reinterpret_cast<uint2 *>(qs + (size_t)n * K + k0) = packed;
-        if ((lane & 1) == 0) bsums[(size_t)n * (K / 16) + sb * 16 + (lane >> 1)] = (int16_t)s16;
-        if (lane == 0) ds[(size_t)n * (K / 256) + sb] = d;
-        if (p.npad > 0) {
-            // tensor-core operand: this lane's 8 codes are K chunk `lane` of column n, in the order
-            // (0, 2, 1, 3, 4, 6, 5, 7) in which the weight nibbles come out of a 32-bit word
-            uint8_t *o = (uint8_t *)ob + p.blob_off + (size_t)sb * p.blob_bytes;
-            __half2 h[4];
-            h[0] = __floats2half2_rn((float)q[0], (float)q[2]);
-            h[1] = __floats2half2_rn((float)q[1], (float)q[3]);
-            h[2] = __floats2half2_rn((float)q[4], (float)q[6]);
-            h[3] = __floats2half2_rn((float)q[5], (float)q[7]);
-            *reinterpret_cast<uint4 *>(o + (size_t)(n / 8) * 4096 + lane * 128 + (n % 8) * 16) = *reinterpret_cast<const uint4 *>(h);
-            if ((lane & 1) == 0)
-                *reinterpret_cast<__half *>(o + (size_t)p.npad * 512 + (size_t)(n / 8) * 256 + (lane >> 4) * 128 + (n % 8) * 16 + ((lane >> 1) & 7) * 2) = __float2half_rn((float)s16);
-            if (lane == 0) reinterpret_cast<float *>(o + (size_t)p.npad * 544)[n] = d;
-        }
+    for (int e = 0; e < 8; e++) s8 += q[e];
+    const int s16 = s8 + __shfl_xor_sync(0xffffffffu, s8, 1);
+    uint2 packed;
+    packed.x = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[1] & 0xff) << 8) | ((uint32_t)(q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
+    packed.y = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
+    *reinterpret_cast<uint2 *>(qs + (size_t)n * K + k0) = packed;
+    if ((lane & 1) == 0) bsums[(size_t)n * (K / 16) + sb * 16 + (lane >> 1)] = (int16_t)s16;
+    if (lane == 0) ds[(size_t)n * (K / 256) + sb] = d;
+    if (p.npad > 0) {
+        // tensor-core operand: this lane's 8 codes are K chunk `lane` of column n, in the order
+        // (0, 2, 1, 3, 4, 6, 5, 7) in which the weight nibbles come out of a 32-bit word
+        uint8_t *o = (uint8_t *)ob + p.blob_off + (size_t)sb * p.blob_bytes;
+        __half2 h[4];
+        h[0] = __floats2half2_rn((float)q[0], (float)q[2]);
+        h[1] = __floats2half2_rn((float)q[1], (float)q[3]);
+        h[2] = __floats2half2_rn((float)q[4], (float)q[6]);
+        h[3] = __floats2half2_rn((float)q[5], (float)q[7]);
+        *reinterpret_cast<uint4 *>(o + (size_t)(n / 8) * 4096 + lane * 128 + (n % 8) * 16) = *reinterpret_cast<const uint4 *>(h);
+        if ((lane & 1) == 0)
+            *reinterpret_cast<__half *>(o + (size_t)p.npad * 512 + (size_t)(n / 8) * 256 + (lane >> 4) * 128 + (n % 8) * 16 + ((lane >> 1) & 7) * 2) = __float2half_rn((float)s16);
+        if (lane == 0) reinterpret_cast<float *>(o + (size_t)p.npad * 544)[n] = d;
     }
 }
 
-bool row_quant_supported(int64_t K) { return K % 256 == 0 && K / 256 <= RQ_MAXB * (RQ_THREADS / 32); }
+bool row_quant_supported(int64_t K) { return K % 256 == 0 && K / 256 <= 65535 * RQ_WARPS; }
 
 cudaError_t launch_row_quant(const RowQuantArgs &p, cudaStream_t st) {
     if (p.N == 0 || p.K == 0) return cudaSuccess;
     const int rows = p.npad > 0 ? p.npad : (int)p.N;
-    k_row_quant_q8k<<<rows, RQ_THREADS, 0, st>>>(p);
+    const int nblk = (int)(p.K / 256);
+    k_row_quant_q8k<<<dim3(rows, (nblk + RQ_WARPS - 1) / RQ_WARPS), RQ_THREADS, 0, st>>>(p);
     return cudaGetLastError();
 }
 
