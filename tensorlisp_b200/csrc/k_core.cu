@@ -287,6 +287,24 @@ cudaError_t launch_norm(const NormArgs &p, const void *a, const void *w, void *d
 // ---------------------------------------------------------------- ROPE (normal and neox pairs, YaRN ramp)
 // theta is built the way the CPU backend builds its cache (ops.cpp:5846-5860): multiplied up
 // sequentially in f32, not powf, so long positions agree.
+// cos/sin of pair `pr` at position `posf` (rope_yarn, ops.cpp:5806-5830)
+__device__ __forceinline__ void rope_cs(const RopeArgs &p, int64_t pr, float posf, const float *ff, float &cs, float &sn) {
+    float theta = posf;
+    for (int64_t k = 0; k < pr; k++) theta *= p.theta_scale;
+    const float fq = p.has_ff ? ff[pr] : 1.0f;
+    const float theta_extrap = theta / fq;
+    const float theta_interp = p.freq_scale * theta_extrap;
+    float th = theta_interp, mscale = p.attn_factor;
+    if (p.ext_factor != 0.0f) {
+        const float yv = ((float)pr - p.corr0) / fmaxf(0.001f, p.corr1 - p.corr0);
+        const float ramp_mix = (1.f - fminf(1.f, fmaxf(0.f, yv))) * p.ext_factor;
+        th = theta_interp * (1.f - ramp_mix) + theta_extrap * ramp_mix;
+        mscale *= 1.0f + 0.1f * logf(1.0f / p.freq_scale);
+    }
+    cs = cosf(th) * mscale;
+    sn = sinf(th) * mscale;
+}
+
 __global__ void k_rope(RopeArgs p, const uint8_t *a, const int32_t *pos, const float *ff, uint8_t *d, int64_t npairs) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= npairs) return;
@@ -304,24 +322,65 @@ __global__ void k_rope(RopeArgs p, const uint8_t *a, const int32_t *pos, const f
         st_elem(dst + (i0 + 1) * p.d.nb[0], p.dty, ld_elem(src + (i0 + 1) * p.a.nb[0], p.aty));
         return;
     }
-    float theta = (float)pos[i2];
-    for (int64_t k = 0; k < pr; k++) theta *= p.theta_scale;
-    const float fq = p.has_ff ? ff[pr] : 1.0f;
-    const float theta_extrap = theta / fq;
-    const float theta_interp = p.freq_scale * theta_extrap;
-    float th = theta_interp, mscale = p.attn_factor;
-    if (p.ext_factor != 0.0f) {
-        const float yv = ((float)(i0 / 2) - p.corr0) / fmaxf(0.001f, p.corr1 - p.corr0);
-        const float ramp_mix = (1.f - fminf(1.f, fmaxf(0.f, yv))) * p.ext_factor;
-        th = theta_interp * (1.f - ramp_mix) + theta_extrap * ramp_mix;
-        mscale *= 1.0f + 0.1f * logf(1.0f / p.freq_scale);
-    }
-    const float cs = cosf(th) * mscale, sn = sinf(th) * mscale;
+    float cs, sn;
+    rope_cs(p, pr, (float)pos[i2], ff, cs, sn);
     const int64_t ic = p.mode == 0 ? i0 : pr;
     const int64_t off = p.mode == 0 ? 1 : p.n_dims / 2;
     const float x0 = ld_elem(src + ic * p.a.nb[0], p.aty), x1 = ld_elem(src + (ic + off) * p.a.nb[0], p.aty);
     st_elem(dst + ic * p.d.nb[0], p.dty, x0 * cs - x1 * sn);
     st_elem(dst + (ic + off) * p.d.nb[0], p.dty, x0 * sn + x1 * cs);
+}
+
+// One launch for the attention inputs of a decode step: rope(q) -> f16 query, rope(k) -> f16 into
+// the key pool at the token's slot, v -> f16 into the value pool. Same arithmetic as k_rope followed
+// by the f32 -> f16 casts and the cache write; a negative slot skips the token's key and value.
+__global__ void k_rope_kv(RopeKvArgs p, const uint8_t *q, const uint8_t *k, const uint8_t *v, const int32_t *pos,
+                          const float *ff, __half *q16, __half *kpool, __half *vpool, const int64_t *slots) {
+    const int tok = blockIdx.x, hsl = blockIdx.y, pr = threadIdx.x;
+    const int hs = p.hs;
+    if (hsl < p.heads + p.kv_heads) {
+        const bool is_q = hsl < p.heads;
+        const int h = is_q ? hsl : hsl - p.heads;
+        const uint8_t *src;
+        __half *dst;
+        if (is_q) {
+            src = q + h * p.rope.a.nb[1] + tok * p.rope.a.nb[2];
+            dst = q16 + ((size_t)tok * p.heads + h) * hs;
+        } else {
+            const int64_t slot = slots[tok];
+            if (slot < 0) return;
+            src = k + h * p.k.nb[1] + tok * p.k.nb[2];
+            dst = kpool + (((size_t)(slot / p.block_size) * p.kv_heads + h) * p.block_size + slot % p.block_size) * hs;
+        }
+        const float *x = reinterpret_cast<const float *>(src);
+        const int i0 = 2 * pr;
+        if (i0 >= p.rope.n_dims) {
+            dst[i0] = __float2half_rn(x[i0]);
+            dst[i0 + 1] = __float2half_rn(x[i0 + 1]);
+            return;
+        }
+        float cs, sn;
+        rope_cs(p.rope, pr, (float)pos[tok], ff, cs, sn);
+        const int ic = p.rope.mode == 0 ? i0 : pr;
+        const int off = p.rope.mode == 0 ? 1 : p.rope.n_dims / 2;
+        const float x0 = x[ic], x1 = x[ic + off];
+        dst[ic] = __float2half_rn(x0 * cs - x1 * sn);
+        dst[ic + off] = __float2half_rn(x0 * sn + x1 * cs);
+    } else {
+        const int64_t slot = slots[tok];
+        if (slot < 0) return;
+        const int h = hsl - p.heads - p.kv_heads;
+        const float2 x = *reinterpret_cast<const float2 *>(v + h * p.v.nb[1] + tok * p.v.nb[2] + pr * 8);
+        __half *dst = vpool + (((size_t)(slot / p.block_size) * p.kv_heads + h) * p.block_size + slot % p.block_size) * hs;
+        *reinterpret_cast<__half2 *>(dst + 2 * pr) = __floats2half2_rn(x.x, x.y);
+    }
+}
+cudaError_t launch_rope_kv(const RopeKvArgs &p, const void *q, const void *k, const void *v, const int32_t *pos, const float *ff,
+                           void *q16, void *kpool, void *vpool, const int64_t *slots, cudaStream_t st) {
+    if (p.tokens == 0) return cudaSuccess;
+    k_rope_kv<<<dim3((unsigned)p.tokens, (unsigned)(p.heads + 2 * p.kv_heads)), p.hs / 2, 0, st>>>(
+        p, (const uint8_t *)q, (const uint8_t *)k, (const uint8_t *)v, pos, ff, (__half *)q16, (__half *)kpool, (__half *)vpool, slots);
+    return cudaGetLastError();
 }
 cudaError_t launch_rope(const RopeArgs &p, const void *a, const int32_t *pos, const float *ff, void *d, cudaStream_t st) {
     const int64_t n = p.a.ne[0] / 2 * p.a.ne[1] * p.a.ne[2] * p.a.ne[3];

@@ -103,6 +103,14 @@ struct RopeArgs {
     int has_ff;
 };
 cudaError_t launch_rope(const RopeArgs &p, const void *a, const int32_t *pos, const float *ff, void *d, cudaStream_t st);
+// rope(q) -> f16, rope(k) -> key pool, v -> value pool in one launch (k and v as [hs, kv_heads, tokens] f32 views)
+struct RopeKvArgs {
+    RopeArgs rope;   // a = the f32 query view [hs, heads, tokens]
+    TView k, v;
+    int heads, kv_heads, hs, block_size, tokens;
+};
+cudaError_t launch_rope_kv(const RopeKvArgs &p, const void *q, const void *k, const void *v, const int32_t *pos, const float *ff,
+                           void *q16, void *kpool, void *vpool, const int64_t *slots, cudaStream_t st);
 struct SoftmaxArgs { TView a, m, d; float scale, max_bias, m0, m1; int n_head_log2; int has_mask; uint32_t mty; };
 cudaError_t launch_soft_max(const SoftmaxArgs &p, const void *a, const void *m, void *d, cudaStream_t st);
 struct RowsArgs { TView a, ids, d; uint32_t aty, idty, dty; };

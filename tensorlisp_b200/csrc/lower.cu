@@ -153,35 +153,40 @@ void lower_norm(L &l, bool fused_mul) {
     l.push([=](const RunCtx &r) { return launch_norm(p, r.at(pa), fused_mul ? r.at(pw) : nullptr, r.at(pd), r.stream); });
 }
 
-void lower_rope(L &l) {
-    const Tensor &t = l.t();
-    const int32_t a = l.src(0), pos = l.src(1);
-    const int32_t ff = t.src[2];
-    const int mode = t.op_params[2];
-    if (mode != 0 && mode != 2) unsupported(t, "only normal and neox rope (mrope/vision are not supported)");
-    if (l.T(pos).ty != TLB_TYPE_I32 || l.T(pos).ne[0] != l.T(a).ne[2]) unsupported(t, "needs one i32 position per token");
-    if (ff >= 0 && (l.T(ff).ty != TLB_TYPE_F32 || l.T(ff).nb[0] != 4)) unsupported(t, "frequency factors must be f32");
-    const uint32_t aty = l.T(a).ty, dty = t.ty;
-    if (!(aty == 0 || aty == 1) || !(dty == 0 || dty == 1)) unsupported(t, "rope takes f32 or f16");
-    RopeArgs p;
-    p.a = view_of(l.T(a));
-    p.d = view_of(t);
-    p.aty = aty;
-    p.dty = dty;
+// rope parameters of a ROPE node (or of a node that carries a copy of them)
+RopeArgs rope_params(const Tensor &t, int64_t row_len) {
+    RopeArgs p{};
     p.n_dims = t.op_params[1];
-    p.mode = mode;
+    p.mode = t.op_params[2];
+    if (p.mode != 0 && p.mode != 2) unsupported(t, "only normal and neox rope (mrope/vision are not supported)");
     const float freq_base = t.param_f32(5);
     p.freq_scale = t.param_f32(6);
     p.ext_factor = t.param_f32(7);
     p.attn_factor = t.param_f32(8);
     const float beta_fast = t.param_f32(9), beta_slow = t.param_f32(10);
     const float n_ctx_orig = (float)t.op_params[4];
-    if (p.n_dims <= 0 || p.n_dims > t.ne[0] || p.n_dims % 2) unsupported(t, "bad n_dims");
+    if (p.n_dims <= 0 || p.n_dims > row_len || p.n_dims % 2) unsupported(t, "bad n_dims");
     p.theta_scale = powf(freq_base, -2.0f / (float)p.n_dims);
     // ggml_rope_yarn_corr_dims (ggml.c:4369-4381)
     auto corr = [&](float beta) { return (float)p.n_dims * logf(n_ctx_orig / (beta * 2.0f * (float)M_PI)) / (2.0f * logf(freq_base)); };
     p.corr0 = fmaxf(0.f, floorf(corr(beta_fast)));
     p.corr1 = fminf((float)p.n_dims - 1.f, ceilf(corr(beta_slow)));
+    return p;
+}
+
+void lower_rope(L &l) {
+    const Tensor &t = l.t();
+    const int32_t a = l.src(0), pos = l.src(1);
+    const int32_t ff = t.src[2];
+    if (l.T(pos).ty != TLB_TYPE_I32 || l.T(pos).ne[0] != l.T(a).ne[2]) unsupported(t, "needs one i32 position per token");
+    if (ff >= 0 && (l.T(ff).ty != TLB_TYPE_F32 || l.T(ff).nb[0] != 4)) unsupported(t, "frequency factors must be f32");
+    const uint32_t aty = l.T(a).ty, dty = t.ty;
+    if (!(aty == 0 || aty == 1) || !(dty == 0 || dty == 1)) unsupported(t, "rope takes f32 or f16");
+    RopeArgs p = rope_params(t, t.ne[0]);
+    p.a = view_of(l.T(a));
+    p.d = view_of(t);
+    p.aty = aty;
+    p.dty = dty;
     p.has_ff = ff >= 0;
     const Place pa = l.place(a), pp = l.place(pos), pd = l.place(l.id);
     Place pf;
@@ -189,6 +194,39 @@ void lower_rope(L &l) {
     const bool hf = ff >= 0;
     l.push([=](const RunCtx &r) {
         return launch_rope(p, r.at(pa), (const int32_t *)r.at(pp), hf ? (const float *)r.at(pf) : nullptr, r.at(pd), r.stream);
+    });
+}
+
+// ROPE_KV_WRITE (pseudo-op made by fuse_rope_cache): src = q, k, v (f32), pos, freq factors or -1,
+// key pool, value pool, slots, and the f16 query it produces. op_params: the rope's, with the
+// kv-head count and block size in [12], [13].
+void lower_rope_kv(L &l) {
+    const Tensor &t = l.t();
+    const int32_t q = l.src(0), k = l.src(1), v = l.src(2), pos = l.src(3), kc = l.src(5), vc = l.src(6), slots = l.src(7), q16 = l.src(8);
+    const int32_t ff = t.src[4];
+    const Tensor &tq = l.T(q), &tk = l.T(k), &tv = l.T(v);
+    RopeKvArgs p{};
+    p.rope = rope_params(t, tq.ne[0]);
+    p.rope.a = view_of(tq);
+    p.rope.has_ff = ff >= 0;
+    p.k = view_of(tk);
+    p.hs = (int)tq.ne[0];
+    p.heads = (int)tq.ne[1];
+    p.tokens = (int)tq.ne[2];
+    p.kv_heads = t.op_params[12];
+    p.block_size = t.op_params[13];
+    // v arrives as [hs * kv_heads, tokens]
+    p.v = view_of(tv);
+    p.v.nb[2] = (int64_t)tv.nb[1];
+    p.v.nb[1] = (int64_t)p.hs * 4;
+    const Place pq = l.place(q), pk = l.place(k), pv = l.place(v), pp = l.place(pos), pkc = l.place(kc), pvc = l.place(vc),
+                psl = l.place(slots), pq16 = l.place(q16);
+    Place pf;
+    if (ff >= 0) pf = l.place(ff);
+    const bool hf = ff >= 0;
+    l.push([=](const RunCtx &r) {
+        return launch_rope_kv(p, r.at(pq), r.at(pk), r.at(pv), (const int32_t *)r.at(pp), hf ? (const float *)r.at(pf) : nullptr,
+                              r.at(pq16), r.at(pkc), r.at(pvc), (const int64_t *)r.at(psl), r.stream);
     });
 }
 
@@ -553,6 +591,7 @@ void lower_node(const LowerCtx &c, int32_t id, int pos, std::vector<Dispatch> &o
     if (op == "NORM" || op == "RMS_NORM") return lower_norm(l, false);
     if (op == "RMS_NORM_MUL") return lower_norm(l, true);
     if (op == "ROPE") return lower_rope(l);
+    if (op == "ROPE_KV_WRITE") return lower_rope_kv(l);
     if (op == "SOFT_MAX") return lower_soft_max(l);
     if (op == "GET_ROWS") return lower_get_rows(l);
     if (op == "SET_ROWS") return lower_set_rows(l);
@@ -567,6 +606,7 @@ void lower_node(const LowerCtx &c, int32_t id, int pos, std::vector<Dispatch> &o
 
 // ---------------------------------------------------------------------------- IR rewrites
 void fuse_row_producers(Graph &g);
+void fuse_rope_cache(Graph &g);
 // Readers of every root (views of a tensor count for the root), as fuse.rs:56-63 requires.
 void rewrite_graph(Graph &g) {
     const size_t nt0 = g.tensors.size();
@@ -711,6 +751,7 @@ void rewrite_graph(Graph &g) {
     }
     g.nodes.swap(nodes);
     if (enabled("ROW_QUANT")) fuse_row_producers(g);
+    if (enabled("ROPE_KV_WRITE")) fuse_rope_cache(g);
 }
 
 // Fold the producer of a quantized activation into its QUANT_ACT node (k_fused.cu): RMS_NORM_MUL
@@ -759,7 +800,8 @@ void fuse_row_producers(Graph &g) {
         // every reader of the producer's storage must be this QUANT_ACT (views of it launch nothing)
         readers(xroot, rd);
         bool only_q = true;
-        for (int r : rd) only_q = only_q && (r == (int)qi || g.tensors[g.nodes[r]].is_view_op());
+        // (a cast lists itself as src[1], ggml.c:3549-3563, so the producer shows up as its own reader)
+        for (int r : rd) only_q = only_q && (r == (int)qi || r == xp || g.tensors[g.nodes[r]].is_view_op());
         if (!only_q) continue;
         Tensor &Q = g.tensors[qid];
         if (P.op == "RMS_NORM_MUL" && xroot == x) {
@@ -809,6 +851,102 @@ void fuse_row_producers(Graph &g) {
             Q.src[5] = x;   // keeps the shape of the activation matrix (a view of the folded cast)
             dead[xp] = 1;
         }
+    }
+    std::vector<int32_t> out;
+    for (size_t i = 0; i < nn; i++)
+        if (!dead[i]) out.push_back(g.nodes[i]);
+    g.nodes.swap(out);
+}
+
+
+// rope(q) -> cast, rope(k) -> cast, v -> cast, cache write: one ROPE_KV_WRITE node in place of the
+// cache write (decode-step shape of scheme/core.ss:222-271 callers). Legality as for the other
+// fusions: every folded intermediate has exactly one reader, is not kept, and is a plain f32/f16
+// tensor of the expected shape; both ropes share position tensor and parameters.
+void fuse_rope_cache(Graph &g) {
+    const size_t nn = g.nodes.size();
+    std::vector<int> pos_of(g.tensors.size(), -1);
+    for (size_t i = 0; i < nn; i++) pos_of[g.nodes[i]] = (int)i;
+    std::vector<char> kept(g.tensors.size(), 0);
+    for (int32_t k : g.keep) kept[g.root(k)] = 1;
+    // readers of a root by node position; a cast lists itself as src[1] and is not its own reader
+    auto n_readers = [&](int32_t root, int self_pos) {
+        int n = 0;
+        for (size_t i = 0; i < nn; i++) {
+            if ((int)i == self_pos) continue;
+            const Tensor &t = g.tensors[g.nodes[i]];
+            if (t.is_view_op()) continue;
+            for (int s = 0; s < 10; s++)
+                if (t.src[s] >= 0 && g.root(t.src[s]) == root) { n++; break; }
+        }
+        return n;
+    };
+    // a cast to f16 of (a view of) `want_op`'s result, read once: returns the producing node or -1
+    auto cast_of = [&](int32_t c16, const char *want_op) -> int32_t {
+        if (c16 < 0 || g.root(c16) != c16) return -1;
+        const Tensor &C = g.tensors[c16];
+        if (C.op != "CPY" || C.ty != TLB_TYPE_F16 || !C.is_contiguous() || C.src[0] < 0 || kept[c16] || pos_of[c16] < 0) return -1;
+        const int32_t src = g.root(C.src[0]);
+        const Tensor &S = g.tensors[src];
+        if (S.ty != TLB_TYPE_F32 || kept[src]) return -1;
+        if (want_op && (S.op != want_op || pos_of[src] < 0)) return -1;
+        if (!g.tensors[C.src[0]].is_contiguous()) return -1;
+        return src;
+    };
+    std::vector<char> dead(nn, 0);
+    for (size_t ci = 0; ci < nn; ci++) {
+        const int32_t cid = g.nodes[ci];
+        Tensor &Cw = g.tensors[cid];
+        if (Cw.op != "CUSTOM" || paged_ud(Cw).kind != 2) continue;
+        const PagedUd u = paged_ud(Cw);
+        const int32_t k16 = Cw.src[0], v16 = Cw.src[1];
+        const int32_t rk = cast_of(k16, "ROPE");
+        const int32_t vsrc = cast_of(v16, nullptr);
+        if (rk < 0 || vsrc < 0) continue;
+        // the attention node that reads the same pools, and its query
+        int ai = -1;
+        for (size_t i = ci + 1; i < nn && ai < 0; i++) {
+            const Tensor &A = g.tensors[g.nodes[i]];
+            if (A.op == "CUSTOM" && paged_ud(A).kind == 1 && A.src[1] == Cw.src[2] && A.src[2] == Cw.src[3]) ai = (int)i;
+        }
+        if (ai < 0) continue;
+        const int32_t q16 = g.tensors[g.nodes[ai]].src[0];
+        const int32_t rq = cast_of(q16, "ROPE");
+        if (rq < 0) continue;
+        const Tensor RQ = g.tensors[rq], RK = g.tensors[rk];
+        bool ok = RQ.src[1] == RK.src[1] && RQ.src[2] == RK.src[2] && RQ.src[0] >= 0 && RK.src[0] >= 0;
+        for (int i = 0; ok && i < 16; i++) ok = RQ.op_params[i] == RK.op_params[i];
+        if (!ok) continue;
+        const Tensor &QI = g.tensors[RQ.src[0]], &KI = g.tensors[RK.src[0]], &VI = g.tensors[g.tensors[v16].src[0]];
+        const int64_t hs = QI.ne[0], tokens = QI.ne[2];
+        ok = QI.ty == 0 && KI.ty == 0 && VI.ty == 0 && QI.nb[0] == 4 && KI.nb[0] == 4 && VI.nb[0] == 4 && QI.ne[3] == 1 && KI.ne[3] == 1 &&
+             KI.ne[0] == hs && KI.ne[1] == u.kv_heads && KI.ne[2] == tokens && VI.ne[0] == hs * u.kv_heads && VI.nrows() == tokens &&
+             hs % 2 == 0 && hs <= 2048 && QI.nb[1] % 8 == 0 && VI.nb[1] % 8 == 0 && g.tensors[RQ.src[1]].ty == TLB_TYPE_I32 &&
+             g.tensors[RQ.src[1]].ne[0] == tokens && g.tensors[q16].ne[0] == hs && g.tensors[k16].nelements() == hs * u.kv_heads * tokens &&
+             (RQ.src[2] < 0 || (g.tensors[RQ.src[2]].ty == 0 && g.tensors[RQ.src[2]].nb[0] == 4));
+        // one reader each: rope results by their casts, casts by the cache write / the attention
+        ok = ok && n_readers(rq, pos_of[rq]) == 1 && n_readers(rk, pos_of[rk]) == 1 && n_readers(k16, pos_of[k16]) == 1 &&
+             n_readers(v16, pos_of[v16]) == 1 && n_readers(q16, pos_of[q16]) == 1;
+        // the folded nodes all sit before the attention; the fused node takes the cache write's place
+        ok = ok && pos_of[rq] < (int)ci && pos_of[rk] < (int)ci && pos_of[k16] < (int)ci && pos_of[v16] < (int)ci && pos_of[q16] < ai;
+        if (!ok) continue;
+        const int32_t pools[2] = {Cw.src[2], Cw.src[3]};
+        const int32_t slots = Cw.src[4];
+        Cw.op = "ROPE_KV_WRITE";
+        for (int i = 0; i < 16; i++) Cw.op_params[i] = RQ.op_params[i];
+        Cw.op_params[12] = u.kv_heads;
+        Cw.op_params[13] = u.block_size;
+        for (int i = 0; i < 10; i++) Cw.src[i] = -1;
+        Cw.src[0] = RQ.src[0];
+        Cw.src[1] = RK.src[0];
+        Cw.src[2] = g.tensors[v16].src[0];
+        Cw.src[3] = RQ.src[1];
+        Cw.src[4] = RQ.src[2];
+        Cw.src[5] = pools[0];
+        Cw.src[6] = pools[1];
+        Cw.src[7] = slots;
+        Cw.src[8] = q16;   // written by this node
+        dead[pos_of[rq]] = dead[pos_of[rk]] = dead[pos_of[k16]] = dead[pos_of[v16]] = dead[pos_of[q16]] = 1;
     }
     std::vector<int32_t> out;
     for (size_t i = 0; i < nn; i++)
