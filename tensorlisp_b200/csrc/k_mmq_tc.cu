@@ -40,10 +40,12 @@ __device__ unsigned long long g_tc_dbg[256];
 namespace tc {
 
 constexpr int ROWS = 128;          // rows per CTA tile (UMMA M)
-constexpr int THREADS = 448;          // TMA warp + 4 epilogue warps + 8 expanding warps + MMA warp
+constexpr int THREADS = 832;          // TMA warp + 8 epilogue warps + 16 expanding warps + MMA warp
+constexpr int EPI_WARP0 = 1, DEQ_WARP0 = 9, MMA_WARP = 25;
 constexpr int RAW_BYTES = ROWS * 144;
-constexpr int A_Q_BYTES = ROWS * 64 * 2;      // one quarter super-block: 128 rows x 64 k of f16
-constexpr int A_HALF_BYTES = 2 * A_Q_BYTES;
+constexpr uint32_t TMEM_COLS = 512;           // all of it: accumulators in [0, 256), the A ring in [256, 512)
+constexpr uint32_t A_COL0 = 256;              // ring of 8 quarter super-blocks, 32 columns (64 f16 per row) each
+constexpr int A_RING = 8;
 constexpr int AMIN_BYTES = ROWS * 16 * 2;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
@@ -62,6 +64,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
 // kernel runs to its end (with a wrong result and the error word set) instead of hanging.
 __device__ __forceinline__ bool mbar_try(uint32_t a, uint32_t parity) {
     uint32_t ok;
+    // No suspend-time hint, and every lane probes for itself: a parked thread wakes up late, and one
+    // probing lane followed by a warp barrier measured 28% slower; every wait here is on the critical path.
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
@@ -110,6 +114,32 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint6
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// A operand in tensor memory: lane = row, each 32-bit column holds two consecutive K elements
+__device__ __forceinline__ void umma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 lanes x 8 consecutive 32-bit columns from registers: thread t of the warp writes lane (warp%4)*32 + t
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]),
+                 "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// true in exactly one lane of a converged warp
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(su32(bar)) : "memory");
 }
@@ -122,6 +152,14 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
                  : "r"(taddr));
 #pragma unroll
     for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
+    uint32_t r[8];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = __uint_as_float(r[i]);
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
@@ -196,16 +234,14 @@ template <int NPAD, int RAW_STAGES, int ACT_STAGES>
 __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_constant__ CUtensorMap wmap, TcParams p) {
     using namespace tc;
     constexpr int BLOB = (NPAD * 548 + 127) / 128 * 128;
-    constexpr uint32_t TMEM_COLS = NPAD * 4 <= 32 ? 32 : (NPAD * 4 <= 64 ? 64 : (NPAD * 4 <= 128 ? 128 : (NPAD * 4 <= 256 ? 256 : 512)));
     constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(NPAD >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);  // f16 x f16 -> f32, K-major A and B
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = smem_raw + ((1024u - (tc::su32(smem_raw) & 1023u)) & 1023u);   // 1 KB of slack is allocated for this
     uint8_t *raw = smem;                                   // RAW_STAGES x RAW_BYTES
     uint8_t *actb = raw + RAW_STAGES * RAW_BYTES;          // ACT_STAGES x BLOB
-    uint8_t *abuf = actb + ACT_STAGES * BLOB;              // 2 x A_HALF_BYTES
-    uint8_t *amin = abuf + 2 * A_HALF_BYTES;               // 2 x AMIN_BYTES (by super-block parity)
+    uint8_t *amin = actb + ACT_STAGES * BLOB;              // 2 x AMIN_BYTES (by super-block parity)
     float2 *dd = reinterpret_cast<float2 *>(amin + 2 * AMIN_BYTES);  // [2][ROWS] (d, dmin) by super-block parity
-    __shared__ uint64_t bar_raw[RAW_STAGES], bar_act[ACT_STAGES], bar_afree[4], bar_mma[2], bar_epi[2], bar_aready[4], bar_rawfree[RAW_STAGES], bar_actfree[ACT_STAGES];
+    __shared__ uint64_t bar_raw[RAW_STAGES], bar_act[ACT_STAGES], bar_afree[A_RING], bar_mma[2], bar_epi[2], bar_aready[A_RING], bar_rawfree[RAW_STAGES], bar_actfree[ACT_STAGES];
     __shared__ uint32_t tmem_base_s;
     __shared__ int s_fail;
     volatile int *fail = &s_fail;
@@ -218,19 +254,19 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
     if (tid == 0) {
         for (int i = 0; i < RAW_STAGES; i++) {
             mbar_init(&bar_raw[i], 1);
-            mbar_init(&bar_rawfree[i], 256);
+            mbar_init(&bar_rawfree[i], 16);
         }
         for (int i = 0; i < ACT_STAGES; i++) {
             mbar_init(&bar_act[i], 1);
-            mbar_init(&bar_actfree[i], 128);
+            mbar_init(&bar_actfree[i], 256);
         }
         for (int i = 0; i < 2; i++) {
             mbar_init(&bar_mma[i], 1);
-            mbar_init(&bar_epi[i], 128);
+            mbar_init(&bar_epi[i], 256);
         }
-        for (int i = 0; i < 4; i++) {
+        for (int i = 0; i < A_RING; i++) {
             mbar_init(&bar_afree[i], 1);
-            mbar_init(&bar_aready[i], 256);
+            mbar_init(&bar_aready[i], 8);   // one arrival per expanding warp
         }
         s_fail = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -259,9 +295,11 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
 
     // ---- warp roles: no CTA-wide barrier inside the loop, the roles meet only through mbarriers
     //   warp 0, lane 0      issues the TMA copies
-    //   warp 13, lane 0     issues the MMAs
-    //   warps 1..4          epilogue: TMEM -> registers, f32 scaling, final store (lane quadrant = warp % 4)
-    //   warps 5..12         expand the raw nibbles into the f16 operand
+    //   warp 25             issues the MMAs (one elected lane)
+    //   warps 1..8          epilogue: TMEM -> registers, f32 scaling, final store (lane quadrant = warp % 4,
+    //                       two warps per quadrant split the columns)
+    //   warps 9..24         expand the raw nibbles into the f16 operand (lane quadrant = warp % 4; per
+    //                       quadrant four warps: low/high 16 bytes of a chunk x even/odd quarters)
     const int lane = tid & 31;
     if (warp == 0) {
         // ---- TMA producer: refills a raw stage once every expanding thread has left it, and an
@@ -278,148 +316,185 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
                 }
             }
         }
-    } else if (warp == 13) {
-        // ---- MMA issuer: nothing but waits on operands and tcgen05.mma / commit
-        if (lane == 0) {
-            // descriptors differ only in their start address (bits 0..13, in 16-byte units)
-            const uint64_t a_desc0 = smem_desc(su32(abuf), 128, 1024);
-            for (int i = 0; i < nsb; i++) {
-                const int as = i % ACT_STAGES, b = i & 1;
-                const uint32_t d_S = tmem_base + (uint32_t)(b * 2 * NPAD), d_T = d_S + NPAD;
-                const uint64_t b_desc0 = smem_desc(su32(actb + as * BLOB), 128, 4096);
-                const uint64_t am_desc = smem_desc(su32(amin + b * AMIN_BYTES), 128, 256);
-                const uint64_t bm_desc = smem_desc(su32(actb + as * BLOB + NPAD * 512), 128, 256);
-                mbar_wait(&bar_act[as], (uint32_t)((i / ACT_STAGES) & 1), fail);
-                if (i >= 2) mbar_wait(&bar_epi[b], (uint32_t)(((i - 2) >> 1) & 1), fail);   // TMEM buffer b drained
+    } else if (warp == MMA_WARP) {
+        // ---- MMA issuer: nothing but waits on operands and tcgen05.mma / commit. The whole warp runs
+        // the loop (converged, so the descriptor arithmetic stays on the uniform datapath); one
+        // elected lane issues.
+        const bool leader = elect_one();
+        for (int i = 0; i < nsb; i++) {
+            const int as = i % ACT_STAGES, b = i & 1;
+            const uint32_t d_S = tmem_base + (uint32_t)(b * 2 * NPAD), d_T = d_S + NPAD;
+            const uint64_t b_desc0 = smem_desc(su32(actb + as * BLOB), 128, 4096);
+            const uint64_t am_desc = smem_desc(su32(amin + b * AMIN_BYTES), 128, 256);
+            const uint64_t bm_desc = smem_desc(su32(actb + as * BLOB + NPAD * 512), 128, 256);
+            mbar_wait(&bar_act[as], (uint32_t)((i / ACT_STAGES) & 1), fail);
+            if (i >= 2) mbar_wait(&bar_epi[b], (uint32_t)(((i - 2) >> 1) & 1), fail);   // TMEM buffer b drained
 #pragma unroll
-                for (int qd = 0; qd < 4; qd++) {
-                    const int buf = qd;   // quarter g = 4i + qd lives in buffer g & 3 = qd
-                    mbar_wait(&bar_aready[buf], (uint32_t)(i & 1), fail);
-                    tc_fence_after();
-                    TC_STAMP(16 + 4 * i + qd);
-                    const uint64_t ad = a_desc0 + (uint64_t)(buf * (A_Q_BYTES >> 4));
-                    const uint64_t bd = b_desc0 + (uint64_t)(qd * 8 * (128 >> 4));
-                    umma_f16(d_S, ad, bd, IDESC, qd ? 1u : 0u);
-                    umma_f16(d_S, ad + 16, bd + 16, IDESC, 1u);
-                    umma_f16(d_S, ad + 32, bd + 32, IDESC, 1u);
-                    umma_f16(d_S, ad + 48, bd + 48, IDESC, 1u);
+            for (int qd = 0; qd < 4; qd++) {
+                const int gq = 4 * i + qd, buf = gq & (A_RING - 1);
+                mbar_wait(&bar_aready[buf], (uint32_t)((gq / A_RING) & 1), fail);
+                tc_fence_after();
+                if (lane == 0) TC_STAMP(16 + 4 * i + qd);
+                const uint32_t ta = tmem_base + A_COL0 + (uint32_t)(buf * 32);   // 4 K chunks x 8 columns
+                const uint64_t bd = b_desc0 + (uint64_t)(qd * 8 * (128 >> 4));
+                if (leader) {
+                    umma_f16_ta(d_S, ta, bd, IDESC, qd ? 1u : 0u);
+                    umma_f16_ta(d_S, ta + 8, bd + 16, IDESC, 1u);
+                    umma_f16_ta(d_S, ta + 16, bd + 32, IDESC, 1u);
+                    umma_f16_ta(d_S, ta + 24, bd + 48, IDESC, 1u);
                     if (qd == 0) umma_f16(d_T, am_desc, bm_desc, IDESC, 0u);
                     umma_commit(&bar_afree[buf]);
                     if (qd == 3) umma_commit(&bar_mma[b]);
                 }
+                __syncwarp();
             }
         }
-    } else if (warp <= 4) {
+    } else if (warp < DEQ_WARP0) {
         const int q = warp & 3;                 // TMEM lane quadrant this warp may read
         const int row_in_tile = q * 32 + lane;
-        float yacc[NPAD];
+        constexpr int CW = NPAD / 2;            // columns of this warp
+        const int col0 = ((warp - EPI_WARP0) >> 2) * CW;
+        float yacc[CW];
 #pragma unroll
-        for (int c = 0; c < NPAD; c++) yacc[c] = 0.f;
+        for (int c = 0; c < CW; c++) yacc[c] = 0.f;
         for (int i = 0; i < nsb; i++) {
             const int b = i & 1;
             mbar_wait(&bar_mma[b], (uint32_t)((i >> 1) & 1), fail);
             tc_fence_after();
+            if (tid == 32) TC_STAMP(96 + 2 * i);
             const float2 sc = dd[b * ROWS + row_in_tile];
-            const float *yd = reinterpret_cast<const float *>(actb + (i % ACT_STAGES) * BLOB + NPAD * 544);
-            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * 2 * NPAD);
+            const float *yd = reinterpret_cast<const float *>(actb + (i % ACT_STAGES) * BLOB + NPAD * 544) + col0;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * 2 * NPAD + col0);
+            // all loads are in flight before the one wait; the TMEM buffer is handed back as soon as
+            // the values sit in registers, before the arithmetic
+            float S[CW], T[CW];
+            if constexpr (CW == 8) {
+                tmem_ld8(lane_addr, *reinterpret_cast<float(*)[8]>(&S[0]));
+                tmem_ld8(lane_addr + NPAD, *reinterpret_cast<float(*)[8]>(&T[0]));
+            } else {
 #pragma unroll
-            for (int c0 = 0; c0 < NPAD; c0 += 16) {
-                float S[16], T[16];
-                tmem_ld16(lane_addr + c0, S);
-                tmem_ld16(lane_addr + NPAD + c0, T);
-                tmem_ld_wait();
-#pragma unroll
-                for (int c = 0; c < 16; c++) yacc[c0 + c] += yd[c0 + c] * (sc.x * S[c] - sc.y * T[c]);
+                for (int c = 0; c < CW; c += 16) {
+                    tmem_ld16(lane_addr + c, *reinterpret_cast<float(*)[16]>(&S[c]));
+                    tmem_ld16(lane_addr + NPAD + c, *reinterpret_cast<float(*)[16]>(&T[c]));
+                }
             }
+            tmem_ld_wait();
             tc_fence_before();
             mbar_arrive(&bar_epi[b]);   // TMEM buffer b, dd[b] and amin[b] may be reused
+#pragma unroll
+            for (int c = 0; c < CW; c++) yacc[c] += yd[c] * (sc.x * S[c] - sc.y * T[c]);
             mbar_arrive(&bar_actfree[i % ACT_STAGES]);
+            if (tid == 32) TC_STAMP(97 + 2 * i);
         }
         const int64_t row = (int64_t)row_tile * ROWS + row_in_tile;
         if (row < p.M) {
             float *o = p.out + (size_t)split * p.N * p.ldy + row;
 #pragma unroll
-            for (int c = 0; c < NPAD; c++)
-                if (c < p.N) o[(size_t)c * p.ldy] = yacc[c];
+            for (int c = 0; c < CW; c++)
+                if (col0 + c < p.N) o[(size_t)(col0 + c) * p.ldy] = yacc[c];
         }
     } else {
-        const int dt = tid - 160;
-        const int r = dt & 127, hp = dt >> 7;   // row, and which 16 bytes of each 32-byte qs chunk
+        // a warp may only touch the 32 TMEM lanes of its quadrant (warp % 4): that fixes its rows
+        const int dt = tid - DEQ_WARP0 * 32;
+        const int grp = (warp - DEQ_WARP0) >> 2;
+        const int r = (warp & 3) * 32 + lane;   // row
+        const int hp = grp & 1;                 // which 16 bytes of each 32-byte qs chunk
+        const int qpar = grp >> 1;              // which quarters of a super-block: 0 -> 0 and 2, 1 -> 1 and 3
+        const uint32_t a_lane = tmem_base + A_COL0 + ((uint32_t)((warp & 3) * 32) << 16);
+        // Stores into the A ring are published one quarter late: the stores of quarter g are issued, the
+        // values of quarter g+1 are computed, and only then does the thread wait for its stores and
+        // arrive on g's barrier, so the TMEM store latency hides behind arithmetic.
+        int pend = -1;   // ring slot with stores in flight
+        auto publish = [&]() {
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_aready[pend]);
+        };
         for (int i = 0; i < nsb; i++) {
             const int rs = i % RAW_STAGES;
             mbar_wait(&bar_raw[rs], (uint32_t)((i / RAW_STAGES) & 1), fail);
             if (dt == 0) TC_STAMP(160 + 4 * i);
             const uint8_t *rrow = raw + rs * RAW_BYTES + r * 144;
             const uint4 hdr = *reinterpret_cast<const uint4 *>(rrow);
+            uint4 wq[2];   // this thread's 16 bytes of its two 32-byte qs chunks
+#pragma unroll
+            for (int h = 0; h < 2; h++) wq[h] = *reinterpret_cast<const uint4 *>(rrow + 16 + (2 * h + qpar) * 32 + hp * 16);
             // 6-bit scales and mins of the eight sub-blocks (get_scale_min_k4, ggml-quants.c:880-887)
             uint32_t sc8[2], mn8[2];   // four bytes each
             sc8[0] = hdr.y & 0x3f3f3f3fu;
             mn8[0] = hdr.z & 0x3f3f3f3fu;
             sc8[1] = (hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u);
             mn8[1] = ((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u);
-            if (hp == 0) {
+            const __half2 k1024 = __half2(__ushort_as_half(0x6400), __ushort_as_half(0x6400));
+            if (grp == 0) {
                 // (d, dmin) for the epilogue and the mins as the f16 operand of the T product
                 if (i >= 2) mbar_wait(&bar_epi[i & 1], (uint32_t)(((i - 2) >> 1) & 1), fail);   // those of i-2 consumed
                 dd[(i & 1) * ROWS + r] = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
                 uint8_t *am = amin + (i & 1) * AMIN_BYTES + (r >> 3) * 256 + (r & 7) * 16;
 #pragma unroll
                 for (int kc = 0; kc < 2; kc++) {
+                    // small integer -> f16 without a conversion: bytes (m, 0x64) are the f16 1024 + m
                     uint32_t hm[4];
-#pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        // small integer -> f16 without a conversion: 0x6400 | m is 1024 + m
-                        const uint32_t m = (mn8[kc] >> (8 * e)) & 0xffu;
-                        uint32_t t = 0x64006400u | m | (m << 16);
-                        const __half2 v = __hsub2(*reinterpret_cast<__half2 *>(&t), __half2(__ushort_as_half(0x6400), __ushort_as_half(0x6400)));
-                        hm[e] = *reinterpret_cast<const uint32_t *>(&v);
-                    }
+                    uint32_t t0 = __byte_perm(mn8[kc], 0x64646464u, 0x4140), t1 = __byte_perm(mn8[kc], 0x64646464u, 0x4342);
+                    const __half2 v0 = __hsub2(*reinterpret_cast<__half2 *>(&t0), k1024), v1 = __hsub2(*reinterpret_cast<__half2 *>(&t1), k1024);
+                    // a min multiplies the two 16-value bsums of its sub-block: each one fills a pair of K slots
+                    const uint32_t p0 = *reinterpret_cast<const uint32_t *>(&v0), p1 = *reinterpret_cast<const uint32_t *>(&v1);
+                    hm[0] = __byte_perm(p0, p0, 0x1010);
+                    hm[1] = __byte_perm(p0, p0, 0x3232);
+                    hm[2] = __byte_perm(p1, p1, 0x1010);
+                    hm[3] = __byte_perm(p1, p1, 0x3232);
                     *reinterpret_cast<uint4 *>(am + kc * 128) = make_uint4(hm[0], hm[1], hm[2], hm[3]);
                 }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> async-proxy (MMA) reads
             }
 #pragma unroll
-            for (int qd = 0; qd < 4; qd++) {
+            for (int h = 0; h < 2; h++) {
                 // quarter qd = qs chunk qd = sub-blocks 2qd (low nibbles) and 2qd+1 (high nibbles)
-                const int gq = i * 4 + qd, buf = gq & 3;
-                const uint32_t scw = sc8[qd >> 1] >> ((qd & 1) * 16);
-                const uint32_t s_lo = scw & 0xffu, s_hi = (scw >> 8) & 0xffu;
-                // f16 scale pairs and their biases, built from the integers without conversions
-                uint32_t tl = 0x64006400u | s_lo | (s_lo << 16), th = 0x64006400u | s_hi | (s_hi << 16);
-                const __half2 k1024 = __half2(__ushort_as_half(0x6400), __ushort_as_half(0x6400));
+                const int qd = 2 * h + qpar;
+                const int gq = i * 4 + qd, buf = gq & (A_RING - 1);
+                // f16 scale pairs (sc, sc) and their biases, built from the integer bytes without conversions
+                uint32_t tl = __byte_perm(sc8[h], 0x64646464u, qpar ? 0x4242 : 0x4040);
+                uint32_t th = __byte_perm(sc8[h], 0x64646464u, qpar ? 0x4343 : 0x4141);
                 const __half2 mlo = __hsub2(*reinterpret_cast<__half2 *>(&tl), k1024), mhi = __hsub2(*reinterpret_cast<__half2 *>(&th), k1024);
                 const __half2 blo = __hmul2(mlo, __half2(__ushort_as_half(0xE400), __ushort_as_half(0xE400)));   // -1024 * sc
                 const __half2 bhi = __hmul2(mhi, __half2(__ushort_as_half(0xD400), __ushort_as_half(0xD400)));   // -64 * sc
-                const uint4 w4 = *reinterpret_cast<const uint4 *>(rrow + 16 + qd * 32 + hp * 16);
-                const uint32_t ws[4] = {w4.x, w4.y, w4.z, w4.w};
-                if (gq >= 4) mbar_wait(&bar_afree[buf], (uint32_t)(((gq - 4) >> 2) & 1), fail);   // MMAs of the previous use done
-                uint8_t *arow = abuf + buf * A_Q_BYTES + (r >> 3) * 1024 + (r & 7) * 16;
+                const uint32_t ws[4] = {wq[h].x, wq[h].y, wq[h].z, wq[h].w};
+                // 16 low-nibble values (K chunk hp of the quarter) and 16 high-nibble values (K chunk 2 + hp),
+                // two per 32-bit column in the order the nibbles leave a word: (0,2) (1,3) (4,6) (5,7) ...
+                uint32_t lo[8], hi[8];
 #pragma unroll
-                for (int pc = 0; pc < 2; pc++) {
-                    __half2 lo[4], hi[4];
-#pragma unroll
-                    for (int k = 0; k < 2; k++) {
-                        const uint32_t a = ws[2 * pc + k], bb = ws[2 * pc + k] >> 8;
-                        uint32_t t0 = (a & 0x000f000fu) | 0x64006400u, t1 = (bb & 0x000f000fu) | 0x64006400u;
-                        uint32_t u0 = (a & 0x00f000f0u) | 0x54005400u, u1 = (bb & 0x00f000f0u) | 0x54005400u;
-                        lo[2 * k] = __hfma2(*reinterpret_cast<__half2 *>(&t0), mlo, blo);       // (1024+q)*sc - 1024*sc, exact
-                        lo[2 * k + 1] = __hfma2(*reinterpret_cast<__half2 *>(&t1), mlo, blo);
-                        hi[2 * k] = __hfma2(*reinterpret_cast<__half2 *>(&u0), mhi, bhi);       // (64+q)*sc - 64*sc, exact
-                        hi[2 * k + 1] = __hfma2(*reinterpret_cast<__half2 *>(&u1), mhi, bhi);
-                    }
-                    const int p4 = hp * 2 + pc;   // 8-element piece of the sub-block = K chunk within it
-                    *reinterpret_cast<uint4 *>(arow + p4 * 128) = *reinterpret_cast<const uint4 *>(lo);
-                    *reinterpret_cast<uint4 *>(arow + (4 + p4) * 128) = *reinterpret_cast<const uint4 *>(hi);
+                for (int k = 0; k < 4; k++) {
+                    const uint32_t a = ws[k], bb = ws[k] >> 8;
+                    uint32_t t0 = (a & 0x000f000fu) | 0x64006400u, t1 = (bb & 0x000f000fu) | 0x64006400u;
+                    uint32_t u0 = (a & 0x00f000f0u) | 0x54005400u, u1 = (bb & 0x00f000f0u) | 0x54005400u;
+                    const __half2 l0 = __hfma2(*reinterpret_cast<__half2 *>(&t0), mlo, blo);   // (1024+q)*sc - 1024*sc, exact
+                    const __half2 l1 = __hfma2(*reinterpret_cast<__half2 *>(&t1), mlo, blo);
+                    const __half2 h0 = __hfma2(*reinterpret_cast<__half2 *>(&u0), mhi, bhi);   // (64+q)*sc - 64*sc, exact
+                    const __half2 h1 = __hfma2(*reinterpret_cast<__half2 *>(&u1), mhi, bhi);
+                    lo[2 * k] = *reinterpret_cast<const uint32_t *>(&l0);
+                    lo[2 * k + 1] = *reinterpret_cast<const uint32_t *>(&l1);
+                    hi[2 * k] = *reinterpret_cast<const uint32_t *>(&h0);
+                    hi[2 * k + 1] = *reinterpret_cast<const uint32_t *>(&h1);
                 }
-#ifndef TC_CONSUMER_FENCE
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> async-proxy (MMA) reads
-#endif
-                mbar_arrive(&bar_aready[buf]);
-                if (dt == 0) TC_STAMP(161 + 4 * i + (qd >> 1));
+                if (pend >= 0) publish();
+                if (gq >= A_RING) {   // the MMAs that read this ring slot last time are done
+                    mbar_wait(&bar_afree[buf], (uint32_t)(((gq / A_RING) - 1) & 1), fail);
+                    tc_fence_after();
+                }
+                tmem_st8(a_lane + (uint32_t)(buf * 32 + hp * 8), lo);
+                tmem_st8(a_lane + (uint32_t)(buf * 32 + (2 + hp) * 8), hi);
+                pend = buf;
+                if (dt == 0) TC_STAMP(161 + 4 * i + h);
             }
-            mbar_arrive(&bar_rawfree[rs]);
+            publish();   // nothing of this super-block stays unpublished while the warp waits for the next one
+            pend = -1;
+            if (lane == 0) mbar_arrive(&bar_rawfree[rs]);
         }
     }
     tc_fence_before();
     __syncthreads();
+    if (tid == 0) TC_STAMP(2);
     if (warp == 0) tmem_dealloc(tmem_base, TMEM_COLS);
     if (tid == 0 && s_fail) atomicExch(p.err, 2);
 }
@@ -449,14 +524,14 @@ static EncodeTiledFn encode_tiled() {
 
 template <int NPAD, int RS, int AS>
 static size_t tc_smem() {
-    return (size_t)RS * tc::RAW_BYTES + (size_t)AS * tc_blob_bytes(NPAD) + 2 * tc::A_HALF_BYTES + 2 * tc::AMIN_BYTES +
+    return (size_t)RS * tc::RAW_BYTES + (size_t)AS * tc_blob_bytes(NPAD) + 2 * tc::AMIN_BYTES +
            2 * tc::ROWS * sizeof(float2) + 1024;
 }
 
 void mmq_tc_configure() {
-    cudaFuncSetAttribute(k_mmq_tc_q4k<16, 4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem<16, 4, 4>());
-    cudaFuncSetAttribute(k_mmq_tc_q4k<32, 4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem<32, 4, 4>());
-    cudaFuncSetAttribute(k_mmq_tc_q4k<64, 3, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem<64, 3, 2>());
+    cudaFuncSetAttribute(k_mmq_tc_q4k<16, 6, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem<16, 6, 4>());
+    cudaFuncSetAttribute(k_mmq_tc_q4k<32, 6, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem<32, 6, 4>());
+    cudaFuncSetAttribute(k_mmq_tc_q4k<64, 5, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem<64, 5, 3>());
 }
 
 bool mmq_tc_supported(uint32_t type, int64_t K, int64_t M, int64_t N) {
@@ -527,9 +602,9 @@ cudaError_t launch_mmq_tc(const TcPlan &t, const void *W, int64_t K, int64_t M, 
     }
     dim3 grid((unsigned)((M + tc::ROWS - 1) / tc::ROWS), (unsigned)t.n_split);
     switch (t.npad) {
-        case 16: k_mmq_tc_q4k<16, 4, 4><<<grid, tc::THREADS, tc_smem<16, 4, 4>(), st>>>(map, p); break;
-        case 32: k_mmq_tc_q4k<32, 4, 4><<<grid, tc::THREADS, tc_smem<32, 4, 4>(), st>>>(map, p); break;
-        default: k_mmq_tc_q4k<64, 3, 2><<<grid, tc::THREADS, tc_smem<64, 3, 2>(), st>>>(map, p); break;
+        case 16: k_mmq_tc_q4k<16, 6, 4><<<grid, tc::THREADS, tc_smem<16, 6, 4>(), st>>>(map, p); break;
+        case 32: k_mmq_tc_q4k<32, 6, 4><<<grid, tc::THREADS, tc_smem<32, 6, 4>(), st>>>(map, p); break;
+        default: k_mmq_tc_q4k<64, 5, 3><<<grid, tc::THREADS, tc_smem<64, 5, 3>(), st>>>(map, p); break;
     }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
