@@ -257,6 +257,7 @@ tlb_status tlb_device_open(int ordinal, tlb_device **dev) {
         gemv_configure();
         attn_configure();
         mmq_tc_configure();
+        mmq_tc8_configure();
     });
     *dev = d;
     return TLB_OK;

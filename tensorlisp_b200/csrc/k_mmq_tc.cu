@@ -20,161 +20,10 @@
 #include <cuda_fp16.h>
 
 #include "kernels.h"
+#include "tc_common.cuh"
 
 namespace tlb {
 
-#ifdef TC_DEBUG
-__device__ unsigned long long g_tc_dbg[256];
-#define TC_STAMP(slot)                                                                         \
-    do {                                                                                       \
-        if (blockIdx.x == 0 && blockIdx.y == 0) {                                              \
-            unsigned long long t__;                                                            \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));                              \
-            g_tc_dbg[slot] = t__;                                                              \
-        }                                                                                      \
-    } while (0)
-#else
-#define TC_STAMP(slot) do {} while (0)
-#endif
-
-namespace tc {
-
-constexpr int ROWS = 128;          // rows per CTA tile (UMMA M)
-constexpr int THREADS = 832;          // TMA warp + 8 epilogue warps + 16 expanding warps + MMA warp
-constexpr int EPI_WARP0 = 1, DEQ_WARP0 = 9, MMA_WARP = 25;
-constexpr int RAW_BYTES = ROWS * 144;
-constexpr uint32_t TMEM_COLS = 512;           // all of it: accumulators in [0, 256), the A ring in [256, 512)
-constexpr uint32_t A_COL0 = 256;              // ring of 8 quarter super-blocks, 32 columns (64 f16 per row) each
-constexpr int A_RING = 8;
-constexpr int AMIN_BYTES = ROWS * 16 * 2;
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
-
-__device__ __forceinline__ uint32_t su32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(su32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(su32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(su32(bar)) : "memory");
-}
-// Bounded wait. Once any wait of the CTA has given up, every later wait returns at once so the
-// kernel runs to its end (with a wrong result and the error word set) instead of hanging.
-__device__ __forceinline__ bool mbar_try(uint32_t a, uint32_t parity) {
-    uint32_t ok;
-    // No suspend-time hint, and every lane probes for itself: a parked thread wakes up late, and one
-    // probing lane followed by a warp barrier measured 28% slower; every wait here is on the critical path.
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(a), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ void mbar_wait(uint64_t *bar, uint32_t parity, volatile int *fail) {
-    const uint32_t a = su32(bar);
-    if (mbar_try(a, parity)) return;   // the common case: the phase has already completed
-    if (*fail) return;
-    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
-        if (mbar_try(a, parity)) return;
-        if ((i & 1023) == 1023 && *fail) return;
-    }
-    *fail = 1;
-}
-__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(su32(dst)),
-                 "l"(src), "r"(bytes), "r"(su32(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void tma_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(su32(dst)),
-                 "l"(map), "r"(x), "r"(y), "r"(su32(bar))
-                 : "memory");
-}
-
-// ---- tcgen05 wrappers
-__device__ __forceinline__ void tmem_alloc(uint32_t *dst_smem, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(su32(dst_smem)), "r"(cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// A operand in tensor memory: lane = row, each 32-bit column holds two consecutive K elements
-__device__ __forceinline__ void umma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// 32 lanes x 8 consecutive 32-bit columns from registers: thread t of the warp writes lane (warp%4)*32 + t
-__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]),
-                 "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-// true in exactly one lane of a converged warp
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "elect.sync _|p, 0xffffffff;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(pred));
-    return pred != 0;
-}
-__device__ __forceinline__ void umma_commit(uint64_t *bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(su32(bar)) : "memory");
-}
-// 32 lanes x 16 consecutive 32-bit columns: thread t of the warp gets lane (warp%4)*32 + t
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
-    uint32_t r[16];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-                   "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                 : "r"(taddr));
-#pragma unroll
-    for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
-    uint32_t r[8];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(taddr));
-#pragma unroll
-    for (int i = 0; i < 8; i++) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// K-major, no swizzle: a core matrix is 8 rows x 16 bytes stored contiguously (128 bytes);
-// `lbo` = byte distance between the two 16-byte K chunks of one MMA, `sbo` = between 8-row groups.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr >> 4) & 0x3fff);
-    d |= (uint64_t)((lbo >> 4) & 0x3fff) << 16;
-    d |= (uint64_t)((sbo >> 4) & 0x3fff) << 32;
-    d |= (uint64_t)1 << 46;  // descriptor version of sm_100
-    return d;
-}
-
-}  // namespace tc
 
 // Bytes of one packed activation blob (one super-block of NPAD columns):
 //   B    f16 [NPAD x 256]  core-matrix layout, sbo 4096, lbo 128       NPAD*512
@@ -307,11 +156,11 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
         if (lane == 0) {
             for (int i = 0; i < nsb; i++) {
                 if (i + RAW_STAGES < nsb) {
-                    mbar_wait(&bar_rawfree[i % RAW_STAGES], (uint32_t)((i / RAW_STAGES) & 1), fail);   // every expanding thread has left it
+                    mbar_wait_relaxed(&bar_rawfree[i % RAW_STAGES], (uint32_t)((i / RAW_STAGES) & 1), fail);   // every expanding thread has left it
                     load_raw(i + RAW_STAGES);
                 }
                 if (i >= 1 && i - 1 + ACT_STAGES < nsb) {
-                    mbar_wait(&bar_actfree[(i - 1) % ACT_STAGES], (uint32_t)(((i - 1) / ACT_STAGES) & 1), fail);
+                    mbar_wait_relaxed(&bar_actfree[(i - 1) % ACT_STAGES], (uint32_t)(((i - 1) / ACT_STAGES) & 1), fail);
                     load_act(i - 1 + ACT_STAGES);
                 }
             }
@@ -359,7 +208,7 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
         for (int c = 0; c < CW; c++) yacc[c] = 0.f;
         for (int i = 0; i < nsb; i++) {
             const int b = i & 1;
-            mbar_wait(&bar_mma[b], (uint32_t)((i >> 1) & 1), fail);
+            mbar_wait_relaxed(&bar_mma[b], (uint32_t)((i >> 1) & 1), fail);
             tc_fence_after();
             if (tid == 32) TC_STAMP(96 + 2 * i);
             const float2 sc = dd[b * ROWS + row_in_tile];
@@ -406,14 +255,19 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
         // arrive on g's barrier, so the TMEM store latency hides behind arithmetic.
         int pend = -1;   // ring slot with stores in flight
         auto publish = [&]() {
+            TC_CLK(c_pub);
             tmem_st_wait();
+            if (warp == DEQ_WARP0 || warp == DEQ_WARP0 + 12) TC_ACC(226 + (warp == DEQ_WARP0 ? 0 : 8), c_pub);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_aready[pend]);
         };
         for (int i = 0; i < nsb; i++) {
             const int rs = i % RAW_STAGES;
+            TC_CLK(c_raw);
             mbar_wait(&bar_raw[rs], (uint32_t)((i / RAW_STAGES) & 1), fail);
+            if (warp == DEQ_WARP0 || warp == DEQ_WARP0 + 12) TC_ACC(224 + (warp == DEQ_WARP0 ? 0 : 8), c_raw);
+            TC_CLK(c_body);
             if (dt == 0) TC_STAMP(160 + 4 * i);
             const uint8_t *rrow = raw + rs * RAW_BYTES + r * 144;
             const uint4 hdr = *reinterpret_cast<const uint4 *>(rrow);
@@ -429,7 +283,9 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
             const __half2 k1024 = __half2(__ushort_as_half(0x6400), __ushort_as_half(0x6400));
             if (grp == 0) {
                 // (d, dmin) for the epilogue and the mins as the f16 operand of the T product
+                TC_CLK(c_ep);
                 if (i >= 2) mbar_wait(&bar_epi[i & 1], (uint32_t)(((i - 2) >> 1) & 1), fail);   // those of i-2 consumed
+                if (warp == DEQ_WARP0) TC_ACC(228, c_ep);
                 dd[(i & 1) * ROWS + r] = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
                 uint8_t *am = amin + (i & 1) * AMIN_BYTES + (r >> 3) * 256 + (r & 7) * 16;
 #pragma unroll
@@ -479,8 +335,10 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
                 }
                 if (pend >= 0) publish();
                 if (gq >= A_RING) {   // the MMAs that read this ring slot last time are done
+                    TC_CLK(c_af);
                     mbar_wait(&bar_afree[buf], (uint32_t)(((gq / A_RING) - 1) & 1), fail);
                     tc_fence_after();
+                    if (warp == DEQ_WARP0 || warp == DEQ_WARP0 + 12) TC_ACC(227 + (warp == DEQ_WARP0 ? 0 : 8), c_af);
                 }
                 tmem_st8(a_lane + (uint32_t)(buf * 32 + hp * 8), lo);
                 tmem_st8(a_lane + (uint32_t)(buf * 32 + (2 + hp) * 8), hi);
@@ -490,6 +348,7 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
             publish();   // nothing of this super-block stays unpublished while the warp waits for the next one
             pend = -1;
             if (lane == 0) mbar_arrive(&bar_rawfree[rs]);
+            if (warp == DEQ_WARP0 || warp == DEQ_WARP0 + 12) TC_ACC(225 + (warp == DEQ_WARP0 ? 0 : 8), c_body);
         }
     }
     tc_fence_before();
@@ -544,7 +403,7 @@ TcPlan mmq_tc_plan(int64_t K, int64_t M, int64_t N, int sm_count) {
     t.nsb = (int)(K / 256);
     const int64_t tiles = (M + tc::ROWS - 1) / tc::ROWS;
     // K split: modelled time = waves x (CTA start-up + super-blocks per CTA x time per super-block)
-    // + the reduce launch when split; constants measured on B200 (start-up 2.3 us, 1.35 us per
+    // + the reduce launch when split; constants measured on B200 (start-up 2.3 us, 1.0 us per
     // super-block, 2 us for the reduce)
     int best = 1;
     double best_score = 1e30;
@@ -555,7 +414,7 @@ TcPlan mmq_tc_plan(int64_t K, int64_t M, int64_t N, int sm_count) {
         if (splits != s) continue;
         const int64_t units = tiles * splits;
         const int64_t waves = (units + sm_count - 1) / sm_count;
-        const double score = (double)waves * (2.3 + 1.35 * per) + (splits > 1 ? 2.0 : 0.0);
+        const double score = (double)waves * (2.3 + 1.0 * per) + (splits > 1 ? 2.0 : 0.0);
         if (score < best_score) { best_score = score; best = splits; }
     }
     t.n_split = best;
@@ -572,18 +431,33 @@ cudaError_t launch_act_pack_tc(const ActLayout &a, const void *act, int npad, vo
     return cudaGetLastError();
 }
 
+// 2-D tensor map over a row-major byte matrix (rows x row_bytes), box box_bytes x box_rows, described in
+// elements of elem_bytes (1 or 2) because a box dimension may not exceed 256 elements
+cudaError_t tc_encode_2d(CUtensorMap *map, const void *base, uint64_t row_bytes, uint64_t rows, uint32_t box_bytes, uint32_t box_rows,
+                         uint32_t elem_bytes) {
+    if (encode_tiled() == nullptr) return cudaErrorNotSupported;
+    const cuuint64_t gdim[2] = {(cuuint64_t)(row_bytes / elem_bytes), (cuuint64_t)rows};
+    const cuuint64_t gstride[1] = {(cuuint64_t)row_bytes};
+    const cuuint32_t box[2] = {box_bytes / elem_bytes, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    if (encode_tiled()(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), gdim,
+                       gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return cudaErrorInvalidValue;
+    return cudaSuccess;
+}
+
+void launch_mmq_reduce(const float *partial, float *y, int64_t total, int n_split, cudaStream_t st) {
+    k_mmq_reduce<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(partial, y, total, n_split);
+}
+
+bool tc_available() { return encode_tiled() != nullptr; }
+
 cudaError_t launch_mmq_tc(const TcPlan &t, const void *W, int64_t K, int64_t M, int64_t N, const void *blobs, float *y,
                           int64_t ldy, void *partial, int *err, cudaStream_t st) {
     CUtensorMap map;
-    const cuuint64_t row_bytes = (cuuint64_t)(K / 256 * 144);
-    const cuuint64_t gdim[2] = {row_bytes, (cuuint64_t)M};
-    const cuuint64_t gstride[1] = {row_bytes};
-    const cuuint32_t box[2] = {144, (cuuint32_t)tc::ROWS};
-    const cuuint32_t estr[2] = {1, 1};
-    if (encode_tiled()(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(W), gdim, gstride, box, estr,
-                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return cudaErrorInvalidValue;
+    cudaError_t e = tc_encode_2d(&map, W, (uint64_t)(K / 256 * 144), (uint64_t)M, 144, tc::ROWS, 1);
+    if (e != cudaSuccess) return e;
     TcParams p;
     p.act = (const uint8_t *)blobs;
     p.M = M;
@@ -606,12 +480,11 @@ cudaError_t launch_mmq_tc(const TcPlan &t, const void *W, int64_t K, int64_t M, 
         case 32: k_mmq_tc_q4k<32, 6, 4><<<grid, tc::THREADS, tc_smem<32, 6, 4>(), st>>>(map, p); break;
         default: k_mmq_tc_q4k<64, 5, 3><<<grid, tc::THREADS, tc_smem<64, 5, 3>(), st>>>(map, p); break;
     }
-    cudaError_t e = cudaGetLastError();
+    e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     if (t.n_split > 1) {
         if (ldy != M) return cudaErrorInvalidValue;   // the reduce writes dense columns
-        const int64_t total = N * M;
-        k_mmq_reduce<<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const float *)partial, y, total, t.n_split);
+        launch_mmq_reduce((const float *)partial, y, N * M, t.n_split, st);
         e = cudaGetLastError();
     }
     return e;

@@ -1,0 +1,401 @@
+// Batched MUL_MAT (5..32 activation columns) with Q8_0 weights on the 5th-generation tensor cores:
+// the output projection of a decode step (vocab x d_model, Q8_0) is the largest matrix of the model.
+//
+// Arithmetic (same integers as the reference's ggml-cpu path, vendor/ggml/src/ggml-cpu/quants.c:451-479):
+// per 32-element block b, output row r and activation column c
+//     D_b = sum_k q[r,k] * q8[k,c]            (int8 x int8 -> int32, exact)
+//     y  += (float)D_b * (d_w[r,b] * d_a[c,b])
+// tcgen05.mma kind::i8 computes D_b for 128 rows x N columns in one instruction (K = 32 = one block),
+// each block into its own TMEM accumulator; the epilogue warps apply the two f32 scales.
+//
+// Data movement: TMA brings a 128-row x 272-byte box (8 blocks of 34 bytes per row) of raw weights and
+// one packed activation blob per 256 elements of K into shared memory. The weight codes need no
+// arithmetic at all: sixteen warps strip the 2-byte scales, realign the codes and store them into
+// tensor memory (tcgen05.st), where the MMA reads its A operand; B (the int8 activations, K-major core
+// matrices) stays in shared memory. Eight warps drain the accumulators, one warp issues the MMAs,
+// one the TMA copies; they meet only through mbarriers, every wait is bounded.
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include "kernels.h"
+#include "tc_common.cuh"
+
+namespace tlb {
+
+namespace tc8 {
+constexpr int ROWS = 128;
+constexpr int THREADS = 832;   // TMA warp + 8 epilogue warps + 16 realigning warps + MMA warp
+constexpr int EPI_WARP0 = 1, DEQ_WARP0 = 9, MMA_WARP = 25;
+constexpr int STAGE_BLOCKS = 8;                       // Q8_0 blocks of a row per pipeline stage (256 elements of K)
+constexpr int ROW_CHUNK = STAGE_BLOCKS * 34;          // 272 bytes: 17 x 16, so 128-bit reads at row stride are conflict-free
+constexpr int RAW_BYTES = ROWS * ROW_CHUNK;
+constexpr uint32_t TMEM_COLS = 512;                   // accumulators in [0, 256), the A ring in [256, 512)
+constexpr uint32_t A_COL0 = 256;
+constexpr int A_RING = 4;                             // stages of A (8 blocks x 8 columns of 4 int8) and of weight scales
+}  // namespace tc8
+
+// Bytes of one packed activation blob (256 elements of K, NPAD columns):
+//   B    int8 [NPAD x 256]  K-major core matrices (8 columns x 16 bytes), lbo 128, sbo 2048     NPAD*256
+//   d_a  f32  [8][NPAD]     activation scale per block and column                              NPAD*32
+static inline __host__ __device__ int tc8_blob_bytes(int npad) { return npad * 288; }
+
+__global__ void __launch_bounds__(256) k_act_pack_q80(const int8_t *__restrict__ qs, const float *__restrict__ ds, int64_t K, int N,
+                                                       int npad, uint8_t *__restrict__ out) {
+    const int st = blockIdx.x;
+    uint8_t *o = out + (size_t)st * tc8_blob_bytes(npad);
+    for (int u = threadIdx.x; u < npad * 16; u += blockDim.x) {
+        const int n = u / 16, kc = u % 16;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (n < N) v = *reinterpret_cast<const uint4 *>(qs + (size_t)n * K + (size_t)st * 256 + kc * 16);
+        *reinterpret_cast<uint4 *>(o + (size_t)(n / 8) * 2048 + kc * 128 + (n % 8) * 16) = v;
+    }
+    float *od = reinterpret_cast<float *>(o + (size_t)npad * 256);
+    for (int u = threadIdx.x; u < npad * 8; u += blockDim.x) {
+        const int b = u / npad, n = u % npad;
+        od[u] = n < N ? ds[(size_t)n * (K / 32) + (size_t)st * 8 + b] : 0.f;
+    }
+}
+
+struct Tc8Params {
+    const uint8_t *act;
+    float *out;
+    int64_t M;
+    int N, npad, nst, st_per_split, n_split;
+    int64_t ldy;
+    int *err;
+};
+
+namespace tc8 {
+__device__ __forceinline__ void umma_i8_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld16i(uint32_t taddr, int (&v)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                   "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld8i(uint32_t taddr, int (&v)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr));
+}
+
+// The two blocks (2G, 2G+1) of a row's 272-byte chunk are bytes [68G, 68G+68) = 17 words that start G
+// words into a 16-byte unit; five aligned 128-bit reads cover them for every G. Block 2G has its scale
+// in the low half of the first word and its codes 2 bytes in; block 2G+1 has its scale in the high half
+// of word 8 and its codes word-aligned after it.
+template <int G>
+__device__ __forceinline__ void split_blocks(const uint8_t *row, uint32_t (&qa)[8], uint32_t (&qb)[8], float &da, float &db) {
+    constexpr int U0 = (68 * G) / 16;      // first 16-byte unit
+    constexpr int W0 = (68 * G) / 4 - 4 * U0;   // word of the chunk start inside it (= G)
+    uint32_t w[20];
+#pragma unroll
+    for (int u = 0; u < 5; u++) {
+        // for G = 3 the fifth unit is bytes 256..271: the last one of the row
+        const uint4 v = *reinterpret_cast<const uint4 *>(row + (U0 + u) * 16);
+        w[4 * u] = v.x; w[4 * u + 1] = v.y; w[4 * u + 2] = v.z; w[4 * u + 3] = v.w;
+    }
+    da = __half2float(__ushort_as_half((unsigned short)(w[W0] & 0xffffu)));
+#pragma unroll
+    for (int j = 0; j < 8; j++) qa[j] = __funnelshift_r(w[W0 + j], w[W0 + j + 1], 16);
+    db = __half2float(__ushort_as_half((unsigned short)(w[W0 + 8] >> 16)));
+#pragma unroll
+    for (int j = 0; j < 8; j++) qb[j] = w[W0 + 9 + j];
+}
+}  // namespace tc8
+
+template <int NPAD, int RAW_STAGES, int ACT_STAGES>
+__global__ void __launch_bounds__(tc8::THREADS, 1) k_mmq_tc_q80(const __grid_constant__ CUtensorMap wmap, Tc8Params p) {
+    using namespace tc;
+    using namespace tc8;
+    constexpr int ROWS = tc8::ROWS;
+    constexpr int BLOB = NPAD * 288;
+    // int8 x int8 -> int32, K-major A and B: c_format s32 (2) at bit 4, a/b format signed 8-bit (1) at bits 7 and 10
+    constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NPAD >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
+    constexpr int GCOLS = 4 * NPAD;   // accumulator columns of one group of four blocks
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = smem_raw + ((1024u - (su32(smem_raw) & 1023u)) & 1023u);
+    uint8_t *raw = smem;                                              // RAW_STAGES x RAW_BYTES
+    uint8_t *actb = raw + RAW_STAGES * tc8::RAW_BYTES;                // ACT_STAGES x BLOB
+    float *dw = reinterpret_cast<float *>(actb + ACT_STAGES * BLOB);  // [A_RING][8][ROWS] weight scales
+    __shared__ uint64_t bar_raw[RAW_STAGES], bar_rawfree[RAW_STAGES], bar_act[ACT_STAGES], bar_actfree[ACT_STAGES];
+    __shared__ uint64_t bar_aready[tc8::A_RING], bar_afree[tc8::A_RING], bar_dwfree[tc8::A_RING], bar_mma[2], bar_epi[2];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int s_fail;
+    volatile int *fail = &s_fail;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int row_tile = blockIdx.x, split = blockIdx.y;
+    const int st0 = split * p.st_per_split;
+    const int nst = min(p.st_per_split, p.nst - st0);
+    if (tid == 0) {
+        for (int i = 0; i < RAW_STAGES; i++) {
+            mbar_init(&bar_raw[i], 1);
+            mbar_init(&bar_rawfree[i], 16);
+        }
+        for (int i = 0; i < ACT_STAGES; i++) {
+            mbar_init(&bar_act[i], 1);
+            mbar_init(&bar_actfree[i], 256);
+        }
+        for (int i = 0; i < tc8::A_RING; i++) {
+            mbar_init(&bar_aready[i], 16);
+            mbar_init(&bar_afree[i], 1);
+            mbar_init(&bar_dwfree[i], 256);
+        }
+        for (int i = 0; i < 2; i++) {
+            mbar_init(&bar_mma[i], 1);
+            mbar_init(&bar_epi[i], 256);
+        }
+        s_fail = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) tmem_alloc(&tmem_base_s, tc8::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+
+    auto load_raw = [&](int i) {
+        const int s = i % RAW_STAGES;
+        mbar_expect_tx(&bar_raw[s], tc8::RAW_BYTES);
+        tma_2d(raw + s * tc8::RAW_BYTES, &wmap, (st0 + i) * (tc8::ROW_CHUNK / 2), row_tile * ROWS, &bar_raw[s]);   // x in 16-bit elements
+    };
+    auto load_act = [&](int i) {
+        const int s = i % ACT_STAGES;
+        mbar_expect_tx(&bar_act[s], BLOB);
+        bulk_g2s(actb + s * BLOB, p.act + (size_t)(st0 + i) * BLOB, BLOB, &bar_act[s]);
+    };
+    if (tid == 0) {
+        for (int i = 0; i < nst && i < RAW_STAGES; i++) load_raw(i);
+        for (int i = 0; i < nst && i < ACT_STAGES; i++) load_act(i);
+    }
+
+    if (warp == 0) {
+        // ---- TMA producer
+        if (lane == 0) {
+            for (int i = 0; i < nst; i++) {
+                if (i + RAW_STAGES < nst) {
+                    mbar_wait_relaxed(&bar_rawfree[i % RAW_STAGES], (uint32_t)((i / RAW_STAGES) & 1), fail);
+                    load_raw(i + RAW_STAGES);
+                }
+                if (i >= 1 && i - 1 + ACT_STAGES < nst) {
+                    mbar_wait_relaxed(&bar_actfree[(i - 1) % ACT_STAGES], (uint32_t)(((i - 1) / ACT_STAGES) & 1), fail);
+                    load_act(i - 1 + ACT_STAGES);
+                }
+            }
+        }
+    } else if (warp == tc8::MMA_WARP) {
+        // ---- MMA issuer: the whole warp runs the loop (converged), one elected lane issues
+        const bool leader = elect_one();
+        for (int i = 0; i < nst; i++) {
+            const int as = i % ACT_STAGES, slot = i % tc8::A_RING;
+            const uint64_t b_desc0 = smem_desc(su32(actb + as * BLOB), 128, 2048);
+            mbar_wait(&bar_act[as], (uint32_t)((i / ACT_STAGES) & 1), fail);
+            mbar_wait(&bar_aready[slot], (uint32_t)((i / tc8::A_RING) & 1), fail);
+            tc_fence_after();
+#pragma unroll
+            for (int hh = 0; hh < 2; hh++) {
+                const int G = 2 * i + hh, gb = G & 1;
+                if (G >= 2) {
+                    mbar_wait(&bar_epi[gb], (uint32_t)(((G - 2) >> 1) & 1), fail);   // accumulator group gb drained
+                    tc_fence_after();
+                }
+                if (leader) {
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const int blk = 4 * hh + j;
+                        umma_i8_ta(tmem_base + (uint32_t)(gb * GCOLS + j * NPAD), tmem_base + tc8::A_COL0 + (uint32_t)(slot * 64 + blk * 8),
+                                   b_desc0 + (uint64_t)(blk * (256 >> 4)), IDESC);
+                    }
+                    umma_commit(&bar_mma[gb]);
+                    if (hh == 1) umma_commit(&bar_afree[slot]);
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp < tc8::DEQ_WARP0) {
+        // ---- epilogue: two warps per TMEM lane quadrant split the columns
+        const int q = warp & 3;
+        const int row_in_tile = q * 32 + lane;
+        constexpr int CW = NPAD / 2;
+        const int col0 = ((warp - tc8::EPI_WARP0) >> 2) * CW;
+        float yacc[CW];
+#pragma unroll
+        for (int c = 0; c < CW; c++) yacc[c] = 0.f;
+        for (int i = 0; i < nst; i++) {
+            const int as = i % ACT_STAGES, slot = i % tc8::A_RING;
+            const float *da = reinterpret_cast<const float *>(actb + as * BLOB + NPAD * 256) + col0;   // [8][NPAD]
+            const float *dwr = dw + (size_t)slot * 8 * ROWS + row_in_tile;
+#pragma unroll
+            for (int hh = 0; hh < 2; hh++) {
+                const int G = 2 * i + hh, gb = G & 1;
+                mbar_wait_relaxed(&bar_mma[gb], (uint32_t)((G >> 1) & 1), fail);
+                tc_fence_after();
+                const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(gb * GCOLS + col0);
+#pragma unroll
+                for (int jp = 0; jp < 4; jp += 2) {
+                    int D0[CW], D1[CW];
+                    if constexpr (CW == 8) {
+                        tmem_ld8i(lane_addr + jp * NPAD, *reinterpret_cast<int(*)[8]>(&D0[0]));
+                        tmem_ld8i(lane_addr + (jp + 1) * NPAD, *reinterpret_cast<int(*)[8]>(&D1[0]));
+                    } else {
+                        tmem_ld16i(lane_addr + jp * NPAD, *reinterpret_cast<int(*)[16]>(&D0[0]));
+                        tmem_ld16i(lane_addr + (jp + 1) * NPAD, *reinterpret_cast<int(*)[16]>(&D1[0]));
+                    }
+                    tmem_ld_wait();
+                    if (jp == 2) {
+                        tc_fence_before();
+                        mbar_arrive(&bar_epi[gb]);   // accumulator group gb may be overwritten
+                    }
+                    const int b0 = 4 * hh + jp;
+                    const float w0 = dwr[b0 * ROWS], w1 = dwr[(b0 + 1) * ROWS];
+#pragma unroll
+                    for (int c = 0; c < CW; c++) {
+                        yacc[c] += (float)D0[c] * (w0 * da[b0 * NPAD + c]);
+                        yacc[c] += (float)D1[c] * (w1 * da[(b0 + 1) * NPAD + c]);
+                    }
+                }
+            }
+            mbar_arrive(&bar_dwfree[slot]);
+            mbar_arrive(&bar_actfree[as]);
+        }
+        const int64_t row = (int64_t)row_tile * ROWS + row_in_tile;
+        if (row < p.M) {
+            float *o = p.out + (size_t)split * p.N * p.ldy + row;
+#pragma unroll
+            for (int c = 0; c < CW; c++)
+                if (col0 + c < p.N) o[(size_t)(col0 + c) * p.ldy] = yacc[c];
+        }
+    } else {
+        // ---- realigning warps: lane quadrant = warp % 4 fixes the rows; per quadrant four warps take two blocks each
+        const int g = (warp - tc8::DEQ_WARP0) >> 2;
+        const int r = (warp & 3) * 32 + lane;
+        const uint32_t a_lane = tmem_base + tc8::A_COL0 + ((uint32_t)((warp & 3) * 32) << 16);
+        for (int i = 0; i < nst; i++) {
+            const int rs = i % RAW_STAGES, slot = i % tc8::A_RING;
+            mbar_wait(&bar_raw[rs], (uint32_t)((i / RAW_STAGES) & 1), fail);
+            const uint8_t *rrow = raw + rs * tc8::RAW_BYTES + r * tc8::ROW_CHUNK;
+            uint32_t qa[8], qb[8];
+            float da, db;
+            switch (g) {   // warp-uniform
+                case 0: split_blocks<0>(rrow, qa, qb, da, db); break;
+                case 1: split_blocks<1>(rrow, qa, qb, da, db); break;
+                case 2: split_blocks<2>(rrow, qa, qb, da, db); break;
+                default: split_blocks<3>(rrow, qa, qb, da, db); break;
+            }
+            if (i >= tc8::A_RING) {
+                // the MMAs that read this ring slot are done, and the epilogue has read its scales
+                mbar_wait(&bar_afree[slot], (uint32_t)(((i / tc8::A_RING) - 1) & 1), fail);
+                mbar_wait(&bar_dwfree[slot], (uint32_t)(((i / tc8::A_RING) - 1) & 1), fail);
+                tc_fence_after();
+            }
+            tmem_st8(a_lane + (uint32_t)(slot * 64 + (2 * g) * 8), qa);
+            tmem_st8(a_lane + (uint32_t)(slot * 64 + (2 * g + 1) * 8), qb);
+            float *dws = dw + (size_t)slot * 8 * ROWS + r;
+            dws[(2 * g) * ROWS] = da;
+            dws[(2 * g + 1) * ROWS] = db;
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&bar_aready[slot]);
+                mbar_arrive(&bar_rawfree[rs]);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, tc8::TMEM_COLS);
+    if (tid == 0 && s_fail) atomicExch(p.err, 2);
+}
+
+// ---------------------------------------------------------------- host side
+template <int NPAD, int RS, int AS>
+static size_t tc8_smem() {
+    return (size_t)RS * tc8::RAW_BYTES + (size_t)AS * tc8_blob_bytes(NPAD) + (size_t)tc8::A_RING * 8 * tc8::ROWS * sizeof(float) + 1024;
+}
+
+void mmq_tc8_configure() {
+    cudaFuncSetAttribute(k_mmq_tc_q80<16, 4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc8_smem<16, 4, 4>());
+    cudaFuncSetAttribute(k_mmq_tc_q80<32, 4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc8_smem<32, 4, 4>());
+}
+
+bool mmq_tc8_supported(int64_t K, int64_t M, int64_t N) { return K % 256 == 0 && K >= 256 && M >= 1 && N > 4 && N <= 32; }
+
+TcPlan mmq_tc8_plan(int64_t K, int64_t M, int64_t N, int sm_count) {
+    TcPlan t;
+    t.npad = N <= 16 ? 16 : 32;
+    t.nsb = (int)(K / 256);
+    const int64_t tiles = (M + tc8::ROWS - 1) / tc8::ROWS;
+    // same model as the Q4_K kernel, with this kernel's time per stage
+    int best = 1;
+    double best_score = 1e30;
+    for (int s = 1; s <= t.nsb && s <= 16; s++) {
+        const int per = (t.nsb + s - 1) / s;
+        if (s > 1 && per < 2) break;
+        const int splits = (t.nsb + per - 1) / per;
+        if (splits != s) continue;
+        const int64_t waves = (tiles * splits + sm_count - 1) / sm_count;
+        const double score = (double)waves * (2.3 + 1.0 * per) + (splits > 1 ? 2.0 : 0.0);
+        if (score < best_score) { best_score = score; best = splits; }
+    }
+    t.n_split = best;
+    t.sb_per_split = (t.nsb + best - 1) / best;
+    t.blob_bytes = (uint64_t)t.nsb * tc8_blob_bytes(t.npad);
+    t.partial_bytes = best > 1 ? (uint64_t)best * N * M * 4 : 0;
+    return t;
+}
+
+cudaError_t launch_act_pack_tc8(const ActLayout &a, const void *act, int npad, void *blobs, cudaStream_t st) {
+    const char *ab = (const char *)act;
+    k_act_pack_q80<<<(unsigned)(a.K / 256), 256, 0, st>>>((const int8_t *)(ab + a.qs_off), (const float *)(ab + a.d_off), a.K, (int)a.N, npad,
+                                                         (uint8_t *)blobs);
+    return cudaGetLastError();
+}
+
+cudaError_t tc_encode_2d(CUtensorMap *map, const void *base, uint64_t row_bytes, uint64_t rows, uint32_t box_bytes, uint32_t box_rows,
+                         uint32_t elem_bytes);
+void launch_mmq_reduce(const float *partial, float *y, int64_t total, int n_split, cudaStream_t st);
+
+cudaError_t launch_mmq_tc8(const TcPlan &t, const void *W, int64_t K, int64_t M, int64_t N, const void *blobs, float *y, int64_t ldy,
+                           void *partial, int *err, cudaStream_t st) {
+    CUtensorMap map;
+    // described in 16-bit elements: a 272-byte box is 136 of them (the limit is 256 elements per dimension)
+    cudaError_t e = tc_encode_2d(&map, W, (uint64_t)(K / 32 * 34), (uint64_t)M, tc8::ROW_CHUNK, tc8::ROWS, 2);
+    if (e != cudaSuccess) return e;
+    Tc8Params p;
+    p.act = (const uint8_t *)blobs;
+    p.M = M;
+    p.N = (int)N;
+    p.npad = t.npad;
+    p.nst = t.nsb;
+    p.st_per_split = t.sb_per_split;
+    p.n_split = t.n_split;
+    p.err = err;
+    if (t.n_split > 1) {
+        p.out = (float *)partial;
+        p.ldy = M;
+    } else {
+        p.out = y;
+        p.ldy = ldy;
+    }
+    dim3 grid((unsigned)((M + tc8::ROWS - 1) / tc8::ROWS), (unsigned)t.n_split);
+    if (t.npad == 16) k_mmq_tc_q80<16, 4, 4><<<grid, tc8::THREADS, tc8_smem<16, 4, 4>(), st>>>(map, p);
+    else k_mmq_tc_q80<32, 4, 4><<<grid, tc8::THREADS, tc8_smem<32, 4, 4>(), st>>>(map, p);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    if (t.n_split > 1) {
+        if (ldy != M) return cudaErrorInvalidValue;
+        launch_mmq_reduce((const float *)partial, y, N * M, t.n_split, st);
+        e = cudaGetLastError();
+    }
+    return e;
+}
+
+}  // namespace tlb

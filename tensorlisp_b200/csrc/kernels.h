@@ -57,6 +57,16 @@ cudaError_t launch_act_pack_tc(const ActLayout &a, const void *act, int npad, vo
 cudaError_t launch_mmq_tc(const TcPlan &t, const void *W, int64_t K, int64_t M, int64_t N, const void *blobs, float *y,
                           int64_t ldy, void *partial, int *err, cudaStream_t st);
 void mmq_tc_configure();
+bool tc_available();   // the driver offers cuTensorMapEncodeTiled
+
+// ---------------------------------------------------------------- k_mmq_tc_q8.cu
+// Q8_0 weights x 5..32 activation columns on tcgen05 (kind::i8, one accumulator per 32-element block).
+bool mmq_tc8_supported(int64_t K, int64_t M, int64_t N);
+TcPlan mmq_tc8_plan(int64_t K, int64_t M, int64_t N, int sm_count);
+cudaError_t launch_act_pack_tc8(const ActLayout &a, const void *act, int npad, void *blobs, cudaStream_t st);
+cudaError_t launch_mmq_tc8(const TcPlan &t, const void *W, int64_t K, int64_t M, int64_t N, const void *blobs, float *y,
+                           int64_t ldy, void *partial, int *err, cudaStream_t st);
+void mmq_tc8_configure();
 
 // ---------------------------------------------------------------- k_fused.cu
 // One row (= activation column n) per CTA: produce the f32 row, quantize it to Q8_K into an ActLayout

@@ -27,6 +27,16 @@ TView view_of(const Tensor &t) {
     return v;
 }
 
+// tensor-core mul_mat kernels by weight type
+bool tc_supported(uint32_t wty, int64_t K, int64_t M, int64_t N) {
+    if (wty == TLB_TYPE_Q4_K) return mmq_tc_supported(wty, K, M, N);
+    if (wty == TLB_TYPE_Q8_0) return tc_available() && mmq_tc8_supported(K, M, N);
+    return false;
+}
+TcPlan tc_plan(uint32_t wty, int64_t K, int64_t M, int64_t N, int sm) {
+    return wty == TLB_TYPE_Q8_0 ? mmq_tc8_plan(K, M, N, sm) : mmq_tc_plan(K, M, N, sm);
+}
+
 int act_kind_for(uint32_t wty) { return wty == TLB_TYPE_Q4_K ? ACT_Q8_K : ACT_Q8_0; }
 bool is_qact(const std::string &op) { return op == "QUANT_ACT" || op == "ROW_QUANT"; }
 
@@ -371,10 +381,10 @@ void lower_mul_mat(L &l) {
     const bool batched = tw.ne[2] * tw.ne[3] * t.ne[2] * t.ne[3] != 1;
     const bool dense_w = tw.nb[1] == tw.row_size();
     const bool dense_y = t.is_contiguous();
-    if (!batched && dense_w && dense_y && l.T(qa).op_params[1] > 0 && mmq_tc_supported(tw.ty, K, M, N) && !getenv("TLB_MM_GENERIC") &&
+    if (!batched && dense_w && dense_y && l.T(qa).op_params[1] > 0 && tc_supported(tw.ty, K, M, N) && !getenv("TLB_MM_GENERIC") &&
         !getenv("TLB_NO_TC")) {
         // tensor-core path: the QUANT_ACT node also packed the activations into per-super-block blobs
-        const TcPlan tp = mmq_tc_plan(K, M, N, sm);
+        const TcPlan tp = tc_plan(tw.ty, K, M, N, sm);
         if (tp.npad != l.T(qa).op_params[1]) throw std::string("activation blobs were packed for another column count");
         const int64_t sc = l.c.layout->scratch[l.pos];
         if (tp.partial_bytes > 0 && sc < 0) throw std::string("split-K scratch was not planned");
@@ -382,8 +392,10 @@ void lower_mul_mat(L &l) {
         ps.buf = BUF_ARENA;
         ps.off = sc < 0 ? 0 : (uint64_t)sc;
         const uint64_t blob_off = a.bytes;
+        const bool q8 = tw.ty == TLB_TYPE_Q8_0;
         l.push([=](const RunCtx &r) {
-            return launch_mmq_tc(tp, r.at(pw), K, M, N, r.at(pq) + blob_off, (float *)r.at(pd), M, r.at(ps), r.err, r.stream);
+            return q8 ? launch_mmq_tc8(tp, r.at(pw), K, M, N, r.at(pq) + blob_off, (float *)r.at(pd), M, r.at(ps), r.err, r.stream)
+                      : launch_mmq_tc(tp, r.at(pw), K, M, N, r.at(pq) + blob_off, (float *)r.at(pd), M, r.at(ps), r.err, r.stream);
         });
         return;
     }
@@ -412,7 +424,9 @@ void lower_quant_act(L &l) {
     const int npad = t.op_params[1];   // > 0: also pack the blobs of the tensor-core path behind the Q8_K block
     l.push([=](const RunCtx &r) {
         cudaError_t e = launch_act_quantize(a, (const float *)r.at(px), ldx, r.at(pd), r.stream);
-        if (e == cudaSuccess && npad > 0) e = launch_act_pack_tc(a, r.at(pd), npad, r.at(pd) + a.bytes, r.stream);
+        if (e == cudaSuccess && npad > 0)
+            e = a.kind == ACT_Q8_0 ? launch_act_pack_tc8(a, r.at(pd), npad, r.at(pd) + a.bytes, r.stream)
+                                   : launch_act_pack_tc(a, r.at(pd), npad, r.at(pd) + a.bytes, r.stream);
         return e;
     });
 }
@@ -564,8 +578,8 @@ uint64_t node_scratch_bytes(const Graph &g, int32_t id, int sm_count) {
         g.tensors[t.src[2]].op_params[1] > 0) {
         // split-K partial sums of the tensor-core path
         const Tensor &tw = g.tensors[t.src[0]], &tx = g.tensors[t.src[1]];
-        if (tw.ne[2] * tw.ne[3] * t.ne[2] * t.ne[3] == 1 && mmq_tc_supported(tw.ty, tw.ne[0], tw.ne[1], tx.ne[1]))
-            return mmq_tc_plan(tw.ne[0], tw.ne[1], tx.ne[1], sm_count).partial_bytes;
+        if (tw.ne[2] * tw.ne[3] * t.ne[2] * t.ne[3] == 1 && tc_supported(tw.ty, tw.ne[0], tw.ne[1], tx.ne[1]))
+            return tc_plan(tw.ty, tw.ne[0], tw.ne[1], tx.ne[1], sm_count).partial_bytes;
     }
     return 0;
 }
@@ -737,8 +751,8 @@ void rewrite_graph(Graph &g) {
                 // a consumer that takes the tensor-core path also needs the packed blobs behind the Q8_K block
                 const Tensor &mm = g.tensors[id];
                 const bool plain2d = tw.ne[2] * tw.ne[3] * mm.ne[2] * mm.ne[3] == 1 && tw.nb[1] == tw.row_size();
-                if (plain2d && mmq_tc_supported(tw.ty, tx.ne[0], tw.ne[1], tx.ne[1]) && !getenv("TLB_NO_TC")) {
-                    const TcPlan tp = mmq_tc_plan(tx.ne[0], tw.ne[1], tx.ne[1], 148);
+                if (plain2d && tc_supported(tw.ty, tx.ne[0], tw.ne[1], tx.ne[1]) && !getenv("TLB_NO_TC")) {
+                    const TcPlan tp = tc_plan(tw.ty, tx.ne[0], tw.ne[1], tx.ne[1], 148);
                     Tensor &q = g.tensors[qa];
                     q.op_params[1] = tp.npad;
                     q.opaque_bytes = act_layout(kind, tx.ne[0], tx.nrows()).bytes + tp.blob_bytes;

@@ -1,0 +1,183 @@
+// mbarrier, TMA and tcgen05 wrappers shared by the tensor-core mul_mat kernels (k_mmq_tc.cu for Q4_K,
+// k_mmq_tc_q8.cu for Q8_0).
+#pragma once
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cstdint>
+
+namespace tlb {
+
+#ifdef TC_DEBUG
+__device__ unsigned long long g_tc_dbg[256];
+#define TC_STAMP(slot)                                                                         \
+    do {                                                                                       \
+        if (blockIdx.x == 0 && blockIdx.y == 0) {                                              \
+            unsigned long long t__;                                                            \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));                              \
+            g_tc_dbg[slot] = t__;                                                              \
+        }                                                                                      \
+    } while (0)
+#define TC_CLK(var) long long var = clock64()
+#define TC_ACC(slot, t0)                                                                       \
+    do {                                                                                       \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0) atomicAdd(&g_tc_dbg[slot], (unsigned long long)(clock64() - (t0))); \
+    } while (0)
+#else
+#define TC_STAMP(slot) do {} while (0)
+#define TC_CLK(var) do {} while (0)
+#define TC_ACC(slot, t0) do {} while (0)
+#endif
+
+namespace tc {
+
+constexpr int ROWS = 128;          // rows per CTA tile (UMMA M)
+constexpr int THREADS = 832;          // TMA warp + 8 epilogue warps + 16 expanding warps + MMA warp
+constexpr int EPI_WARP0 = 1, DEQ_WARP0 = 9, MMA_WARP = 25;
+constexpr int RAW_BYTES = ROWS * 144;
+constexpr uint32_t TMEM_COLS = 512;           // all of it: accumulators in [0, 256), the A ring in [256, 512)
+constexpr uint32_t A_COL0 = 256;              // ring of 8 quarter super-blocks, 32 columns (64 f16 per row) each
+constexpr int A_RING = 8;
+constexpr int AMIN_BYTES = ROWS * 16 * 2;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+__device__ __forceinline__ uint32_t su32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(su32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(su32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(su32(bar)) : "memory");
+}
+// Bounded wait. Once any wait of the CTA has given up, every later wait returns at once so the
+// kernel runs to its end (with a wrong result and the error word set) instead of hanging.
+__device__ __forceinline__ bool mbar_try(uint32_t a, uint32_t parity) {
+    uint32_t ok;
+    // No suspend-time hint, and every lane probes for itself: a parked thread wakes up late, and one
+    // probing lane followed by a warp barrier measured 28% slower; every wait here is on the critical path.
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(a), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void mbar_wait(uint64_t *bar, uint32_t parity, volatile int *fail) {
+    const uint32_t a = su32(bar);
+    if (mbar_try(a, parity)) return;   // the common case: the phase has already completed
+    if (*fail) return;
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+        if (mbar_try(a, parity)) return;
+        if ((i & 1023) == 1023 && *fail) return;
+    }
+    *fail = 1;
+}
+// The same wait for roles with slack (epilogue, TMA refills): sleeps between probes, so a warp that
+// mostly waits does not take issue slots from the warps that expand the weights.
+__device__ __forceinline__ void mbar_wait_relaxed(uint64_t *bar, uint32_t parity, volatile int *fail) {
+    const uint32_t a = su32(bar);
+    if (mbar_try(a, parity)) return;
+    if (*fail) return;
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+        __nanosleep(64);
+        if (mbar_try(a, parity)) return;
+        if ((i & 1023) == 1023 && *fail) return;
+    }
+    *fail = 1;
+}
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(su32(dst)),
+                 "l"(src), "r"(bytes), "r"(su32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tma_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(su32(dst)),
+                 "l"(map), "r"(x), "r"(y), "r"(su32(bar))
+                 : "memory");
+}
+
+// ---- tcgen05 wrappers
+__device__ __forceinline__ void tmem_alloc(uint32_t *dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(su32(dst_smem)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// A operand in tensor memory: lane = row, each 32-bit column holds two consecutive K elements
+__device__ __forceinline__ void umma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 lanes x 8 consecutive 32-bit columns from registers: thread t of the warp writes lane (warp%4)*32 + t
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]),
+                 "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// true in exactly one lane of a converged warp
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(su32(bar)) : "memory");
+}
+// 32 lanes x 16 consecutive 32-bit columns: thread t of the warp gets lane (warp%4)*32 + t
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                   "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+#pragma unroll
+    for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
+    uint32_t r[8];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, no swizzle: a core matrix is 8 rows x 16 bytes stored contiguously (128 bytes);
+// `lbo` = byte distance between the two 16-byte K chunks of one MMA, `sbo` = between 8-row groups.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3fff);
+    d |= (uint64_t)((lbo >> 4) & 0x3fff) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3fff) << 32;
+    d |= (uint64_t)1 << 46;  // descriptor version of sm_100
+    return d;
+}
+
+}  // namespace tc
+
+}  // namespace tlb
