@@ -8,6 +8,7 @@ This file is collected last on purpose: a run that stops at the first failure ha
 every other test.
 """
 import ctypes as C
+import os
 
 import numpy as np
 import pytest
@@ -76,10 +77,14 @@ def test_static_scratch_attention_matches_the_program_path():
         assert err <= 1e-3 * np.abs(want.astype(np.float32)).max(), (call, err)
         assert np.array_equal(got, want), call
 
-    # a shape whose partial sums do not fit the built-in array is refused, not truncated
+    # a shape whose partial sums do not fit the built-in array is refused, not truncated (the chunk
+    # length is forced down to 64 tokens: the planner's own choice splits a context only as far as it
+    # takes to fill the GPU, which keeps the partial sums of any realistic shape far below the limit)
+    os.environ["TLB_PA_CHUNK"] = "64"
     st = L.tlb_paged_attention_static(n.dev, C.c_void_p(q_dev.device_ptr), C.c_void_p(kptr), C.c_void_p(vptr),
                                       C.c_void_p(t_dev.device_ptr), C.c_void_p(l_dev.device_ptr), C.c_void_p(o_dev.device_ptr),
                                       4096, 64, 8, 128, 16, 4096, 65535, scale)
+    del os.environ["TLB_PA_CHUNK"]
     assert st == TLB_INVALID and b"built-in scratch holds" in L.tlb_last_error()
     for b in (q_dev, t_dev, l_dev, o_dev):
         b.free()
