@@ -21,6 +21,7 @@
 #include <math_constants.h>
 
 #include "kernels.h"
+#include "pdl.cuh"
 #include "tlb_internal.h"
 
 namespace tlb {
@@ -66,6 +67,8 @@ struct PagedParams {
 
 template <int HS>
 __global__ void __launch_bounds__(PA_WARPS * 32) k_paged_attn(PagedParams p) {
+    griddep_launch();
+    griddep_wait();   // the pools and the query were written by the kernel before this one
     constexpr int ROW_BYTES = HS * 2;
     constexpr int CHUNKS = ROW_BYTES / 16;             // 16-byte chunks per row
     constexpr int TILE_BYTES = PA_TILE * ROW_BYTES;    // one of K / V
@@ -278,6 +281,8 @@ __global__ void __launch_bounds__(PA_WARPS * 32) k_paged_attn(PagedParams p) {
 
 template <int HS>
 __global__ void __launch_bounds__(128) k_paged_reduce(PagedParams p) {
+    griddep_launch();
+    griddep_wait();
     const int head = blockIdx.x, seq = blockIdx.y;
     const int ctx = p.lens[seq];
     const int valid = ctx > 0 ? min(p.n_chunks, (ctx + p.chunk_tokens - 1) / p.chunk_tokens) : 0;
@@ -352,9 +357,9 @@ uint64_t paged_scratch_bytes(const PagedGeom &g) {
 template <int HS>
 static cudaError_t launch_pa(const PagedGeom &g, const PagedParams &p, cudaStream_t st) {
     dim3 grid((unsigned)g.n_chunks, (unsigned)(g.kv_heads * p.groups_per_kv), (unsigned)g.seqs);
-    k_paged_attn<HS><<<grid, PA_WARPS * 32, pa_smem(HS), st>>>(p);
-    if (g.n_chunks > 1) k_paged_reduce<HS><<<dim3((unsigned)g.heads, (unsigned)g.seqs), 128, 0, st>>>(p);
-    return cudaGetLastError();
+    cudaError_t e = launch_pdl(k_paged_attn<HS>, grid, dim3(PA_WARPS * 32), pa_smem(HS), st, p);
+    if (e == cudaSuccess && g.n_chunks > 1) e = launch_pdl(k_paged_reduce<HS>, dim3((unsigned)g.heads, (unsigned)g.seqs), dim3(128), 0, st, p);
+    return e;
 }
 
 cudaError_t launch_paged_attention(const PagedGeom &g, const void *q, const void *kpool, const void *vpool,

@@ -8,6 +8,7 @@
 #include <math_constants.h>
 
 #include "kernels.h"
+#include "pdl.cuh"
 
 namespace tlb {
 
@@ -336,6 +337,8 @@ __global__ void k_rope(RopeArgs p, const uint8_t *a, const int32_t *pos, const f
 // by the f32 -> f16 casts and the cache write; a negative slot skips the token's key and value.
 __global__ void k_rope_kv(RopeKvArgs p, const uint8_t *q, const uint8_t *k, const uint8_t *v, const int32_t *pos,
                           const float *ff, __half *q16, __half *kpool, __half *vpool, const int64_t *slots) {
+    griddep_launch();
+    griddep_wait();
     const int tok = blockIdx.x, hsl = blockIdx.y, pr = threadIdx.x;
     const int hs = p.hs;
     if (hsl < p.heads + p.kv_heads) {
@@ -378,9 +381,8 @@ __global__ void k_rope_kv(RopeKvArgs p, const uint8_t *q, const uint8_t *k, cons
 cudaError_t launch_rope_kv(const RopeKvArgs &p, const void *q, const void *k, const void *v, const int32_t *pos, const float *ff,
                            void *q16, void *kpool, void *vpool, const int64_t *slots, cudaStream_t st) {
     if (p.tokens == 0) return cudaSuccess;
-    k_rope_kv<<<dim3((unsigned)p.tokens, (unsigned)(p.heads + 2 * p.kv_heads)), p.hs / 2, 0, st>>>(
-        p, (const uint8_t *)q, (const uint8_t *)k, (const uint8_t *)v, pos, ff, (__half *)q16, (__half *)kpool, (__half *)vpool, slots);
-    return cudaGetLastError();
+    return launch_pdl(k_rope_kv, dim3((unsigned)p.tokens, (unsigned)(p.heads + 2 * p.kv_heads)), dim3(p.hs / 2), 0, st, p,
+                      (const uint8_t *)q, (const uint8_t *)k, (const uint8_t *)v, pos, ff, (__half *)q16, (__half *)kpool, (__half *)vpool, slots);
 }
 cudaError_t launch_rope(const RopeArgs &p, const void *a, const int32_t *pos, const float *ff, void *d, cudaStream_t st) {
     const int64_t n = p.a.ne[0] / 2 * p.a.ne[1] * p.a.ne[2] * p.a.ne[3];

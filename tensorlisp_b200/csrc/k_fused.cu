@@ -11,6 +11,7 @@
 #include <cuda_fp16.h>
 
 #include "kernels.h"
+#include "pdl.cuh"
 
 namespace tlb {
 
@@ -56,6 +57,8 @@ __device__ __forceinline__ void rq_load8(const RowQuantArgs &p, int n, int64_t k
 // (the row is a few KB and sits in L2), so all of them use the same scale.
 __global__ void __launch_bounds__(RQ_THREADS) k_row_quant_q8k(RowQuantArgs p) {
     __shared__ float red[RQ_WARPS];
+    griddep_launch();
+    griddep_wait();
     const int n = blockIdx.x;          // activation column (= token)
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t K = p.K;
@@ -169,8 +172,7 @@ cudaError_t launch_row_quant(const RowQuantArgs &p, cudaStream_t st) {
     if (p.N == 0 || p.K == 0) return cudaSuccess;
     const int rows = p.npad > 0 ? p.npad : (int)p.N;
     const int nblk = (int)(p.K / 256);
-    k_row_quant_q8k<<<dim3(rows, (nblk + RQ_WARPS - 1) / RQ_WARPS), RQ_THREADS, 0, st>>>(p);
-    return cudaGetLastError();
+    return launch_pdl(k_row_quant_q8k, dim3(rows, (nblk + RQ_WARPS - 1) / RQ_WARPS), dim3(RQ_THREADS), 0, st, p);
 }
 
 }  // namespace tlb

@@ -21,6 +21,7 @@
 
 #include "kernels.h"
 #include "tc_common.cuh"
+#include "pdl.cuh"
 
 namespace tlb {
 
@@ -137,10 +138,14 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
         mbar_expect_tx(&bar_act[s], BLOB);
         bulk_g2s(actb + s * BLOB, p.act + (size_t)(sb0 + i) * BLOB, BLOB, &bar_act[s]);
     };
-    if (tid == 0) {
+    // the weights do not depend on the kernel before this one: their first loads go out before the
+    // dependency wait; activations (and everything downstream of them) come after it
+    griddep_launch();
+    if (tid == 0)
         for (int i = 0; i < nsb && i < RAW_STAGES; i++) load_raw(i);
+    griddep_wait();
+    if (tid == 0)
         for (int i = 0; i < nsb && i < ACT_STAGES; i++) load_act(i);
-    }
 
     // ---- warp roles: no CTA-wide barrier inside the loop, the roles meet only through mbarriers
     //   warp 0, lane 0      issues the TMA copies
@@ -360,6 +365,8 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
 
 // y[n][m] = sum over the K splits, in split order
 __global__ void k_mmq_reduce(const float *__restrict__ part, float *__restrict__ y, int64_t total, int n_split) {
+    griddep_launch();
+    griddep_wait();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     float s = 0.f;
@@ -448,7 +455,7 @@ cudaError_t tc_encode_2d(CUtensorMap *map, const void *base, uint64_t row_bytes,
 }
 
 void launch_mmq_reduce(const float *partial, float *y, int64_t total, int n_split, cudaStream_t st) {
-    k_mmq_reduce<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(partial, y, total, n_split);
+    launch_pdl(k_mmq_reduce, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, partial, y, total, n_split);
 }
 
 bool tc_available() { return encode_tiled() != nullptr; }
@@ -476,11 +483,10 @@ cudaError_t launch_mmq_tc(const TcPlan &t, const void *W, int64_t K, int64_t M, 
     }
     dim3 grid((unsigned)((M + tc::ROWS - 1) / tc::ROWS), (unsigned)t.n_split);
     switch (t.npad) {
-        case 16: k_mmq_tc_q4k<16, 6, 4><<<grid, tc::THREADS, tc_smem<16, 6, 4>(), st>>>(map, p); break;
-        case 32: k_mmq_tc_q4k<32, 6, 4><<<grid, tc::THREADS, tc_smem<32, 6, 4>(), st>>>(map, p); break;
-        default: k_mmq_tc_q4k<64, 5, 3><<<grid, tc::THREADS, tc_smem<64, 5, 3>(), st>>>(map, p); break;
+        case 16: e = launch_pdl(k_mmq_tc_q4k<16, 6, 4>, grid, dim3(tc::THREADS), tc_smem<16, 6, 4>(), st, map, p); break;
+        case 32: e = launch_pdl(k_mmq_tc_q4k<32, 6, 4>, grid, dim3(tc::THREADS), tc_smem<32, 6, 4>(), st, map, p); break;
+        default: e = launch_pdl(k_mmq_tc_q4k<64, 5, 3>, grid, dim3(tc::THREADS), tc_smem<64, 5, 3>(), st, map, p); break;
     }
-    e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     if (t.n_split > 1) {
         if (ldy != M) return cudaErrorInvalidValue;   // the reduce writes dense columns

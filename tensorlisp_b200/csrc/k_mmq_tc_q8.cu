@@ -19,6 +19,7 @@
 
 #include "kernels.h"
 #include "tc_common.cuh"
+#include "pdl.cuh"
 
 namespace tlb {
 
@@ -171,10 +172,13 @@ __global__ void __launch_bounds__(tc8::THREADS, 1) k_mmq_tc_q80(const __grid_con
         mbar_expect_tx(&bar_act[s], BLOB);
         bulk_g2s(actb + s * BLOB, p.act + (size_t)(st0 + i) * BLOB, BLOB, &bar_act[s]);
     };
-    if (tid == 0) {
+    // weights first, then the dependency wait, then activations (see k_mmq_tc.cu)
+    griddep_launch();
+    if (tid == 0)
         for (int i = 0; i < nst && i < RAW_STAGES; i++) load_raw(i);
+    griddep_wait();
+    if (tid == 0)
         for (int i = 0; i < nst && i < ACT_STAGES; i++) load_act(i);
-    }
 
     if (warp == 0) {
         // ---- TMA producer
@@ -386,9 +390,8 @@ cudaError_t launch_mmq_tc8(const TcPlan &t, const void *W, int64_t K, int64_t M,
         p.ldy = ldy;
     }
     dim3 grid((unsigned)((M + tc8::ROWS - 1) / tc8::ROWS), (unsigned)t.n_split);
-    if (t.npad == 16) k_mmq_tc_q80<16, 4, 4><<<grid, tc8::THREADS, tc8_smem<16, 4, 4>(), st>>>(map, p);
-    else k_mmq_tc_q80<32, 4, 4><<<grid, tc8::THREADS, tc8_smem<32, 4, 4>(), st>>>(map, p);
-    e = cudaGetLastError();
+    if (t.npad == 16) e = launch_pdl(k_mmq_tc_q80<16, 4, 4>, grid, dim3(tc8::THREADS), tc8_smem<16, 4, 4>(), st, map, p);
+    else e = launch_pdl(k_mmq_tc_q80<32, 4, 4>, grid, dim3(tc8::THREADS), tc8_smem<32, 4, 4>(), st, map, p);
     if (e != cudaSuccess) return e;
     if (t.n_split > 1) {
         if (ldy != M) return cudaErrorInvalidValue;
