@@ -95,6 +95,36 @@ def decoder_weights(cfg: DecoderConfig, tp: int = 1) -> list:
     return ws
 
 
+COLUMN_PARALLEL = ("wq", "wk", "wv", "ffn_gate", "ffn_up", "output")   # rows split across ranks
+ROW_PARALLEL = ("wo", "ffn_down")                                        # K split across ranks, results summed
+
+
+def shard_weight(name: str, w: np.ndarray, rank: int, tp: int) -> np.ndarray:
+    """This rank's part of a full f32 weight `w` ([rows, K], or [n] for norms), cut BEFORE quantization:
+    rows of column-parallel matrices (whole heads / FFN units / vocabulary entries), K ranges of
+    row-parallel ones (multiples of 256, so every quantization block stays whole), everything else whole."""
+    base = name.rsplit(".", 1)[-1]
+    if tp == 1 or w.ndim != 2:
+        return w
+    if base in COLUMN_PARALLEL:
+        assert w.shape[0] % tp == 0
+        n = w.shape[0] // tp
+        return np.ascontiguousarray(w[rank * n:(rank + 1) * n])
+    if base in ROW_PARALLEL:
+        assert w.shape[1] % (tp * 256) == 0
+        n = w.shape[1] // tp
+        return np.ascontiguousarray(w[:, rank * n:(rank + 1) * n])
+    return w
+
+
+def combine_argmax(local_max: np.ndarray, local_idx: np.ndarray, vocab_per_rank: int) -> np.ndarray:
+    """Global argmax of column-parallel logits from every rank's (max, index) per token: arrays
+    [ranks, tokens]. Ties go to the lowest global index, as a single argmax over the full row would."""
+    best = np.argmax(local_max, axis=0)   # first rank holding the maximum
+    tok = np.arange(local_max.shape[1])
+    return (best * vocab_per_rank + local_idx[best, tok]).astype(np.int64)
+
+
 def decoder_step(cfg: DecoderConfig, batch: int, max_ctx: int, pool_blocks: int, tp: int = 1,
                  with_argmax: bool = True, taps: bool = False) -> DecoderGraph:
     """One batched decode step over a paged f16 KV pool (the loop body of ports/gemma4/concurrency.ss:120-158):
