@@ -68,11 +68,12 @@ __global__ void __launch_bounds__(RQ_THREADS) k_row_quant_q8k(RowQuantArgs p) {
     if (n >= p.N) {
         // padding columns of the tensor-core blobs are zero
         if (p.npad > 0 && sb < nblk) {
-            uint8_t *o = (uint8_t *)ob + p.blob_off + (size_t)sb * p.blob_bytes;
-            *reinterpret_cast<uint4 *>(o + (size_t)(n / 8) * 4096 + lane * 128 + (n % 8) * 16) = make_uint4(0, 0, 0, 0);
+            const int ch = n / p.npad, nl = n % p.npad;   // blobs: [chunk of npad columns][block]
+            uint8_t *o = (uint8_t *)ob + p.blob_off + ((size_t)ch * nblk + sb) * p.blob_bytes;
+            *reinterpret_cast<uint4 *>(o + (size_t)(nl / 8) * 4096 + lane * 128 + (nl % 8) * 16) = make_uint4(0, 0, 0, 0);
             if ((lane & 1) == 0)
-                *reinterpret_cast<__half *>(o + (size_t)p.npad * 512 + (size_t)(n / 8) * 256 + (lane >> 4) * 128 + (n % 8) * 16 + ((lane >> 1) & 7) * 2) = __float2half_rn(0.f);
-            if (lane == 0) reinterpret_cast<float *>(o + (size_t)p.npad * 544)[n] = 0.f;
+                *reinterpret_cast<__half *>(o + (size_t)p.npad * 512 + (size_t)(nl / 8) * 256 + (lane >> 4) * 128 + (nl % 8) * 16 + ((lane >> 1) & 7) * 2) = __float2half_rn(0.f);
+            if (lane == 0) reinterpret_cast<float *>(o + (size_t)p.npad * 544)[nl] = 0.f;
         }
         return;
     }
@@ -153,16 +154,17 @@ __global__ void __launch_bounds__(RQ_THREADS) k_row_quant_q8k(RowQuantArgs p) {
     if (p.npad > 0) {
         // tensor-core operand: this lane's 8 codes are K chunk `lane` of column n, in the order
         // (0, 2, 1, 3, 4, 6, 5, 7) in which the weight nibbles come out of a 32-bit word
-        uint8_t *o = (uint8_t *)ob + p.blob_off + (size_t)sb * p.blob_bytes;
+        const int ch = n / p.npad, nl = n % p.npad;   // blobs: [chunk of npad columns][block]
+        uint8_t *o = (uint8_t *)ob + p.blob_off + ((size_t)ch * nblk + sb) * p.blob_bytes;
         __half2 h[4];
         h[0] = __floats2half2_rn((float)q[0], (float)q[2]);
         h[1] = __floats2half2_rn((float)q[1], (float)q[3]);
         h[2] = __floats2half2_rn((float)q[4], (float)q[6]);
         h[3] = __floats2half2_rn((float)q[5], (float)q[7]);
-        *reinterpret_cast<uint4 *>(o + (size_t)(n / 8) * 4096 + lane * 128 + (n % 8) * 16) = *reinterpret_cast<const uint4 *>(h);
+        *reinterpret_cast<uint4 *>(o + (size_t)(nl / 8) * 4096 + lane * 128 + (nl % 8) * 16) = *reinterpret_cast<const uint4 *>(h);
         if ((lane & 1) == 0)
-            *reinterpret_cast<__half *>(o + (size_t)p.npad * 512 + (size_t)(n / 8) * 256 + (lane >> 4) * 128 + (n % 8) * 16 + ((lane >> 1) & 7) * 2) = __float2half_rn((float)s16);
-        if (lane == 0) reinterpret_cast<float *>(o + (size_t)p.npad * 544)[n] = d;
+            *reinterpret_cast<__half *>(o + (size_t)p.npad * 512 + (size_t)(nl / 8) * 256 + (lane >> 4) * 128 + (nl % 8) * 16 + ((lane >> 1) & 7) * 2) = __float2half_rn((float)s16);
+        if (lane == 0) reinterpret_cast<float *>(o + (size_t)p.npad * 544)[nl] = d;
     }
 }
 
@@ -170,7 +172,7 @@ bool row_quant_supported(int64_t K) { return K % 256 == 0 && K / 256 <= 65535 * 
 
 cudaError_t launch_row_quant(const RowQuantArgs &p, cudaStream_t st) {
     if (p.N == 0 || p.K == 0) return cudaSuccess;
-    const int rows = p.npad > 0 ? p.npad : (int)p.N;
+    const int rows = p.npad > 0 ? (int)((p.N + p.npad - 1) / p.npad) * p.npad : (int)p.N;   // padding columns of the last chunk too
     const int nblk = (int)(p.K / 256);
     return launch_pdl(k_row_quant_q8k, dim3(rows, (nblk + RQ_WARPS - 1) / RQ_WARPS), dim3(RQ_THREADS), 0, st, p);
 }

@@ -16,6 +16,7 @@
 // double-buffered TMEM accumulator; four warps drain it with tcgen05.ld and apply the f32 scales
 // while the next super-block is being expanded and multiplied. K is split across CTAs; partial sums
 // go to scratch and k_mmq_reduce adds them in a fixed order (deterministic).
+#include <algorithm>
 #include <cuda.h>
 #include <cuda_fp16.h>
 
@@ -39,9 +40,14 @@ static inline __host__ __device__ int tc_blob_bytes(int npad) { return (npad * 5
 __global__ void __launch_bounds__(256) k_act_pack_tc(const int8_t *__restrict__ qs, const float *__restrict__ ds,
                                                       const int16_t *__restrict__ bsums, int64_t K, int N, int npad,
                                                       uint8_t *__restrict__ out) {
+    // grid (super-block, chunk of npad columns); blobs are laid out [chunk][super-block]
     const int sb = blockIdx.x;
     const int blob = tc_blob_bytes(npad);
-    uint8_t *o = out + (size_t)sb * blob;
+    uint8_t *o = out + ((size_t)blockIdx.y * gridDim.x + sb) * blob;
+    qs += (size_t)blockIdx.y * npad * K;
+    ds += (size_t)blockIdx.y * npad * (K / 256);
+    bsums += (size_t)blockIdx.y * npad * (K / 16);
+    N = min(npad, N - (int)blockIdx.y * npad);
     // B tile: one 16-byte chunk per (n, kc)
     for (int u = threadIdx.x; u < npad * 32; u += blockDim.x) {
         const int n = u / 32, kc = u % 32;
@@ -401,7 +407,7 @@ void mmq_tc_configure() {
 }
 
 bool mmq_tc_supported(uint32_t type, int64_t K, int64_t M, int64_t N) {
-    return type == TLB_TYPE_Q4_K && K % 256 == 0 && K >= 256 && M >= 1 && N > 4 && N <= 64 && encode_tiled() != nullptr;
+    return type == TLB_TYPE_Q4_K && K % 256 == 0 && K >= 256 && M >= 1 && N > 4 && N <= 8192 && encode_tiled() != nullptr;
 }
 
 TcPlan mmq_tc_plan(int64_t K, int64_t M, int64_t N, int sm_count) {
@@ -426,14 +432,16 @@ TcPlan mmq_tc_plan(int64_t K, int64_t M, int64_t N, int sm_count) {
     }
     t.n_split = best;
     t.sb_per_split = (t.nsb + best - 1) / best;
-    t.blob_bytes = (uint64_t)t.nsb * tc_blob_bytes(t.npad);
-    t.partial_bytes = best > 1 ? (uint64_t)best * N * M * 4 : 0;
+    t.n_col_chunks = (int)((N + t.npad - 1) / t.npad);
+    t.blob_unit = (uint64_t)tc_blob_bytes(t.npad);
+    t.blob_bytes = (uint64_t)t.n_col_chunks * t.nsb * t.blob_unit;
+    t.partial_bytes = best > 1 ? (uint64_t)best * std::min<int64_t>(N, t.npad) * M * 4 : 0;
     return t;
 }
 
 cudaError_t launch_act_pack_tc(const ActLayout &a, const void *act, int npad, void *blobs, cudaStream_t st) {
     const char *ab = (const char *)act;
-    k_act_pack_tc<<<(unsigned)(a.K / 256), 256, 0, st>>>((const int8_t *)(ab + a.qs_off), (const float *)(ab + a.d_off),
+    k_act_pack_tc<<<dim3((unsigned)(a.K / 256), (unsigned)((a.N + npad - 1) / npad)), 256, 0, st>>>((const int8_t *)(ab + a.qs_off), (const float *)(ab + a.d_off),
                                                         (const int16_t *)(ab + a.bsum_off), a.K, (int)a.N, npad, (uint8_t *)blobs);
     return cudaGetLastError();
 }
@@ -465,35 +473,41 @@ cudaError_t launch_mmq_tc(const TcPlan &t, const void *W, int64_t K, int64_t M, 
     CUtensorMap map;
     cudaError_t e = tc_encode_2d(&map, W, (uint64_t)(K / 256 * 144), (uint64_t)M, 144, tc::ROWS, 1);
     if (e != cudaSuccess) return e;
-    TcParams p;
-    p.act = (const uint8_t *)blobs;
-    p.M = M;
-    p.N = (int)N;
-    p.npad = t.npad;
-    p.nsb = t.nsb;
-    p.sb_per_split = t.sb_per_split;
-    p.n_split = t.n_split;
-    p.err = err;
-    if (t.n_split > 1) {
-        p.out = (float *)partial;
-        p.ldy = M;
-    } else {
-        p.out = y;
-        p.ldy = ldy;
-    }
     dim3 grid((unsigned)((M + tc::ROWS - 1) / tc::ROWS), (unsigned)t.n_split);
-    switch (t.npad) {
-        case 16: e = launch_pdl(k_mmq_tc_q4k<16, 6, 4>, grid, dim3(tc::THREADS), tc_smem<16, 6, 4>(), st, map, p); break;
-        case 32: e = launch_pdl(k_mmq_tc_q4k<32, 6, 4>, grid, dim3(tc::THREADS), tc_smem<32, 6, 4>(), st, map, p); break;
-        default: e = launch_pdl(k_mmq_tc_q4k<64, 5, 3>, grid, dim3(tc::THREADS), tc_smem<64, 5, 3>(), st, map, p); break;
+    // more columns than one launch takes (prefill): one launch per chunk of npad columns
+    for (int c = 0; c < t.n_col_chunks; c++) {
+        const int64_t n0 = (int64_t)c * t.npad, nc = std::min<int64_t>(t.npad, N - n0);
+        TcParams p;
+        p.act = (const uint8_t *)blobs + (size_t)c * t.nsb * t.blob_unit;
+        p.M = M;
+        p.N = (int)nc;
+        p.npad = t.npad;
+        p.nsb = t.nsb;
+        p.sb_per_split = t.sb_per_split;
+        p.n_split = t.n_split;
+        p.err = err;
+        float *yc = y + n0 * ldy;
+        if (t.n_split > 1) {
+            p.out = (float *)partial;
+            p.ldy = M;
+        } else {
+            p.out = yc;
+            p.ldy = ldy;
+        }
+        switch (t.npad) {
+            case 16: e = launch_pdl(k_mmq_tc_q4k<16, 6, 4>, grid, dim3(tc::THREADS), tc_smem<16, 6, 4>(), st, map, p); break;
+            case 32: e = launch_pdl(k_mmq_tc_q4k<32, 6, 4>, grid, dim3(tc::THREADS), tc_smem<32, 6, 4>(), st, map, p); break;
+            default: e = launch_pdl(k_mmq_tc_q4k<64, 5, 3>, grid, dim3(tc::THREADS), tc_smem<64, 5, 3>(), st, map, p); break;
+        }
+        if (e != cudaSuccess) return e;
+        if (t.n_split > 1) {
+            if (ldy != M) return cudaErrorInvalidValue;   // the reduce writes dense columns
+            launch_mmq_reduce((const float *)partial, yc, nc * M, t.n_split, st);
+            e = cudaGetLastError();
+            if (e != cudaSuccess) return e;
+        }
     }
-    if (e != cudaSuccess) return e;
-    if (t.n_split > 1) {
-        if (ldy != M) return cudaErrorInvalidValue;   // the reduce writes dense columns
-        launch_mmq_reduce((const float *)partial, y, N * M, t.n_split, st);
-        e = cudaGetLastError();
-    }
-    return e;
+    return cudaSuccess;
 }
 
 }  // namespace tlb

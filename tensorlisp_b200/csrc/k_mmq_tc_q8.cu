@@ -14,6 +14,7 @@
 // tensor memory (tcgen05.st), where the MMA reads its A operand; B (the int8 activations, K-major core
 // matrices) stays in shared memory. Eight warps drain the accumulators, one warp issues the MMAs,
 // one the TMA copies; they meet only through mbarriers, every wait is bounded.
+#include <algorithm>
 #include <cuda.h>
 #include <cuda_fp16.h>
 
@@ -42,8 +43,12 @@ static inline __host__ __device__ int tc8_blob_bytes(int npad) { return npad * 2
 
 __global__ void __launch_bounds__(256) k_act_pack_q80(const int8_t *__restrict__ qs, const float *__restrict__ ds, int64_t K, int N,
                                                        int npad, uint8_t *__restrict__ out) {
+    // grid (stage, chunk of npad columns); blobs are laid out [chunk][stage]
     const int st = blockIdx.x;
-    uint8_t *o = out + (size_t)st * tc8_blob_bytes(npad);
+    uint8_t *o = out + ((size_t)blockIdx.y * gridDim.x + st) * tc8_blob_bytes(npad);
+    qs += (size_t)blockIdx.y * npad * K;
+    ds += (size_t)blockIdx.y * npad * (K / 32);
+    N = min(npad, N - (int)blockIdx.y * npad);
     for (int u = threadIdx.x; u < npad * 16; u += blockDim.x) {
         const int n = u / 16, kc = u % 16;
         uint4 v = make_uint4(0, 0, 0, 0);
@@ -330,7 +335,7 @@ void mmq_tc8_configure() {
     cudaFuncSetAttribute(k_mmq_tc_q80<32, 4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc8_smem<32, 4, 4>());
 }
 
-bool mmq_tc8_supported(int64_t K, int64_t M, int64_t N) { return K % 256 == 0 && K >= 256 && M >= 1 && N > 4 && N <= 32; }
+bool mmq_tc8_supported(int64_t K, int64_t M, int64_t N) { return K % 256 == 0 && K >= 256 && M >= 1 && N > 4 && N <= 8192; }
 
 TcPlan mmq_tc8_plan(int64_t K, int64_t M, int64_t N, int sm_count) {
     TcPlan t;
@@ -351,14 +356,16 @@ TcPlan mmq_tc8_plan(int64_t K, int64_t M, int64_t N, int sm_count) {
     }
     t.n_split = best;
     t.sb_per_split = (t.nsb + best - 1) / best;
-    t.blob_bytes = (uint64_t)t.nsb * tc8_blob_bytes(t.npad);
-    t.partial_bytes = best > 1 ? (uint64_t)best * N * M * 4 : 0;
+    t.n_col_chunks = (int)((N + t.npad - 1) / t.npad);
+    t.blob_unit = (uint64_t)tc8_blob_bytes(t.npad);
+    t.blob_bytes = (uint64_t)t.n_col_chunks * t.nsb * t.blob_unit;
+    t.partial_bytes = best > 1 ? (uint64_t)best * std::min<int64_t>(N, t.npad) * M * 4 : 0;
     return t;
 }
 
 cudaError_t launch_act_pack_tc8(const ActLayout &a, const void *act, int npad, void *blobs, cudaStream_t st) {
     const char *ab = (const char *)act;
-    k_act_pack_q80<<<(unsigned)(a.K / 256), 256, 0, st>>>((const int8_t *)(ab + a.qs_off), (const float *)(ab + a.d_off), a.K, (int)a.N, npad,
+    k_act_pack_q80<<<dim3((unsigned)(a.K / 256), (unsigned)((a.N + npad - 1) / npad)), 256, 0, st>>>((const int8_t *)(ab + a.qs_off), (const float *)(ab + a.d_off), a.K, (int)a.N, npad,
                                                          (uint8_t *)blobs);
     return cudaGetLastError();
 }
@@ -373,32 +380,37 @@ cudaError_t launch_mmq_tc8(const TcPlan &t, const void *W, int64_t K, int64_t M,
     // described in 16-bit elements: a 272-byte box is 136 of them (the limit is 256 elements per dimension)
     cudaError_t e = tc_encode_2d(&map, W, (uint64_t)(K / 32 * 34), (uint64_t)M, tc8::ROW_CHUNK, tc8::ROWS, 2);
     if (e != cudaSuccess) return e;
-    Tc8Params p;
-    p.act = (const uint8_t *)blobs;
-    p.M = M;
-    p.N = (int)N;
-    p.npad = t.npad;
-    p.nst = t.nsb;
-    p.st_per_split = t.sb_per_split;
-    p.n_split = t.n_split;
-    p.err = err;
-    if (t.n_split > 1) {
-        p.out = (float *)partial;
-        p.ldy = M;
-    } else {
-        p.out = y;
-        p.ldy = ldy;
-    }
     dim3 grid((unsigned)((M + tc8::ROWS - 1) / tc8::ROWS), (unsigned)t.n_split);
-    if (t.npad == 16) e = launch_pdl(k_mmq_tc_q80<16, 4, 4>, grid, dim3(tc8::THREADS), tc8_smem<16, 4, 4>(), st, map, p);
-    else e = launch_pdl(k_mmq_tc_q80<32, 4, 4>, grid, dim3(tc8::THREADS), tc8_smem<32, 4, 4>(), st, map, p);
-    if (e != cudaSuccess) return e;
-    if (t.n_split > 1) {
-        if (ldy != M) return cudaErrorInvalidValue;
-        launch_mmq_reduce((const float *)partial, y, N * M, t.n_split, st);
-        e = cudaGetLastError();
+    for (int c = 0; c < t.n_col_chunks; c++) {   // one launch per chunk of npad columns
+        const int64_t n0 = (int64_t)c * t.npad, nc = std::min<int64_t>(t.npad, N - n0);
+        Tc8Params p;
+        p.act = (const uint8_t *)blobs + (size_t)c * t.nsb * t.blob_unit;
+        p.M = M;
+        p.N = (int)nc;
+        p.npad = t.npad;
+        p.nst = t.nsb;
+        p.st_per_split = t.sb_per_split;
+        p.n_split = t.n_split;
+        p.err = err;
+        float *yc = y + n0 * ldy;
+        if (t.n_split > 1) {
+            p.out = (float *)partial;
+            p.ldy = M;
+        } else {
+            p.out = yc;
+            p.ldy = ldy;
+        }
+        if (t.npad == 16) e = launch_pdl(k_mmq_tc_q80<16, 4, 4>, grid, dim3(tc8::THREADS), tc8_smem<16, 4, 4>(), st, map, p);
+        else e = launch_pdl(k_mmq_tc_q80<32, 4, 4>, grid, dim3(tc8::THREADS), tc8_smem<32, 4, 4>(), st, map, p);
+        if (e != cudaSuccess) return e;
+        if (t.n_split > 1) {
+            if (ldy != M) return cudaErrorInvalidValue;
+            launch_mmq_reduce((const float *)partial, yc, nc * M, t.n_split, st);
+            e = cudaGetLastError();
+            if (e != cudaSuccess) return e;
+        }
     }
-    return e;
+    return cudaSuccess;
 }
 
 }  // namespace tlb

@@ -48,7 +48,9 @@ void gemv_configure();  // sets the dynamic shared-memory attributes once per pr
 // Q4_K weights x 5..64 activation columns on tcgen05 (f16 operands built from the integer codes).
 struct TcPlan {
     int npad, nsb, n_split, sb_per_split;
-    uint64_t blob_bytes;     // packed activation blobs, all super-blocks
+    int n_col_chunks;        // activation columns are processed npad at a time: one launch per chunk
+    uint64_t blob_unit;      // bytes of one packed blob (one chunk of columns, one super-block / stage)
+    uint64_t blob_bytes;     // packed activation blobs: [chunk][super-block] x blob_unit
     uint64_t partial_bytes;  // scratch for the K-split partial sums (0 when not split)
 };
 bool mmq_tc_supported(uint32_t type, int64_t K, int64_t M, int64_t N);

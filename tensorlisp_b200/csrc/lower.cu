@@ -447,7 +447,7 @@ void lower_row_quant(L &l) {
     p.bsum_off = al.bsum_off;
     p.npad = t.op_params[1];
     p.blob_off = al.bytes;
-    p.blob_bytes = p.npad > 0 ? mmq_tc_plan(p.K, 128, p.N, 148).blob_bytes / (uint64_t)(p.K / 256) : 0;
+    p.blob_bytes = p.npad > 0 ? mmq_tc_plan(p.K, 128, p.N, 148).blob_unit : 0;
     p.eps = t.param_f32(15);
     p.lda = mode == RQ_F16 ? p.K : (p.N > 1 ? (int64_t)l.T(a).nb[1] / 4 : p.K);
     const int32_t b = t.src[1], w = t.src[3], sum = t.src[4];

@@ -59,6 +59,41 @@ def test_ffn_block_config2(oracle, T):
     m.close()
 
 
+def test_ffn_block_config2_prefill_512(oracle):
+    """The same block at 512 tokens (prefill-sized: the tensor-core mul_mat runs 64 columns per launch).
+    The CPU check covers a sample of rows of every projection, over all 512 tokens."""
+    d, f, T = 4096, 14336, 512
+    rng = np.random.default_rng(4)
+    wn = (1 + 0.1 * rng.standard_normal(d)).astype(np.float32)
+    from tensorlisp_b200.native import Native, quantize_rows
+    n = Native(0)
+    mats = []
+    for rows, cols in ((f, d), (f, d), (d, f)):
+        w = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float32)
+        mats.append(quantize_rows(n, Q4_K, w))
+    n.close()
+    x = rng.standard_normal((T, d)).astype(np.float32)
+    g = G.Graph()
+    tn = g.weight(G.F32, [d], "norm")
+    tg = g.weight(G.Q4_K, [d, f], "gate")
+    tu = g.weight(G.Q4_K, [d, f], "up")
+    td = g.weight(G.Q4_K, [f, d], "down")
+    tx = g.input(G.F32, [d, T], "x")
+    y = g.output(swiglu_ffn(g, tx, tn, tg, tu, td, 1e-5))
+    act = g.output([t for t in g.nodes if g.tensors[t].name == "ffn_act"][0])
+    m = Model(g, [wn] + mats)
+    got, got_act = m.run(x)
+    got, got_act = got.reshape(T, d), got_act.reshape(T, f)
+    h = oracle.rms_norm(x, 1e-5, wn)
+    rows = rng.choice(f, 48, replace=False)
+    a = oracle.mul_mat(Q4_K, mats[0][rows], d, h)
+    b = oracle.mul_mat(Q4_K, mats[1][rows], d, h)
+    close(got_act[:, rows], oracle.silu_mul(a, b), 1e-3)
+    rows = rng.choice(d, 48, replace=False)
+    close(got[:, rows], oracle.mul_mat(Q4_K, mats[2][rows], f, got_act), 1e-3)
+    m.close()
+
+
 class NoisyOracle:
     """The oracle with its mul_mat outputs perturbed by `eps` relative noise: measures how far the
     reference's own arithmetic moves under a summation-order-sized perturbation."""

@@ -36,7 +36,7 @@ def test_golden(ty, name, oracle):
 
 @pytest.mark.parametrize("ty,name", TYPES)
 @pytest.mark.parametrize("K,M", [(4096, 512), (14336, 64), (256, 96), (1024, 7)])
-@pytest.mark.parametrize("N", [1, 2, 3, 5, 8, 9, 16, 23, 32, 40])
+@pytest.mark.parametrize("N", [1, 2, 3, 5, 8, 9, 16, 23, 32, 40, 70, 129])
 def test_shapes(oracle, ty, name, K, M, N):
     rng = np.random.default_rng(K + M + N)
     W = (rng.standard_normal((M, K)) * 0.02).astype(np.float32)
