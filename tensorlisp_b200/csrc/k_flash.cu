@@ -1,0 +1,224 @@
+// FLASH_ATTN_EXT: dense attention softmax(scale * Q K^T + slope * mask) V for prefill and for caches that
+// are ordinary tensors (reference: crates/kernels/src/cuda/lower.rs:575-657 and native/fa.cu; semantics of
+// ggml_compute_forward_flash_attn_ext_f16, vendor/ggml/src/ggml-cpu/ops.cpp).
+//
+//   q f32 [D, nq, nh, nb]   k [D, nkv, nhkv, nb]   v [Dv, nkv, nhkv, nb] (f16 or f32)
+//   mask f16 [nkv, >= nq, ne32, ne33] or none      out f32 [Dv, nh, nq, nb]
+//
+// A CTA of four warps owns 64 consecutive queries of one (head, batch); each warp keeps 16 of them as
+// the M rows of mma.sync.m16n8k16 (f16 operands, f32 accumulate): the queries live in registers as A
+// fragments for the whole kernel, 64-key tiles of K and V are staged in shared memory as f16 (rows
+// padded by 16 bytes, so fragment loads and ldmatrix are conflict-free), S = Q K^T, online softmax in
+// base 2 on the accumulator fragments, P goes back in as the A operand of O += P V. Like the CPU
+// backend with an f16 cache, q is rounded to f16 before the dot products.
+#include <cuda_fp16.h>
+#include <math_constants.h>
+
+#include "kernels.h"
+#include "pdl.cuh"
+
+namespace tlb {
+
+namespace {
+
+constexpr int FA_WARPS = 4;
+constexpr int FA_QT = 16 * FA_WARPS;   // queries per CTA
+constexpr int FA_KT = 64;              // keys per tile
+
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldsm_x2_trans(uint32_t &r0, uint32_t &r1, uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
+
+// one row of K or V (D elements, f16 or f32 in global memory) -> f16 in shared memory, 8 elements per call
+template <bool F32>
+__device__ __forceinline__ void stage8(__half *dst, const uint8_t *src, bool live) {
+    uint4 out = make_uint4(0, 0, 0, 0);
+    if (live) {
+        if (F32) {
+            const float4 a = *reinterpret_cast<const float4 *>(src), b = *reinterpret_cast<const float4 *>(src + 16);
+            out = make_uint4(pack_h2(a.x, a.y), pack_h2(a.z, a.w), pack_h2(b.x, b.y), pack_h2(b.z, b.w));
+        } else {
+            out = *reinterpret_cast<const uint4 *>(src);
+        }
+    }
+    *reinterpret_cast<uint4 *>(dst) = out;
+}
+
+template <int D, bool KF32, bool VF32>
+__global__ void __launch_bounds__(FA_WARPS * 32) k_flash_attn(FlashArgs p, const uint8_t *__restrict__ q, const uint8_t *__restrict__ k,
+                                                              const uint8_t *__restrict__ v, const uint8_t *__restrict__ mask,
+                                                              float *__restrict__ out) {
+    griddep_launch();
+    griddep_wait();
+    constexpr int LDS = D + 8;                 // padded row length in halves
+    constexpr int KS = D / 16;                 // k-steps of Q K^T
+    constexpr int ND = D / 8;                  // n-tiles of P V
+    __shared__ __align__(16) __half Ks[FA_KT * LDS];
+    __shared__ __align__(16) __half Vs[FA_KT * LDS];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int q0 = blockIdx.x * FA_QT + warp * 16;   // first query of this warp
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int hk = h / (p.nh / p.nhkv);
+    const int qr0 = q0 + (lane >> 2), qr1 = qr0 + 8;  // the two query rows this lane holds pieces of
+    const int cq = (lane & 3) * 2;                    // column pair inside an 8-wide tile
+
+    // ---- queries -> A fragments (rounded to f16), kept for the whole kernel
+    uint32_t qa[KS][4];
+    {
+        const uint8_t *qb = q + (int64_t)h * p.q.nb[2] + (int64_t)b * p.q.nb[3];
+        const float *r0 = reinterpret_cast<const float *>(qb + (int64_t)min(qr0, p.nq - 1) * p.q.nb[1]);
+        const float *r1 = reinterpret_cast<const float *>(qb + (int64_t)min(qr1, p.nq - 1) * p.q.nb[1]);
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++) {
+            const int c = ks * 16 + cq;
+            qa[ks][0] = pack_h2(r0[c], r0[c + 1]);
+            qa[ks][1] = pack_h2(r1[c], r1[c + 1]);
+            qa[ks][2] = pack_h2(r0[c + 8], r0[c + 9]);
+            qa[ks][3] = pack_h2(r1[c + 8], r1[c + 9]);
+        }
+    }
+    float o[ND][4];
+#pragma unroll
+    for (int j = 0; j < ND; j++) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;   // running maxima (base-2 domain) and sums
+
+    const uint8_t *kb = k + (int64_t)hk * p.k.nb[2] + (int64_t)b * p.k.nb[3];
+    const uint8_t *vb = v + (int64_t)hk * p.v.nb[2] + (int64_t)b * p.v.nb[3];
+    const uint8_t *mb = mask ? mask + (int64_t)(h % p.m_ne2) * p.m.nb[2] + (int64_t)(b % p.m_ne3) * p.m.nb[3] : nullptr;
+    const __half *mr0 = mb ? reinterpret_cast<const __half *>(mb + (int64_t)min(qr0, p.nq - 1) * p.m.nb[1]) : nullptr;
+    const __half *mr1 = mb ? reinterpret_cast<const __half *>(mb + (int64_t)min(qr1, p.nq - 1) * p.m.nb[1]) : nullptr;
+    const float LOG2E = 1.4426950408889634f;
+    // ALiBi slope of this head (ggml_compute_forward_flash_attn_ext_f16: m0^(h+1) or m1^(2(h-n)+1)); 1 without a bias
+    float slope = 1.f;
+    if (p.max_bias > 0.f) slope = h < p.n_head_log2 ? powf(p.m0, (float)(h + 1)) : powf(p.m1, (float)(2 * (h - p.n_head_log2) + 1));
+
+    for (int kt = 0; kt < p.nkv; kt += FA_KT) {
+        __syncthreads();   // the previous tile has been consumed
+        for (int u = tid; u < FA_KT * (D / 8); u += FA_WARPS * 32) {
+            const int row = u / (D / 8), c8 = u % (D / 8);
+            const bool live = kt + row < p.nkv;
+            const int64_t key = min(kt + row, p.nkv - 1);
+            stage8<KF32>(Ks + row * LDS + c8 * 8, kb + key * p.k.nb[1] + c8 * 8 * (KF32 ? 4 : 2), live);
+            stage8<VF32>(Vs + row * LDS + c8 * 8, vb + key * p.v.nb[1] + c8 * 8 * (VF32 ? 4 : 2), live);
+        }
+        __syncthreads();
+
+        // ---- S = Q K^T for 64 keys: 8 n-tiles of 8 keys
+        float s[FA_KT / 8][4];
+#pragma unroll
+        for (int j = 0; j < FA_KT / 8; j++) {
+            s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+            const __half *krow = Ks + (j * 8 + (lane >> 2)) * LDS + cq;
+#pragma unroll
+            for (int ks = 0; ks < KS; ks++) {
+                const uint32_t b0 = *reinterpret_cast<const uint32_t *>(krow + ks * 16);
+                const uint32_t b1 = *reinterpret_cast<const uint32_t *>(krow + ks * 16 + 8);
+                mma16816(s[j], qa[ks], b0, b1);
+            }
+        }
+        // ---- scale, soft cap, mask; scores move to the base-2 domain
+        float mx0 = m0, mx1 = m1;
+#pragma unroll
+        for (int j = 0; j < FA_KT / 8; j++) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int key = kt + j * 8 + cq + (e & 1);
+                float x = s[j][e] * p.scale;
+                if (p.softcap != 0.f) x = p.softcap * tanhf(x);
+                const __half *mr = (e & 2) ? mr1 : mr0;
+                if (mr && key < p.nkv) x += slope * __half2float(mr[key]);
+                x = key < p.nkv ? x * LOG2E : -CUDART_INF_F;
+                s[j][e] = x;
+                if (e & 2) mx1 = fmaxf(mx1, x);
+                else mx0 = fmaxf(mx0, x);
+            }
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        // a row that has seen only masked keys keeps a finite reference so that exp2(-inf - ref) = 0
+        const float ref0 = mx0 == -CUDART_INF_F ? 0.f : mx0, ref1 = mx1 == -CUDART_INF_F ? 0.f : mx1;
+        const float a0 = exp2f(m0 - ref0), a1 = exp2f(m1 - ref1);   // m = -inf gives 0: nothing accumulated yet
+        m0 = mx0;
+        m1 = mx1;
+        l0 *= a0;
+        l1 *= a1;
+#pragma unroll
+        for (int j = 0; j < ND; j++) {
+            o[j][0] *= a0; o[j][1] *= a0;
+            o[j][2] *= a1; o[j][3] *= a1;
+        }
+        // ---- P = exp2(S - m) as A fragments; O += P V
+        float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+        for (int t = 0; t < FA_KT / 16; t++) {
+            uint32_t pa[4];
+            float e00 = exp2f(s[2 * t][0] - ref0), e01 = exp2f(s[2 * t][1] - ref0);
+            float e10 = exp2f(s[2 * t][2] - ref1), e11 = exp2f(s[2 * t][3] - ref1);
+            float f00 = exp2f(s[2 * t + 1][0] - ref0), f01 = exp2f(s[2 * t + 1][1] - ref0);
+            float f10 = exp2f(s[2 * t + 1][2] - ref1), f11 = exp2f(s[2 * t + 1][3] - ref1);
+            ps0 += e00 + e01 + f00 + f01;
+            ps1 += e10 + e11 + f10 + f11;
+            pa[0] = pack_h2(e00, e01);
+            pa[1] = pack_h2(e10, e11);
+            pa[2] = pack_h2(f00, f01);
+            pa[3] = pack_h2(f10, f11);
+            const uint32_t vaddr = (uint32_t)__cvta_generic_to_shared(Vs + (t * 16 + (lane & 15)) * LDS);
+#pragma unroll
+            for (int j = 0; j < ND; j++) {
+                uint32_t b0, b1;
+                ldsm_x2_trans(b0, b1, vaddr + j * 16);
+                mma16816(o[j], pa, b0, b1);
+            }
+        }
+        l0 += ps0;
+        l1 += ps1;
+    }
+    // ---- row sums across the quad, normalise, store [Dv, nh, nq, nb]
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
+    if (qr0 < p.nq) {
+        float *d = out + (((int64_t)b * p.nq + qr0) * p.nh + h) * D;
+#pragma unroll
+        for (int j = 0; j < ND; j++) *reinterpret_cast<float2 *>(d + j * 8 + cq) = make_float2(o[j][0] * i0, o[j][1] * i0);
+    }
+    if (qr1 < p.nq) {
+        float *d = out + (((int64_t)b * p.nq + qr1) * p.nh + h) * D;
+#pragma unroll
+        for (int j = 0; j < ND; j++) *reinterpret_cast<float2 *>(d + j * 8 + cq) = make_float2(o[j][2] * i1, o[j][3] * i1);
+    }
+}
+
+}  // namespace
+
+bool flash_supported(int64_t d, int64_t dv) { return d == dv && (d == 64 || d == 128); }
+
+template <int D>
+static cudaError_t launch_fa(const FlashArgs &p, const void *q, const void *k, const void *v, const void *mask, float *out, cudaStream_t st) {
+    const dim3 grid((unsigned)((p.nq + FA_QT - 1) / FA_QT), (unsigned)p.nh, (unsigned)p.nb), block(FA_WARPS * 32);
+    const uint8_t *q8 = (const uint8_t *)q, *k8 = (const uint8_t *)k, *v8 = (const uint8_t *)v, *m8 = (const uint8_t *)mask;
+    if (p.k_f32 && p.v_f32) return launch_pdl(k_flash_attn<D, true, true>, grid, block, 0, st, p, q8, k8, v8, m8, out);
+    if (p.k_f32) return launch_pdl(k_flash_attn<D, true, false>, grid, block, 0, st, p, q8, k8, v8, m8, out);
+    if (p.v_f32) return launch_pdl(k_flash_attn<D, false, true>, grid, block, 0, st, p, q8, k8, v8, m8, out);
+    return launch_pdl(k_flash_attn<D, false, false>, grid, block, 0, st, p, q8, k8, v8, m8, out);
+}
+
+cudaError_t launch_flash_attn(const FlashArgs &p, const void *q, const void *k, const void *v, const void *mask, float *out, cudaStream_t st) {
+    if (p.nq == 0 || p.nh == 0 || p.nb == 0) return cudaSuccess;
+    return p.d == 64 ? launch_fa<64>(p, q, k, v, mask, out, st) : launch_fa<128>(p, q, k, v, mask, out, st);
+}
+
+}  // namespace tlb

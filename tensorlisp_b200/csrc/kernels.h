@@ -137,6 +137,17 @@ cudaError_t launch_repeat(const SimpleArgs &p, const void *a, void *d, cudaStrea
 cudaError_t launch_sum_rows(const SimpleArgs &p, const void *a, void *d, cudaStream_t st);  // i0: 1 = mean
 cudaError_t launch_arange(const SimpleArgs &p, void *d, cudaStream_t st);
 
+// ---------------------------------------------------------------- k_flash.cu
+// FLASH_ATTN_EXT (dense): q f32 [d, nq, nh, nb], k / v f16 or f32 [d, nkv, nhkv, nb], optional f16 mask
+struct FlashArgs {
+    TView q, k, v, m;
+    int nq, nkv, nh, nhkv, nb, d, m_ne2, m_ne3, n_head_log2;
+    float scale, softcap, max_bias, m0, m1;   // scale already divided by softcap when that is set
+    bool k_f32, v_f32;
+};
+bool flash_supported(int64_t d, int64_t dv);
+cudaError_t launch_flash_attn(const FlashArgs &p, const void *q, const void *k, const void *v, const void *mask, float *out, cudaStream_t st);
+
 // ---------------------------------------------------------------- k_attn.cu
 // KV pools are private to the executor (only the two paged nodes touch them): f16
 // [block][kv_head][slot][head_size] for both keys and values.

@@ -554,6 +554,61 @@ void lower_custom(L &l) {
     }
 }
 
+// ---- FLASH_ATTN_EXT (lower.rs:575-657): dense attention, result [dv, heads, queries, batch] f32
+void lower_flash(L &l) {
+    const Tensor &t = l.t();
+    const int32_t q = l.src(0), k = l.src(1), v = l.src(2);
+    const int32_t m = t.src[3];
+    if (t.src[4] >= 0) unsupported(t, "attention sinks are not supported");
+    const Tensor &tq = l.T(q), &tk = l.T(k), &tv = l.T(v);
+    auto f16_or_f32 = [](const Tensor &x) { return (x.ty == TLB_TYPE_F16 && x.nb[0] == 2) || (x.ty == TLB_TYPE_F32 && x.nb[0] == 4); };
+    if (tq.ty != TLB_TYPE_F32 || tq.nb[0] != 4 || t.ty != TLB_TYPE_F32) unsupported(t, "queries and result must be f32");
+    if (!f16_or_f32(tk) || !f16_or_f32(tv)) unsupported(t, "keys and values must be dense f16 or f32 rows");
+    if (!flash_supported(tq.ne[0], tv.ne[0]) || tk.ne[0] != tq.ne[0]) unsupported(t, "head size must be 64 or 128, the same for keys and values");
+    if (tk.ne[1] != tv.ne[1] || tk.ne[2] != tv.ne[2] || tk.ne[2] == 0 || tq.ne[2] % tk.ne[2] != 0 || tk.ne[3] != tq.ne[3] || tv.ne[3] != tq.ne[3])
+        unsupported(t, "inconsistent shapes");
+    if (tk.nb[1] % 16 || tv.nb[1] % 16 || tk.nb[2] % 16 || tv.nb[2] % 16 || tk.nb[3] % 16 || tv.nb[3] % 16 || tq.nb[1] % 8 || tq.nb[2] % 8 || tq.nb[3] % 8)
+        unsupported(t, "rows must start on 16-byte boundaries");
+    if (t.ne[0] != tv.ne[0] || t.ne[1] != tq.ne[2] || t.ne[2] != tq.ne[1] || t.ne[3] != tq.ne[3] || !t.is_contiguous())
+        unsupported(t, "the result must be a contiguous [dv, heads, queries, batch] tensor");
+    FlashArgs p{};
+    p.q = view_of(tq);
+    p.k = view_of(tk);
+    p.v = view_of(tv);
+    p.d = (int)tq.ne[0];
+    p.nq = (int)tq.ne[1];
+    p.nh = (int)tq.ne[2];
+    p.nb = (int)tq.ne[3];
+    p.nkv = (int)tk.ne[1];
+    p.nhkv = (int)tk.ne[2];
+    p.k_f32 = tk.ty == TLB_TYPE_F32;
+    p.v_f32 = tv.ty == TLB_TYPE_F32;
+    p.scale = t.param_f32(0);
+    p.max_bias = t.param_f32(1);
+    p.softcap = t.param_f32(2);
+    if (p.softcap != 0.f) p.scale /= p.softcap;
+    p.n_head_log2 = 1;
+    while (p.n_head_log2 * 2 <= p.nh) p.n_head_log2 *= 2;
+    p.m0 = powf(2.0f, -p.max_bias / (float)p.n_head_log2);
+    p.m1 = powf(2.0f, -(p.max_bias / 2.0f) / (float)p.n_head_log2);
+    p.m_ne2 = p.m_ne3 = 1;
+    Place pm;
+    if (m >= 0) {
+        const Tensor &tm = l.T(m);
+        if (tm.ty != TLB_TYPE_F16 || tm.nb[0] != 2 || tm.ne[0] < tk.ne[1] || tm.ne[1] < tq.ne[1] || tm.ne[2] < 1 || tm.ne[3] < 1)
+            unsupported(t, "the mask must be f16 [keys, >= queries, ...]");
+        p.m = view_of(tm);
+        p.m_ne2 = (int)tm.ne[2];
+        p.m_ne3 = (int)tm.ne[3];
+        pm = l.place(m);
+    }
+    const bool has_mask = m >= 0;
+    const Place pq = l.place(q), pk = l.place(k), pv = l.place(v), pd = l.place(l.id);
+    l.push([=](const RunCtx &r) {
+        return launch_flash_attn(p, r.at(pq), r.at(pk), r.at(pv), has_mask ? r.at(pm) : nullptr, (float *)r.at(pd), r.stream);
+    });
+}
+
 // ---- ALLREDUCE (tensor parallelism; no reference counterpart): the node is a view of its source
 void lower_allreduce(L &l) {
     const Tensor &t = l.t();
@@ -614,6 +669,7 @@ void lower_node(const LowerCtx &c, int32_t id, int pos, std::vector<Dispatch> &o
     if (op == "CONCAT" || op == "REPEAT" || op == "SUM_ROWS" || op == "MEAN" || op == "ARANGE") return lower_simple(l);
     if (op == "MUL_MAT") return lower_mul_mat(l);
     if (op == "CUSTOM") return lower_custom(l);
+    if (op == "FLASH_ATTN_EXT") return lower_flash(l);
     if (op == "ALLREDUCE") return lower_allreduce(l);
     unsupported(t, "op not implemented in the native CUDA backend");
 }

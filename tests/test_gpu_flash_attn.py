@@ -1,0 +1,127 @@
+"""FLASH_ATTN_EXT (dense attention, reference lower.rs:575-657) against (a) the closed form
+softmax(scale q k^T + slope mask) v in f64 on the same f16-rounded K/V, and (b) where the reference's
+own ggml build travels with the repository, ggml's CPU flash_attn_ext with f32 K/V (the f32-accumulator
+mode). Ragged query / key counts, GQA, a causal f16 mask with -inf, a per-head mask, soft cap, ALiBi."""
+import numpy as np
+import pytest
+
+from helpers import Model, close
+from tensorlisp_b200 import graph as G
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+
+
+def closed_form(q, k, v, mask, scale, softcap=0.0, max_bias=0.0):
+    """q [nb, nh, nq, d], k/v [nb, nhkv, nkv, d], mask [nb or 1, nh or 1, nq_pad, nkv] -> [nb, nq, nh, d]"""
+    nb, nh, nq, d = q.shape
+    nhkv = k.shape[1]
+    out = np.zeros((nb, nq, nh, d))
+    n2 = 1
+    while n2 * 2 <= nh:
+        n2 *= 2
+    m0, m1 = 2.0 ** (-max_bias / n2), 2.0 ** (-(max_bias / 2) / n2)
+    for b in range(nb):
+        for h in range(nh):
+            hk = h // (nh // nhkv)
+            s = q[b, h].astype(np.float64) @ k[b, hk].astype(np.float64).T * scale
+            if softcap:
+                s = softcap * np.tanh(s / softcap)
+            if mask is not None:
+                slope = 1.0 if max_bias <= 0 else (m0 ** (h + 1) if h < n2 else m1 ** (2 * (h - n2) + 1))
+                s = s + slope * mask[b % mask.shape[0], h % mask.shape[1], :nq].astype(np.float64)
+            s = s - s.max(axis=1, keepdims=True)
+            p = np.exp(s)
+            out[b, :, h] = (p / p.sum(axis=1, keepdims=True)) @ v[b, hk].astype(np.float64)
+    return out.astype(np.float32)
+
+
+def run_gpu(q, k, v, mask, scale, softcap, max_bias, kv_ty):
+    nb, nh, nq, d = q.shape
+    nhkv, nkv = k.shape[1], k.shape[2]
+    g = G.Graph()
+    tq = g.input(G.F32, [d, nq, nh, nb], "q")
+    tk = g.input(kv_ty, [d, nkv, nhkv, nb], "k")
+    tv = g.input(kv_ty, [d, nkv, nhkv, nb], "v")
+    ins = [q, k, v]
+    tm = None
+    if mask is not None:
+        tm = g.input(G.F16, [nkv, mask.shape[2], mask.shape[1], mask.shape[0]], "mask")
+        ins.append(mask)
+    y = g.output(g.flash_attn_ext(tq, tk, tv, tm, scale, max_bias, softcap, "attn"))
+    m = Model(g)
+    (got,) = m.run(*ins)
+    m.close()
+    return got.reshape(nb, nq, nh, d)
+
+
+CASES = [
+    # d, nq, nkv, nh, nhkv, nb, mask kind, softcap, max_bias, kv type
+    (128, 70, 200, 8, 2, 2, "causal", 0.0, 0.0, G.F16),
+    (128, 1, 333, 4, 4, 1, None, 0.0, 0.0, G.F16),
+    (64, 130, 130, 4, 1, 1, "causal", 0.0, 0.0, G.F32),
+    (128, 33, 96, 8, 8, 1, "per_head", 30.0, 0.0, G.F16),
+    (64, 17, 64, 6, 2, 2, "causal", 0.0, 8.0, G.F16),
+]
+
+
+def make_case(case):
+    d, nq, nkv, nh, nhkv, nb, mk, softcap, max_bias, kv_ty = case
+    rng = np.random.default_rng(d + nq + nkv)
+    q = rng.standard_normal((nb, nh, nq, d)).astype(np.float32)
+    kdt = np.float16 if kv_ty == G.F16 else np.float32
+    k = rng.standard_normal((nb, nhkv, nkv, d)).astype(kdt)
+    v = rng.standard_normal((nb, nhkv, nkv, d)).astype(kdt)
+    mask = None
+    nq_pad = (nq + 31) // 32 * 32
+    if mk == "causal":   # query i sees keys 0 .. nkv - nq + i
+        mask = np.full((1, 1, nq_pad, nkv), -np.inf, np.float16)
+        for i in range(nq):
+            mask[0, 0, i, :nkv - nq + i + 1] = 0
+    elif mk == "per_head":
+        mask = (rng.standard_normal((nb, nh, nq_pad, nkv)) * 2).astype(np.float16)
+        mask[:, :, :, ::7] = -np.inf
+    return q, k, v, mask, 1.0 / np.sqrt(d), softcap, max_bias, kv_ty
+
+
+@pytest.mark.parametrize("case", CASES, ids=[str(c[:6]) for c in CASES])
+def test_flash_attn_closed_form(case):
+    q, k, v, mask, scale, softcap, max_bias, kv_ty = make_case(case)
+    got = run_gpu(q, k, v, mask, scale, softcap, max_bias, kv_ty)
+    # the kernel rounds q to f16, as the CPU backend does with an f16 cache
+    want = closed_form(q.astype(np.float16), k, v, mask, scale, softcap, max_bias)
+    close(got, want, TOL)
+
+
+def test_flash_attn_against_ggml(ref):
+    """The reference's own ggml (f32 K/V so that it accumulates in f32; GGML_PREC_F32)."""
+    from oracle.bindings import RefGraph, F32 as RF32, F16 as RF16
+    case = CASES[0]
+    q, k, v, mask, scale, softcap, max_bias, kv_ty = make_case(case)
+    nb, nh, nq, d = q.shape
+    nhkv, nkv = k.shape[1], k.shape[2]
+    g = RefGraph(ref, 256 << 20, 8)
+    tq = g.tensor(RF32, [d, nq, nh, nb], "q", q)
+    tk = g.tensor(RF32, [d, nkv, nhkv, nb], "k", k.astype(np.float32))
+    tv = g.tensor(RF32, [d, nkv, nhkv, nb], "v", v.astype(np.float32))
+    tm = g.tensor(RF16, [nkv, mask.shape[2], 1, 1], "m", mask)
+    o = g.op("flash_attn_ext", [tq, tk, tv, tm], ints=[10], floats=[scale, 0.0, 0.0])
+    g.compute([o])
+    want = g.read(o).reshape(nb, nq, nh, d)
+    g.close()
+    got = run_gpu(q, k, v, mask, scale, softcap, max_bias, kv_ty)
+    close(got, want, TOL)
+
+
+def test_sinks_are_reported_by_name():
+    from tensorlisp_b200._lib import TlbError
+    g = G.Graph()
+    tq = g.input(G.F32, [128, 4, 2, 1], "q")
+    tk = g.input(G.F16, [128, 8, 2, 1], "k")
+    tv = g.input(G.F16, [128, 8, 2, 1], "v")
+    y = g.flash_attn_ext(tq, tk, tv, None, 0.1, name="attn")
+    g.tensors[y].src[4] = g.input(G.F32, [2], "sinks")
+    g.output(y)
+    with pytest.raises(TlbError) as e:
+        Model(g)
+    assert "FLASH_ATTN_EXT" in str(e.value) and "not implemented" in str(e.value)
