@@ -198,6 +198,17 @@ tlb_status tlb_paged_attention_static(tlb_device *dev, const void *q, const void
 tlb_status tlb_comm_unique_id(void *out128);
 tlb_status tlb_comm_init(tlb_device *dev, int n_ranks, int rank, const void *id128);
 tlb_status tlb_comm_destroy(tlb_device *dev);
+/* One-shot all-reduce over NVLink peer memory for messages up to 1 MiB (the activations of a decode
+ * step), used by "ALLREDUCE" in place of NCCL once set up: every rank calls export (allocates its
+ * exchange buffer, returns a 64-byte CUDA IPC handle), the host gathers the handles of all ranks in
+ * rank order (n_ranks x 64 bytes) and every rank calls import. Up to 8 ranks of one box. The kernel's
+ * waits are bounded; a rank that never arrives makes tlb_program_run fail instead of hanging.
+ * TLB_NO_P2P_ALLREDUCE=1 keeps NCCL. */
+tlb_status tlb_comm_p2p_export(tlb_device *dev, void *handle64);
+tlb_status tlb_comm_p2p_import(tlb_device *dev, const void *handles);
+/* The same protocol with n_ranks emulated ranks on ONE device in one cooperative launch (test hook):
+ * in/out are n_ranks x n floats on the host; `calls` all-reduces in a row, call k on inputs x (k+1). */
+tlb_status tlb_comm_p2p_selftest(tlb_device *dev, int n_ranks, int n, int calls, const float *in, float *out);
 
 #ifdef __cplusplus
 }

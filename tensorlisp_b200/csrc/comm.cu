@@ -8,7 +8,9 @@
 // loaded when it uses torch.distributed), so the library loads on machines without NCCL.
 #include <dlfcn.h>
 
+#include <algorithm>
 #include <mutex>
+#include <vector>
 
 #include "tlb_internal.h"
 
@@ -51,14 +53,117 @@ static NcclApi &nccl() {
     return api;
 }
 
+// ---------------------------------------------------------------- one-shot all-reduce over peer memory
+// For the 512 KB activations of a decode step NCCL's ring costs 20+ us per call, 64 calls per step. Here
+// every rank PUSHES its data into a slot of every peer's exchange buffer with plain stores over NVLink
+// (so remote data always lands in local memory first), raises a per-CTA flag there, waits for the
+// flags of all ranks in its own buffer (bounded), and adds the slots up in rank order - the same order
+// on every rank, so all ranks end with bit-identical sums. CTA c of every rank owns chunk c of the
+// data, so no grid-wide barrier is needed. Sequence numbers only grow; slots alternate by parity
+// (a rank can be one call ahead of a peer, never two: finishing call s needs every peer's flags of call s).
+constexpr int AR_MAX_RANKS = 8;
+constexpr int AR_CTAS = 64;
+constexpr int AR_THREADS = 256;
+constexpr size_t AR_SLOT_BYTES = 1u << 20;                     // largest message
+constexpr size_t AR_FLAG_OFF = 0;                              // u32 [2][AR_MAX_RANKS][AR_CTAS]
+constexpr size_t AR_SEQ_OFF = 4096;                            // u32 [AR_CTAS], local only: calls seen by CTA c
+constexpr size_t AR_DATA_OFF = 8192;                           // [2][AR_MAX_RANKS][AR_SLOT_BYTES]
+constexpr size_t AR_BUF_BYTES = AR_DATA_OFF + 2 * AR_MAX_RANKS * AR_SLOT_BYTES;
+constexpr uint32_t AR_SPIN_LIMIT = 1u << 22;   // probes of a local flag, a few seconds
+
+struct ArRank {
+    float *data;                 // n floats, reduced in place
+    char *peer[AR_MAX_RANKS];    // exchange buffers of all ranks as mapped into this rank (own one included)
+    int rank;
+    int *err;
+};
+
+__device__ __forceinline__ void ar_body(const ArRank &a, int n, int n_ranks, int c, int n_ctas) {
+    __shared__ int s_fail;
+    const int tid = threadIdx.x;
+    char *local = a.peer[a.rank];
+    uint32_t *seqs = reinterpret_cast<uint32_t *>(local + AR_SEQ_OFF);
+    const uint32_t seq = seqs[c] + 1;
+    const uint32_t par = seq & 1;
+    const int per = ((n / 4 + n_ctas - 1) / n_ctas);          // float4 per CTA
+    const int v0 = c * per, v1 = min(n / 4, v0 + per);
+    if (tid == 0) s_fail = 0;
+    // ---- push my chunk into slot [par][my rank] of every rank
+    const float4 *src = reinterpret_cast<const float4 *>(a.data);
+    for (int p = 0; p < n_ranks; p++) {
+        float4 *dst = reinterpret_cast<float4 *>(a.peer[p] + AR_DATA_OFF + ((size_t)par * AR_MAX_RANKS + a.rank) * AR_SLOT_BYTES);
+        for (int i = v0 + tid; i < v1; i += AR_THREADS) dst[i] = src[i];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < n_ranks) {
+        uint32_t *flag = reinterpret_cast<uint32_t *>(a.peer[tid] + AR_FLAG_OFF) + ((size_t)par * AR_MAX_RANKS + a.rank) * AR_CTAS + c;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(seq) : "memory");
+        // ---- wait (bounded) for chunk c of rank `tid` to have landed here
+        const uint32_t *mine = reinterpret_cast<const uint32_t *>(local + AR_FLAG_OFF) + ((size_t)par * AR_MAX_RANKS + tid) * AR_CTAS + c;
+        bool ok = false;
+        for (uint32_t it = 0; it < AR_SPIN_LIMIT; it++) {
+            uint32_t f;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(f) : "l"(mine) : "memory");
+            if ((int32_t)(f - seq) >= 0) { ok = true; break; }
+        }
+        if (!ok) s_fail = 1;
+    }
+    __syncthreads();
+    if (s_fail) {
+        if (tid == 0) {
+            atomicExch(a.err, 3);
+            seqs[c] = seq;
+        }
+        return;
+    }
+    // ---- add the slots in rank order (L2 loads: L1 may still hold this slot's lines of two calls ago)
+    const char *slots = local + AR_DATA_OFF + (size_t)par * AR_MAX_RANKS * AR_SLOT_BYTES;
+    float4 *out = reinterpret_cast<float4 *>(a.data);
+    for (int i = v0 + tid; i < v1; i += AR_THREADS) {
+        float4 acc = __ldcg(reinterpret_cast<const float4 *>(slots) + i);
+        for (int p = 1; p < n_ranks; p++) {
+            const float4 x = __ldcg(reinterpret_cast<const float4 *>(slots + (size_t)p * AR_SLOT_BYTES) + i);
+            acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+        }
+        out[i] = acc;
+    }
+    if (tid == 0) seqs[c] = seq;
+}
+
+__global__ void __launch_bounds__(AR_THREADS) k_allreduce_oneshot(ArRank a, int n, int n_ranks) {
+    ar_body(a, n, n_ranks, blockIdx.x, gridDim.x);
+}
+// All ranks in ONE cooperative launch on one GPU (blockIdx.y = rank): the single-GPU test of the protocol.
+// Ranks that wait on one another must not be separate launches on one device.
+struct ArAll { ArRank r[AR_MAX_RANKS]; };
+__global__ void __launch_bounds__(AR_THREADS) k_allreduce_emulated(ArAll all, int n, int n_ranks) {
+    ar_body(all.r[blockIdx.y], n, n_ranks, blockIdx.x, gridDim.x);
+}
+
+static int ar_grid(size_t n) { return (int)std::max<size_t>(1, std::min<size_t>(AR_CTAS, (n / 4 + 511) / 512)); }
+
 struct Comm {
     ncclComm_t comm = nullptr;
     int n_ranks = 1, rank = 0;
+    char *xbuf = nullptr;                    // this rank's exchange buffer (cudaMalloc)
+    char *peer[AR_MAX_RANKS] = {nullptr};    // all ranks' buffers as mapped here; peer[rank] == xbuf
+    bool p2p = false;
 };
 
-cudaError_t comm_allreduce_f32(tlb_device *dev, float *buf, size_t n, cudaStream_t st) {
+cudaError_t comm_allreduce_f32(tlb_device *dev, float *buf, size_t n, cudaStream_t st, int *err) {
     if (!dev->comm || dev->comm->n_ranks == 1) return cudaSuccess;
-    const int r = nccl().AllReduce(buf, buf, n, ncclFloat32, ncclSum, dev->comm->comm, st);
+    Comm *c = dev->comm;
+    if (c->p2p && n % 4 == 0 && n * 4 <= AR_SLOT_BYTES && ((uintptr_t)buf & 15) == 0 && err) {
+        ArRank a{};
+        a.data = buf;
+        a.rank = c->rank;
+        a.err = err;
+        for (int p = 0; p < c->n_ranks; p++) a.peer[p] = c->peer[p];
+        k_allreduce_oneshot<<<ar_grid(n), AR_THREADS, 0, st>>>(a, (int)n, c->n_ranks);
+        return cudaGetLastError();
+    }
+    const int r = nccl().AllReduce(buf, buf, n, ncclFloat32, ncclSum, c->comm, st);
     return r == ncclSuccess ? cudaSuccess : cudaErrorUnknown;
 }
 int comm_ranks(tlb_device *dev) { return dev->comm ? dev->comm->n_ranks : 1; }
@@ -109,8 +214,112 @@ tlb_status tlb_comm_init(tlb_device *dev, int n_ranks, int rank, const void *id1
     return TLB_OK;
 }
 
+tlb_status tlb_comm_p2p_export(tlb_device *dev, void *handle64) {
+    if (!dev || !dev->comm || !handle64) return fail(TLB_INVALID, "tlb_comm_p2p_export: needs a device with a communicator");
+    Comm *c = dev->comm;
+    if (c->n_ranks > AR_MAX_RANKS) return fail(TLB_INVALID, "the peer-memory all-reduce takes at most 8 ranks");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    cudaSetDevice(dev->ordinal);
+    if (!c->xbuf) {
+        if (cudaMalloc(&c->xbuf, AR_BUF_BYTES) != cudaSuccess) {
+            cudaGetLastError();
+            return fail(TLB_ALLOC, "exchange buffer allocation failed");
+        }
+        cudaMemset(c->xbuf, 0, AR_BUF_BYTES);
+        cudaDeviceSynchronize();
+    }
+    cudaIpcMemHandle_t h;
+    const cudaError_t e = cudaIpcGetMemHandle(&h, c->xbuf);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(TLB_EXECUTION, std::string("cudaIpcGetMemHandle: ") + cudaGetErrorString(e));
+    }
+    std::memcpy(handle64, &h, 64);
+    return TLB_OK;
+}
+
+tlb_status tlb_comm_p2p_import(tlb_device *dev, const void *handles) {
+    if (!dev || !dev->comm || !handles) return fail(TLB_INVALID, "tlb_comm_p2p_import: needs a device with a communicator");
+    Comm *c = dev->comm;
+    if (!c->xbuf) return fail(TLB_INVALID, "call tlb_comm_p2p_export first");
+    cudaSetDevice(dev->ordinal);
+    for (int p = 0; p < c->n_ranks; p++) {
+        if (p == c->rank) {
+            c->peer[p] = c->xbuf;
+            continue;
+        }
+        cudaIpcMemHandle_t h;
+        std::memcpy(&h, (const char *)handles + (size_t)p * 64, 64);
+        void *ptr = nullptr;
+        const cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return fail(TLB_EXECUTION, "cudaIpcOpenMemHandle (rank " + std::to_string(p) + "): " + cudaGetErrorString(e));
+        }
+        c->peer[p] = (char *)ptr;
+    }
+    const char *off = getenv("TLB_NO_P2P_ALLREDUCE");
+    c->p2p = !(off && off[0] == '1');
+    return TLB_OK;
+}
+
+// Single-GPU check of the all-reduce protocol: `n_ranks` emulated ranks (their buffers all on this
+// device) run as ONE cooperative launch; in[r] / out[r] are n floats per rank on the host.
+tlb_status tlb_comm_p2p_selftest(tlb_device *dev, int n_ranks, int n, int calls, const float *in, float *out) {
+    if (!dev || n_ranks < 1 || n_ranks > AR_MAX_RANKS || n < 4 || n % 4 || (size_t)n * 4 > AR_SLOT_BYTES || calls < 1 || !in || !out)
+        return fail(TLB_INVALID, "tlb_comm_p2p_selftest: bad arguments");
+    cudaSetDevice(dev->ordinal);
+    ArAll all{};
+    char *bufs[AR_MAX_RANKS] = {nullptr};
+    float *data[AR_MAX_RANKS] = {nullptr};
+    int *err = nullptr;
+    cudaError_t e = cudaMalloc(&err, 256);
+    if (e == cudaSuccess) e = cudaMemset(err, 0, 256);
+    for (int r = 0; r < n_ranks && e == cudaSuccess; r++) {
+        e = cudaMalloc(&bufs[r], AR_BUF_BYTES);
+        if (e == cudaSuccess) e = cudaMemset(bufs[r], 0, AR_BUF_BYTES);
+        if (e == cudaSuccess) e = cudaMalloc(&data[r], (size_t)n * 4);
+    }
+    for (int r = 0; r < n_ranks && e == cudaSuccess; r++) {
+        all.r[r].data = data[r];
+        all.r[r].rank = r;
+        all.r[r].err = err;
+        for (int p = 0; p < n_ranks; p++) all.r[r].peer[p] = bufs[p];
+    }
+    int flag = 0;
+    for (int call = 0; call < calls && e == cudaSuccess; call++) {
+        // every call reduces fresh inputs scaled by (call + 1), so a stale slot would show
+        for (int r = 0; r < n_ranks && e == cudaSuccess; r++) {
+            std::vector<float> h((size_t)n);
+            for (int i = 0; i < n; i++) h[i] = in[(size_t)r * n + i] * (float)(call + 1);
+            e = cudaMemcpy(data[r], h.data(), (size_t)n * 4, cudaMemcpyHostToDevice);
+        }
+        if (e != cudaSuccess) break;
+        void *args[] = {&all, &n, &n_ranks};
+        e = cudaLaunchCooperativeKernel((void *)k_allreduce_emulated, dim3(ar_grid((size_t)n), n_ranks), dim3(AR_THREADS), args, 0, dev->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(dev->stream);
+    }
+    if (e == cudaSuccess) e = cudaMemcpy(&flag, err, 4, cudaMemcpyDeviceToHost);
+    for (int r = 0; r < n_ranks && e == cudaSuccess; r++) e = cudaMemcpy(out + (size_t)r * n, data[r], (size_t)n * 4, cudaMemcpyDeviceToHost);
+    for (int r = 0; r < n_ranks; r++) {
+        if (bufs[r]) cudaFree(bufs[r]);
+        if (data[r]) cudaFree(data[r]);
+    }
+    if (err) cudaFree(err);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(TLB_EXECUTION, std::string("all-reduce self test: ") + cudaGetErrorString(e));
+    }
+    if (flag) return fail(TLB_EXECUTION, "all-reduce self test: a rank gave up waiting for its peers");
+    return TLB_OK;
+}
+
 tlb_status tlb_comm_destroy(tlb_device *dev) {
     if (!dev || !dev->comm) return TLB_OK;
+    cudaSetDevice(dev->ordinal);
+    for (int p = 0; p < dev->comm->n_ranks && p < AR_MAX_RANKS; p++)
+        if (dev->comm->peer[p] && p != dev->comm->rank) cudaIpcCloseMemHandle(dev->comm->peer[p]);
+    if (dev->comm->xbuf) cudaFree(dev->comm->xbuf);
     if (dev->comm->comm) nccl().CommDestroy(dev->comm->comm);
     delete dev->comm;
     dev->comm = nullptr;

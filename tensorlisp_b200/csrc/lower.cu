@@ -618,7 +618,7 @@ void lower_allreduce(L &l) {
     const Place pd = l.place(l.id);
     const size_t n = (size_t)t.nelements();
     tlb_device *dev = l.c.dev;
-    l.push([=](const RunCtx &r) { return comm_allreduce_f32(dev, (float *)r.at(pd), n, r.stream); });
+    l.push([=](const RunCtx &r) { return comm_allreduce_f32(dev, (float *)r.at(pd), n, r.stream, r.err); });
 }
 
 }  // namespace

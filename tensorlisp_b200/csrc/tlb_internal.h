@@ -162,7 +162,8 @@ struct LowerCtx {
 void lower_node(const LowerCtx &c, int32_t id, int pos, std::vector<Dispatch> &out);
 uint64_t node_scratch_bytes(const Graph &g, int32_t id, int sm_count);
 // comm.cu: sum over the ranks of the device's communicator, in place (no-op without one)
-cudaError_t comm_allreduce_f32(tlb_device *dev, float *buf, size_t n, cudaStream_t st);
+// (err: the device error word of bounded waits; the peer-memory path needs it, NCCL is used without it)
+cudaError_t comm_allreduce_f32(tlb_device *dev, float *buf, size_t n, cudaStream_t st, int *err);
 int comm_ranks(tlb_device *dev);
 // IR rewrites before planning (fusion, shared activation quantization); fuse.cpp
 void rewrite_graph(Graph &g);

@@ -137,6 +137,17 @@ class Native:
         buf = C.create_string_buffer(unique_id, 128) if unique_id is not None else None
         check(self.L.tlb_comm_init(self.dev, n_ranks, rank, buf))
 
+    def comm_p2p_export(self) -> bytes:
+        """This rank's exchange buffer for the peer-memory all-reduce, as a 64-byte CUDA IPC handle."""
+        buf = C.create_string_buffer(64)
+        check(self.L.tlb_comm_p2p_export(self.dev, buf))
+        return buf.raw
+
+    def comm_p2p_import(self, handles: list[bytes]) -> None:
+        """Handles of all ranks, in rank order (as gathered by the host's own channel)."""
+        blob = b"".join(handles)
+        check(self.L.tlb_comm_p2p_import(self.dev, C.create_string_buffer(blob, len(blob))))
+
     @staticmethod
     def comm_unique_id() -> bytes:
         buf = C.create_string_buffer(128)
