@@ -265,7 +265,7 @@ def run_ours(args) -> dict:
     by_kind: dict[str, list] = {}
     for label, ms in prof:
         op = label.split(" ")[0]
-        if op == "MUL_MAT":
+        if op in ("MUL_MAT", "MUL_MAT_GROUP"):
             op = "MUL_MAT(output)" if label.endswith(" logits") else "MUL_MAT(layers)"
         elif op == "CUSTOM":
             op = "CUSTOM(paged_attention)" if label.endswith("attn") else "CUSTOM(cache_write)"
@@ -318,7 +318,7 @@ def run_ours(args) -> dict:
 
 # ---------------------------------------------------------------------------------- single-kernel runs
 def run_kernel(args) -> dict:
-    """`--kernel mul_mat:TYPE:K:M:N` or `--kernel paged_attention:SEQS:CTX` replays a program holding
+    """`--kernel mul_mat:TYPE:K:M:N`, `paged_attention:SEQS:CTX` or `flash_attention:TOKENS` replays a program holding
     only that op (several independent copies, so every replay reads more bytes than L2 holds) and
     prints the launch time and the algorithmic bytes it moved. The commands under profiles/ use it
     to give the profiler one kernel on a small, bounded case."""
@@ -383,6 +383,28 @@ def run_kernel(args) -> dict:
         prog.set_input(2, np.full(seqs, ctx, np.int32))
         bytes_per_launch = seqs * ctx * kvh * hs * 2 * 2
         what = "%d sequences x %d tokens, %d/%d heads of %d, f16 pages of %d tokens" % (seqs, ctx, heads, kvh, hs, bs)
+    elif spec[0] == "flash_attention":
+        # dense causal prefill attention of the 8B shape: NQ queries = keys, f16 K/V, 32/8 heads of 128
+        cfg = DecoderConfig()
+        nq = int(spec[1])
+        copies = args.copies or 2
+        hs, heads, kvh = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
+        n = Native.load([])
+        n.alloc_states([])
+        q = g.input(G.F32, [hs, nq, heads, 1])
+        ks = [g.input(G.F16, [hs, nq, kvh, 1]) for _ in range(copies)]
+        vs = [g.input(G.F16, [hs, nq, kvh, 1]) for _ in range(copies)]
+        mk = g.input(G.F16, [nq, nq, 1, 1])
+        for kk, vv in zip(ks, vs):
+            g.output(g.flash_attn_ext(q, kk, vv, mk, 1.0 / float(np.sqrt(hs))))
+        prog = NativeProgram.compile(n, g)
+        prog.set_input(0, rng.standard_normal((heads, nq, hs)).astype(np.float32))
+        for i in range(2 * copies):
+            prog.set_input(1 + i, rng.standard_normal((kvh, nq, hs)).astype(np.float16))
+        prog.set_input(1 + 2 * copies, np.triu(np.full((nq, nq), -np.inf, np.float16), 1))
+        bytes_per_launch = 2 * kvh * nq * hs * 2 + heads * nq * hs * 8 + nq * nq * 2
+        flops = 4.0 * nq * nq * heads * hs
+        what = "causal prefill attention, %d tokens, %d/%d heads of %d (%.1f GFLOP dense)" % (nq, heads, kvh, hs, flops / 1e9)
     else:
         raise SystemExit("unknown --kernel " + args.kernel)
     for _ in range(max(args.warmup, 1)):
@@ -401,6 +423,8 @@ def run_kernel(args) -> dict:
     out = {"kernel": args.kernel, "what": what, "copies_per_replay": copies, "us_per_launch": ms * 1e3,
            "algorithmic_bytes_per_launch": bytes_per_launch, "achieved_GBps": bytes_per_launch / ms / 1e6,
            "peak_GBps": peak, "frac": bytes_per_launch / ms / 1e6 / peak, "of": src, "launches": prog.labels()}
+    if spec[0] == "flash_attention":
+        out["TFLOPs"] = flops / (ms * 1e-3) / 1e12
     prog.free()
     n.close()
     return out

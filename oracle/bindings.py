@@ -256,6 +256,19 @@ class Ref:
         return RefGraph(self, mem_bytes, n_threads or (os.cpu_count() or 1))
 
 
+def ref_gguf_summary(ref: "Ref", path: str) -> str | None:
+    """What the reference's own GGUF reader sees in `path` (None when it does not parse, or when the
+    reference build predates the hook)."""
+    fn = getattr(ref.L, "tlref_gguf_summary", None)
+    if fn is None:
+        return None
+    fn.restype = _i64
+    fn.argtypes = [C.c_char_p, C.c_char_p, _i64]
+    buf = C.create_string_buffer(1 << 20)
+    n = fn(path.encode(), buf, len(buf))
+    return None if n < 0 else buf.value.decode()
+
+
 class RefGraph:
     """A ggml context + op list; tensors are ids. Mirrors the ggml C constructors by name."""
 

@@ -20,6 +20,7 @@
 #include <vector>
 
 #include "ggml.h"
+#include "gguf.h"
 #include "ggml-cpu.h"
 #include "ggml-backend.h"
 
@@ -204,6 +205,38 @@ const char * tlref_build_flags(void) {
 #else
     return "";
 #endif
+}
+
+
+// What the reference's own GGUF reader (vendored gguf.cpp, the one gguf.rs wraps) sees in a file: one line
+// per key and per tensor. Returns the text length, or -1 when the file does not parse.
+int64_t tlref_gguf_summary(const char * path, char * out, int64_t cap) {
+    struct gguf_init_params ip = { /*no_alloc*/ true, /*ctx*/ nullptr };
+    struct gguf_context * g = gguf_init_from_file(path, ip);
+    if (!g) return -1;
+    std::string t;
+    char line[512];
+    snprintf(line, sizeof line, "version %u alignment %zu data_offset %zu\n", gguf_get_version(g), gguf_get_alignment(g), gguf_get_data_offset(g));
+    t += line;
+    const int64_t nkv = gguf_get_n_kv(g);
+    for (int64_t i = 0; i < nkv; i++) {
+        const enum gguf_type ty = gguf_get_kv_type(g, i);
+        if (ty == GGUF_TYPE_STRING) snprintf(line, sizeof line, "kv %s string %s\n", gguf_get_key(g, i), gguf_get_val_str(g, i));
+        else if (ty == GGUF_TYPE_UINT32) snprintf(line, sizeof line, "kv %s u32 %u\n", gguf_get_key(g, i), gguf_get_val_u32(g, i));
+        else if (ty == GGUF_TYPE_ARRAY) snprintf(line, sizeof line, "kv %s array %d %zu\n", gguf_get_key(g, i), (int)gguf_get_arr_type(g, i), gguf_get_arr_n(g, i));
+        else snprintf(line, sizeof line, "kv %s type %d\n", gguf_get_key(g, i), (int)ty);
+        t += line;
+    }
+    const int64_t nt = gguf_get_n_tensors(g);
+    for (int64_t i = 0; i < nt; i++) {
+        snprintf(line, sizeof line, "tensor %s type %d offset %zu size %zu\n", gguf_get_tensor_name(g, i), (int)gguf_get_tensor_type(g, i),
+                 gguf_get_tensor_offset(g, i), gguf_get_tensor_size(g, i));
+        t += line;
+    }
+    gguf_free(g);
+    if ((int64_t)t.size() + 1 > cap) return -1;
+    memcpy(out, t.c_str(), t.size() + 1);
+    return (int64_t)t.size();
 }
 
 }  // extern "C"

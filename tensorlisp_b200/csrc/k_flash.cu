@@ -102,7 +102,23 @@ __global__ void __launch_bounds__(FA_WARPS * 32) k_flash_attn(FlashArgs p, const
     if (p.max_bias > 0.f) slope = h < p.n_head_log2 ? powf(p.m0, (float)(h + 1)) : powf(p.m1, (float)(2 * (h - p.n_head_log2) + 1));
 
     for (int kt = 0; kt < p.nkv; kt += FA_KT) {
-        __syncthreads();   // the previous tile has been consumed
+        // ---- this lane's mask values of the tile (2 rows x 16 keys); a tile that is -inf for every
+        // query of the CTA (the upper triangle of a causal mask) is skipped before anything is loaded
+        __half mk[FA_KT / 8][4];
+        bool dead = mb != nullptr;
+        if (mb) {
+#pragma unroll
+            for (int j = 0; j < FA_KT / 8; j++) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int key = kt + j * 8 + cq + (e & 1);
+                    const __half *mr = (e & 2) ? mr1 : mr0;
+                    mk[j][e] = key < p.nkv ? mr[key] : __ushort_as_half(0xfc00);   // -inf past the last key
+                    dead = dead && (__half_as_ushort(mk[j][e]) == 0xfc00);
+                }
+            }
+        }
+        if (__syncthreads_and(dead)) continue;   // also: the previous tile has been consumed
         for (int u = tid; u < FA_KT * (D / 8); u += FA_WARPS * 32) {
             const int row = u / (D / 8), c8 = u % (D / 8);
             const bool live = kt + row < p.nkv;
@@ -134,8 +150,7 @@ __global__ void __launch_bounds__(FA_WARPS * 32) k_flash_attn(FlashArgs p, const
                 const int key = kt + j * 8 + cq + (e & 1);
                 float x = s[j][e] * p.scale;
                 if (p.softcap != 0.f) x = p.softcap * tanhf(x);
-                const __half *mr = (e & 2) ? mr1 : mr0;
-                if (mr && key < p.nkv) x += slope * __half2float(mr[key]);
+                if (mb && key < p.nkv) x += slope * __half2float(mk[j][e]);
                 x = key < p.nkv ? x * LOG2E : -CUDART_INF_F;
                 s[j][e] = x;
                 if (e & 2) mx1 = fmaxf(mx1, x);

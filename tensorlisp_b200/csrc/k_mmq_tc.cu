@@ -77,17 +77,25 @@ __global__ void __launch_bounds__(256) k_act_pack_tc(const int8_t *__restrict__ 
 }
 
 // ---------------------------------------------------------------- the GEMM
+// Up to three weight matrices that share the activations (wq / wk / wv of a layer) run as one launch:
+// row tiles [tile0[j], tile0[j+1]) belong to matrix j.
+constexpr int TC_MAX_MATS = 3;
+struct TcMaps {
+    CUtensorMap m[TC_MAX_MATS];
+};
 struct TcParams {
     const uint8_t *act;   // packed blobs, one per super-block
-    float *out;           // y (n_split == 1) or partial sums [split][N][M]
-    int64_t M;
+    float *out[TC_MAX_MATS];   // per matrix: y (n_split == 1) or partial sums [split][N][M]
+    int64_t M[TC_MAX_MATS];
+    int tile0[TC_MAX_MATS + 1];
+    int n_mats;
     int N, npad, nsb, sb_per_split, n_split;
     int64_t ldy;          // elements between output columns
     int *err;
 };
 
 template <int NPAD, int RAW_STAGES, int ACT_STAGES>
-__global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_constant__ CUtensorMap wmap, TcParams p) {
+__global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_constant__ TcMaps maps, TcParams p) {
     using namespace tc;
     constexpr int BLOB = (NPAD * 548 + 127) / 128 * 128;
     constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(NPAD >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);  // f16 x f16 -> f32, K-major A and B
@@ -104,7 +112,10 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
 
     const int tid = threadIdx.x, warp = tid >> 5;
     if (tid == 0) TC_STAMP(0);
-    const int row_tile = blockIdx.x, split = blockIdx.y;
+    const int gtile = blockIdx.x, split = blockIdx.y;
+    const int mat = (p.n_mats > 1 && gtile >= p.tile0[1]) + (p.n_mats > 2 && gtile >= p.tile0[2]);
+    const int row_tile = gtile - p.tile0[mat];
+    const CUtensorMap *wmap = &maps.m[mat];
     const int sb0 = split * p.sb_per_split;
     const int nsb = min(p.sb_per_split, p.nsb - sb0);      // super-blocks of this CTA (>= 1 by construction)
     if (tid == 0) {
@@ -137,7 +148,7 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
     auto load_raw = [&](int i) {   // super-block i of this CTA -> raw stage i % RAW_STAGES
         const int s = i % RAW_STAGES;
         mbar_expect_tx(&bar_raw[s], RAW_BYTES);
-        tma_2d(raw + s * RAW_BYTES, &wmap, (sb0 + i) * 144, row_tile * ROWS, &bar_raw[s]);
+        tma_2d(raw + s * RAW_BYTES, wmap, (sb0 + i) * 144, row_tile * ROWS, &bar_raw[s]);
     };
     auto load_act = [&](int i) {
         const int s = i % ACT_STAGES;
@@ -247,11 +258,13 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
             if (tid == 32) TC_STAMP(97 + 2 * i);
         }
         const int64_t row = (int64_t)row_tile * ROWS + row_in_tile;
-        if (row < p.M) {
-            float *o = p.out + (size_t)split * p.N * p.ldy + row;
+        if (row < p.M[mat]) {
+            // partial sums [split][N][M] and the outputs of a group are dense; a single matrix may have its own stride
+            const int64_t ldo = (p.n_split > 1 || p.n_mats > 1) ? p.M[mat] : p.ldy;
+            float *o = p.out[mat] + (size_t)split * p.N * ldo + row;
 #pragma unroll
             for (int c = 0; c < CW; c++)
-                if (col0 + c < p.N) o[(size_t)(col0 + c) * p.ldy] = yacc[c];
+                if (col0 + c < p.N) o[(size_t)(col0 + c) * ldo] = yacc[c];
         }
     } else {
         // a warp may only touch the 32 TMEM lanes of its quadrant (warp % 4): that fixes its rows
@@ -369,15 +382,36 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
     if (tid == 0 && s_fail) atomicExch(p.err, 2);
 }
 
-// y[n][m] = sum over the K splits, in split order
-__global__ void k_mmq_reduce(const float *__restrict__ part, float *__restrict__ y, int64_t total, int n_split) {
+// y[n][m] = sum over the K splits, in split order. Up to three matrices per launch: element i of the
+// concatenated index space belongs to the first segment whose end exceeds it; segment j has `seg_n[j]`
+// elements, partial sums at part + seg_off[j] laid out [split][seg_n[j]], result y[j].
+struct ReduceSegs {
+    float *y[TC_MAX_MATS];
+    int64_t seg_n[TC_MAX_MATS], seg_off[TC_MAX_MATS];
+    int n_segs;
+};
+__global__ void k_mmq_reduce(const float *__restrict__ part, ReduceSegs g, int64_t total, int n_split) {
     griddep_launch();
     griddep_wait();
-    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
+    int j = 0;
+    while (j + 1 < g.n_segs && i >= g.seg_n[j]) {
+        i -= g.seg_n[j];
+        j++;
+    }
+    const float *p = part + g.seg_off[j] + i;
+    const int64_t stride = g.seg_n[j];
+    // all loads go out before the first add: a warp issues in order, and an add right behind its load
+    // would make every L2 round trip wait for the one before it
+    float v[16];
+#pragma unroll
+    for (int k = 0; k < 16; k++) v[k] = k < n_split ? p[(size_t)k * stride] : 0.f;
     float s = 0.f;
-    for (int k = 0; k < n_split; k++) s += part[(size_t)k * total + i];
-    y[i] = s;
+#pragma unroll
+    for (int k = 0; k < 16; k++)
+        if (k < n_split) s += v[k];
+    g.y[j][i] = s;
 }
 
 // ---------------------------------------------------------------- host side
@@ -463,51 +497,84 @@ cudaError_t tc_encode_2d(CUtensorMap *map, const void *base, uint64_t row_bytes,
 }
 
 void launch_mmq_reduce(const float *partial, float *y, int64_t total, int n_split, cudaStream_t st) {
-    launch_pdl(k_mmq_reduce, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, partial, y, total, n_split);
+    ReduceSegs g{};
+    g.n_segs = 1;
+    g.y[0] = y;
+    g.seg_n[0] = total;
+    g.seg_off[0] = 0;
+    launch_pdl(k_mmq_reduce, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, partial, g, total, n_split);
 }
 
 bool tc_available() { return encode_tiled() != nullptr; }
 
-cudaError_t launch_mmq_tc(const TcPlan &t, const void *W, int64_t K, int64_t M, int64_t N, const void *blobs, float *y,
-                          int64_t ldy, void *partial, int *err, cudaStream_t st) {
-    CUtensorMap map;
-    cudaError_t e = tc_encode_2d(&map, W, (uint64_t)(K / 256 * 144), (uint64_t)M, 144, tc::ROWS, 1);
-    if (e != cudaSuccess) return e;
-    dim3 grid((unsigned)((M + tc::ROWS - 1) / tc::ROWS), (unsigned)t.n_split);
+// n_mats weight matrices [M[j] x K] sharing the activations; y[j] dense [N][M[j]] when n_mats > 1 or K is split
+cudaError_t launch_mmq_tc_group(const TcPlan &t, int n_mats, const void *const *W, int64_t K, const int64_t *M, int64_t N, const void *blobs,
+                                float *const *y, int64_t ldy, void *partial, int *err, cudaStream_t st) {
+    if (n_mats < 1 || n_mats > TC_MAX_MATS || (n_mats > 1 && t.n_col_chunks != 1)) return cudaErrorInvalidValue;
+    if (t.n_split > 16) return cudaErrorInvalidValue;
+    TcMaps maps;
+    int tiles = 0;
+    TcParams base{};
+    for (int j = 0; j < n_mats; j++) {
+        cudaError_t e = tc_encode_2d(&maps.m[j], W[j], (uint64_t)(K / 256 * 144), (uint64_t)M[j], 144, tc::ROWS, 1);
+        if (e != cudaSuccess) return e;
+        base.tile0[j] = tiles;
+        base.M[j] = M[j];
+        tiles += (int)((M[j] + tc::ROWS - 1) / tc::ROWS);
+    }
+    for (int j = n_mats; j < TC_MAX_MATS; j++) maps.m[j] = maps.m[0];
+    for (int j = n_mats; j <= TC_MAX_MATS; j++) base.tile0[j] = tiles;
+    base.n_mats = n_mats;
+    base.npad = t.npad;
+    base.nsb = t.nsb;
+    base.sb_per_split = t.sb_per_split;
+    base.n_split = t.n_split;
+    base.err = err;
+    base.ldy = ldy;
+    dim3 grid((unsigned)tiles, (unsigned)t.n_split);
+    cudaError_t e = cudaSuccess;
     // more columns than one launch takes (prefill): one launch per chunk of npad columns
     for (int c = 0; c < t.n_col_chunks; c++) {
         const int64_t n0 = (int64_t)c * t.npad, nc = std::min<int64_t>(t.npad, N - n0);
-        TcParams p;
+        TcParams p = base;
         p.act = (const uint8_t *)blobs + (size_t)c * t.nsb * t.blob_unit;
-        p.M = M;
         p.N = (int)nc;
-        p.npad = t.npad;
-        p.nsb = t.nsb;
-        p.sb_per_split = t.sb_per_split;
-        p.n_split = t.n_split;
-        p.err = err;
-        float *yc = y + n0 * ldy;
-        if (t.n_split > 1) {
-            p.out = (float *)partial;
-            p.ldy = M;
-        } else {
-            p.out = yc;
-            p.ldy = ldy;
+        ReduceSegs segs{};
+        int64_t poff = 0, total = 0;
+        for (int j = 0; j < n_mats; j++) {
+            float *yc = y[j] + n0 * (n_mats > 1 ? M[j] : ldy);
+            if (t.n_split > 1) {
+                p.out[j] = (float *)partial + poff;
+                segs.y[j] = yc;
+                segs.seg_n[j] = nc * M[j];
+                segs.seg_off[j] = poff;
+                poff += (int64_t)t.n_split * nc * M[j];
+                total += nc * M[j];
+            } else {
+                p.out[j] = yc;
+            }
         }
         switch (t.npad) {
-            case 16: e = launch_pdl(k_mmq_tc_q4k<16, 6, 4>, grid, dim3(tc::THREADS), tc_smem<16, 6, 4>(), st, map, p); break;
-            case 32: e = launch_pdl(k_mmq_tc_q4k<32, 6, 4>, grid, dim3(tc::THREADS), tc_smem<32, 6, 4>(), st, map, p); break;
-            default: e = launch_pdl(k_mmq_tc_q4k<64, 5, 3>, grid, dim3(tc::THREADS), tc_smem<64, 5, 3>(), st, map, p); break;
+            case 16: e = launch_pdl(k_mmq_tc_q4k<16, 6, 4>, grid, dim3(tc::THREADS), tc_smem<16, 6, 4>(), st, maps, p); break;
+            case 32: e = launch_pdl(k_mmq_tc_q4k<32, 6, 4>, grid, dim3(tc::THREADS), tc_smem<32, 6, 4>(), st, maps, p); break;
+            default: e = launch_pdl(k_mmq_tc_q4k<64, 5, 3>, grid, dim3(tc::THREADS), tc_smem<64, 5, 3>(), st, maps, p); break;
         }
         if (e != cudaSuccess) return e;
         if (t.n_split > 1) {
-            if (ldy != M) return cudaErrorInvalidValue;   // the reduce writes dense columns
-            launch_mmq_reduce((const float *)partial, yc, nc * M, t.n_split, st);
-            e = cudaGetLastError();
+            if (n_mats == 1 && ldy != M[0]) return cudaErrorInvalidValue;   // the reduce writes dense columns
+            segs.n_segs = n_mats;
+            e = launch_pdl(k_mmq_reduce, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, (const float *)partial, segs, total, t.n_split);
             if (e != cudaSuccess) return e;
         }
     }
     return cudaSuccess;
+}
+
+cudaError_t launch_mmq_tc(const TcPlan &t, const void *W, int64_t K, int64_t M, int64_t N, const void *blobs, float *y,
+                          int64_t ldy, void *partial, int *err, cudaStream_t st) {
+    const void *Ws[1] = {W};
+    float *ys[1] = {y};
+    return launch_mmq_tc_group(t, 1, Ws, K, &M, N, blobs, ys, ldy, partial, err, st);
 }
 
 }  // namespace tlb

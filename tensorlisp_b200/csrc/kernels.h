@@ -58,6 +58,9 @@ TcPlan mmq_tc_plan(int64_t K, int64_t M, int64_t N, int sm_count);
 cudaError_t launch_act_pack_tc(const ActLayout &a, const void *act, int npad, void *blobs, cudaStream_t st);
 cudaError_t launch_mmq_tc(const TcPlan &t, const void *W, int64_t K, int64_t M, int64_t N, const void *blobs, float *y,
                           int64_t ldy, void *partial, int *err, cudaStream_t st);
+// up to 3 matrices [M[j] x K] that share the activations in one launch; outputs dense [N][M[j]]
+cudaError_t launch_mmq_tc_group(const TcPlan &t, int n_mats, const void *const *W, int64_t K, const int64_t *M, int64_t N, const void *blobs,
+                                float *const *y, int64_t ldy, void *partial, int *err, cudaStream_t st);
 void mmq_tc_configure();
 bool tc_available();   // the driver offers cuTensorMapEncodeTiled
 

@@ -414,6 +414,53 @@ void lower_mul_mat(L &l) {
     });
 }
 
+// MUL_MAT_GROUP (pseudo-op made by fuse_mul_mat_groups): up to three Q4_K mul_mats over the same
+// activations (wq / wk / wv) in one tensor-core launch. src = w0, x, quantized x, w1, y1, w2, y2; the
+// node's own tensor is y0.
+void lower_mul_mat_group(L &l) {
+    const Tensor &t = l.t();
+    const int32_t x = l.src(1), qa = l.src(2);
+    const Tensor &tx = l.T(x);
+    const int64_t K = tx.ne[0], N = tx.ne[1];
+    int n_mats = 0;
+    Place pw[3], py[3];
+    int64_t Ms[3] = {0, 0, 0}, Msum = 0;
+    const int wslot[3] = {0, 3, 5}, yslot[3] = {-1, 4, 6};
+    for (int j = 0; j < 3; j++) {
+        if (t.src[wslot[j]] < 0) break;
+        const int32_t w = t.src[wslot[j]], y = j == 0 ? l.id : l.src(yslot[j]);
+        const Tensor &tw = l.T(w), &ty = l.T(y);
+        if (tw.ty != TLB_TYPE_Q4_K || tw.ne[0] != K || tw.nb[1] != tw.row_size() || ty.ty != TLB_TYPE_F32 || !ty.is_contiguous() ||
+            ty.ne[0] != tw.ne[1] || ty.ne[1] != N)
+            throw std::string("a grouped mul_mat lost its shape invariants");
+        pw[j] = l.place(w);
+        py[j] = l.place(y);
+        Ms[j] = tw.ne[1];
+        Msum += Ms[j];
+        n_mats++;
+    }
+    const int sm = l.c.dev->prop.multiProcessorCount;
+    const TcPlan tp = mmq_tc_plan(K, Msum, N, sm);
+    if (tp.npad != l.T(qa).op_params[1] || tp.n_col_chunks != 1) throw std::string("activation blobs were packed for another column count");
+    const ActLayout a = act_layout(ACT_Q8_K, K, tx.nrows());
+    const int64_t sc = l.c.layout->scratch[l.pos];
+    if (tp.n_split > 1 && sc < 0) throw std::string("split-K scratch was not planned");
+    Place ps;
+    ps.buf = BUF_ARENA;
+    ps.off = sc < 0 ? 0 : (uint64_t)sc;
+    const Place pq = l.place(qa);
+    const uint64_t blob_off = a.bytes;
+    l.push([=](const RunCtx &r) {
+        const void *W[3] = {nullptr, nullptr, nullptr};
+        float *Y[3] = {nullptr, nullptr, nullptr};
+        for (int j = 0; j < n_mats; j++) {
+            W[j] = r.at(pw[j]);
+            Y[j] = (float *)r.at(py[j]);
+        }
+        return launch_mmq_tc_group(tp, n_mats, W, K, Ms, N, r.at(pq) + blob_off, Y, Ms[0], r.at(ps), r.err, r.stream);
+    });
+}
+
 void lower_quant_act(L &l) {
     const Tensor &t = l.t();
     const int32_t x = l.src(0);
@@ -629,6 +676,14 @@ uint64_t node_scratch_bytes(const Graph &g, int32_t id, int sm_count) {
         PagedGeom pg{};
         if (paged_geom(g, t, sm_count, pg)) return paged_scratch_bytes(pg);
     }
+    if (t.op == "MUL_MAT_GROUP") {
+        const Tensor &tx = g.tensors[t.src[1]];
+        int64_t Msum = 0;
+        for (int s : {0, 3, 5})
+            if (t.src[s] >= 0) Msum += g.tensors[t.src[s]].ne[1];
+        const TcPlan tp = mmq_tc_plan(tx.ne[0], Msum, tx.ne[1], sm_count);
+        return tp.n_split > 1 ? (uint64_t)tp.n_split * tx.ne[1] * Msum * 4 : 0;
+    }
     if (t.op == "MUL_MAT" && t.src[0] >= 0 && t.src[1] >= 0 && t.src[2] >= 0 && is_qact(g.tensors[t.src[2]].op) &&
         g.tensors[t.src[2]].op_params[1] > 0) {
         // split-K partial sums of the tensor-core path
@@ -668,6 +723,7 @@ void lower_node(const LowerCtx &c, int32_t id, int pos, std::vector<Dispatch> &o
     if (op == "ARGMAX") return lower_argmax(l);
     if (op == "CONCAT" || op == "REPEAT" || op == "SUM_ROWS" || op == "MEAN" || op == "ARANGE") return lower_simple(l);
     if (op == "MUL_MAT") return lower_mul_mat(l);
+    if (op == "MUL_MAT_GROUP") return lower_mul_mat_group(l);
     if (op == "CUSTOM") return lower_custom(l);
     if (op == "FLASH_ATTN_EXT") return lower_flash(l);
     if (op == "ALLREDUCE") return lower_allreduce(l);
@@ -677,6 +733,7 @@ void lower_node(const LowerCtx &c, int32_t id, int pos, std::vector<Dispatch> &o
 // ---------------------------------------------------------------------------- IR rewrites
 void fuse_row_producers(Graph &g);
 void fuse_rope_cache(Graph &g);
+void fuse_mul_mat_groups(Graph &g);
 // Readers of every root (views of a tensor count for the root), as fuse.rs:56-63 requires.
 void rewrite_graph(Graph &g) {
     const size_t nt0 = g.tensors.size();
@@ -822,6 +879,7 @@ void rewrite_graph(Graph &g) {
     g.nodes.swap(nodes);
     if (enabled("ROW_QUANT")) fuse_row_producers(g);
     if (enabled("ROPE_KV_WRITE")) fuse_rope_cache(g);
+    if (enabled("MUL_MAT_GROUP")) fuse_mul_mat_groups(g);
 }
 
 // Fold the producer of a quantized activation into its QUANT_ACT node (k_fused.cu): RMS_NORM_MUL
@@ -1017,6 +1075,48 @@ void fuse_rope_cache(Graph &g) {
         Cw.src[7] = slots;
         Cw.src[8] = q16;   // written by this node
         dead[pos_of[rq]] = dead[pos_of[rk]] = dead[pos_of[k16]] = dead[pos_of[v16]] = dead[pos_of[q16]] = 1;
+    }
+    std::vector<int32_t> out;
+    for (size_t i = 0; i < nn; i++)
+        if (!dead[i]) out.push_back(g.nodes[i]);
+    g.nodes.swap(out);
+}
+
+
+// Consecutive tensor-core mul_mats over the same quantized activations (wq, wk, wv of a layer) become one
+// MUL_MAT_GROUP launch when together they still fit one wave of CTAs: each of them alone leaves most SMs
+// idle (wk and wv of an 8B-shape layer are 8 row tiles each). Nothing reads a member's result before the
+// last member, because the members are adjacent in node order.
+void fuse_mul_mat_groups(Graph &g) {
+    const size_t nn = g.nodes.size();
+    std::vector<char> dead(nn, 0);
+    auto eligible = [&](const Tensor &t) {
+        if (t.op != "MUL_MAT" || t.src[0] < 0 || t.src[1] < 0 || t.src[2] < 0) return false;
+        const Tensor &tw = g.tensors[t.src[0]], &tx = g.tensors[t.src[1]], &q = g.tensors[t.src[2]];
+        if (!is_qact(q.op) || q.op_params[1] <= 0 || tw.ty != TLB_TYPE_Q4_K) return false;
+        if (tw.ne[2] * tw.ne[3] * t.ne[2] * t.ne[3] != 1 || tw.nb[1] != tw.row_size() || !t.is_contiguous() || t.view_src >= 0) return false;
+        if (tx.ne[1] > 64 || !mmq_tc_supported(tw.ty, tx.ne[0], tw.ne[1], tx.ne[1]) || getenv("TLB_NO_TC") || getenv("TLB_MM_GENERIC")) return false;
+        return true;
+    };
+    for (size_t i = 0; i < nn; i++) {
+        if (dead[i]) continue;
+        Tensor &A = g.tensors[g.nodes[i]];
+        if (!eligible(A)) continue;
+        int64_t tiles = (A.ne[0] + 127) / 128;
+        int members = 1;
+        const int wslot[3] = {0, 3, 5}, yslot[3] = {-1, 4, 6};
+        for (size_t j = i + 1; j < nn && members < 3; j++) {
+            const Tensor &B = g.tensors[g.nodes[j]];
+            if (!eligible(B) || B.src[1] != A.src[1] || B.src[2] != A.src[2]) break;
+            const int64_t tb = (B.ne[0] + 127) / 128;
+            if (tiles + tb > 148) break;   // a group must stay within one wave of CTAs
+            tiles += tb;
+            A.src[wslot[members]] = B.src[0];
+            A.src[yslot[members]] = g.nodes[j];
+            dead[j] = 1;
+            members++;
+        }
+        if (members > 1) A.op = "MUL_MAT_GROUP";
     }
     std::vector<int32_t> out;
     for (size_t i = 0; i < nn; i++)

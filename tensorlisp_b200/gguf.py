@@ -1,0 +1,231 @@
+"""GGUF (version 3) files as tensorlisp uses them (reference: crates/tensorlisp/src/gguf.rs:87-489 over the
+vendored gguf.cpp; program keys crates/tensorlisp/src/program.rs:3-15): a reader that maps tensors without
+copying, a writer, the TL_VER / TL_TXT / TL_ASSET.<name> keys, and `quantize_file`, the `tl quantize`
+counterpart that quantizes weights on the GPU with the library's bit-exact row quantizers
+(crates/tensorlisp/src/quantize.rs:193-267: only 2-D tensors whose rows are a whole number of blocks).
+
+The container format is the published GGUF layout: magic "GGUF", u32 version, u64 tensor count, u64 key
+count, keys (string, u32 type, value), tensor infos (string name, u32 rank, u64 dims, u32 ggml type, u64
+offset into the data section), padding to `general.alignment` (32 by default), tensor data each aligned
+to it. Strings are u64 length + bytes; arrays are u32 element type + u64 count + elements.
+"""
+from __future__ import annotations
+
+import mmap
+import struct
+from dataclasses import dataclass
+
+import numpy as np
+
+from .graph import row_size
+
+MAGIC = 0x46554747
+TL_VER, TL_TXT, TL_BIN, TL_ASSET_PREFIX = "TL_VER", "TL_TXT", "TL_BIN", "TL_ASSET."
+FORMAT_VERSION = 1
+U8, I8, U16, I16, U32, I32, F32, BOOL, STRING, ARRAY, U64, I64, F64 = range(13)
+_SCALAR = {U8: "<B", I8: "<b", U16: "<H", I16: "<h", U32: "<I", I32: "<i", F32: "<f", BOOL: "<?", U64: "<Q", I64: "<q", F64: "<d"}
+_NP = {U8: np.uint8, I8: np.int8, U16: np.uint16, I16: np.int16, U32: np.uint32, I32: np.int32, F32: np.float32,
+       BOOL: np.bool_, U64: np.uint64, I64: np.int64, F64: np.float64}
+
+
+@dataclass
+class TensorInfo:
+    name: str
+    ty: int                 # ggml type
+    ne: list[int]           # ggml order: ne[0] is the row length
+    offset: int             # into the data section
+    nbytes: int
+
+
+class GgufError(ValueError):
+    pass
+
+
+class GgufFile:
+    """Read side. `tensor_bytes(i)` is a zero-copy view into the mapped file."""
+
+    def __init__(self, path: str) -> None:
+        self.path = path
+        self._f = open(path, "rb")
+        self._m = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ)
+        self._p = 0
+        magic, self.version = self._unpack("<II")
+        if magic != MAGIC:
+            raise GgufError("%s is not a GGUF file" % path)
+        if self.version not in (2, 3):
+            raise GgufError("GGUF version %d is not supported" % self.version)
+        n_tensors, n_kv = self._unpack("<QQ")
+        self.kv: dict[str, tuple[int, object]] = {}
+        for _ in range(n_kv):
+            key = self._string()
+            (ty,) = self._unpack("<I")
+            self.kv[key] = (ty, self._value(ty))
+        self.tensors: list[TensorInfo] = []
+        for _ in range(n_tensors):
+            name = self._string()
+            (rank,) = self._unpack("<I")
+            ne = list(self._unpack("<%dQ" % rank)) if rank else []
+            ty, off = self._unpack("<IQ")
+            rows = int(np.prod(ne[1:], dtype=np.int64)) if len(ne) > 1 else 1
+            nbytes = row_size(ty, ne[0]) * rows if ne else 0
+            self.tensors.append(TensorInfo(name, ty, ne, off, nbytes))
+        self.alignment = int(self.kv.get("general.alignment", (U32, 32))[1])
+        self.data_offset = (self._p + self.alignment - 1) // self.alignment * self.alignment
+
+    def close(self) -> None:
+        self._m.close()
+        self._f.close()
+
+    def _unpack(self, fmt: str):
+        n = struct.calcsize(fmt)
+        if self._p + n > len(self._m):
+            raise GgufError("truncated GGUF file")
+        v = struct.unpack_from(fmt, self._m, self._p)
+        self._p += n
+        return v
+
+    def _string(self) -> str:
+        (n,) = self._unpack("<Q")
+        if self._p + n > len(self._m):
+            raise GgufError("truncated GGUF file")
+        s = self._m[self._p:self._p + n].decode("utf-8")
+        self._p += n
+        return s
+
+    def _value(self, ty: int):
+        if ty == STRING:
+            return self._string()
+        if ty == ARRAY:
+            et, n = self._unpack("<IQ")
+            if et == STRING:
+                return [self._string() for _ in range(n)]
+            if et not in _NP:
+                raise GgufError("array of type %d" % et)
+            a = np.frombuffer(self._m, _NP[et], n, self._p).copy()
+            self._p += a.nbytes
+            return a
+        if ty not in _SCALAR:
+            raise GgufError("value of type %d" % ty)
+        return self._unpack(_SCALAR[ty])[0]
+
+    # ---- tensorlisp conventions
+    def program(self) -> str:
+        """The Scheme program of the file (gguf.rs:136-153)."""
+        ver = self.kv.get(TL_VER)
+        if ver is None:
+            raise GgufError("not a tensorlisp file: %s is missing" % TL_VER)
+        if ver[1] != FORMAT_VERSION:
+            raise GgufError("%s is %d, this runtime supports version %d" % (TL_VER, ver[1], FORMAT_VERSION))
+        if TL_TXT in self.kv:
+            return self.kv[TL_TXT][1]
+        if TL_BIN in self.kv:
+            raise GgufError("binary programs (%s) are not supported yet" % TL_BIN)
+        raise GgufError("no program: neither %s nor %s is set" % (TL_TXT, TL_BIN))
+
+    def assets(self) -> dict[str, bytes]:
+        return {k[len(TL_ASSET_PREFIX):]: bytes(v[1]) for k, v in self.kv.items()
+                if k.startswith(TL_ASSET_PREFIX) and v[0] == ARRAY}
+
+    def tensor_bytes(self, i: int) -> np.ndarray:
+        t = self.tensors[i]
+        return np.frombuffer(self._m, np.uint8, t.nbytes, self.data_offset + t.offset)
+
+    def tensor_file_offset(self, i: int) -> int:
+        return self.data_offset + self.tensors[i].offset
+
+
+class GgufWriter:
+    def __init__(self, alignment: int = 32) -> None:
+        self.alignment = alignment
+        self.kv: list[tuple[str, int, object]] = []
+        self.tensors: list[tuple[str, int, list[int], np.ndarray]] = []
+
+    def _set(self, key: str, ty: int, value) -> None:
+        self.kv = [e for e in self.kv if e[0] != key] + [(key, ty, value)]
+
+    def set_str(self, key: str, value: str) -> None:
+        self._set(key, STRING, value)
+
+    def set_u32(self, key: str, value: int) -> None:
+        self._set(key, U32, int(value))
+
+    def set_bytes(self, key: str, data: bytes) -> None:
+        self._set(key, ARRAY, np.frombuffer(bytes(data), np.uint8))
+
+    def set_program(self, text: str) -> None:   # gguf.rs:396-403
+        self.kv = [e for e in self.kv if e[0] != TL_BIN]
+        self.set_u32(TL_VER, FORMAT_VERSION)
+        self.set_str(TL_TXT, text)
+
+    def set_asset(self, name: str, data: bytes) -> None:
+        self.set_bytes(TL_ASSET_PREFIX + name, data)
+
+    def copy_metadata(self, src: GgufFile) -> None:
+        for k, (ty, v) in src.kv.items():
+            self._set(k, ty, v)
+
+    def add_tensor(self, name: str, ty: int, ne: list[int], data: np.ndarray) -> None:
+        data = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+        rows = int(np.prod(ne[1:], dtype=np.int64)) if len(ne) > 1 else 1
+        if data.nbytes != row_size(ty, ne[0]) * rows:
+            raise GgufError("tensor %s: %d bytes for type %d shape %s" % (name, data.nbytes, ty, ne))
+        self.tensors.append((name, ty, list(ne), data))
+
+    @staticmethod
+    def _str(s: str) -> bytes:
+        b = s.encode("utf-8")
+        return struct.pack("<Q", len(b)) + b
+
+    def _val(self, ty: int, v) -> bytes:
+        if ty == STRING:
+            return self._str(v)
+        if ty == ARRAY:
+            if isinstance(v, list):
+                return struct.pack("<IQ", STRING, len(v)) + b"".join(self._str(s) for s in v)
+            v = np.ascontiguousarray(v)
+            et = {np.dtype(d): t for t, d in _NP.items()}[v.dtype]
+            return struct.pack("<IQ", et, v.size) + v.tobytes()
+        return struct.pack(_SCALAR[ty], v)
+
+    def write(self, path: str) -> None:
+        al = self.alignment
+        head = struct.pack("<IIQQ", MAGIC, 3, len(self.tensors), len(self.kv))
+        for k, ty, v in self.kv:
+            head += self._str(k) + struct.pack("<I", ty) + self._val(ty, v)
+        off = 0
+        offsets = []
+        for name, ty, ne, data in self.tensors:
+            offsets.append(off)
+            head += self._str(name) + struct.pack("<I", len(ne)) + struct.pack("<%dQ" % len(ne), *ne) + struct.pack("<IQ", ty, off)
+            off += (data.nbytes + al - 1) // al * al
+        with open(path, "wb") as f:
+            f.write(head)
+            f.write(b"\0" * ((len(head) + al - 1) // al * al - len(head)))
+            for (_, _, _, data), o in zip(self.tensors, offsets):
+                f.write(data.tobytes())
+                f.write(b"\0" * ((data.nbytes + al - 1) // al * al - data.nbytes))
+
+
+def quantize_file(native, src_path: str, dst_path: str, ty: int, only=None) -> list[str]:
+    """`tl quantize`: every f32 tensor of rank 2 whose rows are a whole number of blocks of `ty` (and that
+    `only(name)` accepts, when given) is quantized ON THE GPU; everything else and all metadata are
+    copied. Returns the names that were quantized."""
+    from . import graph as G
+    from .native import quantize_rows
+
+    src = GgufFile(src_path)
+    out = GgufWriter(src.alignment)
+    out.copy_metadata(src)
+    done = []
+    blck = G.TYPE_TRAITS[ty][1]
+    for i, t in enumerate(src.tensors):
+        raw = src.tensor_bytes(i)
+        if t.ty == G.F32 and len(t.ne) == 2 and t.ne[0] % blck == 0 and (only is None or only(t.name)):
+            w = raw.view(np.float32).reshape(t.ne[1], t.ne[0])
+            out.add_tensor(t.name, ty, t.ne, quantize_rows(native, ty, w))
+            done.append(t.name)
+        else:
+            out.add_tensor(t.name, t.ty, t.ne, raw)
+    out.write(dst_path)
+    src.close()
+    return done

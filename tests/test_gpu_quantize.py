@@ -60,3 +60,28 @@ def test_empty_and_bad_rows(native):
     with pytest.raises(TlbError) as e:
         quantize_rows(native, 14, np.zeros((2, 256), np.float32))  # q6_K is not implemented
     assert "not implemented" in str(e.value)
+
+
+def test_quantize_file_like_tl_quantize(native, oracle, tmp_path):
+    """`tl quantize` on the GPU: rank-2 f32 tensors with whole blocks per row become Q4_K, bit-exact with
+    the oracle; the 1-D norm, the ragged matrix, the program and the asset are carried over."""
+    from tensorlisp_b200 import graph as G
+    from tensorlisp_b200.gguf import GgufFile, GgufWriter, quantize_file
+    rng = np.random.default_rng(8)
+    w = (rng.standard_normal((40, 1024)) * 0.02).astype(np.float32)
+    ragged = rng.standard_normal((4, 100)).astype(np.float32)
+    src, dst = str(tmp_path / "f32.gguf"), str(tmp_path / "q4k.gguf")
+    out = GgufWriter()
+    out.set_program("(define (f x) x)")
+    out.set_asset("a.bin", b"abc")
+    out.add_tensor("norm", G.F32, [1024], np.ones(1024, np.float32))
+    out.add_tensor("W", G.F32, [1024, 40], w)
+    out.add_tensor("ragged", G.F32, [100, 4], ragged)
+    out.write(src)
+    assert quantize_file(native, src, dst, G.Q4_K) == ["W"]
+    f = GgufFile(dst)
+    assert f.program() == "(define (f x) x)" and f.assets() == {"a.bin": b"abc"}
+    assert [(t.name, t.ty) for t in f.tensors] == [("norm", G.F32), ("W", G.Q4_K), ("ragged", G.F32)]
+    assert np.array_equal(f.tensor_bytes(1), oracle.quantize(G.Q4_K, w).reshape(-1))
+    assert np.array_equal(f.tensor_bytes(2).view(np.float32).reshape(4, 100), ragged)
+    f.close()
