@@ -164,7 +164,7 @@ def step_inputs(cfg, step: int, rng) -> list[np.ndarray]:
 
 
 def algorithmic_bytes(cfg, world: int) -> dict:
-    """Bytes one rank must move per step (SURVEY 8d figures, divided by the ranks)."""
+    """Algorithmic bytes one rank must move per step: every weight byte and every attended K/V byte once."""
     from tensorlisp_b200.programs import decoder_weights
     specs = decoder_weights(cfg, world)
     w_layers = sum(s.nbytes() for s in specs if s.name.startswith("blk.") and len(s.ne) == 2)
@@ -305,7 +305,7 @@ def run_ours(args) -> dict:
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         try:
-            result["cpu_baseline"] = cpu_reference_step(cfg, budget_s=20.0)
+            result["cpu_baseline"] = cpu_reference_step(cfg, time_limit_s=20.0)
         except Exception as e:  # the checker is optional equipment for a bench line
             result["cpu_baseline"] = {"value": None, "unit": "tok/s", "cores": 0, "kind": "reference", "sample": "failed: %s" % e}
     prog.free()
@@ -431,7 +431,7 @@ def run_kernel(args) -> dict:
 
 
 # ---------------------------------------------------------------------------------- reference arm (CPU)
-def cpu_reference_step(cfg, budget_s: float = 20.0, steps: int = 1, warmup: int = 0) -> dict:
+def cpu_reference_step(cfg, time_limit_s: float = 20.0, steps: int = 1, warmup: int = 0) -> dict:
     """The reference's own ggml CPU backend (the build of oracle/_ref that fits this host's CPU) on a
     bounded sample of the decode step: ONE decoder layer at batch 32 / context 2048 (dense f16 K/V,
     because ggml has no CPU paged attention; FLASH_ATTN_EXT reads the same bytes) plus the output
@@ -492,7 +492,7 @@ def cpu_reference_step(cfg, budget_s: float = 20.0, steps: int = 1, warmup: int 
         gl.compute(outs_l)
         gh.compute(outs_h)
     t_layer, t_head, n = [], [], 0
-    while n < max(steps, 1) or (time.time() - t0 < budget_s and n < 5):
+    while n < max(steps, 1) or (time.time() - t0 < time_limit_s and n < 5):
         t_layer.append(gl.compute(outs_l))
         t_head.append(gh.compute(outs_h))
         n += 1
@@ -513,7 +513,7 @@ def run_reference(args) -> dict:
     from tensorlisp_b200.programs import DecoderConfig
     cfg = DecoderConfig()
     try:
-        cb = cpu_reference_step(cfg, budget_s=0.0, steps=args.steps, warmup=min(args.warmup, 1))
+        cb = cpu_reference_step(cfg, time_limit_s=0.0, steps=args.steps, warmup=min(args.warmup, 1))
     except Exception as e:
         return {"impl": "reference", "unavailable": "the reference's ggml CPU build is missing or failed: %s" % e}
     return {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "tok/s", "n_gpus": args.gpus,

@@ -207,8 +207,10 @@ tlb_status tlb_comm_destroy(tlb_device *dev);
 tlb_status tlb_comm_p2p_export(tlb_device *dev, void *handle64);
 tlb_status tlb_comm_p2p_import(tlb_device *dev, const void *handles);
 /* The same protocol with n_ranks emulated ranks on ONE device in one cooperative launch (test hook):
- * in/out are n_ranks x n floats on the host; `calls` all-reduces in a row, call k on inputs x (k+1). */
-tlb_status tlb_comm_p2p_selftest(tlb_device *dev, int n_ranks, int n, int calls, const float *in, float *out);
+ * out is n_ranks x n floats on the host; `calls` all-reduces in a row, call k on inputs x (k+1). With
+ * n_split > 0 every rank's input is the sum of n_split partial results (in: n_ranks x n_split x n floats),
+ * the form the exchange takes behind a K-split mul_mat; otherwise in is n_ranks x n floats. */
+tlb_status tlb_comm_p2p_selftest(tlb_device *dev, int n_ranks, int n, int calls, int n_split, const float *in, float *out);
 
 #ifdef __cplusplus
 }

@@ -103,7 +103,7 @@ SYMBOLS = {
     "tlb_comm_destroy": (C.c_int, [_P]),
     "tlb_comm_p2p_export": (C.c_int, [_P, _P]),
     "tlb_comm_p2p_import": (C.c_int, [_P, _P]),
-    "tlb_comm_p2p_selftest": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, _P, _P]),
+    "tlb_comm_p2p_selftest": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int, _P, _P]),
 }
 
 _lib = None

@@ -73,6 +73,8 @@ constexpr uint32_t AR_SPIN_LIMIT = 1u << 22;   // probes of a local flag, a few 
 
 struct ArRank {
     float *data;                 // n floats, reduced in place
+    const float *partial;        // n_split > 0: this rank's input is the sum of n_split partial results of n floats each
+    int n_split;                 // (the K split of the row-parallel mul_mat in front of the exchange), `data` is only written
     char *peer[AR_MAX_RANKS];    // exchange buffers of all ranks as mapped into this rank (own one included)
     int rank;
     int *err;
@@ -88,11 +90,21 @@ __device__ __forceinline__ void ar_body(const ArRank &a, int n, int n_ranks, int
     const int per = ((n / 4 + n_ctas - 1) / n_ctas);          // float4 per CTA
     const int v0 = c * per, v1 = min(n / 4, v0 + per);
     if (tid == 0) s_fail = 0;
-    // ---- push my chunk into slot [par][my rank] of every rank
-    const float4 *src = reinterpret_cast<const float4 *>(a.data);
-    for (int p = 0; p < n_ranks; p++) {
-        float4 *dst = reinterpret_cast<float4 *>(a.peer[p] + AR_DATA_OFF + ((size_t)par * AR_MAX_RANKS + a.rank) * AR_SLOT_BYTES);
-        for (int i = v0 + tid; i < v1; i += AR_THREADS) dst[i] = src[i];
+    // ---- push my chunk (first summed over the K split, in split order) into slot [par][my rank] of every rank
+    const float4 *src = reinterpret_cast<const float4 *>(a.n_split > 0 ? a.partial : a.data);
+    const size_t slot_off = AR_DATA_OFF + ((size_t)par * AR_MAX_RANKS + a.rank) * AR_SLOT_BYTES;
+    for (int i = v0 + tid; i < v1; i += AR_THREADS) {
+        float4 v = src[i];
+        for (int s0 = 1; s0 < a.n_split; s0 += 4) {
+            // four loads in flight before the adds that need them
+            float4 t[4];
+#pragma unroll
+            for (int k = 0; k < 4; k++) t[k] = s0 + k < a.n_split ? src[(size_t)(s0 + k) * (n / 4) + i] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                if (s0 + k < a.n_split) { v.x += t[k].x; v.y += t[k].y; v.z += t[k].z; v.w += t[k].w; }
+        }
+        for (int p = 0; p < n_ranks; p++) reinterpret_cast<float4 *>(a.peer[p] + slot_off)[i] = v;
     }
     __threadfence_system();
     __syncthreads();
@@ -151,18 +163,25 @@ struct Comm {
     bool p2p = false;
 };
 
-cudaError_t comm_allreduce_f32(tlb_device *dev, float *buf, size_t n, cudaStream_t st, int *err) {
-    if (!dev->comm || dev->comm->n_ranks == 1) return cudaSuccess;
+bool comm_p2p_takes(tlb_device *dev, size_t n) {
+    return dev->comm && dev->comm->n_ranks > 1 && dev->comm->p2p && n % 4 == 0 && n * 4 <= AR_SLOT_BYTES;
+}
+
+cudaError_t comm_allreduce_f32(tlb_device *dev, float *buf, size_t n, cudaStream_t st, int *err, const float *partial, int n_split) {
+    if (!dev->comm || dev->comm->n_ranks == 1) return n_split > 0 ? cudaErrorInvalidValue : cudaSuccess;
     Comm *c = dev->comm;
-    if (c->p2p && n % 4 == 0 && n * 4 <= AR_SLOT_BYTES && ((uintptr_t)buf & 15) == 0 && err) {
+    if (comm_p2p_takes(dev, n) && ((uintptr_t)buf & 15) == 0 && ((uintptr_t)partial & 15) == 0 && err) {
         ArRank a{};
         a.data = buf;
+        a.partial = partial;
+        a.n_split = partial ? n_split : 0;
         a.rank = c->rank;
         a.err = err;
         for (int p = 0; p < c->n_ranks; p++) a.peer[p] = c->peer[p];
         k_allreduce_oneshot<<<ar_grid(n), AR_THREADS, 0, st>>>(a, (int)n, c->n_ranks);
         return cudaGetLastError();
     }
+    if (n_split > 0) return cudaErrorInvalidValue;   // the caller asks comm_p2p_takes first
     const int r = nccl().AllReduce(buf, buf, n, ncclFloat32, ncclSum, c->comm, st);
     return r == ncclSuccess ? cudaSuccess : cudaErrorUnknown;
 }
@@ -265,13 +284,15 @@ tlb_status tlb_comm_p2p_import(tlb_device *dev, const void *handles) {
 
 // Single-GPU check of the all-reduce protocol: `n_ranks` emulated ranks (their buffers all on this
 // device) run as ONE cooperative launch; in[r] / out[r] are n floats per rank on the host.
-tlb_status tlb_comm_p2p_selftest(tlb_device *dev, int n_ranks, int n, int calls, const float *in, float *out) {
-    if (!dev || n_ranks < 1 || n_ranks > AR_MAX_RANKS || n < 4 || n % 4 || (size_t)n * 4 > AR_SLOT_BYTES || calls < 1 || !in || !out)
+tlb_status tlb_comm_p2p_selftest(tlb_device *dev, int n_ranks, int n, int calls, int n_split, const float *in, float *out) {
+    if (!dev || n_ranks < 1 || n_ranks > AR_MAX_RANKS || n < 4 || n % 4 || (size_t)n * 4 > AR_SLOT_BYTES || calls < 1 || n_split < 0 ||
+        n_split > 16 || !in || !out)
         return fail(TLB_INVALID, "tlb_comm_p2p_selftest: bad arguments");
+    const int parts = n_split > 0 ? n_split : 1;   // floats per rank in `in`: parts x n
     cudaSetDevice(dev->ordinal);
     ArAll all{};
     char *bufs[AR_MAX_RANKS] = {nullptr};
-    float *data[AR_MAX_RANKS] = {nullptr};
+    float *data[AR_MAX_RANKS] = {nullptr}, *part[AR_MAX_RANKS] = {nullptr};
     int *err = nullptr;
     cudaError_t e = cudaMalloc(&err, 256);
     if (e == cudaSuccess) e = cudaMemset(err, 0, 256);
@@ -279,21 +300,27 @@ tlb_status tlb_comm_p2p_selftest(tlb_device *dev, int n_ranks, int n, int calls,
         e = cudaMalloc(&bufs[r], AR_BUF_BYTES);
         if (e == cudaSuccess) e = cudaMemset(bufs[r], 0, AR_BUF_BYTES);
         if (e == cudaSuccess) e = cudaMalloc(&data[r], (size_t)n * 4);
+        if (e == cudaSuccess) e = cudaMemset(data[r], 0, (size_t)n * 4);
+        if (e == cudaSuccess && n_split > 0) e = cudaMalloc(&part[r], (size_t)parts * n * 4);
     }
     for (int r = 0; r < n_ranks && e == cudaSuccess; r++) {
         all.r[r].data = data[r];
+        all.r[r].partial = part[r];
+        all.r[r].n_split = n_split;
         all.r[r].rank = r;
         all.r[r].err = err;
         for (int p = 0; p < n_ranks; p++) all.r[r].peer[p] = bufs[p];
     }
     int flag = 0;
+    std::vector<float> h((size_t)n_ranks * parts * n);
     for (int call = 0; call < calls && e == cudaSuccess; call++) {
-        // every call reduces fresh inputs scaled by (call + 1), so a stale slot would show
-        for (int r = 0; r < n_ranks && e == cudaSuccess; r++) {
-            std::vector<float> h((size_t)n);
-            for (int i = 0; i < n; i++) h[i] = in[(size_t)r * n + i] * (float)(call + 1);
-            e = cudaMemcpy(data[r], h.data(), (size_t)n * 4, cudaMemcpyHostToDevice);
-        }
+        // every call reduces fresh inputs scaled by (call + 1), so a stale slot would show. The copies go
+        // through the launching stream: a plain cudaMemcpy from pageable memory may return before its DMA
+        // has landed, and the stream of this device does not wait for the default stream.
+        for (size_t i = 0; i < h.size(); i++) h[i] = in[i] * (float)(call + 1);
+        for (int r = 0; r < n_ranks && e == cudaSuccess; r++)
+            e = cudaMemcpyAsync(n_split > 0 ? part[r] : data[r], h.data() + (size_t)r * parts * n, (size_t)parts * n * 4, cudaMemcpyHostToDevice,
+                                dev->stream);
         if (e != cudaSuccess) break;
         void *args[] = {&all, &n, &n_ranks};
         e = cudaLaunchCooperativeKernel((void *)k_allreduce_emulated, dim3(ar_grid((size_t)n), n_ranks), dim3(AR_THREADS), args, 0, dev->stream);
@@ -304,6 +331,7 @@ tlb_status tlb_comm_p2p_selftest(tlb_device *dev, int n_ranks, int n, int calls,
     for (int r = 0; r < n_ranks; r++) {
         if (bufs[r]) cudaFree(bufs[r]);
         if (data[r]) cudaFree(data[r]);
+        if (part[r]) cudaFree(part[r]);
     }
     if (err) cudaFree(err);
     if (e != cudaSuccess) {

@@ -127,7 +127,9 @@ Layout plan(const Graph &g, const Leaves &leaves, const std::function<uint64_t(i
     }
     for (size_t pos = 0; pos < n; pos++) {
         const uint64_t bytes = scratch_bytes(g.nodes[pos]);
-        if (bytes > 0) blocks.push_back({g.nodes[pos], pos, pos, align_up(bytes), true, pos});
+        // a scratch block outlives its node by one position: the exchange that follows a K-split mul_mat
+        // reads the partial sums itself
+        if (bytes > 0) blocks.push_back({g.nodes[pos], pos, std::min(pos + 1, n - 1), align_up(bytes), true, pos});
     }
     std::stable_sort(blocks.begin(), blocks.end(), [](const Block &a, const Block &b) {
         if (a.first != b.first) return a.first < b.first;

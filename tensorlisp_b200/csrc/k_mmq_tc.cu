@@ -113,9 +113,13 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
     const int tid = threadIdx.x, warp = tid >> 5;
     if (tid == 0) TC_STAMP(0);
     const int gtile = blockIdx.x, split = blockIdx.y;
+    // (selected with constant indices: indexing kernel parameters with a run-time value makes the compiler
+    // copy them to local memory, and a tensor map must stay in parameter space)
     const int mat = (p.n_mats > 1 && gtile >= p.tile0[1]) + (p.n_mats > 2 && gtile >= p.tile0[2]);
-    const int row_tile = gtile - p.tile0[mat];
-    const CUtensorMap *wmap = &maps.m[mat];
+    const int row_tile = gtile - (mat == 0 ? 0 : (mat == 1 ? p.tile0[1] : p.tile0[2]));
+    const CUtensorMap *wmap = mat == 0 ? &maps.m[0] : (mat == 1 ? &maps.m[1] : &maps.m[2]);
+    const int64_t M_mat = mat == 0 ? p.M[0] : (mat == 1 ? p.M[1] : p.M[2]);
+    float *out_mat = mat == 0 ? p.out[0] : (mat == 1 ? p.out[1] : p.out[2]);
     const int sb0 = split * p.sb_per_split;
     const int nsb = min(p.sb_per_split, p.nsb - sb0);      // super-blocks of this CTA (>= 1 by construction)
     if (tid == 0) {
@@ -258,10 +262,10 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
             if (tid == 32) TC_STAMP(97 + 2 * i);
         }
         const int64_t row = (int64_t)row_tile * ROWS + row_in_tile;
-        if (row < p.M[mat]) {
+        if (row < M_mat) {
             // partial sums [split][N][M] and the outputs of a group are dense; a single matrix may have its own stride
-            const int64_t ldo = (p.n_split > 1 || p.n_mats > 1) ? p.M[mat] : p.ldy;
-            float *o = p.out[mat] + (size_t)split * p.N * ldo + row;
+            const int64_t ldo = (p.n_split > 1 || p.n_mats > 1) ? M_mat : p.ldy;
+            float *o = out_mat + (size_t)split * p.N * ldo + row;
 #pragma unroll
             for (int c = 0; c < CW; c++)
                 if (col0 + c < p.N) o[(size_t)(col0 + c) * ldo] = yacc[c];
@@ -390,28 +394,42 @@ struct ReduceSegs {
     int64_t seg_n[TC_MAX_MATS], seg_off[TC_MAX_MATS];
     int n_segs;
 };
-__global__ void k_mmq_reduce(const float *__restrict__ part, ReduceSegs g, int64_t total, int n_split) {
+template <int NS>   // upper bound of n_split: exactly that many loads are issued before the first add
+__global__ void __launch_bounds__(256) k_mmq_reduce(const float *__restrict__ part, ReduceSegs g, int64_t total, int n_split) {
     griddep_launch();
     griddep_wait();
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
-    int j = 0;
-    while (j + 1 < g.n_segs && i >= g.seg_n[j]) {
-        i -= g.seg_n[j];
-        j++;
+    // segment of element i, chosen with constant indices into the parameter struct
+    int64_t stride = g.seg_n[0], off = g.seg_off[0];
+    float *__restrict__ y = g.y[0];
+    if (g.n_segs > 1 && i >= g.seg_n[0]) {
+        i -= g.seg_n[0];
+        stride = g.seg_n[1]; off = g.seg_off[1]; y = g.y[1];
+        if (g.n_segs > 2 && i >= g.seg_n[1]) {
+            i -= g.seg_n[1];
+            stride = g.seg_n[2]; off = g.seg_off[2]; y = g.y[2];
+        }
     }
-    const float *p = part + g.seg_off[j] + i;
-    const int64_t stride = g.seg_n[j];
+    const float *p = part + off + i;
     // all loads go out before the first add: a warp issues in order, and an add right behind its load
     // would make every L2 round trip wait for the one before it
-    float v[16];
+    float v[NS];
 #pragma unroll
-    for (int k = 0; k < 16; k++) v[k] = k < n_split ? p[(size_t)k * stride] : 0.f;
+    for (int k = 0; k < NS; k++) v[k] = k < n_split ? p[(size_t)k * stride] : 0.f;
     float s = 0.f;
 #pragma unroll
-    for (int k = 0; k < 16; k++)
+    for (int k = 0; k < NS; k++)
         if (k < n_split) s += v[k];
-    g.y[j][i] = s;
+    y[i] = s;
+}
+
+static cudaError_t launch_reduce_segs(const float *partial, const ReduceSegs &g, int64_t total, int n_split, cudaStream_t st) {
+    const dim3 grid((unsigned)((total + 255) / 256)), block(256);
+    if (n_split <= 2) return launch_pdl(k_mmq_reduce<2>, grid, block, 0, st, partial, g, total, n_split);
+    if (n_split <= 4) return launch_pdl(k_mmq_reduce<4>, grid, block, 0, st, partial, g, total, n_split);
+    if (n_split <= 8) return launch_pdl(k_mmq_reduce<8>, grid, block, 0, st, partial, g, total, n_split);
+    return launch_pdl(k_mmq_reduce<16>, grid, block, 0, st, partial, g, total, n_split);
 }
 
 // ---------------------------------------------------------------- host side
@@ -502,14 +520,14 @@ void launch_mmq_reduce(const float *partial, float *y, int64_t total, int n_spli
     g.y[0] = y;
     g.seg_n[0] = total;
     g.seg_off[0] = 0;
-    launch_pdl(k_mmq_reduce, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, partial, g, total, n_split);
+    launch_reduce_segs(partial, g, total, n_split, st);
 }
 
 bool tc_available() { return encode_tiled() != nullptr; }
 
 // n_mats weight matrices [M[j] x K] sharing the activations; y[j] dense [N][M[j]] when n_mats > 1 or K is split
 cudaError_t launch_mmq_tc_group(const TcPlan &t, int n_mats, const void *const *W, int64_t K, const int64_t *M, int64_t N, const void *blobs,
-                                float *const *y, int64_t ldy, void *partial, int *err, cudaStream_t st) {
+                                float *const *y, int64_t ldy, void *partial, int *err, cudaStream_t st, bool leave_partial) {
     if (n_mats < 1 || n_mats > TC_MAX_MATS || (n_mats > 1 && t.n_col_chunks != 1)) return cudaErrorInvalidValue;
     if (t.n_split > 16) return cudaErrorInvalidValue;
     TcMaps maps;
@@ -560,10 +578,10 @@ cudaError_t launch_mmq_tc_group(const TcPlan &t, int n_mats, const void *const *
             default: e = launch_pdl(k_mmq_tc_q4k<64, 5, 3>, grid, dim3(tc::THREADS), tc_smem<64, 5, 3>(), st, maps, p); break;
         }
         if (e != cudaSuccess) return e;
-        if (t.n_split > 1) {
+        if (t.n_split > 1 && !leave_partial) {
             if (n_mats == 1 && ldy != M[0]) return cudaErrorInvalidValue;   // the reduce writes dense columns
             segs.n_segs = n_mats;
-            e = launch_pdl(k_mmq_reduce, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, (const float *)partial, segs, total, t.n_split);
+            e = launch_reduce_segs((const float *)partial, segs, total, t.n_split, st);
             if (e != cudaSuccess) return e;
         }
     }
@@ -571,10 +589,10 @@ cudaError_t launch_mmq_tc_group(const TcPlan &t, int n_mats, const void *const *
 }
 
 cudaError_t launch_mmq_tc(const TcPlan &t, const void *W, int64_t K, int64_t M, int64_t N, const void *blobs, float *y,
-                          int64_t ldy, void *partial, int *err, cudaStream_t st) {
+                          int64_t ldy, void *partial, int *err, cudaStream_t st, bool leave_partial) {
     const void *Ws[1] = {W};
     float *ys[1] = {y};
-    return launch_mmq_tc_group(t, 1, Ws, K, &M, N, blobs, ys, ldy, partial, err, st);
+    return launch_mmq_tc_group(t, 1, Ws, K, &M, N, blobs, ys, ldy, partial, err, st, leave_partial);
 }
 
 }  // namespace tlb

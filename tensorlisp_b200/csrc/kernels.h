@@ -56,11 +56,12 @@ struct TcPlan {
 bool mmq_tc_supported(uint32_t type, int64_t K, int64_t M, int64_t N);
 TcPlan mmq_tc_plan(int64_t K, int64_t M, int64_t N, int sm_count);
 cudaError_t launch_act_pack_tc(const ActLayout &a, const void *act, int npad, void *blobs, cudaStream_t st);
+// leave_partial: with a K split, do not add the partial sums [split][N][M] up (the caller's next kernel does)
 cudaError_t launch_mmq_tc(const TcPlan &t, const void *W, int64_t K, int64_t M, int64_t N, const void *blobs, float *y,
-                          int64_t ldy, void *partial, int *err, cudaStream_t st);
+                          int64_t ldy, void *partial, int *err, cudaStream_t st, bool leave_partial = false);
 // up to 3 matrices [M[j] x K] that share the activations in one launch; outputs dense [N][M[j]]
 cudaError_t launch_mmq_tc_group(const TcPlan &t, int n_mats, const void *const *W, int64_t K, const int64_t *M, int64_t N, const void *blobs,
-                                float *const *y, int64_t ldy, void *partial, int *err, cudaStream_t st);
+                                float *const *y, int64_t ldy, void *partial, int *err, cudaStream_t st, bool leave_partial = false);
 void mmq_tc_configure();
 bool tc_available();   // the driver offers cuTensorMapEncodeTiled
 

@@ -347,6 +347,14 @@ void lower_simple(L &l) {
     }
 }
 
+// the node after this one is an ALLREDUCE of this node's result
+bool allreduce_follows(const L &l) {
+    const Graph &g = *l.c.g;
+    if ((size_t)l.pos + 1 >= g.nodes.size()) return false;
+    const Tensor &nx = g.tensors[g.nodes[l.pos + 1]];
+    return nx.op == "ALLREDUCE" && nx.src[0] == l.id;
+}
+
 // ---- MUL_MAT (lower.rs:543-571). Quantized weights take int8 activations quantized once per
 // distinct activation tensor by a QUANT_ACT node that rewrite_graph put in src[2].
 void lower_mul_mat(L &l) {
@@ -393,9 +401,15 @@ void lower_mul_mat(L &l) {
         ps.off = sc < 0 ? 0 : (uint64_t)sc;
         const uint64_t blob_off = a.bytes;
         const bool q8 = tw.ty == TLB_TYPE_Q8_0;
+        // a row-parallel projection: when the exchange that follows runs over peer memory, it adds the K-split
+        // partial sums itself (decided at launch: the communicator may be set up after the program is compiled)
+        const bool ar_next = !q8 && tp.n_split > 1 && tp.n_col_chunks == 1 && allreduce_follows(l);
+        tlb_device *dev = l.c.dev;
+        const size_t n_out = (size_t)(N * M);
         l.push([=](const RunCtx &r) {
+            const bool leave = ar_next && comm_p2p_takes(dev, n_out);
             return q8 ? launch_mmq_tc8(tp, r.at(pw), K, M, N, r.at(pq) + blob_off, (float *)r.at(pd), M, r.at(ps), r.err, r.stream)
-                      : launch_mmq_tc(tp, r.at(pw), K, M, N, r.at(pq) + blob_off, (float *)r.at(pd), M, r.at(ps), r.err, r.stream);
+                      : launch_mmq_tc(tp, r.at(pw), K, M, N, r.at(pq) + blob_off, (float *)r.at(pd), M, r.at(ps), r.err, r.stream, leave);
         });
         return;
     }
@@ -665,7 +679,33 @@ void lower_allreduce(L &l) {
     const Place pd = l.place(l.id);
     const size_t n = (size_t)t.nelements();
     tlb_device *dev = l.c.dev;
-    l.push([=](const RunCtx &r) { return comm_allreduce_f32(dev, (float *)r.at(pd), n, r.stream, r.err); });
+    // behind a K-split tensor-core mul_mat the peer-memory exchange reads the partial sums itself (same
+    // conditions as in lower_mul_mat, which then leaves them un-added)
+    int n_split = 0;
+    Place ps;
+    const Graph &g = *l.c.g;
+    if (l.pos > 0 && g.nodes[l.pos - 1] == a) {
+        const Tensor &mm = g.tensors[a];
+        if (mm.op == "MUL_MAT" && mm.src[0] >= 0 && mm.src[1] >= 0 && mm.src[2] >= 0 && is_qact(g.tensors[mm.src[2]].op) &&
+            g.tensors[mm.src[2]].op_params[1] > 0 && !getenv("TLB_MM_GENERIC") && !getenv("TLB_NO_TC")) {
+            const Tensor &tw = g.tensors[mm.src[0]], &tx = g.tensors[mm.src[1]];
+            const bool plain2d = tw.ne[2] * tw.ne[3] * mm.ne[2] * mm.ne[3] == 1 && tw.nb[1] == tw.row_size() && mm.is_contiguous();
+            if (plain2d && tw.ty == TLB_TYPE_Q4_K && tc_supported(tw.ty, tw.ne[0], tw.ne[1], tx.ne[1])) {
+                const TcPlan tp = tc_plan(tw.ty, tw.ne[0], tw.ne[1], tx.ne[1], dev->prop.multiProcessorCount);
+                const int64_t sc = l.c.layout->scratch[l.pos - 1];
+                if (tp.n_split > 1 && tp.n_col_chunks == 1 && sc >= 0) {
+                    n_split = tp.n_split;
+                    ps.buf = BUF_ARENA;
+                    ps.off = (uint64_t)sc;
+                }
+            }
+        }
+    }
+    l.push([=](const RunCtx &r) {
+        if (n_split > 0 && comm_p2p_takes(dev, n))
+            return comm_allreduce_f32(dev, (float *)r.at(pd), n, r.stream, r.err, (const float *)r.at(ps), n_split);
+        return comm_allreduce_f32(dev, (float *)r.at(pd), n, r.stream, r.err);
+    });
 }
 
 }  // namespace

@@ -163,7 +163,10 @@ void lower_node(const LowerCtx &c, int32_t id, int pos, std::vector<Dispatch> &o
 uint64_t node_scratch_bytes(const Graph &g, int32_t id, int sm_count);
 // comm.cu: sum over the ranks of the device's communicator, in place (no-op without one)
 // (err: the device error word of bounded waits; the peer-memory path needs it, NCCL is used without it)
-cudaError_t comm_allreduce_f32(tlb_device *dev, float *buf, size_t n, cudaStream_t st, int *err);
+// partial / n_split: the input is the sum of n_split partial results (n floats each) instead of buf; only the
+// peer-memory path takes that form (ask comm_p2p_takes first)
+cudaError_t comm_allreduce_f32(tlb_device *dev, float *buf, size_t n, cudaStream_t st, int *err, const float *partial = nullptr, int n_split = 0);
+bool comm_p2p_takes(tlb_device *dev, size_t n);
 int comm_ranks(tlb_device *dev);
 // IR rewrites before planning (fusion, shared activation quantization); fuse.cpp
 void rewrite_graph(Graph &g);

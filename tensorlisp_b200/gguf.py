@@ -73,7 +73,10 @@ class GgufFile:
         self.data_offset = (self._p + self.alignment - 1) // self.alignment * self.alignment
 
     def close(self) -> None:
-        self._m.close()
+        try:
+            self._m.close()
+        except BufferError:
+            pass   # tensor views handed out by tensor_bytes() still exist: the mapping goes away with the last of them
         self._f.close()
 
     def _unpack(self, fmt: str):
