@@ -197,7 +197,8 @@ def run_ours(args) -> dict:
                 handles = [None] * world
                 dist.all_gather_object(handles, native.comm_p2p_export())
                 native.comm_p2p_import(handles)
-                allreduce = "one-shot over peer memory"
+                allreduce = ("one-shot over peer memory" if world > 2 or os.environ.get("TLB_P2P_ALLREDUCE") == "1"
+                             else "nccl (peer memory set up; used above 2 ranks)")
             except Exception as e:
                 allreduce = "nccl (peer memory unavailable: %s)" % e
 

@@ -203,7 +203,8 @@ tlb_status tlb_comm_destroy(tlb_device *dev);
  * exchange buffer, returns a 64-byte CUDA IPC handle), the host gathers the handles of all ranks in
  * rank order (n_ranks x 64 bytes) and every rank calls import. Up to 8 ranks of one box. The kernel's
  * waits are bounded; a rank that never arrives makes tlb_program_run fail instead of hanging.
- * TLB_NO_P2P_ALLREDUCE=1 keeps NCCL. */
+ * Used by default with more than 2 ranks (measured faster there); TLB_P2P_ALLREDUCE=1 turns it on for 2
+ * ranks, TLB_NO_P2P_ALLREDUCE=1 keeps NCCL everywhere. */
 tlb_status tlb_comm_p2p_export(tlb_device *dev, void *handle64);
 tlb_status tlb_comm_p2p_import(tlb_device *dev, const void *handles);
 /* The same protocol with n_ranks emulated ranks on ONE device in one cooperative launch (test hook):

@@ -350,6 +350,7 @@ void lower_simple(L &l) {
 // the node after this one is an ALLREDUCE of this node's result
 bool allreduce_follows(const L &l) {
     const Graph &g = *l.c.g;
+    if (getenv("TLB_SPLITK_REDUCE_LAUNCH")) return false;   // keep the separate launch that adds the partial sums
     if ((size_t)l.pos + 1 >= g.nodes.size()) return false;
     const Tensor &nx = g.tensors[g.nodes[l.pos + 1]];
     return nx.op == "ALLREDUCE" && nx.src[0] == l.id;
@@ -684,7 +685,7 @@ void lower_allreduce(L &l) {
     int n_split = 0;
     Place ps;
     const Graph &g = *l.c.g;
-    if (l.pos > 0 && g.nodes[l.pos - 1] == a) {
+    if (l.pos > 0 && g.nodes[l.pos - 1] == a && !getenv("TLB_SPLITK_REDUCE_LAUNCH")) {
         const Tensor &mm = g.tensors[a];
         if (mm.op == "MUL_MAT" && mm.src[0] >= 0 && mm.src[1] >= 0 && mm.src[2] >= 0 && is_qact(g.tensors[mm.src[2]].op) &&
             g.tensors[mm.src[2]].op_params[1] > 0 && !getenv("TLB_MM_GENERIC") && !getenv("TLB_NO_TC")) {
