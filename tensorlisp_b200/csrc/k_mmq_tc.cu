@@ -17,6 +17,7 @@
 // while the next super-block is being expanded and multiplied. K is split across CTAs; partial sums
 // go to scratch and k_mmq_reduce adds them in a fixed order (deterministic).
 #include <algorithm>
+#include <cstdlib>
 #include <cuda.h>
 #include <cuda_fp16.h>
 
@@ -92,7 +93,22 @@ struct TcParams {
     int N, npad, nsb, sb_per_split, n_split;
     int64_t ldy;          // elements between output columns
     int *err;
+    // stream-K (streamk != 0): the grid is one CTA per SM; CTA c works through the units [c T / G, (c+1) T / G) of
+    // the flattened (row tile, super-block) space, T = total tiles x nsb, so every SM gets the same number of
+    // super-blocks whatever the tile count. A tile that one CTA covers completely is written to y; a tile cut by
+    // a CTA boundary (at most one cut per tile: the plan requires T / G >= nsb) leaves two partial results
+    // sk_partial[tile][0 = has the tile's start, 1 = has its end][N][128], added by k_mmq_sk_fixup.
+    int streamk, total_tiles;
+    float *sk_partial;
 };
+
+// CTA that works on unit u when G CTAs split T units as above
+__host__ __device__ inline int sk_cta_of(int64_t u, int64_t T, int G) {
+    int c = (int)(u * G / T);
+    while (c + 1 < G && (int64_t)(c + 1) * T / G <= u) c++;
+    while (c > 0 && (int64_t)c * T / G > u) c--;
+    return c;
+}
 
 template <int NPAD, int RAW_STAGES, int ACT_STAGES>
 __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_constant__ TcMaps maps, TcParams p) {
@@ -112,16 +128,26 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
 
     const int tid = threadIdx.x, warp = tid >> 5;
     if (tid == 0) TC_STAMP(0);
-    const int gtile = blockIdx.x, split = blockIdx.y;
-    // (selected with constant indices: indexing kernel parameters with a run-time value makes the compiler
-    // copy them to local memory, and a tensor map must stay in parameter space)
-    const int mat = (p.n_mats > 1 && gtile >= p.tile0[1]) + (p.n_mats > 2 && gtile >= p.tile0[2]);
-    const int row_tile = gtile - (mat == 0 ? 0 : (mat == 1 ? p.tile0[1] : p.tile0[2]));
-    const CUtensorMap *wmap = mat == 0 ? &maps.m[0] : (mat == 1 ? &maps.m[1] : &maps.m[2]);
-    const int64_t M_mat = mat == 0 ? p.M[0] : (mat == 1 ? p.M[1] : p.M[2]);
-    float *out_mat = mat == 0 ? p.out[0] : (mat == 1 ? p.out[1] : p.out[2]);
-    const int sb0 = split * p.sb_per_split;
-    const int nsb = min(p.sb_per_split, p.nsb - sb0);      // super-blocks of this CTA (>= 1 by construction)
+    // This CTA's units of the flattened (row tile, super-block) space: one K range of one tile (grid = tiles x
+    // splits), or with stream-K an equal share of all units.
+    const int split = p.streamk ? 0 : blockIdx.y;
+    int64_t u0;
+    int nsb;   // units of this CTA
+    if (p.streamk) {
+        const int64_t T = (int64_t)p.total_tiles * p.nsb;
+        u0 = (int64_t)blockIdx.x * T / gridDim.x;
+        nsb = (int)((int64_t)(blockIdx.x + 1) * T / gridDim.x - u0);
+    } else {
+        const int sb0 = split * p.sb_per_split;
+        u0 = (int64_t)blockIdx.x * p.nsb + sb0;
+        nsb = min(p.sb_per_split, p.nsb - sb0);            // >= 1 by construction
+    }
+    const int64_t u1 = u0 + nsb;
+    // matrix and row tile of a global tile index (selected with constant indices: indexing kernel parameters
+    // with a run-time value makes the compiler copy them to local memory, and a tensor map must stay in
+    // parameter space)
+    auto mat_of = [&](int gtile) { return (p.n_mats > 1 && gtile >= p.tile0[1]) + (p.n_mats > 2 && gtile >= p.tile0[2]); };
+    auto tile_in_mat = [&](int gtile, int mat) { return gtile - (mat == 0 ? 0 : (mat == 1 ? p.tile0[1] : p.tile0[2])); };
     if (tid == 0) {
         for (int i = 0; i < RAW_STAGES; i++) {
             mbar_init(&bar_raw[i], 1);
@@ -149,15 +175,25 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
     const uint32_t tmem_base = tmem_base_s;
     if (tid == 0) TC_STAMP(1);
 
-    auto load_raw = [&](int i) {   // super-block i of this CTA -> raw stage i % RAW_STAGES
+    // (tile, super-block) of the first unit; the loaders and the epilogue walk on from there without divisions
+    const int tile_first = (int)(u0 / p.nsb), sb_first = (int)(u0 - (int64_t)tile_first * p.nsb);
+    int lr_tile = tile_first, lr_sb = sb_first, la_sb = sb_first;   // next unit of load_raw / load_act (one thread each)
+    auto load_raw = [&](int i) {   // unit i of this CTA -> raw stage i % RAW_STAGES; called for i = 0, 1, 2, ...
         const int s = i % RAW_STAGES;
+        const int mat = mat_of(lr_tile);
+        const CUtensorMap *wmap = mat == 0 ? &maps.m[0] : (mat == 1 ? &maps.m[1] : &maps.m[2]);
         mbar_expect_tx(&bar_raw[s], RAW_BYTES);
-        tma_2d(raw + s * RAW_BYTES, wmap, (sb0 + i) * 144, row_tile * ROWS, &bar_raw[s]);
+        tma_2d(raw + s * RAW_BYTES, wmap, lr_sb * 144, tile_in_mat(lr_tile, mat) * ROWS, &bar_raw[s]);
+        if (++lr_sb == p.nsb) {
+            lr_sb = 0;
+            lr_tile++;
+        }
     };
-    auto load_act = [&](int i) {
+    auto load_act = [&](int i) {   // called for i = 0, 1, 2, ...
         const int s = i % ACT_STAGES;
         mbar_expect_tx(&bar_act[s], BLOB);
-        bulk_g2s(actb + s * BLOB, p.act + (size_t)(sb0 + i) * BLOB, BLOB, &bar_act[s]);
+        bulk_g2s(actb + s * BLOB, p.act + (size_t)la_sb * BLOB, BLOB, &bar_act[s]);
+        if (++la_sb == p.nsb) la_sb = 0;
     };
     // the weights do not depend on the kernel before this one: their first loads go out before the
     // dependency wait; activations (and everything downstream of them) come after it
@@ -232,8 +268,39 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
         float yacc[CW];
 #pragma unroll
         for (int c = 0; c < CW; c++) yacc[c] = 0.f;
+        // the sums of a finished tile go out: to y, to the K-split partial sums, or (stream-K, tile cut by a CTA
+        // boundary) to one of the tile's two stream-K partial results
+        auto store_tile = [&](int gtile) {
+            const int mat = mat_of(gtile);
+            const int64_t M_mat = mat == 0 ? p.M[0] : (mat == 1 ? p.M[1] : p.M[2]);
+            float *out_mat = mat == 0 ? p.out[0] : (mat == 1 ? p.out[1] : p.out[2]);
+            const int64_t row = (int64_t)tile_in_mat(gtile, mat) * ROWS + row_in_tile;
+            const int64_t t0 = (int64_t)gtile * p.nsb;
+            if (p.streamk && (t0 < u0 || t0 + p.nsb > u1)) {
+                float *o = p.sk_partial + ((size_t)gtile * 2 + (t0 >= u0 ? 0 : 1)) * p.N * ROWS + row_in_tile;
+#pragma unroll
+                for (int c = 0; c < CW; c++)
+                    if (col0 + c < p.N) o[(size_t)(col0 + c) * ROWS] = yacc[c];
+            } else if (row < M_mat) {
+                // partial sums [split][N][M] and the outputs of a group are dense; a single matrix may have its own stride
+                const int64_t ldo = (p.n_split > 1 || p.n_mats > 1) ? M_mat : p.ldy;
+                float *o = out_mat + (size_t)split * p.N * ldo + row;
+#pragma unroll
+                for (int c = 0; c < CW; c++)
+                    if (col0 + c < p.N) o[(size_t)(col0 + c) * ldo] = yacc[c];
+            }
+        };
+        int cur_tile = tile_first, e_sb = sb_first;
         for (int i = 0; i < nsb; i++) {
             const int b = i & 1;
+            if (e_sb == p.nsb) {   // stream-K only: the previous unit was the last one of its tile
+                store_tile(cur_tile);
+#pragma unroll
+                for (int c = 0; c < CW; c++) yacc[c] = 0.f;
+                cur_tile++;
+                e_sb = 0;
+            }
+            e_sb++;
             mbar_wait_relaxed(&bar_mma[b], (uint32_t)((i >> 1) & 1), fail);
             tc_fence_after();
             if (tid == 32) TC_STAMP(96 + 2 * i);
@@ -261,15 +328,7 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
             mbar_arrive(&bar_actfree[i % ACT_STAGES]);
             if (tid == 32) TC_STAMP(97 + 2 * i);
         }
-        const int64_t row = (int64_t)row_tile * ROWS + row_in_tile;
-        if (row < M_mat) {
-            // partial sums [split][N][M] and the outputs of a group are dense; a single matrix may have its own stride
-            const int64_t ldo = (p.n_split > 1 || p.n_mats > 1) ? M_mat : p.ldy;
-            float *o = out_mat + (size_t)split * p.N * ldo + row;
-#pragma unroll
-            for (int c = 0; c < CW; c++)
-                if (col0 + c < p.N) o[(size_t)(col0 + c) * ldo] = yacc[c];
-        }
+        store_tile(cur_tile);
     } else {
         // a warp may only touch the 32 TMEM lanes of its quadrant (warp % 4): that fixes its rows
         const int dt = tid - DEQ_WARP0 * 32;
@@ -424,6 +483,31 @@ __global__ void __launch_bounds__(256) k_mmq_reduce(const float *__restrict__ pa
     y[i] = s;
 }
 
+// stream-K: a tile cut by a CTA boundary has two partial results; their sum (start part + end part) is the tile
+struct SkFixup {
+    const float *partial;
+    float *y[TC_MAX_MATS];
+    int64_t M[TC_MAX_MATS];
+    int tile0[TC_MAX_MATS + 1];
+    int n_mats, N, nsb, total_tiles, n_ctas;
+};
+__global__ void __launch_bounds__(256) k_mmq_sk_fixup(SkFixup f) {
+    griddep_launch();
+    griddep_wait();
+    const int gtile = blockIdx.x;
+    const int64_t T = (int64_t)f.total_tiles * f.nsb, t0 = (int64_t)gtile * f.nsb;
+    if (sk_cta_of(t0, T, f.n_ctas) == sk_cta_of(t0 + f.nsb - 1, T, f.n_ctas)) return;   // one CTA had the whole tile
+    const int mat = (f.n_mats > 1 && gtile >= f.tile0[1]) + (f.n_mats > 2 && gtile >= f.tile0[2]);
+    const int64_t M_mat = mat == 0 ? f.M[0] : (mat == 1 ? f.M[1] : f.M[2]);
+    float *y = mat == 0 ? f.y[0] : (mat == 1 ? f.y[1] : f.y[2]);
+    const int64_t row0 = (int64_t)(gtile - (mat == 0 ? 0 : (mat == 1 ? f.tile0[1] : f.tile0[2]))) * tc::ROWS;
+    const float *p0 = f.partial + (size_t)gtile * 2 * f.N * tc::ROWS, *p1 = p0 + (size_t)f.N * tc::ROWS;
+    for (int i = threadIdx.x; i < f.N * tc::ROWS; i += blockDim.x) {
+        const int n = i / tc::ROWS, r = i % tc::ROWS;
+        if (row0 + r < M_mat) y[(size_t)n * M_mat + row0 + r] = p0[i] + p1[i];
+    }
+}
+
 static cudaError_t launch_reduce_segs(const float *partial, const ReduceSegs &g, int64_t total, int n_split, cudaStream_t st) {
     const dim3 grid((unsigned)((total + 255) / 256)), block(256);
     if (n_split <= 2) return launch_pdl(k_mmq_reduce<2>, grid, block, 0, st, partial, g, total, n_split);
@@ -484,10 +568,23 @@ TcPlan mmq_tc_plan(int64_t K, int64_t M, int64_t N, int sm_count) {
     }
     t.n_split = best;
     t.sb_per_split = (t.nsb + best - 1) / best;
+    // stream-K when the tiles make several waves: 2.3 us start + units per CTA + 2.5 us fix-up, against whole
+    // waves of tiles. Measured on B200: [128256 x 4096] x 32 (6.8 waves) 144 -> 126 us; gate + up of an 8B layer
+    // as one launch (1.5 waves) came out 3 us SLOWER per layer than two launches, hence the floor of 2.5 waves.
+    t.streamk = 0;
+    if (tiles * 2 >= (int64_t)sm_count * 5 && N <= t.npad && !getenv("TLB_NO_STREAMK")) {
+        const double sk = 2.3 + (double)((tiles * t.nsb + sm_count - 1) / sm_count) * 1.0 + 2.5;
+        if (sk < best_score) {
+            t.streamk = sm_count;
+            t.n_split = 1;
+            t.sb_per_split = t.nsb;
+        }
+    }
     t.n_col_chunks = (int)((N + t.npad - 1) / t.npad);
     t.blob_unit = (uint64_t)tc_blob_bytes(t.npad);
     t.blob_bytes = (uint64_t)t.n_col_chunks * t.nsb * t.blob_unit;
-    t.partial_bytes = best > 1 ? (uint64_t)best * std::min<int64_t>(N, t.npad) * M * 4 : 0;
+    t.partial_bytes = t.streamk ? (uint64_t)tiles * 2 * std::min<int64_t>(N, t.npad) * tc::ROWS * 4
+                                : (t.n_split > 1 ? (uint64_t)t.n_split * std::min<int64_t>(N, t.npad) * M * 4 : 0);
     return t;
 }
 
@@ -549,7 +646,11 @@ cudaError_t launch_mmq_tc_group(const TcPlan &t, int n_mats, const void *const *
     base.n_split = t.n_split;
     base.err = err;
     base.ldy = ldy;
-    dim3 grid((unsigned)tiles, (unsigned)t.n_split);
+    base.total_tiles = tiles;
+    base.streamk = t.streamk;
+    base.sk_partial = (float *)partial;
+    if (t.streamk && (t.n_split != 1 || t.n_col_chunks != 1 || (int64_t)tiles * t.nsb / t.streamk < t.nsb)) return cudaErrorInvalidValue;
+    dim3 grid(t.streamk ? (unsigned)t.streamk : (unsigned)tiles, (unsigned)t.n_split);
     cudaError_t e = cudaSuccess;
     // more columns than one launch takes (prefill): one launch per chunk of npad columns
     for (int c = 0; c < t.n_col_chunks; c++) {
@@ -578,6 +679,23 @@ cudaError_t launch_mmq_tc_group(const TcPlan &t, int n_mats, const void *const *
             default: e = launch_pdl(k_mmq_tc_q4k<64, 5, 3>, grid, dim3(tc::THREADS), tc_smem<64, 5, 3>(), st, maps, p); break;
         }
         if (e != cudaSuccess) return e;
+        if (t.streamk) {
+            SkFixup f{};
+            f.partial = (const float *)partial;
+            for (int j = 0; j < n_mats; j++) {
+                f.y[j] = y[j];
+                f.M[j] = M[j];
+            }
+            for (int j = 0; j <= TC_MAX_MATS; j++) f.tile0[j] = base.tile0[j];
+            f.n_mats = n_mats;
+            f.N = (int)nc;
+            f.nsb = t.nsb;
+            f.total_tiles = tiles;
+            f.n_ctas = t.streamk;
+            if (n_mats == 1 && ldy != M[0]) return cudaErrorInvalidValue;   // the fix-up writes dense columns
+            e = launch_pdl(k_mmq_sk_fixup, dim3((unsigned)tiles), dim3(256), 0, st, f);
+            if (e != cudaSuccess) return e;
+        }
         if (t.n_split > 1 && !leave_partial) {
             if (n_mats == 1 && ldy != M[0]) return cudaErrorInvalidValue;   // the reduce writes dense columns
             segs.n_segs = n_mats;

@@ -356,6 +356,7 @@ TcPlan mmq_tc8_plan(int64_t K, int64_t M, int64_t N, int sm_count) {
     }
     t.n_split = best;
     t.sb_per_split = (t.nsb + best - 1) / best;
+    t.streamk = 0;
     t.n_col_chunks = (int)((N + t.npad - 1) / t.npad);
     t.blob_unit = (uint64_t)tc8_blob_bytes(t.npad);
     t.blob_bytes = (uint64_t)t.n_col_chunks * t.nsb * t.blob_unit;

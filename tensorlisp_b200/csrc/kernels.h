@@ -48,6 +48,7 @@ void gemv_configure();  // sets the dynamic shared-memory attributes once per pr
 // Q4_K weights x 5..64 activation columns on tcgen05 (f16 operands built from the integer codes).
 struct TcPlan {
     int npad, nsb, n_split, sb_per_split;
+    int streamk;             // > 0: that many CTAs share all (row tile, super-block) units equally (k_mmq_tc.cu)
     int n_col_chunks;        // activation columns are processed npad at a time: one launch per chunk
     uint64_t blob_unit;      // bytes of one packed blob (one chunk of columns, one super-block / stage)
     uint64_t blob_bytes;     // packed activation blobs: [chunk][super-block] x blob_unit

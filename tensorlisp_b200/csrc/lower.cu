@@ -459,7 +459,7 @@ void lower_mul_mat_group(L &l) {
     if (tp.npad != l.T(qa).op_params[1] || tp.n_col_chunks != 1) throw std::string("activation blobs were packed for another column count");
     const ActLayout a = act_layout(ACT_Q8_K, K, tx.nrows());
     const int64_t sc = l.c.layout->scratch[l.pos];
-    if (tp.n_split > 1 && sc < 0) throw std::string("split-K scratch was not planned");
+    if (tp.partial_bytes > 0 && sc < 0) throw std::string("split-K scratch was not planned");
     Place ps;
     ps.buf = BUF_ARENA;
     ps.off = sc < 0 ? 0 : (uint64_t)sc;
@@ -722,8 +722,7 @@ uint64_t node_scratch_bytes(const Graph &g, int32_t id, int sm_count) {
         int64_t Msum = 0;
         for (int s : {0, 3, 5})
             if (t.src[s] >= 0) Msum += g.tensors[t.src[s]].ne[1];
-        const TcPlan tp = mmq_tc_plan(tx.ne[0], Msum, tx.ne[1], sm_count);
-        return tp.n_split > 1 ? (uint64_t)tp.n_split * tx.ne[1] * Msum * 4 : 0;
+        return mmq_tc_plan(tx.ne[0], Msum, tx.ne[1], sm_count).partial_bytes;
     }
     if (t.op == "MUL_MAT" && t.src[0] >= 0 && t.src[1] >= 0 && t.src[2] >= 0 && is_qact(g.tensors[t.src[2]].op) &&
         g.tensors[t.src[2]].op_params[1] > 0) {
@@ -1124,9 +1123,10 @@ void fuse_rope_cache(Graph &g) {
 }
 
 
-// Consecutive tensor-core mul_mats over the same quantized activations (wq, wk, wv of a layer) become one
-// MUL_MAT_GROUP launch when together they still fit one wave of CTAs: each of them alone leaves most SMs
-// idle (wk and wv of an 8B-shape layer are 8 row tiles each). Nothing reads a member's result before the
+// Consecutive tensor-core mul_mats over the same quantized activations (wq, wk, wv of a layer; gate and up)
+// become one MUL_MAT_GROUP launch: each of wq / wk / wv alone leaves most SMs idle (32 / 8 / 8 row tiles on
+// 148 SMs), and gate + up (2 x 112 tiles) together are enough work for the stream-K schedule, which gives
+// every SM the same number of super-blocks instead of one wave of 112 tiles twice. Nothing reads a member's result before the
 // last member, because the members are adjacent in node order.
 void fuse_mul_mat_groups(Graph &g) {
     const size_t nn = g.nodes.size();
@@ -1150,7 +1150,8 @@ void fuse_mul_mat_groups(Graph &g) {
             const Tensor &B = g.tensors[g.nodes[j]];
             if (!eligible(B) || B.src[1] != A.src[1] || B.src[2] != A.src[2]) break;
             const int64_t tb = (B.ne[0] + 127) / 128;
-            if (tiles + tb > 148) break;   // a group must stay within one wave of CTAs
+            // a group stays within one wave of CTAs, or is big enough for the stream-K schedule (gate + up)
+            if (tiles + tb > 148 && !mmq_tc_plan(g.tensors[A.src[1]].ne[0], (tiles + tb) * 128, g.tensors[A.src[1]].ne[1], 148).streamk) break;
             tiles += tb;
             A.src[wslot[members]] = B.src[0];
             A.src[yslot[members]] = g.nodes[j];
