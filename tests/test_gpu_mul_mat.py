@@ -109,3 +109,26 @@ def test_ragged_k_is_reported_by_name():
     with pytest.raises(TlbError) as e:
         Model(g, [np.zeros((4, 100), np.float32)])
     assert "MUL_MAT" in str(e.value) and "not implemented" in str(e.value)
+
+
+@pytest.mark.parametrize("N", [8, 32])
+def test_stream_k_schedule(oracle, N, monkeypatch):
+    """A matrix of several waves of row tiles takes the stream-K schedule (equal super-block counts per
+    SM, tiles cut by a CTA boundary summed by a fix-up launch); ragged last tile, and the same result as
+    the tile-per-CTA schedule up to f32 summation order."""
+    K, M = 512, 48000 + 37
+    rng = np.random.default_rng(N)
+    W = (rng.standard_normal((M, K)) * 0.02).astype(np.float32)
+    X = rng.standard_normal((N, K)).astype(np.float32)
+    Wq = oracle.quantize(Q4_K, W)
+    m, _ = mm_model(Q4_K, K, M, N, Wq)
+    (y,) = m.run(X)
+    m.close()
+    want = oracle.mul_mat(Q4_K, Wq, K, X)
+    err = close(y, want, TOL)
+    assert err <= 2e-5 * np.abs(want).max() + 1e-6
+    monkeypatch.setenv("TLB_NO_STREAMK", "1")
+    m, _ = mm_model(Q4_K, K, M, N, Wq)
+    (y2,) = m.run(X)
+    m.close()
+    assert np.abs(y2 - y).max() <= 2e-5 * np.abs(want).max() + 1e-6
