@@ -361,7 +361,11 @@ def run_kernel(args) -> dict:
         what = "%s weights [%d x %d], %d activation column(s)" % (spec[1], M, K, N)
     elif spec[0] == "paged_attention":
         cfg = DecoderConfig()
-        seqs, ctx = int(spec[1]), int(spec[2])
+        # CTX "ragged": context lengths uniform in [128, 8192] (BASELINE config 3), seeded
+        seqs = int(spec[1])
+        ragged = spec[2] == "ragged"
+        ctx = 8192 if ragged else int(spec[2])
+        lens = rng.integers(128, 8193, seqs).astype(np.int32) if ragged else np.full(seqs, ctx, np.int32)
         copies = args.copies or 2
         bs, kvh, hs, heads = cfg.block_size, cfg.n_kv_heads, cfg.head_dim, cfg.n_heads
         max_blocks = (ctx + bs - 1) // bs
@@ -381,9 +385,10 @@ def run_kernel(args) -> dict:
         prog = NativeProgram.compile(n, g)
         prog.set_input(0, rng.standard_normal((seqs, heads, hs)).astype(np.float32))
         prog.set_input(1, rng.permutation(seqs * max_blocks).astype(np.int32).reshape(seqs, max_blocks))
-        prog.set_input(2, np.full(seqs, ctx, np.int32))
-        bytes_per_launch = seqs * ctx * kvh * hs * 2 * 2
-        what = "%d sequences x %d tokens, %d/%d heads of %d, f16 pages of %d tokens" % (seqs, ctx, heads, kvh, hs, bs)
+        prog.set_input(2, lens)
+        bytes_per_launch = int(lens.sum()) * kvh * hs * 2 * 2
+        what = "%d sequences x %s tokens, %d/%d heads of %d, f16 pages of %d tokens" % (
+            seqs, "U[128, 8192] (%d in all)" % int(lens.sum()) if ragged else str(ctx), heads, kvh, hs, bs)
     elif spec[0] == "flash_attention":
         # dense causal prefill attention of the 8B shape: NQ queries = keys, f16 K/V, 32/8 heads of 128
         cfg = DecoderConfig()
