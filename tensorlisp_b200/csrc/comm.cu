@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "tlb_internal.h"
+#include "exchange.cuh"
 
 namespace tlb {
 
@@ -61,25 +62,6 @@ static NcclApi &nccl() {
 // on every rank, so all ranks end with bit-identical sums. CTA c of every rank owns chunk c of the
 // data, so no grid-wide barrier is needed. Sequence numbers only grow; slots alternate by parity
 // (a rank can be one call ahead of a peer, never two: finishing call s needs every peer's flags of call s).
-constexpr int AR_MAX_RANKS = 8;
-constexpr int AR_CTAS = 64;
-constexpr int AR_THREADS = 256;
-constexpr size_t AR_SLOT_BYTES = 1u << 20;                     // largest message
-constexpr size_t AR_FLAG_OFF = 0;                              // u32 [2][AR_MAX_RANKS][AR_CTAS]
-constexpr size_t AR_SEQ_OFF = 4096;                            // u32 [AR_CTAS], local only: calls seen by CTA c
-constexpr size_t AR_DATA_OFF = 8192;                           // [2][AR_MAX_RANKS][AR_SLOT_BYTES]
-constexpr size_t AR_BUF_BYTES = AR_DATA_OFF + 2 * AR_MAX_RANKS * AR_SLOT_BYTES;
-constexpr uint32_t AR_SPIN_LIMIT = 1u << 22;   // probes of a local flag, a few seconds
-
-struct ArRank {
-    float *data;                 // n floats, reduced in place
-    const float *partial;        // n_split > 0: this rank's input is the sum of n_split partial results of n floats each
-    int n_split;                 // (the K split of the row-parallel mul_mat in front of the exchange), `data` is only written
-    char *peer[AR_MAX_RANKS];    // exchange buffers of all ranks as mapped into this rank (own one included)
-    int rank;
-    int *err;
-};
-
 __device__ __forceinline__ void ar_body(const ArRank &a, int n, int n_ranks, int c, int n_ctas) {
     __shared__ int s_fail;
     const int tid = threadIdx.x;

@@ -1,0 +1,34 @@
+// Layout of a rank's exchange buffer and the per-rank arguments of the peer-memory all-reduce kernels
+// (comm.cu: plain all-reduce; k_fused.cu: all-reduce fused with residual add, RMS norm and quantization).
+// The buffer holds two independent sets (flags, per-CTA sequence counters, data slots): kernels that cut the
+// data into different chunks must not share a set, because the parity argument that protects a slot from
+// being overwritten while a peer still reads it needs CTA c to own the same bytes in every call.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+
+namespace tlb {
+
+constexpr int AR_MAX_RANKS = 8;
+constexpr int AR_CTAS = 64;
+constexpr int AR_THREADS = 256;
+constexpr size_t AR_SLOT_BYTES = 1u << 20;                     // largest message
+constexpr size_t AR_FLAG_OFF = 0;                              // u32 [2][AR_MAX_RANKS][AR_CTAS]
+constexpr size_t AR_SEQ_OFF = 4096;                            // u32 [AR_CTAS], local only: calls seen by CTA c
+constexpr size_t AR_DATA_OFF = 8192;                           // [2][AR_MAX_RANKS][AR_SLOT_BYTES]
+constexpr size_t AR_SET_BYTES = AR_DATA_OFF + 2 * AR_MAX_RANKS * AR_SLOT_BYTES;
+constexpr int AR_SETS = 2;                                    // 0: plain all-reduce, 1: the fused row kernel
+constexpr size_t AR_BUF_BYTES = AR_SETS * AR_SET_BYTES;
+constexpr uint32_t AR_SPIN_LIMIT = 1u << 22;   // probes of a local flag, a few seconds
+
+struct ArRank {
+    float *data;                 // n floats, reduced in place
+    const float *partial;        // n_split > 0: this rank's input is the sum of n_split partial results of n floats each
+    int n_split;                 // (the K split of the row-parallel mul_mat in front of the exchange), `data` is only written
+    char *peer[AR_MAX_RANKS];    // exchange buffers of all ranks as mapped into this rank (own one included)
+    int rank;
+    int *err;
+};
+
+
+}  // namespace tlb
