@@ -212,6 +212,14 @@ tlb_status tlb_comm_p2p_import(tlb_device *dev, const void *handles);
  * n_split > 0 every rank's input is the sum of n_split partial results (in: n_ranks x n_split x n floats),
  * the form the exchange takes behind a K-split mul_mat; otherwise in is n_ranks x n floats. */
 tlb_status tlb_comm_p2p_selftest(tlb_device *dev, int n_ranks, int n, int calls, int n_split, const float *in, float *out);
+/* The exchange fused with what follows it in a decoder layer (residual add + RMS norm * w + Q8_K quantization of
+ * the next mul_mat's input), checked the same way with up to 4 emulated ranks: in is n_ranks x n_split x rows x K
+ * partial results, resid rows x K, w K floats; out_sum gets n_ranks x rows x K (the new residual stream as every
+ * rank sees it), out_q n_ranks x act_bytes (the Q8_K activation block: int8 codes, f32 d per 256, int16 sums
+ * per 16, each section 256-byte aligned; act_bytes must be the size the library computes for (K, rows)). */
+tlb_status tlb_comm_p2p_selftest_rows(tlb_device *dev, int n_ranks, int rows, int K, int n_split, int calls, const float *in,
+                                      const float *resid, const float *w, float eps, float *out_sum, void *out_q,
+                                      uint64_t act_bytes);
 
 #ifdef __cplusplus
 }

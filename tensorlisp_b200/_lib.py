@@ -104,6 +104,7 @@ SYMBOLS = {
     "tlb_comm_p2p_export": (C.c_int, [_P, _P]),
     "tlb_comm_p2p_import": (C.c_int, [_P, _P]),
     "tlb_comm_p2p_selftest": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int, _P, _P]),
+    "tlb_comm_p2p_selftest_rows": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _P, _P, _P, C.c_float, _P, _P, C.c_uint64]),
 }
 
 _lib = None

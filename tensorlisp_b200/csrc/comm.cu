@@ -12,6 +12,7 @@
 #include <mutex>
 #include <vector>
 
+#include "kernels.h"
 #include "tlb_internal.h"
 #include "exchange.cuh"
 
@@ -169,6 +170,22 @@ cudaError_t comm_allreduce_f32(tlb_device *dev, float *buf, size_t n, cudaStream
 }
 int comm_ranks(tlb_device *dev) { return dev->comm ? dev->comm->n_ranks : 1; }
 
+// the exchange fused with residual add + RMS norm + quantizer (k_fused.cu); the caller asked comm_p2p_takes and
+// exchange_row_quant_supported first
+cudaError_t comm_exchange_row_quant(tlb_device *dev, float *data, const float *partial, int n_split, const RowQuantArgs &p, cudaStream_t st,
+                                    int *err) {
+    Comm *c = dev->comm;
+    if (!c || !c->p2p || !err) return cudaErrorInvalidValue;
+    ArRank a{};
+    a.data = data;
+    a.partial = partial;
+    a.n_split = partial ? n_split : 0;
+    a.rank = c->rank;
+    a.err = err;
+    for (int r = 0; r < c->n_ranks; r++) a.peer[r] = c->peer[r];
+    return launch_exchange_row_quant(a, p, c->n_ranks, st);
+}
+
 }  // namespace tlb
 
 using namespace tlb;
@@ -324,6 +341,92 @@ tlb_status tlb_comm_p2p_selftest(tlb_device *dev, int n_ranks, int n, int calls,
         return fail(TLB_EXECUTION, std::string("all-reduce self test: ") + cudaGetErrorString(e));
     }
     if (flag) return fail(TLB_EXECUTION, "all-reduce self test: a rank gave up waiting for its peers");
+    return TLB_OK;
+}
+
+// Single-GPU check of the fused exchange + residual add + RMS norm + Q8_K kernel: n_ranks <= 4 emulated ranks in one
+// cooperative launch. in: n_ranks x n_split x rows x K partial results (n_split >= 1), resid: rows x K, w: K.
+// out_sum: n_ranks x rows x K (the new residual stream of every rank), out_q: n_ranks x act_bytes (the Q8_K block).
+tlb_status tlb_comm_p2p_selftest_rows(tlb_device *dev, int n_ranks, int rows, int K, int n_split, int calls, const float *in,
+                                      const float *resid, const float *w, float eps, float *out_sum, void *out_q, uint64_t act_bytes) {
+    if (!dev || n_ranks < 1 || n_ranks > 4 || n_split < 1 || n_split > 16 || calls < 1 || !in || !resid || !w || !out_sum || !out_q ||
+        !exchange_row_quant_supported(K, rows))
+        return fail(TLB_INVALID, "tlb_comm_p2p_selftest_rows: bad arguments");
+    const ActLayout al = act_layout(ACT_Q8_K, K, rows);
+    if (act_bytes != al.bytes) return fail(TLB_INVALID, "tlb_comm_p2p_selftest_rows: out_q must hold " + std::to_string(al.bytes) + " bytes per rank");
+    cudaSetDevice(dev->ordinal);
+    const size_t n = (size_t)rows * K;
+    char *bufs[4] = {nullptr};
+    float *part[4] = {nullptr}, *sum[4] = {nullptr}, *d_res = nullptr, *d_w = nullptr;
+    char *q[4] = {nullptr};
+    int *err = nullptr;
+    cudaError_t e = cudaMalloc(&err, 256);
+    if (e == cudaSuccess) e = cudaMemset(err, 0, 256);
+    if (e == cudaSuccess) e = cudaMalloc(&d_res, n * 4);
+    if (e == cudaSuccess) e = cudaMalloc(&d_w, (size_t)K * 4);
+    for (int r = 0; r < n_ranks && e == cudaSuccess; r++) {
+        e = cudaMalloc(&bufs[r], AR_BUF_BYTES);
+        if (e == cudaSuccess) e = cudaMemset(bufs[r], 0, AR_BUF_BYTES);
+        if (e == cudaSuccess) e = cudaMalloc(&part[r], (size_t)n_split * n * 4);
+        if (e == cudaSuccess) e = cudaMalloc(&sum[r], n * 4);
+        if (e == cudaSuccess) e = cudaMalloc(&q[r], al.bytes);
+    }
+    ArRank a[4];
+    RowQuantArgs p[4];
+    for (int r = 0; r < n_ranks && e == cudaSuccess; r++) {
+        a[r] = ArRank{};
+        a[r].data = nullptr;
+        a[r].partial = part[r];
+        a[r].n_split = n_split;
+        a[r].rank = r;
+        a[r].err = err;
+        for (int k = 0; k < n_ranks; k++) a[r].peer[k] = bufs[k];
+        p[r] = RowQuantArgs{};
+        p[r].mode = RQ_NORM;
+        p[r].K = K;
+        p[r].N = rows;
+        p[r].a = d_res;
+        p[r].lda = K;
+        p[r].sum_out = sum[r];
+        p[r].ld_sum = K;
+        p[r].w = d_w;
+        p[r].wn = K;
+        p[r].eps = eps;
+        p[r].out = q[r];
+        p[r].qs_off = al.qs_off;
+        p[r].d_off = al.d_off;
+        p[r].bsum_off = al.bsum_off;
+    }
+    std::vector<float> h((size_t)n_ranks * n_split * n);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_res, resid, n * 4, cudaMemcpyHostToDevice, dev->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_w, w, (size_t)K * 4, cudaMemcpyHostToDevice, dev->stream);
+    for (int call = 0; call < calls && e == cudaSuccess; call++) {
+        for (size_t i = 0; i < h.size(); i++) h[i] = in[i] * (float)(call + 1);
+        for (int r = 0; r < n_ranks && e == cudaSuccess; r++)
+            e = cudaMemcpyAsync(part[r], h.data() + (size_t)r * n_split * n, (size_t)n_split * n * 4, cudaMemcpyHostToDevice, dev->stream);
+        if (e == cudaSuccess) e = launch_exchange_row_quant_emulated(a, p, n_ranks, dev->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(dev->stream);
+    }
+    int flag = 0;
+    if (e == cudaSuccess) e = cudaMemcpy(&flag, err, 4, cudaMemcpyDeviceToHost);
+    for (int r = 0; r < n_ranks && e == cudaSuccess; r++) {
+        e = cudaMemcpy(out_sum + (size_t)r * n, sum[r], n * 4, cudaMemcpyDeviceToHost);
+        if (e == cudaSuccess) e = cudaMemcpy((char *)out_q + (size_t)r * al.bytes, q[r], al.bytes, cudaMemcpyDeviceToHost);
+    }
+    for (int r = 0; r < n_ranks; r++) {
+        if (bufs[r]) cudaFree(bufs[r]);
+        if (part[r]) cudaFree(part[r]);
+        if (sum[r]) cudaFree(sum[r]);
+        if (q[r]) cudaFree(q[r]);
+    }
+    if (d_res) cudaFree(d_res);
+    if (d_w) cudaFree(d_w);
+    if (err) cudaFree(err);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(TLB_EXECUTION, std::string("fused exchange self test: ") + cudaGetErrorString(e));
+    }
+    if (flag) return fail(TLB_EXECUTION, "fused exchange self test: a rank gave up waiting for its peers");
     return TLB_OK;
 }
 

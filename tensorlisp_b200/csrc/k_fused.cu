@@ -11,6 +11,7 @@
 #include <cuda_fp16.h>
 
 #include "kernels.h"
+#include "exchange.cuh"
 #include "pdl.cuh"
 
 namespace tlb {
@@ -174,6 +175,154 @@ __global__ void __launch_bounds__(RQ_THREADS) k_row_quant_q8k(RowQuantArgs p) {
         }
     }
     rq_quant_block(p, n, sb, nblk, lane, v);
+}
+
+// ---------------------------------------------------------------- exchange + residual add + RMS norm + quantizer
+// Tensor parallelism: the all-reduce behind a row-parallel projection, the residual add, the RMS norm and the
+// Q8_K quantization of the next mul_mat's input as ONE kernel. A CTA owns one activation row (token): it adds up
+// the K-split partial sums of its rank (if any), pushes the row into a slot of every peer's exchange buffer with
+// plain stores over NVLink, raises its flag there, waits (bounded) for the same row of every rank in its own
+// buffer, adds the slots in rank order (so all ranks hold identical sums), and then has the whole reduced row in
+// the registers of its 16 warps: residual add, sum of squares, scale, quantize, pack. Protocol and buffer layout
+// are those of the plain all-reduce (comm.cu, exchange.cuh), in the second buffer set.
+constexpr int XR_THREADS = 512;   // 16 warps, one 256-value block each: rows up to 4096 elements
+
+__device__ __forceinline__ void xr_body(const ArRank &a, const RowQuantArgs &p, int n_ranks, int n, int rows) {
+    __shared__ float red[XR_THREADS / 32];
+    __shared__ int s_fail;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int64_t K = p.K;
+    const int nblk = (int)(K / 256);
+    if (n >= p.N) {   // padding columns of the tensor-core blobs are zero; they take no part in the exchange
+        if (p.npad > 0 && warp < nblk) {
+            const int ch = n / p.npad, nl = n % p.npad;
+            uint8_t *o = (uint8_t *)p.out + p.blob_off + ((size_t)ch * nblk + warp) * p.blob_bytes;
+            *reinterpret_cast<uint4 *>(o + (size_t)(nl / 8) * 4096 + lane * 128 + (nl % 8) * 16) = make_uint4(0, 0, 0, 0);
+            if ((lane & 1) == 0)
+                *reinterpret_cast<__half *>(o + (size_t)p.npad * 512 + (size_t)(nl / 8) * 256 + (lane >> 4) * 128 + (nl % 8) * 16 + ((lane >> 1) & 7) * 2) = __float2half_rn(0.f);
+            if (lane == 0) reinterpret_cast<float *>(o + (size_t)p.npad * 544)[nl] = 0.f;
+        }
+        return;
+    }
+    char *local = a.peer[a.rank] + AR_SET_BYTES;   // second set: this kernel cuts the data by rows
+    uint32_t *seqs = reinterpret_cast<uint32_t *>(local + AR_SEQ_OFF);
+    const uint32_t seq = seqs[n] + 1, par = seq & 1;
+    const bool live = warp < nblk;
+    const int64_t e0 = (int64_t)n * K + warp * 256 + lane * 8;   // this lane's 8 elements of the [rows][K] matrix
+    if (tid == 0) s_fail = 0;
+    float b[8];
+    if (live) {
+        const float *src = (a.n_split > 0 ? a.partial : a.data) + e0;
+        float4 b0 = *reinterpret_cast<const float4 *>(src), b1 = *reinterpret_cast<const float4 *>(src + 4);
+        for (int s = 1; s < a.n_split; s++) {   // K-split partial sums of this rank, in split order
+            const float *ps = src + (size_t)s * rows * K;
+            const float4 c0 = *reinterpret_cast<const float4 *>(ps), c1 = *reinterpret_cast<const float4 *>(ps + 4);
+            b0.x = __fadd_rn(b0.x, c0.x); b0.y = __fadd_rn(b0.y, c0.y); b0.z = __fadd_rn(b0.z, c0.z); b0.w = __fadd_rn(b0.w, c0.w);
+            b1.x = __fadd_rn(b1.x, c1.x); b1.y = __fadd_rn(b1.y, c1.y); b1.z = __fadd_rn(b1.z, c1.z); b1.w = __fadd_rn(b1.w, c1.w);
+        }
+        const size_t off = AR_SET_BYTES + AR_DATA_OFF + ((size_t)par * AR_MAX_RANKS + a.rank) * AR_SLOT_BYTES + (size_t)e0 * 4;
+        for (int r = 0; r < n_ranks; r++) {
+            float4 *dst = reinterpret_cast<float4 *>(a.peer[r] + off);
+            dst[0] = b0;
+            dst[1] = b1;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < n_ranks) {
+        uint32_t *flag = reinterpret_cast<uint32_t *>(a.peer[tid] + AR_SET_BYTES + AR_FLAG_OFF) + ((size_t)par * AR_MAX_RANKS + a.rank) * AR_CTAS + n;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(seq) : "memory");
+        const uint32_t *mine = reinterpret_cast<const uint32_t *>(local + AR_FLAG_OFF) + ((size_t)par * AR_MAX_RANKS + tid) * AR_CTAS + n;
+        bool ok = false;
+        for (uint32_t it = 0; it < AR_SPIN_LIMIT; it++) {
+            uint32_t f;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(f) : "l"(mine) : "memory");
+            if ((int32_t)(f - seq) >= 0) { ok = true; break; }
+        }
+        if (!ok) s_fail = 1;
+    }
+    __syncthreads();
+    if (s_fail) {
+        if (tid == 0) {
+            atomicExch(a.err, 3);
+            seqs[n] = seq;
+        }
+        return;
+    }
+    // ---- sum over the ranks in rank order (L2 loads: L1 may hold this slot's lines of two calls ago), residual add
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float ss = 0.f;
+    const int64_t k0 = (int64_t)warp * 256 + lane * 8;
+    if (live) {
+        const char *slots = local + AR_DATA_OFF + (size_t)par * AR_MAX_RANKS * AR_SLOT_BYTES + (size_t)e0 * 4;
+        float4 s0 = __ldcg(reinterpret_cast<const float4 *>(slots)), s1 = __ldcg(reinterpret_cast<const float4 *>(slots) + 1);
+        for (int r = 1; r < n_ranks; r++) {
+            const float4 c0 = __ldcg(reinterpret_cast<const float4 *>(slots + (size_t)r * AR_SLOT_BYTES));
+            const float4 c1 = __ldcg(reinterpret_cast<const float4 *>(slots + (size_t)r * AR_SLOT_BYTES) + 1);
+            s0.x = __fadd_rn(s0.x, c0.x); s0.y = __fadd_rn(s0.y, c0.y); s0.z = __fadd_rn(s0.z, c0.z); s0.w = __fadd_rn(s0.w, c0.w);
+            s1.x = __fadd_rn(s1.x, c1.x); s1.y = __fadd_rn(s1.y, c1.y); s1.z = __fadd_rn(s1.z, c1.z); s1.w = __fadd_rn(s1.w, c1.w);
+        }
+        const float4 a0 = *reinterpret_cast<const float4 *>(p.a + n * p.lda + k0), a1 = *reinterpret_cast<const float4 *>(p.a + n * p.lda + k0 + 4);
+        v[0] = __fadd_rn(a0.x, s0.x); v[1] = __fadd_rn(a0.y, s0.y); v[2] = __fadd_rn(a0.z, s0.z); v[3] = __fadd_rn(a0.w, s0.w);
+        v[4] = __fadd_rn(a1.x, s1.x); v[5] = __fadd_rn(a1.y, s1.y); v[6] = __fadd_rn(a1.z, s1.z); v[7] = __fadd_rn(a1.w, s1.w);
+        if (p.sum_out) {   // the new residual stream
+            *reinterpret_cast<float4 *>(p.sum_out + n * p.ld_sum + k0) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4 *>(p.sum_out + n * p.ld_sum + k0 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; e++) ss = __fadd_rn(ss, __fmul_rn(v[e], v[e]));
+    }
+    // ---- RMS norm over the row, weight, Q8_K block of this warp
+#pragma unroll
+    for (int sft = 16; sft > 0; sft >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, sft));
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < XR_THREADS / 32; i++) tot = __fadd_rn(tot, red[i]);
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)K), p.eps)));
+    if (live) {
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            const int wi = p.wn == K ? (int)(k0 + e) : (int)((uint32_t)(k0 + e) % (uint32_t)p.wn);
+            v[e] = __fmul_rn(__fmul_rn(v[e], scale), p.w[wi]);
+        }
+        rq_quant_block(p, n, warp, nblk, lane, v);
+    }
+    if (tid == 0) seqs[n] = seq;
+}
+
+__global__ void __launch_bounds__(XR_THREADS) k_exchange_row_quant(ArRank a, RowQuantArgs p, int n_ranks) {
+    xr_body(a, p, n_ranks, blockIdx.x, (int)p.N);
+}
+// All ranks in ONE cooperative launch on one GPU (blockIdx.y = rank): the single-GPU test of the fused kernel
+struct XrAll {
+    ArRank a[4];
+    RowQuantArgs p[4];
+};
+__global__ void __launch_bounds__(XR_THREADS) k_exchange_row_quant_emulated(XrAll all, int n_ranks) {
+    xr_body(all.a[blockIdx.y], all.p[blockIdx.y], n_ranks, blockIdx.x, (int)all.p[blockIdx.y].N);
+}
+
+bool exchange_row_quant_supported(int64_t K, int64_t N) { return K % 256 == 0 && K / 256 <= XR_THREADS / 32 && N >= 1 && N <= AR_CTAS && N * K * 4 <= (int64_t)AR_SLOT_BYTES; }
+
+static int xr_rows(const RowQuantArgs &p) { return p.npad > 0 ? (int)((p.N + p.npad - 1) / p.npad) * p.npad : (int)p.N; }
+
+cudaError_t launch_exchange_row_quant(const ArRank &a, const RowQuantArgs &p, int n_ranks, cudaStream_t st) {
+    k_exchange_row_quant<<<xr_rows(p), XR_THREADS, 0, st>>>(a, p, n_ranks);
+    return cudaGetLastError();
+}
+
+// n_ranks <= 4 emulated ranks, one cooperative launch
+cudaError_t launch_exchange_row_quant_emulated(const ArRank *a, const RowQuantArgs *p, int n_ranks, cudaStream_t st) {
+    if (n_ranks < 1 || n_ranks > 4) return cudaErrorInvalidValue;
+    XrAll all{};
+    for (int r = 0; r < n_ranks; r++) {
+        all.a[r] = a[r];
+        all.p[r] = p[r];
+    }
+    void *args[] = {&all, &n_ranks};
+    return cudaLaunchCooperativeKernel((void *)k_exchange_row_quant_emulated, dim3(xr_rows(p[0]), n_ranks), dim3(XR_THREADS), args, 0, st);
 }
 
 bool row_quant_supported(int64_t K) { return K % 256 == 0 && K / 256 <= 65535 * RQ_WARPS; }

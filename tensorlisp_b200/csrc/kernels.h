@@ -100,6 +100,12 @@ struct RowQuantArgs {
 };
 bool row_quant_supported(int64_t K);
 cudaError_t launch_row_quant(const RowQuantArgs &p, cudaStream_t st);
+// the all-reduce in front of a residual add + RMS norm + quantizer fused into one kernel (tensor parallelism):
+// p as for launch_row_quant in RQ_NORM mode with p.a the residual stream; the addend is the all-reduced `a`
+struct ArRank;
+bool exchange_row_quant_supported(int64_t K, int64_t N);
+cudaError_t launch_exchange_row_quant(const ArRank &a, const RowQuantArgs &p, int n_ranks, cudaStream_t st);
+cudaError_t launch_exchange_row_quant_emulated(const ArRank *a, const RowQuantArgs *p, int n_ranks, cudaStream_t st);
 
 // ---------------------------------------------------------------- k_core.cu
 struct BinArgs { TView a, b, d; int op; };  // 0 add 1 sub 2 mul 3 div; all f32

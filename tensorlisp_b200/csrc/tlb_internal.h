@@ -167,6 +167,9 @@ uint64_t node_scratch_bytes(const Graph &g, int32_t id, int sm_count);
 // peer-memory path takes that form (ask comm_p2p_takes first)
 cudaError_t comm_allreduce_f32(tlb_device *dev, float *buf, size_t n, cudaStream_t st, int *err, const float *partial = nullptr, int n_split = 0);
 bool comm_p2p_takes(tlb_device *dev, size_t n);
+struct RowQuantArgs;
+cudaError_t comm_exchange_row_quant(tlb_device *dev, float *data, const float *partial, int n_split, const RowQuantArgs &p, cudaStream_t st,
+                                    int *err);
 int comm_ranks(tlb_device *dev);
 // IR rewrites before planning (fusion, shared activation quantization); fuse.cpp
 void rewrite_graph(Graph &g);

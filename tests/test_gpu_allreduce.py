@@ -47,3 +47,46 @@ def test_exchange_behind_a_k_split(native, ranks, splits):
         want = (want + per_rank[r]).astype(np.float32)
     for r in range(ranks):
         assert np.array_equal(out[r], want), r
+
+
+@pytest.mark.parametrize("ranks,splits", [(2, 1), (4, 4), (3, 2)])
+def test_exchange_fused_with_add_norm_quant(native, oracle, ranks, splits):
+    """The exchange behind a row-parallel projection fused with the residual add, the RMS norm and the Q8_K
+    quantizer of the next mul_mat (emulated ranks, one cooperative launch): the new residual stream is the
+    exact f32 sum in split, then rank, order on every rank; the Q8_K block is the oracle's quantization of
+    the oracle's norm of that stream (codes may differ by one where the sum of squares was added up in
+    another order)."""
+    rows, K, calls, eps = 32, 4096, 3, 1e-5
+    rng = np.random.default_rng(ranks * 7 + splits)
+    x = (rng.standard_normal((ranks, splits, rows, K)) * 0.5).astype(np.float32)
+    resid = rng.standard_normal((rows, K)).astype(np.float32)
+    w = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    al = lambda v: (v + 255) // 256 * 256
+    d_off = al(rows * K)
+    bsum_off = d_off + al(rows * (K // 256) * 4)
+    act_bytes = bsum_off + al(rows * (K // 16) * 2)
+    out_sum = np.zeros((ranks, rows, K), np.float32)
+    out_q = np.zeros((ranks, act_bytes), np.uint8)
+    p = lambda a: a.ctypes.data_as(C.c_void_p)
+    check(lib().tlb_comm_p2p_selftest_rows(native.dev, ranks, rows, K, splits, calls, p(x), p(resid), p(w), eps, p(out_sum), p(out_q), act_bytes))
+    scaled = (x * np.float32(calls)).astype(np.float32)
+    per_rank = scaled[:, 0].copy()
+    for s in range(1, splits):
+        per_rank = (per_rank + scaled[:, s]).astype(np.float32)
+    total = per_rank[0].copy()
+    for r in range(1, ranks):
+        total = (total + per_rank[r]).astype(np.float32)
+    want_sum = (resid + total).astype(np.float32)
+    want_q = oracle.quantize_q8_K(oracle.rms_norm(want_sum, eps, w)).reshape(rows, K // 256, 292)   # f32 d, 256 codes, 16 sums
+    want_d = want_q[:, :, :4].copy().view(np.float32).reshape(rows, K // 256)
+    want_codes = want_q[:, :, 4:260].copy().view(np.int8).reshape(rows, K)
+    for r in range(ranks):
+        assert np.array_equal(out_sum[r], want_sum), r
+        codes = out_q[r, :rows * K].view(np.int8).reshape(rows, K)
+        d = out_q[r, d_off:d_off + rows * (K // 256) * 4].view(np.float32).reshape(rows, K // 256)
+        bs = out_q[r, bsum_off:bsum_off + rows * (K // 16) * 2].view(np.int16).reshape(rows, K // 16)
+        assert np.allclose(d, want_d, rtol=2e-6, atol=0)
+        diff = np.abs(codes.astype(np.int32) - want_codes.astype(np.int32))
+        assert diff.max() <= 1 and (diff != 0).mean() < 1e-3
+        assert np.array_equal(bs, codes.reshape(rows, K // 16, 16).astype(np.int32).sum(axis=2).astype(np.int16))
+        assert np.array_equal(out_q[r], out_q[0])    # every rank holds the same bytes
