@@ -126,6 +126,7 @@ def build_model(rank: int, world: int, local_rank: int):
     for s, (_, off) in zip(dg.weights, native.weight_loc):
         if len(s.ne) == 1:
             w = (1 + 0.1 * torch.randn(s.ne[0], generator=gen, device="cuda", dtype=torch.float32)).contiguous()
+            torch.cuda.synchronize()   # the copy runs on the library's stream: torch's must have written w first
             native.weights.copy_device(off, w.data_ptr(), w.numel() * 4)
         else:
             rows_left, done = s.ne[1], 0
@@ -143,6 +144,7 @@ def build_model(rank: int, world: int, local_rank: int):
     native.alloc_states(dg.state_bytes)
     for off, nbytes in zip(native.state_offsets, dg.state_bytes):
         kv = torch.randn(nbytes // 2, generator=gen, device="cuda", dtype=torch.float16)
+        torch.cuda.synchronize()
         native.state.copy_device(off, kv.data_ptr(), nbytes)
     del kv, w
     torch.cuda.empty_cache()
@@ -381,6 +383,7 @@ def run_kernel(args) -> dict:
         n.alloc_states([pool * 2] * (2 * copies))
         for off in n.state_offsets:
             kv = torch.randn(pool, device="cuda", dtype=torch.float16)
+            torch.cuda.synchronize()
             n.state.copy_device(off, kv.data_ptr(), pool * 2)
         prog = NativeProgram.compile(n, g)
         prog.set_input(0, rng.standard_normal((seqs, heads, hs)).astype(np.float32))

@@ -127,9 +127,9 @@ Layout plan(const Graph &g, const Leaves &leaves, const std::function<uint64_t(i
     }
     for (size_t pos = 0; pos < n; pos++) {
         const uint64_t bytes = scratch_bytes(g.nodes[pos]);
-        // a scratch block outlives its node by one position: the exchange that follows a K-split mul_mat
-        // reads the partial sums itself
-        if (bytes > 0) blocks.push_back({g.nodes[pos], pos, std::min(pos + 1, n - 1), align_up(bytes), true, pos});
+        // a scratch block outlives its node by two positions: the exchange that follows a K-split mul_mat,
+        // or the row quantizer that took the exchange in, reads the partial sums itself
+        if (bytes > 0) blocks.push_back({g.nodes[pos], pos, std::min(pos + 2, n - 1), align_up(bytes), true, pos});
     }
     std::stable_sort(blocks.begin(), blocks.end(), [](const Block &a, const Block &b) {
         if (a.first != b.first) return a.first < b.first;
@@ -457,7 +457,7 @@ tlb_status tlb_program_compile(tlb_device *dev, const tlb_graph *graph, const tl
     p->ordinal = dev->ordinal;
     p->n_user_tensors = graph->n_tensors;
     p->graph = std::move(g);
-    if (!getenv("TL_NATIVE_NOFUSE") || std::string(getenv("TL_NATIVE_NOFUSE")) != "1") rewrite_graph(p->graph);
+    rewrite_graph(p->graph);   // TL_NATIVE_NOFUSE turns the fusions off inside; the shared activation quantizers always go in
     const int sm = dev->prop.multiProcessorCount;
     const Graph &G = p->graph;
     p->layout = plan(G, lv, [&](int32_t id) { return node_scratch_bytes(G, id, sm); });

@@ -188,7 +188,8 @@ __global__ void __launch_bounds__(RQ_THREADS) k_row_quant_q8k(RowQuantArgs p) {
 constexpr int XR_THREADS = 512;   // 16 warps, one 256-value block each: rows up to 4096 elements
 
 __device__ __forceinline__ void xr_body(const ArRank &a, const RowQuantArgs &p, int n_ranks, int n, int rows) {
-    __shared__ float red[XR_THREADS / 32];
+    __shared__ float red[RQ_WARPS];
+    __shared__ float xs[XR_THREADS / 32 - RQ_WARPS][32][9];   // values of warps 8..15, handed to warps 0..7 (padded rows)
     __shared__ int s_fail;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t K = p.K;
@@ -269,17 +270,34 @@ __device__ __forceinline__ void xr_body(const ArRank &a, const RowQuantArgs &p, 
             *reinterpret_cast<float4 *>(p.sum_out + n * p.ld_sum + k0) = make_float4(v[0], v[1], v[2], v[3]);
             *reinterpret_cast<float4 *>(p.sum_out + n * p.ld_sum + k0 + 4) = make_float4(v[4], v[5], v[6], v[7]);
         }
+    }
+    // ---- RMS norm over the row. The squares are added in the order of k_row_quant_q8k (256 threads, thread t
+    // takes elements t*8.. of every 2048-element stretch in turn, then a shuffle tree, then the 8 warp sums in
+    // order), so this kernel and the unfused pair of launches give the same bits: warps 8..15 hand their values
+    // to the warps that would have read them in the second pass.
+    if (warp >= RQ_WARPS) {
+#pragma unroll
+        for (int e = 0; e < 8; e++) xs[warp - RQ_WARPS][lane][e] = v[e];
+    }
+    __syncthreads();
+    if (warp < RQ_WARPS) {
 #pragma unroll
         for (int e = 0; e < 8; e++) ss = __fadd_rn(ss, __fmul_rn(v[e], v[e]));
-    }
-    // ---- RMS norm over the row, weight, Q8_K block of this warp
+        if (warp + RQ_WARPS < nblk) {
 #pragma unroll
-    for (int sft = 16; sft > 0; sft >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, sft));
-    if (lane == 0) red[warp] = ss;
+            for (int e = 0; e < 8; e++) {
+                const float x = xs[warp][lane][e];
+                ss = __fadd_rn(ss, __fmul_rn(x, x));
+            }
+        }
+#pragma unroll
+        for (int sft = 16; sft > 0; sft >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, sft));
+        if (lane == 0) red[warp] = ss;
+    }
     __syncthreads();
     float tot = 0.f;
 #pragma unroll
-    for (int i = 0; i < XR_THREADS / 32; i++) tot = __fadd_rn(tot, red[i]);
+    for (int i = 0; i < RQ_WARPS; i++) tot = __fadd_rn(tot, red[i]);
     const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)K), p.eps)));
     if (live) {
 #pragma unroll

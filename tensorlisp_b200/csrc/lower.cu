@@ -493,6 +493,9 @@ void lower_quant_act(L &l) {
     });
 }
 
+void partial_sums_in_front(const LowerCtx &c, int pos, int32_t mm_id, int &n_split, Place &ps);
+bool exchange_fused_with_row_quant(const LowerCtx &c, int pos);
+
 // ---- ROW_QUANT: a QUANT_ACT node that absorbed its producer (fuse_row_producers)
 void lower_row_quant(L &l) {
     const Tensor &t = l.t();
@@ -521,6 +524,17 @@ void lower_row_quant(L &l) {
     if (b >= 0) pb = l.place(b);
     if (w >= 0) pw = l.place(w);
     if (sum >= 0) ps = l.place(sum);
+    // the all-reduce right in front may be folded into this launch (exchange_fused_with_row_quant)
+    const bool fused_ar = l.pos > 0 && exchange_fused_with_row_quant(l.c, l.pos - 1);
+    int ar_split = 0;
+    Place par_data, par_part;
+    tlb_device *dev = l.c.dev;
+    if (fused_ar) {
+        const int32_t ar = l.c.g->nodes[l.pos - 1];
+        par_data = l.place(ar);
+        partial_sums_in_front(l.c, l.pos - 1, l.T(ar).src[0], ar_split, par_part);
+    }
+    const size_t n_ar = (size_t)(p.N * p.K);
     l.push([=](const RunCtx &r) {
         RowQuantArgs q = p;
         q.a = (const float *)r.at(pa);
@@ -529,6 +543,9 @@ void lower_row_quant(L &l) {
         q.sum_out = sum >= 0 ? (float *)r.at(ps) : nullptr;
         q.y_out = nullptr;
         q.out = r.at(pd);
+        if (fused_ar && comm_p2p_takes(dev, n_ar))
+            return comm_exchange_row_quant(dev, (float *)r.at(par_data), ar_split > 0 ? (const float *)r.at(par_part) : nullptr, ar_split, q,
+                                           r.stream, r.err);
         return launch_row_quant(q, r.stream);
     });
 }
@@ -671,6 +688,52 @@ void lower_flash(L &l) {
     });
 }
 
+// Behind a K-split tensor-core mul_mat (node `mm` right in front of position `pos`) the peer-memory exchange
+// reads the partial sums itself (same conditions as in lower_mul_mat, which then leaves them un-added)
+void partial_sums_in_front(const LowerCtx &c, int pos, int32_t mm_id, int &n_split, Place &ps) {
+    const Graph &g = *c.g;
+    n_split = 0;
+    if (pos <= 0 || g.nodes[pos - 1] != mm_id || getenv("TLB_SPLITK_REDUCE_LAUNCH")) return;
+    const Tensor &mm = g.tensors[mm_id];
+    if (mm.op != "MUL_MAT" || mm.src[0] < 0 || mm.src[1] < 0 || mm.src[2] < 0 || !is_qact(g.tensors[mm.src[2]].op) ||
+        g.tensors[mm.src[2]].op_params[1] <= 0 || getenv("TLB_MM_GENERIC") || getenv("TLB_NO_TC"))
+        return;
+    const Tensor &tw = g.tensors[mm.src[0]], &tx = g.tensors[mm.src[1]];
+    const bool plain2d = tw.ne[2] * tw.ne[3] * mm.ne[2] * mm.ne[3] == 1 && tw.nb[1] == tw.row_size() && mm.is_contiguous();
+    if (!plain2d || tw.ty != TLB_TYPE_Q4_K || !tc_supported(tw.ty, tw.ne[0], tw.ne[1], tx.ne[1])) return;
+    const TcPlan tp = tc_plan(tw.ty, tw.ne[0], tw.ne[1], tx.ne[1], c.dev->prop.multiProcessorCount);
+    const int64_t sc = c.layout->scratch[pos - 1];
+    if (tp.n_split > 1 && tp.n_col_chunks == 1 && sc >= 0) {
+        n_split = tp.n_split;
+        ps.buf = BUF_ARENA;
+        ps.off = (uint64_t)sc;
+    }
+}
+
+// The ALLREDUCE at position `pos` feeds only the ROW_QUANT right behind it, as the addend of a residual add in
+// front of an RMS norm: the two run as one kernel when the peer-memory exchange is in use.
+bool exchange_fused_with_row_quant(const LowerCtx &c, int pos) {
+    const Graph &g = *c.g;
+    if (getenv("TLB_NO_FUSED_EXCHANGE") || pos < 0 || (size_t)pos + 1 >= g.nodes.size()) return false;
+    const int32_t ar = g.nodes[pos];
+    const Tensor &A = g.tensors[ar], &R = g.tensors[g.nodes[pos + 1]];
+    if (A.op != "ALLREDUCE" || R.op != "ROW_QUANT" || R.op_params[2] != RQ_NORM || R.src[1] != ar || R.src[0] < 0 || R.src[3] < 0) return false;
+    if (!exchange_row_quant_supported(A.ne[0], A.nrows()) || !A.is_contiguous()) return false;
+    const Tensor &X = g.tensors[R.src[0]], &W = g.tensors[R.src[3]];
+    if (X.ne[0] != A.ne[0] || X.nrows() != A.nrows() || W.ne[0] != A.ne[0]) return false;
+    const int32_t root = g.root(ar);
+    for (int32_t k : g.keep)
+        if (g.root(k) == root) return false;
+    int readers = 0;
+    for (size_t i = 0; i < g.nodes.size(); i++) {
+        const Tensor &t = g.tensors[g.nodes[i]];
+        if ((int)i == pos || t.is_view_op()) continue;
+        for (int s = 0; s < 10; s++)
+            if (t.src[s] >= 0 && g.root(t.src[s]) == root) readers++;
+    }
+    return readers == 1;   // the row quantizer
+}
+
 // ---- ALLREDUCE (tensor parallelism; no reference counterpart): the node is a view of its source
 void lower_allreduce(L &l) {
     const Tensor &t = l.t();
@@ -680,29 +743,13 @@ void lower_allreduce(L &l) {
     const Place pd = l.place(l.id);
     const size_t n = (size_t)t.nelements();
     tlb_device *dev = l.c.dev;
-    // behind a K-split tensor-core mul_mat the peer-memory exchange reads the partial sums itself (same
-    // conditions as in lower_mul_mat, which then leaves them un-added)
     int n_split = 0;
     Place ps;
-    const Graph &g = *l.c.g;
-    if (l.pos > 0 && g.nodes[l.pos - 1] == a && !getenv("TLB_SPLITK_REDUCE_LAUNCH")) {
-        const Tensor &mm = g.tensors[a];
-        if (mm.op == "MUL_MAT" && mm.src[0] >= 0 && mm.src[1] >= 0 && mm.src[2] >= 0 && is_qact(g.tensors[mm.src[2]].op) &&
-            g.tensors[mm.src[2]].op_params[1] > 0 && !getenv("TLB_MM_GENERIC") && !getenv("TLB_NO_TC")) {
-            const Tensor &tw = g.tensors[mm.src[0]], &tx = g.tensors[mm.src[1]];
-            const bool plain2d = tw.ne[2] * tw.ne[3] * mm.ne[2] * mm.ne[3] == 1 && tw.nb[1] == tw.row_size() && mm.is_contiguous();
-            if (plain2d && tw.ty == TLB_TYPE_Q4_K && tc_supported(tw.ty, tw.ne[0], tw.ne[1], tx.ne[1])) {
-                const TcPlan tp = tc_plan(tw.ty, tw.ne[0], tw.ne[1], tx.ne[1], dev->prop.multiProcessorCount);
-                const int64_t sc = l.c.layout->scratch[l.pos - 1];
-                if (tp.n_split > 1 && tp.n_col_chunks == 1 && sc >= 0) {
-                    n_split = tp.n_split;
-                    ps.buf = BUF_ARENA;
-                    ps.off = (uint64_t)sc;
-                }
-            }
-        }
-    }
+    partial_sums_in_front(l.c, l.pos, a, n_split, ps);
+    // the exchange may be done by the row quantizer that follows (fused kernel): then this node launches nothing
+    const bool fused_next = exchange_fused_with_row_quant(l.c, l.pos);
     l.push([=](const RunCtx &r) {
+        if (fused_next && comm_p2p_takes(dev, n)) return cudaSuccess;
         if (n_split > 0 && comm_p2p_takes(dev, n))
             return comm_allreduce_f32(dev, (float *)r.at(pd), n, r.stream, r.err, (const float *)r.at(ps), n_split);
         return comm_allreduce_f32(dev, (float *)r.at(pd), n, r.stream, r.err);
@@ -793,7 +840,8 @@ void rewrite_graph(Graph &g) {
     std::vector<char> dead(g.nodes.size(), 0);
     const char *nf = getenv("TL_NATIVE_NOFUSE");
     const std::string nofuse = nf ? nf : "";
-    auto enabled = [&](const char *name) { return nofuse.find(name) == std::string::npos; };
+    // "1" turns every fusion off, a list of names only those
+    auto enabled = [&](const char *name) { return nofuse != "1" && nofuse.find(name) == std::string::npos; };
 
     for (size_t i = 0; i < g.nodes.size(); i++) {
         const int32_t id = g.nodes[i];
