@@ -96,9 +96,10 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------------- our arm
-def build_model(rank: int, world: int, local_rank: int):
+def build_model(rank: int, world: int, local_rank: int, make_graph=None):
     """Random-init 8B-shape decoder resident in HBM: weights drawn and quantized on the GPU into the
-    weight buffer, KV pools filled with N(0,1) f16 pages, one compiled decode-step program."""
+    weight buffer, KV pools filled with N(0,1) f16 pages, one compiled decode-step program (or the program
+    `make_graph(world)` builds: a DecoderGraph over the same weight list)."""
     import torch
 
     from tensorlisp_b200.graph import F32, align256
@@ -107,10 +108,14 @@ def build_model(rank: int, world: int, local_rank: int):
     from tensorlisp_b200._lib import check
 
     torch.cuda.set_device(local_rank)
-    cfg = DecoderConfig()
-    max_blocks = CONTEXT // cfg.block_size
-    pool_blocks = BATCH * max_blocks
-    dg = decoder_step(cfg, BATCH, CONTEXT, pool_blocks, tp=world)
+    if make_graph is None:
+        cfg = DecoderConfig()
+        max_blocks = CONTEXT // cfg.block_size
+        pool_blocks = BATCH * max_blocks
+        dg = decoder_step(cfg, BATCH, CONTEXT, pool_blocks, tp=world)
+    else:
+        dg = make_graph(world)
+        cfg = dg.cfg
     native = Native(local_rank)
     # ---- weights: one buffer, 256-byte aligned offsets (Native::load's layout)
     total = 0
@@ -142,6 +147,7 @@ def build_model(rank: int, world: int, local_rank: int):
                 rows_left -= r
     # ---- KV pools
     native.alloc_states(dg.state_bytes)
+    kv = None
     for off, nbytes in zip(native.state_offsets, dg.state_bytes):
         kv = torch.randn(nbytes // 2, generator=gen, device="cuda", dtype=torch.float16)
         torch.cuda.synchronize()
@@ -317,6 +323,117 @@ def run_ours(args) -> dict:
         dist.destroy_process_group()
     return result if rank == 0 else {}
 
+
+
+# ---------------------------------------------------------------------------------- prompt pass (BASELINE config 5)
+def run_prefill(args) -> dict:
+    """`--prefill SEQS:TOKENS[:LAYERS]`: the prompt pass of the same decoder with Q8_0 weights, SEQS prompts of
+    TOKENS tokens, dense causal attention, K/V written to the paged pools, logits of every prompt's last
+    token. Reported as prompt tokens per second and as a fraction of the measured dense tensor peak
+    (2 flops per weight element and token, plus 4 per causal query-key pair and head dimension)."""
+    import torch
+
+    from tensorlisp_b200.graph import Q8_0
+    from tensorlisp_b200.programs import DecoderConfig, decoder_weights, prefill_step
+
+    spec = args.prefill.split(":")
+    n_seqs, n_tokens = int(spec[0]), int(spec[1])
+    layers = int(spec[2]) if len(spec) > 2 else 32
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world)
+    cfg0 = DecoderConfig(n_layers=layers, wtype=Q8_0)
+    cfg, dg, native, prog, weight_bytes = build_model(rank, world, local_rank,
+                                                      make_graph=lambda tp: prefill_step(cfg0, n_seqs, n_tokens, tp=tp))
+    if world > 1:
+        from tensorlisp_b200.native import Native
+        box = [Native.comm_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        native.comm_init(world, rank, box[0])   # 268 MB messages: NCCL
+    T = n_seqs * n_tokens
+    rng = np.random.default_rng(100)
+    bs = cfg.block_size
+    blocks_per_seq = (n_tokens + bs - 1) // bs
+    tables = np.random.default_rng(7).permutation(n_seqs * blocks_per_seq).astype(np.int64).reshape(n_seqs, blocks_per_seq)
+    t_in = np.arange(n_tokens)
+    slots = (tables[:, t_in // bs] * bs + t_in % bs).reshape(-1)
+    inputs = [rng.integers(0, cfg.vocab, T).astype(np.int32), np.tile(t_in.astype(np.int32), n_seqs),
+              np.triu(np.full((n_tokens, n_tokens), -np.inf, np.float16), 1),
+              (np.arange(n_seqs) * n_tokens + n_tokens - 1).astype(np.int32), slots.view(np.int32)]
+    for i, a in enumerate(inputs):
+        prog.set_input(i, a)
+    stream = torch.cuda.ExternalStream(native.stream())
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        native.sync()
+
+    for _ in range(max(args.warmup, 1)):
+        prog.run()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        prog.enqueue()
+    e1.record(stream)
+    native.sync()
+    barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / args.steps
+    prof = prog.profile()
+    barrier()
+    if dist is not None:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    by_kind: dict[str, list] = {}
+    for label, v in prof:
+        op = label.split(" ")[0]
+        by_kind.setdefault(op, [0.0, 0])
+        by_kind[op][0] += v
+        by_kind[op][1] += 1
+    total_prof = sum(v[0] for v in by_kind.values())
+    specs = decoder_weights(cfg, 1)
+    mm_elems = sum(s.ne[0] * s.ne[1] for s in specs if s.name.startswith("blk.") and len(s.ne) == 2)
+    head_elems = [s for s in specs if s.name == "output"][0].ne
+    flops_mm = 2.0 * mm_elems * T + 2.0 * head_elems[0] * head_elems[1] * n_seqs
+    flops_attn = 4.0 * cfg.n_layers * n_seqs * cfg.n_heads * cfg.head_dim * (n_tokens * (n_tokens + 1) / 2)
+    try:
+        with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")) as f:
+            pk = json.load(f)
+        peak_tf, peak_src = float(pk["bf16_tflops_sustained"]), "measured"
+    except Exception:
+        peak_tf, peak_src = 1400.0, "fallback"
+    tf = (flops_mm + flops_attn) / (ms * 1e-3) / 1e12 / world
+    mm_ms = sum(v[0] for k, v in by_kind.items() if k.startswith("MUL_MAT"))
+    result = {
+        "metric": "prefill tok/s (8B-shape Q8_0, %d x %d prompt tokens)" % (n_seqs, n_tokens), "value": T / (ms * 1e-3),
+        "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "int8 codes on tcgen05 kind::i8, f16 mma.sync attention, f32 scales and accumulate",
+        "data": "synthetic",
+        "config": {"workload": "BASELINE config 5: Llama-3-8B shape, %d layers, Q8_0 weights, %d prompts x %d tokens, causal" % (cfg.n_layers, n_seqs, n_tokens),
+                   "parallelism": "tp%d" % world},
+        "gpu_launches": prog.dispatch_count() * args.steps, "clocks": clocks,
+        "roofline": {"bound": "tensor", "kernel": "whole step", "achieved": tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": tf / peak_tf,
+                     "of": peak_src + " sustained bf16 (per GPU)", "traffic": None,
+                     "mul_mat_only_TFLOPs": flops_mm / world / (mm_ms * 1e-3) / 1e12 if mm_ms > 0 else None},
+        "launch_share": {k: {"ms": round(v[0], 3), "launches": v[1], "share": round(v[0] / total_prof, 4)} for k, v in
+                         sorted(by_kind.items(), key=lambda kv: -kv[1][0])},
+    }
+    prog.free()
+    native.close()
+    if dist is not None:
+        dist.destroy_process_group()
+    return result if rank == 0 else {}
 
 
 # ---------------------------------------------------------------------------------- single-kernel runs
@@ -542,10 +659,16 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernel", default="", help="time one kernel instead of the decode step, e.g. mul_mat:q4_K:4096:14336:1 "
                                                  "or paged_attention:32:2048")
+    ap.add_argument("--prefill", default="", help="time the prompt pass instead: SEQS:TOKENS[:LAYERS], e.g. 8:2048 (BASELINE config 5)")
     ap.add_argument("--copies", type=int, default=0, help="--kernel: independent copies of the op per replay")
     args = ap.parse_args()
     if args.kernel:
         print(json.dumps(run_kernel(args)), flush=True)
+        return
+    if args.prefill:
+        out = run_prefill(args)
+        if out:
+            print(json.dumps(out), flush=True)
         return
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     out = run_reference(args) if args.impl == "reference" else run_ours(args)

@@ -188,3 +188,62 @@ def decoder_step(cfg: DecoderConfig, batch: int, max_ctx: int, pool_blocks: int,
         extras["taps"] = tap
     return DecoderGraph(g, specs, [pool_elems * 2] * (2 * cfg.n_layers),
                         dict(ids=0, pos=1, tables=2, lens=3, slots=4), logits, token, cfg, tp, extras)
+
+
+def prefill_step(cfg: DecoderConfig, n_seqs: int, n_tokens: int, tp: int = 1, write_cache: bool = True) -> DecoderGraph:
+    """Prompt pass of BASELINE config 5: `n_seqs` prompts of `n_tokens` tokens each through the whole decoder with
+    dense causal attention (attn:flash of stdlib/attn.ss over permuted views, the way the reference's ports
+    build prefill), the new keys and values written to the paged pools, logits for the last token of every
+    prompt. Inputs: token ids [n_seqs*n_tokens], positions, the f16 causal mask [n_tokens, n_tokens] shared by
+    all heads and prompts, the row index of every prompt's last token, and the cache slots."""
+    g = Graph()
+    hd = cfg.head_dim
+    heads, kvh = cfg.n_heads // tp, cfg.n_kv_heads // tp
+    T = n_seqs * n_tokens
+    specs = decoder_weights(cfg, tp)
+    wid = {s.name: g.weight(s.ty, s.ne, s.name) for s in specs}
+    pool_blocks = n_seqs * ((n_tokens + cfg.block_size - 1) // cfg.block_size)
+    pool_elems = pool_blocks * kvh * cfg.block_size * hd
+    pools = [(g.state(F16, [pool_elems], "k_pool.%d" % i), g.state(F16, [pool_elems], "v_pool.%d" % i))
+             for i in range(cfg.n_layers)] if write_cache else []
+    ids = g.input(I32, [T], "ids")
+    pos = g.input(I32, [T], "pos")
+    mask = g.input(F16, [n_tokens, n_tokens], "mask")
+    last = g.input(I32, [n_seqs], "last")
+    slots = g.input(I32, [2 * T], "slots") if write_cache else -1
+    scale = 1.0 / float(np.sqrt(hd))
+
+    x = g.get_rows(wid["token_embd"], ids, "embd")
+    for i in range(cfg.n_layers):
+        p = "blk.%d." % i
+        h = rms_norm_w(g, x, wid[p + "attn_norm"], cfg.eps, p + "attn_in")
+        q = g.mul_mat(wid[p + "wq"], h, p + "q")
+        k = g.mul_mat(wid[p + "wk"], h, p + "k")
+        v = g.mul_mat(wid[p + "wv"], h, p + "v")
+        q = g.set_name(rope_neox(g, g.reshape(q, [hd, heads, T]), pos, hd, cfg.rope_theta), p + "q_rope")
+        k = g.set_name(rope_neox(g, g.reshape(k, [hd, kvh, T]), pos, hd, cfg.rope_theta), p + "k_rope")
+        k16 = g.cast(g.reshape(k, [hd * kvh, T]), F16, p + "k16")
+        v16 = g.cast(v, F16, p + "v16")
+        if write_cache:
+            kc, vc = pools[i]
+            g.paged_cache_write(k16, v16, kc, vc, slots, cfg.block_size, kvh, p + "cache_write")
+        # [hd, heads, tokens, prompts] -> views [hd, tokens, heads, prompts], as ggml_flash_attn_ext wants them
+        qv = g.permute(g.reshape(q, [hd, heads, n_tokens, n_seqs]), 0, 2, 1, 3)
+        kv = g.permute(g.reshape(k16, [hd, kvh, n_tokens, n_seqs]), 0, 2, 1, 3)
+        vv = g.permute(g.reshape(v16, [hd, kvh, n_tokens, n_seqs]), 0, 2, 1, 3)
+        a = g.flash_attn_ext(qv, kv, vv, mask, scale, name=p + "attn")      # [hd, heads, tokens, prompts]
+        o = g.mul_mat(wid[p + "wo"], g.reshape(a, [hd * heads, T]), p + "attn_out")
+        if tp > 1:
+            o = g.allreduce(o, p + "attn_out_sum")
+        x = g.add(x, o, p + "res1")
+        f = swiglu_ffn(g, x, wid[p + "ffn_norm"], wid[p + "ffn_gate"], wid[p + "ffn_up"], wid[p + "ffn_down"], cfg.eps, p)
+        if tp > 1:
+            f = g.allreduce(f, p + "ffn_down_sum")
+        x = g.add(x, f, p + "res2")
+    x = g.get_rows(x, last, "last_rows")
+    x = rms_norm_w(g, x, wid["output_norm"], cfg.eps, "final_norm")
+    logits = g.output(g.mul_mat(wid["output"], x, "logits"))
+    names = dict(ids=0, pos=1, mask=2, last=3)
+    if write_cache:
+        names["slots"] = 4
+    return DecoderGraph(g, specs, [pool_elems * 2] * (2 * len(pools)), names, logits, -1, cfg, tp)

@@ -1,0 +1,124 @@
+"""Prompt pass (BASELINE config 5 geometry at reduced depth / width / vocabulary, Q8_0 weights): several prompts
+through the whole decoder with dense causal attention, keys and values written to the paged pools, logits
+of every prompt's last token.
+
+ * teacher-forced: the attention of layer 0 against the closed-form f32 softmax(q k^T) v over the GPU's own
+   roped queries and f16 keys / values (1e-3 of max|want|), and the pools against those same f16 rows (exact);
+ * end to end: logits against the oracle run from the token ids, with the bar of the decode-step test (the
+   reference's arithmetic re-quantizes activations before every mul_mat, so logits are a discontinuous function
+   of the inputs: max(1e-2, the oracle's own envelope under 1e-6 relative noise)).
+"""
+import numpy as np
+import pytest
+
+from helpers import Model, close, make_decoder_weights
+from tensorlisp_b200.graph import Q8_0
+from tensorlisp_b200.programs import DecoderConfig, prefill_step
+
+pytestmark = pytest.mark.gpu
+
+
+def causal_attention(q, k16, v16, n_seqs, n_tokens, heads, kvh, hd):
+    """q f32 [T, heads, hd], k16 / v16 f16 [T, kvh, hd] -> f32 [T, heads*hd], prompts independent."""
+    out = np.zeros((n_seqs * n_tokens, heads, hd), np.float32)
+    grp = heads // kvh
+    mask = np.triu(np.full((n_tokens, n_tokens), -np.inf, np.float32), 1)
+    for s in range(n_seqs):
+        r = slice(s * n_tokens, (s + 1) * n_tokens)
+        for h in range(heads):
+            kk = k16[r, h // grp].astype(np.float32)
+            vv = v16[r, h // grp].astype(np.float32)
+            sc = q[r, h] @ kk.T / np.float32(np.sqrt(hd)) + mask
+            p = np.exp(sc - sc.max(axis=1, keepdims=True))
+            out[r, h] = (p / p.sum(axis=1, keepdims=True)) @ vv
+    return out.reshape(n_seqs * n_tokens, heads * hd)
+
+
+def oracle_prefill(oracle, cfg, specs, weights, ids, pos, n_seqs, n_tokens):
+    W = {s.name: (s, w) for s, w in zip(specs, weights)}
+    T = len(ids)
+    hd, heads, kvh = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
+
+    def lin(name, x):
+        s, w = W[name]
+        return oracle.mul_mat(s.ty, w, s.ne[0], np.ascontiguousarray(x, np.float32))
+
+    s, w = W["token_embd"]
+    x = oracle.get_rows(s.ty, w, cfg.d_model, ids)
+    for l in range(cfg.n_layers):
+        p = "blk.%d." % l
+        h = oracle.rms_norm(x, cfg.eps, W[p + "attn_norm"][1])
+        q, k, v = lin(p + "wq", h), lin(p + "wk", h), lin(p + "wv", h)
+        q = oracle.rope(q.reshape(T, heads, hd), pos, hd, 2, cfg.rope_theta)
+        k = oracle.rope(k.reshape(T, kvh, hd), pos, hd, 2, cfg.rope_theta)
+        a = causal_attention(q, k.astype(np.float16), v.reshape(T, kvh, hd).astype(np.float16), n_seqs, n_tokens, heads, kvh, hd)
+        x = x + lin(p + "wo", a)
+        h = oracle.rms_norm(x, cfg.eps, W[p + "ffn_norm"][1])
+        x = x + lin(p + "ffn_down", oracle.silu_mul(lin(p + "ffn_gate", h), lin(p + "ffn_up", h)))
+    last = np.arange(n_seqs) * n_tokens + n_tokens - 1
+    x = oracle.rms_norm(np.ascontiguousarray(x[last]), cfg.eps, W["output_norm"][1])
+    return lin("output", x)
+
+
+class NoisyOracle:
+    def __init__(self, oracle, eps, seed):
+        self.o, self.eps, self.r = oracle, eps, np.random.default_rng(seed)
+
+    def __getattr__(self, name):
+        return getattr(self.o, name)
+
+    def mul_mat(self, *a, **k):
+        y = self.o.mul_mat(*a, **k)
+        return (y * (1 + self.eps * self.r.standard_normal(y.shape))).astype(np.float32)
+
+
+@pytest.mark.parametrize("n_seqs,n_tokens", [(2, 80), (3, 37)])
+def test_prefill(oracle, n_seqs, n_tokens):
+    cfg = DecoderConfig(n_layers=2, d_model=512, n_heads=4, n_kv_heads=2, head_dim=128, d_ffn=1024, vocab=1024, wtype=Q8_0)
+    dg = prefill_step(cfg, n_seqs, n_tokens)
+    g = dg.graph
+    T, bs = n_seqs * n_tokens, cfg.block_size
+    hd, heads, kvh = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
+    rng = np.random.default_rng(11)
+    weights = make_decoder_weights(oracle, dg.weights, seed=3)
+    by_name = {g.tensors[t].name: t for t in g.nodes}
+    taps = [(n, by_name["blk.0." + n]) for n in ("q_rope", "k16", "v16", "attn")]
+    for _, t in taps:
+        g.keep.append(t)
+    m = Model(g, weights, dg.state_bytes, [("logits", dg.logits)] + taps)
+    ids = rng.integers(0, cfg.vocab, T).astype(np.int32)
+    pos = np.tile(np.arange(n_tokens, dtype=np.int32), n_seqs)
+    blocks_per_seq = (n_tokens + bs - 1) // bs
+    tables = rng.permutation(n_seqs * blocks_per_seq).astype(np.int64).reshape(n_seqs, blocks_per_seq)
+    t_in = np.arange(n_tokens)
+    slots = (tables[:, t_in // bs] * bs + t_in % bs).reshape(-1)
+    mask = np.triu(np.full((n_tokens, n_tokens), -np.inf, np.float16), 1)
+    last = (np.arange(n_seqs) * n_tokens + n_tokens - 1).astype(np.int32)
+    logits, q_rope, k16, v16, attn = m.run(ids, pos, mask, last, slots.view(np.int32))
+
+    # ---- layer 0 attention from the GPU's own operands
+    want_a = causal_attention(q_rope.reshape(T, heads, hd), k16.reshape(T, kvh, hd), v16.reshape(T, kvh, hd), n_seqs, n_tokens, heads, kvh, hd)
+    close(attn.reshape(T, heads * hd), want_a, 1e-3)
+    # ---- the pools hold exactly those f16 rows at the tokens' slots
+    pool_blocks = n_seqs * blocks_per_seq
+    nbytes = pool_blocks * kvh * bs * hd * 2
+    kp = m.native.state.read(m.native.state_offsets[0], nbytes).view(np.float16)
+    vp = m.native.state.read(m.native.state_offsets[1], nbytes).view(np.float16)
+    kp, vp = kp.reshape(pool_blocks, kvh, bs, hd), vp.reshape(pool_blocks, kvh, bs, hd)
+    k16, v16 = k16.reshape(T, kvh, hd), v16.reshape(T, kvh, hd)
+    for t in range(T):
+        assert np.array_equal(kp[slots[t] // bs, :, slots[t] % bs], k16[t])
+        assert np.array_equal(vp[slots[t] // bs, :, slots[t] % bs], v16[t])
+
+    # ---- end to end
+    want = oracle_prefill(oracle, cfg, dg.weights, weights, ids, pos, n_seqs, n_tokens)
+    envelope = 0.0
+    for seed in range(3):
+        noisy = oracle_prefill(NoisyOracle(oracle, 1e-6, seed), cfg, dg.weights, weights, ids, pos, n_seqs, n_tokens)
+        envelope = max(envelope, float(np.abs(noisy - want).max()))
+    err = float(np.abs(logits.reshape(want.shape) - want).max())
+    assert err <= max(1e-2, 1.5 * envelope), (err, envelope)
+    top2 = np.sort(want, axis=1)[:, -2:]
+    decided = (top2[:, 1] - top2[:, 0]) > 2 * max(err, envelope)
+    assert np.array_equal(logits.reshape(want.shape).argmax(axis=1)[decided], want.argmax(axis=1)[decided])
+    m.close()
