@@ -1,4 +1,4 @@
-// Batched MUL_MAT (5..32 activation columns) with Q8_0 weights on the 5th-generation tensor cores:
+// Batched MUL_MAT (5 activation columns and up) with Q8_0 weights on the 5th-generation tensor cores:
 // the output projection of a decode step (vocab x d_model, Q8_0) is the largest matrix of the model.
 //
 // Arithmetic (same integers as the reference's ggml-cpu path, vendor/ggml/src/ggml-cpu/quants.c:451-479):
@@ -15,6 +15,7 @@
 // matrices) stays in shared memory. Eight warps drain the accumulators, one warp issues the MMAs,
 // one the TMA copies; they meet only through mbarriers, every wait is bounded.
 #include <algorithm>
+#include <cstdlib>
 #include <cuda.h>
 #include <cuda_fp16.h>
 
@@ -324,6 +325,224 @@ __global__ void __launch_bounds__(tc8::THREADS, 1) k_mmq_tc_q80(const __grid_con
     if (tid == 0 && s_fail) atomicExch(p.err, 2);
 }
 
+// ---------------------------------------------------------------- many activation columns (prompt pass)
+// Same arithmetic, a 128-row x 128-column output tile per CTA (grid: row tiles x column tiles, row tiles
+// fastest so that the CTAs in flight share a few activation blobs and sweep the weights through L2).
+// One MMA (128 x 128 x 32) per block into one of two accumulators; draining an accumulator costs an
+// int->float conversion, a scale product and an FMA per element and block, which bounds this kernel (the
+// MMA itself is six times faster), so sixteen warps drain (lane quadrant x 32-column slice, sums in
+// registers), four realign the weight codes, one issues MMAs, one TMA copies.
+namespace tc8w {
+constexpr int NW = 128;                                  // activation columns per tile
+constexpr int EPI_WARPS = 16, DEQ_WARPS = 4;
+constexpr int EPI_WARP0 = 1, DEQ_WARP0 = EPI_WARP0 + EPI_WARPS, MMA_WARP = DEQ_WARP0 + DEQ_WARPS;
+constexpr int THREADS = (MMA_WARP + 1) * 32;             // 704
+constexpr int RAW_STAGES = 2, ACT_STAGES = 3;
+constexpr int BLOB = NW * 288;
+constexpr int CW = NW / (EPI_WARPS / 4);                 // 32 columns per draining warp
+}  // namespace tc8w
+
+__global__ void __launch_bounds__(tc8w::THREADS, 1) k_mmq_tc_q80_wide(const __grid_constant__ CUtensorMap wmap, Tc8Params p) {
+    using namespace tc;
+    using namespace tc8w;
+    constexpr int ROWS = tc8::ROWS;
+    constexpr int A_RING = tc8::A_RING;
+    constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NW >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = smem_raw + ((1024u - (su32(smem_raw) & 1023u)) & 1023u);
+    uint8_t *raw = smem;                                              // RAW_STAGES x RAW_BYTES
+    uint8_t *actb = raw + RAW_STAGES * tc8::RAW_BYTES;                // ACT_STAGES x BLOB
+    float *dw = reinterpret_cast<float *>(actb + ACT_STAGES * BLOB);  // [A_RING][8][ROWS] weight scales
+    __shared__ uint64_t bar_raw[RAW_STAGES], bar_rawfree[RAW_STAGES], bar_act[ACT_STAGES], bar_actfree[ACT_STAGES];
+    __shared__ uint64_t bar_aready[A_RING], bar_afree[A_RING], bar_dwfree[A_RING], bar_mma[2], bar_epi[2];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int s_fail;
+    volatile int *fail = &s_fail;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int row_tile = blockIdx.x, col_tile = blockIdx.y;
+    const int nst = p.nst;
+    const uint8_t *act = p.act + (size_t)col_tile * nst * BLOB;
+    if (tid == 0) {
+        for (int i = 0; i < RAW_STAGES; i++) {
+            mbar_init(&bar_raw[i], 1);
+            mbar_init(&bar_rawfree[i], DEQ_WARPS);
+        }
+        for (int i = 0; i < ACT_STAGES; i++) {
+            mbar_init(&bar_act[i], 1);
+            mbar_init(&bar_actfree[i], EPI_WARPS * 32);
+        }
+        for (int i = 0; i < A_RING; i++) {
+            mbar_init(&bar_aready[i], DEQ_WARPS);
+            mbar_init(&bar_afree[i], 1);
+            mbar_init(&bar_dwfree[i], EPI_WARPS * 32);
+        }
+        for (int i = 0; i < 2; i++) {
+            mbar_init(&bar_mma[i], 1);
+            mbar_init(&bar_epi[i], EPI_WARPS * 32);
+        }
+        s_fail = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) tmem_alloc(&tmem_base_s, tc8::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+
+    auto load_raw = [&](int i) {
+        const int s = i % RAW_STAGES;
+        mbar_expect_tx(&bar_raw[s], tc8::RAW_BYTES);
+        tma_2d(raw + s * tc8::RAW_BYTES, &wmap, i * (tc8::ROW_CHUNK / 2), row_tile * ROWS, &bar_raw[s]);   // x in 16-bit elements
+    };
+    auto load_act = [&](int i) {
+        const int s = i % ACT_STAGES;
+        mbar_expect_tx(&bar_act[s], BLOB);
+        bulk_g2s(actb + s * BLOB, act + (size_t)i * BLOB, BLOB, &bar_act[s]);
+    };
+    griddep_launch();
+    if (tid == 0)
+        for (int i = 0; i < nst && i < RAW_STAGES; i++) load_raw(i);
+    griddep_wait();
+    if (tid == 0)
+        for (int i = 0; i < nst && i < ACT_STAGES; i++) load_act(i);
+
+    if (warp == 0) {
+        // ---- TMA producer
+        if (lane == 0) {
+            for (int i = 0; i < nst; i++) {
+                if (i + RAW_STAGES < nst) {
+                    mbar_wait_relaxed(&bar_rawfree[i % RAW_STAGES], (uint32_t)((i / RAW_STAGES) & 1), fail);
+                    load_raw(i + RAW_STAGES);
+                }
+                if (i + ACT_STAGES < nst) {
+                    mbar_wait_relaxed(&bar_actfree[i % ACT_STAGES], (uint32_t)((i / ACT_STAGES) & 1), fail);
+                    load_act(i + ACT_STAGES);
+                }
+            }
+        }
+    } else if (warp == tc8w::MMA_WARP) {
+        // ---- MMA issuer: the whole warp runs the loop (converged), one elected lane issues
+        const bool leader = elect_one();
+        for (int i = 0; i < nst; i++) {
+            const int as = i % ACT_STAGES, slot = i % A_RING;
+            const uint64_t b_desc0 = smem_desc(su32(actb + as * BLOB), 128, 2048);
+            mbar_wait(&bar_act[as], (uint32_t)((i / ACT_STAGES) & 1), fail);
+            mbar_wait(&bar_aready[slot], (uint32_t)((i / A_RING) & 1), fail);
+            tc_fence_after();
+#pragma unroll 1
+            for (int blk = 0; blk < 8; blk++) {
+                const int G = 8 * i + blk, gb = G & 1;
+                if (G >= 2) {
+                    mbar_wait(&bar_epi[gb], (uint32_t)(((G - 2) >> 1) & 1), fail);   // accumulator gb drained
+                    tc_fence_after();
+                }
+                if (leader) {
+                    tc8::umma_i8_ta(tmem_base + (uint32_t)(gb * NW), tmem_base + tc8::A_COL0 + (uint32_t)(slot * 64 + blk * 8),
+                                    b_desc0 + (uint64_t)(blk * (256 >> 4)), IDESC);
+                    umma_commit(&bar_mma[gb]);
+                    if (blk == 7) umma_commit(&bar_afree[slot]);
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp < tc8w::DEQ_WARP0) {
+        // ---- draining warps: TMEM lane quadrant warp % 4, column slice (warp - 1) / 4
+        const int q = warp & 3;
+        const int row_in_tile = q * 32 + lane;
+        const int col0 = ((warp - tc8w::EPI_WARP0) >> 2) * CW;
+        float yacc[CW];
+#pragma unroll
+        for (int c = 0; c < CW; c++) yacc[c] = 0.f;
+        const uint32_t lane_addr0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)col0;
+        for (int i = 0; i < nst; i++) {
+            const int as = i % ACT_STAGES, slot = i % A_RING;
+            const float *da = reinterpret_cast<const float *>(actb + as * BLOB + NW * 256) + col0;   // [8][NW]
+            const float *dwr = dw + (size_t)slot * 8 * ROWS + row_in_tile;
+#pragma unroll 1
+            for (int blk = 0; blk < 8; blk++) {
+                const int G = 8 * i + blk, gb = G & 1;
+                mbar_wait_relaxed(&bar_mma[gb], (uint32_t)((G >> 1) & 1), fail);
+                tc_fence_after();
+                const float w = dwr[blk * ROWS];
+                const float4 *dab = reinterpret_cast<const float4 *>(da + blk * NW);
+#pragma unroll
+                for (int h = 0; h < CW / 16; h++) {
+                    int D[16];
+                    tc8::tmem_ld16i(lane_addr0 + (uint32_t)(gb * NW + h * 16), D);
+                    tmem_ld_wait();
+                    if (h == CW / 16 - 1) {
+                        tc_fence_before();
+                        mbar_arrive(&bar_epi[gb]);   // accumulator gb may be overwritten
+                    }
+#pragma unroll
+                    for (int c4 = 0; c4 < 4; c4++) {
+                        const float4 s = dab[h * 4 + c4];
+                        yacc[h * 16 + c4 * 4 + 0] += (float)D[c4 * 4 + 0] * (w * s.x);
+                        yacc[h * 16 + c4 * 4 + 1] += (float)D[c4 * 4 + 1] * (w * s.y);
+                        yacc[h * 16 + c4 * 4 + 2] += (float)D[c4 * 4 + 2] * (w * s.z);
+                        yacc[h * 16 + c4 * 4 + 3] += (float)D[c4 * 4 + 3] * (w * s.w);
+                    }
+                }
+            }
+            mbar_arrive(&bar_dwfree[slot]);
+            mbar_arrive(&bar_actfree[as]);
+        }
+        const int64_t row = (int64_t)row_tile * ROWS + row_in_tile;
+        const int ncol = min(NW, p.N - col_tile * NW);
+        if (row < p.M) {
+            float *o = p.out + (size_t)col_tile * NW * p.ldy + row;
+#pragma unroll
+            for (int c = 0; c < CW; c++)
+                if (col0 + c < ncol) o[(size_t)(col0 + c) * p.ldy] = yacc[c];
+        }
+    } else {
+        // ---- realigning warps: lane quadrant = warp % 4 fixes the rows, every warp takes all eight blocks of its rows
+        const int r = (warp & 3) * 32 + lane;
+        const uint32_t a_lane = tmem_base + tc8::A_COL0 + ((uint32_t)((warp & 3) * 32) << 16);
+        for (int i = 0; i < nst; i++) {
+            const int rs = i % RAW_STAGES, slot = i % A_RING;
+            mbar_wait(&bar_raw[rs], (uint32_t)((i / RAW_STAGES) & 1), fail);
+            if (i >= A_RING) {
+                // the MMAs that read this ring slot are done, and the draining warps have read its scales
+                mbar_wait(&bar_afree[slot], (uint32_t)(((i / A_RING) - 1) & 1), fail);
+                mbar_wait(&bar_dwfree[slot], (uint32_t)(((i / A_RING) - 1) & 1), fail);
+                tc_fence_after();
+            }
+            const uint8_t *rrow = raw + rs * tc8::RAW_BYTES + r * tc8::ROW_CHUNK;
+            float *dws = dw + (size_t)slot * 8 * ROWS + r;
+#pragma unroll
+            for (int g = 0; g < 4; g++) {
+                uint32_t qa[8], qb[8];
+                float da, db;
+                if (g == 0) tc8::split_blocks<0>(rrow, qa, qb, da, db);
+                else if (g == 1) tc8::split_blocks<1>(rrow, qa, qb, da, db);
+                else if (g == 2) tc8::split_blocks<2>(rrow, qa, qb, da, db);
+                else tc8::split_blocks<3>(rrow, qa, qb, da, db);
+                tmem_st8(a_lane + (uint32_t)(slot * 64 + (2 * g) * 8), qa);
+                tmem_st8(a_lane + (uint32_t)(slot * 64 + (2 * g + 1) * 8), qb);
+                dws[(2 * g) * ROWS] = da;
+                dws[(2 * g + 1) * ROWS] = db;
+            }
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&bar_aready[slot]);
+                mbar_arrive(&bar_rawfree[rs]);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, tc8::TMEM_COLS);
+    if (tid == 0 && s_fail) atomicExch(p.err, 2);
+}
+
+static size_t tc8w_smem() {
+    return (size_t)tc8w::RAW_STAGES * tc8::RAW_BYTES + (size_t)tc8w::ACT_STAGES * tc8w::BLOB + (size_t)tc8::A_RING * 8 * tc8::ROWS * sizeof(float) + 1024;
+}
+
 // ---------------------------------------------------------------- host side
 template <int NPAD, int RS, int AS>
 static size_t tc8_smem() {
@@ -333,14 +552,29 @@ static size_t tc8_smem() {
 void mmq_tc8_configure() {
     cudaFuncSetAttribute(k_mmq_tc_q80<16, 4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc8_smem<16, 4, 4>());
     cudaFuncSetAttribute(k_mmq_tc_q80<32, 4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc8_smem<32, 4, 4>());
+    cudaFuncSetAttribute(k_mmq_tc_q80_wide, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc8w_smem());
 }
 
-bool mmq_tc8_supported(int64_t K, int64_t M, int64_t N) { return K % 256 == 0 && K >= 256 && M >= 1 && N > 4 && N <= 8192; }
+bool mmq_tc8_supported(int64_t K, int64_t M, int64_t N) {
+    return K % 256 == 0 && K >= 256 && M >= 1 && N > 4 && N <= (int64_t)tc8w::NW * 65535;   // column tiles are grid.y
+}
 
 TcPlan mmq_tc8_plan(int64_t K, int64_t M, int64_t N, int sm_count) {
     TcPlan t;
-    t.npad = N <= 16 ? 16 : 32;
     t.nsb = (int)(K / 256);
+    if (N > 64 && !getenv("TLB_NO_WIDE_TC")) {
+        // 128-column tiles, whole K per CTA (k_mmq_tc_q80_wide): row tiles x column tiles fill the GPU
+        t.npad = tc8w::NW;
+        t.n_split = 1;
+        t.sb_per_split = t.nsb;
+        t.streamk = 0;
+        t.n_col_chunks = (int)((N + t.npad - 1) / t.npad);
+        t.blob_unit = (uint64_t)tc8_blob_bytes(t.npad);
+        t.blob_bytes = (uint64_t)t.n_col_chunks * t.nsb * t.blob_unit;
+        t.partial_bytes = 0;
+        return t;
+    }
+    t.npad = N <= 16 ? 16 : 32;
     const int64_t tiles = (M + tc8::ROWS - 1) / tc8::ROWS;
     // same model as the Q4_K kernel, with this kernel's time per stage
     int best = 1;
@@ -381,6 +615,20 @@ cudaError_t launch_mmq_tc8(const TcPlan &t, const void *W, int64_t K, int64_t M,
     // described in 16-bit elements: a 272-byte box is 136 of them (the limit is 256 elements per dimension)
     cudaError_t e = tc_encode_2d(&map, W, (uint64_t)(K / 32 * 34), (uint64_t)M, tc8::ROW_CHUNK, tc8::ROWS, 2);
     if (e != cudaSuccess) return e;
+    if (t.npad == tc8w::NW) {
+        Tc8Params p{};
+        p.act = (const uint8_t *)blobs;
+        p.out = y;
+        p.M = M;
+        p.N = (int)N;
+        p.npad = t.npad;
+        p.nst = p.st_per_split = t.nsb;
+        p.n_split = 1;
+        p.ldy = ldy;
+        p.err = err;
+        return launch_pdl(k_mmq_tc_q80_wide, dim3((unsigned)((M + tc8::ROWS - 1) / tc8::ROWS), (unsigned)t.n_col_chunks), dim3(tc8w::THREADS),
+                          tc8w_smem(), st, map, p);
+    }
     dim3 grid((unsigned)((M + tc8::ROWS - 1) / tc8::ROWS), (unsigned)t.n_split);
     for (int c = 0; c < t.n_col_chunks; c++) {   // one launch per chunk of npad columns
         const int64_t n0 = (int64_t)c * t.npad, nc = std::min<int64_t>(t.npad, N - n0);

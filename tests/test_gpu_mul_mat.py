@@ -50,6 +50,20 @@ def test_shapes(oracle, ty, name, K, M, N):
     m.close()
 
 
+@pytest.mark.parametrize("K,M,N", [(2048, 300, 300), (4096, 1024, 1000), (512, 130, 128), (14336, 256, 257)])
+def test_q8_0_many_columns(oracle, K, M, N):
+    """Prompt-sized batches take 128-column tiles on the tensor cores: same integers, ragged rows and columns."""
+    rng = np.random.default_rng(K + M + N)
+    W = (rng.standard_normal((M, K)) * 0.02).astype(np.float32)
+    X = rng.standard_normal((N, K)).astype(np.float32)
+    Wq = oracle.quantize(Q8_0, W)
+    m, _ = mm_model(Q8_0, K, M, N, Wq)
+    (y,) = m.run(X)
+    err = close(y, oracle.mul_mat(Q8_0, Wq, K, X), TOL)
+    assert err <= 2e-5 * np.abs(y).max() + 1e-6
+    m.close()
+
+
 def test_config1_q8_0_4096(oracle):
     """BASELINE config 1: W 4096x4096 N(0,0.02) seed 0 -> Q8_0, x N(0,1) seed 1, batch 1 and 16."""
     W = (np.random.default_rng(0).standard_normal((4096, 4096)) * 0.02).astype(np.float32)
