@@ -549,6 +549,8 @@ def run_kernel(args) -> dict:
     out = {"kernel": args.kernel, "what": what, "copies_per_replay": copies, "us_per_launch": ms * 1e3,
            "algorithmic_bytes_per_launch": bytes_per_launch, "achieved_GBps": bytes_per_launch / ms / 1e6,
            "peak_GBps": peak, "frac": bytes_per_launch / ms / 1e6 / peak, "of": src, "launches": prog.labels()}
+    if spec[0] == "mul_mat":
+        out["TFLOPs"] = 2.0 * K * M * N / (ms * 1e-3) / 1e12
     if spec[0] == "flash_attention":
         out["TFLOPs"] = flops / (ms * 1e-3) / 1e12
     prog.free()

@@ -226,8 +226,28 @@ __global__ void k_glu(GluArgs p, const float *a, const float *b, float *d) {
         d[i] = glu_act(p.glu_op, a[r * p.lda + c]) * b[r * p.ldb + c];
     }
 }
+// Prompt-sized operands (hundreds of MB): four columns per thread, 128-bit accesses
+__global__ void k_glu4(GluArgs p, const float *a, const float *b, float *d) {
+    const int64_t n4 = p.n / 4, total = n4 * p.rows;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / n4, c = (i - r * n4) * 4;
+        const float4 x = *reinterpret_cast<const float4 *>(a + r * p.lda + c);
+        const float4 y = *reinterpret_cast<const float4 *>(b + r * p.ldb + c);
+        float4 o;
+        o.x = glu_act(p.glu_op, x.x) * y.x;
+        o.y = glu_act(p.glu_op, x.y) * y.y;
+        o.z = glu_act(p.glu_op, x.z) * y.z;
+        o.w = glu_act(p.glu_op, x.w) * y.w;
+        *reinterpret_cast<float4 *>(d + r * p.n + c) = o;
+    }
+}
 cudaError_t launch_glu(const GluArgs &p, const float *a, const float *b, float *d, cudaStream_t st) {
     if (p.n * p.rows == 0) return cudaSuccess;
+    const bool vec = p.n % 4 == 0 && p.lda % 4 == 0 && p.ldb % 4 == 0 && (((uintptr_t)a | (uintptr_t)b | (uintptr_t)d) & 15) == 0;
+    if (vec) {
+        k_glu4<<<nblocks(p.n / 4 * p.rows, 256), 256, 0, st>>>(p, a, b, d);
+        return cudaGetLastError();
+    }
     k_glu<<<nblocks(p.n * p.rows, 256), 256, 0, st>>>(p, a, b, d);
     return cudaGetLastError();
 }

@@ -328,10 +328,12 @@ __global__ void __launch_bounds__(tc8::THREADS, 1) k_mmq_tc_q80(const __grid_con
 // ---------------------------------------------------------------- many activation columns (prompt pass)
 // Same arithmetic, a 128-row x 128-column output tile per CTA (grid: row tiles x column tiles, row tiles
 // fastest so that the CTAs in flight share a few activation blobs and sweep the weights through L2).
-// One MMA (128 x 128 x 32) per block into one of two accumulators; draining an accumulator costs an
-// int->float conversion, a scale product and an FMA per element and block, which bounds this kernel (the
-// MMA itself is six times faster), so sixteen warps drain (lane quadrant x 32-column slice, sums in
-// registers), four realign the weight codes, one issues MMAs, one TMA copies.
+// One MMA (128 x 128 x 32) per block into one of two accumulators; every block's accumulator has to come back
+// out of tensor memory (64 KB per block and tile) and costs an int->float conversion, a scale product and an
+// FMA per element. That drain bounds this kernel, not the MMA (measured: 490 us of 790 with the arithmetic
+// left out, tensor pipe 7% busy), so sixteen warps drain (lane quadrant x 32-column slice, sums in registers,
+// two f32 lanes per instruction), four realign the weight codes, one issues MMAs, one TMA copies; the warps
+// that mostly wait nap between probes.
 namespace tc8w {
 constexpr int NW = 128;                                  // activation columns per tile
 constexpr int EPI_WARPS = 16, DEQ_WARPS = 4;
@@ -340,6 +342,31 @@ constexpr int THREADS = (MMA_WARP + 1) * 32;             // 704
 constexpr int RAW_STAGES = 2, ACT_STAGES = 3;
 constexpr int BLOB = NW * 288;
 constexpr int CW = NW / (EPI_WARPS / 4);                 // 32 columns per draining warp
+// two f32 lanes per instruction (each lane rounds as the scalar instruction does)
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+// y += float(D) * (w * s) for 16 columns
+__device__ __forceinline__ void drain16(uint64_t *y, const int (&D)[16], uint64_t ww, const ulonglong2 *s) {
+#pragma unroll
+    for (int c4 = 0; c4 < 4; c4++) {
+        const ulonglong2 sv = s[c4];
+        y[2 * c4] = fma2(pack2((float)D[4 * c4], (float)D[4 * c4 + 1]), mul2(ww, sv.x), y[2 * c4]);
+        y[2 * c4 + 1] = fma2(pack2((float)D[4 * c4 + 2], (float)D[4 * c4 + 3]), mul2(ww, sv.y), y[2 * c4 + 1]);
+    }
+}
 }  // namespace tc8w
 
 __global__ void __launch_bounds__(tc8w::THREADS, 1) k_mmq_tc_q80_wide(const __grid_constant__ CUtensorMap wmap, Tc8Params p) {
@@ -370,16 +397,16 @@ __global__ void __launch_bounds__(tc8w::THREADS, 1) k_mmq_tc_q80_wide(const __gr
         }
         for (int i = 0; i < ACT_STAGES; i++) {
             mbar_init(&bar_act[i], 1);
-            mbar_init(&bar_actfree[i], EPI_WARPS * 32);
+            mbar_init(&bar_actfree[i], EPI_WARPS);
         }
         for (int i = 0; i < A_RING; i++) {
             mbar_init(&bar_aready[i], DEQ_WARPS);
             mbar_init(&bar_afree[i], 1);
-            mbar_init(&bar_dwfree[i], EPI_WARPS * 32);
+            mbar_init(&bar_dwfree[i], EPI_WARPS);
         }
         for (int i = 0; i < 2; i++) {
             mbar_init(&bar_mma[i], 1);
-            mbar_init(&bar_epi[i], EPI_WARPS * 32);
+            mbar_init(&bar_epi[i], EPI_WARPS);   // one arrival per draining warp
         }
         s_fail = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -427,14 +454,14 @@ __global__ void __launch_bounds__(tc8w::THREADS, 1) k_mmq_tc_q80_wide(const __gr
         for (int i = 0; i < nst; i++) {
             const int as = i % ACT_STAGES, slot = i % A_RING;
             const uint64_t b_desc0 = smem_desc(su32(actb + as * BLOB), 128, 2048);
-            mbar_wait(&bar_act[as], (uint32_t)((i / ACT_STAGES) & 1), fail);
-            mbar_wait(&bar_aready[slot], (uint32_t)((i / A_RING) & 1), fail);
+            mbar_wait_nap(&bar_act[as], (uint32_t)((i / ACT_STAGES) & 1), fail, 32);
+            mbar_wait_nap(&bar_aready[slot], (uint32_t)((i / A_RING) & 1), fail, 32);
             tc_fence_after();
 #pragma unroll 1
             for (int blk = 0; blk < 8; blk++) {
                 const int G = 8 * i + blk, gb = G & 1;
                 if (G >= 2) {
-                    mbar_wait(&bar_epi[gb], (uint32_t)(((G - 2) >> 1) & 1), fail);   // accumulator gb drained
+                    mbar_wait_nap(&bar_epi[gb], (uint32_t)(((G - 2) >> 1) & 1), fail, 32);   // accumulator gb drained
                     tc_fence_after();
                 }
                 if (leader) {
@@ -451,9 +478,10 @@ __global__ void __launch_bounds__(tc8w::THREADS, 1) k_mmq_tc_q80_wide(const __gr
         const int q = warp & 3;
         const int row_in_tile = q * 32 + lane;
         const int col0 = ((warp - tc8w::EPI_WARP0) >> 2) * CW;
-        float yacc[CW];
+        static_assert(CW == 32, "the draining loop below takes two 16-column loads per block");
+        uint64_t yacc[CW / 2];
 #pragma unroll
-        for (int c = 0; c < CW; c++) yacc[c] = 0.f;
+        for (int c = 0; c < CW / 2; c++) yacc[c] = 0ull;   // two +0.0f
         const uint32_t lane_addr0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)col0;
         for (int i = 0; i < nst; i++) {
             const int as = i % ACT_STAGES, slot = i % A_RING;
@@ -465,36 +493,37 @@ __global__ void __launch_bounds__(tc8w::THREADS, 1) k_mmq_tc_q80_wide(const __gr
                 mbar_wait_relaxed(&bar_mma[gb], (uint32_t)((G >> 1) & 1), fail);
                 tc_fence_after();
                 const float w = dwr[blk * ROWS];
-                const float4 *dab = reinterpret_cast<const float4 *>(da + blk * NW);
-#pragma unroll
-                for (int h = 0; h < CW / 16; h++) {
-                    int D[16];
-                    tc8::tmem_ld16i(lane_addr0 + (uint32_t)(gb * NW + h * 16), D);
-                    tmem_ld_wait();
-                    if (h == CW / 16 - 1) {
-                        tc_fence_before();
-                        mbar_arrive(&bar_epi[gb]);   // accumulator gb may be overwritten
-                    }
-#pragma unroll
-                    for (int c4 = 0; c4 < 4; c4++) {
-                        const float4 s = dab[h * 4 + c4];
-                        yacc[h * 16 + c4 * 4 + 0] += (float)D[c4 * 4 + 0] * (w * s.x);
-                        yacc[h * 16 + c4 * 4 + 1] += (float)D[c4 * 4 + 1] * (w * s.y);
-                        yacc[h * 16 + c4 * 4 + 2] += (float)D[c4 * 4 + 2] * (w * s.z);
-                        yacc[h * 16 + c4 * 4 + 3] += (float)D[c4 * 4 + 3] * (w * s.w);
-                    }
-                }
+                const uint64_t ww = pack2(w, w);
+                const ulonglong2 *dab = reinterpret_cast<const ulonglong2 *>(da + blk * NW);
+                // the second load is in flight while the first half is added up
+                int D0[16], D1[16];
+                tc8::tmem_ld16i(lane_addr0 + (uint32_t)(gb * NW), D0);
+                tmem_ld_wait();
+                tc8::tmem_ld16i(lane_addr0 + (uint32_t)(gb * NW + 16), D1);
+                drain16(yacc, D0, ww, dab);
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_epi[gb]);   // accumulator gb may be overwritten
+                drain16(yacc + 8, D1, ww, dab + 4);
             }
-            mbar_arrive(&bar_dwfree[slot]);
-            mbar_arrive(&bar_actfree[as]);
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&bar_dwfree[slot]);
+                mbar_arrive(&bar_actfree[as]);
+            }
         }
         const int64_t row = (int64_t)row_tile * ROWS + row_in_tile;
         const int ncol = min(NW, p.N - col_tile * NW);
         if (row < p.M) {
             float *o = p.out + (size_t)col_tile * NW * p.ldy + row;
 #pragma unroll
-            for (int c = 0; c < CW; c++)
-                if (col0 + c < ncol) o[(size_t)(col0 + c) * p.ldy] = yacc[c];
+            for (int c = 0; c < CW / 2; c++) {
+                float lo, hi;
+                asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(yacc[c]));
+                if (col0 + 2 * c < ncol) o[(size_t)(col0 + 2 * c) * p.ldy] = lo;
+                if (col0 + 2 * c + 1 < ncol) o[(size_t)(col0 + 2 * c + 1) * p.ldy] = hi;
+            }
         }
     } else {
         // ---- realigning warps: lane quadrant = warp % 4 fixes the rows, every warp takes all eight blocks of its rows
@@ -502,11 +531,11 @@ __global__ void __launch_bounds__(tc8w::THREADS, 1) k_mmq_tc_q80_wide(const __gr
         const uint32_t a_lane = tmem_base + tc8::A_COL0 + ((uint32_t)((warp & 3) * 32) << 16);
         for (int i = 0; i < nst; i++) {
             const int rs = i % RAW_STAGES, slot = i % A_RING;
-            mbar_wait(&bar_raw[rs], (uint32_t)((i / RAW_STAGES) & 1), fail);
+            mbar_wait_nap(&bar_raw[rs], (uint32_t)((i / RAW_STAGES) & 1), fail, 128);
             if (i >= A_RING) {
                 // the MMAs that read this ring slot are done, and the draining warps have read its scales
-                mbar_wait(&bar_afree[slot], (uint32_t)(((i / A_RING) - 1) & 1), fail);
-                mbar_wait(&bar_dwfree[slot], (uint32_t)(((i / A_RING) - 1) & 1), fail);
+                mbar_wait_nap(&bar_afree[slot], (uint32_t)(((i / A_RING) - 1) & 1), fail, 128);
+                mbar_wait_nap(&bar_dwfree[slot], (uint32_t)(((i / A_RING) - 1) & 1), fail, 128);
                 tc_fence_after();
             }
             const uint8_t *rrow = raw + rs * tc8::RAW_BYTES + r * tc8::ROW_CHUNK;

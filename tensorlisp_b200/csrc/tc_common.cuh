@@ -89,6 +89,19 @@ __device__ __forceinline__ void mbar_wait_relaxed(uint64_t *bar, uint32_t parity
     }
     *fail = 1;
 }
+// The same with a chosen nap: for warps whose work is far ahead of its consumer, so that their probing does
+// not take issue slots from the warps that share their scheduler.
+__device__ __forceinline__ void mbar_wait_nap(uint64_t *bar, uint32_t parity, volatile int *fail, unsigned ns) {
+    const uint32_t a = su32(bar);
+    if (mbar_try(a, parity)) return;
+    if (*fail) return;
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+        __nanosleep(ns);
+        if (mbar_try(a, parity)) return;
+        if ((i & 1023) == 1023 && *fail) return;
+    }
+    *fail = 1;
+}
 __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(su32(dst)),
                  "l"(src), "r"(bytes), "r"(su32(bar))
