@@ -340,6 +340,9 @@ constexpr int EPI_WARPS = 16, DEQ_WARPS = 4;
 constexpr int EPI_WARP0 = 1, DEQ_WARP0 = EPI_WARP0 + EPI_WARPS, MMA_WARP = DEQ_WARP0 + DEQ_WARPS;
 constexpr int THREADS = (MMA_WARP + 1) * 32;             // 704
 constexpr int RAW_STAGES = 2, ACT_STAGES = 3;
+constexpr int N_ACC = 3;                                 // accumulators of NW columns in tensor memory columns [0, 384)
+constexpr uint32_t A_COL0 = N_ACC * NW;                  // the A ring behind them: 2 stages x 64 columns
+constexpr int A_RING = 2;
 constexpr int BLOB = NW * 288;
 constexpr int CW = NW / (EPI_WARPS / 4);                 // 32 columns per draining warp
 // two f32 lanes per instruction (each lane rounds as the scalar instruction does)
@@ -373,7 +376,7 @@ __global__ void __launch_bounds__(tc8w::THREADS, 1) k_mmq_tc_q80_wide(const __gr
     using namespace tc;
     using namespace tc8w;
     constexpr int ROWS = tc8::ROWS;
-    constexpr int A_RING = tc8::A_RING;
+    constexpr int A_RING = tc8w::A_RING;
     constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NW >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = smem_raw + ((1024u - (su32(smem_raw) & 1023u)) & 1023u);
@@ -381,7 +384,7 @@ __global__ void __launch_bounds__(tc8w::THREADS, 1) k_mmq_tc_q80_wide(const __gr
     uint8_t *actb = raw + RAW_STAGES * tc8::RAW_BYTES;                // ACT_STAGES x BLOB
     float *dw = reinterpret_cast<float *>(actb + ACT_STAGES * BLOB);  // [A_RING][8][ROWS] weight scales
     __shared__ uint64_t bar_raw[RAW_STAGES], bar_rawfree[RAW_STAGES], bar_act[ACT_STAGES], bar_actfree[ACT_STAGES];
-    __shared__ uint64_t bar_aready[A_RING], bar_afree[A_RING], bar_dwfree[A_RING], bar_mma[2], bar_epi[2];
+    __shared__ uint64_t bar_aready[A_RING], bar_afree[A_RING], bar_dwfree[A_RING], bar_mma[N_ACC], bar_epi[N_ACC];
     __shared__ uint32_t tmem_base_s;
     __shared__ int s_fail;
     volatile int *fail = &s_fail;
@@ -404,7 +407,7 @@ __global__ void __launch_bounds__(tc8w::THREADS, 1) k_mmq_tc_q80_wide(const __gr
             mbar_init(&bar_afree[i], 1);
             mbar_init(&bar_dwfree[i], EPI_WARPS);
         }
-        for (int i = 0; i < 2; i++) {
+        for (int i = 0; i < N_ACC; i++) {
             mbar_init(&bar_mma[i], 1);
             mbar_init(&bar_epi[i], EPI_WARPS);   // one arrival per draining warp
         }
@@ -451,6 +454,8 @@ __global__ void __launch_bounds__(tc8w::THREADS, 1) k_mmq_tc_q80_wide(const __gr
     } else if (warp == tc8w::MMA_WARP) {
         // ---- MMA issuer: the whole warp runs the loop (converged), one elected lane issues
         const bool leader = elect_one();
+        int gb = 0;            // accumulator of block G = 8 * i + blk: G % N_ACC, in its (G / N_ACC)-th use
+        uint32_t use = 0;
         for (int i = 0; i < nst; i++) {
             const int as = i % ACT_STAGES, slot = i % A_RING;
             const uint64_t b_desc0 = smem_desc(su32(actb + as * BLOB), 128, 2048);
@@ -459,18 +464,21 @@ __global__ void __launch_bounds__(tc8w::THREADS, 1) k_mmq_tc_q80_wide(const __gr
             tc_fence_after();
 #pragma unroll 1
             for (int blk = 0; blk < 8; blk++) {
-                const int G = 8 * i + blk, gb = G & 1;
-                if (G >= 2) {
-                    mbar_wait_nap(&bar_epi[gb], (uint32_t)(((G - 2) >> 1) & 1), fail, 32);   // accumulator gb drained
+                if (use > 0) {
+                    mbar_wait_nap(&bar_epi[gb], (use - 1) & 1, fail, 32);   // accumulator gb drained
                     tc_fence_after();
                 }
                 if (leader) {
-                    tc8::umma_i8_ta(tmem_base + (uint32_t)(gb * NW), tmem_base + tc8::A_COL0 + (uint32_t)(slot * 64 + blk * 8),
+                    tc8::umma_i8_ta(tmem_base + (uint32_t)(gb * NW), tmem_base + tc8w::A_COL0 + (uint32_t)(slot * 64 + blk * 8),
                                     b_desc0 + (uint64_t)(blk * (256 >> 4)), IDESC);
                     umma_commit(&bar_mma[gb]);
                     if (blk == 7) umma_commit(&bar_afree[slot]);
                 }
                 __syncwarp();
+                if (++gb == N_ACC) {
+                    gb = 0;
+                    use++;
+                }
             }
         }
     } else if (warp < tc8w::DEQ_WARP0) {
@@ -483,14 +491,15 @@ __global__ void __launch_bounds__(tc8w::THREADS, 1) k_mmq_tc_q80_wide(const __gr
 #pragma unroll
         for (int c = 0; c < CW / 2; c++) yacc[c] = 0ull;   // two +0.0f
         const uint32_t lane_addr0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)col0;
+        int gb = 0;
+        uint32_t use = 0;
         for (int i = 0; i < nst; i++) {
             const int as = i % ACT_STAGES, slot = i % A_RING;
             const float *da = reinterpret_cast<const float *>(actb + as * BLOB + NW * 256) + col0;   // [8][NW]
             const float *dwr = dw + (size_t)slot * 8 * ROWS + row_in_tile;
 #pragma unroll 1
             for (int blk = 0; blk < 8; blk++) {
-                const int G = 8 * i + blk, gb = G & 1;
-                mbar_wait_relaxed(&bar_mma[gb], (uint32_t)((G >> 1) & 1), fail);
+                mbar_wait_relaxed(&bar_mma[gb], use & 1, fail);
                 tc_fence_after();
                 const float w = dwr[blk * ROWS];
                 const uint64_t ww = pack2(w, w);
@@ -506,6 +515,10 @@ __global__ void __launch_bounds__(tc8w::THREADS, 1) k_mmq_tc_q80_wide(const __gr
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bar_epi[gb]);   // accumulator gb may be overwritten
                 drain16(yacc + 8, D1, ww, dab + 4);
+                if (++gb == N_ACC) {
+                    gb = 0;
+                    use++;
+                }
             }
             __syncwarp();
             if (lane == 0) {
@@ -528,7 +541,7 @@ __global__ void __launch_bounds__(tc8w::THREADS, 1) k_mmq_tc_q80_wide(const __gr
     } else {
         // ---- realigning warps: lane quadrant = warp % 4 fixes the rows, every warp takes all eight blocks of its rows
         const int r = (warp & 3) * 32 + lane;
-        const uint32_t a_lane = tmem_base + tc8::A_COL0 + ((uint32_t)((warp & 3) * 32) << 16);
+        const uint32_t a_lane = tmem_base + tc8w::A_COL0 + ((uint32_t)((warp & 3) * 32) << 16);
         for (int i = 0; i < nst; i++) {
             const int rs = i % RAW_STAGES, slot = i % A_RING;
             mbar_wait_nap(&bar_raw[rs], (uint32_t)((i / RAW_STAGES) & 1), fail, 128);
@@ -569,7 +582,7 @@ __global__ void __launch_bounds__(tc8w::THREADS, 1) k_mmq_tc_q80_wide(const __gr
 }
 
 static size_t tc8w_smem() {
-    return (size_t)tc8w::RAW_STAGES * tc8::RAW_BYTES + (size_t)tc8w::ACT_STAGES * tc8w::BLOB + (size_t)tc8::A_RING * 8 * tc8::ROWS * sizeof(float) + 1024;
+    return (size_t)tc8w::RAW_STAGES * tc8::RAW_BYTES + (size_t)tc8w::ACT_STAGES * tc8w::BLOB + (size_t)tc8w::A_RING * 8 * tc8::ROWS * sizeof(float) + 1024;
 }
 
 // ---------------------------------------------------------------- host side
