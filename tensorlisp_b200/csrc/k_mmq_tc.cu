@@ -100,6 +100,7 @@ struct TcParams {
     // sk_partial[tile][0 = has the tile's start, 1 = has its end][N][128], added by k_mmq_sk_fixup.
     int streamk, total_tiles;
     float *sk_partial;
+    int nap_mma, nap_epi, nap_tma;   // nanoseconds between barrier probes of the roles that run ahead of the expanding warps
 };
 
 // CTA that works on unit u when G CTAs split T units as above
@@ -110,24 +111,47 @@ __host__ __device__ inline int sk_cta_of(int64_t u, int64_t T, int G) {
     return c;
 }
 
+// packed f32 pairs: one instruction for two columns of the epilogue
+__device__ __forceinline__ uint64_t f2pack(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void f2unpack(uint64_t v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t f2mul(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t f2fma(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
 template <int NPAD, int RAW_STAGES, int ACT_STAGES>
 __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_constant__ TcMaps maps, TcParams p) {
     using namespace tc;
     constexpr int BLOB = (NPAD * 548 + 127) / 128 * 128;
     constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(NPAD >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);  // f16 x f16 -> f32, K-major A and B
+    // Tensor memory: the S and T accumulators of two super-blocks in [0, 4 NPAD); behind them a ring of whole
+    // super-blocks of the A operand, four quarters of 32 columns (64 f16 per row) each.
+    constexpr uint32_t A_COL0 = 4 * NPAD;
+    constexpr int RING = (int)(TMEM_COLS - A_COL0) / 128;   // super-blocks in the ring: 3 (2 for 64 columns)
+    constexpr int META = 4;                                  // (d, dmin) and the mins operand are kept for four super-blocks
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = smem_raw + ((1024u - (tc::su32(smem_raw) & 1023u)) & 1023u);   // 1 KB of slack is allocated for this
     uint8_t *raw = smem;                                   // RAW_STAGES x RAW_BYTES
     uint8_t *actb = raw + RAW_STAGES * RAW_BYTES;          // ACT_STAGES x BLOB
-    uint8_t *amin = actb + ACT_STAGES * BLOB;              // 2 x AMIN_BYTES (by super-block parity)
-    float2 *dd = reinterpret_cast<float2 *>(amin + 2 * AMIN_BYTES);  // [2][ROWS] (d, dmin) by super-block parity
-    __shared__ uint64_t bar_raw[RAW_STAGES], bar_act[ACT_STAGES], bar_afree[A_RING], bar_mma[2], bar_epi[2], bar_aready[A_RING], bar_rawfree[RAW_STAGES], bar_actfree[ACT_STAGES];
+    uint8_t *amin = actb + ACT_STAGES * BLOB;              // META x AMIN_BYTES
+    float2 *dd = reinterpret_cast<float2 *>(amin + META * AMIN_BYTES);  // [META][ROWS] (d, dmin)
+    __shared__ uint64_t bar_raw[RAW_STAGES], bar_act[ACT_STAGES], bar_afree[RING * 4], bar_mma[2], bar_epi[META], bar_aready[RING * 4], bar_rawfree[RAW_STAGES],
+        bar_actfree[ACT_STAGES];
     __shared__ uint32_t tmem_base_s;
     __shared__ int s_fail;
     volatile int *fail = &s_fail;
 
     const int tid = threadIdx.x, warp = tid >> 5;
-    if (tid == 0) TC_STAMP(0);
     // This CTA's units of the flattened (row tile, super-block) space: one K range of one tile (grid = tiles x
     // splits), or with stream-K an equal share of all units.
     const int split = p.streamk ? 0 : blockIdx.y;
@@ -151,19 +175,17 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
     if (tid == 0) {
         for (int i = 0; i < RAW_STAGES; i++) {
             mbar_init(&bar_raw[i], 1);
-            mbar_init(&bar_rawfree[i], 16);
+            mbar_init(&bar_rawfree[i], 16);   // one arrival per expanding warp
         }
         for (int i = 0; i < ACT_STAGES; i++) {
             mbar_init(&bar_act[i], 1);
             mbar_init(&bar_actfree[i], 256);
         }
-        for (int i = 0; i < 2; i++) {
-            mbar_init(&bar_mma[i], 1);
-            mbar_init(&bar_epi[i], 256);
-        }
-        for (int i = 0; i < A_RING; i++) {
+        for (int i = 0; i < 2; i++) mbar_init(&bar_mma[i], 1);
+        for (int i = 0; i < META; i++) mbar_init(&bar_epi[i], 256);
+        for (int i = 0; i < RING * 4; i++) {
             mbar_init(&bar_afree[i], 1);
-            mbar_init(&bar_aready[i], 8);   // one arrival per expanding warp
+            mbar_init(&bar_aready[i], 4);   // the four warps (one per lane quadrant) that expand this quarter
         }
         s_fail = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -173,7 +195,6 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
-    if (tid == 0) TC_STAMP(1);
 
     // (tile, super-block) of the first unit; the loaders and the epilogue walk on from there without divisions
     const int tile_first = (int)(u0 / p.nsb), sb_first = (int)(u0 - (int64_t)tile_first * p.nsb);
@@ -209,20 +230,22 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
     //   warp 25             issues the MMAs (one elected lane)
     //   warps 1..8          epilogue: TMEM -> registers, f32 scaling, final store (lane quadrant = warp % 4,
     //                       two warps per quadrant split the columns)
-    //   warps 9..24         expand the raw nibbles into the f16 operand (lane quadrant = warp % 4; per
-    //                       quadrant four warps: low/high 16 bytes of a chunk x even/odd quarters)
+    //   warps 9..24         expand the raw nibbles into the f16 operand: lane quadrant = warp % 4 (a warp may
+    //                       only touch the 32 TMEM lanes of its quadrant), quarter of the super-block =
+    //                       (warp - 9) / 4, so a thread owns one 32-byte qs chunk of its row: 64 weights of two
+    //                       sub-blocks, and nobody decodes a scale twice
     const int lane = tid & 31;
     if (warp == 0) {
-        // ---- TMA producer: refills a raw stage once every expanding thread has left it, and an
+        // ---- TMA producer: refills a raw stage once every expanding warp has left it, and an
         // activation stage once the epilogue of its super-block has read its scales
         if (lane == 0) {
             for (int i = 0; i < nsb; i++) {
                 if (i + RAW_STAGES < nsb) {
-                    mbar_wait_relaxed(&bar_rawfree[i % RAW_STAGES], (uint32_t)((i / RAW_STAGES) & 1), fail);   // every expanding thread has left it
+                    mbar_wait_nap(&bar_rawfree[i % RAW_STAGES], (uint32_t)((i / RAW_STAGES) & 1), fail, p.nap_tma);
                     load_raw(i + RAW_STAGES);
                 }
                 if (i >= 1 && i - 1 + ACT_STAGES < nsb) {
-                    mbar_wait_relaxed(&bar_actfree[(i - 1) % ACT_STAGES], (uint32_t)(((i - 1) / ACT_STAGES) & 1), fail);
+                    mbar_wait_nap(&bar_actfree[(i - 1) % ACT_STAGES], (uint32_t)(((i - 1) / ACT_STAGES) & 1), fail, p.nap_tma);
                     load_act(i - 1 + ACT_STAGES);
                 }
             }
@@ -232,21 +255,22 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
         // the loop (converged, so the descriptor arithmetic stays on the uniform datapath); one
         // elected lane issues.
         const bool leader = elect_one();
+        int ring_u = 0;
+        uint32_t ring_ph = 0;
         for (int i = 0; i < nsb; i++) {
-            const int as = i % ACT_STAGES, b = i & 1;
+            const int as = i % ACT_STAGES, b = i & 1, mt = i & (META - 1);
             const uint32_t d_S = tmem_base + (uint32_t)(b * 2 * NPAD), d_T = d_S + NPAD;
             const uint64_t b_desc0 = smem_desc(su32(actb + as * BLOB), 128, 4096);
-            const uint64_t am_desc = smem_desc(su32(amin + b * AMIN_BYTES), 128, 256);
+            const uint64_t am_desc = smem_desc(su32(amin + mt * AMIN_BYTES), 128, 256);
             const uint64_t bm_desc = smem_desc(su32(actb + as * BLOB + NPAD * 512), 128, 256);
-            mbar_wait(&bar_act[as], (uint32_t)((i / ACT_STAGES) & 1), fail);
-            if (i >= 2) mbar_wait(&bar_epi[b], (uint32_t)(((i - 2) >> 1) & 1), fail);   // TMEM buffer b drained
+            mbar_wait_nap(&bar_act[as], (uint32_t)((i / ACT_STAGES) & 1), fail, p.nap_mma);
+            if (i >= 2) mbar_wait_nap(&bar_epi[(i - 2) & (META - 1)], (uint32_t)(((i - 2) / META) & 1), fail, p.nap_mma);   // TMEM buffer b drained
 #pragma unroll
             for (int qd = 0; qd < 4; qd++) {
-                const int gq = 4 * i + qd, buf = gq & (A_RING - 1);
-                mbar_wait(&bar_aready[buf], (uint32_t)((gq / A_RING) & 1), fail);
+                const int slot = ring_u * 4 + qd;
+                mbar_wait_nap(&bar_aready[slot], ring_ph, fail, p.nap_mma);
                 tc_fence_after();
-                if (lane == 0) TC_STAMP(16 + 4 * i + qd);
-                const uint32_t ta = tmem_base + A_COL0 + (uint32_t)(buf * 32);   // 4 K chunks x 8 columns
+                const uint32_t ta = tmem_base + A_COL0 + (uint32_t)(slot * 32);   // 4 K chunks x 8 columns
                 const uint64_t bd = b_desc0 + (uint64_t)(qd * 8 * (128 >> 4));
                 if (leader) {
                     umma_f16_ta(d_S, ta, bd, IDESC, qd ? 1u : 0u);
@@ -254,10 +278,14 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
                     umma_f16_ta(d_S, ta + 16, bd + 32, IDESC, 1u);
                     umma_f16_ta(d_S, ta + 24, bd + 48, IDESC, 1u);
                     if (qd == 0) umma_f16(d_T, am_desc, bm_desc, IDESC, 0u);
-                    umma_commit(&bar_afree[buf]);
+                    umma_commit(&bar_afree[slot]);
                     if (qd == 3) umma_commit(&bar_mma[b]);
                 }
                 __syncwarp();
+            }
+            if (++ring_u == RING) {
+                ring_u = 0;
+                ring_ph ^= 1u;
             }
         }
     } else if (warp < DEQ_WARP0) {
@@ -265,9 +293,9 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
         const int row_in_tile = q * 32 + lane;
         constexpr int CW = NPAD / 2;            // columns of this warp
         const int col0 = ((warp - EPI_WARP0) >> 2) * CW;
-        float yacc[CW];
+        uint64_t yacc[CW / 2];                  // two columns per register pair
 #pragma unroll
-        for (int c = 0; c < CW; c++) yacc[c] = 0.f;
+        for (int c = 0; c < CW / 2; c++) yacc[c] = 0ull;
         // the sums of a finished tile go out: to y, to the K-split partial sums, or (stream-K, tile cut by a CTA
         // boundary) to one of the tile's two stream-K partial results
         auto store_tile = [&](int gtile) {
@@ -276,36 +304,41 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
             float *out_mat = mat == 0 ? p.out[0] : (mat == 1 ? p.out[1] : p.out[2]);
             const int64_t row = (int64_t)tile_in_mat(gtile, mat) * ROWS + row_in_tile;
             const int64_t t0 = (int64_t)gtile * p.nsb;
+            float *o;
+            int64_t ldo;
             if (p.streamk && (t0 < u0 || t0 + p.nsb > u1)) {
-                float *o = p.sk_partial + ((size_t)gtile * 2 + (t0 >= u0 ? 0 : 1)) * p.N * ROWS + row_in_tile;
-#pragma unroll
-                for (int c = 0; c < CW; c++)
-                    if (col0 + c < p.N) o[(size_t)(col0 + c) * ROWS] = yacc[c];
+                o = p.sk_partial + ((size_t)gtile * 2 + (t0 >= u0 ? 0 : 1)) * p.N * ROWS + row_in_tile;
+                ldo = ROWS;
             } else if (row < M_mat) {
                 // partial sums [split][N][M] and the outputs of a group are dense; a single matrix may have its own stride
-                const int64_t ldo = (p.n_split > 1 || p.n_mats > 1) ? M_mat : p.ldy;
-                float *o = out_mat + (size_t)split * p.N * ldo + row;
+                ldo = (p.n_split > 1 || p.n_mats > 1) ? M_mat : p.ldy;
+                o = out_mat + (size_t)split * p.N * ldo + row;
+            } else {
+                return;
+            }
 #pragma unroll
-                for (int c = 0; c < CW; c++)
-                    if (col0 + c < p.N) o[(size_t)(col0 + c) * ldo] = yacc[c];
+            for (int c = 0; c < CW / 2; c++) {
+                float v0, v1;
+                f2unpack(yacc[c], v0, v1);
+                if (col0 + 2 * c < p.N) o[(size_t)(col0 + 2 * c) * ldo] = v0;
+                if (col0 + 2 * c + 1 < p.N) o[(size_t)(col0 + 2 * c + 1) * ldo] = v1;
             }
         };
         int cur_tile = tile_first, e_sb = sb_first;
         for (int i = 0; i < nsb; i++) {
-            const int b = i & 1;
+            const int b = i & 1, mt = i & (META - 1);
             if (e_sb == p.nsb) {   // stream-K only: the previous unit was the last one of its tile
                 store_tile(cur_tile);
 #pragma unroll
-                for (int c = 0; c < CW; c++) yacc[c] = 0.f;
+                for (int c = 0; c < CW / 2; c++) yacc[c] = 0ull;
                 cur_tile++;
                 e_sb = 0;
             }
             e_sb++;
-            mbar_wait_relaxed(&bar_mma[b], (uint32_t)((i >> 1) & 1), fail);
+            mbar_wait_nap(&bar_mma[b], (uint32_t)((i >> 1) & 1), fail, p.nap_epi);
             tc_fence_after();
-            if (tid == 32) TC_STAMP(96 + 2 * i);
-            const float2 sc = dd[b * ROWS + row_in_tile];
-            const float *yd = reinterpret_cast<const float *>(actb + (i % ACT_STAGES) * BLOB + NPAD * 544) + col0;
+            const float2 sc = dd[mt * ROWS + row_in_tile];
+            const float2 *yd = reinterpret_cast<const float2 *>(actb + (i % ACT_STAGES) * BLOB + NPAD * 544) + (col0 >> 1);
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * 2 * NPAD + col0);
             // all loads are in flight before the one wait; the TMEM buffer is handed back as soon as
             // the values sit in registers, before the arithmetic
@@ -322,59 +355,65 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
             }
             tmem_ld_wait();
             tc_fence_before();
-            mbar_arrive(&bar_epi[b]);   // TMEM buffer b, dd[b] and amin[b] may be reused
+            mbar_arrive(&bar_epi[mt]);   // TMEM buffer b, dd[mt] and amin[mt] may be reused
+            const float ds = sc.x * 16384.f;   // the weight operand carries 2^-14
+            const uint64_t d2 = f2pack(ds, ds), m2 = f2pack(-sc.y, -sc.y);
 #pragma unroll
-            for (int c = 0; c < CW; c++) yacc[c] += yd[c] * (sc.x * S[c] - sc.y * T[c]);
+            for (int c = 0; c < CW / 2; c++) {
+                const float2 y2 = yd[c];
+                // yd * (d * S - dmin * T), two columns per instruction
+                const uint64_t t = f2fma(m2, f2pack(T[2 * c], T[2 * c + 1]), f2mul(d2, f2pack(S[2 * c], S[2 * c + 1])));
+                yacc[c] = f2fma(f2pack(y2.x, y2.y), t, yacc[c]);
+            }
             mbar_arrive(&bar_actfree[i % ACT_STAGES]);
-            if (tid == 32) TC_STAMP(97 + 2 * i);
         }
         store_tile(cur_tile);
     } else {
-        // a warp may only touch the 32 TMEM lanes of its quadrant (warp % 4): that fixes its rows
-        const int dt = tid - DEQ_WARP0 * 32;
-        const int grp = (warp - DEQ_WARP0) >> 2;
-        const int r = (warp & 3) * 32 + lane;   // row
-        const int hp = grp & 1;                 // which 16 bytes of each 32-byte qs chunk
-        const int qpar = grp >> 1;              // which quarters of a super-block: 0 -> 0 and 2, 1 -> 1 and 3
-        const uint32_t a_lane = tmem_base + A_COL0 + ((uint32_t)((warp & 3) * 32) << 16);
-        // Stores into the A ring are published one quarter late: the stores of quarter g are issued, the
-        // values of quarter g+1 are computed, and only then does the thread wait for its stores and
-        // arrive on g's barrier, so the TMEM store latency hides behind arithmetic.
+        const int q = warp & 3;                            // lane quadrant
+        const int qd = (warp - DEQ_WARP0) >> 2;            // quarter of the super-block: qs chunk qd = sub-blocks 2qd (low nibbles), 2qd+1 (high)
+        const int r = q * 32 + lane;                       // row
+        const uint32_t a_lane = tmem_base + A_COL0 + ((uint32_t)(q * 32) << 16);
+        const __half2 k1024 = __half2(__ushort_as_half(0x6400), __ushort_as_half(0x6400));
+        // A quarter is published (its barrier arrived on) only after the low nibbles of the NEXT super-block
+        // have been computed, so the latency of the TMEM stores hides behind arithmetic; the first
+        // super-block is published at once so that the first MMA starts early, the last one after the loop.
         int pend = -1;   // ring slot with stores in flight
         auto publish = [&]() {
-            TC_CLK(c_pub);
             tmem_st_wait();
-            if (warp == DEQ_WARP0 || warp == DEQ_WARP0 + 12) TC_ACC(226 + (warp == DEQ_WARP0 ? 0 : 8), c_pub);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_aready[pend]);
+            pend = -1;
         };
+        int ring_u = 0;
+        uint32_t ring_ph = 0;
+        // The loop is software-pipelined: the 48 raw bytes of the next super-block are read into registers at the
+        // end of an iteration, and the barriers an iteration will need (raw data of the next super-block, the ring
+        // slot being free) are tested without blocking at its start, so that their latencies run under the
+        // arithmetic; a blocking wait follows only where the early test said "not yet".
+        const uint8_t *rbase = raw + r * 144;
+        mbar_wait(&bar_raw[0], 0u, fail);
+        uint4 hdr = *reinterpret_cast<const uint4 *>(rbase);
+        uint4 w0 = *reinterpret_cast<const uint4 *>(rbase + 16 + qd * 32);
+        uint4 w1 = *reinterpret_cast<const uint4 *>(rbase + 32 + qd * 32);
         for (int i = 0; i < nsb; i++) {
-            const int rs = i % RAW_STAGES;
-            TC_CLK(c_raw);
-            mbar_wait(&bar_raw[rs], (uint32_t)((i / RAW_STAGES) & 1), fail);
-            if (warp == DEQ_WARP0 || warp == DEQ_WARP0 + 12) TC_ACC(224 + (warp == DEQ_WARP0 ? 0 : 8), c_raw);
-            TC_CLK(c_body);
-            if (dt == 0) TC_STAMP(160 + 4 * i);
-            const uint8_t *rrow = raw + rs * RAW_BYTES + r * 144;
-            const uint4 hdr = *reinterpret_cast<const uint4 *>(rrow);
-            uint4 wq[2];   // this thread's 16 bytes of its two 32-byte qs chunks
-#pragma unroll
-            for (int h = 0; h < 2; h++) wq[h] = *reinterpret_cast<const uint4 *>(rrow + 16 + (2 * h + qpar) * 32 + hp * 16);
-            // 6-bit scales and mins of the eight sub-blocks (get_scale_min_k4, ggml-quants.c:880-887)
-            uint32_t sc8[2], mn8[2];   // four bytes each
-            sc8[0] = hdr.y & 0x3f3f3f3fu;
-            mn8[0] = hdr.z & 0x3f3f3f3fu;
-            sc8[1] = (hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u);
-            mn8[1] = ((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u);
-            const __half2 k1024 = __half2(__ushort_as_half(0x6400), __ushort_as_half(0x6400));
-            if (grp == 0) {
+            const int rs = i % RAW_STAGES, rn = (i + 1) % RAW_STAGES;
+            const uint32_t rn_par = (uint32_t)(((i + 1) / RAW_STAGES) & 1);
+            const int slot = ring_u * 4 + qd;
+            const bool next_ready = i + 1 < nsb ? mbar_test(su32(&bar_raw[rn]), rn_par) : true;
+            const bool slot_free = i >= RING ? mbar_test(su32(&bar_afree[slot]), ring_ph ^ 1u) : true;
+            // 6-bit scales of the eight sub-blocks, four per word (get_scale_min_k4, ggml-quants.c:880-887);
+            // this warp needs bytes 2 (qd & 1) and 2 (qd & 1) + 1 of the word that holds sub-blocks 4 (qd / 2) ...
+            const uint32_t sc4 = qd < 2 ? (hdr.y & 0x3f3f3f3fu) : ((hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u));
+            if (qd == 0) {
                 // (d, dmin) for the epilogue and the mins as the f16 operand of the T product
-                TC_CLK(c_ep);
-                if (i >= 2) mbar_wait(&bar_epi[i & 1], (uint32_t)(((i - 2) >> 1) & 1), fail);   // those of i-2 consumed
-                if (warp == DEQ_WARP0) TC_ACC(228, c_ep);
-                dd[(i & 1) * ROWS + r] = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
-                uint8_t *am = amin + (i & 1) * AMIN_BYTES + (r >> 3) * 256 + (r & 7) * 16;
+                const int mt = i & (META - 1);
+                if (i >= META) mbar_wait(&bar_epi[mt], (uint32_t)(((i - META) / META) & 1), fail);   // those of i - META consumed
+                dd[mt * ROWS + r] = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
+                uint32_t mn8[2];
+                mn8[0] = hdr.z & 0x3f3f3f3fu;
+                mn8[1] = ((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u);
+                uint8_t *am = amin + mt * AMIN_BYTES + (r >> 3) * 256 + (r & 7) * 16;
 #pragma unroll
                 for (int kc = 0; kc < 2; kc++) {
                     // small integer -> f16 without a conversion: bytes (m, 0x64) are the f16 1024 + m
@@ -391,56 +430,63 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> async-proxy (MMA) reads
             }
+            // f16 scale pairs (sc, sc), built from the integer bytes without conversions: bytes (sc, 0x64) are the
+            // f16 1024 + sc. A 4-bit code masked out of a word where it stands, (w & 0x000f) or (w & 0x00f0), is
+            // the f16 SUBNORMAL q * 2^-24 or q * 2^-20; times sc * 2^10 or sc * 2^6 that is sc * q * 2^-14, a normal
+            // f16 number, exactly (sc * q <= 945 has 10 bits). So a pair of weights costs one AND with an immediate
+            // and one HMUL2, no constants are held in registers, and the epilogue multiplies S by 2^14.
+            uint32_t tl = __byte_perm(sc4, 0x64646464u, (qd & 1) ? 0x4242 : 0x4040);
+            uint32_t th = __byte_perm(sc4, 0x64646464u, (qd & 1) ? 0x4343 : 0x4141);
+            const __half2 mlo = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&tl), k1024), __half2(__ushort_as_half(0x6400), __ushort_as_half(0x6400)));   // sc * 2^10
+            const __half2 mhi = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&th), k1024), __half2(__ushort_as_half(0x5400), __ushort_as_half(0x5400)));   // sc * 2^6
+            const uint32_t ws[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+            // 32 low-nibble values (K chunks 0 and 1 of the quarter), two per 32-bit column in the order the nibbles
+            // leave a word: (0,2) (1,3) (4,6) (5,7) ...; then the 32 high-nibble values (K chunks 2 and 3)
+            uint32_t v[16];
 #pragma unroll
-            for (int h = 0; h < 2; h++) {
-                // quarter qd = qs chunk qd = sub-blocks 2qd (low nibbles) and 2qd+1 (high nibbles)
-                const int qd = 2 * h + qpar;
-                const int gq = i * 4 + qd, buf = gq & (A_RING - 1);
-                // f16 scale pairs (sc, sc) and their biases, built from the integer bytes without conversions
-                uint32_t tl = __byte_perm(sc8[h], 0x64646464u, qpar ? 0x4242 : 0x4040);
-                uint32_t th = __byte_perm(sc8[h], 0x64646464u, qpar ? 0x4343 : 0x4141);
-                const __half2 mlo = __hsub2(*reinterpret_cast<__half2 *>(&tl), k1024), mhi = __hsub2(*reinterpret_cast<__half2 *>(&th), k1024);
-                const __half2 blo = __hmul2(mlo, __half2(__ushort_as_half(0xE400), __ushort_as_half(0xE400)));   // -1024 * sc
-                const __half2 bhi = __hmul2(mhi, __half2(__ushort_as_half(0xD400), __ushort_as_half(0xD400)));   // -64 * sc
-                const uint32_t ws[4] = {wq[h].x, wq[h].y, wq[h].z, wq[h].w};
-                // 16 low-nibble values (K chunk hp of the quarter) and 16 high-nibble values (K chunk 2 + hp),
-                // two per 32-bit column in the order the nibbles leave a word: (0,2) (1,3) (4,6) (5,7) ...
-                uint32_t lo[8], hi[8];
-#pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    const uint32_t a = ws[k], bb = ws[k] >> 8;
-                    uint32_t t0 = (a & 0x000f000fu) | 0x64006400u, t1 = (bb & 0x000f000fu) | 0x64006400u;
-                    uint32_t u0 = (a & 0x00f000f0u) | 0x54005400u, u1 = (bb & 0x00f000f0u) | 0x54005400u;
-                    const __half2 l0 = __hfma2(*reinterpret_cast<__half2 *>(&t0), mlo, blo);   // (1024+q)*sc - 1024*sc, exact
-                    const __half2 l1 = __hfma2(*reinterpret_cast<__half2 *>(&t1), mlo, blo);
-                    const __half2 h0 = __hfma2(*reinterpret_cast<__half2 *>(&u0), mhi, bhi);   // (64+q)*sc - 64*sc, exact
-                    const __half2 h1 = __hfma2(*reinterpret_cast<__half2 *>(&u1), mhi, bhi);
-                    lo[2 * k] = *reinterpret_cast<const uint32_t *>(&l0);
-                    lo[2 * k + 1] = *reinterpret_cast<const uint32_t *>(&l1);
-                    hi[2 * k] = *reinterpret_cast<const uint32_t *>(&h0);
-                    hi[2 * k + 1] = *reinterpret_cast<const uint32_t *>(&h1);
-                }
-                if (pend >= 0) publish();
-                if (gq >= A_RING) {   // the MMAs that read this ring slot last time are done
-                    TC_CLK(c_af);
-                    mbar_wait(&bar_afree[buf], (uint32_t)(((gq / A_RING) - 1) & 1), fail);
-                    tc_fence_after();
-                    if (warp == DEQ_WARP0 || warp == DEQ_WARP0 + 12) TC_ACC(227 + (warp == DEQ_WARP0 ? 0 : 8), c_af);
-                }
-                tmem_st8(a_lane + (uint32_t)(buf * 32 + hp * 8), lo);
-                tmem_st8(a_lane + (uint32_t)(buf * 32 + (2 + hp) * 8), hi);
-                pend = buf;
-                if (dt == 0) TC_STAMP(161 + 4 * i + h);
+            for (int k = 0; k < 8; k++) {
+                uint32_t t0 = ws[k] & 0x000f000fu, t1 = (ws[k] >> 8) & 0x000f000fu;
+                const __half2 l0 = __hmul2(*reinterpret_cast<__half2 *>(&t0), mlo);
+                const __half2 l1 = __hmul2(*reinterpret_cast<__half2 *>(&t1), mlo);
+                v[2 * k] = *reinterpret_cast<const uint32_t *>(&l0);
+                v[2 * k + 1] = *reinterpret_cast<const uint32_t *>(&l1);
             }
-            publish();   // nothing of this super-block stays unpublished while the warp waits for the next one
-            pend = -1;
+            if (pend >= 0) publish();
+            if (i >= RING) {   // the MMAs that read this ring slot last time are done
+                if (!slot_free) mbar_wait(&bar_afree[slot], ring_ph ^ 1u, fail);
+                tc_fence_after();
+            }
+            tmem_st16(a_lane + (uint32_t)(slot * 32), v);
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                uint32_t u0 = ws[k] & 0x00f000f0u, u1 = (ws[k] >> 8) & 0x00f000f0u;
+                const __half2 h0 = __hmul2(*reinterpret_cast<__half2 *>(&u0), mhi);
+                const __half2 h1 = __hmul2(*reinterpret_cast<__half2 *>(&u1), mhi);
+                v[2 * k] = *reinterpret_cast<const uint32_t *>(&h0);
+                v[2 * k + 1] = *reinterpret_cast<const uint32_t *>(&h1);
+            }
+            tmem_st16(a_lane + (uint32_t)(slot * 32 + 16), v);
+            pend = slot;
+            if (i == 0) publish();
+            // the next super-block's bytes into registers; then this raw stage may be refilled
+            if (i + 1 < nsb) {
+                if (!next_ready) mbar_wait(&bar_raw[rn], rn_par, fail);
+                const uint8_t *rrow = rbase + rn * RAW_BYTES;
+                hdr = *reinterpret_cast<const uint4 *>(rrow);
+                w0 = *reinterpret_cast<const uint4 *>(rrow + 16 + qd * 32);
+                w1 = *reinterpret_cast<const uint4 *>(rrow + 32 + qd * 32);
+            }
+            __syncwarp();
             if (lane == 0) mbar_arrive(&bar_rawfree[rs]);
-            if (warp == DEQ_WARP0 || warp == DEQ_WARP0 + 12) TC_ACC(225 + (warp == DEQ_WARP0 ? 0 : 8), c_body);
+            if (++ring_u == RING) {
+                ring_u = 0;
+                ring_ph ^= 1u;
+            }
         }
+        if (pend >= 0) publish();
     }
     tc_fence_before();
     __syncthreads();
-    if (tid == 0) TC_STAMP(2);
     if (warp == 0) tmem_dealloc(tmem_base, TMEM_COLS);
     if (tid == 0 && s_fail) atomicExch(p.err, 2);
 }
@@ -532,8 +578,8 @@ static EncodeTiledFn encode_tiled() {
 
 template <int NPAD, int RS, int AS>
 static size_t tc_smem() {
-    return (size_t)RS * tc::RAW_BYTES + (size_t)AS * tc_blob_bytes(NPAD) + 2 * tc::AMIN_BYTES +
-           2 * tc::ROWS * sizeof(float2) + 1024;
+    return (size_t)RS * tc::RAW_BYTES + (size_t)AS * tc_blob_bytes(NPAD) + 4 * tc::AMIN_BYTES +
+           4 * tc::ROWS * sizeof(float2) + 1024;
 }
 
 void mmq_tc_configure() {
@@ -649,6 +695,13 @@ cudaError_t launch_mmq_tc_group(const TcPlan &t, int n_mats, const void *const *
     base.total_tiles = tiles;
     base.streamk = t.streamk;
     base.sk_partial = (float *)partial;
+    {
+        static const int nm = getenv("TLB_NAP_MMA") ? atoi(getenv("TLB_NAP_MMA")) : 0, ne = getenv("TLB_NAP_EPI") ? atoi(getenv("TLB_NAP_EPI")) : 64,
+                         nt = getenv("TLB_NAP_TMA") ? atoi(getenv("TLB_NAP_TMA")) : 64;
+        base.nap_mma = nm;
+        base.nap_epi = ne;
+        base.nap_tma = nt;
+    }
     if (t.streamk && (t.n_split != 1 || t.n_col_chunks != 1 || (int64_t)tiles * t.nsb / t.streamk < t.nsb)) return cudaErrorInvalidValue;
     dim3 grid(t.streamk ? (unsigned)t.streamk : (unsigned)tiles, (unsigned)t.n_split);
     cudaError_t e = cudaSuccess;

@@ -7,26 +7,6 @@
 
 namespace tlb {
 
-#ifdef TC_DEBUG
-__device__ unsigned long long g_tc_dbg[256];
-#define TC_STAMP(slot)                                                                         \
-    do {                                                                                       \
-        if (blockIdx.x == 0 && blockIdx.y == 0) {                                              \
-            unsigned long long t__;                                                            \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));                              \
-            g_tc_dbg[slot] = t__;                                                              \
-        }                                                                                      \
-    } while (0)
-#define TC_CLK(var) long long var = clock64()
-#define TC_ACC(slot, t0)                                                                       \
-    do {                                                                                       \
-        if (blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0) atomicAdd(&g_tc_dbg[slot], (unsigned long long)(clock64() - (t0))); \
-    } while (0)
-#else
-#define TC_STAMP(slot) do {} while (0)
-#define TC_CLK(var) do {} while (0)
-#define TC_ACC(slot, t0) do {} while (0)
-#endif
 
 namespace tc {
 
@@ -34,9 +14,7 @@ constexpr int ROWS = 128;          // rows per CTA tile (UMMA M)
 constexpr int THREADS = 832;          // TMA warp + 8 epilogue warps + 16 expanding warps + MMA warp
 constexpr int EPI_WARP0 = 1, DEQ_WARP0 = 9, MMA_WARP = 25;
 constexpr int RAW_BYTES = ROWS * 144;
-constexpr uint32_t TMEM_COLS = 512;           // all of it: accumulators in [0, 256), the A ring in [256, 512)
-constexpr uint32_t A_COL0 = 256;              // ring of 8 quarter super-blocks, 32 columns (64 f16 per row) each
-constexpr int A_RING = 8;
+constexpr uint32_t TMEM_COLS = 512;           // all of it: accumulators first, the ring of A quarters behind them
 constexpr int AMIN_BYTES = ROWS * 16 * 2;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
@@ -66,42 +44,50 @@ __device__ __forceinline__ bool mbar_try(uint32_t a, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// non-blocking test of a phase
+__device__ __forceinline__ bool mbar_test(uint32_t a, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(a), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// The waits below give up after WAIT_LIMIT probes; `fail` is checked only once a wait has had to loop, so a
+// wait whose phase is already complete costs one probe.
 __device__ __forceinline__ void mbar_wait(uint64_t *bar, uint32_t parity, volatile int *fail) {
     const uint32_t a = su32(bar);
     if (mbar_try(a, parity)) return;   // the common case: the phase has already completed
     if (*fail) return;
-    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
-        if (mbar_try(a, parity)) return;
-        if ((i & 1023) == 1023 && *fail) return;
+    uint32_t n = WAIT_LIMIT;
+    while (!mbar_try(a, parity)) {
+        if (--n == 0) {
+            *fail = 1;
+            return;
+        }
     }
-    *fail = 1;
 }
-// The same wait for roles with slack (epilogue, TMA refills): sleeps between probes, so a warp that
-// mostly waits does not take issue slots from the warps that expand the weights.
-__device__ __forceinline__ void mbar_wait_relaxed(uint64_t *bar, uint32_t parity, volatile int *fail) {
-    const uint32_t a = su32(bar);
-    if (mbar_try(a, parity)) return;
-    if (*fail) return;
-    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
-        __nanosleep(64);
-        if (mbar_try(a, parity)) return;
-        if ((i & 1023) == 1023 && *fail) return;
-    }
-    *fail = 1;
-}
-// The same with a chosen nap: for warps whose work is far ahead of its consumer, so that their probing does
-// not take issue slots from the warps that share their scheduler.
+// The same wait with a nap between probes: for roles that run ahead of the role they wait for (epilogue, TMA
+// refills, MMA issue), so that their probing does not take issue slots and ALU cycles from the warps that
+// expand the weights. ns == 0 probes back to back.
 __device__ __forceinline__ void mbar_wait_nap(uint64_t *bar, uint32_t parity, volatile int *fail, unsigned ns) {
     const uint32_t a = su32(bar);
     if (mbar_try(a, parity)) return;
     if (*fail) return;
-    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
-        __nanosleep(ns);
+    uint32_t n = WAIT_LIMIT;
+    for (;;) {
+        if (ns) __nanosleep(ns);
         if (mbar_try(a, parity)) return;
-        if ((i & 1023) == 1023 && *fail) return;
+        if (--n == 0) {
+            *fail = 1;
+            return;
+        }
     }
-    *fail = 1;
 }
+__device__ __forceinline__ void mbar_wait_relaxed(uint64_t *bar, uint32_t parity, volatile int *fail) { mbar_wait_nap(bar, parity, fail, 64); }
 __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(su32(dst)),
                  "l"(src), "r"(bytes), "r"(su32(bar))
@@ -144,6 +130,12 @@ __device__ __forceinline__ void umma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, ui
 __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]),
                  "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr), "r"(r[0]),
+                 "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]),
+                 "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
                  : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
