@@ -175,7 +175,7 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
     if (tid == 0) {
         for (int i = 0; i < RAW_STAGES; i++) {
             mbar_init(&bar_raw[i], 1);
-            mbar_init(&bar_rawfree[i], 16);   // one arrival per expanding warp
+            mbar_init(&bar_rawfree[i], 8);    // one arrival per warp of the set that expands this super-block
         }
         for (int i = 0; i < ACT_STAGES; i++) {
             mbar_init(&bar_act[i], 1);
@@ -230,10 +230,8 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
     //   warp 25             issues the MMAs (one elected lane)
     //   warps 1..8          epilogue: TMEM -> registers, f32 scaling, final store (lane quadrant = warp % 4,
     //                       two warps per quadrant split the columns)
-    //   warps 9..24         expand the raw nibbles into the f16 operand: lane quadrant = warp % 4 (a warp may
-    //                       only touch the 32 TMEM lanes of its quadrant), quarter of the super-block =
-    //                       (warp - 9) / 4, so a thread owns one 32-byte qs chunk of its row: 64 weights of two
-    //                       sub-blocks, and nobody decodes a scale twice
+    //   warps 9..24         expand the raw nibbles into the f16 operand (two sets of eight warps on alternate
+    //                       super-blocks; see there)
     const int lane = tid & 31;
     if (warp == 0) {
         // ---- TMA producer: refills a raw stage once every expanding warp has left it, and an
@@ -369,46 +367,50 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
         }
         store_tile(cur_tile);
     } else {
+        // Two sets of eight warps take alternate super-blocks (set 0 the even ones of this CTA, set 1 the odd ones), so
+        // a warp's chain of barrier waits, shared-memory loads, TMEM stores and arrivals (several hundred cycles of
+        // latency that nothing in the same warp can hide) is paid once per TWO super-blocks of CTA progress, and the
+        // two sets are half a period apart. Inside a set: lane quadrant = warp % 4 (a warp may only touch the 32
+        // TMEM lanes of its quadrant), half = which two 32-byte qs chunks (quarters of the super-block) of its
+        // row the thread expands.
+        const int e = warp - DEQ_WARP0;
         const int q = warp & 3;                            // lane quadrant
-        const int qd = (warp - DEQ_WARP0) >> 2;            // quarter of the super-block: qs chunk qd = sub-blocks 2qd (low nibbles), 2qd+1 (high)
+        const int half = (e >> 2) & 1;                     // quarters 2 half and 2 half + 1
+        const int set = e >> 3;
         const int r = q * 32 + lane;                       // row
         const uint32_t a_lane = tmem_base + A_COL0 + ((uint32_t)(q * 32) << 16);
         const __half2 k1024 = __half2(__ushort_as_half(0x6400), __ushort_as_half(0x6400));
-        // A quarter is published (its barrier arrived on) only after the low nibbles of the NEXT super-block
-        // have been computed, so the latency of the TMEM stores hides behind arithmetic; the first
-        // super-block is published at once so that the first MMA starts early, the last one after the loop.
-        int pend = -1;   // ring slot with stores in flight
+        // The two quarters of a super-block are published (their barriers arrived on) only after the first values of
+        // the set's NEXT super-block have been computed, so the latency of the TMEM stores hides behind arithmetic;
+        // a set's first super-block is published at once so that the first MMA starts early, its last one after
+        // the loop.
+        int pend = -1;   // ring slot (super-block) with stores in flight
         auto publish = [&]() {
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bar_aready[pend]);
+            if (lane == 0) {
+                mbar_arrive(&bar_aready[pend * 4 + 2 * half]);
+                mbar_arrive(&bar_aready[pend * 4 + 2 * half + 1]);
+            }
             pend = -1;
         };
-        int ring_u = 0;
-        uint32_t ring_ph = 0;
-        // The loop is software-pipelined: the 48 raw bytes of the next super-block are read into registers at the
-        // end of an iteration, and the barriers an iteration will need (raw data of the next super-block, the ring
-        // slot being free) are tested without blocking at its start, so that their latencies run under the
-        // arithmetic; a blocking wait follows only where the early test said "not yet".
-        const uint8_t *rbase = raw + r * 144;
-        mbar_wait(&bar_raw[0], 0u, fail);
-        uint4 hdr = *reinterpret_cast<const uint4 *>(rbase);
-        uint4 w0 = *reinterpret_cast<const uint4 *>(rbase + 16 + qd * 32);
-        uint4 w1 = *reinterpret_cast<const uint4 *>(rbase + 32 + qd * 32);
-        for (int i = 0; i < nsb; i++) {
-            const int rs = i % RAW_STAGES, rn = (i + 1) % RAW_STAGES;
-            const uint32_t rn_par = (uint32_t)(((i + 1) / RAW_STAGES) & 1);
-            const int slot = ring_u * 4 + qd;
-            const bool next_ready = i + 1 < nsb ? mbar_test(su32(&bar_raw[rn]), rn_par) : true;
-            const bool slot_free = i >= RING ? mbar_test(su32(&bar_afree[slot]), ring_ph ^ 1u) : true;
-            // 6-bit scales of the eight sub-blocks, four per word (get_scale_min_k4, ggml-quants.c:880-887);
-            // this warp needs bytes 2 (qd & 1) and 2 (qd & 1) + 1 of the word that holds sub-blocks 4 (qd / 2) ...
-            const uint32_t sc4 = qd < 2 ? (hdr.y & 0x3f3f3f3fu) : ((hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u));
-            if (qd == 0) {
+        int ru = set % RING, rs = set % RAW_STAGES;        // ring slot and raw stage of super-block i, and their phases
+        uint32_t ring_ph = (uint32_t)((set / RING) & 1), raw_ph = 0;
+        for (int i = set; i < nsb; i += 2) {
+            mbar_wait(&bar_raw[rs], raw_ph, fail);
+            const uint8_t *rrow = raw + rs * RAW_BYTES + r * 144;
+            const uint4 hdr = *reinterpret_cast<const uint4 *>(rrow);
+            uint4 wv[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) wv[j] = *reinterpret_cast<const uint4 *>(rrow + 16 + half * 64 + j * 16);
+            // 6-bit scales of the eight sub-blocks (get_scale_min_k4, ggml-quants.c:880-887): this thread's four
+            // (sub-blocks 4 half ... 4 half + 3) as the bytes of one word
+            const uint32_t sc4 = half == 0 ? (hdr.y & 0x3f3f3f3fu) : ((hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u));
+            if (half == 0) {
                 // (d, dmin) for the epilogue and the mins as the f16 operand of the T product
                 const int mt = i & (META - 1);
-                if (i >= META) mbar_wait(&bar_epi[mt], (uint32_t)(((i - META) / META) & 1), fail);   // those of i - META consumed
+                if (i >= META) mbar_wait(&bar_epi[mt], (uint32_t)(((i >> 2) - 1) & 1), fail);   // those of i - META consumed
                 dd[mt * ROWS + r] = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
                 uint32_t mn8[2];
                 mn8[0] = hdr.z & 0x3f3f3f3fu;
@@ -430,57 +432,60 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> async-proxy (MMA) reads
             }
-            // f16 scale pairs (sc, sc), built from the integer bytes without conversions: bytes (sc, 0x64) are the
-            // f16 1024 + sc. A 4-bit code masked out of a word where it stands, (w & 0x000f) or (w & 0x00f0), is
-            // the f16 SUBNORMAL q * 2^-24 or q * 2^-20; times sc * 2^10 or sc * 2^6 that is sc * q * 2^-14, a normal
-            // f16 number, exactly (sc * q <= 945 has 10 bits). So a pair of weights costs one AND with an immediate
-            // and one HMUL2, no constants are held in registers, and the epilogue multiplies S by 2^14.
-            uint32_t tl = __byte_perm(sc4, 0x64646464u, (qd & 1) ? 0x4242 : 0x4040);
-            uint32_t th = __byte_perm(sc4, 0x64646464u, (qd & 1) ? 0x4343 : 0x4141);
-            const __half2 mlo = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&tl), k1024), __half2(__ushort_as_half(0x6400), __ushort_as_half(0x6400)));   // sc * 2^10
-            const __half2 mhi = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&th), k1024), __half2(__ushort_as_half(0x5400), __ushort_as_half(0x5400)));   // sc * 2^6
-            const uint32_t ws[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-            // 32 low-nibble values (K chunks 0 and 1 of the quarter), two per 32-bit column in the order the nibbles
-            // leave a word: (0,2) (1,3) (4,6) (5,7) ...; then the 32 high-nibble values (K chunks 2 and 3)
-            uint32_t v[16];
 #pragma unroll
-            for (int k = 0; k < 8; k++) {
-                uint32_t t0 = ws[k] & 0x000f000fu, t1 = (ws[k] >> 8) & 0x000f000fu;
-                const __half2 l0 = __hmul2(*reinterpret_cast<__half2 *>(&t0), mlo);
-                const __half2 l1 = __hmul2(*reinterpret_cast<__half2 *>(&t1), mlo);
-                v[2 * k] = *reinterpret_cast<const uint32_t *>(&l0);
-                v[2 * k + 1] = *reinterpret_cast<const uint32_t *>(&l1);
-            }
-            if (pend >= 0) publish();
-            if (i >= RING) {   // the MMAs that read this ring slot last time are done
-                if (!slot_free) mbar_wait(&bar_afree[slot], ring_ph ^ 1u, fail);
-                tc_fence_after();
-            }
-            tmem_st16(a_lane + (uint32_t)(slot * 32), v);
+            for (int qq = 0; qq < 2; qq++) {
+                // quarter 2 half + qq = qs chunk of 32 bytes = sub-blocks 2 (2 half + qq) (low nibbles) and + 1 (high nibbles).
+                // f16 scale pairs (sc, sc), built from the integer bytes without conversions: bytes (sc, 0x64) are the
+                // f16 1024 + sc. A 4-bit code masked out of a word where it stands, (w & 0x000f) or (w & 0x00f0), is
+                // the f16 SUBNORMAL q * 2^-24 or q * 2^-20; times sc * 2^10 or sc * 2^6 that is sc * q * 2^-14, a normal
+                // f16 number, exactly (sc * q <= 945 has 10 bits). So a pair of weights costs one AND with an immediate
+                // and one HMUL2, no constants are held in registers, and the epilogue multiplies S by 2^14.
+                uint32_t tl = __byte_perm(sc4, 0x64646464u, qq ? 0x4242 : 0x4040);
+                uint32_t th = __byte_perm(sc4, 0x64646464u, qq ? 0x4343 : 0x4141);
+                const __half2 mlo = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&tl), k1024), __half2(__ushort_as_half(0x6400), __ushort_as_half(0x6400)));   // sc * 2^10
+                const __half2 mhi = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&th), k1024), __half2(__ushort_as_half(0x5400), __ushort_as_half(0x5400)));   // sc * 2^6
+                const uint32_t ws[8] = {wv[2 * qq].x, wv[2 * qq].y, wv[2 * qq].z, wv[2 * qq].w, wv[2 * qq + 1].x, wv[2 * qq + 1].y, wv[2 * qq + 1].z, wv[2 * qq + 1].w};
+                const int slot = ru * 4 + 2 * half + qq;
+                // 32 low-nibble values (K chunks 0 and 1 of the quarter), two per 32-bit column in the order the nibbles
+                // leave a word: (0,2) (1,3) (4,6) (5,7) ...; then the 32 high-nibble values (K chunks 2 and 3)
+                uint32_t v[16];
 #pragma unroll
-            for (int k = 0; k < 8; k++) {
-                uint32_t u0 = ws[k] & 0x00f000f0u, u1 = (ws[k] >> 8) & 0x00f000f0u;
-                const __half2 h0 = __hmul2(*reinterpret_cast<__half2 *>(&u0), mhi);
-                const __half2 h1 = __hmul2(*reinterpret_cast<__half2 *>(&u1), mhi);
-                v[2 * k] = *reinterpret_cast<const uint32_t *>(&h0);
-                v[2 * k + 1] = *reinterpret_cast<const uint32_t *>(&h1);
+                for (int k = 0; k < 8; k++) {
+                    uint32_t t0 = ws[k] & 0x000f000fu, t1 = (ws[k] >> 8) & 0x000f000fu;
+                    const __half2 l0 = __hmul2(*reinterpret_cast<__half2 *>(&t0), mlo);
+                    const __half2 l1 = __hmul2(*reinterpret_cast<__half2 *>(&t1), mlo);
+                    v[2 * k] = *reinterpret_cast<const uint32_t *>(&l0);
+                    v[2 * k + 1] = *reinterpret_cast<const uint32_t *>(&l1);
+                }
+                if (qq == 0 && pend >= 0) publish();
+                if (i >= RING) {   // the MMAs that read this ring slot last time are done
+                    mbar_wait(&bar_afree[slot], ring_ph ^ 1u, fail);
+                    tc_fence_after();
+                }
+                tmem_st16(a_lane + (uint32_t)(slot * 32), v);
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    uint32_t u0 = ws[k] & 0x00f000f0u, u1 = (ws[k] >> 8) & 0x00f000f0u;
+                    const __half2 h0 = __hmul2(*reinterpret_cast<__half2 *>(&u0), mhi);
+                    const __half2 h1 = __hmul2(*reinterpret_cast<__half2 *>(&u1), mhi);
+                    v[2 * k] = *reinterpret_cast<const uint32_t *>(&h0);
+                    v[2 * k + 1] = *reinterpret_cast<const uint32_t *>(&h1);
+                }
+                tmem_st16(a_lane + (uint32_t)(slot * 32 + 16), v);
             }
-            tmem_st16(a_lane + (uint32_t)(slot * 32 + 16), v);
-            pend = slot;
-            if (i == 0) publish();
-            // the next super-block's bytes into registers; then this raw stage may be refilled
-            if (i + 1 < nsb) {
-                if (!next_ready) mbar_wait(&bar_raw[rn], rn_par, fail);
-                const uint8_t *rrow = rbase + rn * RAW_BYTES;
-                hdr = *reinterpret_cast<const uint4 *>(rrow);
-                w0 = *reinterpret_cast<const uint4 *>(rrow + 16 + qd * 32);
-                w1 = *reinterpret_cast<const uint4 *>(rrow + 32 + qd * 32);
-            }
+            pend = ru;
+            if (i < 2) publish();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_rawfree[rs]);
-            if (++ring_u == RING) {
-                ring_u = 0;
+            ru += 2;
+            if (ru >= RING) {
+                ru -= RING;
                 ring_ph ^= 1u;
+            }
+            rs += 2;
+            if (rs >= RAW_STAGES) {
+                rs -= RAW_STAGES;
+                raw_ph ^= 1u;
             }
         }
         if (pend >= 0) publish();
