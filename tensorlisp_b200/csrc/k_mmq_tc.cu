@@ -145,7 +145,7 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
     uint8_t *actb = raw + RAW_STAGES * RAW_BYTES;          // ACT_STAGES x BLOB
     uint8_t *amin = actb + ACT_STAGES * BLOB;              // META x AMIN_BYTES
     float2 *dd = reinterpret_cast<float2 *>(amin + META * AMIN_BYTES);  // [META][ROWS] (d, dmin)
-    __shared__ uint64_t bar_raw[RAW_STAGES], bar_act[ACT_STAGES], bar_afree[RING * 4], bar_mma[2], bar_epi[META], bar_aready[RING * 4], bar_rawfree[RAW_STAGES],
+    __shared__ uint64_t bar_raw[RAW_STAGES], bar_act[ACT_STAGES], bar_afree[RING], bar_mma[2], bar_epi[META], bar_aready[RING], bar_rawfree[RAW_STAGES],
         bar_actfree[ACT_STAGES];
     __shared__ uint32_t tmem_base_s;
     __shared__ int s_fail;
@@ -183,9 +183,9 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
         }
         for (int i = 0; i < 2; i++) mbar_init(&bar_mma[i], 1);
         for (int i = 0; i < META; i++) mbar_init(&bar_epi[i], 256);
-        for (int i = 0; i < RING * 4; i++) {
+        for (int i = 0; i < RING; i++) {
             mbar_init(&bar_afree[i], 1);
-            mbar_init(&bar_aready[i], 4);   // the four warps (one per lane quadrant) that expand this quarter
+            mbar_init(&bar_aready[i], 8);   // the eight warps of the set that expands this super-block
         }
         s_fail = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -255,35 +255,34 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
         const bool leader = elect_one();
         int ring_u = 0;
         uint32_t ring_ph = 0;
+        // One wait per super-block on the issue path (its A operand), then 17 instructions back to back; the waits
+        // for the NEXT super-block's activations and accumulator buffer come after the issue, where their
+        // latency runs under the tensor pipe's work.
+        mbar_wait_nap(&bar_act[0], 0u, fail, p.nap_mma);
         for (int i = 0; i < nsb; i++) {
             const int as = i % ACT_STAGES, b = i & 1, mt = i & (META - 1);
             const uint32_t d_S = tmem_base + (uint32_t)(b * 2 * NPAD), d_T = d_S + NPAD;
             const uint64_t b_desc0 = smem_desc(su32(actb + as * BLOB), 128, 4096);
             const uint64_t am_desc = smem_desc(su32(amin + mt * AMIN_BYTES), 128, 256);
             const uint64_t bm_desc = smem_desc(su32(actb + as * BLOB + NPAD * 512), 128, 256);
-            mbar_wait_nap(&bar_act[as], (uint32_t)((i / ACT_STAGES) & 1), fail, p.nap_mma);
-            if (i >= 2) mbar_wait_nap(&bar_epi[(i - 2) & (META - 1)], (uint32_t)(((i - 2) / META) & 1), fail, p.nap_mma);   // TMEM buffer b drained
+            const uint32_t ta0 = tmem_base + A_COL0 + (uint32_t)(ring_u * 128);   // 16 K chunks x 8 columns
+            mbar_wait_nap(&bar_aready[ring_u], ring_ph, fail, p.nap_mma);
+            tc_fence_after();
+            if (leader) {
+                umma_f16(d_T, am_desc, bm_desc, IDESC, 0u);
 #pragma unroll
-            for (int qd = 0; qd < 4; qd++) {
-                const int slot = ring_u * 4 + qd;
-                mbar_wait_nap(&bar_aready[slot], ring_ph, fail, p.nap_mma);
-                tc_fence_after();
-                const uint32_t ta = tmem_base + A_COL0 + (uint32_t)(slot * 32);   // 4 K chunks x 8 columns
-                const uint64_t bd = b_desc0 + (uint64_t)(qd * 8 * (128 >> 4));
-                if (leader) {
-                    umma_f16_ta(d_S, ta, bd, IDESC, qd ? 1u : 0u);
-                    umma_f16_ta(d_S, ta + 8, bd + 16, IDESC, 1u);
-                    umma_f16_ta(d_S, ta + 16, bd + 32, IDESC, 1u);
-                    umma_f16_ta(d_S, ta + 24, bd + 48, IDESC, 1u);
-                    if (qd == 0) umma_f16(d_T, am_desc, bm_desc, IDESC, 0u);
-                    umma_commit(&bar_afree[slot]);
-                    if (qd == 3) umma_commit(&bar_mma[b]);
-                }
-                __syncwarp();
+                for (int kc = 0; kc < 16; kc++) umma_f16_ta(d_S, ta0 + (uint32_t)(kc * 8), b_desc0 + (uint64_t)(kc * 16), IDESC, kc ? 1u : 0u);
+                umma_commit(&bar_afree[ring_u]);
+                umma_commit(&bar_mma[b]);
             }
+            __syncwarp();
             if (++ring_u == RING) {
                 ring_u = 0;
                 ring_ph ^= 1u;
+            }
+            if (i + 1 < nsb) {
+                mbar_wait_nap(&bar_act[(i + 1) % ACT_STAGES], (uint32_t)(((i + 1) / ACT_STAGES) & 1), fail, p.nap_mma);
+                if (i >= 1) mbar_wait_nap(&bar_epi[(i - 1) & (META - 1)], (uint32_t)(((i - 1) / META) & 1), fail, p.nap_mma);   // TMEM buffer of i + 1 drained
             }
         }
     } else if (warp < DEQ_WARP0) {
@@ -389,10 +388,7 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&bar_aready[pend * 4 + 2 * half]);
-                mbar_arrive(&bar_aready[pend * 4 + 2 * half + 1]);
-            }
+            if (lane == 0) mbar_arrive(&bar_aready[pend]);
             pend = -1;
         };
         int ru = set % RING, rs = set % RAW_STAGES;        // ring slot and raw stage of super-block i, and their phases
@@ -457,10 +453,12 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
                     v[2 * k] = *reinterpret_cast<const uint32_t *>(&l0);
                     v[2 * k + 1] = *reinterpret_cast<const uint32_t *>(&l1);
                 }
-                if (qq == 0 && pend >= 0) publish();
-                if (i >= RING) {   // the MMAs that read this ring slot last time are done
-                    mbar_wait(&bar_afree[slot], ring_ph ^ 1u, fail);
-                    tc_fence_after();
+                if (qq == 0) {
+                    if (pend >= 0) publish();
+                    if (i >= RING) {   // the MMAs that read this ring slot last time are done
+                        mbar_wait(&bar_afree[ru], ring_ph ^ 1u, fail);
+                        tc_fence_after();
+                    }
                 }
                 tmem_st16(a_lane + (uint32_t)(slot * 32), v);
 #pragma unroll
