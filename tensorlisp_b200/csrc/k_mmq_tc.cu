@@ -100,7 +100,6 @@ struct TcParams {
     // sk_partial[tile][0 = has the tile's start, 1 = has its end][N][128], added by k_mmq_sk_fixup.
     int streamk, total_tiles;
     float *sk_partial;
-    int nap_mma, nap_epi, nap_tma;   // nanoseconds between barrier probes of the roles that run ahead of the expanding warps
 };
 
 // CTA that works on unit u when G CTAs split T units as above
@@ -110,6 +109,8 @@ __host__ __device__ inline int sk_cta_of(int64_t u, int64_t T, int G) {
     while (c > 0 && (int64_t)c * T / G > u) c--;
     return c;
 }
+
+constexpr int Q4K_THREADS = tc::THREADS + 32;   // the common roles plus a second MMA-issuing warp (warp 26)
 
 // packed f32 pairs: one instruction for two columns of the epilogue
 __device__ __forceinline__ uint64_t f2pack(float lo, float hi) {
@@ -130,7 +131,7 @@ __device__ __forceinline__ uint64_t f2fma(uint64_t a, uint64_t b, uint64_t c) {
 }
 
 template <int NPAD, int RAW_STAGES, int ACT_STAGES>
-__global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_constant__ TcMaps maps, TcParams p) {
+__global__ void __launch_bounds__(Q4K_THREADS, 1) k_mmq_tc_q4k(const __grid_constant__ TcMaps maps, TcParams p) {
     using namespace tc;
     constexpr int BLOB = (NPAD * 548 + 127) / 128 * 128;
     constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(NPAD >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);  // f16 x f16 -> f32, K-major A and B
@@ -138,14 +139,17 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
     // super-blocks of the A operand, four quarters of 32 columns (64 f16 per row) each.
     constexpr uint32_t A_COL0 = 4 * NPAD;
     constexpr int RING = (int)(TMEM_COLS - A_COL0) / 128;   // super-blocks in the ring: 3 (2 for 64 columns)
-    constexpr int META = 4;                                  // (d, dmin) and the mins operand are kept for four super-blocks
+    // (d, dmin) and the mins operand are kept for eight super-blocks. Nobody waits before overwriting an entry:
+    // the set that writes super-block i waited, two super-blocks earlier, for the MMAs of i - 5 to finish (its ring
+    // slot), those were issued only after the epilogue of i - 7 had read its entry, and the epilogue works in order.
+    constexpr int META = 8;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = smem_raw + ((1024u - (tc::su32(smem_raw) & 1023u)) & 1023u);   // 1 KB of slack is allocated for this
     uint8_t *raw = smem;                                   // RAW_STAGES x RAW_BYTES
     uint8_t *actb = raw + RAW_STAGES * RAW_BYTES;          // ACT_STAGES x BLOB
     uint8_t *amin = actb + ACT_STAGES * BLOB;              // META x AMIN_BYTES
     float2 *dd = reinterpret_cast<float2 *>(amin + META * AMIN_BYTES);  // [META][ROWS] (d, dmin)
-    __shared__ uint64_t bar_raw[RAW_STAGES], bar_act[ACT_STAGES], bar_afree[RING], bar_mma[2], bar_epi[META], bar_aready[RING], bar_rawfree[RAW_STAGES],
+    __shared__ uint64_t bar_raw[RAW_STAGES], bar_act[ACT_STAGES], bar_afree[RING], bar_mma[2], bar_epi[4], bar_aready[RING], bar_rawfree[RAW_STAGES],
         bar_actfree[ACT_STAGES];
     __shared__ uint32_t tmem_base_s;
     __shared__ int s_fail;
@@ -182,7 +186,7 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
             mbar_init(&bar_actfree[i], 256);
         }
         for (int i = 0; i < 2; i++) mbar_init(&bar_mma[i], 1);
-        for (int i = 0; i < META; i++) mbar_init(&bar_epi[i], 256);
+        for (int i = 0; i < 4; i++) mbar_init(&bar_epi[i], 256);
         for (int i = 0; i < RING; i++) {
             mbar_init(&bar_afree[i], 1);
             mbar_init(&bar_aready[i], 8);   // the eight warps of the set that expands this super-block
@@ -227,7 +231,7 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
 
     // ---- warp roles: no CTA-wide barrier inside the loop, the roles meet only through mbarriers
     //   warp 0, lane 0      issues the TMA copies
-    //   warp 25             issues the MMAs (one elected lane)
+    //   warps 25, 26        issue the MMAs of alternate super-blocks (one elected lane each)
     //   warps 1..8          epilogue: TMEM -> registers, f32 scaling, final store (lane quadrant = warp % 4,
     //                       two warps per quadrant split the columns)
     //   warps 9..24         expand the raw nibbles into the f16 operand (two sets of eight warps on alternate
@@ -239,50 +243,48 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
         if (lane == 0) {
             for (int i = 0; i < nsb; i++) {
                 if (i + RAW_STAGES < nsb) {
-                    mbar_wait_nap(&bar_rawfree[i % RAW_STAGES], (uint32_t)((i / RAW_STAGES) & 1), fail, p.nap_tma);
+                    mbar_wait_nap(&bar_rawfree[i % RAW_STAGES], (uint32_t)((i / RAW_STAGES) & 1), fail, 64);
                     load_raw(i + RAW_STAGES);
                 }
                 if (i >= 1 && i - 1 + ACT_STAGES < nsb) {
-                    mbar_wait_nap(&bar_actfree[(i - 1) % ACT_STAGES], (uint32_t)(((i - 1) / ACT_STAGES) & 1), fail, p.nap_tma);
+                    mbar_wait_nap(&bar_actfree[(i - 1) % ACT_STAGES], (uint32_t)(((i - 1) / ACT_STAGES) & 1), fail, 64);
                     load_act(i - 1 + ACT_STAGES);
                 }
             }
         }
-    } else if (warp == MMA_WARP) {
-        // ---- MMA issuer: nothing but waits on operands and tcgen05.mma / commit. The whole warp runs
-        // the loop (converged, so the descriptor arithmetic stays on the uniform datapath); one
-        // elected lane issues.
+    } else if (warp >= MMA_WARP) {
+        // ---- MMA issuers: nothing but waits on operands and tcgen05.mma / commit. Two warps take alternate
+        // super-blocks: the waits of one (each costs 100 to 300 cycles even when the barrier has long completed)
+        // run while the other one's instructions keep the tensor pipe busy. A whole warp runs the loop (converged,
+        // so the descriptor arithmetic stays on the uniform datapath); one elected lane issues. The accumulator
+        // buffer (i & 1) and the mins operand belong to one warp each, and a commit covers the MMAs of its own thread.
         const bool leader = elect_one();
-        int ring_u = 0;
-        uint32_t ring_ph = 0;
-        // One wait per super-block on the issue path (its A operand), then 17 instructions back to back; the waits
-        // for the NEXT super-block's activations and accumulator buffer come after the issue, where their
-        // latency runs under the tensor pipe's work.
-        mbar_wait_nap(&bar_act[0], 0u, fail, p.nap_mma);
-        for (int i = 0; i < nsb; i++) {
-            const int as = i % ACT_STAGES, b = i & 1, mt = i & (META - 1);
-            const uint32_t d_S = tmem_base + (uint32_t)(b * 2 * NPAD), d_T = d_S + NPAD;
+        const int w = warp - MMA_WARP;
+        int ring_u = w % RING;
+        uint32_t ring_ph = (uint32_t)((w / RING) & 1);
+        for (int i = w; i < nsb; i += 2) {
+            const int as = i % ACT_STAGES, mt = i & (META - 1);
+            const uint32_t d_S = tmem_base + (uint32_t)(w * 2 * NPAD), d_T = d_S + NPAD;
             const uint64_t b_desc0 = smem_desc(su32(actb + as * BLOB), 128, 4096);
             const uint64_t am_desc = smem_desc(su32(amin + mt * AMIN_BYTES), 128, 256);
             const uint64_t bm_desc = smem_desc(su32(actb + as * BLOB + NPAD * 512), 128, 256);
             const uint32_t ta0 = tmem_base + A_COL0 + (uint32_t)(ring_u * 128);   // 16 K chunks x 8 columns
-            mbar_wait_nap(&bar_aready[ring_u], ring_ph, fail, p.nap_mma);
+            mbar_wait_nap(&bar_act[as], (uint32_t)((i / ACT_STAGES) & 1), fail, 32);
+            if (i >= 2) mbar_wait_nap(&bar_epi[(i - 2) & 3], (uint32_t)(((i - 2) >> 2) & 1), fail, 32);   // TMEM buffer drained
+            mbar_wait_nap(&bar_aready[ring_u], ring_ph, fail, 32);
             tc_fence_after();
             if (leader) {
                 umma_f16(d_T, am_desc, bm_desc, IDESC, 0u);
 #pragma unroll
                 for (int kc = 0; kc < 16; kc++) umma_f16_ta(d_S, ta0 + (uint32_t)(kc * 8), b_desc0 + (uint64_t)(kc * 16), IDESC, kc ? 1u : 0u);
                 umma_commit(&bar_afree[ring_u]);
-                umma_commit(&bar_mma[b]);
+                umma_commit(&bar_mma[w]);
             }
             __syncwarp();
-            if (++ring_u == RING) {
-                ring_u = 0;
+            ring_u += 2;
+            if (ring_u >= RING) {
+                ring_u -= RING;
                 ring_ph ^= 1u;
-            }
-            if (i + 1 < nsb) {
-                mbar_wait_nap(&bar_act[(i + 1) % ACT_STAGES], (uint32_t)(((i + 1) / ACT_STAGES) & 1), fail, p.nap_mma);
-                if (i >= 1) mbar_wait_nap(&bar_epi[(i - 1) & (META - 1)], (uint32_t)(((i - 1) / META) & 1), fail, p.nap_mma);   // TMEM buffer of i + 1 drained
             }
         }
     } else if (warp < DEQ_WARP0) {
@@ -332,7 +334,7 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
                 e_sb = 0;
             }
             e_sb++;
-            mbar_wait_nap(&bar_mma[b], (uint32_t)((i >> 1) & 1), fail, p.nap_epi);
+            mbar_wait_nap(&bar_mma[b], (uint32_t)((i >> 1) & 1), fail, 64);
             tc_fence_after();
             const float2 sc = dd[mt * ROWS + row_in_tile];
             const float2 *yd = reinterpret_cast<const float2 *>(actb + (i % ACT_STAGES) * BLOB + NPAD * 544) + (col0 >> 1);
@@ -352,7 +354,7 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
             }
             tmem_ld_wait();
             tc_fence_before();
-            mbar_arrive(&bar_epi[mt]);   // TMEM buffer b, dd[mt] and amin[mt] may be reused
+            mbar_arrive(&bar_epi[i & 3]);   // TMEM buffer b may be reused
             const float ds = sc.x * 16384.f;   // the weight operand carries 2^-14
             const uint64_t d2 = f2pack(ds, ds), m2 = f2pack(-sc.y, -sc.y);
 #pragma unroll
@@ -406,7 +408,6 @@ __global__ void __launch_bounds__(tc::THREADS, 1) k_mmq_tc_q4k(const __grid_cons
             if (half == 0) {
                 // (d, dmin) for the epilogue and the mins as the f16 operand of the T product
                 const int mt = i & (META - 1);
-                if (i >= META) mbar_wait(&bar_epi[mt], (uint32_t)(((i >> 2) - 1) & 1), fail);   // those of i - META consumed
                 dd[mt * ROWS + r] = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
                 uint32_t mn8[2];
                 mn8[0] = hdr.z & 0x3f3f3f3fu;
@@ -581,14 +582,14 @@ static EncodeTiledFn encode_tiled() {
 
 template <int NPAD, int RS, int AS>
 static size_t tc_smem() {
-    return (size_t)RS * tc::RAW_BYTES + (size_t)AS * tc_blob_bytes(NPAD) + 4 * tc::AMIN_BYTES +
-           4 * tc::ROWS * sizeof(float2) + 1024;
+    return (size_t)RS * tc::RAW_BYTES + (size_t)AS * tc_blob_bytes(NPAD) + 8 * tc::AMIN_BYTES +
+           8 * tc::ROWS * sizeof(float2) + 1024;
 }
 
 void mmq_tc_configure() {
     cudaFuncSetAttribute(k_mmq_tc_q4k<16, 6, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem<16, 6, 4>());
     cudaFuncSetAttribute(k_mmq_tc_q4k<32, 6, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem<32, 6, 4>());
-    cudaFuncSetAttribute(k_mmq_tc_q4k<64, 5, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem<64, 5, 3>());
+    cudaFuncSetAttribute(k_mmq_tc_q4k<64, 5, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem<64, 5, 2>());
 }
 
 bool mmq_tc_supported(uint32_t type, int64_t K, int64_t M, int64_t N) {
@@ -600,8 +601,8 @@ TcPlan mmq_tc_plan(int64_t K, int64_t M, int64_t N, int sm_count) {
     t.npad = N <= 16 ? 16 : (N <= 32 ? 32 : 64);
     t.nsb = (int)(K / 256);
     const int64_t tiles = (M + tc::ROWS - 1) / tc::ROWS;
-    // K split: modelled time = waves x (CTA start-up + super-blocks per CTA x time per super-block)
-    // + the reduce launch when split; constants measured on B200 (start-up 2.3 us, 1.0 us per
+    // K split: modelled time = waves x (CTA start-up and tail + super-blocks per CTA x time per super-block)
+    // + the reduce launch when split; constants measured on B200 (3.4 us start-up and tail, 0.66 us per
     // super-block, 2 us for the reduce)
     int best = 1;
     double best_score = 1e30;
@@ -612,17 +613,17 @@ TcPlan mmq_tc_plan(int64_t K, int64_t M, int64_t N, int sm_count) {
         if (splits != s) continue;
         const int64_t units = tiles * splits;
         const int64_t waves = (units + sm_count - 1) / sm_count;
-        const double score = (double)waves * (2.3 + 1.0 * per) + (splits > 1 ? 2.0 : 0.0);
+        const double score = (double)waves * (3.4 + 0.66 * per) + (splits > 1 ? 2.0 : 0.0);
         if (score < best_score) { best_score = score; best = splits; }
     }
     t.n_split = best;
     t.sb_per_split = (t.nsb + best - 1) / best;
-    // stream-K when the tiles make several waves: 2.3 us start + units per CTA + 2.5 us fix-up, against whole
+    // stream-K when the tiles make several waves: start-up and tail + units per CTA + 2.5 us fix-up, against whole
     // waves of tiles. Measured on B200: [128256 x 4096] x 32 (6.8 waves) 144 -> 126 us; gate + up of an 8B layer
     // as one launch (1.5 waves) came out 3 us SLOWER per layer than two launches, hence the floor of 2.5 waves.
     t.streamk = 0;
     if (tiles * 2 >= (int64_t)sm_count * 5 && N <= t.npad && !getenv("TLB_NO_STREAMK")) {
-        const double sk = 2.3 + (double)((tiles * t.nsb + sm_count - 1) / sm_count) * 1.0 + 2.5;
+        const double sk = 3.4 + (double)((tiles * t.nsb + sm_count - 1) / sm_count) * 0.66 + 2.5;
         if (sk < best_score) {
             t.streamk = sm_count;
             t.n_split = 1;
@@ -698,13 +699,6 @@ cudaError_t launch_mmq_tc_group(const TcPlan &t, int n_mats, const void *const *
     base.total_tiles = tiles;
     base.streamk = t.streamk;
     base.sk_partial = (float *)partial;
-    {
-        static const int nm = getenv("TLB_NAP_MMA") ? atoi(getenv("TLB_NAP_MMA")) : 0, ne = getenv("TLB_NAP_EPI") ? atoi(getenv("TLB_NAP_EPI")) : 64,
-                         nt = getenv("TLB_NAP_TMA") ? atoi(getenv("TLB_NAP_TMA")) : 64;
-        base.nap_mma = nm;
-        base.nap_epi = ne;
-        base.nap_tma = nt;
-    }
     if (t.streamk && (t.n_split != 1 || t.n_col_chunks != 1 || (int64_t)tiles * t.nsb / t.streamk < t.nsb)) return cudaErrorInvalidValue;
     dim3 grid(t.streamk ? (unsigned)t.streamk : (unsigned)tiles, (unsigned)t.n_split);
     cudaError_t e = cudaSuccess;
@@ -730,9 +724,9 @@ cudaError_t launch_mmq_tc_group(const TcPlan &t, int n_mats, const void *const *
             }
         }
         switch (t.npad) {
-            case 16: e = launch_pdl(k_mmq_tc_q4k<16, 6, 4>, grid, dim3(tc::THREADS), tc_smem<16, 6, 4>(), st, maps, p); break;
-            case 32: e = launch_pdl(k_mmq_tc_q4k<32, 6, 4>, grid, dim3(tc::THREADS), tc_smem<32, 6, 4>(), st, maps, p); break;
-            default: e = launch_pdl(k_mmq_tc_q4k<64, 5, 3>, grid, dim3(tc::THREADS), tc_smem<64, 5, 3>(), st, maps, p); break;
+            case 16: e = launch_pdl(k_mmq_tc_q4k<16, 6, 4>, grid, dim3(Q4K_THREADS), tc_smem<16, 6, 4>(), st, maps, p); break;
+            case 32: e = launch_pdl(k_mmq_tc_q4k<32, 6, 4>, grid, dim3(Q4K_THREADS), tc_smem<32, 6, 4>(), st, maps, p); break;
+            default: e = launch_pdl(k_mmq_tc_q4k<64, 5, 2>, grid, dim3(Q4K_THREADS), tc_smem<64, 5, 2>(), st, maps, p); break;
         }
         if (e != cudaSuccess) return e;
         if (t.streamk) {
