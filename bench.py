@@ -1,5 +1,5 @@
 """Headline benchmark: batch-32 decode step of a random-init Llama-3-8B-shaped decoder with Q4_K
-weights (embeddings/output Q8_0) over a paged f16 KV cache at context 2048 (BASELINE config 4),
+weights (embeddings/output Q8_0) over a paged f16 KV cache at context 2048 (benchmark config 4),
 through the C ABI of include/tlb200.h.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
@@ -126,30 +126,48 @@ def build_model(rank: int, world: int, local_rank: int, make_graph=None):
     check(native.L.tlb_weights_create(native.dev, total, C.byref(h)))
     native.weights = StateBlock(h)
     base = native.weights.device_ptr
+    # The model is ONE random-init decoder whatever the rank count: every full tensor is drawn from its own seed
+    # (the same on every rank) and this rank keeps its shard -- rows of the column-parallel matrices, K ranges of
+    # the row-parallel ones (whole 256-element blocks, so quantizing the shard equals cutting the quantized
+    # matrix), its own KV heads of the pools; norms and embeddings are replicated.
+    from tensorlisp_b200.programs import COLUMN_PARALLEL, ROW_PARALLEL, decoder_weights
+    full = {f.name: f for f in decoder_weights(cfg, 1)}
     gen = torch.Generator(device="cuda")
-    gen.manual_seed(1234 + rank)
-    for s, (_, off) in zip(dg.weights, native.weight_loc):
+    for idx, (s, (_, off)) in enumerate(zip(dg.weights, native.weight_loc)):
+        gen.manual_seed(1234 + 7919 * idx)
+        base_name = s.name.rsplit(".", 1)[-1]
         if len(s.ne) == 1:
             w = (1 + 0.1 * torch.randn(s.ne[0], generator=gen, device="cuda", dtype=torch.float32)).contiguous()
             torch.cuda.synchronize()   # the copy runs on the library's stream: torch's must have written w first
             native.weights.copy_device(off, w.data_ptr(), w.numel() * 4)
-        else:
-            rows_left, done = s.ne[1], 0
-            row_bytes = s.nbytes() // s.ne[1]
-            while rows_left:
-                r = min(rows_left, 16384)
-                w = torch.randn((r, s.ne[0]), generator=gen, device="cuda", dtype=torch.float32) * 0.02
+            continue
+        K_full, M_full = full[s.name].ne
+        K, M = s.ne
+        row0 = rank * M if (world > 1 and base_name in COLUMN_PARALLEL) else 0      # first full row this rank keeps
+        k0 = rank * K if (world > 1 and base_name in ROW_PARALLEL) else 0           # first K element it keeps
+        row_bytes = s.nbytes() // M
+        r_full = 0
+        while r_full < M_full:
+            r = min(M_full - r_full, 16384)
+            w = torch.randn((r, K_full), generator=gen, device="cuda", dtype=torch.float32) * 0.02
+            lo, hi = max(r_full, row0), min(r_full + r, row0 + M)
+            if lo < hi:
+                part = w[lo - r_full:hi - r_full, k0:k0 + K].contiguous()
                 torch.cuda.synchronize()
-                check(native.L.tlb_quantize_rows_device(native.dev, s.ty, C.c_void_p(w.data_ptr()), r, s.ne[0],
-                                                        C.c_void_p(base + off + done * row_bytes)))
+                check(native.L.tlb_quantize_rows_device(native.dev, s.ty, C.c_void_p(part.data_ptr()), hi - lo, K,
+                                                        C.c_void_p(base + off + (lo - row0) * row_bytes)))
                 native.sync()
-                done += r
-                rows_left -= r
-    # ---- KV pools
+            r_full += r
+    # ---- KV pools: f16 N(0, 1) pages [block][kv head][slot][head_dim]; a rank holds its own KV heads of the full pool
     native.alloc_states(dg.state_bytes)
-    kv = None
-    for off, nbytes in zip(native.state_offsets, dg.state_bytes):
-        kv = torch.randn(nbytes // 2, generator=gen, device="cuda", dtype=torch.float16)
+    kv = w = None
+    kvh_full, kvh = cfg.n_kv_heads, cfg.n_kv_heads // world
+    for idx, (off, nbytes) in enumerate(zip(native.state_offsets, dg.state_bytes)):
+        gen.manual_seed(99991 + 31 * idx)
+        per_head = nbytes // 2 // kvh                      # elements of one head over all blocks: blocks x slot x head_dim
+        blocks = per_head // (cfg.block_size * cfg.head_dim)
+        kv = torch.randn((blocks, kvh_full, cfg.block_size * cfg.head_dim), generator=gen, device="cuda", dtype=torch.float16)
+        kv = kv[:, rank * kvh:(rank + 1) * kvh].contiguous() if world > 1 else kv
         torch.cuda.synchronize()
         native.state.copy_device(off, kv.data_ptr(), nbytes)
     del kv, w
@@ -181,6 +199,142 @@ def algorithmic_bytes(cfg, world: int) -> dict:
     return {"weights": w_layers + w_head, "w_layers": w_layers, "w_head": w_head, "kv": kv}
 
 
+def tp_parity(world: int, rank: int, local_rank: int, dist, batch: int = 8) -> dict:
+    """Correctness evidence for a tensor-parallel run: a two-layer decoder at the benchmark's own width (d_model 4096,
+    32 / 8 heads of 128, FFN 14336: the tile shapes, K splits, grouped launches and exchanges of the timed step), small
+    vocabulary, sharded over `world` ranks exactly like the timed model, one decode step with ragged contexts
+    through the production lowering (no taps), checked on rank 0 against the CPU oracle run on the unsharded
+    weights. Outside every timed region. The oracle is used as the checker only."""
+    import torch
+
+    if os.path.join(ROOT, "tests") not in sys.path:
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from helpers import oracle_decoder_step
+    from oracle.bindings import Oracle
+    from tensorlisp_b200.graph import align256
+    from tensorlisp_b200.native import Native, NativeProgram, StateBlock
+    from tensorlisp_b200.programs import COLUMN_PARALLEL, ROW_PARALLEL, DecoderConfig, decoder_step, decoder_weights
+    from tensorlisp_b200._lib import check
+
+    torch.cuda.set_device(local_rank)
+    cfg = DecoderConfig(n_layers=2, vocab=2048)
+    ctx_before = np.array([0, 5, 31, 100, 255, 16, 77, 200][:batch], np.int32)
+    B, bs, max_ctx = len(ctx_before), cfg.block_size, 256
+    max_blocks = max_ctx // bs
+    pool_blocks = B * max_blocks
+    dg = decoder_step(cfg, B, max_ctx, pool_blocks, tp=world)
+    final_norm = [t for t in dg.graph.nodes if dg.graph.tensors[t].name == "final_norm"][0]
+    dg.graph.keep.append(final_norm)   # replicated on every rank: equal bits there mean equal residual streams
+    native = Native(local_rank)
+    total = 0
+    for sp in dg.weights:
+        native.weight_loc.append((0, total))
+        total += align256(sp.nbytes())
+    h = C.c_void_p()
+    check(native.L.tlb_weights_create(native.dev, total, C.byref(h)))
+    native.weights = StateBlock(h)
+    base = native.weights.device_ptr
+    full_specs = decoder_weights(cfg, 1)
+    full_host = []      # rank 0: the unsharded weights as the oracle wants them (quantized bytes / f32 norms)
+    gen = torch.Generator(device="cuda")
+    for idx, (sp, fs, (_, off)) in enumerate(zip(dg.weights, full_specs, native.weight_loc)):
+        gen.manual_seed(4242 + 101 * idx)
+        name = sp.name.rsplit(".", 1)[-1]
+        if len(sp.ne) == 1:
+            w = (1 + 0.1 * torch.randn(sp.ne[0], generator=gen, device="cuda", dtype=torch.float32)).contiguous()
+            torch.cuda.synchronize()
+            native.weights.copy_device(off, w.data_ptr(), w.numel() * 4)
+            if rank == 0:
+                full_host.append(w.cpu().numpy())
+            continue
+        K_full, M_full = fs.ne
+        K, M = sp.ne
+        w = torch.randn((M_full, K_full), generator=gen, device="cuda", dtype=torch.float32) * 0.02
+        row0 = rank * M if (world > 1 and name in COLUMN_PARALLEL) else 0
+        k0 = rank * K if (world > 1 and name in ROW_PARALLEL) else 0
+        part = w[row0:row0 + M, k0:k0 + K].contiguous()
+        torch.cuda.synchronize()
+        check(native.L.tlb_quantize_rows_device(native.dev, sp.ty, C.c_void_p(part.data_ptr()), M, K, C.c_void_p(base + off)))
+        native.sync()
+        if rank == 0:
+            q = torch.empty(fs.nbytes(), dtype=torch.uint8, device="cuda")
+            torch.cuda.synchronize()
+            check(native.L.tlb_quantize_rows_device(native.dev, fs.ty, C.c_void_p(w.data_ptr()), M_full, K_full, C.c_void_p(q.data_ptr())))
+            native.sync()
+            full_host.append(q.cpu().numpy().reshape(M_full, -1))
+    # ---- the cached tokens: full-width K/V histories; this rank's pools hold its own KV heads
+    rng = np.random.default_rng(77)
+    kvh_full, hd = cfg.n_kv_heads, cfg.head_dim
+    kvh = kvh_full // world
+    ids = rng.integers(0, cfg.vocab, B).astype(np.int32)
+    pos, lens = ctx_before.copy(), ctx_before + 1
+    tables = rng.permutation(pool_blocks).astype(np.int32).reshape(B, max_blocks)
+    slots = np.array([tables[b, pos[b] // bs] * bs + pos[b] % bs for b in range(B)], np.int64)
+    native.alloc_states(dg.state_bytes)
+    ks = [[np.zeros((lens[b], kvh_full, hd), np.float16) for b in range(B)] for _ in range(cfg.n_layers)]
+    vs = [[np.zeros((lens[b], kvh_full, hd), np.float16) for b in range(B)] for _ in range(cfg.n_layers)]
+    for l in range(cfg.n_layers):
+        kp = np.zeros((pool_blocks, kvh, bs, hd), np.float16)
+        vp = np.zeros((pool_blocks, kvh, bs, hd), np.float16)
+        for b in range(B):
+            ks[l][b][:ctx_before[b]] = rng.standard_normal((ctx_before[b], kvh_full, hd)).astype(np.float16)
+            vs[l][b][:ctx_before[b]] = rng.standard_normal((ctx_before[b], kvh_full, hd)).astype(np.float16)
+            for t in range(ctx_before[b]):
+                kp[tables[b, t // bs], :, t % bs] = ks[l][b][t, rank * kvh:(rank + 1) * kvh]
+                vp[tables[b, t // bs], :, t % bs] = vs[l][b][t, rank * kvh:(rank + 1) * kvh]
+        native.state.write(native.state_offsets[2 * l], kp)
+        native.state.write(native.state_offsets[2 * l + 1], vp)
+    # ---- its own communicator (the timed model sets up another one on its own device handle)
+    path = "single GPU"
+    if world > 1:
+        box = [Native.comm_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        native.comm_init(world, rank, box[0])
+        path = "nccl"
+        if os.environ.get("TLB_NO_P2P_ALLREDUCE", "0") != "1":
+            handles = [None] * world
+            dist.all_gather_object(handles, native.comm_p2p_export())
+            native.comm_p2p_import(handles)
+            if world > 2 or os.environ.get("TLB_P2P_ALLREDUCE") == "1":
+                path = "peer memory" + (", exchange not fused" if os.environ.get("TLB_NO_FUSED_EXCHANGE") == "1" else ", fused exchange")
+    prog = NativeProgram.compile(native, dg.graph)
+    for i, a in enumerate([ids, pos, tables, lens, slots.view(np.int32)]):
+        prog.set_input(i, a)
+    if dist is not None:
+        dist.barrier()
+    for _ in range(3):       # several steps in a row: the exchange buffers alternate, sequence numbers grow
+        prog.run()
+    logits = prog.read(dg.logits).reshape(B, cfg.vocab // world)
+    token = prog.read(dg.token).reshape(B)
+    fin = prog.read(final_norm).reshape(B, cfg.d_model)
+    labels = prog.labels()
+    if dist is not None:
+        parts = [None] * world
+        dist.all_gather_object(parts, (logits, fin, token))
+        dist.barrier()       # no rank tears its exchange buffers down while a peer may still be in a step
+    else:
+        parts = [(logits, fin, token)]
+    prog.free()
+    native.close()
+    if rank != 0:
+        return {}
+    full_logits = np.concatenate([p[0] for p in parts], axis=1)
+    want = oracle_decoder_step(Oracle(), cfg, full_specs, full_host, ids, pos, ks, vs)
+    err = float(np.abs(full_logits - want).max())
+    local_best = np.stack([p[0].max(axis=1) for p in parts]), np.stack([p[2].astype(np.int64) for p in parts])
+    from tensorlisp_b200.programs import combine_argmax
+    tok = combine_argmax(local_best[0], local_best[1], cfg.vocab // world)
+    top2 = np.sort(want, axis=1)[:, -2:]
+    return {"model": "2 layers at the benchmark's width (d_model 4096, 32/8 heads, FFN 14336), vocabulary 2048, %d sequences, contexts %s"
+                     % (B, ctx_before.tolist()),
+            "tp": world, "allreduce": path, "checked_against": "CPU oracle on the unsharded weights",
+            "logits_max_abs_err": err, "logits_max_rel_err": err / float(np.abs(want).max()),
+            "top1_equal": int((tok == want.argmax(axis=1)).sum()), "rows": B,
+            "smallest_top1_margin_of_the_oracle": float((top2[:, 1] - top2[:, 0]).min()),
+            "ranks_hold_identical_final_norm": bool(all(np.array_equal(p[1], parts[0][1]) for p in parts)),
+            "exchange_launches": sorted(set(l.split(" ")[0] for l in labels if "ALLREDUCE" in l or "EXCHANGE" in l or "ROW_QUANT" in l))}
+
+
 def run_ours(args) -> dict:
     import torch
 
@@ -192,6 +346,12 @@ def run_ours(args) -> dict:
         import torch.distributed as dist
         torch.cuda.set_device(local_rank)
         dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world)
+    parity = None
+    if not args.no_parity:
+        try:
+            parity = tp_parity(world, rank, local_rank, dist)
+        except Exception as e:   # the line still carries the timing; the missing evidence is visible
+            parity = {"failed": "%s: %s" % (type(e).__name__, e)}
     cfg, dg, native, prog, weight_bytes = build_model(rank, world, local_rank)
     if world > 1:
         from tensorlisp_b200.native import Native
@@ -295,7 +455,7 @@ def run_ours(args) -> dict:
         "metric": METRIC, "value": BATCH / (ms_dev * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_dev, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int8 codes: f16 / int8 tcgen05 mma and dp4a, f32 scales and accumulate", "data": "synthetic",
-        "config": {"workload": "BASELINE config 4: Llama-3-8B shape, 32 layers, Q4_K weights (Q8_0 embed/output), "
+        "config": {"workload": "benchmark config 4: Llama-3-8B shape, 32 layers, Q4_K weights (Q8_0 embed/output), "
                                "batch 32 decode step at context 2048, paged f16 KV (16-token pages)",
                    "parallelism": "tp%d" % world, **({"allreduce": allreduce} if world > 1 else {}), "l2": "inputs larger than L2: %.2f GB weights + %.2f GB KV read per step per GPU"
                                                         % (ab["weights"] / 1e9, ab["kv"] / 1e9)},
@@ -312,6 +472,8 @@ def run_ours(args) -> dict:
         "launch_share": {k: {"ms": round(v[0], 4), "launches": v[1], "share": round(v[0] / total_prof, 4)} for k, v in
                          sorted(by_kind.items(), key=lambda kv: -kv[1][0])},
     }
+    if parity is not None:
+        result["parity"] = parity
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         try:
             result["cpu_baseline"] = cpu_reference_step(cfg, time_limit_s=20.0)
@@ -325,7 +487,7 @@ def run_ours(args) -> dict:
 
 
 
-# ---------------------------------------------------------------------------------- prompt pass (BASELINE config 5)
+# ---------------------------------------------------------------------------------- prompt pass (benchmark config 5)
 def run_prefill(args) -> dict:
     """`--prefill SEQS:TOKENS[:LAYERS]`: the prompt pass of the same decoder with Q8_0 weights, SEQS prompts of
     TOKENS tokens, dense causal attention, K/V written to the paged pools, logits of every prompt's last
@@ -420,7 +582,7 @@ def run_prefill(args) -> dict:
         "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "int8 codes on tcgen05 kind::i8, f16 mma.sync attention, f32 scales and accumulate",
         "data": "synthetic",
-        "config": {"workload": "BASELINE config 5: Llama-3-8B shape, %d layers, Q8_0 weights, %d prompts x %d tokens, causal" % (cfg.n_layers, n_seqs, n_tokens),
+        "config": {"workload": "benchmark config 5: Llama-3-8B shape, %d layers, Q8_0 weights, %d prompts x %d tokens, causal" % (cfg.n_layers, n_seqs, n_tokens),
                    "parallelism": "tp%d" % world},
         "gpu_launches": prog.dispatch_count() * args.steps, "clocks": clocks,
         "roofline": {"bound": "tensor", "kernel": "whole step", "achieved": tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": tf / peak_tf,
@@ -480,7 +642,7 @@ def run_kernel(args) -> dict:
         what = "%s weights [%d x %d], %d activation column(s)" % (spec[1], M, K, N)
     elif spec[0] == "paged_attention":
         cfg = DecoderConfig()
-        # CTX "ragged": context lengths uniform in [128, 8192] (BASELINE config 3), seeded
+        # CTX "ragged": context lengths uniform in [128, 8192] (benchmark config 3), seeded
         seqs = int(spec[1])
         ragged = spec[2] == "ragged"
         ctx = 8192 if ragged else int(spec[2])
@@ -647,7 +809,7 @@ def run_reference(args) -> dict:
     return {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "tok/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["ms_per_step"], "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int8 dot, f32 accumulate (ggml CPU)", "data": "synthetic",
-            "config": {"workload": "BASELINE config 4 (bounded sample, see cpu_baseline.sample)", "parallelism": "cpu"},
+            "config": {"workload": "benchmark config 4 (bounded sample, see cpu_baseline.sample)", "parallelism": "cpu"},
             "cpu_baseline": cb, "gpu_launches": 0,
             "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
 
@@ -659,9 +821,11 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the reduced-model check against the CPU oracle before the timed region")
+    ap.add_argument("--parity-only", action="store_true", help="run only that check (every rank) and print its result")
     ap.add_argument("--kernel", default="", help="time one kernel instead of the decode step, e.g. mul_mat:q4_K:4096:14336:1 "
                                                  "or paged_attention:32:2048")
-    ap.add_argument("--prefill", default="", help="time the prompt pass instead: SEQS:TOKENS[:LAYERS], e.g. 8:2048 (BASELINE config 5)")
+    ap.add_argument("--prefill", default="", help="time the prompt pass instead: SEQS:TOKENS[:LAYERS], e.g. 8:2048 (benchmark config 5)")
     ap.add_argument("--copies", type=int, default=0, help="--kernel: independent copies of the op per replay")
     args = ap.parse_args()
     if args.kernel:
@@ -669,6 +833,21 @@ def main() -> None:
         return
     if args.prefill:
         out = run_prefill(args)
+        if out:
+            print(json.dumps(out), flush=True)
+        return
+    if args.parity_only:
+        import torch
+        world, rank, local_rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+        dist = None
+        if world > 1:
+            import torch.distributed as dist
+            torch.cuda.set_device(local_rank)
+            dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world)
+        out = tp_parity(world, rank, local_rank, dist)
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
         if out:
             print(json.dumps(out), flush=True)
         return

@@ -3,8 +3,8 @@
  * The reference reaches its native CUDA executor through Rust types
  * (crates/tensorlisp/src/native_cuda.rs:28-168 over crates/kernels/src/cuda/exec.rs:20-240); there
  * is no C ABI at that seam. This header is the seam restated as plain C so a Rust shim with the
- * same eleven methods as native_cuda.rs can bind it (the stub is shown in INTEGRATION.md).
- * Every entry point names the reference item it replaces.
+ * same eleven methods as native_cuda.rs can bind it through `extern "C"` declarations of the
+ * functions below. Every entry point names the reference item it replaces.
  *
  * Conventions
  *  - every function returns a tlb_status; TLB_OK is 0. No entry point aborts, throws or exits.
@@ -145,6 +145,10 @@ tlb_status tlb_program_read(tlb_program *prog, uint32_t tensor_id, uint64_t byte
 /* Program::dispatch_count / labels (exec.rs:81-88) */
 uint32_t   tlb_program_dispatch_count(tlb_program *prog);
 const char *tlb_program_label(tlb_program *prog, uint32_t i);
+/* How many CUDA graphs the program holds: one is captured per set of (weight buffers, state block, communicator
+ * generation) it has been run with, and replayed on later runs with the same set (no counterpart: the reference
+ * relaunches every kernel, exec.rs:186-225). */
+uint32_t   tlb_program_graph_count(tlb_program *prog);
 /* Device address and size of an input / kept tensor, so a caller that already has data in HBM can
  * write inputs and read results without the host (no counterpart: the reference only has the
  * blocking host copies). Returns NULL for tensors outside the io buffer and the arena. */
@@ -205,6 +209,10 @@ tlb_status tlb_comm_destroy(tlb_device *dev);
  * waits are bounded; a rank that never arrives makes tlb_program_run fail instead of hanging.
  * Used by default with more than 2 ranks (measured faster there); TLB_P2P_ALLREDUCE=1 turns it on for 2
  * ranks, TLB_NO_P2P_ALLREDUCE=1 keeps NCCL everywhere. */
+/* A counter that grows with every change of the device's communicator (init, import, destroy). A captured CUDA graph
+ * has the communicator's state baked into its launches (the all-reduce path, the peers' mapped addresses), so a
+ * program run after such a change captures a new graph instead of replaying an old one. */
+uint64_t   tlb_device_comm_generation(tlb_device *dev);
 tlb_status tlb_comm_p2p_export(tlb_device *dev, void *handle64);
 tlb_status tlb_comm_p2p_import(tlb_device *dev, const void *handles);
 /* The same protocol with n_ranks emulated ranks on ONE device in one cooperative launch (test hook):
@@ -220,6 +228,21 @@ tlb_status tlb_comm_p2p_selftest(tlb_device *dev, int n_ranks, int n, int calls,
 tlb_status tlb_comm_p2p_selftest_rows(tlb_device *dev, int n_ranks, int rows, int K, int n_split, int calls, const float *in,
                                       const float *resid, const float *w, float eps, float *out_sum, void *out_q,
                                       uint64_t act_bytes);
+
+/* The two self tests with one emulated rank (`absent_rank`) that never pushes: the other ranks' waits run out after
+ * `spin_limit` probes of its flag, the launch ends, and the call returns TLB_EXECUTION ("gave up waiting") -- what
+ * tlb_program_run reports when a real rank never arrives. TLB_AR_SPIN_LIMIT sets the limit of the real kernels
+ * (default 2^22 probes). */
+tlb_status tlb_comm_p2p_selftest_absent(tlb_device *dev, int n_ranks, int n, int absent_rank, uint32_t spin_limit, const float *in,
+                                        float *out);
+tlb_status tlb_comm_p2p_selftest_rows_absent(tlb_device *dev, int n_ranks, int rows, int K, int absent_rank, uint32_t spin_limit,
+                                             const float *in, const float *resid, const float *w, float eps, float *out_sum,
+                                             void *out_q, uint64_t act_bytes);
+/* Test hook for the bounded mbarrier waits of the TMA / tcgen05 kernels: one CTA waits on a barrier nothing arrives
+ * on, gives up after `limit` probes (`nap_ns` nanoseconds apart, 0 = back to back) and sets the device error word
+ * the way the mul_mat kernels do; the call then fails with TLB_EXECUTION like tlb_program_run would, and
+ * *waited_us says how long the wait lasted. No counterpart in the reference (its kernels have no waits). */
+tlb_status tlb_selftest_wait_runs_out(tlb_device *dev, uint32_t limit, uint32_t nap_ns, double *waited_us);
 
 #ifdef __cplusplus
 }

@@ -97,7 +97,8 @@ def build_ref(ref: Path, variants: list[str], force: bool = False) -> list[Path]
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("TENSORLISP_REFERENCE") or str(Path(__file__).resolve().parent.parent.parent / "reference"),
+                    help="checkout of the reference (default: TENSORLISP_REFERENCE, else a `reference` directory beside this repository)")
     ap.add_argument("--variants", default="base,v3,v4")
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args()

@@ -103,6 +103,11 @@ SYMBOLS = {
     "tlb_comm_destroy": (C.c_int, [_P]),
     "tlb_comm_p2p_export": (C.c_int, [_P, _P]),
     "tlb_comm_p2p_import": (C.c_int, [_P, _P]),
+    "tlb_program_graph_count": (C.c_uint32, [_P]),
+    "tlb_device_comm_generation": (C.c_uint64, [_P]),
+    "tlb_comm_p2p_selftest_absent": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_uint32, _P, _P]),
+    "tlb_comm_p2p_selftest_rows_absent": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint32, _P, _P, _P, C.c_float, _P, _P, C.c_uint64]),
+    "tlb_selftest_wait_runs_out": (C.c_int, [_P, C.c_uint32, C.c_uint32, C.POINTER(C.c_double)]),
     "tlb_comm_p2p_selftest": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int, _P, _P]),
     "tlb_comm_p2p_selftest_rows": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _P, _P, _P, C.c_float, _P, _P, C.c_uint64]),
 }

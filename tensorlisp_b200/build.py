@@ -44,7 +44,7 @@ def _run(cmd: list[str], verbose: bool) -> str:
 
 def build(force: bool = False, verbose: bool = False) -> Path:
     srcs = sorted(CSRC.glob("*.cu"))
-    hdrs = list(CSRC.glob("*.h")) + [HERE.parent / "include" / "tlb200.h"]
+    hdrs = list(CSRC.glob("*.h")) + list(CSRC.glob("*.cuh")) + [HERE.parent / "include" / "tlb200.h"]
     newest_hdr = max(h.stat().st_mtime for h in hdrs)
     OBJ.mkdir(exist_ok=True)
     nvcc = _nvcc()

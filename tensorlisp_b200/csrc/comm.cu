@@ -66,6 +66,7 @@ static NcclApi &nccl() {
 __device__ __forceinline__ void ar_body(const ArRank &a, int n, int n_ranks, int c, int n_ctas) {
     __shared__ int s_fail;
     const int tid = threadIdx.x;
+    if (a.skip_push) return;   // self tests: a rank that never shows up
     char *local = a.peer[a.rank];
     uint32_t *seqs = reinterpret_cast<uint32_t *>(local + AR_SEQ_OFF);
     const uint32_t seq = seqs[c] + 1;
@@ -97,7 +98,7 @@ __device__ __forceinline__ void ar_body(const ArRank &a, int n, int n_ranks, int
         // ---- wait (bounded) for chunk c of rank `tid` to have landed here
         const uint32_t *mine = reinterpret_cast<const uint32_t *>(local + AR_FLAG_OFF) + ((size_t)par * AR_MAX_RANKS + tid) * AR_CTAS + c;
         bool ok = false;
-        for (uint32_t it = 0; it < AR_SPIN_LIMIT; it++) {
+        for (uint32_t it = 0; it < a.spin_limit; it++) {
             uint32_t f;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(f) : "l"(mine) : "memory");
             if ((int32_t)(f - seq) >= 0) { ok = true; break; }
@@ -160,6 +161,7 @@ cudaError_t comm_allreduce_f32(tlb_device *dev, float *buf, size_t n, cudaStream
         a.n_split = partial ? n_split : 0;
         a.rank = c->rank;
         a.err = err;
+        a.spin_limit = ar_spin_limit();
         for (int p = 0; p < c->n_ranks; p++) a.peer[p] = c->peer[p];
         k_allreduce_oneshot<<<ar_grid(n), AR_THREADS, 0, st>>>(a, (int)n, c->n_ranks);
         return cudaGetLastError();
@@ -182,6 +184,7 @@ cudaError_t comm_exchange_row_quant(tlb_device *dev, float *data, const float *p
     a.n_split = partial ? n_split : 0;
     a.rank = c->rank;
     a.err = err;
+    a.spin_limit = ar_spin_limit();
     for (int r = 0; r < c->n_ranks; r++) a.peer[r] = c->peer[r];
     return launch_exchange_row_quant(a, p, c->n_ranks, st);
 }
@@ -229,6 +232,7 @@ tlb_status tlb_comm_init(tlb_device *dev, int n_ranks, int rank, const void *id1
         }
     }
     dev->comm = c;
+    dev->comm_generation++;
     return TLB_OK;
 }
 
@@ -281,12 +285,25 @@ tlb_status tlb_comm_p2p_import(tlb_device *dev, const void *handles) {
     const char *off = getenv("TLB_NO_P2P_ALLREDUCE"), *on = getenv("TLB_P2P_ALLREDUCE");
     c->p2p = c->n_ranks > 2 || (on && on[0] == '1');
     if (off && off[0] == '1') c->p2p = false;
+    dev->comm_generation++;
     return TLB_OK;
 }
 
 // Single-GPU check of the all-reduce protocol: `n_ranks` emulated ranks (their buffers all on this
 // device) run as ONE cooperative launch; in[r] / out[r] are n floats per rank on the host.
+static tlb_status p2p_selftest(tlb_device *dev, int n_ranks, int n, int calls, int n_split, const float *in, float *out, int absent_rank,
+                               uint32_t spin_limit);
 tlb_status tlb_comm_p2p_selftest(tlb_device *dev, int n_ranks, int n, int calls, int n_split, const float *in, float *out) {
+    return p2p_selftest(dev, n_ranks, n, calls, n_split, in, out, -1, ar_spin_limit());
+}
+// The same launch with one emulated rank that never pushes: the waits of the others run out after `spin_limit`
+// probes, the kernel returns, and the call reports TLB_EXECUTION ("gave up waiting") instead of hanging.
+tlb_status tlb_comm_p2p_selftest_absent(tlb_device *dev, int n_ranks, int n, int absent_rank, uint32_t spin_limit, const float *in, float *out) {
+    if (absent_rank < 0 || absent_rank >= n_ranks || spin_limit == 0) return fail(TLB_INVALID, "tlb_comm_p2p_selftest_absent: bad arguments");
+    return p2p_selftest(dev, n_ranks, n, 1, 0, in, out, absent_rank, spin_limit);
+}
+static tlb_status p2p_selftest(tlb_device *dev, int n_ranks, int n, int calls, int n_split, const float *in, float *out, int absent_rank,
+                               uint32_t spin_limit) {
     if (!dev || n_ranks < 1 || n_ranks > AR_MAX_RANKS || n < 4 || n % 4 || (size_t)n * 4 > AR_SLOT_BYTES || calls < 1 || n_split < 0 ||
         n_split > 16 || !in || !out)
         return fail(TLB_INVALID, "tlb_comm_p2p_selftest: bad arguments");
@@ -311,6 +328,8 @@ tlb_status tlb_comm_p2p_selftest(tlb_device *dev, int n_ranks, int n, int calls,
         all.r[r].n_split = n_split;
         all.r[r].rank = r;
         all.r[r].err = err;
+        all.r[r].spin_limit = spin_limit;
+        all.r[r].skip_push = r == absent_rank;
         for (int p = 0; p < n_ranks; p++) all.r[r].peer[p] = bufs[p];
     }
     int flag = 0;
@@ -347,8 +366,20 @@ tlb_status tlb_comm_p2p_selftest(tlb_device *dev, int n_ranks, int n, int calls,
 // Single-GPU check of the fused exchange + residual add + RMS norm + Q8_K kernel: n_ranks <= 4 emulated ranks in one
 // cooperative launch. in: n_ranks x n_split x rows x K partial results (n_split >= 1), resid: rows x K, w: K.
 // out_sum: n_ranks x rows x K (the new residual stream of every rank), out_q: n_ranks x act_bytes (the Q8_K block).
+static tlb_status p2p_selftest_rows(tlb_device *dev, int n_ranks, int rows, int K, int n_split, int calls, const float *in, const float *resid,
+                                    const float *w, float eps, float *out_sum, void *out_q, uint64_t act_bytes, int absent_rank, uint32_t spin_limit);
 tlb_status tlb_comm_p2p_selftest_rows(tlb_device *dev, int n_ranks, int rows, int K, int n_split, int calls, const float *in,
                                       const float *resid, const float *w, float eps, float *out_sum, void *out_q, uint64_t act_bytes) {
+    return p2p_selftest_rows(dev, n_ranks, rows, K, n_split, calls, in, resid, w, eps, out_sum, out_q, act_bytes, -1, ar_spin_limit());
+}
+// One emulated rank never pushes its rows: the others give up after `spin_limit` probes and the call fails.
+tlb_status tlb_comm_p2p_selftest_rows_absent(tlb_device *dev, int n_ranks, int rows, int K, int absent_rank, uint32_t spin_limit, const float *in,
+                                             const float *resid, const float *w, float eps, float *out_sum, void *out_q, uint64_t act_bytes) {
+    if (absent_rank < 0 || absent_rank >= n_ranks || spin_limit == 0) return fail(TLB_INVALID, "tlb_comm_p2p_selftest_rows_absent: bad arguments");
+    return p2p_selftest_rows(dev, n_ranks, rows, K, 1, 1, in, resid, w, eps, out_sum, out_q, act_bytes, absent_rank, spin_limit);
+}
+static tlb_status p2p_selftest_rows(tlb_device *dev, int n_ranks, int rows, int K, int n_split, int calls, const float *in, const float *resid,
+                                    const float *w, float eps, float *out_sum, void *out_q, uint64_t act_bytes, int absent_rank, uint32_t spin_limit) {
     if (!dev || n_ranks < 1 || n_ranks > 4 || n_split < 1 || n_split > 16 || calls < 1 || !in || !resid || !w || !out_sum || !out_q ||
         !exchange_row_quant_supported(K, rows))
         return fail(TLB_INVALID, "tlb_comm_p2p_selftest_rows: bad arguments");
@@ -380,6 +411,8 @@ tlb_status tlb_comm_p2p_selftest_rows(tlb_device *dev, int n_ranks, int rows, in
         a[r].n_split = n_split;
         a[r].rank = r;
         a[r].err = err;
+        a[r].spin_limit = spin_limit;
+        a[r].skip_push = r == absent_rank;
         for (int k = 0; k < n_ranks; k++) a[r].peer[k] = bufs[k];
         p[r] = RowQuantArgs{};
         p[r].mode = RQ_NORM;
@@ -439,6 +472,7 @@ tlb_status tlb_comm_destroy(tlb_device *dev) {
     if (dev->comm->comm) nccl().CommDestroy(dev->comm->comm);
     delete dev->comm;
     dev->comm = nullptr;
+    dev->comm_generation++;   // captured graphs that hold the closed peer mappings are never replayed
     return TLB_OK;
 }
 

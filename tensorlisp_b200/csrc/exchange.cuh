@@ -6,6 +6,7 @@
 #pragma once
 #include <cstddef>
 #include <cstdint>
+#include <cstdlib>
 
 namespace tlb {
 
@@ -19,7 +20,7 @@ constexpr size_t AR_DATA_OFF = 8192;                           // [2][AR_MAX_RAN
 constexpr size_t AR_SET_BYTES = AR_DATA_OFF + 2 * AR_MAX_RANKS * AR_SLOT_BYTES;
 constexpr int AR_SETS = 2;                                    // 0: plain all-reduce, 1: the fused row kernel
 constexpr size_t AR_BUF_BYTES = AR_SETS * AR_SET_BYTES;
-constexpr uint32_t AR_SPIN_LIMIT = 1u << 22;   // probes of a local flag, a few seconds
+constexpr uint32_t AR_SPIN_LIMIT = 1u << 22;   // default number of probes of a local flag, a few seconds (TLB_AR_SPIN_LIMIT overrides)
 
 struct ArRank {
     float *data;                 // n floats, reduced in place
@@ -28,7 +29,15 @@ struct ArRank {
     char *peer[AR_MAX_RANKS];    // exchange buffers of all ranks as mapped into this rank (own one included)
     int rank;
     int *err;
+    uint32_t spin_limit;         // probes of a peer's flag before the wait gives up and the error word is set
+    int skip_push;               // self tests only: this rank neither pushes nor raises its flags, so its peers' waits run out
 };
+// the limit the host passes to the kernels
+inline uint32_t ar_spin_limit() {
+    const char *v = getenv("TLB_AR_SPIN_LIMIT");
+    const long n = v ? atol(v) : 0;
+    return n > 0 ? (uint32_t)n : AR_SPIN_LIMIT;
+}
 
 
 }  // namespace tlb

@@ -202,7 +202,20 @@ Layout plan(const Graph &g, const Leaves &leaves, const std::function<uint64_t(i
     return L;
 }
 
-static std::once_flag g_configure_once;
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) applies to the device that is current when it is called, so the
+// kernels are configured once per ordinal, with that ordinal current.
+static std::mutex g_configure_mutex;
+static uint64_t g_configured_ordinals = 0;   // bit per ordinal (a box has at most 64 GPUs)
+static void configure_kernels_once(int ordinal) {
+    std::lock_guard<std::mutex> lock(g_configure_mutex);
+    const uint64_t bit = 1ull << (ordinal & 63);
+    if (g_configured_ordinals & bit) return;
+    gemv_configure();
+    attn_configure();
+    mmq_tc_configure();
+    mmq_tc8_configure();
+    g_configured_ordinals |= bit;
+}
 
 }  // namespace tlb
 
@@ -255,12 +268,7 @@ tlb_status tlb_device_open(int ordinal, tlb_device **dev) {
         return fail(TLB_NO_DEVICE, "cudaStreamCreate: " + cuda_msg(e));
     }
     d->name = std::string("native ") + d->prop.name;
-    std::call_once(g_configure_once, [] {
-        gemv_configure();
-        attn_configure();
-        mmq_tc_configure();
-        mmq_tc8_configure();
-    });
+    configure_kernels_once(ordinal);   // cudaSetDevice(ordinal) above made it current
     *dev = d;
     return TLB_OK;
 }
@@ -583,6 +591,7 @@ tlb_status tlb_program_enqueue(tlb_program *prog, tlb_buffer *const *weights, ui
     std::vector<void *> key;
     for (char *w : rc.weights) key.push_back(w);
     key.push_back(rc.state);
+    key.push_back((void *)(uintptr_t)prog->dev->comm_generation);   // the launches bake the communicator's state in
     for (auto &c : prog->captured)
         if (c.key == key) {
             TLB_TRY_CUDA(cudaGraphLaunch(c.exec, rc.stream), TLB_EXECUTION);
@@ -688,6 +697,8 @@ tlb_status tlb_program_read(tlb_program *prog, uint32_t tensor_id, uint64_t byte
     return TLB_OK;
 }
 
+uint32_t tlb_program_graph_count(tlb_program *prog) { return prog ? (uint32_t)prog->captured.size() : 0; }
+uint64_t tlb_device_comm_generation(tlb_device *dev) { return dev ? dev->comm_generation : 0; }
 uint32_t tlb_program_dispatch_count(tlb_program *prog) { return prog ? (uint32_t)prog->dispatches.size() : 0; }
 const char *tlb_program_label(tlb_program *prog, uint32_t i) {
     return prog && i < prog->dispatches.size() ? prog->dispatches[i].label.c_str() : "";
@@ -701,6 +712,32 @@ void *tlb_program_tensor_ptr(tlb_program *prog, uint32_t tensor_id, uint64_t *by
     if (pl.buf == BUF_ARENA) return (char *)prog->arena + pl.off;
     if (pl.buf == BUF_IO) return (char *)prog->io + pl.off;
     return nullptr;
+}
+
+// ------------------------------------------------------------------ test hook: a bounded wait that runs out
+tlb_status tlb_selftest_wait_runs_out(tlb_device *dev, uint32_t limit, uint32_t nap_ns, double *waited_us) {
+    if (!dev || limit == 0) return fail(TLB_INVALID, "tlb_selftest_wait_runs_out: bad arguments");
+    cudaSetDevice(dev->ordinal);
+    char *buf = nullptr;
+    if (cudaMalloc(&buf, 512) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(TLB_ALLOC, "buffer allocation of 512 bytes failed");
+    }
+    cudaError_t e = cudaMemsetAsync(buf, 0, 512, dev->stream);
+    if (e == cudaSuccess) e = launch_wait_runs_out(limit, nap_ns, (int *)buf, (unsigned long long *)(buf + 256), dev->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(dev->stream);
+    int flag = 0;
+    unsigned long long ns = 0;
+    if (e == cudaSuccess) e = cudaMemcpy(&flag, buf, 4, cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess) e = cudaMemcpy(&ns, buf + 256, 8, cudaMemcpyDeviceToHost);
+    cudaFree(buf);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(TLB_EXECUTION, "wait self test: " + cuda_msg(e));
+    }
+    if (waited_us) *waited_us = (double)ns / 1e3;
+    if (flag != 0) return fail(TLB_EXECUTION, "a kernel gave up waiting for its own copies (device error word " + std::to_string(flag) + ")");
+    return TLB_OK;
 }
 
 // ------------------------------------------------------------------ quantizers

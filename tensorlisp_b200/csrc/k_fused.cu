@@ -205,6 +205,7 @@ __device__ __forceinline__ void xr_body(const ArRank &a, const RowQuantArgs &p, 
         }
         return;
     }
+    if (a.skip_push) return;   // self tests: a rank that never shows up
     char *local = a.peer[a.rank] + AR_SET_BYTES;   // second set: this kernel cuts the data by rows
     uint32_t *seqs = reinterpret_cast<uint32_t *>(local + AR_SEQ_OFF);
     const uint32_t seq = seqs[n] + 1, par = seq & 1;
@@ -235,7 +236,7 @@ __device__ __forceinline__ void xr_body(const ArRank &a, const RowQuantArgs &p, 
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(seq) : "memory");
         const uint32_t *mine = reinterpret_cast<const uint32_t *>(local + AR_FLAG_OFF) + ((size_t)par * AR_MAX_RANKS + tid) * AR_CTAS + n;
         bool ok = false;
-        for (uint32_t it = 0; it < AR_SPIN_LIMIT; it++) {
+        for (uint32_t it = 0; it < a.spin_limit; it++) {
             uint32_t f;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(f) : "l"(mine) : "memory");
             if ((int32_t)(f - seq) >= 0) { ok = true; break; }

@@ -672,6 +672,33 @@ void launch_mmq_reduce(const float *partial, float *y, int64_t total, int n_spli
 
 bool tc_available() { return encode_tiled() != nullptr; }
 
+// Test hook: every thread of one CTA waits, with the kernels' own bounded wait, on a barrier that nothing ever
+// arrives on. After `limit` probes the wait gives up, the error word is set the way the mul_mat kernels set it,
+// and the kernel returns; *ns receives how long thread 0 waited (globaltimer).
+__global__ void k_wait_runs_out(uint32_t limit, unsigned nap_ns, int *err, unsigned long long *ns) {
+    __shared__ uint64_t bar;
+    __shared__ int s_fail;
+    if (threadIdx.x == 0) {
+        tc::mbar_init(&bar, 1);
+        s_fail = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    unsigned long long t0, t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    tc::mbar_wait_nap(&bar, 0u, &s_fail, nap_ns, limit);
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        *ns = t1 - t0;
+        if (s_fail) atomicExch(err, 2);
+    }
+}
+cudaError_t launch_wait_runs_out(uint32_t limit, unsigned nap_ns, int *err, unsigned long long *ns, cudaStream_t st) {
+    k_wait_runs_out<<<1, 64, 0, st>>>(limit, nap_ns, err, ns);
+    return cudaGetLastError();
+}
+
 // n_mats weight matrices [M[j] x K] sharing the activations; y[j] dense [N][M[j]] when n_mats > 1 or K is split
 cudaError_t launch_mmq_tc_group(const TcPlan &t, int n_mats, const void *const *W, int64_t K, const int64_t *M, int64_t N, const void *blobs,
                                 float *const *y, int64_t ldy, void *partial, int *err, cudaStream_t st, bool leave_partial) {

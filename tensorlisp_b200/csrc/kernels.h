@@ -64,7 +64,8 @@ cudaError_t launch_mmq_tc(const TcPlan &t, const void *W, int64_t K, int64_t M, 
 cudaError_t launch_mmq_tc_group(const TcPlan &t, int n_mats, const void *const *W, int64_t K, const int64_t *M, int64_t N, const void *blobs,
                                 float *const *y, int64_t ldy, void *partial, int *err, cudaStream_t st, bool leave_partial = false);
 void mmq_tc_configure();
-bool tc_available();   // the driver offers cuTensorMapEncodeTiled
+bool tc_available();
+cudaError_t launch_wait_runs_out(uint32_t limit, unsigned nap_ns, int *err, unsigned long long *ns, cudaStream_t st);   // the driver offers cuTensorMapEncodeTiled
 
 // ---------------------------------------------------------------- k_mmq_tc_q8.cu
 // Q8_0 weights x 5..32 activation columns on tcgen05 (kind::i8, one accumulator per 32-element block).

@@ -56,28 +56,17 @@ __device__ __forceinline__ bool mbar_test(uint32_t a, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// The waits below give up after WAIT_LIMIT probes; `fail` is checked only once a wait has had to loop, so a
-// wait whose phase is already complete costs one probe.
-__device__ __forceinline__ void mbar_wait(uint64_t *bar, uint32_t parity, volatile int *fail) {
+// The waits below give up after `limit` probes (WAIT_LIMIT in the kernels; the self test passes a small one): `fail`
+// is set, and every later wait of the CTA returns at once, so the kernel runs to its end (with a wrong result
+// and the error word set) instead of hanging. `fail` is looked at only once a wait has had to loop, so a wait
+// whose phase is already complete costs one probe.
+// ns > 0 naps between probes: for roles that run ahead of the role they wait for (epilogue, TMA refills, MMA
+// issue), so that their probing does not take issue slots from the warps that expand the weights.
+__device__ __forceinline__ void mbar_wait_nap(uint64_t *bar, uint32_t parity, volatile int *fail, unsigned ns, uint32_t limit = WAIT_LIMIT) {
     const uint32_t a = su32(bar);
     if (mbar_try(a, parity)) return;   // the common case: the phase has already completed
     if (*fail) return;
-    uint32_t n = WAIT_LIMIT;
-    while (!mbar_try(a, parity)) {
-        if (--n == 0) {
-            *fail = 1;
-            return;
-        }
-    }
-}
-// The same wait with a nap between probes: for roles that run ahead of the role they wait for (epilogue, TMA
-// refills, MMA issue), so that their probing does not take issue slots and ALU cycles from the warps that
-// expand the weights. ns == 0 probes back to back.
-__device__ __forceinline__ void mbar_wait_nap(uint64_t *bar, uint32_t parity, volatile int *fail, unsigned ns) {
-    const uint32_t a = su32(bar);
-    if (mbar_try(a, parity)) return;
-    if (*fail) return;
-    uint32_t n = WAIT_LIMIT;
+    uint32_t n = limit;
     for (;;) {
         if (ns) __nanosleep(ns);
         if (mbar_try(a, parity)) return;
@@ -87,6 +76,7 @@ __device__ __forceinline__ void mbar_wait_nap(uint64_t *bar, uint32_t parity, vo
         }
     }
 }
+__device__ __forceinline__ void mbar_wait(uint64_t *bar, uint32_t parity, volatile int *fail) { mbar_wait_nap(bar, parity, fail, 0); }
 __device__ __forceinline__ void mbar_wait_relaxed(uint64_t *bar, uint32_t parity, volatile int *fail) { mbar_wait_nap(bar, parity, fail, 64); }
 __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(su32(dst)),

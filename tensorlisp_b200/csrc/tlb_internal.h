@@ -118,6 +118,10 @@ struct tlb_device {
     cudaDeviceProp prop{};
     std::string name;
     tlb::Comm *comm = nullptr;
+    // Bumped whenever the communicator changes (tlb_comm_init, tlb_comm_p2p_import, tlb_comm_destroy). The launches of
+    // a captured CUDA graph have the communicator's state baked in (which all-reduce path, the peers' mapped
+    // pointers), so the generation is part of the key a captured graph is replayed under.
+    uint64_t comm_generation = 0;
 };
 
 struct tlb_buffer {

@@ -1,4 +1,4 @@
-"""The graphs of the BASELINE configurations, written against ``Graph`` the way the reference's
+"""The graphs of the benchmark configurations, written against ``Graph`` the way the reference's
 Scheme programs are written against the generated ``(ggml-*)`` ops: each helper is the stdlib form
 it restates (crates/tensorlisp/src/scheme/stdlib/nn.ss, attn.ss; ports/gemma4/concurrency.ss for
 the paged decode loop). Weights are declared in a fixed order so a caller can lay the weight buffer
@@ -15,7 +15,7 @@ from .graph import F16, F32, I32, Q4_K, Q8_0, Graph, row_size
 
 @dataclass
 class DecoderConfig:
-    """Llama-style decoder. Defaults are the Llama-3-8B shape of BASELINE config 4."""
+    """Llama-style decoder. Defaults are the Llama-3-8B shape of benchmark config 4."""
     n_layers: int = 32
     d_model: int = 4096
     n_heads: int = 32
@@ -49,7 +49,7 @@ def rms_norm_w(g: Graph, x: int, w: int, eps: float, name: str = "") -> int:
 
 
 def swiglu_ffn(g: Graph, x: int, norm_w: int, gate: int, up: int, down: int, eps: float, p: str = "") -> int:
-    """BASELINE config 2: RMSNorm -> gate/up -> SiLU(gate)*up -> down (gated MLP of ports/gemma4/gemma4.ss:62-64)."""
+    """benchmark config 2: RMSNorm -> gate/up -> SiLU(gate)*up -> down (gated MLP of ports/gemma4/gemma4.ss:62-64)."""
     h = rms_norm_w(g, x, norm_w, eps, p + "ffn_in")
     a = g.mul_mat(gate, h, p + "ffn_gate_out")
     b = g.mul_mat(up, h, p + "ffn_up_out")
@@ -191,7 +191,7 @@ def decoder_step(cfg: DecoderConfig, batch: int, max_ctx: int, pool_blocks: int,
 
 
 def prefill_step(cfg: DecoderConfig, n_seqs: int, n_tokens: int, tp: int = 1, write_cache: bool = True) -> DecoderGraph:
-    """Prompt pass of BASELINE config 5: `n_seqs` prompts of `n_tokens` tokens each through the whole decoder with
+    """Prompt pass of benchmark config 5: `n_seqs` prompts of `n_tokens` tokens each through the whole decoder with
     dense causal attention (attn:flash of stdlib/attn.ss over permuted views, the way the reference's ports
     build prefill), the new keys and values written to the paged pools, logits for the last token of every
     prompt. Inputs: token ids [n_seqs*n_tokens], positions, the f16 causal mask [n_tokens, n_tokens] shared by

@@ -90,3 +90,42 @@ def test_exchange_fused_with_add_norm_quant(native, oracle, ranks, splits):
         assert diff.max() <= 1 and (diff != 0).mean() < 1e-3
         assert np.array_equal(bs, codes.reshape(rows, K // 16, 16).astype(np.int32).sum(axis=2).astype(np.int16))
         assert np.array_equal(out_q[r], out_q[0])    # every rank holds the same bytes
+
+
+@pytest.mark.parametrize("ranks,absent", [(2, 1), (4, 0), (8, 5)])
+def test_a_rank_that_never_arrives_ends_the_wait(native, ranks, absent):
+    """One emulated rank never pushes. The waits of the others are bounded: after `spin_limit` probes they
+    give up, the launch ends (nothing is left waiting on the device), the call reports Execution with the
+    "gave up waiting" message that tlb_program_run gives for a real missing rank, and the device is usable
+    afterwards (a complete exchange right behind it succeeds)."""
+    import time
+    from tensorlisp_b200._lib import TLB_EXECUTION
+    n = 32 * 4096
+    x = np.ones((ranks, n), np.float32)
+    out = np.zeros_like(x)
+    p = lambda a: a.ctypes.data_as(C.c_void_p)
+    t0 = time.time()
+    st = lib().tlb_comm_p2p_selftest_absent(native.dev, ranks, n, absent, 2000, p(x), p(out))
+    assert st == TLB_EXECUTION, st
+    assert b"gave up waiting" in lib().tlb_last_error()
+    assert time.time() - t0 < 5.0
+    check(lib().tlb_comm_p2p_selftest(native.dev, ranks, n, 2, 0, p(x), p(out)))
+    assert np.array_equal(out, np.full_like(out, 2.0 * ranks))
+
+
+def test_a_rank_that_never_arrives_ends_the_fused_exchange(native):
+    from tensorlisp_b200._lib import TLB_EXECUTION
+    ranks, rows, K, eps = 4, 32, 4096, 1e-5
+    x = np.ones((ranks, 1, rows, K), np.float32)
+    resid = np.ones((rows, K), np.float32)
+    w = np.ones(K, np.float32)
+    al = lambda v: (v + 255) // 256 * 256
+    act_bytes = al(rows * K) + al(rows * (K // 256) * 4) + al(rows * (K // 16) * 2)
+    out_sum = np.zeros((ranks, rows, K), np.float32)
+    out_q = np.zeros((ranks, act_bytes), np.uint8)
+    p = lambda a: a.ctypes.data_as(C.c_void_p)
+    st = lib().tlb_comm_p2p_selftest_rows_absent(native.dev, ranks, rows, K, 2, 2000, p(x), p(resid), p(w), eps, p(out_sum), p(out_q), act_bytes)
+    assert st == TLB_EXECUTION, st
+    assert b"gave up waiting" in lib().tlb_last_error()
+    check(lib().tlb_comm_p2p_selftest_rows(native.dev, ranks, rows, K, 1, 1, p(x), p(resid), p(w), eps, p(out_sum), p(out_q), act_bytes))
+    assert np.array_equal(out_sum, np.full_like(out_sum, 1.0 + ranks))

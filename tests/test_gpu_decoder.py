@@ -1,5 +1,5 @@
-"""End-to-end parity of the SwiGLU FFN block (BASELINE config 2) and of a whole decode step of a
-Llama-shaped decoder (BASELINE config 4 geometry at reduced depth / width / vocabulary) against the
+"""End-to-end parity of the SwiGLU FFN block (benchmark config 2) and of a whole decode step of a
+Llama-shaped decoder (benchmark config 4 geometry at reduced depth / width / vocabulary) against the
 oracle.
 
 Two kinds of check on the decode step:
@@ -111,10 +111,20 @@ class NoisyOracle:
 
 def test_decode_step(oracle):
     cfg = DecoderConfig(n_layers=2, d_model=512, n_heads=4, n_kv_heads=2, head_dim=128, d_ffn=1024, vocab=1024)
-    B, max_ctx, bs = 3, 64, cfg.block_size
+    _decode_step_case(oracle, cfg, np.array([0, 17, 40], np.int32), 64, 4)
+
+
+def test_decode_step_full_width(oracle):
+    """Two layers at the benchmark's own width (d_model 4096, 32 / 8 heads of 128, FFN 14336: the real tile shapes,
+    K splits and grouped launches of the 8B-shape step), 8 sequences, a small vocabulary."""
+    cfg = DecoderConfig(n_layers=2, d_model=4096, n_heads=32, n_kv_heads=8, head_dim=128, d_ffn=14336, vocab=2048)
+    _decode_step_case(oracle, cfg, np.array([0, 5, 31, 100, 255, 16, 77, 200], np.int32), 256, 2)
+
+
+def _decode_step_case(oracle, cfg, ctx_before, max_ctx, noise_seeds):
+    B, bs = len(ctx_before), cfg.block_size
     rng = np.random.default_rng(5)
-    ctx_before = np.array([0, 17, 40], np.int32)          # tokens already cached per sequence
-    pos = ctx_before.copy()
+    pos = ctx_before.copy()                               # tokens already cached per sequence
     lens = ctx_before + 1
     ids = rng.integers(0, cfg.vocab, B).astype(np.int32)
     max_blocks = max_ctx // bs
@@ -187,13 +197,18 @@ def test_decode_step(oracle):
     # ---- end to end from the token ids
     want = oracle_decoder_step(oracle, cfg, dg.weights, weights, ids, pos, copy.deepcopy(ks), copy.deepcopy(vs))
     envelope = 0.0
-    for seed in range(4):
+    for seed in range(noise_seeds):
         noisy = oracle_decoder_step(NoisyOracle(oracle, 1e-6, seed), cfg, dg.weights, weights, ids, pos,
                                     copy.deepcopy(ks), copy.deepcopy(vs))
         envelope = max(envelope, float(np.abs(noisy - want).max()))
     err = float(np.abs(out["logits"] - want).max())
-    assert err <= max(1e-2, 1.5 * envelope), (err, envelope)
     top2 = np.sort(want, axis=1)[:, -2:]
     decided = (top2[:, 1] - top2[:, 0]) > 2 * max(err, envelope)
+    same_top1 = out["logits"].argmax(axis=1) == want.argmax(axis=1)
+    plain_bar = err <= 1e-2 and bool(same_top1.all())
+    print("decode step d_model %d: end-to-end logits error %.3e (the oracle's own 1e-6-noise envelope %.3e), top-1 equal in %d of %d rows, "
+          "%d rows undecided at that noise; the plain bar (1e-2 abs, identical top-1) %s"
+          % (cfg.d_model, err, envelope, int(same_top1.sum()), B, int((~decided).sum()), "holds" if plain_bar else "does not hold"))
+    assert err <= max(1e-2, 1.5 * envelope), (err, envelope)
     assert np.array_equal(out["logits"].argmax(axis=1)[decided], want.argmax(axis=1)[decided])
     m.close()

@@ -125,3 +125,28 @@ def test_sinks_are_reported_by_name():
     with pytest.raises(TlbError) as e:
         Model(g)
     assert "FLASH_ATTN_EXT" in str(e.value) and "not implemented" in str(e.value)
+
+
+def test_causal_prompt_2048_tokens():
+    """The prompt-pass shape: 2048 queries over 2048 keys, 32 heads over 8 KV heads of 128, causal f16 mask. The kernel
+    skips key tiles that the mask hides completely (most of the upper triangle); the closed form is evaluated on a
+    sample of query rows of every head, which covers first / last rows of tiles and the diagonal tiles."""
+    d, n, nh, nhkv = 128, 2048, 32, 8
+    rng = np.random.default_rng(2048)
+    q = rng.standard_normal((1, nh, n, d)).astype(np.float32)
+    k = rng.standard_normal((1, nhkv, n, d)).astype(np.float16)
+    v = rng.standard_normal((1, nhkv, n, d)).astype(np.float16)
+    mask = np.triu(np.full((n, n), -np.inf, np.float16), 1).reshape(1, 1, n, n)
+    scale = 1.0 / np.sqrt(d)
+    got = run_gpu(q, k, v, mask, scale, 0.0, 0.0, G.F16)[0]          # [nq, nh, d]
+    rows = sorted(set([0, 1, 63, 64, 65, 127, 128, 1023, 1024, 2047] + [int(i) for i in rng.integers(0, n, 54)]))
+    q16 = q.astype(np.float16).astype(np.float64)
+    worst = 0.0
+    for h in range(nh):
+        kk, vv = k[0, h // (nh // nhkv)].astype(np.float64), v[0, h // (nh // nhkv)].astype(np.float64)
+        for i in rows:
+            s = q16[0, h, i] @ kk[:i + 1].T * scale
+            p = np.exp(s - s.max())
+            want = (p / p.sum()) @ vv[:i + 1]
+            worst = max(worst, float(np.abs(got[i, h] - want).max() / max(np.abs(want).max(), 1e-6)))
+    assert worst <= TOL, worst

@@ -1,6 +1,6 @@
 """MUL_MAT through compiled programs against the oracle (= the reference's CPU backend semantics:
 activations quantized to Q8_0 / Q8_K, integer block dots, f32 scaling).
-Bar: max|got-want| <= 1e-3 * max|want| (BASELINE north_star); observed ~1e-6 (summation order)."""
+Bar: max|got-want| <= 1e-3 * max|want| (the bar the benchmark sets); observed ~1e-6 (summation order)."""
 import os
 
 import numpy as np
@@ -65,7 +65,7 @@ def test_q8_0_many_columns(oracle, K, M, N):
 
 
 def test_config1_q8_0_4096(oracle):
-    """BASELINE config 1: W 4096x4096 N(0,0.02) seed 0 -> Q8_0, x N(0,1) seed 1, batch 1 and 16."""
+    """benchmark config 1: W 4096x4096 N(0,0.02) seed 0 -> Q8_0, x N(0,1) seed 1, batch 1 and 16."""
     W = (np.random.default_rng(0).standard_normal((4096, 4096)) * 0.02).astype(np.float32)
     Wq = oracle.quantize(Q8_0, W)
     for N in (1, 16):
@@ -77,7 +77,7 @@ def test_config1_q8_0_4096(oracle):
 
 
 def test_linearity_full_size(oracle):
-    """Size-independent property at a BASELINE shape (Q4_K 4096->14336): scaling the activations by
+    """Size-independent property at a benchmark shape (Q4_K 4096->14336): scaling the activations by
     a power of two scales the result exactly (quantization commutes with powers of two)."""
     rng = np.random.default_rng(11)
     W = (rng.standard_normal((14336, 4096)) * 0.02).astype(np.float32)

@@ -88,8 +88,16 @@ def test_split_context_and_ragged_lengths(oracle):
 
 
 def test_config3_shape_reduced(oracle):
-    """BASELINE config 3 geometry (32 q heads, 8 kv heads, hd 128, 16-token pages, permuted pool) at
+    """benchmark config 3 geometry (32 q heads, 8 kv heads, hd 128, 16-token pages, permuted pool) at
     8 sequences with contexts drawn from U[128, 8192]."""
     ctxs = np.random.default_rng(3).integers(128, 8193, 8)
     got, want = paged_case(oracle, 8, 32, 8, 128, 16, ctxs, seed=3)
+    close(got, want, 1e-3)
+
+
+def test_config3_full_size(oracle):
+    """benchmark config 3 as it is stated: 64 sequences, contexts drawn from U[128, 8192] (seeded, about 266 k cached
+    tokens, 1.1 GB of f16 K/V in 16-token pages behind a permuted block table), 32 query heads over 8 KV heads of 128."""
+    ctxs = np.random.default_rng(3).integers(128, 8193, 64)
+    got, want = paged_case(oracle, 64, 32, 8, 128, 16, ctxs, seed=33)
     close(got, want, 1e-3)

@@ -1,4 +1,4 @@
-"""Prompt pass (BASELINE config 5 geometry at reduced depth / width / vocabulary, Q8_0 weights): several prompts
+"""Prompt pass (benchmark config 5 geometry at reduced depth / width / vocabulary, Q8_0 weights): several prompts
 through the whole decoder with dense causal attention, keys and values written to the paged pools, logits
 of every prompt's last token.
 
@@ -117,8 +117,13 @@ def test_prefill(oracle, n_seqs, n_tokens):
         noisy = oracle_prefill(NoisyOracle(oracle, 1e-6, seed), cfg, dg.weights, weights, ids, pos, n_seqs, n_tokens)
         envelope = max(envelope, float(np.abs(noisy - want).max()))
     err = float(np.abs(logits.reshape(want.shape) - want).max())
-    assert err <= max(1e-2, 1.5 * envelope), (err, envelope)
     top2 = np.sort(want, axis=1)[:, -2:]
     decided = (top2[:, 1] - top2[:, 0]) > 2 * max(err, envelope)
+    same_top1 = logits.reshape(want.shape).argmax(axis=1) == want.argmax(axis=1)
+    plain_bar = err <= 1e-2 and bool(same_top1.all())
+    print("prompt pass %d x %d: end-to-end logits error %.3e (the oracle's own 1e-6-noise envelope %.3e), top-1 equal in %d of %d rows, "
+          "%d rows undecided at that noise; the plain bar (1e-2 abs, identical top-1) %s"
+          % (n_seqs, n_tokens, err, envelope, int(same_top1.sum()), len(same_top1), int((~decided).sum()), "holds" if plain_bar else "does not hold"))
+    assert err <= max(1e-2, 1.5 * envelope), (err, envelope)
     assert np.array_equal(logits.reshape(want.shape).argmax(axis=1)[decided], want.argmax(axis=1)[decided])
     m.close()

@@ -30,7 +30,7 @@ def test_against_oracle(native, oracle, ty, name, shape, scale, seed):
 
 
 def test_config1_matrix_q8_0_bit_exact(native, oracle):
-    """BASELINE config 1: 4096x4096 N(0, 0.02) seed 0 -> Q8_0."""
+    """benchmark config 1: 4096x4096 N(0, 0.02) seed 0 -> Q8_0."""
     x = (np.random.default_rng(0).standard_normal((4096, 4096)) * 0.02).astype(np.float32)
     got = quantize_rows(native, Q8_0, x)
     assert got.shape == (4096, 4352)

@@ -1,4 +1,4 @@
-"""The CPU oracle against the reference's own ggml build on larger seeded inputs at BASELINE shapes
+"""The CPU oracle against the reference's own ggml build on larger seeded inputs at benchmark shapes
 (runs where oracle/_ref exists; the committed golden vectors cover machines where it does not)."""
 import numpy as np
 import pytest
