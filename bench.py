@@ -209,7 +209,7 @@ def tp_parity(world: int, rank: int, local_rank: int, dist, batch: int = 8) -> d
 
     if os.path.join(ROOT, "tests") not in sys.path:
         sys.path.insert(0, os.path.join(ROOT, "tests"))
-    from helpers import oracle_decoder_step
+    from helpers import NoisyOracle, oracle_decoder_step
     from oracle.bindings import Oracle
     from tensorlisp_b200.graph import align256
     from tensorlisp_b200.native import Native, NativeProgram, StateBlock
@@ -319,7 +319,16 @@ def tp_parity(world: int, rank: int, local_rank: int, dist, batch: int = 8) -> d
     if rank != 0:
         return {}
     full_logits = np.concatenate([p[0] for p in parts], axis=1)
-    want = oracle_decoder_step(Oracle(), cfg, full_specs, full_host, ids, pos, ks, vs)
+    import copy
+    oracle = Oracle()
+    want = oracle_decoder_step(oracle, cfg, full_specs, full_host, ids, pos, copy.deepcopy(ks), copy.deepcopy(vs))
+    # How far the reference's own arithmetic moves when its mul_mat outputs are perturbed by 1e-6 relative (the size of
+    # a summation-order difference): it re-quantizes activations to int8 before every mul_mat, so one flipped code,
+    # amplified by the RMS norms of a random-init residual stream, moves the logits by far more than 1e-6.
+    envelope = 0.0
+    for seed in range(2):
+        noisy = oracle_decoder_step(NoisyOracle(oracle, 1e-6, seed), cfg, full_specs, full_host, ids, pos, copy.deepcopy(ks), copy.deepcopy(vs))
+        envelope = max(envelope, float(np.abs(noisy - want).max()))
     err = float(np.abs(full_logits - want).max())
     local_best = np.stack([p[0].max(axis=1) for p in parts]), np.stack([p[2].astype(np.int64) for p in parts])
     from tensorlisp_b200.programs import combine_argmax
@@ -329,6 +338,7 @@ def tp_parity(world: int, rank: int, local_rank: int, dist, batch: int = 8) -> d
                      % (B, ctx_before.tolist()),
             "tp": world, "allreduce": path, "checked_against": "CPU oracle on the unsharded weights",
             "logits_max_abs_err": err, "logits_max_rel_err": err / float(np.abs(want).max()),
+            "oracle_noise_envelope_1e-6": envelope, "within_envelope": bool(err <= max(1e-2, 1.5 * envelope)),
             "top1_equal": int((tok == want.argmax(axis=1)).sum()), "rows": B,
             "smallest_top1_margin_of_the_oracle": float((top2[:, 1] - top2[:, 0]).min()),
             "ranks_hold_identical_final_norm": bool(all(np.array_equal(p[1], parts[0][1]) for p in parts)),

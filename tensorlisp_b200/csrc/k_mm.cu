@@ -29,7 +29,7 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 // Bounded wait: gives up after `limit` polls and returns false.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t limit = (1u << 22)) {
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t limit = (1u << 19)) {   // about two seconds: a probe of an incomplete phase takes about 4 us
     const uint32_t a = smem_u32(bar);
     for (uint32_t i = 0; i < limit; i++) {
         uint32_t ok;

@@ -16,7 +16,7 @@ constexpr int EPI_WARP0 = 1, DEQ_WARP0 = 9, MMA_WARP = 25;
 constexpr int RAW_BYTES = ROWS * 144;
 constexpr uint32_t TMEM_COLS = 512;           // all of it: accumulators first, the ring of A quarters behind them
 constexpr int AMIN_BYTES = ROWS * 16 * 2;
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr uint32_t WAIT_LIMIT = 1u << 19;   // a probe that finds the phase incomplete takes about 4 us: two seconds in all
 
 __device__ __forceinline__ uint32_t su32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

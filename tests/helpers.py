@@ -40,6 +40,21 @@ class Model:
         self.native.close()
 
 
+class NoisyOracle:
+    """The oracle with its mul_mat outputs perturbed by `eps` relative noise: measures how far the
+    reference's own arithmetic moves under a summation-order-sized perturbation."""
+
+    def __init__(self, oracle, eps, seed):
+        self.o, self.eps, self.r = oracle, eps, np.random.default_rng(seed)
+
+    def __getattr__(self, name):
+        return getattr(self.o, name)
+
+    def mul_mat(self, *a, **k):
+        y = self.o.mul_mat(*a, **k)
+        return (y * (1 + self.eps * self.r.standard_normal(y.shape))).astype(np.float32)
+
+
 # ------------------------------------------------------------------ oracle-side decoder step
 def make_decoder_weights(oracle, specs, seed=0):
     """N(0, 0.02) f32 matrices quantized with the oracle (bit-exact with the reference), norm weights N(1, 0.1)."""

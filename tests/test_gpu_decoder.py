@@ -18,7 +18,7 @@ import copy
 import numpy as np
 import pytest
 
-from helpers import Model, close, make_decoder_weights, oracle_decoder_step
+from helpers import Model, NoisyOracle, close, make_decoder_weights, oracle_decoder_step
 from oracle.bindings import Q4_K
 from tensorlisp_b200 import graph as G
 from tensorlisp_b200.programs import DecoderConfig, decoder_step, swiglu_ffn
@@ -92,21 +92,6 @@ def test_ffn_block_config2_prefill_512(oracle):
     rows = rng.choice(d, 48, replace=False)
     close(got[:, rows], oracle.mul_mat(Q4_K, mats[2][rows], f, got_act), 1e-3)
     m.close()
-
-
-class NoisyOracle:
-    """The oracle with its mul_mat outputs perturbed by `eps` relative noise: measures how far the
-    reference's own arithmetic moves under a summation-order-sized perturbation."""
-
-    def __init__(self, oracle, eps, seed):
-        self.o, self.eps, self.r = oracle, eps, np.random.default_rng(seed)
-
-    def __getattr__(self, name):
-        return getattr(self.o, name)
-
-    def mul_mat(self, *a, **k):
-        y = self.o.mul_mat(*a, **k)
-        return (y * (1 + self.eps * self.r.standard_normal(y.shape))).astype(np.float32)
 
 
 def test_decode_step(oracle):

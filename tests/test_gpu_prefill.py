@@ -11,7 +11,7 @@ of every prompt's last token.
 import numpy as np
 import pytest
 
-from helpers import Model, close, make_decoder_weights
+from helpers import NoisyOracle, Model, close, make_decoder_weights
 from tensorlisp_b200.graph import Q8_0
 from tensorlisp_b200.programs import DecoderConfig, prefill_step
 
@@ -58,18 +58,6 @@ def oracle_prefill(oracle, cfg, specs, weights, ids, pos, n_seqs, n_tokens):
     last = np.arange(n_seqs) * n_tokens + n_tokens - 1
     x = oracle.rms_norm(np.ascontiguousarray(x[last]), cfg.eps, W["output_norm"][1])
     return lin("output", x)
-
-
-class NoisyOracle:
-    def __init__(self, oracle, eps, seed):
-        self.o, self.eps, self.r = oracle, eps, np.random.default_rng(seed)
-
-    def __getattr__(self, name):
-        return getattr(self.o, name)
-
-    def mul_mat(self, *a, **k):
-        y = self.o.mul_mat(*a, **k)
-        return (y * (1 + self.eps * self.r.standard_normal(y.shape))).astype(np.float32)
 
 
 @pytest.mark.parametrize("n_seqs,n_tokens", [(2, 80), (3, 37)])
