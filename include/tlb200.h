@@ -131,6 +131,13 @@ void       tlb_buffer_free(tlb_buffer *b);
 tlb_status tlb_program_compile(tlb_device *dev, const tlb_graph *graph, const tlb_leaves *leaves,
                                tlb_program **prog, char *err, size_t errlen);
 void       tlb_program_free(tlb_program *prog);
+/* plan::plan alone (crates/kernels/src/plan.rs:56-189), without a device and without lowering, for tests of its
+ * invariants (live tensors never share bytes, a node never writes over a source it still reads, views keep their
+ * root alive; the reference's own checks are plan.rs:191-315). node_scratch (n_nodes entries, may be NULL) is the
+ * scratch each node asks for. Outputs: arena and io sizes; per tensor the buffer it resolves to (0 weights, 1 state,
+ * 2 io, 3 arena) and its byte offset there; per node the arena offset of its scratch block, -1 for none. */
+tlb_status tlb_plan_only(const tlb_graph *graph, const tlb_leaves *leaves, const uint64_t *node_scratch, uint64_t *arena_size,
+                         uint64_t *io_size, uint8_t *tensor_buffer, uint64_t *tensor_offset, int64_t *scratch_offset);
 /* Program::set_input (exec.rs:91-98): n must equal the input tensor's byte size, else
  * "input i takes N bytes, got M". Blocking host-to-device copy into the program's io buffer. */
 tlb_status tlb_program_set_input(tlb_program *prog, uint32_t i, const void *bytes, uint64_t n);

@@ -84,6 +84,7 @@ SYMBOLS = {
     "tlb_buffer_free": (None, [_P]),
     "tlb_program_compile": (C.c_int, [_P, C.POINTER(tlb_graph), C.POINTER(tlb_leaves), C.POINTER(_P), C.c_char_p, C.c_size_t]),
     "tlb_program_free": (None, [_P]),
+    "tlb_plan_only": (C.c_int, [C.POINTER(tlb_graph), C.POINTER(tlb_leaves), _P, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), _P, _P, _P]),
     "tlb_program_set_input": (C.c_int, [_P, C.c_uint32, _P, C.c_uint64]),
     "tlb_program_run": (C.c_int, [_P, C.POINTER(_P), C.c_uint32, _P]),
     "tlb_program_enqueue": (C.c_int, [_P, C.POINTER(_P), C.c_uint32, _P]),

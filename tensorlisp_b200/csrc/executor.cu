@@ -393,6 +393,60 @@ void tlb_buffer_free(tlb_buffer *b) {
     delete b;
 }
 
+// Copies and validates the IR of a caller (tensor ids in range, views of roots only, known types, leaves present).
+// Returns an empty string, or what is wrong.
+static std::string import_graph(const tlb_graph *graph, const tlb_leaves *leaves, Graph &g, Leaves &lv) {
+    g.tensors.resize(graph->n_tensors);
+    const int32_t nt = (int32_t)graph->n_tensors;
+    for (int32_t i = 0; i < nt; i++) {
+        const tlb_tensor &s = graph->tensors[i];
+        Tensor &t = g.tensors[i];
+        t.ty = s.ty;
+        for (int k = 0; k < 4; k++) {
+            t.ne[k] = s.ne[k];
+            t.nb[k] = s.nb[k];
+            if (s.ne[k] < 0) return "tensor " + std::to_string(i) + " has a negative dimension";
+        }
+        t.op.assign(s.op, strnlen(s.op, sizeof(s.op)));
+        std::memcpy(t.op_params, s.op_params, sizeof(t.op_params));
+        for (int k = 0; k < 10; k++) {
+            t.src[k] = s.src[k];
+            if (s.src[k] >= nt || s.src[k] < -1) return "tensor " + std::to_string(i) + " has a source out of range";
+        }
+        t.view_src = s.view_src;
+        if (s.view_src >= nt || s.view_src < -1) return "tensor " + std::to_string(i) + " has a view source out of range";
+        t.view_offs = s.view_offs;
+        t.storage_kind = s.storage_kind;
+        t.storage_index = s.storage_index;
+        t.name.assign(s.name, strnlen(s.name, sizeof(s.name)));
+        if (!type_traits(t.ty)) return "tensor `" + t.name + "` has unknown ggml type " + std::to_string(t.ty);
+        if (t.storage_kind > TEMP) return "tensor `" + t.name + "` has an unknown storage kind";
+    }
+    for (int32_t i = 0; i < nt; i++) {
+        const Tensor &t = g.tensors[i];
+        if (t.view_src >= 0 && g.tensors[t.view_src].view_src >= 0) return "tensor `" + t.name + "`: view_src must be a root";
+        if (t.view_src < 0) {
+            if (t.storage_kind == WEIGHT && (!leaves || t.storage_index >= leaves->n_weights))
+                return "tensor `" + t.name + "` names weight " + std::to_string(t.storage_index) + ", which the leaves do not have";
+            if (t.storage_kind == STATE && (!leaves || t.storage_index >= leaves->n_states))
+                return "tensor `" + t.name + "` names state " + std::to_string(t.storage_index) + ", which the leaves do not have";
+        }
+    }
+    for (uint32_t i = 0; i < graph->n_nodes; i++) {
+        if (graph->nodes[i] < 0 || graph->nodes[i] >= nt) return "node id out of range";
+        g.nodes.push_back(graph->nodes[i]);
+    }
+    for (uint32_t i = 0; i < graph->n_keep; i++) {
+        if (graph->keep[i] < 0 || graph->keep[i] >= nt) return "kept tensor id out of range";
+        g.keep.push_back(graph->keep[i]);
+    }
+    if (leaves) {
+        for (uint32_t i = 0; i < leaves->n_weights; i++) lv.weights.push_back({leaves->weight_buffer[i], leaves->weight_offset[i]});
+        for (uint32_t i = 0; i < leaves->n_states; i++) lv.states.push_back(leaves->state_offset[i]);
+    }
+    return "";
+}
+
 // ------------------------------------------------------------------ programs
 static void copy_err(const std::string &m, char *err, size_t errlen) {
     if (err && errlen) snprintf(err, errlen, "%s", m.c_str());
@@ -407,57 +461,11 @@ tlb_status tlb_program_compile(tlb_device *dev, const tlb_graph *graph, const tl
     };
     if (!dev || !graph || !prog) return bad(TLB_INVALID, "tlb_program_compile: bad arguments");
     *prog = nullptr;
-    // ---- copy and validate the IR
     Graph g;
-    g.tensors.resize(graph->n_tensors);
-    const int32_t nt = (int32_t)graph->n_tensors;
-    for (int32_t i = 0; i < nt; i++) {
-        const tlb_tensor &s = graph->tensors[i];
-        Tensor &t = g.tensors[i];
-        t.ty = s.ty;
-        for (int k = 0; k < 4; k++) {
-            t.ne[k] = s.ne[k];
-            t.nb[k] = s.nb[k];
-            if (s.ne[k] < 0) return bad(TLB_INVALID, "tensor " + std::to_string(i) + " has a negative dimension");
-        }
-        t.op.assign(s.op, strnlen(s.op, sizeof(s.op)));
-        std::memcpy(t.op_params, s.op_params, sizeof(t.op_params));
-        for (int k = 0; k < 10; k++) {
-            t.src[k] = s.src[k];
-            if (s.src[k] >= nt || s.src[k] < -1) return bad(TLB_INVALID, "tensor " + std::to_string(i) + " has a source out of range");
-        }
-        t.view_src = s.view_src;
-        if (s.view_src >= nt || s.view_src < -1) return bad(TLB_INVALID, "tensor " + std::to_string(i) + " has a view source out of range");
-        t.view_offs = s.view_offs;
-        t.storage_kind = s.storage_kind;
-        t.storage_index = s.storage_index;
-        t.name.assign(s.name, strnlen(s.name, sizeof(s.name)));
-        if (!type_traits(t.ty)) return bad(TLB_INVALID, "tensor `" + t.name + "` has unknown ggml type " + std::to_string(t.ty));
-        if (t.storage_kind > TEMP) return bad(TLB_INVALID, "tensor `" + t.name + "` has an unknown storage kind");
-    }
-    for (int32_t i = 0; i < nt; i++) {
-        const Tensor &t = g.tensors[i];
-        if (t.view_src >= 0 && g.tensors[t.view_src].view_src >= 0)
-            return bad(TLB_INVALID, "tensor `" + t.name + "`: view_src must be a root");
-        if (t.view_src < 0) {
-            if (t.storage_kind == WEIGHT && (!leaves || t.storage_index >= leaves->n_weights))
-                return bad(TLB_INVALID, "tensor `" + t.name + "` names weight " + std::to_string(t.storage_index) + ", which the leaves do not have");
-            if (t.storage_kind == STATE && (!leaves || t.storage_index >= leaves->n_states))
-                return bad(TLB_INVALID, "tensor `" + t.name + "` names state " + std::to_string(t.storage_index) + ", which the leaves do not have");
-        }
-    }
-    for (uint32_t i = 0; i < graph->n_nodes; i++) {
-        if (graph->nodes[i] < 0 || graph->nodes[i] >= nt) return bad(TLB_INVALID, "node id out of range");
-        g.nodes.push_back(graph->nodes[i]);
-    }
-    for (uint32_t i = 0; i < graph->n_keep; i++) {
-        if (graph->keep[i] < 0 || graph->keep[i] >= nt) return bad(TLB_INVALID, "kept tensor id out of range");
-        g.keep.push_back(graph->keep[i]);
-    }
     Leaves lv;
-    if (leaves) {
-        for (uint32_t i = 0; i < leaves->n_weights; i++) lv.weights.push_back({leaves->weight_buffer[i], leaves->weight_offset[i]});
-        for (uint32_t i = 0; i < leaves->n_states; i++) lv.states.push_back(leaves->state_offset[i]);
+    {
+        const std::string why = import_graph(graph, leaves, g, lv);
+        if (!why.empty()) return bad(TLB_INVALID, why);
     }
 
     tlb_program *p = new tlb_program;
@@ -518,6 +526,30 @@ tlb_status tlb_program_compile(tlb_device *dev, const tlb_graph *graph, const tl
     const char *ng = getenv("TLB_NO_CUDA_GRAPH");
     p->use_graph = !(ng && ng[0] == '1');
     *prog = p;
+    return TLB_OK;
+}
+
+// The planner alone, for tests that check its invariants on graphs no kernel could run: no device, no lowering, no
+// rewrites. node_scratch[i] (may be NULL) is the scratch node i asks for. Per tensor: the buffer kind it resolves to
+// (0 weights, 1 state, 2 io, 3 arena) and its byte offset there; per node: the offset of its scratch block or -1.
+tlb_status tlb_plan_only(const tlb_graph *graph, const tlb_leaves *leaves, const uint64_t *node_scratch, uint64_t *arena_size, uint64_t *io_size,
+                         uint8_t *tensor_buffer, uint64_t *tensor_offset, int64_t *scratch_offset) {
+    if (!graph || !arena_size || !io_size || !tensor_buffer || !tensor_offset || !scratch_offset) return fail(TLB_INVALID, "tlb_plan_only: bad arguments");
+    Graph g;
+    Leaves lv;
+    const std::string why = import_graph(graph, leaves, g, lv);
+    if (!why.empty()) return fail(TLB_INVALID, why);
+    std::vector<uint64_t> want(g.tensors.size(), 0);
+    if (node_scratch)
+        for (size_t pos = 0; pos < g.nodes.size(); pos++) want[g.nodes[pos]] = node_scratch[pos];
+    const Layout L = plan(g, lv, [&](int32_t id) { return want[id]; });
+    *arena_size = L.arena_size;
+    *io_size = L.io_size;
+    for (size_t i = 0; i < g.tensors.size(); i++) {
+        tensor_buffer[i] = (uint8_t)L.place[i].buf;
+        tensor_offset[i] = L.place[i].off;
+    }
+    for (size_t pos = 0; pos < g.nodes.size(); pos++) scratch_offset[pos] = L.scratch[pos];
     return TLB_OK;
 }
 
