@@ -209,26 +209,141 @@ class GgufWriter:
                 f.write(b"\0" * ((data.nbytes + al - 1) // al * al - data.nbytes))
 
 
-def quantize_file(native, src_path: str, dst_path: str, ty: int, only=None) -> list[str]:
-    """`tl quantize`: every f32 tensor of rank 2 whose rows are a whole number of blocks of `ty` (and that
-    `only(name)` accepts, when given) is quantized ON THE GPU; everything else and all metadata are
-    copied. Returns the names that were quantized."""
+# ------------------------------------------------------------------ `tl quantize`
+VIEW_OPS = ("RESHAPE", "VIEW", "PERMUTE", "TRANSPOSE")   # uses of their result count as uses of their source
+QUANTIZABLE_USES = (("MUL_MAT", 0), ("MUL_MAT_ID", 0), ("GET_ROWS", 0), ("IM2COL", 0))   # (op, source index) that take quantized weights
+
+
+def glob_match(pattern: str, name: str) -> bool:
+    """`*` and `?` globs over the whole name (crates/tensorlisp-cli/src/common.rs:236-257)."""
+    import re
+    rx = "".join(".*" if c == "*" else "." if c == "?" else re.escape(c) for c in pattern)
+    return re.fullmatch(rx, name, flags=re.S) is not None
+
+
+def weight_uses(graphs) -> dict:
+    """Every (op, source index) that consumes each weight tensor (by name) in any of the graphs, looking through
+    view ops (crates/tensorlisp-cli/src/quantize.rs:59-80): a weight is used however any entry uses it."""
+    from . import graph as G
+
+    uses: dict[str, list] = {}
+    for g in graphs:
+        def weight_of(t: int):
+            T = g.tensors[t]
+            seen = 0
+            # the builder resolves views to their root (`view_src`); a chain of view NODES is followed through src[0]
+            while True:
+                root = g.tensors[T.view_src] if T.view_src >= 0 else T
+                if root.storage_kind == G.WEIGHT and root.op == "NONE":
+                    return root.name
+                if T.op in VIEW_OPS and T.src[0] >= 0 and seen < 64:
+                    T = g.tensors[T.src[0]]
+                    seen += 1
+                    continue
+                return None
+        for t in g.nodes:
+            T = g.tensors[t]
+            is_view = T.op in VIEW_OPS
+            for j, s in enumerate(T.src):
+                if s < 0:
+                    continue
+                w = weight_of(s)
+                if w is not None and not (is_view and j == 0):
+                    uses.setdefault(w, []).append((T.op, j))
+    return uses
+
+
+def skip_reason(t, target: int, uses, include=(), exclude=(), min_elements: int = 1024, include_1d: bool = False,
+                requantize: bool = False):
+    """Why a tensor keeps its type, or None to convert it: the rules and the wording of
+    crates/tensorlisp-cli/src/quantize.rs:148-191, in the same order."""
+    from . import graph as G
+
+    tname = lambda ty: G.TYPE_TRAITS[ty][0]
+    elements = int(np.prod(t.ne, dtype=np.int64)) if t.ne else 1
+    if t.ty == target:
+        return "already %s" % tname(target)
+    if include and not any(glob_match(g, t.name) for g in include):
+        return "not included"
+    for g in exclude:
+        if glob_match(g, t.name):
+            return "excluded by %s" % g
+    if tname(t.ty) in ("i8", "i16", "i32", "i64"):
+        return "integer tensor"
+    if uses is not None:
+        lst = uses.get(t.name)
+        if lst is None:
+            return "not used by the program"
+        for op, j in lst:
+            if (op, j) not in QUANTIZABLE_USES:
+                return "used by %s (source %d); only matmul/get-rows weights are quantized" % (op, j)
+    if G.TYPE_TRAITS[t.ty][1] > 1 and not requantize:
+        return "already quantized (use --requantize)"
+    if len(t.ne) < 2 and not include_1d:
+        return "1-D (use --include-1d)"
+    if elements < min_elements:
+        return "fewer than %d elements" % min_elements
+    row = t.ne[0] if t.ne else 1
+    blck = G.TYPE_TRAITS[target][1]
+    if row % blck != 0:
+        return "row length %d is not a multiple of the %s block size %d" % (row, tname(target), blck)
+    return None
+
+
+def _to_f32(native, t, raw: np.ndarray) -> np.ndarray:
+    """The tensor's values as f32 rows (DType::to_f32): plain types on the host, block-quantized ones through a
+    one-node program (CPY with a dequantizing read) on the GPU."""
+    from . import graph as G
+    from .native import Native, NativeProgram
+
+    rows = int(np.prod(t.ne[1:], dtype=np.int64)) if len(t.ne) > 1 else 1
+    if t.ty == G.F32:
+        return raw.view(np.float32).reshape(rows, t.ne[0])
+    if t.ty == G.F16:
+        return raw.view(np.float16).astype(np.float32).reshape(rows, t.ne[0])
+    if t.ty == G.BF16:
+        return (raw.view(np.uint16).astype(np.uint32) << 16).view(np.float32).reshape(rows, t.ne[0])
+    g = G.Graph()
+    w = g.weight(t.ty, [t.ne[0], rows], t.name)
+    y = g.output(g.cast(w, G.F32, "values"))
+    n = Native.load([raw])
+    prog = NativeProgram.compile(n, g)
+    prog.run()
+    out = prog.read(y).reshape(rows, t.ne[0]).copy()
+    prog.free()
+    n.close()
+    return out
+
+
+def quantize_file(native, src_path: str, dst_path: str, ty: int, graphs=None, include=(), exclude=(), min_elements: int = 1024,
+                  include_1d: bool = False, requantize: bool = False) -> list[dict]:
+    """`tl quantize` (crates/tensorlisp-cli/src/quantize.rs:193-267) with the rows quantized ON THE GPU. With `graphs`
+    (the program's entries as Graph objects; the reference builds them from the Scheme program stored in the file)
+    only weights whose every use is source 0 of MUL_MAT / MUL_MAT_ID / GET_ROWS / IM2COL are converted, seen through
+    view ops; without, tensors are chosen by name, rank and size only (`--no-graph`). Everything else and all metadata
+    are copied. Returns the report: one dict per tensor (name, from, to, shape, bytes_before, bytes_after, kept_because)."""
     from . import graph as G
     from .native import quantize_rows
 
+    if src_path == dst_path:
+        raise GgufError("output must differ from input")
     src = GgufFile(src_path)
     out = GgufWriter(src.alignment)
     out.copy_metadata(src)
-    done = []
-    blck = G.TYPE_TRAITS[ty][1]
+    uses = weight_uses(graphs) if graphs is not None else None
+    report = []
     for i, t in enumerate(src.tensors):
         raw = src.tensor_bytes(i)
-        if t.ty == G.F32 and len(t.ne) == 2 and t.ne[0] % blck == 0 and (only is None or only(t.name)):
-            w = raw.view(np.float32).reshape(t.ne[1], t.ne[0])
-            out.add_tensor(t.name, ty, t.ne, quantize_rows(native, ty, w))
-            done.append(t.name)
+        reason = skip_reason(t, ty, uses, include, exclude, min_elements, include_1d, requantize)
+        if reason is None:
+            data = quantize_rows(native, ty, np.ascontiguousarray(_to_f32(native, t, raw)))
+            out.add_tensor(t.name, ty, t.ne, data)
+            after = int(data.nbytes)
         else:
             out.add_tensor(t.name, t.ty, t.ne, raw)
+            after = int(t.nbytes)
+        report.append({"name": t.name, "from": G.TYPE_TRAITS[t.ty][0], "to": G.TYPE_TRAITS[ty if reason is None else t.ty][0],
+                       "shape": list(t.ne), "bytes_before": int(t.nbytes), "bytes_after": after, "kept_because": reason})
     out.write(dst_path)
     src.close()
-    return done
+    return report

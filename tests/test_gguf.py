@@ -73,3 +73,40 @@ def test_the_reference_reader_sees_the_same_file(tmp_path, oracle, ref):
     tl = [l for l in lines if l.startswith("tensor ")]
     assert tl == ["tensor %s type %d offset %d size %d" % (t.name, t.ty, t.offset, t.nbytes) for t in f.tensors]
     f.close()
+
+
+def test_quantize_selection_rules():
+    """Which tensors `tl quantize` converts (crates/tensorlisp-cli/src/quantize.rs:54-80,148-191): host logic only."""
+    from types import SimpleNamespace as T
+    from tensorlisp_b200.gguf import glob_match, skip_reason, weight_uses
+    g = G.Graph()
+    w = g.weight(G.F32, [256, 8], "w")
+    b = g.weight(G.F32, [8], "b")
+    e = g.weight(G.F32, [256, 100], "e")
+    both = g.weight(G.F32, [256, 8], "both")
+    x = g.get_rows(e, g.input(G.I32, [2], "ids"))
+    y = g.add(g.mul_mat(g.permute(g.permute(w, 1, 0, 2, 3), 1, 0, 2, 3), x), b)      # w behind two view ops
+    y = g.add(y, g.mul_mat(both, x))
+    z = g.mul_mat(x, both)            # `both` also as source 1 of a MUL_MAT
+    g.output(y)
+    g.output(z)
+    uses = weight_uses([g])
+    assert uses["w"] == [("MUL_MAT", 0)] and uses["e"] == [("GET_ROWS", 0)] and uses["b"] == [("ADD", 1)]
+    assert sorted(uses["both"]) == [("MUL_MAT", 0), ("MUL_MAT", 1)]
+    info = lambda name, ty, ne: T(name=name, ty=ty, ne=ne, nbytes=0)
+    assert skip_reason(info("w", G.F32, [256, 8]), G.Q8_0, uses) is None
+    assert skip_reason(info("e", G.F32, [256, 100]), G.Q8_0, uses) is None
+    assert skip_reason(info("both", G.F32, [256, 8]), G.Q8_0, uses).startswith("used by MUL_MAT (source 1)")
+    assert skip_reason(info("b", G.F32, [8]), G.Q8_0, uses).startswith("used by ADD (source 1)")
+    assert skip_reason(info("gone", G.F32, [256, 8]), G.Q8_0, uses) == "not used by the program"
+    assert skip_reason(info("w", G.Q8_0, [256, 8]), G.Q8_0, uses) == "already q8_0"
+    assert skip_reason(info("w", G.Q4_0, [256, 8]), G.Q8_0, uses) == "already quantized (use --requantize)"
+    assert skip_reason(info("w", G.Q4_0, [256, 8]), G.Q8_0, uses, requantize=True) is None
+    assert skip_reason(info("w", G.F32, [256, 8]), G.Q8_0, uses, include=["blk.*"]) == "not included"
+    assert skip_reason(info("w", G.F32, [256, 8]), G.Q8_0, uses, exclude=["?"]) == "excluded by ?"
+    assert skip_reason(info("w", G.I32, [256, 8]), G.Q8_0, None) == "integer tensor"
+    assert skip_reason(info("w", G.F32, [256, 2]), G.Q8_0, None) == "fewer than 1024 elements"
+    assert skip_reason(info("w", G.F32, [4096]), G.Q8_0, None) == "1-D (use --include-1d)"
+    assert skip_reason(info("w", G.F32, [4096]), G.Q8_0, None, include_1d=True) is None
+    assert skip_reason(info("w", G.F32, [100, 50]), G.Q4_K, None) == "row length 100 is not a multiple of the q4_K block size 256"
+    assert glob_match("blk.*.attn_?", "blk.12.attn_q") and not glob_match("blk.*", "output") and glob_match("*", "")

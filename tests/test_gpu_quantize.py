@@ -63,25 +63,65 @@ def test_empty_and_bad_rows(native):
 
 
 def test_quantize_file_like_tl_quantize(native, oracle, tmp_path):
-    """`tl quantize` on the GPU: rank-2 f32 tensors with whole blocks per row become Q4_K, bit-exact with
-    the oracle; the 1-D norm, the ragged matrix, the program and the asset are carried over."""
+    """`tl quantize` on the GPU: the weights the program feeds into MUL_MAT / GET_ROWS (seen through views) become Q4_K,
+    bit-exact with the oracle; a matrix the graph also ADDs, the 1-D norm, the ragged matrix, the program and the
+    asset are carried over, each with the reference's reason (crates/tensorlisp-cli/src/quantize.rs:148-191). An
+    already quantized tensor is converted only with `requantize`, from its dequantized values."""
     from tensorlisp_b200 import graph as G
     from tensorlisp_b200.gguf import GgufFile, GgufWriter, quantize_file
     rng = np.random.default_rng(8)
     w = (rng.standard_normal((40, 1024)) * 0.02).astype(np.float32)
+    emb = (rng.standard_normal((64, 1024)) * 0.02).astype(np.float32)
+    bias_like = rng.standard_normal((40, 1024)).astype(np.float32)
     ragged = rng.standard_normal((4, 100)).astype(np.float32)
+    w8 = oracle.quantize(G.Q8_0, w)
     src, dst = str(tmp_path / "f32.gguf"), str(tmp_path / "q4k.gguf")
     out = GgufWriter()
     out.set_program("(define (f x) x)")
     out.set_asset("a.bin", b"abc")
     out.add_tensor("norm", G.F32, [1024], np.ones(1024, np.float32))
     out.add_tensor("W", G.F32, [1024, 40], w)
+    out.add_tensor("emb", G.F32, [1024, 64], emb)
+    out.add_tensor("added", G.F32, [1024, 40], bias_like)
     out.add_tensor("ragged", G.F32, [100, 4], ragged)
+    out.add_tensor("W8", G.Q8_0, [1024, 40], w8)
+    out.add_tensor("unused", G.F32, [1024, 40], w)
     out.write(src)
-    assert quantize_file(native, src, dst, G.Q4_K) == ["W"]
+    # the program: y = W . norm(emb[ids]) + W8 . h, with `added` used by an ADD as well as by a MUL_MAT
+    g = G.Graph()
+    tn = g.weight(G.F32, [1024], "norm")
+    tw = g.weight(G.F32, [1024, 40], "W")
+    te = g.weight(G.F32, [1024, 64], "emb")
+    ta = g.weight(G.F32, [1024, 40], "added")
+    t8 = g.weight(G.Q8_0, [1024, 40], "W8")
+    ids = g.input(G.I32, [3], "ids")
+    h = g.mul(g.rms_norm(g.get_rows(te, ids), 1e-5), tn)
+    y = g.add(g.mul_mat(g.reshape(tw, [1024, 40]), h), g.mul_mat(t8, h))       # W is seen through a view op
+    y = g.add(y, g.mul_mat(ta, h))
+    g.output(g.add(g.sum_rows(ta), g.sum_rows(ta)))
+    g.output(y)
+    rep = {r["name"]: r for r in quantize_file(native, src, dst, G.Q4_K, graphs=[g])}
+    assert rep["W"]["kept_because"] is None and rep["emb"]["kept_because"] is None
+    assert rep["norm"]["kept_because"] == "used by MUL (source 1); only matmul/get-rows weights are quantized"
+    assert rep["added"]["kept_because"] == "used by SUM_ROWS (source 0); only matmul/get-rows weights are quantized"
+    assert rep["ragged"]["kept_because"] == "not used by the program"
+    assert rep["unused"]["kept_because"] == "not used by the program"
+    assert rep["W8"]["kept_because"] == "already quantized (use --requantize)"
     f = GgufFile(dst)
     assert f.program() == "(define (f x) x)" and f.assets() == {"a.bin": b"abc"}
-    assert [(t.name, t.ty) for t in f.tensors] == [("norm", G.F32), ("W", G.Q4_K), ("ragged", G.F32)]
+    assert [(t.name, t.ty) for t in f.tensors] == [("norm", G.F32), ("W", G.Q4_K), ("emb", G.Q4_K), ("added", G.F32), ("ragged", G.F32),
+                                                   ("W8", G.Q8_0), ("unused", G.F32)]
     assert np.array_equal(f.tensor_bytes(1), oracle.quantize(G.Q4_K, w).reshape(-1))
-    assert np.array_equal(f.tensor_bytes(2).view(np.float32).reshape(4, 100), ragged)
+    assert np.array_equal(f.tensor_bytes(4).view(np.float32).reshape(4, 100), ragged)
+    f.close()
+    # without a graph: by name, rank and size only
+    rep = {r["name"]: r for r in quantize_file(native, src, dst, G.Q4_K, exclude=["un*"], requantize=True)}
+    assert rep["norm"]["kept_because"] == "1-D (use --include-1d)"
+    assert rep["ragged"]["kept_because"] == "fewer than 1024 elements"
+    assert rep["unused"]["kept_because"] == "excluded by un*"
+    assert rep["added"]["kept_because"] is None and rep["W8"]["kept_because"] is None
+    f = GgufFile(dst)
+    i8 = [t.name for t in f.tensors].index("W8")
+    assert f.tensors[i8].ty == G.Q4_K
+    assert np.array_equal(f.tensor_bytes(i8), oracle.quantize(G.Q4_K, oracle.dequantize(G.Q8_0, w8, 1024)).reshape(-1))
     f.close()
