@@ -110,6 +110,13 @@ tlb_status tlb_weights_create(tlb_device *dev, uint64_t total_bytes, tlb_buffer 
 tlb_status tlb_state_create(tlb_device *dev, uint64_t bytes, tlb_buffer **s);
 tlb_status tlb_state_zero(tlb_buffer *s);
 tlb_status tlb_state_fork(tlb_buffer *src, tlb_buffer **copy);
+/* copy_blocks (crates/kernels/src/cuda/paged_attn.rs:423-448, shaders/copy_blocks.cu:9-27): for every pair (src, dst)
+ * of `pairs` (n_pairs x 2 block numbers, host memory) page src is copied to page dst in the K pool and in the V pool
+ * of a state block -- the copy a forked sequence needs for the partly filled page it cannot share. The pools start at
+ * the given byte offsets of the block and hold `pool_blocks` pages of `bytes_per_block` bytes (all of one block's
+ * KV heads). Bounds-checked; a page that is written may not be read or written by another pair. Waits. */
+tlb_status tlb_state_copy_blocks(tlb_buffer *state, uint64_t k_pool_offset, uint64_t v_pool_offset, uint64_t pool_blocks,
+                                 uint64_t bytes_per_block, const int64_t *pairs, uint32_t n_pairs);
 /* Buffer::write_at / read_range (cuda/mod.rs:79-120): bounds-checked blocking copies. */
 tlb_status tlb_buffer_write(tlb_buffer *b, uint64_t offset, const void *host, uint64_t n);
 tlb_status tlb_buffer_read(tlb_buffer *b, uint64_t offset, void *host, uint64_t n);
@@ -141,6 +148,11 @@ tlb_status tlb_plan_only(const tlb_graph *graph, const tlb_leaves *leaves, const
 /* Program::set_input (exec.rs:91-98): n must equal the input tensor's byte size, else
  * "input i takes N bytes, got M". Blocking host-to-device copy into the program's io buffer. */
 tlb_status tlb_program_set_input(tlb_program *prog, uint32_t i, const void *bytes, uint64_t n);
+/* Device-side feedback for loops: copies the bytes of a KEPT tensor of the arena into graph input `input` (same byte
+ * size), on the device stream, without waiting -- the next run sees them. A decode loop feeds the ARGMAX of a step
+ * to the token-id input of the next one this way, so the ids never visit the host (the reference's graph-updatable
+ * inputs, crates/kernels/src/cuda/backend.rs:57-260, serve the same loop). */
+tlb_status tlb_program_feed_input(tlb_program *prog, uint32_t input, uint32_t tensor_id);
 /* Program::run (exec.rs:186-225): enqueues every launch and waits. `weights` are the buffers the
  * leaves' weight_buffer indices refer to; `state` may be NULL when the graph has no state. */
 tlb_status tlb_program_run(tlb_program *prog, tlb_buffer *const *weights, uint32_t n_weights, tlb_buffer *state);

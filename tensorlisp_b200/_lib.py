@@ -76,6 +76,7 @@ SYMBOLS = {
     "tlb_state_create": (C.c_int, [_P, C.c_uint64, C.POINTER(_P)]),
     "tlb_state_zero": (C.c_int, [_P]),
     "tlb_state_fork": (C.c_int, [_P, C.POINTER(_P)]),
+    "tlb_state_copy_blocks": (C.c_int, [_P, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, _P, C.c_uint32]),
     "tlb_buffer_write": (C.c_int, [_P, C.c_uint64, _P, C.c_uint64]),
     "tlb_buffer_read": (C.c_int, [_P, C.c_uint64, _P, C.c_uint64]),
     "tlb_buffer_size": (C.c_uint64, [_P]),
@@ -86,6 +87,7 @@ SYMBOLS = {
     "tlb_program_free": (None, [_P]),
     "tlb_plan_only": (C.c_int, [C.POINTER(tlb_graph), C.POINTER(tlb_leaves), _P, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), _P, _P, _P]),
     "tlb_program_set_input": (C.c_int, [_P, C.c_uint32, _P, C.c_uint64]),
+    "tlb_program_feed_input": (C.c_int, [_P, C.c_uint32, C.c_uint32]),
     "tlb_program_run": (C.c_int, [_P, C.POINTER(_P), C.c_uint32, _P]),
     "tlb_program_enqueue": (C.c_int, [_P, C.POINTER(_P), C.c_uint32, _P]),
     "tlb_program_read": (C.c_int, [_P, C.c_uint32, C.c_uint64, _P]),

@@ -351,6 +351,41 @@ tlb_status tlb_state_fork(tlb_buffer *src, tlb_buffer **copy) {
     return TLB_OK;
 }
 
+// copy_blocks of the reference (crates/kernels/src/cuda/paged_attn.rs:423-448): pages copied inside the K and V pools of
+// one state block.
+tlb_status tlb_state_copy_blocks(tlb_buffer *state, uint64_t k_pool_offset, uint64_t v_pool_offset, uint64_t pool_blocks, uint64_t bytes_per_block,
+                                 const int64_t *pairs, uint32_t n_pairs) {
+    if (!state || (!pairs && n_pairs)) return fail(TLB_INVALID, "tlb_state_copy_blocks: bad arguments");
+    if (bytes_per_block == 0 || bytes_per_block % 16 || k_pool_offset % 16 || v_pool_offset % 16)
+        return fail(TLB_INVALID, "tlb_state_copy_blocks: pools and pages must be multiples of 16 bytes");
+    const uint64_t pool_bytes = pool_blocks * bytes_per_block;
+    if (k_pool_offset > state->size || pool_bytes > state->size - k_pool_offset || v_pool_offset > state->size || pool_bytes > state->size - v_pool_offset)
+        return fail(TLB_INVALID, "tlb_state_copy_blocks: a pool of " + std::to_string(pool_bytes) + " bytes does not fit the state block of " + std::to_string(state->size));
+    for (uint32_t i = 0; i < 2 * n_pairs; i++)
+        if (pairs[i] < 0 || (uint64_t)pairs[i] >= pool_blocks) return fail(TLB_INVALID, "tlb_state_copy_blocks: block " + std::to_string(pairs[i]) + " is outside a pool of " + std::to_string(pool_blocks) + " blocks");
+    for (uint32_t i = 0; i < n_pairs; i++)
+        for (uint32_t j = 0; j < n_pairs; j++)
+            if (pairs[2 * i + 1] == pairs[2 * j] || (i != j && pairs[2 * i + 1] == pairs[2 * j + 1]))
+                return fail(TLB_INVALID, "tlb_state_copy_blocks: block " + std::to_string(pairs[2 * i + 1]) + " is written and also read or written by another pair");
+    if (n_pairs == 0) return TLB_OK;
+    cudaSetDevice(state->dev->ordinal);
+    int64_t *map = nullptr;
+    if (cudaMalloc(&map, (size_t)n_pairs * 16) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(TLB_ALLOC, "buffer allocation of " + std::to_string((size_t)n_pairs * 16) + " bytes failed");
+    }
+    cudaError_t e = cudaMemcpyAsync(map, pairs, (size_t)n_pairs * 16, cudaMemcpyHostToDevice, state->dev->stream);
+    if (e == cudaSuccess)
+        e = launch_copy_blocks((char *)state->ptr + k_pool_offset, (char *)state->ptr + v_pool_offset, map, (int)n_pairs, (int64_t)bytes_per_block, state->dev->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(state->dev->stream);
+    cudaFree(map);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(TLB_EXECUTION, "copying cache pages failed: " + cuda_msg(e));
+    }
+    return TLB_OK;
+}
+
 tlb_status tlb_buffer_write(tlb_buffer *b, uint64_t offset, const void *host, uint64_t n) {
     if (!b || (!host && n)) return fail(TLB_INVALID, "tlb_buffer_write: bad arguments");
     if (offset > b->size || n > b->size - offset)
@@ -573,6 +608,26 @@ tlb_status tlb_program_set_input(tlb_program *prog, uint32_t i, const void *byte
     cudaSetDevice(prog->dev->ordinal);
     TLB_TRY_CUDA(cudaMemcpyAsync((char *)prog->io + in.first, bytes, n, cudaMemcpyHostToDevice, prog->dev->stream), TLB_EXECUTION);
     TLB_TRY_CUDA(cudaStreamSynchronize(prog->dev->stream), TLB_EXECUTION);
+    return TLB_OK;
+}
+
+// Device-side feedback: the bytes of a kept arena tensor become the next run's input, without the host (a decode loop
+// feeds the ARGMAX of one step to the GET_ROWS of the next). Enqueued on the device stream, not waited for.
+tlb_status tlb_program_feed_input(tlb_program *prog, uint32_t input, uint32_t tensor_id) {
+    if (!prog) return fail(TLB_INVALID, "null program");
+    if (input >= prog->layout.inputs.size()) return fail(TLB_INVALID, "no graph input " + std::to_string(input));
+    if (tensor_id >= prog->n_user_tensors) return fail(TLB_INVALID, "no tensor " + std::to_string(tensor_id));
+    const Place pl = prog->layout.place[tensor_id];
+    const auto in = prog->layout.inputs[input];
+    const uint64_t n = prog->graph.tensors[tensor_id].nbytes();
+    if (pl.buf != BUF_ARENA) return fail(TLB_INVALID, "tensor " + std::to_string(tensor_id) + " does not live in the arena");
+    if (n != in.second) return fail(TLB_INVALID, "input " + std::to_string(input) + " takes " + std::to_string(in.second) + " bytes, got " + std::to_string(n));
+    bool kept = false;
+    for (int32_t k : prog->graph.keep) kept = kept || (uint32_t)k == tensor_id;
+    if (!kept) return fail(TLB_INVALID, "tensor " + std::to_string(tensor_id) + " is not kept: its bytes may be reused before the run ends");
+    if (n == 0) return TLB_OK;
+    cudaSetDevice(prog->dev->ordinal);
+    TLB_TRY_CUDA(cudaMemcpyAsync((char *)prog->io + in.first, (char *)prog->arena + pl.off, n, cudaMemcpyDeviceToDevice, prog->dev->stream), TLB_EXECUTION);
     return TLB_OK;
 }
 

@@ -439,6 +439,21 @@ cudaError_t launch_paged_gather(int seqs, int kv_heads, int hs, int block_size, 
     return cudaGetLastError();
 }
 
+// Copies whole pages inside a K pool and a V pool: pair i copies block map[2i] to block map[2i+1] in both (what a forked
+// sequence needs for the one partly filled page it may not share). One CTA per pair, 16-byte accesses.
+__global__ void __launch_bounds__(256) k_copy_blocks(uint4 *kpool, uint4 *vpool, const int64_t *__restrict__ map, int64_t vec_per_block) {
+    const int64_t src = map[2 * blockIdx.x] * vec_per_block, dst = map[2 * blockIdx.x + 1] * vec_per_block;
+    for (int64_t i = threadIdx.x; i < vec_per_block; i += blockDim.x) {
+        kpool[dst + i] = kpool[src + i];
+        vpool[dst + i] = vpool[src + i];
+    }
+}
+cudaError_t launch_copy_blocks(void *kpool, void *vpool, const int64_t *map_dev, int n_pairs, int64_t bytes_per_block, cudaStream_t st) {
+    if (n_pairs == 0) return cudaSuccess;
+    k_copy_blocks<<<n_pairs, 256, 0, st>>>((uint4 *)kpool, (uint4 *)vpool, map_dev, bytes_per_block / 16);
+    return cudaGetLastError();
+}
+
 }  // namespace tlb
 
 // ---------------------------------------------------------------- paged attention without any allocation

@@ -177,6 +177,7 @@ cudaError_t launch_paged_attention(const PagedGeom &g, const void *q, const void
 cudaError_t launch_cache_write(int tokens, int kv_heads, int hs, int block_size, const void *key, const void *value,
                                void *kpool, void *vpool, const int64_t *slots, cudaStream_t st);
 // paged pool -> dense f16 [ctx, kv_heads, hs] per sequence, concatenated in sequence order
+cudaError_t launch_copy_blocks(void *kpool, void *vpool, const int64_t *map_dev, int n_pairs, int64_t bytes_per_block, cudaStream_t st);
 cudaError_t launch_paged_gather(int seqs, int kv_heads, int hs, int block_size, int max_blocks, const void *pool,
                                 const int32_t *tables, const int32_t *lens, const int64_t *seq_offsets, void *out,
                                 int max_ctx, cudaStream_t st);

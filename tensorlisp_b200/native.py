@@ -49,6 +49,11 @@ class StateBlock:
         check(_lib.lib().tlb_buffer_read(self.h, offset, out.ctypes.data_as(C.c_void_p), nbytes))
         return out
 
+    def copy_blocks(self, k_pool_offset: int, v_pool_offset: int, pool_blocks: int, bytes_per_block: int, pairs) -> None:
+        """copy_blocks (cuda/paged_attn.rs:434-448): page src -> page dst for every (src, dst), in the K and the V pool."""
+        m = np.ascontiguousarray(pairs, np.int64).reshape(-1, 2)
+        check(_lib.lib().tlb_state_copy_blocks(self.h, k_pool_offset, v_pool_offset, pool_blocks, bytes_per_block, m.ctypes.data_as(C.c_void_p), len(m)))
+
     def copy_device(self, offset: int, device_ptr: int, nbytes: int) -> None:
         """Device-to-device copy into the buffer (for data that is already in HBM)."""
         check(_lib.lib().tlb_buffer_copy_device(self.h, offset, C.c_void_p(device_ptr), nbytes))
@@ -204,6 +209,10 @@ class NativeProgram:
         w = self.native.weights
         arr = (C.c_void_p * 1)(w.h if w else None)
         return arr, (1 if w else 0), (st.h if st else None)
+
+    def feed_input(self, i: int, tensor: int) -> None:
+        """The bytes of a kept arena tensor become input i of the next run (device-side copy, enqueued)."""
+        check(self.native.L.tlb_program_feed_input(self.h, i, tensor))
 
     def run(self, state: StateBlock | None = None) -> None:
         arr, n, st = self._buffers(state)

@@ -247,3 +247,63 @@ def prefill_step(cfg: DecoderConfig, n_seqs: int, n_tokens: int, tp: int = 1, wr
     if write_cache:
         names["slots"] = 4
     return DecoderGraph(g, specs, [pool_elems * 2] * (2 * len(pools)), names, logits, -1, cfg, tp)
+
+
+class DecodeLoop:
+    """The host side of a batched greedy decode loop over the paged pool: the loop of ports/gemma4/concurrency.ss:120-158
+    (the reference's callers in crates/tensorlisp/tests/native_concurrency.rs:100-143 drive it step by step). One compiled
+    decode-step program is replayed; per step the host uploads the three small arrays that advance (positions, context
+    lengths, cache slots), and the token ids never leave the GPU: the ARGMAX of a step is copied into the id input of the
+    next one on the device stream (`tlb_program_feed_input`). Block tables are assigned up front for `max_ctx` tokens per
+    sequence, so no step has to allocate a page."""
+
+    def __init__(self, native, cfg: DecoderConfig, batch: int, max_ctx: int, tables: np.ndarray) -> None:
+        from .native import NativeProgram
+
+        self.cfg, self.batch, self.max_ctx = cfg, batch, max_ctx
+        self.tables = np.ascontiguousarray(tables, np.int32)
+        max_blocks = (max_ctx + cfg.block_size - 1) // cfg.block_size
+        assert self.tables.shape == (batch, max_blocks)
+        pool_blocks = int(self.tables.max()) + 1
+        self.dg = decoder_step(cfg, batch, max_ctx, pool_blocks)
+        g = self.dg.graph
+        self.argmax = [t for t in g.nodes if g.tensors[t].name == "argmax"][0]
+        g.keep.append(self.argmax)   # its i32 bytes feed the next step
+        self.native = native
+        if not native.state_offsets:
+            native.alloc_states(self.dg.state_bytes)
+        self.prog = NativeProgram.compile(native, g)
+        self.pos = None
+        self.steps = 0
+
+    def begin(self, first_ids: np.ndarray, cached_tokens: np.ndarray) -> None:
+        """`first_ids`: the token each sequence feeds first; `cached_tokens`: how many tokens of it the pools already hold."""
+        self.pos = np.ascontiguousarray(cached_tokens, np.int32).copy()
+        self.prog.set_input(self.dg.inputs["ids"], np.ascontiguousarray(first_ids, np.int32))
+        self.prog.set_input(self.dg.inputs["tables"], self.tables)
+        self.steps = 0
+
+    def step(self, wait: bool = True) -> None:
+        """One token for every sequence; afterwards the id input already holds the tokens just chosen."""
+        bs = self.cfg.block_size
+        assert self.pos is not None and int(self.pos.max()) < self.max_ctx
+        slots = self.tables[np.arange(self.batch), self.pos // bs].astype(np.int64) * bs + self.pos % bs
+        self.prog.set_input(self.dg.inputs["pos"], self.pos)
+        self.prog.set_input(self.dg.inputs["lens"], self.pos + 1)
+        self.prog.set_input(self.dg.inputs["slots"], slots.view(np.int32))
+        self.prog.enqueue()
+        self.prog.feed_input(self.dg.inputs["ids"], self.argmax)
+        if wait:
+            self.native.sync()
+        self.pos = self.pos + 1
+        self.steps += 1
+
+    def tokens(self) -> np.ndarray:
+        """The tokens the last step chose (reads them back: waits for the step)."""
+        return self.prog.read(self.argmax).reshape(self.batch).astype(np.int64)
+
+    def logits(self) -> np.ndarray:
+        return self.prog.read(self.dg.logits).reshape(self.batch, -1)
+
+    def free(self) -> None:
+        self.prog.free()

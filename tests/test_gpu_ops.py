@@ -9,7 +9,7 @@ import pytest
 from helpers import Model, close
 from oracle.bindings import Q8_0
 from tensorlisp_b200 import graph as G
-from tensorlisp_b200.native import TlbError
+from tensorlisp_b200.native import Native, TlbError
 
 pytestmark = pytest.mark.gpu
 GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "golden.npz"))
@@ -242,3 +242,30 @@ def test_device_name():
     n = Native(0)
     assert n.device_name().startswith("native ")
     n.close()
+
+
+def test_copy_blocks_copies_pairs():
+    """The reference's own check (crates/kernels/tests/paged_attn_cuda.rs:269-299): pairs (0 -> 4) and (2 -> 5) of a
+    6-page pool, in the K pool and the V pool of one state block; other pages keep their bytes; bad pairs are refused."""
+    from tensorlisp_b200._lib import TlbError
+    nb, n = 6, 40 * 4            # pages of 160 f32 = 640 bytes
+    kc = np.arange(nb * n, dtype=np.float32)
+    vc = -kc
+    native = Native.load([])
+    native.alloc_states([kc.nbytes, vc.nbytes])
+    ko, vo = native.state_offsets
+    native.state.write(ko, kc)
+    native.state.write(vo, vc)
+    native.state.copy_blocks(ko, vo, nb, n * 4, [(0, 4), (2, 5)])
+    k2 = native.state.read(ko, kc.nbytes).view(np.float32)
+    v2 = native.state.read(vo, vc.nbytes).view(np.float32)
+    for src, dst in ((0, 4), (2, 5)):
+        assert np.array_equal(k2[dst * n:(dst + 1) * n], kc[src * n:(src + 1) * n])
+        assert np.array_equal(v2[dst * n:(dst + 1) * n], vc[src * n:(src + 1) * n])
+    for blk in (0, 1, 2, 3):
+        assert np.array_equal(k2[blk * n:(blk + 1) * n], kc[blk * n:(blk + 1) * n]), "untouched block changed"
+        assert np.array_equal(v2[blk * n:(blk + 1) * n], vc[blk * n:(blk + 1) * n])
+    for bad in ([(0, 6)], [(0, 4), (4, 5)], [(1, 3), (2, 3)], [(-1, 2)]):
+        with pytest.raises(TlbError):
+            native.state.copy_blocks(ko, vo, nb, n * 4, bad)
+    native.close()
