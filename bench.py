@@ -491,6 +491,18 @@ def run_ours(args) -> dict:
             result["cpu_baseline"] = {"value": None, "unit": "tok/s", "cores": 0, "kind": "reference", "sample": "failed: %s" % e}
     prog.free()
     native.close()
+    del prog, native
+    torch.cuda.empty_cache()
+    if not args.no_prefill:
+        # benchmark config 5 next to the headline number: the prompt pass of the same decoder with Q8_0 weights,
+        # 8 prompts x 2048 tokens, all 32 layers, its own roofline (dense tensor peak)
+        try:
+            pf = prefill_measure(8, 2048, 32, 2, 1, world, rank, local_rank, dist)
+        except Exception as e:
+            pf = {"failed": "%s: %s" % (type(e).__name__, e)}
+        if rank == 0:
+            result["prefill"] = {k: pf[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "warmup", "dtype", "config", "roofline", "launch_share",
+                                                    "failed") if k in pf}
     if dist is not None:
         dist.destroy_process_group()
     return result if rank == 0 else {}
@@ -498,8 +510,8 @@ def run_ours(args) -> dict:
 
 
 # ---------------------------------------------------------------------------------- prompt pass (benchmark config 5)
-def run_prefill(args) -> dict:
-    """`--prefill SEQS:TOKENS[:LAYERS]`: the prompt pass of the same decoder with Q8_0 weights, SEQS prompts of
+def prefill_measure(n_seqs: int, n_tokens: int, layers: int, steps: int, warmup: int, world: int, rank: int, local_rank: int, dist) -> dict:
+    """The prompt pass of the same decoder with Q8_0 weights, SEQS prompts of
     TOKENS tokens, dense causal attention, K/V written to the paged pools, logits of every prompt's last
     token. Reported as prompt tokens per second and as a fraction of the measured dense tensor peak
     (2 flops per weight element and token, plus 4 per causal query-key pair and head dimension)."""
@@ -508,17 +520,6 @@ def run_prefill(args) -> dict:
     from tensorlisp_b200.graph import Q8_0
     from tensorlisp_b200.programs import DecoderConfig, decoder_weights, prefill_step
 
-    spec = args.prefill.split(":")
-    n_seqs, n_tokens = int(spec[0]), int(spec[1])
-    layers = int(spec[2]) if len(spec) > 2 else 32
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        torch.cuda.set_device(local_rank)
-        dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world)
     cfg0 = DecoderConfig(n_layers=layers, wtype=Q8_0)
     cfg, dg, native, prog, weight_bytes = build_model(rank, world, local_rank,
                                                       make_graph=lambda tp: prefill_step(cfg0, n_seqs, n_tokens, tp=tp))
@@ -547,20 +548,20 @@ def run_prefill(args) -> dict:
         torch.cuda.synchronize()
         native.sync()
 
-    for _ in range(max(args.warmup, 1)):
+    for _ in range(max(warmup, 1)):
         prog.run()
     barrier()
     sampler = ClockSampler(local_rank)
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
-    for _ in range(args.steps):
+    for _ in range(steps):
         prog.enqueue()
     e1.record(stream)
     native.sync()
     barrier()
     clocks = sampler.stop()
-    ms = e0.elapsed_time(e1) / args.steps
+    ms = e0.elapsed_time(e1) / steps
     prof = prog.profile()
     barrier()
     if dist is not None:
@@ -589,12 +590,12 @@ def run_prefill(args) -> dict:
     mm_ms = sum(v[0] for k, v in by_kind.items() if k.startswith("MUL_MAT"))
     result = {
         "metric": "prefill tok/s (8B-shape Q8_0, %d x %d prompt tokens)" % (n_seqs, n_tokens), "value": T / (ms * 1e-3),
-        "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "int8 codes on tcgen05 kind::i8, f16 mma.sync attention, f32 scales and accumulate",
         "data": "synthetic",
         "config": {"workload": "benchmark config 5: Llama-3-8B shape, %d layers, Q8_0 weights, %d prompts x %d tokens, causal" % (cfg.n_layers, n_seqs, n_tokens),
                    "parallelism": "tp%d" % world},
-        "gpu_launches": prog.dispatch_count() * args.steps, "clocks": clocks,
+        "gpu_launches": prog.dispatch_count() * steps, "clocks": clocks,
         "roofline": {"bound": "tensor", "kernel": "whole step", "achieved": tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": tf / peak_tf,
                      "of": peak_src + " sustained bf16 (per GPU)", "traffic": None,
                      "mul_mat_only_TFLOPs": flops_mm / world / (mm_ms * 1e-3) / 1e12 if mm_ms > 0 else None},
@@ -603,14 +604,30 @@ def run_prefill(args) -> dict:
     }
     prog.free()
     native.close()
+    return result if rank == 0 else {}
+
+
+def run_prefill(args) -> dict:
+    """`--prefill SEQS:TOKENS[:LAYERS]` on its own."""
+    spec = args.prefill.split(":")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world)
+    out = prefill_measure(int(spec[0]), int(spec[1]), int(spec[2]) if len(spec) > 2 else 32, args.steps, args.warmup, world, rank, local_rank, dist)
     if dist is not None:
         dist.destroy_process_group()
-    return result if rank == 0 else {}
+    return out
 
 
 # ---------------------------------------------------------------------------------- single-kernel runs
 def run_kernel(args) -> dict:
-    """`--kernel mul_mat:TYPE:K:M:N`, `paged_attention:SEQS:CTX` or `flash_attention:TOKENS` replays a program holding
+    """`--kernel mul_mat:TYPE:K:M:N`, `ffn:TOKENS`, `paged_attention:SEQS:CTX` or `flash_attention:TOKENS` replays a program holding
     only that op (several independent copies, so every replay reads more bytes than L2 holds) and
     prints the launch time and the algorithmic bytes it moved. The commands under profiles/ use it
     to give the profiler one kernel on a small, bounded case."""
@@ -650,6 +667,42 @@ def run_kernel(args) -> dict:
         prog.set_input(0, rng.standard_normal((N, K)).astype(np.float32))
         bytes_per_launch = rs * M
         what = "%s weights [%d x %d], %d activation column(s)" % (spec[1], M, K, N)
+    elif spec[0] == "ffn":
+        # benchmark config 2: RMSNorm -> gate / up 4096 -> 14336 (Q4_K) -> SiLU(gate) * up -> down 14336 -> 4096 (Q4_K), T tokens
+        from tensorlisp_b200.programs import swiglu_ffn
+        n = Native(0)
+        T, d, f = int(spec[1]), 4096, 14336
+        copies = args.copies or 4
+        shapes = [("norm", G.F32, d, 1), ("gate", G.Q4_K, d, f), ("up", G.Q4_K, d, f), ("down", G.Q4_K, f, d)]
+        x = g.input(G.F32, [d, T], "x")
+        offs, total = [], 0
+        for c in range(copies):
+            ids = []
+            for nm, ty, k, m in shapes:
+                ids.append(g.weight(ty, [k] if m == 1 else [k, m], "%s%d" % (nm, c)))
+                offs.append((ty, k, m, total))
+                total += G.align256(G.row_size(ty, k) * m)
+            g.output(swiglu_ffn(g, x, ids[0], ids[1], ids[2], ids[3], 1e-5, "c%d." % c))
+        h = C.c_void_p()
+        check(n.L.tlb_weights_create(n.dev, total, C.byref(h)))
+        n.weights = StateBlock(h)
+        for ty, k, m, off in offs:
+            n.weight_loc.append((0, off))
+            if m == 1:
+                w = (1 + 0.1 * torch.randn(k, device="cuda")).contiguous()
+                torch.cuda.synchronize()
+                n.weights.copy_device(off, w.data_ptr(), k * 4)
+            else:
+                w = torch.randn((m, k), device="cuda") * 0.02
+                torch.cuda.synchronize()
+                check(n.L.tlb_quantize_rows_device(n.dev, ty, C.c_void_p(w.data_ptr()), m, k, C.c_void_p(n.weights.device_ptr + off)))
+                n.sync()
+        n.alloc_states([])
+        prog = NativeProgram.compile(n, g)
+        prog.set_input(0, rng.standard_normal((T, d)).astype(np.float32))
+        bytes_per_launch = 3 * G.row_size(G.Q4_K, d) * f + d * 4 + 2 * d * 4 * T     # weights + norm + x in, y out
+        flops = 6.0 * d * f * T
+        what = "SwiGLU FFN block, Q4_K 4096 -> 14336 -> 4096, %d token(s) (%.1f GFLOP); one launch = the whole block" % (T, flops / 1e9)
     elif spec[0] == "paged_attention":
         cfg = DecoderConfig()
         # CTX "ragged": context lengths uniform in [128, 8192] (benchmark config 3), seeded
@@ -723,7 +776,7 @@ def run_kernel(args) -> dict:
            "peak_GBps": peak, "frac": bytes_per_launch / ms / 1e6 / peak, "of": src, "launches": prog.labels()}
     if spec[0] == "mul_mat":
         out["TFLOPs"] = 2.0 * K * M * N / (ms * 1e-3) / 1e12
-    if spec[0] == "flash_attention":
+    if spec[0] in ("flash_attention", "ffn"):
         out["TFLOPs"] = flops / (ms * 1e-3) / 1e12
     prog.free()
     n.close()
@@ -831,6 +884,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prompt-pass measurement (benchmark config 5) behind the decode timing")
     ap.add_argument("--no-parity", action="store_true", help="skip the reduced-model check against the CPU oracle before the timed region")
     ap.add_argument("--parity-only", action="store_true", help="run only that check (every rank) and print its result")
     ap.add_argument("--kernel", default="", help="time one kernel instead of the decode step, e.g. mul_mat:q4_K:4096:14336:1 "
