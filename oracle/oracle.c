@@ -77,6 +77,13 @@ int64_t orc_row_size(int type, int64_t ne0) {
         case ORC_Q4_0: return ne0 / 32 * 18;
         case ORC_Q8_0: return ne0 / 32 * 34;
         case ORC_Q4_K: return ne0 / 256 * 144;
+        case ORC_Q4_1: return ne0 / 32 * 20;
+        case ORC_Q5_0: return ne0 / 32 * 22;
+        case ORC_Q5_1: return ne0 / 32 * 24;
+        case ORC_Q2_K: return ne0 / 256 * 84;
+        case ORC_Q3_K: return ne0 / 256 * 110;
+        case ORC_Q5_K: return ne0 / 256 * 176;
+        case ORC_Q6_K: return ne0 / 256 * 210;
         default: return -1;
     }
 }
@@ -308,9 +315,73 @@ int orc_quantize_rows(int type, const float *src, int64_t nrows, int64_t n, void
     return 0;
 }
 
+/* Element e of one block of the other block types, decoded the way ggml-quants.c does it row by row
+ * (dequantize_row_q4_1 :479, _q5_0 :500, _q5_1 :526, _q2_K :961, _q3_K :1305, _q5_K :1731, _q6_K :1939; block layouts
+ * ggml-common.h): every product and sum is a separate f32 operation, in ggml's order. */
+static float f16_at(const uint8_t *p) { return orc_f16_to_f32((uint16_t)(p[0] | (p[1] << 8))); }
+static float decode_elem(int type, const uint8_t *b, int e) {
+    switch (type) {
+        case ORC_Q4_1: {  /* {f16 d, m; u8 qs[16]} */
+            const int q = e < 16 ? (b[4 + e] & 0x0F) : (b[4 + e - 16] >> 4);
+            const float t = (float)q * f16_at(b);
+            return t + f16_at(b + 2);
+        }
+        case ORC_Q5_0: case ORC_Q5_1: {  /* {f16 d[, m]; u8 qh[4]; u8 qs[16]}: bit e of qh is the fifth bit of element e */
+            const int one = type == ORC_Q5_1;
+            const uint8_t *hb = b + (one ? 4 : 2), *qs = hb + 4;
+            const uint32_t qh = (uint32_t)hb[0] | ((uint32_t)hb[1] << 8) | ((uint32_t)hb[2] << 16) | ((uint32_t)hb[3] << 24);
+            const int q = (e < 16 ? (qs[e] & 0x0F) : (qs[e - 16] >> 4)) | (int)(((qh >> e) & 1u) << 4);
+            if (one) { const float t = (float)q * f16_at(b); return t + f16_at(b + 2); }
+            return (float)(q - 16) * f16_at(b);
+        }
+        case ORC_Q2_K: {  /* {u8 scales[16]; u8 qs[64]; f16 d, dmin} */
+            const int n = e >> 7, j = (e >> 5) & 3, sub = (e >> 4) & 1, l = e & 15;
+            const uint8_t sc = b[n * 8 + 2 * j + sub];
+            const int q = (b[16 + n * 32 + sub * 16 + l] >> (2 * j)) & 3;
+            const float dl = f16_at(b + 80) * (float)(sc & 0xF), ml = f16_at(b + 82) * (float)(sc >> 4);
+            const float t = dl * (float)q;
+            return t - ml;
+        }
+        case ORC_Q3_K: {  /* {u8 hmask[32]; u8 qs[64]; u8 scales[12]; f16 d} */
+            const int n = e >> 7, j = (e >> 5) & 3, sub = (e >> 4) & 1, l = e & 15;
+            const int is = n * 8 + 2 * j + sub, g = is >> 2, i = is & 3;
+            const uint8_t *s = b + 96;
+            const int lo = g < 2 ? (s[4 * g + i] & 0xF) : (s[4 * (g - 2) + i] >> 4);
+            const int hi = (s[8 + i] >> (2 * g)) & 3;
+            const int scale = (int)(int8_t)(lo | (hi << 4)) - 32;
+            const int q = ((b[32 + n * 32 + sub * 16 + l] >> (2 * j)) & 3) - ((b[sub * 16 + l] & (1 << (4 * n + j))) ? 0 : 4);
+            const float dl = f16_at(b + 108) * (float)scale;
+            return dl * (float)q;
+        }
+        case ORC_Q5_K: {  /* {f16 d, dmin; u8 scales[12]; u8 qh[32]; u8 qs[128]} */
+            const int j = e >> 5, l = e & 31;
+            uint8_t sc, m;
+            scale_min_k4(j, b + 4, &sc, &m);
+            const int q = ((b[48 + (j >> 1) * 32 + l] >> ((j & 1) * 4)) & 0xF) + ((b[16 + l] & (1 << j)) ? 16 : 0);
+            const float d1 = f16_at(b) * (float)sc, m1 = f16_at(b + 2) * (float)m;
+            const float t = d1 * (float)q;
+            return t - m1;
+        }
+        case ORC_Q6_K: {  /* {u8 ql[128]; u8 qh[64]; i8 scales[16]; f16 d} */
+            const int n = e >> 7, quarter = (e >> 5) & 3, l = e & 31;
+            const uint8_t lo = b[n * 64 + (quarter & 1) * 32 + l];
+            const int q = (int)(int8_t)(((quarter & 2) ? (lo >> 4) : (lo & 0xF)) | (((b[128 + n * 32 + l] >> (2 * quarter)) & 3) << 4)) - 32;
+            const float ds = f16_at(b + 208) * (float)((const int8_t *)(b + 192))[n * 8 + (l >> 4) + 2 * quarter];
+            return ds * (float)q;
+        }
+        default: return 0.f;
+    }
+}
+
 /* ggml-quants.c dequantize_row_q8_0 / _q4_0 / _q4_K (:1529-1551) */
 int orc_dequantize_row(int type, const void *src, float *y, int64_t k) {
     switch (type) {
+        case ORC_Q4_1: case ORC_Q5_0: case ORC_Q5_1: case ORC_Q2_K: case ORC_Q3_K: case ORC_Q5_K: case ORC_Q6_K: {
+            const int blck = (type == ORC_Q4_1 || type == ORC_Q5_0 || type == ORC_Q5_1) ? 32 : 256;
+            const int64_t bytes = orc_row_size(type, blck);
+            for (int64_t i = 0; i < k; i++) y[i] = decode_elem(type, (const uint8_t *)src + (i / blck) * bytes, (int)(i % blck));
+            return 0;
+        }
         case ORC_F32: memcpy(y, src, (size_t)k * 4); return 0;
         case ORC_F16: for (int64_t i = 0; i < k; i++) y[i] = orc_f16_to_f32(((const uint16_t *)src)[i]); return 0;
         case ORC_Q8_0: {

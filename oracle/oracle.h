@@ -15,7 +15,8 @@
 extern "C" {
 #endif
 
-enum { ORC_F32 = 0, ORC_F16 = 1, ORC_Q4_0 = 2, ORC_Q8_0 = 8, ORC_Q4_K = 12 };
+enum { ORC_F32 = 0, ORC_F16 = 1, ORC_Q4_0 = 2, ORC_Q4_1 = 3, ORC_Q5_0 = 6, ORC_Q5_1 = 7, ORC_Q8_0 = 8, ORC_Q2_K = 10, ORC_Q3_K = 11, ORC_Q4_K = 12,
+       ORC_Q5_K = 13, ORC_Q6_K = 14 };
 
 uint16_t orc_f32_to_f16(float f);
 float    orc_f16_to_f32(uint16_t h);

@@ -8,21 +8,12 @@
 #include <math_constants.h>
 
 #include "kernels.h"
+#include "dequant.cuh"
 #include "pdl.cuh"
 
 namespace tlb {
 
-// ---------------------------------------------------------------- typed element access
-__device__ __forceinline__ float ld_elem(const uint8_t *p, uint32_t ty) {
-    switch (ty) {
-        case TLB_TYPE_F32: return *reinterpret_cast<const float *>(p);
-        case TLB_TYPE_F16: return __half2float(*reinterpret_cast<const __half *>(p));
-        case TLB_TYPE_BF16: return __bfloat162float(*reinterpret_cast<const __nv_bfloat16 *>(p));
-        case TLB_TYPE_I32: return (float)*reinterpret_cast<const int32_t *>(p);
-        case TLB_TYPE_I64: return (float)*reinterpret_cast<const int64_t *>(p);
-        default: return 0.f;
-    }
-}
+// ---------------------------------------------------------------- typed element access (reads: dequant.cuh)
 __device__ __forceinline__ void st_elem(uint8_t *p, uint32_t ty, float v) {
     switch (ty) {
         case TLB_TYPE_F32: *reinterpret_cast<float *>(p) = v; break;
@@ -33,44 +24,6 @@ __device__ __forceinline__ void st_elem(uint8_t *p, uint32_t ty, float v) {
         default: break;
     }
 }
-
-// element `i0` of a row of block-quantized data (ggml-quants.c dequantize_row_*)
-__device__ __forceinline__ float dq_elem(const uint8_t *row, uint32_t ty, int64_t i0) {
-    switch (ty) {
-        case TLB_TYPE_Q8_0: {
-            const uint8_t *b = row + (i0 >> 5) * 34;
-            const float d = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(b)));
-            return (float)reinterpret_cast<const int8_t *>(b + 2)[i0 & 31] * d;
-        }
-        case TLB_TYPE_Q4_0: {
-            const uint8_t *b = row + (i0 >> 5) * 18;
-            const float d = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(b)));
-            const int j = (int)(i0 & 31);
-            const int q = j < 16 ? (b[2 + j] & 0x0F) : (b[2 + j - 16] >> 4);
-            return (float)(q - 8) * d;
-        }
-        case TLB_TYPE_Q4_K: {
-            const uint8_t *b = row + (i0 >> 8) * 144;
-            const float d = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(b)));
-            const float dmin = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(b + 2)));
-            const int e = (int)(i0 & 255), j = e >> 5, l = e & 31;
-            const uint8_t *s = b + 4;
-            int sc, mn;
-            if (j < 4) {
-                sc = s[j] & 63;
-                mn = s[j + 4] & 63;
-            } else {
-                sc = (s[j + 4] & 0xF) | ((s[j - 4] >> 6) << 4);
-                mn = (s[j + 4] >> 4) | ((s[j] >> 6) << 4);
-            }
-            const int q = (b[16 + (j >> 1) * 32 + l] >> ((j & 1) * 4)) & 0xF;
-            return d * (float)sc * (float)q - dmin * (float)mn;
-        }
-        default: return ld_elem(row + i0 * (ty == TLB_TYPE_F32 || ty == TLB_TYPE_I32 ? 4 : (ty == TLB_TYPE_I64 ? 8 : 2)), ty);
-    }
-}
-
-__device__ __forceinline__ bool is_quant(uint32_t ty) { return ty == TLB_TYPE_Q8_0 || ty == TLB_TYPE_Q4_0 || ty == TLB_TYPE_Q4_K; }
 
 __device__ __forceinline__ void decomp(int64_t i, const int64_t *ne, int64_t &i0, int64_t &i1, int64_t &i2, int64_t &i3) {
     i0 = i % ne[0]; i /= ne[0];

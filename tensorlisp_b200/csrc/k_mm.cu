@@ -16,6 +16,7 @@
 #include <cuda_bf16.h>
 
 #include "kernels.h"
+#include "dequant.cuh"
 
 namespace tlb {
 
@@ -455,6 +456,11 @@ __global__ void __launch_bounds__(128) k_mm_generic(MMGeneric p, const uint8_t *
             else wv = __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(wrow)[k]);
             f += wv * *reinterpret_cast<const float *>(xcol + k * p.x.nb[0]);
         }
+    } else if (p.wtype != TLB_TYPE_Q8_0 && p.wtype != TLB_TYPE_Q4_0 && p.wtype != TLB_TYPE_Q4_K) {
+        // the other block types: decoded weights times the f32 activations, the reference executor's own arithmetic
+        // for every type (crates/kernels/src/cuda/native/mm.cu:16-42)
+        const uint8_t *xcol = X + n * p.x.nb[1] + i2 * p.x.nb[2] + i3 * p.x.nb[3];
+        for (int64_t k = lane; k < K; k += 32) f += dq_elem(wrow, p.wtype, k) * *reinterpret_cast<const float *>(xcol + k * p.x.nb[0]);
     } else {
         const int64_t col = n + N * (i2 + p.y.ne[2] * i3);  // column of the quantized activation block
         const char *ab = (const char *)p.act;

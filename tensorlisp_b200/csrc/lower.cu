@@ -16,7 +16,13 @@ namespace {
 
 bool plain(uint32_t ty) { return ty == 0 || ty == 1 || ty == 30 || ty == 26 || ty == 27; }
 bool gemv_type(uint32_t ty) { return ty == TLB_TYPE_Q8_0 || ty == TLB_TYPE_Q4_0 || ty == TLB_TYPE_Q4_K; }
-bool mm_weight_ok(uint32_t ty) { return ty == 0 || ty == 1 || ty == 30 || gemv_type(ty); }
+// block types that are read through the element decoders only (dequant.cuh): rows for GET_ROWS / CPY, weights of the
+// generic mul_mat (decoded weights times f32 activations)
+bool decoded_type(uint32_t ty) {
+    return ty == TLB_TYPE_Q4_1 || ty == TLB_TYPE_Q5_0 || ty == TLB_TYPE_Q5_1 || ty == TLB_TYPE_Q2_K || ty == TLB_TYPE_Q3_K || ty == TLB_TYPE_Q5_K ||
+           ty == TLB_TYPE_Q6_K;
+}
+bool mm_weight_ok(uint32_t ty) { return ty == 0 || ty == 1 || ty == 30 || gemv_type(ty) || decoded_type(ty); }
 
 TView view_of(const Tensor &t) {
     TView v;
@@ -270,7 +276,7 @@ void lower_get_rows(L &l) {
     const Tensor &t = l.t();
     const int32_t a = l.src(0), ids = l.src(1);
     const uint32_t aty = l.T(a).ty;
-    if (!(plain(aty) || gemv_type(aty))) unsupported(t, std::string("rows of ggml type ") + type_traits(aty)->name);
+    if (!(plain(aty) || gemv_type(aty) || decoded_type(aty))) unsupported(t, std::string("rows of ggml type ") + type_traits(aty)->name);
     if (!(l.T(ids).ty == 26 || l.T(ids).ty == 27)) unsupported(t, "row indices must be i32 or i64");
     if (!plain(t.ty)) unsupported(t, "operand type");
     RowsArgs p{view_of(l.T(a)), view_of(l.T(ids)), view_of(t), aty, l.T(ids).ty, t.ty};
@@ -295,7 +301,7 @@ void lower_cpy(L &l) {
     const int32_t a = l.src(0);
     const Tensor &ta = l.T(a);
     if (ta.nelements() != t.nelements()) unsupported(t, "source and destination differ in size");
-    if (!(plain(ta.ty) || gemv_type(ta.ty))) unsupported(t, "operand type");
+    if (!(plain(ta.ty) || gemv_type(ta.ty) || decoded_type(ta.ty))) unsupported(t, "operand type");
     if (!plain(t.ty)) unsupported(t, "operand type");
     CpyArgs p{view_of(ta), view_of(t), ta.ty, t.ty};
     const Place pa = l.place(a), pd = l.place(l.id);
@@ -791,7 +797,7 @@ void lower_node(const LowerCtx &c, int32_t id, int pos, std::vector<Dispatch> &o
     for (int s : t.src)
         if (s >= 0) {
             const uint32_t ty = c.g->tensors[s].ty;
-            if (!(plain(ty) || gemv_type(ty)) && !is_qact(c.g->tensors[s].op)) unsupported(t, "operand type");
+            if (!(plain(ty) || gemv_type(ty) || decoded_type(ty)) && !is_qact(c.g->tensors[s].op)) unsupported(t, "operand type");
         }
     if (!plain(t.ty)) unsupported(t, "operand type");
     if (op == "ADD" || op == "SUB" || op == "MUL" || op == "DIV") return lower_bin(l);

@@ -68,3 +68,18 @@ def test_attention_decode(oracle):
     _, out32 = oracle.attention_decode(q, ks, vs, 2, 1.0 / np.sqrt(128.0))
     want = G["att_out"]
     assert np.abs(out32 - want).max() <= 2e-5 * np.abs(want).max()
+
+
+DEC = np.load(os.path.join(os.path.dirname(__file__), "golden", "golden_decoders.npz"))
+DECODED = [(3, "q4_1"), (6, "q5_0"), (7, "q5_1"), (10, "q2_K"), (11, "q3_K"), (13, "q5_K"), (14, "q6_K")]
+
+
+@pytest.mark.parametrize("ty,name", DECODED)
+def test_decoders_of_the_other_block_types(oracle, ty, name):
+    """The bytes are the reference's (ggml_quantize_chunk); the oracle's dequantizer must give ggml's values, bit for bit."""
+    q = DEC["quant_" + name]
+    assert q.shape[1] == oracle.row_size(ty, 512)
+    assert np.array_equal(oracle.dequantize(ty, q, 512).view(np.uint32), DEC["dequant_" + name].view(np.uint32))
+    # the values are what the type can hold of x: a few percent of the row scale at most (2- and 3-bit types are coarse)
+    x, y = DEC["x"], DEC["dequant_" + name]
+    assert np.abs(x - y).max() <= 0.5 * np.abs(x).max()

@@ -41,3 +41,12 @@ def test_mul_mat_matches_cpu_backend(oracle, ref, ty, name):
     exact = oracle.mul_mat(ty, Wq, 4096, X, dequant=True)
     gap = np.abs(exact - want).max() / np.abs(want).max()
     assert 1e-3 < gap < 3e-2
+
+
+@pytest.mark.parametrize("ty", [3, 6, 7, 10, 11, 13, 14])
+def test_decoders_match_reference(oracle, ref, ty):
+    """q4_1 q5_0 q5_1 q2_K q3_K q5_K q6_K: bytes from the reference's quantizer, values from both dequantizers."""
+    rng = np.random.default_rng(ty)
+    x = (rng.standard_normal((12, 4096)) * 0.05).astype(np.float32)
+    q = ref.quantize(ty, x)
+    assert np.array_equal(oracle.dequantize(ty, q, 4096).view(np.uint32), ref.dequantize(ty, q, 4096).view(np.uint32))
