@@ -168,6 +168,10 @@ const char *tlb_program_label(tlb_program *prog, uint32_t i);
  * generation) it has been run with, and replayed on later runs with the same set (no counterpart: the reference
  * relaunches every kernel, exec.rs:186-225). */
 uint32_t   tlb_program_graph_count(tlb_program *prog);
+/* Kernel launches in the CUDA graph captured last, i.e. per run of the program (0 before the first run or when
+ * runs are not captured). A dispatch may launch more than one kernel (a K-split mul_mat and the launch that adds its
+ * partial sums) or none (a view), so this is the count to quote next to a timing (no counterpart in the reference). */
+uint32_t   tlb_program_kernel_count(tlb_program *prog);
 /* Device address and size of an input / kept tensor, so a caller that already has data in HBM can
  * write inputs and read results without the host (no counterpart: the reference only has the
  * blocking host copies). Returns NULL for tensors outside the io buffer and the arena. */

@@ -92,6 +92,7 @@ SYMBOLS = {
     "tlb_program_enqueue": (C.c_int, [_P, C.POINTER(_P), C.c_uint32, _P]),
     "tlb_program_read": (C.c_int, [_P, C.c_uint32, C.c_uint64, _P]),
     "tlb_program_dispatch_count": (C.c_uint32, [_P]),
+    "tlb_program_kernel_count": (C.c_uint32, [_P]),
     "tlb_program_label": (C.c_char_p, [_P, C.c_uint32]),
     "tlb_program_tensor_ptr": (_P, [_P, C.c_uint32, C.POINTER(C.c_uint64)]),
     "tlb_program_arena_bytes": (C.c_uint64, [_P]),

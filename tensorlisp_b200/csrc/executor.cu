@@ -699,6 +699,19 @@ tlb_status tlb_program_enqueue(tlb_program *prog, tlb_buffer *const *weights, ui
         prog->use_graph = false;
         return launch_all(prog, rc, false);
     }
+    {   // how many kernels one run of the program launches (tlb_program_kernel_count)
+        size_t n_nodes = 0;
+        prog->kernel_nodes = 0;
+        if (cudaGraphGetNodes(graph, nullptr, &n_nodes) == cudaSuccess && n_nodes > 0) {
+            std::vector<cudaGraphNode_t> nodes(n_nodes);
+            if (cudaGraphGetNodes(graph, nodes.data(), &n_nodes) == cudaSuccess)
+                for (size_t i = 0; i < n_nodes; i++) {
+                    cudaGraphNodeType ty;
+                    if (cudaGraphNodeGetType(nodes[i], &ty) == cudaSuccess && ty == cudaGraphNodeTypeKernel) prog->kernel_nodes++;
+                }
+        }
+        cudaGetLastError();
+    }
     cudaGraphExec_t exec = nullptr;
     e = cudaGraphInstantiate(&exec, graph, 0);
     cudaGraphDestroy(graph);
@@ -756,6 +769,8 @@ tlb_status tlb_program_run(tlb_program *prog, tlb_buffer *const *weights, uint32
     if (e != cudaSuccess) return fail(TLB_EXECUTION, cuda_msg(e));
     if (flag != 0) {
         cudaMemset((char *)prog->arena + std::max<uint64_t>(prog->layout.arena_size, 1), 0, 4);
+        if (flag == TLB_ERR_INDEX)
+            return fail(TLB_EXECUTION, "a context length, block id or cache slot from the caller was out of range (skipped on the device; device error word 4)");
         return fail(TLB_EXECUTION, "a kernel gave up waiting for its own copies (device error word " + std::to_string(flag) + ")");
     }
     return TLB_OK;
@@ -785,6 +800,7 @@ tlb_status tlb_program_read(tlb_program *prog, uint32_t tensor_id, uint64_t byte
 }
 
 uint32_t tlb_program_graph_count(tlb_program *prog) { return prog ? (uint32_t)prog->captured.size() : 0; }
+uint32_t tlb_program_kernel_count(tlb_program *prog) { return prog ? prog->kernel_nodes : 0; }
 uint64_t tlb_device_comm_generation(tlb_device *dev) { return dev ? dev->comm_generation : 0; }
 uint32_t tlb_program_dispatch_count(tlb_program *prog) { return prog ? (uint32_t)prog->dispatches.size() : 0; }
 const char *tlb_program_label(tlb_program *prog, uint32_t i) {

@@ -62,8 +62,21 @@ struct PagedParams {
     __half *out;           // [seqs][heads][HS]
     float *partial;        // [seqs][heads][n_chunks][HS + 2]  (max, sum, O) when n_chunks > 1
     int heads, kv_heads, group, groups_per_kv, block_size, block_shift, max_blocks, chunk_tokens, n_chunks;
+    int ctx_cap;           // min(maximum context, max_blocks * block_size): no length from the caller reaches past a table row
+    uint32_t pool_blocks;  // pages in each pool; 0x80000000 when this launch does not know (block ids are then only checked for sign)
+    int *err;              // device error word, or null: set to TLB_ERR_INDEX when a length or a block id was out of range
     float scale_log2;      // softmax scale * log2(e)
 };
+// A context length beyond the cap is cut to the cap; a CTA that meets a block id outside the pools leaves without
+// touching them; either way the error word tells the host that the result is not to be used.
+__device__ __forceinline__ int paged_ctx(const PagedParams &p, int seq) {
+    const int n = p.lens[seq];
+    if (n < 0 || n > p.ctx_cap) {
+        if (p.err) atomicExch(p.err, TLB_ERR_INDEX);
+        return n < 0 ? 0 : p.ctx_cap;
+    }
+    return n;
+}
 
 template <int HS>
 __global__ void __launch_bounds__(PA_WARPS * 32) k_paged_attn(PagedParams p) {
@@ -81,13 +94,27 @@ __global__ void __launch_bounds__(PA_WARPS * 32) k_paged_attn(PagedParams p) {
     const int g = lane >> 2, t = lane & 3;
     const int chunk = blockIdx.x, seq = blockIdx.z;
     const int kvh = blockIdx.y / p.groups_per_kv, grp = blockIdx.y % p.groups_per_kv;
-    const int ctx = p.lens[seq];
+    const int ctx = paged_ctx(p, seq);
     const int c_begin = chunk * p.chunk_tokens;
     if (c_begin >= ctx && !(chunk == 0)) return;  // nothing to do; the reduce skips this chunk
     const int c_end = min(ctx, c_begin + p.chunk_tokens);
     const int head0 = kvh * p.group + grp * 16;               // first query head of this CTA
     const int nrows = min(16, p.group - grp * 16);            // query heads served here
     const int n_tiles = c_end > c_begin ? (c_end - c_begin + PA_TILE - 1) / PA_TILE : 0;
+    const int32_t *table = p.tables + (size_t)seq * p.max_blocks;
+    {
+        // The block ids of this CTA's stretch of the context are checked here, once, and not in the copy loop below
+        // (every instruction there is paid per 16 bytes moved): an id outside the pools never becomes an address,
+        // the CTA reports it and leaves, and its part of the result stays unwritten.
+        bool bad = false;
+        if (c_end > c_begin)
+            for (int b = (c_begin >> p.block_shift) + (int)threadIdx.x; b <= ((c_end - 1) >> p.block_shift); b += PA_WARPS * 32)
+                bad |= (uint32_t)table[b] >= p.pool_blocks;   // negative ids are large here
+        if (__syncthreads_or(bad)) {
+            if (threadIdx.x == 0 && p.err) atomicExch(p.err, TLB_ERR_INDEX);
+            return;
+        }
+    }
 
     // ---- Q fragments (A operand, rows = query heads of the group, zero beyond nrows)
     uint32_t qa[KS][4];
@@ -104,7 +131,6 @@ __global__ void __launch_bounds__(PA_WARPS * 32) k_paged_attn(PagedParams p) {
     }
 
     uint8_t *ring = smem + (size_t)warp * PA_STAGES * STAGE_BYTES;
-    const int32_t *table = p.tables + (size_t)seq * p.max_blocks;
     const size_t page_stride = (size_t)p.block_size * HS;  // elements per (block, kv_head)
 
     // issue the cp.asyncs of this warp's tile `i` (tile index within the warp's sequence)
@@ -113,21 +139,48 @@ __global__ void __launch_bounds__(PA_WARPS * 32) k_paged_attn(PagedParams p) {
         if (tile < n_tiles) {
             uint8_t *st = ring + (size_t)(i % PA_STAGES) * STAGE_BYTES;
             const int tok0 = c_begin + tile * PA_TILE;
-            // K and V rows of a token sit at the same offset of their pools: one table lookup and one
-            // address per (lane, row), shifts instead of divisions (block sizes are powers of two)
+            // K and V rows of a token sit at the same offset of their pools, and the rows of a page follow one
+            // another there. With pages of 8 tokens or more (block sizes are powers of two) the tile's first 8
+            // tokens lie in one page and its last 8 in one page: two table lookups and two base addresses per tile, so that every
+            // 16-byte copy below costs an add and little else (each instruction here is paid per 16 bytes moved).
             constexpr int ROWS_PER_IT = 32 / CHUNKS, N_IT = PA_TILE / ROWS_PER_IT;
+            static_assert(N_IT % 2 == 0 && 8 % ROWS_PER_IT == 0, "a copy step stays inside one half of the tile");
             const int col = lane % CHUNKS, row0 = lane / CHUNKS;
+            const int n_live = c_end - tok0;   // >= 1: rows at and past it are zero-filled
+            const uint32_t dst0 = s_u32(st);
+            if (p.block_shift < 3) {
+                // pages of fewer than 8 tokens: a lookup and an address per row
+#pragma unroll
+                for (int it = 0; it < N_IT; it++) {
+                    const int row = it * ROWS_PER_IT + row0;
+                    const int tok = tok0 + row;
+                    const bool live = row < n_live;
+                    size_t off = 0;
+                    if (live) {
+                        const int blk = table[tok >> p.block_shift];
+                        off = ((size_t)blk * p.kv_heads + kvh) * page_stride + (size_t)(tok & (p.block_size - 1)) * HS + col * 8;
+                    }
+                    const uint32_t dst = dst0 + row * ROW_BYTES + ((col ^ (row & 7)) * 16);
+                    cp_async16(dst, p.kpool + off, live ? 16 : 0);
+                    cp_async16(dst + TILE_BYTES, p.vpool + off, live ? 16 : 0);
+                }
+                cp_commit();
+                return;
+            }
+            size_t off_half[2];
+#pragma unroll
+            for (int hf = 0; hf < 2; hf++) {
+                const int tok = tok0 + 8 * hf;
+                const int blk = tok < c_end ? table[tok >> p.block_shift] : 0;
+                off_half[hf] = ((size_t)blk * p.kv_heads + kvh) * page_stride + (size_t)((tok & (p.block_size - 1)) + row0) * HS + col * 8;
+            }
 #pragma unroll
             for (int it = 0; it < N_IT; it++) {
+                constexpr int HALF_IT = N_IT / 2;
                 const int row = it * ROWS_PER_IT + row0;
-                const int tok = tok0 + row;
-                const bool live = tok < c_end;
-                size_t off = 0;
-                if (live) {
-                    const int blk = table[tok >> p.block_shift];
-                    off = ((size_t)blk * p.kv_heads + kvh) * page_stride + (size_t)(tok & (p.block_size - 1)) * HS + col * 8;
-                }
-                const uint32_t dst = s_u32(st + row * ROW_BYTES + ((col ^ (row & 7)) * 16));
+                const bool live = row < n_live;
+                const size_t off = live ? off_half[it / HALF_IT] + (size_t)((it % HALF_IT) * ROWS_PER_IT) * HS : 0;
+                const uint32_t dst = dst0 + row * ROW_BYTES + ((col ^ (row & 7)) * 16);
                 cp_async16(dst, p.kpool + off, live ? 16 : 0);   // rows past the context are zero-filled
                 cp_async16(dst + TILE_BYTES, p.vpool + off, live ? 16 : 0);
             }
@@ -284,7 +337,7 @@ __global__ void __launch_bounds__(128) k_paged_reduce(PagedParams p) {
     griddep_launch();
     griddep_wait();
     const int head = blockIdx.x, seq = blockIdx.y;
-    const int ctx = p.lens[seq];
+    const int ctx = paged_ctx(p, seq);
     const int valid = ctx > 0 ? min(p.n_chunks, (ctx + p.chunk_tokens - 1) / p.chunk_tokens) : 0;
     const float *pp = p.partial + ((size_t)seq * p.heads + head) * p.n_chunks * (HS + 2);
     float m = -CUDART_INF_F;
@@ -364,7 +417,7 @@ static cudaError_t launch_pa(const PagedGeom &g, const PagedParams &p, cudaStrea
 
 cudaError_t launch_paged_attention(const PagedGeom &g, const void *q, const void *kpool, const void *vpool,
                                    const int32_t *tables, const int32_t *lens, void *out, void *scratch,
-                                   cudaStream_t st) {
+                                   int64_t pool_blocks, int *err, cudaStream_t st) {
     if (g.seqs == 0 || g.heads == 0) return cudaSuccess;
     PagedParams p;
     p.q = (const __half *)q;
@@ -384,6 +437,9 @@ cudaError_t launch_paged_attention(const PagedGeom &g, const void *q, const void
     p.max_blocks = g.max_blocks;
     p.chunk_tokens = g.chunk_tokens;
     p.n_chunks = g.n_chunks;
+    p.ctx_cap = (int)std::min<int64_t>(g.max_ctx, (int64_t)g.max_blocks * g.block_size);
+    p.pool_blocks = pool_blocks > 0 && pool_blocks < 0x80000000ll ? (uint32_t)pool_blocks : 0x80000000u;
+    p.err = err;
     p.scale_log2 = g.scale * 1.4426950408889634f;
     switch (g.hs) {
         case 64: return launch_pa<64>(g, p, st);
@@ -396,10 +452,14 @@ cudaError_t launch_paged_attention(const PagedGeom &g, const void *q, const void
 // cache write: key/value f16 [kv_heads*hs, tokens] -> pools at slot = block*block_size + offset
 // (reshape_and_cache of the reference; a negative slot skips the token)
 __global__ void k_cache_write(int kv_heads, int hs, int block_size, const uint4 *key, const uint4 *value, uint4 *kpool,
-                              uint4 *vpool, const int64_t *slots) {
+                              uint4 *vpool, const int64_t *slots, int64_t pool_slots, int *err) {
     const int tok = blockIdx.x;
     const int64_t slot = slots[tok];
     if (slot < 0) return;
+    if (slot >= pool_slots) {   // beyond the pools: nothing is written, the host hears of it
+        if (threadIdx.x == 0 && err) atomicExch(err, TLB_ERR_INDEX);
+        return;
+    }
     const int64_t blk = slot / block_size, off = slot % block_size;
     const int cpr = hs / 8;  // 16-byte chunks per head row
     for (int i = threadIdx.x; i < kv_heads * cpr; i += blockDim.x) {
@@ -411,10 +471,10 @@ __global__ void k_cache_write(int kv_heads, int hs, int block_size, const uint4 
     }
 }
 cudaError_t launch_cache_write(int tokens, int kv_heads, int hs, int block_size, const void *key, const void *value,
-                               void *kpool, void *vpool, const int64_t *slots, cudaStream_t st) {
+                               void *kpool, void *vpool, const int64_t *slots, int64_t pool_slots, int *err, cudaStream_t st) {
     if (tokens == 0) return cudaSuccess;
     k_cache_write<<<tokens, 128, 0, st>>>(kv_heads, hs, block_size, (const uint4 *)key, (const uint4 *)value, (uint4 *)kpool,
-                                          (uint4 *)vpool, slots);
+                                          (uint4 *)vpool, slots, pool_slots, err);
     return cudaGetLastError();
 }
 
@@ -464,6 +524,7 @@ cudaError_t launch_copy_blocks(void *kpool, void *vpool, const int64_t *map_dev,
 // the library image: every GPU that loads the library holds these bytes until the process exits.
 #define TLB_PA_STATIC_SCRATCH_BYTES (8u << 20)
 static __device__ __align__(256) unsigned char g_pa_static_scratch[TLB_PA_STATIC_SCRATCH_BYTES];
+static __device__ int g_pa_static_err;   // error word of the launches of tlb_paged_attention_static (zero at load)
 
 namespace tlb {
 // In host code the array's name is only a handle for the runtime, not a device address; the address
@@ -510,12 +571,22 @@ extern "C" tlb_status tlb_paged_attention_static(tlb_device *dev, const void *q,
     void *scratch = nullptr;
     cudaError_t e = pa_static_scratch(dev->ordinal, &scratch);
     if (e != cudaSuccess) return fail(TLB_EXECUTION, "cudaGetSymbolAddress: " + cuda_msg(e));
-    // nothing in the scratch has to start at zero: every chunk that the reduce reads is written by this launch
-    e = launch_paged_attention(g, q, k_pool, v_pool, block_tables, context_lens, out, scratch, dev->stream);
+    int *errw = nullptr;
+    e = cudaGetSymbolAddress((void **)&errw, g_pa_static_err);
+    if (e != cudaSuccess) return fail(TLB_EXECUTION, "cudaGetSymbolAddress: " + cuda_msg(e));
+    // nothing in the scratch has to start at zero: every chunk that the reduce reads is written by this launch.
+    // The pools' size is not an argument of this call: lengths are cut to the table row, block ids checked for sign.
+    e = launch_paged_attention(g, q, k_pool, v_pool, block_tables, context_lens, out, scratch, 0, errw, dev->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(dev->stream);
+    int flag = 0;
+    if (e == cudaSuccess) e = cudaMemcpy(&flag, errw, 4, cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) {
         cudaGetLastError();
         return fail(TLB_EXECUTION, "tlb_paged_attention_static: " + cuda_msg(e));
+    }
+    if (flag != 0) {
+        cudaMemset(errw, 0, 4);
+        return fail(TLB_EXECUTION, "tlb_paged_attention_static: a context length or block id from the caller was out of range (skipped on the device)");
     }
     return TLB_OK;
 }

@@ -309,7 +309,7 @@ __global__ void k_rope(RopeArgs p, const uint8_t *a, const int32_t *pos, const f
 // the key pool at the token's slot, v -> f16 into the value pool. Same arithmetic as k_rope followed
 // by the f32 -> f16 casts and the cache write; a negative slot skips the token's key and value.
 __global__ void k_rope_kv(RopeKvArgs p, const uint8_t *q, const uint8_t *k, const uint8_t *v, const int32_t *pos,
-                          const float *ff, __half *q16, __half *kpool, __half *vpool, const int64_t *slots) {
+                          const float *ff, __half *q16, __half *kpool, __half *vpool, const int64_t *slots, int *err) {
     griddep_launch();
     griddep_wait();
     const int tok = blockIdx.x, hsl = blockIdx.y, pr = threadIdx.x;
@@ -325,6 +325,10 @@ __global__ void k_rope_kv(RopeKvArgs p, const uint8_t *q, const uint8_t *k, cons
         } else {
             const int64_t slot = slots[tok];
             if (slot < 0) return;
+            if (slot >= p.pool_slots) {   // beyond the pools: nothing is written, the host hears of it
+                if (pr == 0 && err) atomicExch(err, TLB_ERR_INDEX);
+                return;
+            }
             src = k + h * p.k.nb[1] + tok * p.k.nb[2];
             dst = kpool + (((size_t)(slot / p.block_size) * p.kv_heads + h) * p.block_size + slot % p.block_size) * hs;
         }
@@ -344,7 +348,7 @@ __global__ void k_rope_kv(RopeKvArgs p, const uint8_t *q, const uint8_t *k, cons
         dst[ic + off] = __float2half_rn(x0 * sn + x1 * cs);
     } else {
         const int64_t slot = slots[tok];
-        if (slot < 0) return;
+        if (slot < 0 || slot >= p.pool_slots) return;   // reported by the key's CTA
         const int h = hsl - p.heads - p.kv_heads;
         const float2 x = *reinterpret_cast<const float2 *>(v + h * p.v.nb[1] + tok * p.v.nb[2] + pr * 8);
         __half *dst = vpool + (((size_t)(slot / p.block_size) * p.kv_heads + h) * p.block_size + slot % p.block_size) * hs;
@@ -352,10 +356,10 @@ __global__ void k_rope_kv(RopeKvArgs p, const uint8_t *q, const uint8_t *k, cons
     }
 }
 cudaError_t launch_rope_kv(const RopeKvArgs &p, const void *q, const void *k, const void *v, const int32_t *pos, const float *ff,
-                           void *q16, void *kpool, void *vpool, const int64_t *slots, cudaStream_t st) {
+                           void *q16, void *kpool, void *vpool, const int64_t *slots, int *err, cudaStream_t st) {
     if (p.tokens == 0) return cudaSuccess;
     return launch_pdl(k_rope_kv, dim3((unsigned)p.tokens, (unsigned)(p.heads + 2 * p.kv_heads)), dim3(p.hs / 2), 0, st, p,
-                      (const uint8_t *)q, (const uint8_t *)k, (const uint8_t *)v, pos, ff, (__half *)q16, (__half *)kpool, (__half *)vpool, slots);
+                      (const uint8_t *)q, (const uint8_t *)k, (const uint8_t *)v, pos, ff, (__half *)q16, (__half *)kpool, (__half *)vpool, slots, err);
 }
 cudaError_t launch_rope(const RopeArgs &p, const void *a, const int32_t *pos, const float *ff, void *d, cudaStream_t st) {
     const int64_t n = p.a.ne[0] / 2 * p.a.ne[1] * p.a.ne[2] * p.a.ne[3];

@@ -132,9 +132,10 @@ struct RopeKvArgs {
     RopeArgs rope;   // a = the f32 query view [hs, heads, tokens]
     TView k, v;
     int heads, kv_heads, hs, block_size, tokens;
+    int64_t pool_slots;   // block_size * pages of each pool: a slot at or beyond it is skipped and reported
 };
 cudaError_t launch_rope_kv(const RopeKvArgs &p, const void *q, const void *k, const void *v, const int32_t *pos, const float *ff,
-                           void *q16, void *kpool, void *vpool, const int64_t *slots, cudaStream_t st);
+                           void *q16, void *kpool, void *vpool, const int64_t *slots, int *err, cudaStream_t st);
 struct SoftmaxArgs { TView a, m, d; float scale, max_bias, m0, m1; int n_head_log2; int has_mask; uint32_t mty; };
 cudaError_t launch_soft_max(const SoftmaxArgs &p, const void *a, const void *m, void *d, cudaStream_t st);
 struct RowsArgs { TView a, ids, d; uint32_t aty, idty, dty; };
@@ -160,6 +161,11 @@ struct FlashArgs {
 bool flash_supported(int64_t d, int64_t dv);
 cudaError_t launch_flash_attn(const FlashArgs &p, const void *q, const void *k, const void *v, const void *mask, float *out, cudaStream_t st);
 
+// Values of the device error word behind a program's arena: 1-3 are bounded waits that gave up (GEMV copies, tensor-core
+// pipelines, the peer exchange); 4 is a context length, block id or cache slot from the caller that a kernel skipped
+// because it pointed outside the tables or pools.
+#define TLB_ERR_INDEX 4
+
 // ---------------------------------------------------------------- k_attn.cu
 // KV pools are private to the executor (only the two paged nodes touch them): f16
 // [block][kv_head][slot][head_size] for both keys and values.
@@ -173,9 +179,10 @@ uint64_t paged_scratch_bytes(const PagedGeom &g);
 bool paged_supported(const PagedGeom &g);
 cudaError_t launch_paged_attention(const PagedGeom &g, const void *q, const void *kpool, const void *vpool,
                                    const int32_t *tables, const int32_t *lens, void *out, void *scratch,
-                                   cudaStream_t st);
+                                   int64_t pool_blocks, int *err, cudaStream_t st);
+// pool_slots: block_size * pages of each pool; a slot at or beyond it is skipped and reported through err
 cudaError_t launch_cache_write(int tokens, int kv_heads, int hs, int block_size, const void *key, const void *value,
-                               void *kpool, void *vpool, const int64_t *slots, cudaStream_t st);
+                               void *kpool, void *vpool, const int64_t *slots, int64_t pool_slots, int *err, cudaStream_t st);
 // paged pool -> dense f16 [ctx, kv_heads, hs] per sequence, concatenated in sequence order
 cudaError_t launch_copy_blocks(void *kpool, void *vpool, const int64_t *map_dev, int n_pairs, int64_t bytes_per_block, cudaStream_t st);
 cudaError_t launch_paged_gather(int seqs, int kv_heads, int hs, int block_size, int max_blocks, const void *pool,

@@ -231,6 +231,8 @@ void lower_rope_kv(L &l) {
     p.tokens = (int)tq.ne[2];
     p.kv_heads = t.op_params[12];
     p.block_size = t.op_params[13];
+    if (p.block_size < 1) unsupported(t, "the block size of a cache write must be at least 1");
+    p.pool_slots = l.T(kc).nelements() / ((int64_t)p.kv_heads * p.hs);
     // v arrives as [hs * kv_heads, tokens]
     p.v = view_of(tv);
     p.v.nb[2] = (int64_t)tv.nb[1];
@@ -242,7 +244,7 @@ void lower_rope_kv(L &l) {
     const bool hf = ff >= 0;
     l.push([=](const RunCtx &r) {
         return launch_rope_kv(p, r.at(pq), r.at(pk), r.at(pv), (const int32_t *)r.at(pp), hf ? (const float *)r.at(pf) : nullptr,
-                              r.at(pq16), r.at(pkc), r.at(pvc), (const int64_t *)r.at(psl), r.stream);
+                              r.at(pq16), r.at(pkc), r.at(pvc), (const int64_t *)r.at(psl), r.err, r.stream);
     });
 }
 
@@ -615,9 +617,10 @@ void lower_custom(L &l) {
         ps.buf = BUF_ARENA;
         ps.off = sc < 0 ? 0 : (uint64_t)sc;
         const Place pq = l.place(q), pk = l.place(kc), pv = l.place(vc), pt = l.place(tables), pl = l.place(lens), pd = l.place(l.id);
+        const int64_t pool_blocks = std::min(l.T(kc).nelements(), l.T(vc).nelements()) / ((int64_t)pg.kv_heads * pg.block_size * pg.hs);
         l.push([=](const RunCtx &r) {
             return launch_paged_attention(pg, r.at(pq), r.at(pk), r.at(pv), (const int32_t *)r.at(pt), (const int32_t *)r.at(pl),
-                                          r.at(pd), r.at(ps), r.stream);
+                                          r.at(pd), r.at(ps), pool_blocks, r.err, r.stream);
         });
     } else if (u.kind == 2) {
         const int32_t key = l.src(0), value = l.src(1), kc = l.src(2), vc = l.src(3), slots = l.src(4);
@@ -629,10 +632,12 @@ void lower_custom(L &l) {
             unsupported(t, "the cache write takes contiguous keys and one i64 slot per token");
         if (u.kv_heads < 1 || tk.ne[0] % u.kv_heads != 0 || (tk.ne[0] / u.kv_heads) % 8 != 0) unsupported(t, "head size must be a multiple of 8");
         const int hs = (int)(tk.ne[0] / u.kv_heads);
+        if (u.block_size < 1) unsupported(t, "the block size of a cache write must be at least 1");
+        const int64_t pool_slots = std::min(l.T(kc).nelements(), l.T(vc).nelements()) / ((int64_t)u.kv_heads * hs);
         const Place pk = l.place(key), pv = l.place(value), pkc = l.place(kc), pvc = l.place(vc), psl = l.place(slots);
         const int kvh = u.kv_heads, bs = u.block_size;
         l.push([=](const RunCtx &r) {
-            return launch_cache_write(tokens, kvh, hs, bs, r.at(pk), r.at(pv), r.at(pkc), r.at(pvc), (const int64_t *)r.at(psl), r.stream);
+            return launch_cache_write(tokens, kvh, hs, bs, r.at(pk), r.at(pv), r.at(pkc), r.at(pvc), (const int64_t *)r.at(psl), pool_slots, r.err, r.stream);
         });
     } else {
         unsupported(t, "unknown custom op");

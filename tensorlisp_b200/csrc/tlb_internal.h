@@ -195,5 +195,6 @@ struct tlb_program {
         cudaGraphExec_t exec = nullptr;
     };
     std::vector<Captured> captured;
+    uint32_t kernel_nodes = 0;   // kernel launches in the most recently captured graph
     bool use_graph = true;
 };

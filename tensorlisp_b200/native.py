@@ -250,6 +250,10 @@ class NativeProgram:
     def dispatch_count(self) -> int:
         return int(self.native.L.tlb_program_dispatch_count(self.h))
 
+    def kernel_count(self) -> int:
+        """Kernel launches per run (those of the CUDA graph captured last; 0 before the first run)."""
+        return int(self.native.L.tlb_program_kernel_count(self.h))
+
     def labels(self) -> list[str]:
         return [self.native.L.tlb_program_label(self.h, i).decode() for i in range(self.dispatch_count())]
 

@@ -197,3 +197,4 @@ def _decode_step_case(oracle, cfg, ctx_before, max_ctx, noise_seeds):
     assert err <= max(1e-2, 1.5 * envelope), (err, envelope)
     assert np.array_equal(out["logits"].argmax(axis=1)[decided], want.argmax(axis=1)[decided])
     m.close()
+

@@ -57,8 +57,13 @@ def paged_case(oracle, seqs, heads, kvh, hs, bs, ctxs, seed=0, shuffle=True, ski
     tt = g.input(G.I32, [max_blocks, seqs], "tables")
     tl = g.input(G.I32, [seqs], "lens")
     ts = g.input(G.I32, [2 * (tokens + extra)], "slots")
-    g.paged_cache_write(g.cast(tk, G.F16), g.cast(tv, G.F16), kc, vc, ts, bs, kvh)
-    pa = g.paged_attention(g.cast(tq, G.F16), kc, vc, tt, tl, bs, max_ctx, scale, kvh)
+    # the constructors take the block sizes the reference's scheme layer allows (8, 16, 32); the executor itself
+    # takes any power of two, reached here by rewriting the block-size byte of the nodes' userdata
+    gbs = bs if bs in (8, 16, 32) else 8
+    cw = g.paged_cache_write(g.cast(tk, G.F16), g.cast(tv, G.F16), kc, vc, ts, gbs, kvh)
+    pa = g.paged_attention(g.cast(tq, G.F16), kc, vc, tt, tl, gbs, max_ctx, scale, kvh)
+    for node in (cw, pa):
+        g.tensors[node].op_params[4] = (g.tensors[node].op_params[4] & ~0xff00) | (bs << 8)
     out = g.output(g.cast(pa, G.F32))
     m = Model(g, state_bytes=[pool_elems * 2, pool_elems * 2])
     (got,) = m.run(q.astype(np.float32), key.astype(np.float32), val.astype(np.float32), tables, ctxs,
@@ -71,6 +76,13 @@ def paged_case(oracle, seqs, heads, kvh, hs, bs, ctxs, seed=0, shuffle=True, ski
 @pytest.mark.parametrize("hs,kvh,heads,bs", [(64, 1, 4, 16), (128, 2, 8, 8), (256, 1, 2, 16), (128, 8, 32, 16), (128, 2, 2, 32), (64, 1, 20, 16)])
 def test_paged_matches_dense(oracle, hs, kvh, heads, bs):
     got, want = paged_case(oracle, 4, heads, kvh, hs, bs, [1, 17, 64, 150], seed=hs + bs)
+    close(got, want, 1e-3)
+
+
+@pytest.mark.parametrize("bs", [1, 4, 64])
+def test_block_sizes_outside_the_scheme_layer(oracle, bs):
+    """Pages of fewer than 8 tokens take the copy path with a table lookup per row; pages longer than a tile span tiles."""
+    got, want = paged_case(oracle, 3, 8, 2, 128, bs, [5, 70, 131], seed=bs)
     close(got, want, 1e-3)
 
 
@@ -101,3 +113,77 @@ def test_config3_full_size(oracle):
     ctxs = np.random.default_rng(3).integers(128, 8193, 64)
     got, want = paged_case(oracle, 64, 32, 8, 128, 16, ctxs, seed=33)
     close(got, want, 1e-3)
+
+
+def _bad_index_model(seqs=2, heads=4, kvh=2, hs=64, bs=16, max_ctx=48, n_blocks=6):
+    """A cache write and a paged attention over pools of `n_blocks` pages; returns the model and its shapes."""
+    max_blocks = (max_ctx + bs - 1) // bs
+    tokens = 4
+    pool_elems = n_blocks * kvh * bs * hs
+    g = G.Graph()
+    kc = g.state(G.F16, [pool_elems], "pk")
+    vc = g.state(G.F16, [pool_elems], "pv")
+    tq = g.input(G.F32, [hs, heads, seqs], "q")
+    tk = g.input(G.F32, [hs * kvh, tokens], "k")
+    tv = g.input(G.F32, [hs * kvh, tokens], "v")
+    tt = g.input(G.I32, [max_blocks, seqs], "tables")
+    tl = g.input(G.I32, [seqs], "lens")
+    ts = g.input(G.I32, [2 * tokens], "slots")
+    g.paged_cache_write(g.cast(tk, G.F16), g.cast(tv, G.F16), kc, vc, ts, bs, kvh)
+    g.output(g.cast(g.paged_attention(g.cast(tq, G.F16), kc, vc, tt, tl, bs, max_ctx, 0.125, kvh), G.F32))
+    m = Model(g, state_bytes=[pool_elems * 2, pool_elems * 2])
+    rng = np.random.default_rng(5)
+    inputs = dict(q=rng.standard_normal((seqs, heads, hs)).astype(np.float32),
+                  k=rng.standard_normal((tokens, kvh * hs)).astype(np.float32),
+                  v=rng.standard_normal((tokens, kvh * hs)).astype(np.float32),
+                  tables=np.arange(seqs * max_blocks, dtype=np.int32).reshape(seqs, max_blocks) % n_blocks,
+                  lens=np.full(seqs, max_ctx, np.int32), slots=np.arange(tokens, dtype=np.int64))
+    return m, inputs
+
+
+def _run_bad(m, inputs):
+    return m.run(inputs["q"], inputs["k"], inputs["v"], inputs["tables"], inputs["lens"], inputs["slots"].view(np.int32))
+
+
+@pytest.mark.parametrize("what", ["length beyond the tables", "negative length", "block id beyond the pool", "negative block id",
+                                  "slot beyond the pool"])
+def test_indices_outside_the_tables_or_pools_are_skipped_and_reported(what):
+    """A context length, block id or cache slot that points outside the block tables or the pools never becomes an
+    address: the kernel skips it and sets the program's error word, the run returns Execution with a message that
+    names the cause, and the same program runs cleanly right afterwards with good inputs."""
+    from tensorlisp_b200._lib import TLB_EXECUTION, TlbError
+    m, good = _bad_index_model()
+    (clean,) = _run_bad(m, good)
+    bad = {k: v.copy() for k, v in good.items()}
+    if what == "length beyond the tables":
+        bad["lens"][1] = 48 + 1000
+    elif what == "negative length":
+        bad["lens"][0] = -7
+    elif what == "block id beyond the pool":
+        bad["tables"][1, 2] = 6          # pools hold pages 0..5
+    elif what == "negative block id":
+        bad["tables"][0, 0] = -3
+    else:
+        bad["slots"][2] = 6 * 16         # first slot past the last page
+    with pytest.raises(TlbError) as e:
+        _run_bad(m, bad)
+    assert e.value.status == TLB_EXECUTION and "out of range" in str(e.value)
+    (again,) = _run_bad(m, good)
+    assert np.array_equal(again, clean)
+    m.close()
+
+
+def test_cache_write_with_block_size_zero_is_refused():
+    from tensorlisp_b200._lib import TlbError
+    g = G.Graph()
+    kc = g.state(G.F16, [4096], "pk")
+    vc = g.state(G.F16, [4096], "pv")
+    tk = g.input(G.F32, [128, 2], "k")
+    tv = g.input(G.F32, [128, 2], "v")
+    ts = g.input(G.I32, [4], "slots")
+    node = g.paged_cache_write(g.cast(tk, G.F16), g.cast(tv, G.F16), kc, vc, ts, 8, 2)
+    g.tensors[node].op_params[4] &= ~0xff00      # the host mirror refuses a block size of 0 itself: clear the bits behind it
+    g.output(node)
+    with pytest.raises(TlbError) as e:
+        Model(g, state_bytes=[8192, 8192])
+    assert "block size" in str(e.value)

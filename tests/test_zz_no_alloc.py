@@ -86,6 +86,19 @@ def test_static_scratch_attention_matches_the_program_path():
                                       4096, 64, 8, 128, 16, 4096, 65535, scale)
     del os.environ["TLB_PA_CHUNK"]
     assert st == TLB_INVALID and b"built-in scratch holds" in L.tlb_last_error()
+
+    # a context length beyond the table row is cut on the device and reported, not followed past the row; the
+    # next call with the true lengths gives the same bytes as before
+    from tensorlisp_b200._lib import TLB_EXECUTION
+    bad = ctxs.copy()
+    bad[2] = max_ctx + 5000
+    l_dev.write(0, bad)
+    args = (n.dev, C.c_void_p(q_dev.device_ptr), C.c_void_p(kptr), C.c_void_p(vptr), C.c_void_p(t_dev.device_ptr),
+            C.c_void_p(l_dev.device_ptr), C.c_void_p(o_dev.device_ptr), seqs, heads, kvh, hs, bs, max_blocks, max_ctx, scale)
+    assert L.tlb_paged_attention_static(*args) == TLB_EXECUTION and b"out of range" in L.tlb_last_error()
+    l_dev.write(0, ctxs)
+    check(L.tlb_paged_attention_static(*args))
+    assert np.array_equal(o_dev.read(0, seqs * heads * hs * 2).view(np.float16).reshape(seqs, heads, hs), got)
     for b in (q_dev, t_dev, l_dev, o_dev):
         b.free()
     m.close()
