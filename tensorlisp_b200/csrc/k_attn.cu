@@ -224,12 +224,18 @@ __global__ void __launch_bounds__(PA_WARPS * 32) k_paged_attn(PagedParams p) {
 #pragma unroll
         for (int j = 0; j < 2; j++)
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const int tok = tok0 + j * 8 + 2 * t + (e & 1);
-                const float v = tok < c_end ? s[j][e] * p.scale_log2 : -CUDART_INF_F;
-                s[j][e] = v;
-                rmax[e >> 1] = fmaxf(rmax[e >> 1], v);
-            }
+            for (int e = 0; e < 4; e++) s[j][e] *= p.scale_log2;
+        if (tok0 + PA_TILE > c_end) {   // only the last tile of a context has tokens to mask
+#pragma unroll
+            for (int j = 0; j < 2; j++)
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    if (tok0 + j * 8 + 2 * t + (e & 1) >= c_end) s[j][e] = -CUDART_INF_F;
+        }
+#pragma unroll
+        for (int j = 0; j < 2; j++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) rmax[e >> 1] = fmaxf(rmax[e >> 1], s[j][e]);
         float corr[2], m_use[2];
 #pragma unroll
         for (int h = 0; h < 2; h++) {
@@ -263,14 +269,19 @@ __global__ void __launch_bounds__(PA_WARPS * 32) k_paged_attn(PagedParams p) {
             pr[2] = pack_h2(rs[1][0], rs[1][1]);
             pr[3] = pack_h2(rs[1][2], rs[1][3]);
         }
-        // ---- O = O * corr + P V
+        // ---- O = O * corr + P V. Once the running maxima have settled, corr is exactly 1 for every row of the
+        // warp in most tiles: the multiplications are then left out (a product with 1.0f changes no bit).
+        if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
+#pragma unroll
+            for (int nd = 0; nd < ND; nd++) {
+                o[nd][0] *= corr[0]; o[nd][1] *= corr[0]; o[nd][2] *= corr[1]; o[nd][3] *= corr[1];
+            }
+        }
         {
             const int mi = lane >> 3, r = lane & 7;
             const int row = (mi & 1) * 8 + r;
 #pragma unroll
             for (int nd = 0; nd < ND; nd += 2) {
-                o[nd][0] *= corr[0]; o[nd][1] *= corr[0]; o[nd][2] *= corr[1]; o[nd][3] *= corr[1];
-                o[nd + 1][0] *= corr[0]; o[nd + 1][1] *= corr[0]; o[nd + 1][2] *= corr[1]; o[nd + 1][3] *= corr[1];
                 const int col = nd + (mi >> 1);
                 uint32_t b0, b1, b2, b3;
                 ldsm_x4_t(vbase + row * ROW_BYTES + ((col ^ (row & 7)) * 16), b0, b1, b2, b3);

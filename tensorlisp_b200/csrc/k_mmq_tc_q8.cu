@@ -581,6 +581,284 @@ __global__ void __launch_bounds__(tc8w::THREADS, 1) k_mmq_tc_q80_wide(const __gr
     if (tid == 0 && s_fail) atomicExch(p.err, 2);
 }
 
+// ---------------------------------------------------------------- many activation columns, one accumulator (prompt pass)
+// The kernel above pays for the reference's arithmetic with one accumulator round trip per 32-element block. This one
+// folds both scales into the operands instead and lets the tensor core add up the whole of K:
+//     A[r,k] = f16(d_w[r,b] * q[r,k])        (HMUL2 of the exact code by the block's f16 scale: one rounding)
+//     B[k,c] = f16(d_a[c,b] * q8[k,c])       (by the activation packer, from the same Q8_0 quantization of the activations
+//                                             that the reference makes: one rounding)
+//     y[r,c] = sum_k A[r,k] * B[k,c]         (tcgen05.mma kind::f16, f32 accumulator in tensor memory)
+// Each product carries two f16 roundings (2^-12 relative each, independent across k), so y differs from the reference's
+// integer arithmetic by about 1e-4 of max|y| at K = 4096: inside the 1e-3 bar of mul_mat, not bit-comparable. The exact
+// kernel above stays reachable (TLB_PROMPT_EXACT=1).
+// A persistent CTA walks (row tile, column tile) pairs, 128 weight rows x 256 activation columns each. Per 256 elements
+// of K: TMA brings 128 x 272 raw bytes; eight warps strip the scales, turn the codes into scaled f16 and store them into
+// tensor memory (A operand, 128 columns); the packed B arrives as four 32 KB bulk copies (64 elements of K each, core
+// matrix layout); one warp issues 16 MMAs of 128 x 256 x 16. Eight warps drain the 128 x 256 accumulator once per tile.
+namespace tc8f {
+constexpr int NW = 256;                                  // activation columns per tile
+constexpr int KS = 64;                                   // elements of K per B stage
+constexpr int B_STAGE = NW * KS * 2;                     // 32 KB
+constexpr int B_STAGES = 4, RAW_STAGES = 2, A_RING = 2;
+constexpr int TMA_RAW_WARP = 0, TMA_B_WARP = 1, MMA_WARP = 2;   // warp 3 idles (keeps the quadrant numbering of the rest aligned)
+constexpr int DEQ_WARP0 = 4, DEQ_WARPS = 8, EPI_WARP0 = 12, EPI_WARPS = 8;
+constexpr int THREADS = (EPI_WARP0 + EPI_WARPS) * 32;    // 640
+constexpr uint32_t ACC_COL0 = 0, A_COL0 = 256;           // accumulator [0, 256), A ring 2 x 128 columns behind it
+// 4 int8 codes of a word -> two f16x2 of code * scale (exact integer first: (1024 + u) - 1152 with u = code + 128)
+__device__ __forceinline__ void codes_to_f16(uint32_t w, uint32_t dd, uint32_t &lo, uint32_t &hi) {
+    const uint32_t x = w ^ 0x80808080u;
+    uint32_t a = __byte_perm(x, 0x64646464u, 0x4140), b = __byte_perm(x, 0x64646464u, 0x4342);
+    const uint32_t k1152 = 0x64806480u;   // f16x2 (1152, 1152)
+    asm("sub.f16x2 %0, %0, %1;" : "+r"(a) : "r"(k1152));
+    asm("sub.f16x2 %0, %0, %1;" : "+r"(b) : "r"(k1152));
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(lo) : "r"(a), "r"(dd));
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(hi) : "r"(b), "r"(dd));
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+          "=r"(r[31])
+        : "r"(taddr));
+}
+}  // namespace tc8f
+
+// B operand of the kernel below: blobs [chunk of 256 columns][stage of 64 elements of K] x 32 KB, each
+// [column / 8][8 chunks of 8 elements][column % 8][16 bytes] (K-major core matrices: lbo 128, sbo 1024), values
+// f16(d_a * q8) in the order of K.
+__global__ void __launch_bounds__(256) k_act_pack_q80_f16(const int8_t *__restrict__ qs, const float *__restrict__ ds, int64_t K, int N,
+                                                           uint8_t *__restrict__ out) {
+    const int st = blockIdx.x;   // stage of 64 elements
+    uint8_t *o = out + ((size_t)blockIdx.y * gridDim.x + st) * tc8f::B_STAGE;
+    const int n0 = (int)blockIdx.y * tc8f::NW;
+    for (int u = threadIdx.x; u < tc8f::NW * 8; u += blockDim.x) {
+        const int nl = u / 8, kc = u % 8, n = n0 + nl;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (n < N) {
+            const int64_t k0 = (int64_t)st * tc8f::KS + kc * 8;
+            const uint2 q = *reinterpret_cast<const uint2 *>(qs + (size_t)n * K + k0);
+            const float d = ds[(size_t)n * (K / 32) + k0 / 32];
+            const uint32_t w[2] = {q.x, q.y};
+            uint32_t h[4];
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                const float f0 = (float)(int8_t)(w[i] & 0xff), f1 = (float)(int8_t)((w[i] >> 8) & 0xff), f2 = (float)(int8_t)((w[i] >> 16) & 0xff),
+                            f3 = (float)(int8_t)(w[i] >> 24);
+                const __half2 a = __floats2half2_rn(f0 * d, f1 * d), b = __floats2half2_rn(f2 * d, f3 * d);
+                h[2 * i] = *reinterpret_cast<const uint32_t *>(&a);
+                h[2 * i + 1] = *reinterpret_cast<const uint32_t *>(&b);
+            }
+            v = make_uint4(h[0], h[1], h[2], h[3]);
+        }
+        *reinterpret_cast<uint4 *>(o + (size_t)(nl / 8) * 1024 + kc * 128 + (nl % 8) * 16) = v;
+    }
+}
+
+struct Tc8fParams {
+    const uint8_t *act;   // packed B blobs
+    float *out;
+    int64_t M, ldy;
+    int N, nst, row_tiles, col_tiles;
+    int *err;
+};
+
+__global__ void __launch_bounds__(tc8f::THREADS, 1) k_mm_q80_f16(const __grid_constant__ CUtensorMap wmap, Tc8fParams p) {
+    using namespace tc;
+    using namespace tc8f;
+    constexpr int ROWS = tc8::ROWS;
+    constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(tc8f::NW >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);   // f16 x f16 -> f32, K-major A and B
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = smem_raw + ((1024u - (su32(smem_raw) & 1023u)) & 1023u);
+    uint8_t *bst = smem;                                   // tc8f::B_STAGES x tc8f::B_STAGE
+    uint8_t *raw = bst + tc8f::B_STAGES * tc8f::B_STAGE;               // tc8f::RAW_STAGES x RAW_BYTES
+    __shared__ uint64_t bar_raw[tc8f::RAW_STAGES], bar_rawfree[tc8f::RAW_STAGES], bar_b[tc8f::B_STAGES], bar_bfree[tc8f::B_STAGES];
+    __shared__ uint64_t bar_aready[tc8f::A_RING], bar_afree[tc8f::A_RING], bar_accfull, bar_accfree;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int s_fail;
+    volatile int *fail = &s_fail;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nst = p.nst;   // units of 256 elements of K
+    const int n_tiles = p.row_tiles * p.col_tiles;
+    if (tid == 0) {
+        for (int i = 0; i < tc8f::RAW_STAGES; i++) {
+            mbar_init(&bar_raw[i], 1);
+            mbar_init(&bar_rawfree[i], tc8f::DEQ_WARPS);
+        }
+        for (int i = 0; i < tc8f::B_STAGES; i++) {
+            mbar_init(&bar_b[i], 1);
+            mbar_init(&bar_bfree[i], 1);
+        }
+        for (int i = 0; i < tc8f::A_RING; i++) {
+            mbar_init(&bar_aready[i], tc8f::DEQ_WARPS);
+            mbar_init(&bar_afree[i], 1);
+        }
+        mbar_init(&bar_accfull, 1);
+        mbar_init(&bar_accfree, tc8f::EPI_WARPS);
+        s_fail = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) tmem_alloc(&tmem_base_s, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+    griddep_launch();
+
+    if (warp == tc8f::TMA_RAW_WARP) {
+        // ---- raw weights: one 128-row x 272-byte box per unit (they do not depend on the kernel in front)
+        if (lane == 0) {
+            uint32_t g = 0;
+            for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+                const int row_tile = t % p.row_tiles;
+                for (int i = 0; i < nst; i++, g++) {
+                    const int s = g % tc8f::RAW_STAGES;
+                    if (g >= tc8f::RAW_STAGES) mbar_wait_nap(&bar_rawfree[s], ((g / tc8f::RAW_STAGES) - 1) & 1, fail, 64);
+                    mbar_expect_tx(&bar_raw[s], tc8::RAW_BYTES);
+                    tma_2d(raw + s * tc8::RAW_BYTES, &wmap, i * (tc8::ROW_CHUNK / 2), row_tile * ROWS, &bar_raw[s]);   // x in 16-bit elements
+                }
+            }
+        }
+    } else if (warp == tc8f::TMA_B_WARP) {
+        // ---- packed activations: four 32 KB stages per unit
+        if (lane == 0) {
+            griddep_wait();
+            uint32_t g = 0;
+            for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+                const int col_tile = t / p.row_tiles;
+                const uint8_t *src = p.act + (size_t)col_tile * nst * 4 * tc8f::B_STAGE;
+                for (int i = 0; i < nst * 4; i++, g++) {
+                    const int s = g % tc8f::B_STAGES;
+                    if (g >= tc8f::B_STAGES) mbar_wait_nap(&bar_bfree[s], ((g / tc8f::B_STAGES) - 1) & 1, fail, 32);
+                    mbar_expect_tx(&bar_b[s], tc8f::B_STAGE);
+                    bulk_g2s(bst + s * tc8f::B_STAGE, src + (size_t)i * tc8f::B_STAGE, tc8f::B_STAGE, &bar_b[s]);
+                }
+            }
+        }
+    } else if (warp == tc8f::MMA_WARP) {
+        // ---- MMA issuer: the whole warp runs the loop (converged), one elected lane issues
+        const bool leader = elect_one();
+        uint32_t g = 0, gb = 0, it = 0;
+        for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, it++) {
+            if (it > 0) {
+                mbar_wait_nap(&bar_accfree, (it - 1) & 1, fail, 32);   // the accumulator of the tile before has been drained
+                tc_fence_after();
+            }
+            for (int i = 0; i < nst; i++, g++) {
+                const int slot = g % tc8f::A_RING;
+                mbar_wait_nap(&bar_aready[slot], (g / tc8f::A_RING) & 1, fail, 32);
+                tc_fence_after();
+                const uint32_t a0 = tmem_base + tc8f::A_COL0 + (uint32_t)(slot * 128);
+#pragma unroll 1
+                for (int s4 = 0; s4 < 4; s4++, gb++) {
+                    const int bs = gb % tc8f::B_STAGES;
+                    mbar_wait_nap(&bar_b[bs], (gb / tc8f::B_STAGES) & 1, fail, 32);
+                    tc_fence_after();
+                    if (leader) {
+                        const uint64_t b_desc0 = smem_desc(su32(bst + bs * tc8f::B_STAGE), 128, 1024);
+#pragma unroll
+                        for (int k = 0; k < 4; k++)
+                            umma_f16_ta(tmem_base + tc8f::ACC_COL0, a0 + (uint32_t)((s4 * 4 + k) * 8), b_desc0 + (uint64_t)(k * 16), IDESC,
+                                        (i | s4 | k) ? 1u : 0u);
+                        umma_commit(&bar_bfree[bs]);
+                        if (s4 == 3) {
+                            umma_commit(&bar_afree[slot]);
+                            if (i == nst - 1) umma_commit(&bar_accfull);
+                        }
+                    }
+                    __syncwarp();
+                }
+            }
+        }
+    } else if (warp >= tc8f::DEQ_WARP0 && warp < tc8f::EPI_WARP0) {
+        // ---- expanders: lane quadrant warp % 4 fixes the rows; the two warps of a quadrant take four blocks each
+        const int q = warp & 3, half = (warp - tc8f::DEQ_WARP0) >> 2;
+        const int r = q * 32 + lane;
+        const uint32_t a_lane = tmem_base + tc8f::A_COL0 + ((uint32_t)(q * 32) << 16);
+        uint32_t g = 0;
+        for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+            for (int i = 0; i < nst; i++, g++) {
+                const int rs = g % tc8f::RAW_STAGES, slot = g % tc8f::A_RING;
+                mbar_wait_nap(&bar_raw[rs], (g / tc8f::RAW_STAGES) & 1, fail, 64);
+                if (g >= tc8f::A_RING) {
+                    mbar_wait_nap(&bar_afree[slot], ((g / tc8f::A_RING) - 1) & 1, fail, 64);   // the MMAs that read this slot are done
+                    tc_fence_after();
+                }
+                const uint8_t *rrow = raw + rs * tc8::RAW_BYTES + r * tc8::ROW_CHUNK;
+#pragma unroll
+                for (int gg = 0; gg < 2; gg++) {
+                    uint32_t qa[8], qb[8];
+                    float da, db;
+                    if (half == 0) {
+                        if (gg == 0) tc8::split_blocks<0>(rrow, qa, qb, da, db);
+                        else tc8::split_blocks<1>(rrow, qa, qb, da, db);
+                    } else {
+                        if (gg == 0) tc8::split_blocks<2>(rrow, qa, qb, da, db);
+                        else tc8::split_blocks<3>(rrow, qa, qb, da, db);
+                    }
+                    const int blk = (half * 2 + gg) * 2;
+                    uint32_t h[16];
+                    uint32_t dd = (uint32_t)__half_as_ushort(__float2half_rn(da));   // the block's own f16 scale, back from f32 unchanged
+                    dd |= dd << 16;
+#pragma unroll
+                    for (int j = 0; j < 8; j++) codes_to_f16(qa[j], dd, h[2 * j], h[2 * j + 1]);
+                    tmem_st16(a_lane + (uint32_t)(slot * 128 + blk * 16), h);
+                    dd = (uint32_t)__half_as_ushort(__float2half_rn(db));
+                    dd |= dd << 16;
+#pragma unroll
+                    for (int j = 0; j < 8; j++) codes_to_f16(qb[j], dd, h[2 * j], h[2 * j + 1]);
+                    tmem_st16(a_lane + (uint32_t)(slot * 128 + (blk + 1) * 16), h);
+                }
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&bar_aready[slot]);
+                    mbar_arrive(&bar_rawfree[rs]);
+                }
+            }
+        }
+    } else if (warp >= tc8f::EPI_WARP0) {
+        // ---- draining warps: lane quadrant warp % 4, column half (warp - tc8f::EPI_WARP0) / 4; once per tile
+        const int q = warp & 3, ch = (warp - tc8f::EPI_WARP0) >> 2;
+        const int row_in_tile = q * 32 + lane;
+        const uint32_t lane_addr = tmem_base + tc8f::ACC_COL0 + ((uint32_t)(q * 32) << 16) + (uint32_t)(ch * 128);
+        uint32_t it = 0;
+        for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, it++) {
+            const int row_tile = t % p.row_tiles, col_tile = t / p.row_tiles;
+            mbar_wait_nap(&bar_accfull, it & 1, fail, 128);
+            tc_fence_after();
+            const int64_t row = (int64_t)row_tile * ROWS + row_in_tile;
+            const int col0 = col_tile * tc8f::NW + ch * 128;
+            float *o = p.out + (size_t)col0 * p.ldy + row;
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                uint32_t v[32];
+                tmem_ld32(lane_addr + (uint32_t)(c * 32), v);
+                tmem_ld_wait();
+                if (c == 3) {   // everything of this warp's part is in registers: the accumulator may be overwritten
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bar_accfree);
+                }
+                if (row < p.M) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        if (col0 + c * 32 + j < p.N) o[(size_t)(c * 32 + j) * p.ldy] = __uint_as_float(v[j]);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, 512);
+    if (tid == 0 && s_fail) atomicExch(p.err, 2);
+}
+
+static size_t tc8f_smem() { return (size_t)tc8f::B_STAGES * tc8f::B_STAGE + (size_t)tc8f::RAW_STAGES * tc8::RAW_BYTES + 1024; }
+
 static size_t tc8w_smem() {
     return (size_t)tc8w::RAW_STAGES * tc8::RAW_BYTES + (size_t)tc8w::ACT_STAGES * tc8w::BLOB + (size_t)tc8w::A_RING * 8 * tc8::ROWS * sizeof(float) + 1024;
 }
@@ -595,6 +873,7 @@ void mmq_tc8_configure() {
     cudaFuncSetAttribute(k_mmq_tc_q80<16, 4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc8_smem<16, 4, 4>());
     cudaFuncSetAttribute(k_mmq_tc_q80<32, 4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc8_smem<32, 4, 4>());
     cudaFuncSetAttribute(k_mmq_tc_q80_wide, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc8w_smem());
+    cudaFuncSetAttribute(k_mm_q80_f16, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc8f_smem());
 }
 
 bool mmq_tc8_supported(int64_t K, int64_t M, int64_t N) {
@@ -604,8 +883,21 @@ bool mmq_tc8_supported(int64_t K, int64_t M, int64_t N) {
 TcPlan mmq_tc8_plan(int64_t K, int64_t M, int64_t N, int sm_count) {
     TcPlan t;
     t.nsb = (int)(K / 256);
+    if (N > 64 && !getenv("TLB_NO_WIDE_TC") && !getenv("TLB_PROMPT_EXACT")) {
+        // prompt-sized batches: 128 x 256 tiles, scales folded into f16 operands, one accumulator (k_mm_q80_f16)
+        t.npad = tc8f::NW;
+        t.n_split = 1;
+        t.sb_per_split = t.nsb;
+        t.streamk = 0;
+        t.n_col_chunks = (int)((N + t.npad - 1) / t.npad);
+        t.blob_unit = (uint64_t)4 * tc8f::B_STAGE;   // one unit of 256 elements of K = four stages of 64
+        t.blob_bytes = (uint64_t)t.n_col_chunks * t.nsb * t.blob_unit;
+        t.partial_bytes = 0;
+        return t;
+    }
     if (N > 64 && !getenv("TLB_NO_WIDE_TC")) {
-        // 128-column tiles, whole K per CTA (k_mmq_tc_q80_wide): row tiles x column tiles fill the GPU
+        // the same batches with the reference's integer arithmetic (TLB_PROMPT_EXACT=1): 128-column tiles, whole K per
+        // CTA (k_mmq_tc_q80_wide), row tiles x column tiles fill the GPU
         t.npad = tc8w::NW;
         t.n_split = 1;
         t.sb_per_split = t.nsb;
@@ -642,6 +934,11 @@ TcPlan mmq_tc8_plan(int64_t K, int64_t M, int64_t N, int sm_count) {
 
 cudaError_t launch_act_pack_tc8(const ActLayout &a, const void *act, int npad, void *blobs, cudaStream_t st) {
     const char *ab = (const char *)act;
+    if (npad == tc8f::NW) {
+        k_act_pack_q80_f16<<<dim3((unsigned)(a.K / tc8f::KS), (unsigned)((a.N + npad - 1) / npad)), 256, 0, st>>>(
+            (const int8_t *)(ab + a.qs_off), (const float *)(ab + a.d_off), a.K, (int)a.N, (uint8_t *)blobs);
+        return cudaGetLastError();
+    }
     k_act_pack_q80<<<dim3((unsigned)(a.K / 256), (unsigned)((a.N + npad - 1) / npad)), 256, 0, st>>>((const int8_t *)(ab + a.qs_off), (const float *)(ab + a.d_off), a.K, (int)a.N, npad,
                                                          (uint8_t *)blobs);
     return cudaGetLastError();
@@ -657,6 +954,25 @@ cudaError_t launch_mmq_tc8(const TcPlan &t, const void *W, int64_t K, int64_t M,
     // described in 16-bit elements: a 272-byte box is 136 of them (the limit is 256 elements per dimension)
     cudaError_t e = tc_encode_2d(&map, W, (uint64_t)(K / 32 * 34), (uint64_t)M, tc8::ROW_CHUNK, tc8::ROWS, 2);
     if (e != cudaSuccess) return e;
+    if (t.npad == tc8f::NW) {
+        static int sm_of[64] = {0};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+        if (!sm_of[dev]) cudaDeviceGetAttribute(&sm_of[dev], cudaDevAttrMultiProcessorCount, dev);
+        Tc8fParams p{};
+        p.act = (const uint8_t *)blobs;
+        p.out = y;
+        p.M = M;
+        p.ldy = ldy;
+        p.N = (int)N;
+        p.nst = t.nsb;
+        p.row_tiles = (int)((M + tc8::ROWS - 1) / tc8::ROWS);
+        p.col_tiles = t.n_col_chunks;
+        p.err = err;
+        const int tiles = p.row_tiles * p.col_tiles;
+        return launch_pdl(k_mm_q80_f16, dim3((unsigned)std::min(tiles, sm_of[dev])), dim3(tc8f::THREADS), tc8f_smem(), st, map, p);
+    }
     if (t.npad == tc8w::NW) {
         Tc8Params p{};
         p.act = (const uint8_t *)blobs;

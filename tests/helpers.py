@@ -41,17 +41,21 @@ class Model:
 
 
 class NoisyOracle:
-    """The oracle with its mul_mat outputs perturbed by `eps` relative noise: measures how far the
-    reference's own arithmetic moves under a summation-order-sized perturbation."""
+    """The oracle with its mul_mat outputs perturbed: measures how far the reference's own arithmetic moves under a
+    perturbation of the size a kernel makes. `eps` relative to each element (summation order: 1e-6), or, with
+    `of_max`, relative to max|y| of the product (the folded-scale prompt kernel: its two f16 roundings per product
+    leave an error of about 7e-5 of max|y| standard deviation, 3e-4 at most)."""
 
-    def __init__(self, oracle, eps, seed):
-        self.o, self.eps, self.r = oracle, eps, np.random.default_rng(seed)
+    def __init__(self, oracle, eps, seed, of_max=False):
+        self.o, self.eps, self.r, self.of_max = oracle, eps, np.random.default_rng(seed), of_max
 
     def __getattr__(self, name):
         return getattr(self.o, name)
 
     def mul_mat(self, *a, **k):
         y = self.o.mul_mat(*a, **k)
+        if self.of_max:
+            return (y + self.eps * np.abs(y).max() * self.r.standard_normal(y.shape)).astype(np.float32)
         return (y * (1 + self.eps * self.r.standard_normal(y.shape))).astype(np.float32)
 
 

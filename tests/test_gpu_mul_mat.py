@@ -45,22 +45,42 @@ def test_shapes(oracle, ty, name, K, M, N):
     m, _ = mm_model(ty, K, M, N, Wq)
     (y,) = m.run(X)
     err = close(y, oracle.mul_mat(ty, Wq, K, X), TOL)
-    assert err <= 2e-5 * np.abs(y).max() + 1e-6   # only the f32 summation order differs
-    # and it is the reference's arithmetic, not dequantize-then-f32: that differs by ~5e-3
+    if name == "q8_0" and N > 64:
+        # prompt-sized Q8_0 batches: both block scales folded into f16 operands (two f16 roundings per product)
+        assert err <= 5e-4 * np.abs(y).max() + 1e-6
+    else:
+        assert err <= 2e-5 * np.abs(y).max() + 1e-6   # only the f32 summation order differs
+    # either way it is the reference's arithmetic (activations quantized to int8 blocks first), not
+    # dequantize-then-f32: that differs by ~5e-3
     m.close()
 
 
-@pytest.mark.parametrize("K,M,N", [(2048, 300, 300), (4096, 1024, 1000), (512, 130, 128), (14336, 256, 257)])
-def test_q8_0_many_columns(oracle, K, M, N):
-    """Prompt-sized batches take 128-column tiles on the tensor cores: same integers, ragged rows and columns."""
+@pytest.mark.parametrize("exact", [False, True])
+@pytest.mark.parametrize("K,M,N", [(2048, 300, 300), (4096, 1024, 1000), (512, 130, 128), (14336, 256, 257), (4096, 4096, 2048)])
+def test_q8_0_many_columns(oracle, K, M, N, exact):
+    """Prompt-sized batches on the tensor cores, ragged rows and columns. The default kernel folds both block scales into
+    f16 operands and lets the tensor core add up all of K (two f16 roundings per product): within the 1e-3 bar of mul_mat,
+    measured around 1e-4 of max|y|. TLB_PROMPT_EXACT=1 selects the kernel that keeps the reference's integers (one int32
+    accumulator per 32-element block): that one agrees to f32 rounding."""
+    import os
     rng = np.random.default_rng(K + M + N)
     W = (rng.standard_normal((M, K)) * 0.02).astype(np.float32)
     X = rng.standard_normal((N, K)).astype(np.float32)
     Wq = oracle.quantize(Q8_0, W)
-    m, _ = mm_model(Q8_0, K, M, N, Wq)
+    if exact:
+        os.environ["TLB_PROMPT_EXACT"] = "1"
+    try:
+        m, _ = mm_model(Q8_0, K, M, N, Wq)
+    finally:
+        os.environ.pop("TLB_PROMPT_EXACT", None)
     (y,) = m.run(X)
-    err = close(y, oracle.mul_mat(Q8_0, Wq, K, X), TOL)
-    assert err <= 2e-5 * np.abs(y).max() + 1e-6
+    want = oracle.mul_mat(Q8_0, Wq, K, X)
+    err = close(y, want, TOL)
+    print("q8_0 [%d x %d] x %d columns, %s kernel: max error %.2e of max|y|" % (M, K, N, "exact" if exact else "folded-scale", err / np.abs(want).max()))
+    if exact:
+        assert err <= 2e-5 * np.abs(y).max() + 1e-6
+    else:
+        assert err <= 5e-4 * np.abs(want).max()     # half the bar: the two f16 roundings per product, not more
     m.close()
 
 

@@ -60,8 +60,13 @@ def oracle_prefill(oracle, cfg, specs, weights, ids, pos, n_seqs, n_tokens):
     return lin("output", x)
 
 
+@pytest.mark.parametrize("exact", [True, False])
 @pytest.mark.parametrize("n_seqs,n_tokens", [(2, 80), (3, 37)])
-def test_prefill(oracle, n_seqs, n_tokens):
+def test_prefill(oracle, n_seqs, n_tokens, exact):
+    """exact: the prompt mul_mat that keeps the reference's integers (TLB_PROMPT_EXACT=1), judged against the oracle's
+    sensitivity to summation-order noise (1e-6). Otherwise the default folded-scale kernel, judged against the oracle's
+    sensitivity to that kernel's own error (7e-5 of max|y| per product, measured in test_gpu_mul_mat.py)."""
+    import os
     cfg = DecoderConfig(n_layers=2, d_model=512, n_heads=4, n_kv_heads=2, head_dim=128, d_ffn=1024, vocab=1024, wtype=Q8_0)
     dg = prefill_step(cfg, n_seqs, n_tokens)
     g = dg.graph
@@ -73,7 +78,12 @@ def test_prefill(oracle, n_seqs, n_tokens):
     taps = [(n, by_name["blk.0." + n]) for n in ("q_rope", "k16", "v16", "attn")]
     for _, t in taps:
         g.keep.append(t)
-    m = Model(g, weights, dg.state_bytes, [("logits", dg.logits)] + taps)
+    if exact:
+        os.environ["TLB_PROMPT_EXACT"] = "1"
+    try:
+        m = Model(g, weights, dg.state_bytes, [("logits", dg.logits)] + taps)
+    finally:
+        os.environ.pop("TLB_PROMPT_EXACT", None)
     ids = rng.integers(0, cfg.vocab, T).astype(np.int32)
     pos = np.tile(np.arange(n_tokens, dtype=np.int32), n_seqs)
     blocks_per_seq = (n_tokens + bs - 1) // bs
@@ -102,16 +112,17 @@ def test_prefill(oracle, n_seqs, n_tokens):
     want = oracle_prefill(oracle, cfg, dg.weights, weights, ids, pos, n_seqs, n_tokens)
     envelope = 0.0
     for seed in range(3):
-        noisy = oracle_prefill(NoisyOracle(oracle, 1e-6, seed), cfg, dg.weights, weights, ids, pos, n_seqs, n_tokens)
+        noise = NoisyOracle(oracle, 1e-6, seed) if exact else NoisyOracle(oracle, 7e-5, seed, of_max=True)
+        noisy = oracle_prefill(noise, cfg, dg.weights, weights, ids, pos, n_seqs, n_tokens)
         envelope = max(envelope, float(np.abs(noisy - want).max()))
     err = float(np.abs(logits.reshape(want.shape) - want).max())
     top2 = np.sort(want, axis=1)[:, -2:]
     decided = (top2[:, 1] - top2[:, 0]) > 2 * max(err, envelope)
     same_top1 = logits.reshape(want.shape).argmax(axis=1) == want.argmax(axis=1)
     plain_bar = err <= 1e-2 and bool(same_top1.all())
-    print("prompt pass %d x %d: end-to-end logits error %.3e (the oracle's own 1e-6-noise envelope %.3e), top-1 equal in %d of %d rows, "
+    print("prompt pass %d x %d, %s mul_mat: end-to-end logits error %.3e (the oracle's own envelope under %s noise %.3e), top-1 equal in %d of %d rows, "
           "%d rows undecided at that noise; the plain bar (1e-2 abs, identical top-1) %s"
-          % (n_seqs, n_tokens, err, envelope, int(same_top1.sum()), len(same_top1), int((~decided).sum()), "holds" if plain_bar else "does not hold"))
+          % (n_seqs, n_tokens, "exact" if exact else "folded-scale", err, "1e-6 relative" if exact else "7e-5-of-max", envelope, int(same_top1.sum()), len(same_top1), int((~decided).sum()), "holds" if plain_bar else "does not hold"))
     assert err <= max(1e-2, 1.5 * envelope), (err, envelope)
     assert np.array_equal(logits.reshape(want.shape).argmax(axis=1)[decided], want.argmax(axis=1)[decided])
     m.close()
