@@ -214,6 +214,7 @@ static void configure_kernels_once(int ordinal) {
     attn_configure();
     mmq_tc_configure();
     mmq_tc8_configure();
+    flash_tc_configure();
     g_configured_ordinals |= bit;
 }
 

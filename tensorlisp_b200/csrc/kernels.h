@@ -160,6 +160,14 @@ struct FlashArgs {
 };
 bool flash_supported(int64_t d, int64_t dv);
 cudaError_t launch_flash_attn(const FlashArgs &p, const void *q, const void *k, const void *v, const void *mask, float *out, cudaStream_t st);
+// ---------------------------------------------------------------- k_flash_tc.cu
+// The same op on tcgen05 for prompt-sized query counts (head size 128, f16 keys / values, no soft cap, no ALiBi);
+// scratch holds the packed operands and the per-tile mask flags.
+bool flash_tc_supported(const FlashArgs &p, bool has_mask);
+uint64_t flash_tc_scratch_bytes(const FlashArgs &p, bool has_mask);
+cudaError_t launch_flash_attn_tc(const FlashArgs &p, const void *q, const void *k, const void *v, const void *mask, float *out, void *scratch,
+                                 int *err, cudaStream_t st);
+void flash_tc_configure();
 
 // Values of the device error word behind a program's arena: 1-3 are bounded waits that gave up (GEMV copies, tensor-core
 // pipelines, the peer exchange); 4 is a context length, block id or cache slot from the caller that a kernel skipped

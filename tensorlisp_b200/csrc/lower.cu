@@ -645,23 +645,23 @@ void lower_custom(L &l) {
 }
 
 // ---- FLASH_ATTN_EXT (lower.rs:575-657): dense attention, result [dv, heads, queries, batch] f32
-void lower_flash(L &l) {
-    const Tensor &t = l.t();
-    const int32_t q = l.src(0), k = l.src(1), v = l.src(2);
+// The kernel arguments of a node, or a reason why it is not supported
+static const char *flash_args(const Graph &g, const Tensor &t, FlashArgs &p) {
+    if (t.src[0] < 0 || t.src[1] < 0 || t.src[2] < 0) return "missing operands";
     const int32_t m = t.src[3];
-    if (t.src[4] >= 0) unsupported(t, "attention sinks are not supported");
-    const Tensor &tq = l.T(q), &tk = l.T(k), &tv = l.T(v);
+    if (t.src[4] >= 0) return "attention sinks are not supported";
+    const Tensor &tq = g.tensors[t.src[0]], &tk = g.tensors[t.src[1]], &tv = g.tensors[t.src[2]];
     auto f16_or_f32 = [](const Tensor &x) { return (x.ty == TLB_TYPE_F16 && x.nb[0] == 2) || (x.ty == TLB_TYPE_F32 && x.nb[0] == 4); };
-    if (tq.ty != TLB_TYPE_F32 || tq.nb[0] != 4 || t.ty != TLB_TYPE_F32) unsupported(t, "queries and result must be f32");
-    if (!f16_or_f32(tk) || !f16_or_f32(tv)) unsupported(t, "keys and values must be dense f16 or f32 rows");
-    if (!flash_supported(tq.ne[0], tv.ne[0]) || tk.ne[0] != tq.ne[0]) unsupported(t, "head size must be 64 or 128, the same for keys and values");
+    if (tq.ty != TLB_TYPE_F32 || tq.nb[0] != 4 || t.ty != TLB_TYPE_F32) return "queries and result must be f32";
+    if (!f16_or_f32(tk) || !f16_or_f32(tv)) return "keys and values must be dense f16 or f32 rows";
+    if (!flash_supported(tq.ne[0], tv.ne[0]) || tk.ne[0] != tq.ne[0]) return "head size must be 64 or 128, the same for keys and values";
     if (tk.ne[1] != tv.ne[1] || tk.ne[2] != tv.ne[2] || tk.ne[2] == 0 || tq.ne[2] % tk.ne[2] != 0 || tk.ne[3] != tq.ne[3] || tv.ne[3] != tq.ne[3])
-        unsupported(t, "inconsistent shapes");
+        return "inconsistent shapes";
     if (tk.nb[1] % 16 || tv.nb[1] % 16 || tk.nb[2] % 16 || tv.nb[2] % 16 || tk.nb[3] % 16 || tv.nb[3] % 16 || tq.nb[1] % 8 || tq.nb[2] % 8 || tq.nb[3] % 8)
-        unsupported(t, "rows must start on 16-byte boundaries");
+        return "rows must start on 16-byte boundaries";
     if (t.ne[0] != tv.ne[0] || t.ne[1] != tq.ne[2] || t.ne[2] != tq.ne[1] || t.ne[3] != tq.ne[3] || !t.is_contiguous())
-        unsupported(t, "the result must be a contiguous [dv, heads, queries, batch] tensor");
-    FlashArgs p{};
+        return "the result must be a contiguous [dv, heads, queries, batch] tensor";
+    p = FlashArgs{};
     p.q = view_of(tq);
     p.k = view_of(tk);
     p.v = view_of(tv);
@@ -682,18 +682,38 @@ void lower_flash(L &l) {
     p.m0 = powf(2.0f, -p.max_bias / (float)p.n_head_log2);
     p.m1 = powf(2.0f, -(p.max_bias / 2.0f) / (float)p.n_head_log2);
     p.m_ne2 = p.m_ne3 = 1;
-    Place pm;
     if (m >= 0) {
-        const Tensor &tm = l.T(m);
+        const Tensor &tm = g.tensors[m];
         if (tm.ty != TLB_TYPE_F16 || tm.nb[0] != 2 || tm.ne[0] < tk.ne[1] || tm.ne[1] < tq.ne[1] || tm.ne[2] < 1 || tm.ne[3] < 1)
-            unsupported(t, "the mask must be f16 [keys, >= queries, ...]");
+            return "the mask must be f16 [keys, >= queries, ...]";
         p.m = view_of(tm);
         p.m_ne2 = (int)tm.ne[2];
         p.m_ne3 = (int)tm.ne[3];
-        pm = l.place(m);
     }
+    return nullptr;
+}
+
+void lower_flash(L &l) {
+    const Tensor &t = l.t();
+    FlashArgs p{};
+    if (const char *why = flash_args(*l.c.g, t, p)) unsupported(t, why);
+    const int32_t q = l.src(0), k = l.src(1), v = l.src(2), m = t.src[3];
     const bool has_mask = m >= 0;
+    Place pm;
+    if (has_mask) pm = l.place(m);
     const Place pq = l.place(q), pk = l.place(k), pv = l.place(v), pd = l.place(l.id);
+    if (flash_tc_supported(p, has_mask)) {
+        // prompt-sized: packed operands and mask flags in the node's scratch, tcgen05 kernel
+        const int64_t sc = l.c.layout->scratch[l.pos];
+        if (sc < 0) throw std::string("attention scratch was not planned");
+        Place ps;
+        ps.buf = BUF_ARENA;
+        ps.off = (uint64_t)sc;
+        l.push([=](const RunCtx &r) {
+            return launch_flash_attn_tc(p, r.at(pq), r.at(pk), r.at(pv), has_mask ? r.at(pm) : nullptr, (float *)r.at(pd), r.at(ps), r.err, r.stream);
+        });
+        return;
+    }
     l.push([=](const RunCtx &r) {
         return launch_flash_attn(p, r.at(pq), r.at(pk), r.at(pv), has_mask ? r.at(pm) : nullptr, (float *)r.at(pd), r.stream);
     });
@@ -774,6 +794,10 @@ uint64_t node_scratch_bytes(const Graph &g, int32_t id, int sm_count) {
     if (t.op == "CUSTOM") {
         PagedGeom pg{};
         if (paged_geom(g, t, sm_count, pg)) return paged_scratch_bytes(pg);
+    }
+    if (t.op == "FLASH_ATTN_EXT") {
+        FlashArgs p{};
+        if (flash_args(g, t, p) == nullptr && flash_tc_supported(p, t.src[3] >= 0)) return flash_tc_scratch_bytes(p, t.src[3] >= 0);
     }
     if (t.op == "MUL_MAT_GROUP") {
         const Tensor &tx = g.tensors[t.src[1]];
