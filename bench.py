@@ -591,7 +591,7 @@ def prefill_measure(n_seqs: int, n_tokens: int, layers: int, steps: int, warmup:
     result = {
         "metric": "prefill tok/s (8B-shape Q8_0, %d x %d prompt tokens)" % (n_seqs, n_tokens), "value": T / (ms * 1e-3),
         "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "Q8_0 codes x block scales as f16 operands on tcgen05 kind::f16 (f32 accumulate in tensor memory), f16 mma.sync attention",
+        "scaling": "strong", "vs_baseline": None, "dtype": "Q8_0 codes x block scales as f16 operands on tcgen05 kind::f16 (f32 accumulate in tensor memory), f16 attention on tcgen05 (S, P and O in tensor memory)",
         "data": "synthetic",
         "config": {"workload": "benchmark config 5: Llama-3-8B shape, %d layers, Q8_0 weights, %d prompts x %d tokens, causal" % (cfg.n_layers, n_seqs, n_tokens),
                    "parallelism": "tp%d" % world},

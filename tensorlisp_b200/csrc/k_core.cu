@@ -3,6 +3,7 @@
 // vendor/ggml/src/ggml-cpu/ops.cpp). All of these are HBM-bound: rows are read with 128-bit
 // loads where the layout allows it, and the fusions that matter for a decode step (norm*weight,
 // act(gate)*up, rope+cast) are single passes.
+#include <algorithm>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <math_constants.h>
@@ -279,30 +280,38 @@ __device__ __forceinline__ void rope_cs(const RopeArgs &p, int64_t pr, float pos
     sn = sinf(th) * mscale;
 }
 
-__global__ void k_rope(RopeArgs p, const uint8_t *a, const int32_t *pos, const float *ff, uint8_t *d, int64_t npairs) {
+// A thread owns one (pair, position) and walks `hc` heads with it: cos and sin depend on the position and the pair
+// only, and the sequential product behind theta is the costly part (a prompt of 16k tokens has 32 heads per position).
+__global__ void k_rope(RopeArgs p, const uint8_t *a, const int32_t *pos, const float *ff, uint8_t *d, int64_t npairs, int hc) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= npairs) return;
     const int64_t half = p.a.ne[0] / 2;
     const int64_t pr = i % half;
     int64_t r = i / half;
-    const int64_t i1 = r % p.a.ne[1]; r /= p.a.ne[1];
     const int64_t i2 = r % p.a.ne[2];
     const int64_t i3 = r / p.a.ne[2];
-    const uint8_t *src = a + i1 * p.a.nb[1] + i2 * p.a.nb[2] + i3 * p.a.nb[3];
-    uint8_t *dst = d + i1 * p.d.nb[1] + i2 * p.d.nb[2] + i3 * p.d.nb[3];
+    const int64_t h0 = (int64_t)blockIdx.y * hc, h1 = min(h0 + hc, p.a.ne[1]);
+    const uint8_t *src = a + i2 * p.a.nb[2] + i3 * p.a.nb[3];
+    uint8_t *dst = d + i2 * p.d.nb[2] + i3 * p.d.nb[3];
     const int64_t i0 = 2 * pr;
     if (i0 >= p.n_dims) {  // dims past n_dims are copied through
-        st_elem(dst + i0 * p.d.nb[0], p.dty, ld_elem(src + i0 * p.a.nb[0], p.aty));
-        st_elem(dst + (i0 + 1) * p.d.nb[0], p.dty, ld_elem(src + (i0 + 1) * p.a.nb[0], p.aty));
+        for (int64_t i1 = h0; i1 < h1; i1++) {
+            st_elem(dst + i1 * p.d.nb[1] + i0 * p.d.nb[0], p.dty, ld_elem(src + i1 * p.a.nb[1] + i0 * p.a.nb[0], p.aty));
+            st_elem(dst + i1 * p.d.nb[1] + (i0 + 1) * p.d.nb[0], p.dty, ld_elem(src + i1 * p.a.nb[1] + (i0 + 1) * p.a.nb[0], p.aty));
+        }
         return;
     }
     float cs, sn;
     rope_cs(p, pr, (float)pos[i2], ff, cs, sn);
     const int64_t ic = p.mode == 0 ? i0 : pr;
     const int64_t off = p.mode == 0 ? 1 : p.n_dims / 2;
-    const float x0 = ld_elem(src + ic * p.a.nb[0], p.aty), x1 = ld_elem(src + (ic + off) * p.a.nb[0], p.aty);
-    st_elem(dst + ic * p.d.nb[0], p.dty, x0 * cs - x1 * sn);
-    st_elem(dst + (ic + off) * p.d.nb[0], p.dty, x0 * sn + x1 * cs);
+    for (int64_t i1 = h0; i1 < h1; i1++) {
+        const uint8_t *s1 = src + i1 * p.a.nb[1];
+        uint8_t *d1 = dst + i1 * p.d.nb[1];
+        const float x0 = ld_elem(s1 + ic * p.a.nb[0], p.aty), x1 = ld_elem(s1 + (ic + off) * p.a.nb[0], p.aty);
+        st_elem(d1 + ic * p.d.nb[0], p.dty, x0 * cs - x1 * sn);
+        st_elem(d1 + (ic + off) * p.d.nb[0], p.dty, x0 * sn + x1 * cs);
+    }
 }
 
 // One launch for the attention inputs of a decode step: rope(q) -> f16 query, rope(k) -> f16 into
@@ -362,9 +371,13 @@ cudaError_t launch_rope_kv(const RopeKvArgs &p, const void *q, const void *k, co
                       (const uint8_t *)q, (const uint8_t *)k, (const uint8_t *)v, pos, ff, (__half *)q16, (__half *)kpool, (__half *)vpool, slots, err);
 }
 cudaError_t launch_rope(const RopeArgs &p, const void *a, const int32_t *pos, const float *ff, void *d, cudaStream_t st) {
-    const int64_t n = p.a.ne[0] / 2 * p.a.ne[1] * p.a.ne[2] * p.a.ne[3];
-    if (n == 0) return cudaSuccess;
-    k_rope<<<nblocks(n, 256), 256, 0, st>>>(p, (const uint8_t *)a, pos, ff, (uint8_t *)d, n);
+    const int64_t n = p.a.ne[0] / 2 * p.a.ne[2] * p.a.ne[3];   // (pair, position) units
+    if (n == 0 || p.a.ne[1] == 0) return cudaSuccess;
+    // heads per thread: all of them once the units alone fill the GPU, one each for short inputs
+    int hc = (int)std::max<int64_t>(1, std::min<int64_t>(p.a.ne[1], n / 65536));
+    hc = (int)std::max<int64_t>(hc, (p.a.ne[1] + 65534) / 65535);   // grid.y stays below its limit
+    const dim3 grid(nblocks(n, 256), (unsigned)((p.a.ne[1] + hc - 1) / hc));
+    k_rope<<<grid, 256, 0, st>>>(p, (const uint8_t *)a, pos, ff, (uint8_t *)d, n, hc);
     return cudaGetLastError();
 }
 
