@@ -177,6 +177,80 @@ __global__ void __launch_bounds__(RQ_THREADS) k_row_quant_q8k(RowQuantArgs p) {
     rq_quant_block(p, n, sb, nblk, lane, v);
 }
 
+// ---------------------------------------------------------------- the same producers in front of a Q8_0 quantizer (prompt pass)
+// Q8_0 weights against prompt-sized batches read one operand only: f16(code x f16 scale) of the activations' Q8_0
+// quantization, packed in blobs of 256 columns x 64 elements of K (k_mm_q80_f16, k_mmq_tc_q8.cu). This kernel
+// produces exactly that from the f32 row source (a, a + b with the sum written back, RMS norm of either, SiLU(g) * u,
+// f16 values), so the normalised / gated f32 row never goes to memory. Quantization follows quantize_row_q8_0_ref
+// (ggml-quants.c): d = amax / 127 over 32 values, codes roundf(x / d), the scale rounded to f16.
+// A lane holds 8 consecutive values (a block is 4 lanes), a warp 256. With a norm ONE CTA owns the row (rows up to 8192
+// elements: 32 warps) and the row is read once; without, a row is spread over CTAs of 8 warps.
+__global__ void __launch_bounds__(1024) k_row_quant_q80(RowQuantArgs p) {
+    __shared__ float red[32];
+    griddep_launch();
+    griddep_wait();
+    const int n = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int64_t K = p.K;
+    const int nblk = (int)(K / 256);
+    const int sb = blockIdx.y * nwarps + warp;
+    const bool live = sb < nblk;
+    const int64_t k0 = (int64_t)sb * 256 + lane * 8;
+    // this lane's 16 bytes of the operand: column n of tile n / 256, stage k0 / 64, chunk (k0 % 64) / 8
+    uint8_t *blob = (uint8_t *)p.out + p.blob_off + ((size_t)(n >> 8) * (size_t)(K / 64) + (size_t)(k0 >> 6)) * 32768 +
+                    (size_t)((n & 255) >> 3) * 1024 + (size_t)((k0 & 63) >> 3) * 128 + (size_t)(n & 7) * 16;
+    if (n >= p.N) {   // padding columns of the last tile are zero
+        if (live) *reinterpret_cast<uint4 *>(blob) = make_uint4(0, 0, 0, 0);
+        return;
+    }
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (live) {
+        rq_load8(p, n, k0, v);
+        if (p.mode != RQ_GLU && p.mode != RQ_F16 && p.b && p.sum_out) {   // the sum is the new residual stream
+            *reinterpret_cast<float4 *>(p.sum_out + n * p.ld_sum + k0) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4 *>(p.sum_out + n * p.ld_sum + k0 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+        }
+    }
+    if (p.mode == RQ_NORM) {   // gridDim.y == 1: the whole row is in this CTA's registers
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; e++) ss = __fadd_rn(ss, __fmul_rn(v[e], v[e]));
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, s));
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+        for (int i = 0; i < nwarps; i++) tot = __fadd_rn(tot, red[i]);
+        const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)K), p.eps)));
+        if (live) {
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                const int wi = p.wn == K ? (int)(k0 + e) : (int)((uint32_t)(k0 + e) % (uint32_t)p.wn);
+                v[e] = __fmul_rn(__fmul_rn(v[e], scale), p.w[wi]);
+            }
+        }
+    }
+    if (!live) return;
+    float amax = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; e++) amax = fmaxf(amax, fabsf(v[e]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const float d = __fdiv_rn(amax, 127.f);
+    const float id = d != 0.f ? __fdiv_rn(1.0f, d) : 0.0f;
+    const float dh = __half2float(__float2half_rn(d));   // the block's scale as the dot product reads it
+    uint32_t h[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        const float q0 = roundf(__fmul_rn(v[2 * e], id)), q1 = roundf(__fmul_rn(v[2 * e + 1], id));
+        const __half2 t = __floats2half2_rn(__fmul_rn(q0, dh), __fmul_rn(q1, dh));
+        h[e] = *reinterpret_cast<const uint32_t *>(&t);
+    }
+    *reinterpret_cast<uint4 *>(blob) = make_uint4(h[0], h[1], h[2], h[3]);
+}
+
+bool row_quant_q80_supported(int64_t K, int mode) { return K % 256 == 0 && K >= 256 && (mode != RQ_NORM || K <= 8192); }
+
 // ---------------------------------------------------------------- exchange + residual add + RMS norm + quantizer
 // Tensor parallelism: the all-reduce behind a row-parallel projection, the residual add, the RMS norm and the
 // Q8_K quantization of the next mul_mat's input as ONE kernel. A CTA owns one activation row (token): it adds up
@@ -348,6 +422,12 @@ bool row_quant_supported(int64_t K) { return K % 256 == 0 && K / 256 <= 65535 * 
 
 cudaError_t launch_row_quant(const RowQuantArgs &p, cudaStream_t st) {
     if (p.N == 0 || p.K == 0) return cudaSuccess;
+    if (p.q80) {
+        if (p.npad != 256 || !row_quant_q80_supported(p.K, p.mode)) return cudaErrorInvalidValue;
+        const int rows256 = (int)((p.N + 255) / 256) * 256, nb = (int)(p.K / 256);
+        if (p.mode == RQ_NORM) return launch_pdl(k_row_quant_q80, dim3(rows256, 1), dim3(nb * 32), 0, st, p);
+        return launch_pdl(k_row_quant_q80, dim3(rows256, (nb + 7) / 8), dim3(256), 0, st, p);
+    }
     const int rows = p.npad > 0 ? (int)((p.N + p.npad - 1) / p.npad) * p.npad : (int)p.N;   // padding columns of the last chunk too
     const int nblk = (int)(p.K / 256);
     return launch_pdl(k_row_quant_q8k, dim3(rows, (nblk + RQ_WARPS - 1) / RQ_WARPS), dim3(RQ_THREADS), 0, st, p);

@@ -98,8 +98,11 @@ struct RowQuantArgs {
     uint64_t qs_off, d_off, bsum_off;
     int npad;            // > 0: also pack blobs of npad columns at out + blob_off
     uint64_t blob_off, blob_bytes;
+    int q80;             // 0: Q8_K (the default). 1: Q8_0 for the prompt mul_mat of Q8_0 weights: only its packed f16
+                         // operand (blobs of 256 columns x 64 elements, value = code x f16 scale) is produced
 };
 bool row_quant_supported(int64_t K);
+bool row_quant_q80_supported(int64_t K, int mode);
 cudaError_t launch_row_quant(const RowQuantArgs &p, cudaStream_t st);
 // the all-reduce in front of a residual add + RMS norm + quantizer fused into one kernel (tensor parallelism):
 // p as for launch_row_quant in RQ_NORM mode with p.a the residual stream; the addend is the all-reduced `a`

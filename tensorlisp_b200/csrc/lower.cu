@@ -521,6 +521,8 @@ void lower_row_quant(L &l) {
     p.npad = t.op_params[1];
     p.blob_off = al.bytes;
     p.blob_bytes = p.npad > 0 ? mmq_tc_plan(p.K, 128, p.N, 148).blob_unit : 0;
+    p.q80 = t.op_params[0] == ACT_Q8_0;
+    if (p.q80) p.blob_off = act_layout(ACT_Q8_0, p.K, p.N).bytes;   // the blobs sit behind the Q8_0 block
     p.eps = t.param_f32(15);
     p.lda = mode == RQ_F16 ? p.K : (p.N > 1 ? (int64_t)l.T(a).nb[1] / 4 : p.K);
     const int32_t b = t.src[1], w = t.src[3], sum = t.src[4];
@@ -748,7 +750,9 @@ bool exchange_fused_with_row_quant(const LowerCtx &c, int pos) {
     if (getenv("TLB_NO_FUSED_EXCHANGE") || pos < 0 || (size_t)pos + 1 >= g.nodes.size()) return false;
     const int32_t ar = g.nodes[pos];
     const Tensor &A = g.tensors[ar], &R = g.tensors[g.nodes[pos + 1]];
-    if (A.op != "ALLREDUCE" || R.op != "ROW_QUANT" || R.op_params[2] != RQ_NORM || R.src[1] != ar || R.src[0] < 0 || R.src[3] < 0) return false;
+    if (A.op != "ALLREDUCE" || R.op != "ROW_QUANT" || R.op_params[0] != ACT_Q8_K || R.op_params[2] != RQ_NORM || R.src[1] != ar || R.src[0] < 0 ||
+        R.src[3] < 0)
+        return false;
     if (!exchange_row_quant_supported(A.ne[0], A.nrows()) || !A.is_contiguous()) return false;
     const Tensor &X = g.tensors[R.src[0]], &W = g.tensors[R.src[3]];
     if (X.ne[0] != A.ne[0] || X.nrows() != A.nrows() || W.ne[0] != A.ne[0]) return false;
@@ -1039,7 +1043,10 @@ void fuse_row_producers(Graph &g) {
     std::vector<int> rd;
     for (size_t qi = 0; qi < nn; qi++) {
         const int32_t qid = g.nodes[qi];
-        if (g.tensors[qid].op != "QUANT_ACT" || g.tensors[qid].op_params[0] != ACT_Q8_K) continue;
+        if (g.tensors[qid].op != "QUANT_ACT") continue;
+        // Q8_K activations (Q4_K weights), or the Q8_0 activations of the prompt mul_mat (operand blobs of 256 columns)
+        const bool q80 = g.tensors[qid].op_params[0] == ACT_Q8_0;
+        if (q80 && g.tensors[qid].op_params[1] != 256) continue;
         const int32_t x = g.tensors[qid].src[0];
         const Tensor X = g.tensors[x];
         if (X.ty != 0 || !row_quant_supported(X.ne[0]) || !dense_rows(X, 4)) continue;
@@ -1059,6 +1066,7 @@ void fuse_row_producers(Graph &g) {
             const int32_t a = P.src[0], w = P.src[1];
             const Tensor &A = g.tensors[a], &W = g.tensors[w];
             if (A.ty != 0 || W.ty != 0 || W.nb[0] != 4 || W.ne[1] * W.ne[2] * W.ne[3] != 1 || !dense_rows(A, 4)) continue;
+            if (q80 && !row_quant_q80_supported(X.ne[0], RQ_NORM)) continue;
             Q.op = "ROW_QUANT";
             Q.op_params[2] = RQ_NORM;
             Q.op_params[15] = P.op_params[15];
