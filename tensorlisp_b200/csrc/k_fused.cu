@@ -180,7 +180,7 @@ __global__ void __launch_bounds__(RQ_THREADS) k_row_quant_q8k(RowQuantArgs p) {
 // ---------------------------------------------------------------- the same producers in front of a Q8_0 quantizer (prompt pass)
 // Q8_0 weights against prompt-sized batches read one operand only: f16(code x f16 scale) of the activations' Q8_0
 // quantization, packed in blobs of 256 columns x 64 elements of K (k_mm_q80_f16, k_mmq_tc_q8.cu). This kernel
-// produces exactly that from the f32 row source (a, a + b with the sum written back, RMS norm of either, SiLU(g) * u,
+// produces that (and the Q8_0 block itself) from the f32 row source (a, a + b with the sum written back, RMS norm of either, SiLU(g) * u,
 // f16 values), so the normalised / gated f32 row never goes to memory. Quantization follows quantize_row_q8_0_ref
 // (ggml-quants.c): d = amax / 127 over 32 values, codes roundf(x / d), the scale rounded to f16.
 // A lane holds 8 consecutive values (a block is 4 lanes), a warp 256. With a norm ONE CTA owns the row (rows up to 8192
@@ -240,13 +240,22 @@ __global__ void __launch_bounds__(1024) k_row_quant_q80(RowQuantArgs p) {
     const float id = d != 0.f ? __fdiv_rn(1.0f, d) : 0.0f;
     const float dh = __half2float(__float2half_rn(d));   // the block's scale as the dot product reads it
     uint32_t h[4];
+    int q[8];
 #pragma unroll
     for (int e = 0; e < 4; e++) {
         const float q0 = roundf(__fmul_rn(v[2 * e], id)), q1 = roundf(__fmul_rn(v[2 * e + 1], id));
+        q[2 * e] = (int)q0;
+        q[2 * e + 1] = (int)q1;
         const __half2 t = __floats2half2_rn(__fmul_rn(q0, dh), __fmul_rn(q1, dh));
         h[e] = *reinterpret_cast<const uint32_t *>(&t);
     }
     *reinterpret_cast<uint4 *>(blob) = make_uint4(h[0], h[1], h[2], h[3]);
+    // the Q8_0 block itself too (int8 codes and f32 scales): a consumer that is not a prompt-sized 2-D mul_mat reads those
+    uint2 packed;
+    packed.x = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[1] & 0xff) << 8) | ((uint32_t)(q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
+    packed.y = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
+    *reinterpret_cast<uint2 *>((int8_t *)p.out + p.qs_off + (size_t)n * K + k0) = packed;
+    if ((lane & 3) == 0) reinterpret_cast<float *>((char *)p.out + p.d_off)[(size_t)n * (K / 32) + (k0 >> 5)] = dh;
 }
 
 bool row_quant_q80_supported(int64_t K, int mode) { return K % 256 == 0 && K >= 256 && (mode != RQ_NORM || K <= 8192); }

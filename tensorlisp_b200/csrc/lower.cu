@@ -492,6 +492,26 @@ void lower_quant_act(L &l) {
     const int64_t ldx = tx.nrows() > 1 ? (int64_t)tx.nb[1] / 4 : tx.ne[0];
     const Place px = l.place(x), pd = l.place(l.id);
     const int npad = t.op_params[1];   // > 0: also pack the blobs of the tensor-core path behind the Q8_K block
+    if (a.kind == ACT_Q8_0 && npad == 256 && row_quant_q80_supported(a.K, RQ_PLAIN) && tx.nb[0] == 4 && ldx % 4 == 0) {
+        // the prompt mul_mat reads the packed f16 operand only: one launch from the f32 rows straight to it
+        RowQuantArgs p{};
+        p.mode = RQ_PLAIN;
+        p.K = a.K;
+        p.N = a.N;
+        p.lda = ldx;
+        p.npad = npad;
+        p.q80 = 1;
+        p.qs_off = a.qs_off;
+        p.d_off = a.d_off;
+        p.blob_off = a.bytes;
+        l.push([=](const RunCtx &r) {
+            RowQuantArgs q = p;
+            q.a = (const float *)r.at(px);
+            q.out = r.at(pd);
+            return launch_row_quant(q, r.stream);
+        });
+        return;
+    }
     l.push([=](const RunCtx &r) {
         cudaError_t e = launch_act_quantize(a, (const float *)r.at(px), ldx, r.at(pd), r.stream);
         if (e == cudaSuccess && npad > 0)
@@ -514,7 +534,7 @@ void lower_row_quant(L &l) {
     p.mode = mode;
     p.K = shape.ne[0];
     p.N = shape.nrows();
-    const ActLayout al = act_layout(ACT_Q8_K, p.K, p.N);
+    const ActLayout al = act_layout(t.op_params[0] == ACT_Q8_0 ? ACT_Q8_0 : ACT_Q8_K, p.K, p.N);
     p.qs_off = al.qs_off;
     p.d_off = al.d_off;
     p.bsum_off = al.bsum_off;
@@ -522,7 +542,6 @@ void lower_row_quant(L &l) {
     p.blob_off = al.bytes;
     p.blob_bytes = p.npad > 0 ? mmq_tc_plan(p.K, 128, p.N, 148).blob_unit : 0;
     p.q80 = t.op_params[0] == ACT_Q8_0;
-    if (p.q80) p.blob_off = act_layout(ACT_Q8_0, p.K, p.N).bytes;   // the blobs sit behind the Q8_0 block
     p.eps = t.param_f32(15);
     p.lda = mode == RQ_F16 ? p.K : (p.N > 1 ? (int64_t)l.T(a).nb[1] / 4 : p.K);
     const int32_t b = t.src[1], w = t.src[3], sum = t.src[4];
