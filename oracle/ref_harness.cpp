@@ -143,6 +143,13 @@ int tlref_op(tlref_ctx * c, const char * op, const int * src, int nsrc, const in
     else if (o == "mean")      r = ggml_mean(g, S(0));
     else if (o == "arange")    r = ggml_arange(g, F(0), F(1), F(2));
     else if (o == "cumsum")    r = ggml_cumsum(g, S(0));
+    else if (o == "im2col")    r = ggml_im2col(g, S(0), S(1), (int)I(0), (int)I(1), (int)I(2), (int)I(3), (int)I(4), (int)I(5), I(6) != 0,
+                                               (ggml_type)I(7));
+    else if (o == "interpolate") r = ggml_interpolate(g, S(0), I(0), I(1), I(2), I(3), (uint32_t)I(4));
+    else if (o == "pool_2d")   r = ggml_pool_2d(g, S(0), (ggml_op_pool)I(0), (int)I(1), (int)I(2), (int)I(3), (int)I(4), F(0), F(1));
+    else if (o == "conv_2d_dw") r = ggml_conv_2d_dw_direct(g, S(0), S(1), (int)I(0), (int)I(1), (int)I(2), (int)I(3), (int)I(4), (int)I(5));
+    else if (o == "pad_ext")   r = ggml_pad_ext(g, S(0), (int)I(0), (int)I(1), (int)I(2), (int)I(3), (int)I(4), (int)I(5), (int)I(6), (int)I(7));
+    else if (o == "pad_reflect_1d") r = ggml_pad_reflect_1d(g, S(0), (int)I(0), (int)I(1));
     else if (o == "custom") {
         // The paged nodes of scheme/core.ss:222-271: no function, userdata = packed u64.
         ggml_tensor * args[GGML_MAX_SRC] = {};

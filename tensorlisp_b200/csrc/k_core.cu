@@ -607,4 +607,173 @@ cudaError_t launch_arange(const SimpleArgs &p, void *d, cudaStream_t st) {
     return cudaGetLastError();
 }
 
+// ---------------------------------------------------------------- image ops
+// The reference's native executor runs these one thread per destination element (crates/kernels/src/cuda/native/
+// core.cu:240-261 im2col, 285-358 upscale, 405-427 pool_2d, 483-536 conv_2d_dw / pad / pad_reflect_1d); the arithmetic is
+// that of ggml's CPU operators (vendor/ggml/src/ggml-cpu/ops.cpp).
+
+// IM2COL: d[n][oh][ow][ic*KH*KW + ky*KW + kx] = x[n][ic][oh*s1 + ky*d1 - p1][ow*s0 + kx*d0 - p0], zero outside
+// (1-D: d[n][ow][ic*KW + kx] = x[n][ic][ow*s0 + kx*d0 - p0])
+__global__ void k_im2col(Im2colArgs p, const uint8_t *x, uint8_t *d, int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    int64_t i0, i1, i2, i3;
+    decomp(i, p.d.ne, i0, i1, i2, i3);
+    const int64_t ow = i1, oh = p.is2d ? i2 : 0, img = p.is2d ? i3 : i2;
+    const int64_t khw = p.KW * p.KH, ic = i0 / khw, r = i0 % khw, ky = r / p.KW, kx = r % p.KW;
+    const int64_t iy = oh * p.s1 + ky * p.d1 - p.p1, ix = ow * p.s0 + kx * p.d0 - p.p0;
+    float v = 0.f;
+    if (iy >= 0 && iy < p.IH && ix >= 0 && ix < p.IW)
+        v = ld_elem(x + (p.is2d ? img * p.x.nb[3] + ic * p.x.nb[2] + iy * p.x.nb[1] : img * p.x.nb[2] + ic * p.x.nb[1]) + ix * p.x.nb[0], p.xty);
+    st_elem(d + offs(p.d, i0, i1, i2, i3), p.dty, v);
+}
+cudaError_t launch_im2col(const Im2colArgs &p, const void *x, void *d, cudaStream_t st) {
+    const int64_t n = p.d.ne[0] * p.d.ne[1] * p.d.ne[2] * p.d.ne[3];
+    if (n == 0) return cudaSuccess;
+    k_im2col<<<nblocks(n, 256), 256, 0, st>>>(p, (const uint8_t *)x, (uint8_t *)d, n);
+    return cudaGetLastError();
+}
+
+// UPSCALE (ggml_compute_forward_upscale_f32, ops.cpp:7832-8024): nearest, bilinear (optionally antialiased), bicubic
+__device__ __forceinline__ float cubic_w1(float x) { return ((-0.75f + 2.f) * x - (-0.75f + 3.f)) * x * x + 1.f; }
+__device__ __forceinline__ float cubic_w2(float x) { return ((-0.75f * x - 5.f * -0.75f) * x + 8.f * -0.75f) * x - 4.f * -0.75f; }
+__device__ __forceinline__ float cubic4(float p0, float p1, float p2, float p3, float x) {
+    return p0 * cubic_w2(x + 1.f) + p1 * cubic_w1(x) + p2 * cubic_w1(1.f - x) + p3 * cubic_w2(2.f - x);
+}
+__global__ void k_upscale(UpscaleArgs p, const uint8_t *a, uint8_t *d, int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    int64_t i0, i1, i2, i3;
+    decomp(i, p.d.ne, i0, i1, i2, i3);
+    const int64_t w = p.a.ne[0], h = p.a.ne[1];
+    const uint8_t *plane = a + (int64_t)((float)i2 / p.sf2) * p.a.nb[2] + (int64_t)((float)i3 / p.sf3) * p.a.nb[3];
+    auto px = [&](int64_t xx, int64_t yy) { return *reinterpret_cast<const float *>(plane + xx * p.a.nb[0] + yy * p.a.nb[1]); };
+    auto clampi = [](int64_t v, int64_t hi) { return v < 0 ? (int64_t)0 : (v > hi ? hi : v); };
+    float val;
+    if (p.mode == 0) {
+        val = px((int64_t)((float)i0 / p.sf0), (int64_t)((float)i1 / p.sf1));
+    } else if (p.mode == 1 && p.antialias) {
+        const float sup1 = fmaxf(1.0f, 1.0f / p.sf1), inv1 = 1.0f / sup1, sup0 = fmaxf(1.0f, 1.0f / p.sf0), inv0 = 1.0f / sup0;
+        const float y = ((float)i1 + p.poff) / p.sf1, x = ((float)i0 + p.poff) / p.sf0;
+        const int64_t x_min = max((int64_t)(x - sup0 + p.poff), (int64_t)0), x_max = min((int64_t)(x + sup0 + p.poff), w);
+        const int64_t y_min = max((int64_t)(y - sup1 + p.poff), (int64_t)0), y_max = min((int64_t)(y + sup1 + p.poff), h);
+        float sum = 0.f, total = 0.f;
+        for (int64_t sy = y_min; sy < y_max; sy++) {
+            const float wy = fmaxf(1.0f - fabsf(((float)sy - y + p.poff) * inv1), 0.0f);
+            for (int64_t sx = x_min; sx < x_max; sx++) {
+                const float wx = fmaxf(1.0f - fabsf(((float)sx - x + p.poff) * inv0), 0.0f);
+                const float wt = wx * wy;
+                if (wt <= 0.0f) continue;
+                sum += px(sx, sy) * wt;
+                total += wt;
+            }
+        }
+        val = total > 0.f ? sum / total : sum;
+    } else if (p.mode == 1) {
+        const float y = ((float)i1 + p.poff) / p.sf1 - p.poff, x = ((float)i0 + p.poff) / p.sf0 - p.poff;
+        const int64_t yf = (int64_t)floorf(y), xf = (int64_t)floorf(x);
+        const int64_t y0 = clampi(yf, h - 1), y1 = clampi(yf + 1, h - 1), x0 = clampi(xf, w - 1), x1 = clampi(xf + 1, w - 1);
+        const float dy = fmaxf(0.0f, fminf(y - (float)y0, 1.0f)), dx = fmaxf(0.0f, fminf(x - (float)x0, 1.0f));
+        val = px(x0, y0) * (1 - dx) * (1 - dy) + px(x1, y0) * dx * (1 - dy) + px(x0, y1) * (1 - dx) * dy + px(x1, y1) * dx * dy;
+    } else {
+        const float y = ((float)i1 + p.poff) / p.sf1 - p.poff, x = ((float)i0 + p.poff) / p.sf0 - p.poff;
+        const int64_t y0 = (int64_t)floorf(y), x0 = (int64_t)floorf(x);
+        const float dy = y - (float)y0, dx = x - (float)x0;
+        float rows[4];
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+            const int64_t yy = clampi(y0 + r - 1, h - 1);
+            rows[r] = cubic4(px(clampi(x0 - 1, w - 1), yy), px(clampi(x0, w - 1), yy), px(clampi(x0 + 1, w - 1), yy), px(clampi(x0 + 2, w - 1), yy), dx);
+        }
+        val = cubic4(rows[0], rows[1], rows[2], rows[3], dy);
+    }
+    *reinterpret_cast<float *>(d + offs(p.d, i0, i1, i2, i3)) = val;
+}
+cudaError_t launch_upscale(const UpscaleArgs &p, const void *a, void *d, cudaStream_t st) {
+    const int64_t n = p.d.ne[0] * p.d.ne[1] * p.d.ne[2] * p.d.ne[3];
+    if (n == 0) return cudaSuccess;
+    k_upscale<<<nblocks(n, 256), 256, 0, st>>>(p, (const uint8_t *)a, (uint8_t *)d, n);
+    return cudaGetLastError();
+}
+
+// POOL_2D: max (kind 0) or average over the k0 x k1 window (kind 1; the divisor is the whole window, as on the CPU)
+__global__ void k_pool_2d(Pool2dArgs p, const uint8_t *a, uint8_t *d, int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    int64_t i0, i1, i2, i3;
+    decomp(i, p.d.ne, i0, i1, i2, i3);
+    const uint8_t *plane = a + i2 * p.a.nb[2] + i3 * p.a.nb[3];
+    const int64_t ix = i0 * p.s0 - p.p0, iy = i1 * p.s1 - p.p1;
+    float res = p.kind == 1 ? 0.f : -3.402823466e+38f;
+    for (int ky = 0; ky < p.k1; ky++) {
+        if (iy + ky < 0 || iy + ky >= p.a.ne[1]) continue;
+        for (int kx = 0; kx < p.k0; kx++) {
+            if (ix + kx < 0 || ix + kx >= p.a.ne[0]) continue;
+            const float v = ld_elem(plane + (iy + ky) * p.a.nb[1] + (ix + kx) * p.a.nb[0], p.aty);
+            res = p.kind == 1 ? res + v : fmaxf(v, res);
+        }
+    }
+    if (p.kind == 1) res /= (float)(p.k0 * p.k1);
+    st_elem(d + offs(p.d, i0, i1, i2, i3), p.dty, res);
+}
+cudaError_t launch_pool_2d(const Pool2dArgs &p, const void *a, void *d, cudaStream_t st) {
+    const int64_t n = p.d.ne[0] * p.d.ne[1] * p.d.ne[2] * p.d.ne[3];
+    if (n == 0) return cudaSuccess;
+    k_pool_2d<<<nblocks(n, 256), 256, 0, st>>>(p, (const uint8_t *)a, (uint8_t *)d, n);
+    return cudaGetLastError();
+}
+
+// CONV_2D_DW: depthwise convolution, kernel [KW, KH, 1, C] over data [W, H, C, N]
+__global__ void k_conv_2d_dw(ConvDwArgs p, const uint8_t *k, const uint8_t *x, uint8_t *d, int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    int64_t i0, i1, i2, i3;
+    decomp(i, p.d.ne, i0, i1, i2, i3);
+    const uint8_t *xp = x + i2 * p.x.nb[2] + i3 * p.x.nb[3], *kp = k + i2 * p.k.nb[3];
+    float sum = 0.f;
+    for (int64_t ky = 0; ky < p.k.ne[1]; ky++) {
+        const int64_t iy = i1 * p.s1 + ky * p.d1 - p.p1;
+        if (iy < 0 || iy >= p.x.ne[1]) continue;
+        for (int64_t kx = 0; kx < p.k.ne[0]; kx++) {
+            const int64_t ix = i0 * p.s0 + kx * p.d0 - p.p0;
+            if (ix < 0 || ix >= p.x.ne[0]) continue;
+            sum += ld_elem(xp + iy * p.x.nb[1] + ix * p.x.nb[0], p.xty) * ld_elem(kp + ky * p.k.nb[1] + kx * p.k.nb[0], p.kty);
+        }
+    }
+    st_elem(d + offs(p.d, i0, i1, i2, i3), p.dty, sum);
+}
+cudaError_t launch_conv_2d_dw(const ConvDwArgs &p, const void *k, const void *x, void *d, cudaStream_t st) {
+    const int64_t n = p.d.ne[0] * p.d.ne[1] * p.d.ne[2] * p.d.ne[3];
+    if (n == 0) return cudaSuccess;
+    k_conv_2d_dw<<<nblocks(n, 256), 256, 0, st>>>(p, (const uint8_t *)k, (const uint8_t *)x, (uint8_t *)d, n);
+    return cudaGetLastError();
+}
+
+// PAD (zeros around the source, lp[] elements in front of each dimension) and PAD_REFLECT_1D (dimension 0 mirrored);
+// elements are copied as bytes (2 or 4), so every plain type passes through unchanged
+__global__ void k_pad(PadArgs p, const uint8_t *a, uint8_t *d, int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    int64_t i0, i1, i2, i3;
+    decomp(i, p.d.ne, i0, i1, i2, i3);
+    int64_t j0 = i0 - p.lp[0], j1 = i1 - p.lp[1], j2 = i2 - p.lp[2], j3 = i3 - p.lp[3];
+    bool inside = true;
+    if (p.reflect) {
+        if (j0 < 0) j0 = -j0;
+        if (j0 >= p.a.ne[0]) j0 = 2 * (p.a.ne[0] - 1) - j0;
+    } else {
+        inside = j0 >= 0 && j0 < p.a.ne[0] && j1 >= 0 && j1 < p.a.ne[1] && j2 >= 0 && j2 < p.a.ne[2] && j3 >= 0 && j3 < p.a.ne[3];
+    }
+    uint8_t *dp = d + offs(p.d, i0, i1, i2, i3);
+    const uint8_t *sp = a + (inside ? offs(p.a, j0, j1, j2, j3) : 0);
+    if (p.elem_bytes == 4) *reinterpret_cast<uint32_t *>(dp) = inside ? *reinterpret_cast<const uint32_t *>(sp) : 0u;
+    else *reinterpret_cast<uint16_t *>(dp) = inside ? *reinterpret_cast<const uint16_t *>(sp) : (uint16_t)0;
+}
+cudaError_t launch_pad(const PadArgs &p, const void *a, void *d, cudaStream_t st) {
+    const int64_t n = p.d.ne[0] * p.d.ne[1] * p.d.ne[2] * p.d.ne[3];
+    if (n == 0) return cudaSuccess;
+    k_pad<<<nblocks(n, 256), 256, 0, st>>>(p, (const uint8_t *)a, (uint8_t *)d, n);
+    return cudaGetLastError();
+}
+
 }  // namespace tlb

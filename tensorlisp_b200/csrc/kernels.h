@@ -153,6 +153,18 @@ cudaError_t launch_repeat(const SimpleArgs &p, const void *a, void *d, cudaStrea
 cudaError_t launch_sum_rows(const SimpleArgs &p, const void *a, void *d, cudaStream_t st);  // i0: 1 = mean
 cudaError_t launch_arange(const SimpleArgs &p, void *d, cudaStream_t st);
 
+// image ops (IM2COL, UPSCALE, POOL_2D, CONV_2D_DW, PAD, PAD_REFLECT_1D): one thread per destination element
+struct Im2colArgs { TView x, d; uint32_t xty, dty; int s0, s1, p0, p1, d0, d1, is2d; int64_t KW, KH, IH, IW; };
+cudaError_t launch_im2col(const Im2colArgs &p, const void *x, void *d, cudaStream_t st);
+struct UpscaleArgs { TView a, d; float sf0, sf1, sf2, sf3, poff; int mode, antialias; };   // f32 -> f32
+cudaError_t launch_upscale(const UpscaleArgs &p, const void *a, void *d, cudaStream_t st);
+struct Pool2dArgs { TView a, d; uint32_t aty, dty; int kind, k0, k1, s0, s1, p0, p1; };
+cudaError_t launch_pool_2d(const Pool2dArgs &p, const void *a, void *d, cudaStream_t st);
+struct ConvDwArgs { TView k, x, d; uint32_t kty, xty, dty; int s0, s1, p0, p1, d0, d1; };
+cudaError_t launch_conv_2d_dw(const ConvDwArgs &p, const void *k, const void *x, void *d, cudaStream_t st);
+struct PadArgs { TView a, d; int64_t lp[4]; int elem_bytes, reflect; };
+cudaError_t launch_pad(const PadArgs &p, const void *a, void *d, cudaStream_t st);
+
 // ---------------------------------------------------------------- k_flash.cu
 // FLASH_ATTN_EXT (dense): q f32 [d, nq, nh, nb], k / v f16 or f32 [d, nkv, nhkv, nb], optional f16 mask
 struct FlashArgs {

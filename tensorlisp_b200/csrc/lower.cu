@@ -839,6 +839,112 @@ uint64_t node_scratch_bytes(const Graph &g, int32_t id, int sm_count) {
     return 0;
 }
 
+// ---- image ops (lower.rs:366-382 im2col, 392-420 upscale, 469-482 pool_2d, 506-539 conv_2d_dw / pad)
+void lower_image(L &l) {
+    const Tensor &t = l.t();
+    const std::string &op = t.op;
+    auto float_type = [](uint32_t ty) { return ty == TLB_TYPE_F32 || ty == TLB_TYPE_F16 || ty == TLB_TYPE_BF16; };
+    const Place pd = l.place(l.id);
+    if (op == "IM2COL") {
+        const int32_t k = l.src(0), x = l.src(1);
+        const Tensor &tk = l.T(k), &tx = l.T(x);
+        if (!float_type(tx.ty) || !float_type(t.ty)) unsupported(t, "im2col takes f32 / f16 / bf16 data");
+        Im2colArgs p{};
+        p.x = view_of(tx);
+        p.d = view_of(t);
+        p.xty = tx.ty;
+        p.dty = t.ty;
+        p.s0 = t.op_params[0]; p.s1 = t.op_params[1]; p.p0 = t.op_params[2]; p.p1 = t.op_params[3]; p.d0 = t.op_params[4]; p.d1 = t.op_params[5];
+        p.is2d = t.op_params[6] == 1;
+        p.KW = tk.ne[0];
+        p.KH = p.is2d ? tk.ne[1] : 1;
+        p.IH = p.is2d ? tx.ne[1] : 1;
+        p.IW = tx.ne[0];
+        if (p.s0 < 1 || (p.is2d && p.s1 < 1) || p.KW < 1 || p.KH < 1 || t.ne[0] % (p.KW * p.KH) != 0) unsupported(t, "inconsistent im2col parameters");
+        const Place px = l.place(x);
+        l.push([=](const RunCtx &r) { return launch_im2col(p, r.at(px), r.at(pd), r.stream); });
+    } else if (op == "UPSCALE") {
+        const int32_t a = l.src(0);
+        const Tensor &ta = l.T(a);
+        if (ta.ty != TLB_TYPE_F32 || t.ty != TLB_TYPE_F32) unsupported(t, "upscale takes f32");
+        const int32_t flags = t.op_params[0];
+        UpscaleArgs p{};
+        p.a = view_of(ta);
+        p.d = view_of(t);
+        p.mode = flags & 0xFF;
+        p.antialias = (flags & (1 << 9)) != 0;
+        if (p.mode < 0 || p.mode > 2) unsupported(t, "unknown upscale mode");
+        if (p.antialias && p.mode != 1) unsupported(t, "antialiasing is bilinear only");
+        for (int i = 0; i < 4; i++)
+            if (ta.ne[i] < 1) unsupported(t, "empty source");
+        float sf[4];
+        for (int i = 0; i < 4; i++) sf[i] = (float)t.ne[i] / (float)ta.ne[i];
+        p.poff = 0.5f;
+        if (flags & (1 << 8)) {   // align corners
+            p.poff = 0.0f;
+            for (int i = 0; i < 2; i++)
+                if (t.ne[i] > 1 && ta.ne[i] > 1) sf[i] = (float)(t.ne[i] - 1) / (float)(ta.ne[i] - 1);
+        }
+        p.sf0 = sf[0]; p.sf1 = sf[1]; p.sf2 = sf[2]; p.sf3 = sf[3];
+        const Place pa = l.place(a);
+        l.push([=](const RunCtx &r) { return launch_upscale(p, r.at(pa), r.at(pd), r.stream); });
+    } else if (op == "POOL_2D") {
+        const int32_t a = l.src(0);
+        const Tensor &ta = l.T(a);
+        if (!float_type(ta.ty) || !float_type(t.ty)) unsupported(t, "pooling takes f32 / f16 / bf16");
+        Pool2dArgs p{};
+        p.a = view_of(ta);
+        p.d = view_of(t);
+        p.aty = ta.ty;
+        p.dty = t.ty;
+        p.kind = t.op_params[0]; p.k0 = t.op_params[1]; p.k1 = t.op_params[2]; p.s0 = t.op_params[3]; p.s1 = t.op_params[4];
+        p.p0 = t.op_params[5]; p.p1 = t.op_params[6];
+        if (p.kind != 0 && p.kind != 1) unsupported(t, "unknown pooling op");
+        if (p.k0 < 1 || p.k1 < 1 || p.s0 < 1 || p.s1 < 1 || t.ne[2] != ta.ne[2] || t.ne[3] != ta.ne[3]) unsupported(t, "inconsistent pooling parameters");
+        const Place pa = l.place(a);
+        l.push([=](const RunCtx &r) { return launch_pool_2d(p, r.at(pa), r.at(pd), r.stream); });
+    } else if (op == "CONV_2D_DW") {
+        const int32_t k = l.src(0), x = l.src(1);
+        const Tensor &tk = l.T(k), &tx = l.T(x);
+        if (!float_type(tk.ty) || !float_type(tx.ty) || !float_type(t.ty)) unsupported(t, "depthwise convolution takes f32 / f16 / bf16");
+        if (tk.ne[2] != 1 || tk.ne[3] != tx.ne[2] || t.ne[2] != tx.ne[2] || t.ne[3] != tx.ne[3]) unsupported(t, "inconsistent shapes");
+        ConvDwArgs p{};
+        p.k = view_of(tk);
+        p.x = view_of(tx);
+        p.d = view_of(t);
+        p.kty = tk.ty; p.xty = tx.ty; p.dty = t.ty;
+        p.s0 = t.op_params[0]; p.s1 = t.op_params[1]; p.p0 = t.op_params[2]; p.p1 = t.op_params[3]; p.d0 = t.op_params[4]; p.d1 = t.op_params[5];
+        if (p.s0 < 1 || p.s1 < 1) unsupported(t, "strides must be positive");
+        const Place pk = l.place(k), px = l.place(x);
+        l.push([=](const RunCtx &r) { return launch_conv_2d_dw(p, r.at(pk), r.at(px), r.at(pd), r.stream); });
+    } else {
+        const int32_t a = l.src(0);
+        const Tensor &ta = l.T(a);
+        if (ta.ty != t.ty) unsupported(t, "padding keeps the element type");
+        const uint64_t es = type_traits(t.ty)->size;
+        if (type_traits(t.ty)->blck != 1 || (es != 2 && es != 4)) unsupported(t, "padding takes 2- or 4-byte elements");
+        PadArgs p{};
+        p.a = view_of(ta);
+        p.d = view_of(t);
+        p.elem_bytes = (int)es;
+        if (op == "PAD") {
+            if (t.op_params[8] != 0) unsupported(t, "circular padding");
+            for (int i = 0; i < 4; i++) {
+                p.lp[i] = t.op_params[2 * i];
+                if (p.lp[i] < 0 || t.op_params[2 * i + 1] < 0 || t.ne[i] != ta.ne[i] + p.lp[i] + t.op_params[2 * i + 1]) unsupported(t, "inconsistent padding");
+            }
+        } else {
+            p.reflect = 1;
+            p.lp[0] = t.op_params[0];
+            if (p.lp[0] < 0 || t.op_params[1] < 0 || p.lp[0] >= ta.ne[0] || t.op_params[1] >= ta.ne[0] || t.ne[0] != ta.ne[0] + p.lp[0] + t.op_params[1] ||
+                t.ne[1] != ta.ne[1] || t.ne[2] != ta.ne[2] || t.ne[3] != ta.ne[3])
+                unsupported(t, "reflection needs pads shorter than the row");
+        }
+        const Place pa = l.place(a);
+        l.push([=](const RunCtx &r) { return launch_pad(p, r.at(pa), r.at(pd), r.stream); });
+    }
+}
+
 void lower_node(const LowerCtx &c, int32_t id, int pos, std::vector<Dispatch> &out) {
     const Tensor &t = c.g->tensors[id];
     if (t.is_view_op() || t.nelements() == 0) return;
@@ -867,6 +973,7 @@ void lower_node(const LowerCtx &c, int32_t id, int pos, std::vector<Dispatch> &o
     if (op == "DUP" || op == "CPY" || op == "CONT") return lower_cpy(l);
     if (op == "ARGMAX") return lower_argmax(l);
     if (op == "CONCAT" || op == "REPEAT" || op == "SUM_ROWS" || op == "MEAN" || op == "ARANGE") return lower_simple(l);
+    if (op == "IM2COL" || op == "UPSCALE" || op == "POOL_2D" || op == "CONV_2D_DW" || op == "PAD" || op == "PAD_REFLECT_1D") return lower_image(l);
     if (op == "MUL_MAT") return lower_mul_mat(l);
     if (op == "MUL_MAT_GROUP") return lower_mul_mat_group(l);
     if (op == "CUSTOM") return lower_custom(l);

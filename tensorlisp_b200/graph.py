@@ -14,6 +14,8 @@ from __future__ import annotations
 
 import ctypes as C
 import struct
+
+import numpy as np
 from dataclasses import dataclass, field
 
 from . import _lib
@@ -320,6 +322,67 @@ class Graph:
     def sum_rows(self, a: int, name: str = "") -> int:
         A = self.tensors[a]
         return self._node(self._new(A.ty, [1, A.ne[1], A.ne[2], A.ne[3]]), "SUM_ROWS", [a], name=name)
+
+    # ------------------------------------------------------------------ image ops (shape rules of ggml.c)
+    @staticmethod
+    def _conv_out(ins: int, ks: int, s: int, p: int, d: int) -> int:  # ggml_calc_conv_output_size (ggml.c:4444-4446)
+        return (ins + 2 * p - d * (ks - 1) - 1) // s + 1
+
+    def im2col(self, kernel: int, data: int, s0: int, s1: int, p0: int, p1: int, d0: int, d1: int, is_2d: bool,
+               dst_type: int = F32, name: str = "") -> int:  # ggml_im2col (ggml.c:4452-4494)
+        A, B = self.tensors[kernel], self.tensors[data]
+        if is_2d:
+            assert A.ne[2] == B.ne[2]
+        else:
+            assert B.ne[1] == A.ne[1] and B.ne[3] == 1
+        oh = self._conv_out(B.ne[1], A.ne[1], s1, p1, d1) if is_2d else 0
+        ow = self._conv_out(B.ne[0], A.ne[0], s0, p0, d0)
+        assert ow > 0 and (not is_2d or oh > 0), "data too small for the kernel"
+        ne = [A.ne[2] * A.ne[1] * A.ne[0] if is_2d else A.ne[1] * A.ne[0], ow, oh if is_2d else B.ne[2], B.ne[3] if is_2d else 1]
+        return self._node(self._new(dst_type, ne), "IM2COL", [kernel, data],
+                          {0: s0, 1: s1, 2: p0, 3: p1, 4: d0, 5: d1, 6: 1 if is_2d else 0}, name)
+
+    def interpolate(self, a: int, ne0: int, ne1: int, ne2: int, ne3: int, mode: int, name: str = "") -> int:
+        """ggml_interpolate (ggml.c:5061-5082): mode = 0 nearest / 1 bilinear / 2 bicubic, | 1<<8 align corners, | 1<<9 antialias."""
+        A = self.tensors[a]
+        assert (mode & 0xFF) < 3 and A.ty == F32
+        assert not (mode & (1 << 9)) or (mode & 0xFF) == 1, "antialias is bilinear only"
+        return self._node(self._new(A.ty, [ne0, ne1, ne2, ne3]), "UPSCALE", [a], {0: mode}, name)
+
+    def upscale(self, a: int, scale_factor: int, mode: int = 0, name: str = "") -> int:  # ggml_upscale (ggml.c:5084-5091)
+        A = self.tensors[a]
+        assert scale_factor > 1
+        return self.interpolate(a, A.ne[0] * scale_factor, A.ne[1] * scale_factor, A.ne[2], A.ne[3], mode, name)
+
+    def pool_2d(self, a: int, op: int, k0: int, k1: int, s0: int, s1: int, p0: float, p1: float, name: str = "") -> int:
+        """ggml_pool_2d (ggml.c:4970-4972, 5004-5033): op 0 = max, 1 = average; the output size is computed in f32."""
+        A = self.tensors[a]
+        out = lambda ins, ks, s, p: int((np.float32(ins) + np.float32(2) * np.float32(p) - np.float32(ks)) / np.float32(s) + np.float32(1))
+        ne = [out(A.ne[0], k0, s0, p0), out(A.ne[1], k1, s1, p1), A.ne[2], A.ne[3]]
+        assert ne[0] > 0 and ne[1] > 0
+        return self._node(self._new(F32, ne), "POOL_2D", [a], {0: op, 1: k0, 2: k1, 3: s0, 4: s1, 5: int(p0), 6: int(p1)}, name)
+
+    def conv_2d_dw(self, kernel: int, data: int, s0: int, s1: int, p0: int, p1: int, d0: int, d1: int, name: str = "") -> int:
+        """ggml_conv_2d_dw_direct (ggml.c:4812-4848) on WHCN data (contiguous rows)."""
+        A, B = self.tensors[kernel], self.tensors[data]
+        assert A.ne[2] == 1 and A.ne[3] == B.ne[2]
+        assert not (B.nb[0] > B.nb[2] and B.nb[1] > B.nb[0] and B.nb[2] == TYPE_TRAITS[B.ty][2]), "channel-contiguous data is not modelled here"
+        ne = [self._conv_out(B.ne[0], A.ne[0], s0, p0, d0), self._conv_out(B.ne[1], A.ne[1], s1, p1, d1), B.ne[2], B.ne[3]]
+        return self._node(self._new(B.ty, ne), "CONV_2D_DW", [kernel, data], {0: s0, 1: s1, 2: p0, 3: p1, 4: d0, 5: d1}, name)
+
+    def pad_ext(self, a: int, lp0: int, rp0: int, lp1: int, rp1: int, lp2: int, rp2: int, lp3: int, rp3: int, name: str = "") -> int:
+        A = self.tensors[a]   # ggml_pad_ext (ggml.c:5139-5172)
+        ne = [A.ne[0] + lp0 + rp0, A.ne[1] + lp1 + rp1, A.ne[2] + lp2 + rp2, A.ne[3] + lp3 + rp3]
+        return self._node(self._new(A.ty, ne), "PAD", [a], {0: lp0, 1: rp0, 2: lp1, 3: rp1, 4: lp2, 5: rp2, 6: lp3, 7: rp3, 8: 0}, name)
+
+    def pad(self, a: int, p0: int, p1: int, p2: int, p3: int, name: str = "") -> int:  # ggml_pad: right padding only
+        return self.pad_ext(a, 0, p0, 0, p1, 0, p2, 0, p3, name)
+
+    def pad_reflect_1d(self, a: int, p0: int, p1: int, name: str = "") -> int:  # ggml_pad_reflect_1d (ggml.c:5195-5222)
+        A = self.tensors[a]
+        assert 0 <= p0 < A.ne[0] and 0 <= p1 < A.ne[0] and A.ty == F32
+        assert A.nb[0] == 4 and all(A.nb[i] == A.nb[i - 1] * A.ne[i - 1] for i in (1, 2, 3)), "contiguous input only"
+        return self._node(self._new(A.ty, [A.ne[0] + p0 + p1, A.ne[1], A.ne[2], A.ne[3]]), "PAD_REFLECT_1D", [a], {0: p0, 1: p1}, name)
 
     def cumsum(self, a: int, name: str = "") -> int:
         return self._node(self._dup(a), "CUMSUM", [a], name=name)

@@ -138,3 +138,32 @@ def test_glu_and_paged_nodes_ir(ref):
     u = g2.input(G.F32, [512, 4], "u")
     t = g2.glu(a, "swiglu", b=u)
     assert g2.tensors[t].ne == [512, 4, 1, 1] and g2.tensors[t].src[:2] == [a, u]
+
+
+def image_ops_program(b):
+    """Every image-op constructor once or more, with ggml's own constructor beside it; returns (name, node pair) list."""
+    x = b.leaf("input", G.F32, [10, 12, 4, 2], "img")
+    k16 = b.leaf("input", G.F16, [3, 3, 4, 8], "kernel")
+    kdw = b.leaf("input", G.F32, [3, 2, 1, 4], "dw_kernel")
+    x1 = b.leaf("input", G.F32, [50, 6, 3], "signal")
+    k1 = b.leaf("input", G.F16, [5, 6, 7], "kernel_1d")
+    out = []
+    out.append(("im2col 2d f16", b.op("im2col", "im2col", [k16, x], (1, 2, 1, 0, 1, 2, True, G.F16), ints=[1, 2, 1, 0, 1, 2, 1, G.F16])))
+    out.append(("im2col 2d f32", b.op("im2col", "im2col", [k16, x], (2, 1, 0, 1, 1, 1, True, G.F32), ints=[2, 1, 0, 1, 1, 1, 1, G.F32])))
+    out.append(("im2col 1d", b.op("im2col", "im2col", [k1, x1], (2, 0, 3, 0, 2, 0, False, G.F16), ints=[2, 0, 3, 0, 2, 0, 0, G.F16])))
+    for mode in (0, 1, 2, 1 | (1 << 8), 2 | (1 << 8), 1 | (1 << 9)):
+        out.append(("upscale mode %d" % mode, b.op("interpolate", "interpolate", [x], (23, 17, 4, 2, mode), ints=[23, 17, 4, 2, mode])))
+    out.append(("downscale antialias", b.op("interpolate", "interpolate", [x], (4, 5, 4, 2, 1 | (1 << 9)), ints=[4, 5, 4, 2, 1 | (1 << 9)])))
+    out.append(("upscale x2", b.op("interpolate", "interpolate", [x], (20, 24, 4, 2, 0), ints=[20, 24, 4, 2, 0])))
+    out.append(("pool max", b.op("pool_2d", "pool_2d", [x], (0, 3, 2, 2, 2, 1.0, 0.0), ints=[0, 3, 2, 2, 2], floats=[1.0, 0.0])))
+    out.append(("pool avg", b.op("pool_2d", "pool_2d", [x], (1, 2, 2, 2, 2, 0.0, 0.0), ints=[1, 2, 2, 2, 2], floats=[0.0, 0.0])))
+    out.append(("conv_2d_dw", b.op("conv_2d_dw", "conv_2d_dw", [kdw, x], (1, 2, 1, 1, 2, 1), ints=[1, 2, 1, 1, 2, 1])))
+    out.append(("pad_ext", b.op("pad_ext", "pad_ext", [x], (1, 2, 0, 3, 2, 0, 1, 1), ints=[1, 2, 0, 3, 2, 0, 1, 1])))
+    out.append(("pad_reflect_1d", b.op("pad_reflect_1d", "pad_reflect_1d", [x], (3, 5), ints=[3, 5])))
+    return out
+
+
+def test_image_op_ir_matches_ggml(ref):
+    g, rg, pairs = build_both(ref, image_ops_program)
+    compare(g, rg, pairs)
+    rg.close()
