@@ -11,6 +11,10 @@
 // padded by 16 bytes, so fragment loads and ldmatrix are conflict-free), S = Q K^T, online softmax in
 // base 2 on the accumulator fragments, P goes back in as the A operand of O += P V. Like the CPU
 // backend with an f16 cache, q is rounded to f16 before the dot products.
+#include <algorithm>
+#include <cstdlib>
+#include <string>
+
 #include <cuda_fp16.h>
 #include <math_constants.h>
 
@@ -56,7 +60,7 @@ __device__ __forceinline__ void stage8(__half *dst, const uint8_t *src, bool liv
 template <int D, bool KF32, bool VF32>
 __global__ void __launch_bounds__(FA_WARPS * 32) k_flash_attn(FlashArgs p, const uint8_t *__restrict__ q, const uint8_t *__restrict__ k,
                                                               const uint8_t *__restrict__ v, const uint8_t *__restrict__ mask,
-                                                              float *__restrict__ out) {
+                                                              float *__restrict__ out, float *__restrict__ partial) {
     griddep_launch();
     griddep_wait();
     constexpr int LDS = D + 8;                 // padded row length in halves
@@ -65,7 +69,9 @@ __global__ void __launch_bounds__(FA_WARPS * 32) k_flash_attn(FlashArgs p, const
     __shared__ __align__(16) __half Ks[FA_KT * LDS];
     __shared__ __align__(16) __half Vs[FA_KT * LDS];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int q0 = blockIdx.x * FA_QT + warp * 16;   // first query of this warp
+    const int part = blockIdx.x % p.parts;           // stretch of the keys this CTA covers (all of them without a split)
+    const int q0 = (blockIdx.x / p.parts) * FA_QT + warp * 16;   // first query of this warp
+    const int k_begin = part * p.part_len, k_end = min(p.nkv, k_begin + p.part_len);
     const int h = blockIdx.y, b = blockIdx.z;
     const int hk = h / (p.nh / p.nhkv);
     const int qr0 = q0 + (lane >> 2), qr1 = qr0 + 8;  // the two query rows this lane holds pieces of
@@ -101,7 +107,7 @@ __global__ void __launch_bounds__(FA_WARPS * 32) k_flash_attn(FlashArgs p, const
     float slope = 1.f;
     if (p.max_bias > 0.f) slope = h < p.n_head_log2 ? powf(p.m0, (float)(h + 1)) : powf(p.m1, (float)(2 * (h - p.n_head_log2) + 1));
 
-    for (int kt = 0; kt < p.nkv; kt += FA_KT) {
+    for (int kt = k_begin; kt < k_end; kt += FA_KT) {
         // ---- this lane's mask values of the tile (2 rows x 16 keys); a tile that is -inf for every
         // query of the CTA (the upper triangle of a causal mask) is skipped before anything is loaded
         __half mk[FA_KT / 8][4];
@@ -113,7 +119,7 @@ __global__ void __launch_bounds__(FA_WARPS * 32) k_flash_attn(FlashArgs p, const
                 for (int e = 0; e < 4; e++) {
                     const int key = kt + j * 8 + cq + (e & 1);
                     const __half *mr = (e & 2) ? mr1 : mr0;
-                    mk[j][e] = key < p.nkv ? mr[key] : __ushort_as_half(0xfc00);   // -inf past the last key
+                    mk[j][e] = key < k_end ? mr[key] : __ushort_as_half(0xfc00);   // -inf past the last key
                     dead = dead && (__half_as_ushort(mk[j][e]) == 0xfc00);
                 }
             }
@@ -121,8 +127,8 @@ __global__ void __launch_bounds__(FA_WARPS * 32) k_flash_attn(FlashArgs p, const
         if (__syncthreads_and(dead)) continue;   // also: the previous tile has been consumed
         for (int u = tid; u < FA_KT * (D / 8); u += FA_WARPS * 32) {
             const int row = u / (D / 8), c8 = u % (D / 8);
-            const bool live = kt + row < p.nkv;
-            const int64_t key = min(kt + row, p.nkv - 1);
+            const bool live = kt + row < k_end;
+            const int64_t key = min(kt + row, k_end - 1);
             stage8<KF32>(Ks + row * LDS + c8 * 8, kb + key * p.k.nb[1] + c8 * 8 * (KF32 ? 4 : 2), live);
             stage8<VF32>(Vs + row * LDS + c8 * 8, vb + key * p.v.nb[1] + c8 * 8 * (VF32 ? 4 : 2), live);
         }
@@ -150,8 +156,8 @@ __global__ void __launch_bounds__(FA_WARPS * 32) k_flash_attn(FlashArgs p, const
                 const int key = kt + j * 8 + cq + (e & 1);
                 float x = s[j][e] * p.scale;
                 if (p.softcap != 0.f) x = p.softcap * tanhf(x);
-                if (mb && key < p.nkv) x += slope * __half2float(mk[j][e]);
-                x = key < p.nkv ? x * LOG2E : -CUDART_INF_F;
+                if (mb && key < k_end) x += slope * __half2float(mk[j][e]);
+                x = key < k_end ? x * LOG2E : -CUDART_INF_F;
                 s[j][e] = x;
                 if (e & 2) mx1 = fmaxf(mx1, x);
                 else mx0 = fmaxf(mx0, x);
@@ -204,6 +210,22 @@ __global__ void __launch_bounds__(FA_WARPS * 32) k_flash_attn(FlashArgs p, const
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if (p.parts > 1) {
+        // (maximum, sum, unnormalised output) of this stretch: [batch][head][query][part][D + 2]
+        if (qr0 < p.nq) {
+            float *d = partial + ((((int64_t)b * p.nh + h) * p.nq + qr0) * p.parts + part) * (D + 2);
+            if (cq == 0) { d[0] = m0; d[1] = l0; }
+#pragma unroll
+            for (int j = 0; j < ND; j++) *reinterpret_cast<float2 *>(d + 2 + j * 8 + cq) = make_float2(o[j][0], o[j][1]);
+        }
+        if (qr1 < p.nq) {
+            float *d = partial + ((((int64_t)b * p.nh + h) * p.nq + qr1) * p.parts + part) * (D + 2);
+            if (cq == 0) { d[0] = m1; d[1] = l1; }
+#pragma unroll
+            for (int j = 0; j < ND; j++) *reinterpret_cast<float2 *>(d + 2 + j * 8 + cq) = make_float2(o[j][2], o[j][3]);
+        }
+        return;
+    }
     const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
     if (qr0 < p.nq) {
         float *d = out + (((int64_t)b * p.nq + qr0) * p.nh + h) * D;
@@ -217,23 +239,69 @@ __global__ void __launch_bounds__(FA_WARPS * 32) k_flash_attn(FlashArgs p, const
     }
 }
 
+// merges the stretches of a split: one CTA per (query, head, batch), one thread per output element
+template <int D>
+__global__ void __launch_bounds__(D) k_flash_merge(FlashArgs p, const float *__restrict__ partial, float *__restrict__ out) {
+    griddep_launch();
+    griddep_wait();
+    const int q = blockIdx.x, h = blockIdx.y, b = blockIdx.z, d = threadIdx.x;
+    const float *pp = partial + (((int64_t)b * p.nh + h) * p.nq + q) * p.parts * (D + 2);
+    float m = -CUDART_INF_F;
+    for (int c = 0; c < p.parts; c++) m = fmaxf(m, pp[(int64_t)c * (D + 2)]);
+    const float ref = m == -CUDART_INF_F ? 0.f : m;
+    float l = 0.f, a = 0.f;
+    for (int c = 0; c < p.parts; c++) {
+        const float f = exp2f(pp[(int64_t)c * (D + 2)] - ref);   // a stretch that saw only masked keys has m = -inf: weight 0
+        l += pp[(int64_t)c * (D + 2) + 1] * f;
+        a += pp[(int64_t)c * (D + 2) + 2 + d] * f;
+    }
+    out[(((int64_t)b * p.nq + q) * p.nh + h) * D + d] = l > 0.f ? a / l : 0.f;
+}
+
 }  // namespace
 
 bool flash_supported(int64_t d, int64_t dv) { return d == dv && (d == 64 || d == 128); }
 
-template <int D>
-static cudaError_t launch_fa(const FlashArgs &p, const void *q, const void *k, const void *v, const void *mask, float *out, cudaStream_t st) {
-    const dim3 grid((unsigned)((p.nq + FA_QT - 1) / FA_QT), (unsigned)p.nh, (unsigned)p.nb), block(FA_WARPS * 32);
-    const uint8_t *q8 = (const uint8_t *)q, *k8 = (const uint8_t *)k, *v8 = (const uint8_t *)v, *m8 = (const uint8_t *)mask;
-    if (p.k_f32 && p.v_f32) return launch_pdl(k_flash_attn<D, true, true>, grid, block, 0, st, p, q8, k8, v8, m8, out);
-    if (p.k_f32) return launch_pdl(k_flash_attn<D, true, false>, grid, block, 0, st, p, q8, k8, v8, m8, out);
-    if (p.v_f32) return launch_pdl(k_flash_attn<D, false, true>, grid, block, 0, st, p, q8, k8, v8, m8, out);
-    return launch_pdl(k_flash_attn<D, false, false>, grid, block, 0, st, p, q8, k8, v8, m8, out);
+// Split-KV for few queries over a long dense cache (the reference's rule, crates/kernels/src/cuda/lower.rs:764-779, on
+// this kernel's 64-key tiles): without it a one-query node runs heads x batch CTAs whatever the length of the cache.
+void flash_split_plan(FlashArgs &p, int sm_count) {
+    p.part_len = p.nkv > 0 ? p.nkv : 1;
+    p.parts = 1;
+    const char *e = getenv("TL_NATIVE_FA");
+    if (p.nq > FA_QT || p.nkv < 256 || (e && std::string(e) == "plain")) return;
+    const int64_t blocks = (int64_t)p.nh * p.nb;
+    const int64_t want = ((int64_t)p.nkv * blocks + 4 * (int64_t)sm_count - 1) / (4 * (int64_t)sm_count);
+    const int64_t part_len = std::max<int64_t>(FA_KT, (want + FA_KT - 1) / FA_KT * FA_KT);
+    const int64_t parts = (p.nkv + part_len - 1) / part_len;
+    if (parts >= 2) {
+        p.part_len = (int)part_len;
+        p.parts = (int)parts;
+    }
+}
+uint64_t flash_split_scratch_bytes(const FlashArgs &p) {
+    return p.parts > 1 ? (uint64_t)p.nb * p.nh * p.nq * p.parts * (p.d + 2) * 4 : 0;
 }
 
-cudaError_t launch_flash_attn(const FlashArgs &p, const void *q, const void *k, const void *v, const void *mask, float *out, cudaStream_t st) {
+template <int D>
+static cudaError_t launch_fa(const FlashArgs &p, const void *q, const void *k, const void *v, const void *mask, float *out, float *partial,
+                             cudaStream_t st) {
+    const dim3 grid((unsigned)((p.nq + FA_QT - 1) / FA_QT * p.parts), (unsigned)p.nh, (unsigned)p.nb), block(FA_WARPS * 32);
+    const uint8_t *q8 = (const uint8_t *)q, *k8 = (const uint8_t *)k, *v8 = (const uint8_t *)v, *m8 = (const uint8_t *)mask;
+    cudaError_t e;
+    if (p.k_f32 && p.v_f32) e = launch_pdl(k_flash_attn<D, true, true>, grid, block, 0, st, p, q8, k8, v8, m8, out, partial);
+    else if (p.k_f32) e = launch_pdl(k_flash_attn<D, true, false>, grid, block, 0, st, p, q8, k8, v8, m8, out, partial);
+    else if (p.v_f32) e = launch_pdl(k_flash_attn<D, false, true>, grid, block, 0, st, p, q8, k8, v8, m8, out, partial);
+    else e = launch_pdl(k_flash_attn<D, false, false>, grid, block, 0, st, p, q8, k8, v8, m8, out, partial);
+    if (e == cudaSuccess && p.parts > 1)
+        e = launch_pdl(k_flash_merge<D>, dim3((unsigned)p.nq, (unsigned)p.nh, (unsigned)p.nb), dim3(D), 0, st, p, (const float *)partial, out);
+    return e;
+}
+
+cudaError_t launch_flash_attn(const FlashArgs &p, const void *q, const void *k, const void *v, const void *mask, float *out, void *scratch,
+                              cudaStream_t st) {
     if (p.nq == 0 || p.nh == 0 || p.nb == 0) return cudaSuccess;
-    return p.d == 64 ? launch_fa<64>(p, q, k, v, mask, out, st) : launch_fa<128>(p, q, k, v, mask, out, st);
+    if (p.parts < 1 || (p.parts > 1 && !scratch)) return cudaErrorInvalidValue;
+    return p.d == 64 ? launch_fa<64>(p, q, k, v, mask, out, (float *)scratch, st) : launch_fa<128>(p, q, k, v, mask, out, (float *)scratch, st);
 }
 
 }  // namespace tlb

@@ -172,9 +172,16 @@ struct FlashArgs {
     int nq, nkv, nh, nhkv, nb, d, m_ne2, m_ne3, n_head_log2;
     float scale, softcap, max_bias, m0, m1;   // scale already divided by softcap when that is set
     bool k_f32, v_f32;
+    // split-KV (few queries over a long cache): the keys are cut into `parts` stretches of part_len, every stretch is a
+    // CTA of its own that leaves (maximum, sum, unnormalised output) in scratch, and a second launch merges them
+    int part_len, parts;
 };
 bool flash_supported(int64_t d, int64_t dv);
-cudaError_t launch_flash_attn(const FlashArgs &p, const void *q, const void *k, const void *v, const void *mask, float *out, cudaStream_t st);
+// fills p.part_len / p.parts (parts = 1: no split) for a device of sm_count SMs; bytes of scratch the split needs
+void flash_split_plan(FlashArgs &p, int sm_count);
+uint64_t flash_split_scratch_bytes(const FlashArgs &p);
+cudaError_t launch_flash_attn(const FlashArgs &p, const void *q, const void *k, const void *v, const void *mask, float *out, void *scratch,
+                              cudaStream_t st);
 // ---------------------------------------------------------------- k_flash_tc.cu
 // The same op on tcgen05 for prompt-sized query counts (head size 128, f16 keys / values, no soft cap, no ALiBi);
 // scratch holds the packed operands and the per-tile mask flags.

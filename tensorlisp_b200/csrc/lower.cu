@@ -735,8 +735,19 @@ void lower_flash(L &l) {
         });
         return;
     }
+    // few queries over a long cache: the keys are split over CTAs, partial results in the node's scratch
+    flash_split_plan(p, l.c.dev->prop.multiProcessorCount);
+    Place ps;
+    if (p.parts > 1) {
+        const int64_t sc = l.c.layout->scratch[l.pos];
+        if (sc < 0) throw std::string("attention scratch was not planned");
+        ps.buf = BUF_ARENA;
+        ps.off = (uint64_t)sc;
+    }
+    const bool split = p.parts > 1;
     l.push([=](const RunCtx &r) {
-        return launch_flash_attn(p, r.at(pq), r.at(pk), r.at(pv), has_mask ? r.at(pm) : nullptr, (float *)r.at(pd), r.stream);
+        return launch_flash_attn(p, r.at(pq), r.at(pk), r.at(pv), has_mask ? r.at(pm) : nullptr, (float *)r.at(pd), split ? r.at(ps) : nullptr,
+                                 r.stream);
     });
 }
 
@@ -820,7 +831,11 @@ uint64_t node_scratch_bytes(const Graph &g, int32_t id, int sm_count) {
     }
     if (t.op == "FLASH_ATTN_EXT") {
         FlashArgs p{};
-        if (flash_args(g, t, p) == nullptr && flash_tc_supported(p, t.src[3] >= 0)) return flash_tc_scratch_bytes(p, t.src[3] >= 0);
+        if (flash_args(g, t, p) == nullptr) {
+            if (flash_tc_supported(p, t.src[3] >= 0)) return flash_tc_scratch_bytes(p, t.src[3] >= 0);
+            flash_split_plan(p, sm_count);
+            return flash_split_scratch_bytes(p);
+        }
     }
     if (t.op == "MUL_MAT_GROUP") {
         const Tensor &tx = g.tensors[t.src[1]];

@@ -150,3 +150,30 @@ def test_causal_prompt_2048_tokens():
             want = (p / p.sum()) @ vv[:i + 1]
             worst = max(worst, float(np.abs(got[i, h] - want).max() / max(np.abs(want).max(), 1e-6)))
     assert worst <= TOL, worst
+
+
+@pytest.mark.parametrize("nq,nkv,nh,nhkv,nb", [(1, 4000, 8, 2, 2), (3, 1111, 4, 4, 1), (1, 300, 32, 8, 1)])
+def test_few_queries_over_a_long_cache_split_the_keys(nq, nkv, nh, nhkv, nb):
+    """A one-query FLASH_ATTN_EXT over a long dense cache cuts the keys into stretches, one CTA each, and merges them with a
+    second launch (the reference's split-KV decode, crates/kernels/src/cuda/native/fa.cu:114-231, lower.rs:764-779). The mask
+    hides a tail of the cache (what a decode step over a preallocated dense cache passes). Checked against the closed form
+    and against the same node with the split turned off (TL_NATIVE_FA=plain)."""
+    import os
+    d = 128
+    rng = np.random.default_rng(nq + nkv)
+    q = rng.standard_normal((nb, nh, nq, d)).astype(np.float32)
+    k = rng.standard_normal((nb, nhkv, nkv, d)).astype(np.float16)
+    v = rng.standard_normal((nb, nhkv, nkv, d)).astype(np.float16)
+    nq_pad = (nq + 31) // 32 * 32
+    mask = np.zeros((1, 1, nq_pad, nkv), np.float16)
+    mask[..., nkv - nkv // 5:] = -np.inf
+    scale = 1.0 / np.sqrt(d)
+    got = run_gpu(q, k, v, mask, scale, 0.0, 0.0, G.F16)
+    os.environ["TL_NATIVE_FA"] = "plain"
+    try:
+        plain = run_gpu(q, k, v, mask, scale, 0.0, 0.0, G.F16)
+    finally:
+        del os.environ["TL_NATIVE_FA"]
+    want = closed_form(q.astype(np.float16), k, v, mask, scale, 0.0, 0.0)
+    close(got, want, TOL)
+    close(got, plain, 5e-4)     # P is rounded to f16 against a different running maximum in the two schedules
