@@ -295,8 +295,7 @@ def tp_parity(world: int, rank: int, local_rank: int, dist, batch: int = 8) -> d
             handles = [None] * world
             dist.all_gather_object(handles, native.comm_p2p_export())
             native.comm_p2p_import(handles)
-            if world > 2 or os.environ.get("TLB_P2P_ALLREDUCE") == "1":
-                path = "peer memory" + (", exchange not fused" if os.environ.get("TLB_NO_FUSED_EXCHANGE") == "1" else ", fused exchange")
+            path = "peer memory" + (", exchange not fused" if os.environ.get("TLB_NO_FUSED_EXCHANGE") == "1" else ", fused exchange")
     prog = NativeProgram.compile(native, dg.graph)
     for i, a in enumerate([ids, pos, tables, lens, slots.view(np.int32)]):
         prog.set_input(i, a)
@@ -375,8 +374,7 @@ def run_ours(args) -> dict:
                 handles = [None] * world
                 dist.all_gather_object(handles, native.comm_p2p_export())
                 native.comm_p2p_import(handles)
-                allreduce = ("one-shot over peer memory" if world > 2 or os.environ.get("TLB_P2P_ALLREDUCE") == "1"
-                             else "nccl (peer memory set up; used above 2 ranks)")
+                allreduce = "one-shot over peer memory"
             except Exception as e:
                 allreduce = "nccl (peer memory unavailable: %s)" % e
 

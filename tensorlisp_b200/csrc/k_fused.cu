@@ -264,10 +264,11 @@ bool row_quant_q80_supported(int64_t K, int mode) { return K % 256 == 0 && K >= 
 // Tensor parallelism: the all-reduce behind a row-parallel projection, the residual add, the RMS norm and the
 // Q8_K quantization of the next mul_mat's input as ONE kernel. A CTA owns one activation row (token): it adds up
 // the K-split partial sums of its rank (if any), pushes the row into a slot of every peer's exchange buffer with
-// plain stores over NVLink, raises its flag there, waits (bounded) for the same row of every rank in its own
-// buffer, adds the slots in rank order (so all ranks hold identical sums), and then has the whole reduced row in
-// the registers of its 16 warps: residual add, sum of squares, scale, quantize, pack. Protocol and buffer layout
-// are those of the plain all-reduce (comm.cu, exchange.cuh), in the second buffer set.
+// plain stores over NVLink, each value in one 8-byte word with the call's sequence number; every thread then waits
+// (bounded) for its own eight values of every rank in the local buffer, adds them in rank order (so all ranks hold
+// identical sums), and the CTA has the whole reduced row in the registers of its 16 warps: residual add, sum of
+// squares, scale, quantize, pack. Slots alternate by call parity as in the plain all-reduce (comm.cu, exchange.cuh);
+// this kernel uses the second buffer set, whose flag area it does not need.
 constexpr int XR_THREADS = 512;   // 16 warps, one 256-value block each: rows up to 4096 elements
 
 __device__ __forceinline__ void xr_body(const ArRank &a, const RowQuantArgs &p, int n_ranks, int n, int rows) {
@@ -305,26 +306,45 @@ __device__ __forceinline__ void xr_body(const ArRank &a, const RowQuantArgs &p, 
             b0.x = __fadd_rn(b0.x, c0.x); b0.y = __fadd_rn(b0.y, c0.y); b0.z = __fadd_rn(b0.z, c0.z); b0.w = __fadd_rn(b0.w, c0.w);
             b1.x = __fadd_rn(b1.x, c1.x); b1.y = __fadd_rn(b1.y, c1.y); b1.z = __fadd_rn(b1.z, c1.z); b1.w = __fadd_rn(b1.w, c1.w);
         }
-        const size_t off = AR_SET_BYTES + AR_DATA_OFF + ((size_t)par * AR_MAX_RANKS + a.rank) * AR_SLOT_BYTES + (size_t)e0 * 4;
+        // Every value travels with the call's sequence number in the same 8-byte word (the data slots of this set hold
+        // {f32, u32} pairs), so there is no fence, no separate flag and no second round trip: a reader that sees the
+        // number sees the value. An aligned 8-byte store is not torn on the way.
+        const size_t off = AR_SET_BYTES + AR_DATA_OFF + ((size_t)par * AR_MAX_RANKS + a.rank) * AR_SLOT_BYTES + (size_t)e0 * 8;
+        const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
         for (int r = 0; r < n_ranks; r++) {
-            float4 *dst = reinterpret_cast<float4 *>(a.peer[r] + off);
-            dst[0] = b0;
-            dst[1] = b1;
+            char *dst = a.peer[r] + off;
+#pragma unroll
+            for (int e = 0; e < 8; e += 2)
+                asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst + e * 8), "r"(__float_as_uint(bv[e])), "r"(seq),
+                             "r"(__float_as_uint(bv[e + 1])), "r"(seq)
+                             : "memory");
         }
     }
-    __threadfence_system();
-    __syncthreads();
-    if (tid < n_ranks) {
-        uint32_t *flag = reinterpret_cast<uint32_t *>(a.peer[tid] + AR_SET_BYTES + AR_FLAG_OFF) + ((size_t)par * AR_MAX_RANKS + a.rank) * AR_CTAS + n;
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(seq) : "memory");
-        const uint32_t *mine = reinterpret_cast<const uint32_t *>(local + AR_FLAG_OFF) + ((size_t)par * AR_MAX_RANKS + tid) * AR_CTAS + n;
-        bool ok = false;
-        for (uint32_t it = 0; it < a.spin_limit; it++) {
-            uint32_t f;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(f) : "l"(mine) : "memory");
-            if ((int32_t)(f - seq) >= 0) { ok = true; break; }
+    __syncthreads();   // s_fail is initialised for everybody
+    // ---- wait (bounded) for this thread's eight values of every rank in the local slots, add them in rank order
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float ss = 0.f;
+    const int64_t k0 = (int64_t)warp * 256 + lane * 8;
+    float s8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (live) {
+        const char *slots = local + AR_DATA_OFF + (size_t)par * AR_MAX_RANKS * AR_SLOT_BYTES + (size_t)e0 * 8;
+        bool gave_up = false;
+        for (int r = 0; r < n_ranks && !gave_up; r++) {
+            const char *src = slots + (size_t)r * AR_SLOT_BYTES;
+#pragma unroll
+            for (int e = 0; e < 8; e += 2) {
+                uint32_t d0 = 0, f0 = 0, d1 = 0, f1 = 0, it = 0;
+                for (;;) {
+                    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(d0), "=r"(f0), "=r"(d1), "=r"(f1) : "l"(src + e * 8) : "memory");
+                    if (f0 == seq && f1 == seq) break;
+                    if (++it >= a.spin_limit || *(volatile int *)&s_fail) { gave_up = true; break; }
+                }
+                // rank 0's values start the sums (0 + x would turn -0 into +0)
+                s8[e] = r == 0 ? __uint_as_float(d0) : __fadd_rn(s8[e], __uint_as_float(d0));
+                s8[e + 1] = r == 0 ? __uint_as_float(d1) : __fadd_rn(s8[e + 1], __uint_as_float(d1));
+            }
         }
-        if (!ok) s_fail = 1;
+        if (gave_up) s_fail = 1;
     }
     __syncthreads();
     if (s_fail) {
@@ -334,19 +354,8 @@ __device__ __forceinline__ void xr_body(const ArRank &a, const RowQuantArgs &p, 
         }
         return;
     }
-    // ---- sum over the ranks in rank order (L2 loads: L1 may hold this slot's lines of two calls ago), residual add
-    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    float ss = 0.f;
-    const int64_t k0 = (int64_t)warp * 256 + lane * 8;
     if (live) {
-        const char *slots = local + AR_DATA_OFF + (size_t)par * AR_MAX_RANKS * AR_SLOT_BYTES + (size_t)e0 * 4;
-        float4 s0 = __ldcg(reinterpret_cast<const float4 *>(slots)), s1 = __ldcg(reinterpret_cast<const float4 *>(slots) + 1);
-        for (int r = 1; r < n_ranks; r++) {
-            const float4 c0 = __ldcg(reinterpret_cast<const float4 *>(slots + (size_t)r * AR_SLOT_BYTES));
-            const float4 c1 = __ldcg(reinterpret_cast<const float4 *>(slots + (size_t)r * AR_SLOT_BYTES) + 1);
-            s0.x = __fadd_rn(s0.x, c0.x); s0.y = __fadd_rn(s0.y, c0.y); s0.z = __fadd_rn(s0.z, c0.z); s0.w = __fadd_rn(s0.w, c0.w);
-            s1.x = __fadd_rn(s1.x, c1.x); s1.y = __fadd_rn(s1.y, c1.y); s1.z = __fadd_rn(s1.z, c1.z); s1.w = __fadd_rn(s1.w, c1.w);
-        }
+        const float4 s0 = make_float4(s8[0], s8[1], s8[2], s8[3]), s1 = make_float4(s8[4], s8[5], s8[6], s8[7]);
         const float4 a0 = *reinterpret_cast<const float4 *>(p.a + n * p.lda + k0), a1 = *reinterpret_cast<const float4 *>(p.a + n * p.lda + k0 + 4);
         v[0] = __fadd_rn(a0.x, s0.x); v[1] = __fadd_rn(a0.y, s0.y); v[2] = __fadd_rn(a0.z, s0.z); v[3] = __fadd_rn(a0.w, s0.w);
         v[4] = __fadd_rn(a1.x, s1.x); v[5] = __fadd_rn(a1.y, s1.y); v[6] = __fadd_rn(a1.z, s1.z); v[7] = __fadd_rn(a1.w, s1.w);
@@ -395,6 +404,10 @@ __device__ __forceinline__ void xr_body(const ArRank &a, const RowQuantArgs &p, 
 }
 
 __global__ void __launch_bounds__(XR_THREADS) k_exchange_row_quant(ArRank a, RowQuantArgs p, int n_ranks) {
+    // the mul_mat behind this kernel may start and prefetch its weights while the ranks exchange their rows (it waits
+    // for this grid before it touches the activations); the trigger fires once every CTA of this grid is running
+    griddep_launch();
+    griddep_wait();
     xr_body(a, p, n_ranks, blockIdx.x, (int)p.N);
 }
 // All ranks in ONE cooperative launch on one GPU (blockIdx.y = rank): the single-GPU test of the fused kernel
@@ -406,13 +419,13 @@ __global__ void __launch_bounds__(XR_THREADS) k_exchange_row_quant_emulated(XrAl
     xr_body(all.a[blockIdx.y], all.p[blockIdx.y], n_ranks, blockIdx.x, (int)all.p[blockIdx.y].N);
 }
 
-bool exchange_row_quant_supported(int64_t K, int64_t N) { return K % 256 == 0 && K / 256 <= XR_THREADS / 32 && N >= 1 && N <= AR_CTAS && N * K * 4 <= (int64_t)AR_SLOT_BYTES; }
+// (a slot holds {value, sequence number} pairs: 8 bytes per element)
+bool exchange_row_quant_supported(int64_t K, int64_t N) { return K % 256 == 0 && K / 256 <= XR_THREADS / 32 && N >= 1 && N <= AR_CTAS && N * K * 8 <= (int64_t)AR_SLOT_BYTES; }
 
 static int xr_rows(const RowQuantArgs &p) { return p.npad > 0 ? (int)((p.N + p.npad - 1) / p.npad) * p.npad : (int)p.N; }
 
 cudaError_t launch_exchange_row_quant(const ArRank &a, const RowQuantArgs &p, int n_ranks, cudaStream_t st) {
-    k_exchange_row_quant<<<xr_rows(p), XR_THREADS, 0, st>>>(a, p, n_ranks);
-    return cudaGetLastError();
+    return launch_pdl(k_exchange_row_quant, dim3((unsigned)xr_rows(p)), dim3(XR_THREADS), 0, st, a, p, n_ranks);
 }
 
 // n_ranks <= 4 emulated ranks, one cooperative launch

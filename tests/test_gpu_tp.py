@@ -16,14 +16,14 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 PATHS = {
     "nccl": {"TLB_NO_P2P_ALLREDUCE": "1"},
-    "peer memory, fused exchange": {"TLB_P2P_ALLREDUCE": "1"},
-    "peer memory, exchange not fused": {"TLB_P2P_ALLREDUCE": "1", "TLB_NO_FUSED_EXCHANGE": "1"},
+    "peer memory, fused exchange": {},
+    "peer memory, exchange not fused": {"TLB_NO_FUSED_EXCHANGE": "1"},
 }
 
 
 def run_ranks(n, env_extra, port):
     env = dict(os.environ)
-    for k in ("TLB_NO_P2P_ALLREDUCE", "TLB_P2P_ALLREDUCE", "TLB_NO_FUSED_EXCHANGE"):
+    for k in ("TLB_NO_P2P_ALLREDUCE", "TLB_NO_FUSED_EXCHANGE"):
         env.pop(k, None)
     env.update(env_extra)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(n), "--master-addr", "127.0.0.1",
