@@ -185,6 +185,7 @@ cudaError_t comm_exchange_row_quant(tlb_device *dev, float *data, const float *p
     a.rank = c->rank;
     a.err = err;
     a.spin_limit = ar_spin_limit();
+    a.flagged_words = xr_flagged_words(c->n_ranks);
     for (int r = 0; r < c->n_ranks; r++) a.peer[r] = c->peer[r];
     return launch_exchange_row_quant(a, p, c->n_ranks, st);
 }
@@ -411,6 +412,7 @@ static tlb_status p2p_selftest_rows(tlb_device *dev, int n_ranks, int rows, int 
         a[r].rank = r;
         a[r].err = err;
         a[r].spin_limit = spin_limit;
+        a[r].flagged_words = xr_flagged_words(n_ranks);
         a[r].skip_push = r == absent_rank;
         for (int k = 0; k < n_ranks; k++) a[r].peer[k] = bufs[k];
         p[r] = RowQuantArgs{};

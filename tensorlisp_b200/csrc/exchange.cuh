@@ -31,7 +31,18 @@ struct ArRank {
     int *err;
     uint32_t spin_limit;         // probes of a peer's flag before the wait gives up and the error word is set
     int skip_push;               // self tests only: this rank neither pushes nor raises its flags, so its peers' waits run out
+    int flagged_words;           // fused row exchange: 1 = every value carries the sequence number (lowest latency, twice the
+                                 // bytes), 0 = plain values, a system fence and one flag per (rank, row)
 };
+// Which of the two the fused row exchange uses: flagged words at 2 ranks, fence and flag above. Measured on B200, batch-32
+// decode step: 2 ranks 3.56 ms with flagged words against 3.95 with fence and flag; 4 ranks 3.96 against 3.59; 8 ranks 5.40
+// against 3.76 (every rank pushes to every peer, so the doubled bytes (7.3 MB per exchange and GPU at 8 ranks) and sixteen
+// thousand polling threads per GPU cost more than the round trip they save). TLB_XR_FLAGGED=0/1 overrides.
+inline int xr_flagged_words(int n_ranks) {
+    const char *v = getenv("TLB_XR_FLAGGED");
+    if (v && (v[0] == '0' || v[0] == '1')) return v[0] == '1';
+    return n_ranks <= 2;
+}
 // the limit the host passes to the kernels
 inline uint32_t ar_spin_limit() {
     const char *v = getenv("TLB_AR_SPIN_LIMIT");

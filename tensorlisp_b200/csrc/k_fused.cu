@@ -306,45 +306,84 @@ __device__ __forceinline__ void xr_body(const ArRank &a, const RowQuantArgs &p, 
             b0.x = __fadd_rn(b0.x, c0.x); b0.y = __fadd_rn(b0.y, c0.y); b0.z = __fadd_rn(b0.z, c0.z); b0.w = __fadd_rn(b0.w, c0.w);
             b1.x = __fadd_rn(b1.x, c1.x); b1.y = __fadd_rn(b1.y, c1.y); b1.z = __fadd_rn(b1.z, c1.z); b1.w = __fadd_rn(b1.w, c1.w);
         }
-        // Every value travels with the call's sequence number in the same 8-byte word (the data slots of this set hold
-        // {f32, u32} pairs), so there is no fence, no separate flag and no second round trip: a reader that sees the
-        // number sees the value. An aligned 8-byte store is not torn on the way.
-        const size_t off = AR_SET_BYTES + AR_DATA_OFF + ((size_t)par * AR_MAX_RANKS + a.rank) * AR_SLOT_BYTES + (size_t)e0 * 8;
-        const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-        for (int r = 0; r < n_ranks; r++) {
-            char *dst = a.peer[r] + off;
+        if (a.flagged_words) {
+            // Every value travels with the call's sequence number in the same 8-byte word (the data slots then hold
+            // {f32, u32} pairs), so there is no fence, no separate flag and no second round trip: a reader that sees
+            // the number sees the value. An aligned 8-byte store is not torn on the way. Twice the bytes on the wire.
+            const size_t off = AR_SET_BYTES + AR_DATA_OFF + ((size_t)par * AR_MAX_RANKS + a.rank) * AR_SLOT_BYTES + (size_t)e0 * 8;
+            const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            for (int r = 0; r < n_ranks; r++) {
+                char *dst = a.peer[r] + off;
 #pragma unroll
-            for (int e = 0; e < 8; e += 2)
-                asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst + e * 8), "r"(__float_as_uint(bv[e])), "r"(seq),
-                             "r"(__float_as_uint(bv[e + 1])), "r"(seq)
-                             : "memory");
+                for (int e = 0; e < 8; e += 2)
+                    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst + e * 8), "r"(__float_as_uint(bv[e])), "r"(seq),
+                                 "r"(__float_as_uint(bv[e + 1])), "r"(seq)
+                                 : "memory");
+            }
+        } else {
+            const size_t off = AR_SET_BYTES + AR_DATA_OFF + ((size_t)par * AR_MAX_RANKS + a.rank) * AR_SLOT_BYTES + (size_t)e0 * 4;
+            for (int r = 0; r < n_ranks; r++) {
+                float4 *dst = reinterpret_cast<float4 *>(a.peer[r] + off);
+                dst[0] = b0;
+                dst[1] = b1;
+            }
         }
     }
-    __syncthreads();   // s_fail is initialised for everybody
-    // ---- wait (bounded) for this thread's eight values of every rank in the local slots, add them in rank order
+    if (!a.flagged_words) __threadfence_system();
+    __syncthreads();   // (s_fail is initialised for everybody)
     float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     float ss = 0.f;
     const int64_t k0 = (int64_t)warp * 256 + lane * 8;
     float s8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    if (live) {
-        const char *slots = local + AR_DATA_OFF + (size_t)par * AR_MAX_RANKS * AR_SLOT_BYTES + (size_t)e0 * 8;
-        bool gave_up = false;
-        for (int r = 0; r < n_ranks && !gave_up; r++) {
-            const char *src = slots + (size_t)r * AR_SLOT_BYTES;
+    if (a.flagged_words) {
+        // ---- wait (bounded) for this thread's eight values of every rank in the local slots, add them in rank order
+        if (live) {
+            const char *slots = local + AR_DATA_OFF + (size_t)par * AR_MAX_RANKS * AR_SLOT_BYTES + (size_t)e0 * 8;
+            bool gave_up = false;
+            for (int r = 0; r < n_ranks && !gave_up; r++) {
+                const char *src = slots + (size_t)r * AR_SLOT_BYTES;
 #pragma unroll
-            for (int e = 0; e < 8; e += 2) {
-                uint32_t d0 = 0, f0 = 0, d1 = 0, f1 = 0, it = 0;
-                for (;;) {
-                    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(d0), "=r"(f0), "=r"(d1), "=r"(f1) : "l"(src + e * 8) : "memory");
-                    if (f0 == seq && f1 == seq) break;
-                    if (++it >= a.spin_limit || *(volatile int *)&s_fail) { gave_up = true; break; }
+                for (int e = 0; e < 8; e += 2) {
+                    uint32_t d0 = 0, f0 = 0, d1 = 0, f1 = 0, it = 0;
+                    for (;;) {
+                        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(d0), "=r"(f0), "=r"(d1), "=r"(f1) : "l"(src + e * 8) : "memory");
+                        if (f0 == seq && f1 == seq) break;
+                        if (++it >= a.spin_limit || *(volatile int *)&s_fail) { gave_up = true; break; }
+                        __nanosleep(100);   // sixteen thousand threads polling without a pause hold up the writes they wait for
+                    }
+                    // rank 0's values start the sums (0 + x would turn -0 into +0)
+                    s8[e] = r == 0 ? __uint_as_float(d0) : __fadd_rn(s8[e], __uint_as_float(d0));
+                    s8[e + 1] = r == 0 ? __uint_as_float(d1) : __fadd_rn(s8[e + 1], __uint_as_float(d1));
                 }
-                // rank 0's values start the sums (0 + x would turn -0 into +0)
-                s8[e] = r == 0 ? __uint_as_float(d0) : __fadd_rn(s8[e], __uint_as_float(d0));
-                s8[e + 1] = r == 0 ? __uint_as_float(d1) : __fadd_rn(s8[e + 1], __uint_as_float(d1));
+            }
+            if (gave_up) s_fail = 1;
+        }
+    } else {
+        // ---- one flag per (rank, row): raised behind the fence above, awaited (bounded) by one thread per rank
+        if (tid < n_ranks) {
+            uint32_t *flag = reinterpret_cast<uint32_t *>(a.peer[tid] + AR_SET_BYTES + AR_FLAG_OFF) + ((size_t)par * AR_MAX_RANKS + a.rank) * AR_CTAS + n;
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(seq) : "memory");
+            const uint32_t *mine = reinterpret_cast<const uint32_t *>(local + AR_FLAG_OFF) + ((size_t)par * AR_MAX_RANKS + tid) * AR_CTAS + n;
+            bool ok = false;
+            for (uint32_t it = 0; it < a.spin_limit; it++) {
+                uint32_t f;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(f) : "l"(mine) : "memory");
+                if ((int32_t)(f - seq) >= 0) { ok = true; break; }
+            }
+            if (!ok) s_fail = 1;
+        }
+        __syncthreads();
+        // the slots in rank order (L2 loads: L1 may hold this slot's lines of two calls ago)
+        if (live && !s_fail) {
+            const char *slots = local + AR_DATA_OFF + (size_t)par * AR_MAX_RANKS * AR_SLOT_BYTES + (size_t)e0 * 4;
+            for (int r = 0; r < n_ranks; r++) {
+                const float4 c0 = __ldcg(reinterpret_cast<const float4 *>(slots + (size_t)r * AR_SLOT_BYTES));
+                const float4 c1 = __ldcg(reinterpret_cast<const float4 *>(slots + (size_t)r * AR_SLOT_BYTES) + 1);
+                const float cv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+                for (int e = 0; e < 8; e++) s8[e] = r == 0 ? cv[e] : __fadd_rn(s8[e], cv[e]);
             }
         }
-        if (gave_up) s_fail = 1;
     }
     __syncthreads();
     if (s_fail) {
@@ -419,7 +458,7 @@ __global__ void __launch_bounds__(XR_THREADS) k_exchange_row_quant_emulated(XrAl
     xr_body(all.a[blockIdx.y], all.p[blockIdx.y], n_ranks, blockIdx.x, (int)all.p[blockIdx.y].N);
 }
 
-// (a slot holds {value, sequence number} pairs: 8 bytes per element)
+// (with flagged words a slot holds {value, sequence number} pairs: 8 bytes per element)
 bool exchange_row_quant_supported(int64_t K, int64_t N) { return K % 256 == 0 && K / 256 <= XR_THREADS / 32 && N >= 1 && N <= AR_CTAS && N * K * 8 <= (int64_t)AR_SLOT_BYTES; }
 
 static int xr_rows(const RowQuantArgs &p) { return p.npad > 0 ? (int)((p.N + p.npad - 1) / p.npad) * p.npad : (int)p.N; }

@@ -49,13 +49,16 @@ def test_exchange_behind_a_k_split(native, ranks, splits):
         assert np.array_equal(out[r], want), r
 
 
+@pytest.mark.parametrize("flagged", ["0", "1"])
 @pytest.mark.parametrize("ranks,splits", [(2, 1), (4, 4), (3, 2)])
-def test_exchange_fused_with_add_norm_quant(native, oracle, ranks, splits):
-    """The exchange behind a row-parallel projection fused with the residual add, the RMS norm and the Q8_K
+def test_exchange_fused_with_add_norm_quant(native, oracle, ranks, splits, flagged, monkeypatch):
+    """Both protocols of the fused exchange (TLB_XR_FLAGGED: every value in one 8-byte word with the call's sequence
+    number, or plain values behind a system fence and one flag per rank and row). The exchange behind a row-parallel projection fused with the residual add, the RMS norm and the Q8_K
     quantizer of the next mul_mat (emulated ranks, one cooperative launch): the new residual stream is the
     exact f32 sum in split, then rank, order on every rank; the Q8_K block is the oracle's quantization of
     the oracle's norm of that stream (codes may differ by one where the sum of squares was added up in
     another order)."""
+    monkeypatch.setenv("TLB_XR_FLAGGED", flagged)
     rows, K, calls, eps = 32, 4096, 3, 1e-5
     rng = np.random.default_rng(ranks * 7 + splits)
     x = (rng.standard_normal((ranks, splits, rows, K)) * 0.5).astype(np.float32)
@@ -113,8 +116,10 @@ def test_a_rank_that_never_arrives_ends_the_wait(native, ranks, absent):
     assert np.array_equal(out, np.full_like(out, 2.0 * ranks))
 
 
-def test_a_rank_that_never_arrives_ends_the_fused_exchange(native):
+@pytest.mark.parametrize("flagged", ["0", "1"])
+def test_a_rank_that_never_arrives_ends_the_fused_exchange(native, flagged, monkeypatch):
     from tensorlisp_b200._lib import TLB_EXECUTION
+    monkeypatch.setenv("TLB_XR_FLAGGED", flagged)
     ranks, rows, K, eps = 4, 32, 4096, 1e-5
     x = np.ones((ranks, 1, rows, K), np.float32)
     resid = np.ones((rows, K), np.float32)
