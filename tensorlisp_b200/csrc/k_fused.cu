@@ -97,7 +97,19 @@ __device__ __forceinline__ void rq_quant_block(const RowQuantArgs &p, int n, int
     *reinterpret_cast<uint2 *>(qs + (size_t)n * K + k0) = packed;
     if ((lane & 1) == 0) bsums[(size_t)n * (K / 16) + sb * 16 + (lane >> 1)] = (int16_t)s16;
     if (lane == 0) ds[(size_t)n * (K / 256) + sb] = d;
-    if (p.npad > 0) {
+    if (p.npad == MM_FOLD_NPAD) {
+        // operand of the folded-scale prompt GEMM: f16(code x scale), blobs of 256 columns x 64 elements of K, natural order
+        const int64_t kk = (int64_t)sb * 256 + lane * 8;
+        uint8_t *o = (uint8_t *)ob + p.blob_off + ((size_t)(n >> 8) * (size_t)(K / 64) + (size_t)(kk >> 6)) * 32768 + (size_t)((n & 255) >> 3) * 1024 +
+                     (size_t)((kk & 63) >> 3) * 128 + (size_t)(n & 7) * 16;
+        uint32_t h[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const __half2 t = __floats2half2_rn(__fmul_rn((float)q[2 * e], d), __fmul_rn((float)q[2 * e + 1], d));
+            h[e] = *reinterpret_cast<const uint32_t *>(&t);
+        }
+        *reinterpret_cast<uint4 *>(o) = make_uint4(h[0], h[1], h[2], h[3]);
+    } else if (p.npad > 0) {
         // tensor-core operand: this lane's 8 codes are K chunk `lane` of column n, in the order
         // (0, 2, 1, 3, 4, 6, 5, 7) in which the weight nibbles come out of a 32-bit word
         const int ch = n / p.npad, nl = n % p.npad;   // blobs: [chunk of npad columns][block]
@@ -130,7 +142,13 @@ __global__ void __launch_bounds__(RQ_THREADS) k_row_quant_q8k(RowQuantArgs p) {
     char *ob = (char *)p.out;
     if (n >= p.N) {
         // padding columns of the tensor-core blobs are zero
-        if (p.npad > 0 && sb < nblk) {
+        if (p.npad == MM_FOLD_NPAD) {
+            if (sb < nblk) {
+                const int64_t kk = (int64_t)sb * 256 + lane * 8;
+                *reinterpret_cast<uint4 *>((uint8_t *)ob + p.blob_off + ((size_t)(n >> 8) * (size_t)(K / 64) + (size_t)(kk >> 6)) * 32768 +
+                                           (size_t)((n & 255) >> 3) * 1024 + (size_t)((kk & 63) >> 3) * 128 + (size_t)(n & 7) * 16) = make_uint4(0, 0, 0, 0);
+            }
+        } else if (p.npad > 0 && sb < nblk) {
             const int ch = n / p.npad, nl = n % p.npad;   // blobs: [chunk of npad columns][block]
             uint8_t *o = (uint8_t *)ob + p.blob_off + ((size_t)ch * nblk + sb) * p.blob_bytes;
             *reinterpret_cast<uint4 *>(o + (size_t)(nl / 8) * 4096 + lane * 128 + (nl % 8) * 16) = make_uint4(0, 0, 0, 0);

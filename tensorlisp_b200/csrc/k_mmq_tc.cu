@@ -593,13 +593,26 @@ void mmq_tc_configure() {
 }
 
 bool mmq_tc_supported(uint32_t type, int64_t K, int64_t M, int64_t N) {
-    return type == TLB_TYPE_Q4_K && K % 256 == 0 && K >= 256 && M >= 1 && N > 4 && N <= 8192 && encode_tiled() != nullptr;
+    return type == TLB_TYPE_Q4_K && K % 256 == 0 && K >= 256 && M >= 1 && N > 4 && N <= (int64_t)MM_FOLD_NPAD * 65535 && encode_tiled() != nullptr;
 }
 
 TcPlan mmq_tc_plan(int64_t K, int64_t M, int64_t N, int sm_count) {
     TcPlan t;
-    t.npad = N <= 16 ? 16 : (N <= 32 ? 32 : 64);
     t.nsb = (int)(K / 256);
+    if (N > 64 && !getenv("TLB_PROMPT_EXACT")) {
+        // prompt-sized batches: the folded-scale GEMM of k_mmq_tc_q8.cu (weights dequantized to f16 in the kernel, one
+        // accumulator per 128 x 256 tile) instead of 64-column chunks with the reference's integer sums
+        t.npad = MM_FOLD_NPAD;
+        t.n_split = 1;
+        t.sb_per_split = t.nsb;
+        t.streamk = 0;
+        t.n_col_chunks = (int)((N + t.npad - 1) / t.npad);
+        t.blob_unit = mm_fold_blob_unit();
+        t.blob_bytes = (uint64_t)t.n_col_chunks * t.nsb * t.blob_unit;
+        t.partial_bytes = 0;
+        return t;
+    }
+    t.npad = N <= 16 ? 16 : (N <= 32 ? 32 : 64);
     const int64_t tiles = (M + tc::ROWS - 1) / tc::ROWS;
     // K split: modelled time = waves x (CTA start-up and tail + super-blocks per CTA x time per super-block)
     // + the reduce launch when split; constants measured on B200 (3.4 us start-up and tail, 0.66 us per
@@ -639,6 +652,7 @@ TcPlan mmq_tc_plan(int64_t K, int64_t M, int64_t N, int sm_count) {
 }
 
 cudaError_t launch_act_pack_tc(const ActLayout &a, const void *act, int npad, void *blobs, cudaStream_t st) {
+    if (npad == MM_FOLD_NPAD) return launch_act_pack_fold(a, act, blobs, st);
     const char *ab = (const char *)act;
     k_act_pack_tc<<<dim3((unsigned)(a.K / 256), (unsigned)((a.N + npad - 1) / npad)), 256, 0, st>>>((const int8_t *)(ab + a.qs_off), (const float *)(ab + a.d_off),
                                                         (const int16_t *)(ab + a.bsum_off), a.K, (int)a.N, npad, (uint8_t *)blobs);
@@ -702,6 +716,10 @@ cudaError_t launch_wait_runs_out(uint32_t limit, unsigned nap_ns, int *err, unsi
 // n_mats weight matrices [M[j] x K] sharing the activations; y[j] dense [N][M[j]] when n_mats > 1 or K is split
 cudaError_t launch_mmq_tc_group(const TcPlan &t, int n_mats, const void *const *W, int64_t K, const int64_t *M, int64_t N, const void *blobs,
                                 float *const *y, int64_t ldy, void *partial, int *err, cudaStream_t st, bool leave_partial) {
+    if (t.npad == MM_FOLD_NPAD) {
+        if (n_mats != 1) return cudaErrorInvalidValue;
+        return launch_mm_fold_f16(true, W[0], K, M[0], N, blobs, y[0], ldy, err, st);
+    }
     if (n_mats < 1 || n_mats > TC_MAX_MATS || (n_mats > 1 && t.n_col_chunks != 1)) return cudaErrorInvalidValue;
     if (t.n_split > 16) return cudaErrorInvalidValue;
     TcMaps maps;

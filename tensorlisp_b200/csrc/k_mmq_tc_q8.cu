@@ -628,7 +628,8 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 // B operand of the kernel below: blobs [chunk of 256 columns][stage of 64 elements of K] x 32 KB, each
 // [column / 8][8 chunks of 8 elements][column % 8][16 bytes] (K-major core matrices: lbo 128, sbo 1024), values
 // f16(d_a * q8) in the order of K.
-__global__ void __launch_bounds__(256) k_act_pack_q80_f16(const int8_t *__restrict__ qs, const float *__restrict__ ds, int64_t K, int N,
+// `blk`: elements per activation scale (32 for Q8_0 activations, 256 for the Q8_K activations of Q4_K weights).
+__global__ void __launch_bounds__(256) k_act_pack_q80_f16(const int8_t *__restrict__ qs, const float *__restrict__ ds, int64_t K, int N, int blk,
                                                            uint8_t *__restrict__ out) {
     const int st = blockIdx.x;   // stage of 64 elements
     uint8_t *o = out + ((size_t)blockIdx.y * gridDim.x + st) * tc8f::B_STAGE;
@@ -639,7 +640,7 @@ __global__ void __launch_bounds__(256) k_act_pack_q80_f16(const int8_t *__restri
         if (n < N) {
             const int64_t k0 = (int64_t)st * tc8f::KS + kc * 8;
             const uint2 q = *reinterpret_cast<const uint2 *>(qs + (size_t)n * K + k0);
-            const float d = ds[(size_t)n * (K / 32) + k0 / 32];
+            const float d = ds[(size_t)n * (K / blk) + k0 / blk];
             const uint32_t w[2] = {q.x, q.y};
             uint32_t h[4];
 #pragma unroll
@@ -664,6 +665,10 @@ struct Tc8fParams {
     int *err;
 };
 
+// WQ4K = false: Q8_0 weights (raw rows of 8 x 34 bytes per unit); true: Q4_K weights (one 144-byte super-block per unit:
+// f16 d, dmin, twelve bytes of 6-bit scales and mins, 128 bytes of nibbles), expanded to f16(d * sc * q - dmin * m), the f32
+// value that ggml's dequantizer produces (dequantize_row_q4_K, ggml-quants.c) rounded once.
+template <bool WQ4K>
 __global__ void __launch_bounds__(tc8f::THREADS, 1) k_mm_q80_f16(const __grid_constant__ CUtensorMap wmap, Tc8fParams p) {
     using namespace tc;
     using namespace tc8f;
@@ -671,6 +676,8 @@ __global__ void __launch_bounds__(tc8f::THREADS, 1) k_mm_q80_f16(const __grid_co
     constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(tc8f::NW >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);   // f16 x f16 -> f32, K-major A and B
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = smem_raw + ((1024u - (su32(smem_raw) & 1023u)) & 1023u);
+    constexpr int ROW_CHUNK = WQ4K ? 144 : tc8::ROW_CHUNK;   // raw bytes of a row per unit of 256 elements
+    constexpr int RAW_BYTES = ROWS * ROW_CHUNK;
     uint8_t *bst = smem;                                   // tc8f::B_STAGES x tc8f::B_STAGE
     uint8_t *raw = bst + tc8f::B_STAGES * tc8f::B_STAGE;               // tc8f::RAW_STAGES x RAW_BYTES
     __shared__ uint64_t bar_raw[tc8f::RAW_STAGES], bar_rawfree[tc8f::RAW_STAGES], bar_b[tc8f::B_STAGES], bar_bfree[tc8f::B_STAGES];
@@ -716,8 +723,8 @@ __global__ void __launch_bounds__(tc8f::THREADS, 1) k_mm_q80_f16(const __grid_co
                 for (int i = 0; i < nst; i++, g++) {
                     const int s = g % tc8f::RAW_STAGES;
                     if (g >= tc8f::RAW_STAGES) mbar_wait_nap(&bar_rawfree[s], ((g / tc8f::RAW_STAGES) - 1) & 1, fail, 64);
-                    mbar_expect_tx(&bar_raw[s], tc8::RAW_BYTES);
-                    tma_2d(raw + s * tc8::RAW_BYTES, &wmap, i * (tc8::ROW_CHUNK / 2), row_tile * ROWS, &bar_raw[s]);   // x in 16-bit elements
+                    mbar_expect_tx(&bar_raw[s], RAW_BYTES);
+                    tma_2d(raw + s * RAW_BYTES, &wmap, i * (ROW_CHUNK / 2), row_tile * ROWS, &bar_raw[s]);   // x in 16-bit elements
                 }
             }
         }
@@ -786,7 +793,58 @@ __global__ void __launch_bounds__(tc8f::THREADS, 1) k_mm_q80_f16(const __grid_co
                     mbar_wait_nap(&bar_afree[slot], ((g / tc8f::A_RING) - 1) & 1, fail, 64);   // the MMAs that read this slot are done
                     tc_fence_after();
                 }
-                const uint8_t *rrow = raw + rs * tc8::RAW_BYTES + r * tc8::ROW_CHUNK;
+                const uint8_t *rrow = raw + rs * RAW_BYTES + r * ROW_CHUNK;
+                if constexpr (WQ4K) {
+                    // this warp's half of the super-block: the 64-value groups 2 * half and 2 * half + 1 (the low nibbles of
+                    // a group's 32 bytes are one sub-block, the high nibbles the next)
+                    const uint4 hdr = *reinterpret_cast<const uint4 *>(rrow);   // d, dmin, scales[12]
+                    const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu)));
+                    const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+                    // byte i of scales[12], taken out of the three words with shifts (no byte array in local memory)
+                    auto sb = [&](int i) -> int { return (int)(((i < 4 ? hdr.y : (i < 8 ? hdr.z : hdr.w)) >> ((i & 3) * 8)) & 0xffu); };
+                    auto scale_min = [&](int jj, int &sc, int &mn) {   // get_scale_min_k4 (ggml-quants.c:880-887)
+                        if (jj < 4) {
+                            sc = sb(jj) & 63;
+                            mn = sb(jj + 4) & 63;
+                        } else {
+                            sc = (sb(jj + 4) & 0xF) | ((sb(jj - 4) >> 6) << 4);
+                            mn = (sb(jj + 4) >> 4) | ((sb(jj) >> 6) << 4);
+                        }
+                    };
+#pragma unroll
+                    for (int gg = 0; gg < 2; gg++) {
+                        const int j = half * 2 + gg;
+                        int sc0, mn0, sc1, mn1;
+                        scale_min(2 * j, sc0, mn0);
+                        scale_min(2 * j + 1, sc1, mn1);
+                        const float a0 = __fmul_rn(d, (float)sc0), b0 = __fmul_rn(dmin, (float)mn0);
+                        const float a1 = __fmul_rn(d, (float)sc1), b1 = __fmul_rn(dmin, (float)mn1);
+                        uint32_t lo[16], hi[16];
+#pragma unroll
+                        for (int u = 0; u < 2; u++) {
+                            const uint4 qv = *reinterpret_cast<const uint4 *>(rrow + 16 + j * 32 + u * 16);
+                            const uint32_t w4[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+                            for (int wi = 0; wi < 4; wi++) {
+                                const uint32_t w = w4[wi];
+                                float fl[4], fh[4];
+#pragma unroll
+                                for (int e = 0; e < 4; e++) {
+                                    fl[e] = __fsub_rn(__fmul_rn(a0, (float)((w >> (8 * e)) & 0xF)), b0);
+                                    fh[e] = __fsub_rn(__fmul_rn(a1, (float)((w >> (8 * e + 4)) & 0xF)), b1);
+                                }
+                                const __half2 l0 = __floats2half2_rn(fl[0], fl[1]), l1 = __floats2half2_rn(fl[2], fl[3]);
+                                const __half2 h0 = __floats2half2_rn(fh[0], fh[1]), h1 = __floats2half2_rn(fh[2], fh[3]);
+                                lo[(u * 4 + wi) * 2] = *reinterpret_cast<const uint32_t *>(&l0);
+                                lo[(u * 4 + wi) * 2 + 1] = *reinterpret_cast<const uint32_t *>(&l1);
+                                hi[(u * 4 + wi) * 2] = *reinterpret_cast<const uint32_t *>(&h0);
+                                hi[(u * 4 + wi) * 2 + 1] = *reinterpret_cast<const uint32_t *>(&h1);
+                            }
+                        }
+                        tmem_st16(a_lane + (uint32_t)(slot * 128 + j * 32), lo);
+                        tmem_st16(a_lane + (uint32_t)(slot * 128 + j * 32 + 16), hi);
+                    }
+                } else {
 #pragma unroll
                 for (int gg = 0; gg < 2; gg++) {
                     uint32_t qa[8], qb[8];
@@ -810,6 +868,7 @@ __global__ void __launch_bounds__(tc8f::THREADS, 1) k_mm_q80_f16(const __grid_co
 #pragma unroll
                     for (int j = 0; j < 8; j++) codes_to_f16(qb[j], dd, h[2 * j], h[2 * j + 1]);
                     tmem_st16(a_lane + (uint32_t)(slot * 128 + (blk + 1) * 16), h);
+                }
                 }
                 tmem_st_wait();
                 tc_fence_before();
@@ -857,7 +916,44 @@ __global__ void __launch_bounds__(tc8f::THREADS, 1) k_mm_q80_f16(const __grid_co
     if (tid == 0 && s_fail) atomicExch(p.err, 2);
 }
 
-static size_t tc8f_smem() { return (size_t)tc8f::B_STAGES * tc8f::B_STAGE + (size_t)tc8f::RAW_STAGES * tc8::RAW_BYTES + 1024; }
+static size_t tc8f_smem() { return (size_t)tc8f::B_STAGES * tc8f::B_STAGE + (size_t)tc8f::RAW_STAGES * tc8::RAW_BYTES + 1024; }   // the larger raw stage (Q8_0)
+
+// The folded-scale GEMM for either weight format (the Q4_K planner and launcher in k_mmq_tc.cu call it for more than 64 columns)
+uint64_t mm_fold_blob_unit() { return (uint64_t)4 * tc8f::B_STAGE; }
+cudaError_t tc_encode_2d(CUtensorMap *map, const void *base, uint64_t row_bytes, uint64_t rows, uint32_t box_bytes, uint32_t box_rows,
+                         uint32_t elem_bytes);
+cudaError_t launch_mm_fold_f16(bool q4k, const void *W, int64_t K, int64_t M, int64_t N, const void *blobs, float *y, int64_t ldy, int *err,
+                               cudaStream_t st) {
+    CUtensorMap map;
+    cudaError_t e = q4k ? tc_encode_2d(&map, W, (uint64_t)(K / 256 * 144), (uint64_t)M, 144, tc8::ROWS, 2)
+                        : tc_encode_2d(&map, W, (uint64_t)(K / 32 * 34), (uint64_t)M, tc8::ROW_CHUNK, tc8::ROWS, 2);
+    if (e != cudaSuccess) return e;
+    static int sm_of[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!sm_of[dev]) cudaDeviceGetAttribute(&sm_of[dev], cudaDevAttrMultiProcessorCount, dev);
+    Tc8fParams p{};
+    p.act = (const uint8_t *)blobs;
+    p.out = y;
+    p.M = M;
+    p.ldy = ldy;
+    p.N = (int)N;
+    p.nst = (int)(K / 256);
+    p.row_tiles = (int)((M + tc8::ROWS - 1) / tc8::ROWS);
+    p.col_tiles = (int)((N + tc8f::NW - 1) / tc8f::NW);
+    p.err = err;
+    const int tiles = p.row_tiles * p.col_tiles;
+    const dim3 grid((unsigned)std::min(tiles, sm_of[dev]));
+    return q4k ? launch_pdl(k_mm_q80_f16<true>, grid, dim3(tc8f::THREADS), tc8f_smem(), st, map, p)
+               : launch_pdl(k_mm_q80_f16<false>, grid, dim3(tc8f::THREADS), tc8f_smem(), st, map, p);
+}
+cudaError_t launch_act_pack_fold(const ActLayout &a, const void *act, void *blobs, cudaStream_t st) {
+    const char *ab = (const char *)act;
+    k_act_pack_q80_f16<<<dim3((unsigned)(a.K / tc8f::KS), (unsigned)((a.N + tc8f::NW - 1) / tc8f::NW)), 256, 0, st>>>(
+        (const int8_t *)(ab + a.qs_off), (const float *)(ab + a.d_off), a.K, (int)a.N, a.kind == ACT_Q8_K ? 256 : 32, (uint8_t *)blobs);
+    return cudaGetLastError();
+}
 
 static size_t tc8w_smem() {
     return (size_t)tc8w::RAW_STAGES * tc8::RAW_BYTES + (size_t)tc8w::ACT_STAGES * tc8w::BLOB + (size_t)tc8w::A_RING * 8 * tc8::ROWS * sizeof(float) + 1024;
@@ -873,7 +969,8 @@ void mmq_tc8_configure() {
     cudaFuncSetAttribute(k_mmq_tc_q80<16, 4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc8_smem<16, 4, 4>());
     cudaFuncSetAttribute(k_mmq_tc_q80<32, 4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc8_smem<32, 4, 4>());
     cudaFuncSetAttribute(k_mmq_tc_q80_wide, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc8w_smem());
-    cudaFuncSetAttribute(k_mm_q80_f16, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc8f_smem());
+    cudaFuncSetAttribute(k_mm_q80_f16<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc8f_smem());
+    cudaFuncSetAttribute(k_mm_q80_f16<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc8f_smem());
 }
 
 bool mmq_tc8_supported(int64_t K, int64_t M, int64_t N) {
@@ -936,7 +1033,7 @@ cudaError_t launch_act_pack_tc8(const ActLayout &a, const void *act, int npad, v
     const char *ab = (const char *)act;
     if (npad == tc8f::NW) {
         k_act_pack_q80_f16<<<dim3((unsigned)(a.K / tc8f::KS), (unsigned)((a.N + npad - 1) / npad)), 256, 0, st>>>(
-            (const int8_t *)(ab + a.qs_off), (const float *)(ab + a.d_off), a.K, (int)a.N, (uint8_t *)blobs);
+            (const int8_t *)(ab + a.qs_off), (const float *)(ab + a.d_off), a.K, (int)a.N, a.kind == ACT_Q8_K ? 256 : 32, (uint8_t *)blobs);
         return cudaGetLastError();
     }
     k_act_pack_q80<<<dim3((unsigned)(a.K / 256), (unsigned)((a.N + npad - 1) / npad)), 256, 0, st>>>((const int8_t *)(ab + a.qs_off), (const float *)(ab + a.d_off), a.K, (int)a.N, npad,
@@ -954,25 +1051,7 @@ cudaError_t launch_mmq_tc8(const TcPlan &t, const void *W, int64_t K, int64_t M,
     // described in 16-bit elements: a 272-byte box is 136 of them (the limit is 256 elements per dimension)
     cudaError_t e = tc_encode_2d(&map, W, (uint64_t)(K / 32 * 34), (uint64_t)M, tc8::ROW_CHUNK, tc8::ROWS, 2);
     if (e != cudaSuccess) return e;
-    if (t.npad == tc8f::NW) {
-        static int sm_of[64] = {0};
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-        if (!sm_of[dev]) cudaDeviceGetAttribute(&sm_of[dev], cudaDevAttrMultiProcessorCount, dev);
-        Tc8fParams p{};
-        p.act = (const uint8_t *)blobs;
-        p.out = y;
-        p.M = M;
-        p.ldy = ldy;
-        p.N = (int)N;
-        p.nst = t.nsb;
-        p.row_tiles = (int)((M + tc8::ROWS - 1) / tc8::ROWS);
-        p.col_tiles = t.n_col_chunks;
-        p.err = err;
-        const int tiles = p.row_tiles * p.col_tiles;
-        return launch_pdl(k_mm_q80_f16, dim3((unsigned)std::min(tiles, sm_of[dev])), dim3(tc8f::THREADS), tc8f_smem(), st, map, p);
-    }
+    if (t.npad == tc8f::NW) return launch_mm_fold_f16(false, W, K, M, N, blobs, y, ldy, err, st);
     if (t.npad == tc8w::NW) {
         Tc8Params p{};
         p.act = (const uint8_t *)blobs;

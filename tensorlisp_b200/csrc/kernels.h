@@ -75,6 +75,12 @@ cudaError_t launch_act_pack_tc8(const ActLayout &a, const void *act, int npad, v
 cudaError_t launch_mmq_tc8(const TcPlan &t, const void *W, int64_t K, int64_t M, int64_t N, const void *blobs, float *y,
                            int64_t ldy, void *partial, int *err, cudaStream_t st);
 void mmq_tc8_configure();
+// the folded-scale prompt GEMM (k_mm_q80_f16) for Q8_0 or Q4_K weights: blobs of 256 columns x 64 elements, f16(code x scale)
+constexpr int MM_FOLD_NPAD = 256;
+uint64_t mm_fold_blob_unit();   // bytes of the blobs of one 256-element unit of K (four stages)
+cudaError_t launch_mm_fold_f16(bool q4k, const void *W, int64_t K, int64_t M, int64_t N, const void *blobs, float *y, int64_t ldy, int *err,
+                               cudaStream_t st);
+cudaError_t launch_act_pack_fold(const ActLayout &a, const void *act, void *blobs, cudaStream_t st);
 
 // ---------------------------------------------------------------- k_fused.cu
 // One row (= activation column n) per CTA: produce the f32 row, quantize it to Q8_K into an ActLayout

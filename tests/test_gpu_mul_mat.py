@@ -45,8 +45,8 @@ def test_shapes(oracle, ty, name, K, M, N):
     m, _ = mm_model(ty, K, M, N, Wq)
     (y,) = m.run(X)
     err = close(y, oracle.mul_mat(ty, Wq, K, X), TOL)
-    if name == "q8_0" and N > 64:
-        # prompt-sized Q8_0 batches: both block scales folded into f16 operands (two f16 roundings per product)
+    if name in ("q8_0", "q4_K") and N > 64:
+        # prompt-sized batches: weights and activations as scaled f16 operands (two f16 roundings per product)
         assert err <= 5e-4 * np.abs(y).max() + 1e-6
     else:
         assert err <= 2e-5 * np.abs(y).max() + 1e-6   # only the f32 summation order differs
@@ -56,27 +56,29 @@ def test_shapes(oracle, ty, name, K, M, N):
 
 
 @pytest.mark.parametrize("exact", [False, True])
+@pytest.mark.parametrize("ty,name", [(Q8_0, "q8_0"), (Q4_K, "q4_K")])
 @pytest.mark.parametrize("K,M,N", [(2048, 300, 300), (4096, 1024, 1000), (512, 130, 128), (14336, 256, 257), (4096, 4096, 2048)])
-def test_q8_0_many_columns(oracle, K, M, N, exact):
-    """Prompt-sized batches on the tensor cores, ragged rows and columns. The default kernel folds both block scales into
-    f16 operands and lets the tensor core add up all of K (two f16 roundings per product): within the 1e-3 bar of mul_mat,
-    measured around 1e-4 of max|y|. TLB_PROMPT_EXACT=1 selects the kernel that keeps the reference's integers (one int32
-    accumulator per 32-element block): that one agrees to f32 rounding."""
+def test_many_columns(oracle, K, M, N, ty, name, exact):
+    """Prompt-sized batches on the tensor cores, ragged rows and columns, Q8_0 and Q4_K weights. The default kernel turns
+    weights (code x block scale, for Q4_K d * sc * q - dmin * m) and activations (code x block scale of the reference's own
+    Q8_0 / Q8_K quantization) into f16 operands and lets the tensor core add up all of K: two f16 roundings per product,
+    within the 1e-3 bar of mul_mat, measured around 3e-4 of max|y|. TLB_PROMPT_EXACT=1 selects the kernels that keep the
+    reference's integer block sums: those agree to f32 rounding."""
     import os
     rng = np.random.default_rng(K + M + N)
     W = (rng.standard_normal((M, K)) * 0.02).astype(np.float32)
     X = rng.standard_normal((N, K)).astype(np.float32)
-    Wq = oracle.quantize(Q8_0, W)
+    Wq = oracle.quantize(ty, W)
     if exact:
         os.environ["TLB_PROMPT_EXACT"] = "1"
     try:
-        m, _ = mm_model(Q8_0, K, M, N, Wq)
+        m, _ = mm_model(ty, K, M, N, Wq)
     finally:
         os.environ.pop("TLB_PROMPT_EXACT", None)
     (y,) = m.run(X)
-    want = oracle.mul_mat(Q8_0, Wq, K, X)
+    want = oracle.mul_mat(ty, Wq, K, X)
     err = close(y, want, TOL)
-    print("q8_0 [%d x %d] x %d columns, %s kernel: max error %.2e of max|y|" % (M, K, N, "exact" if exact else "folded-scale", err / np.abs(want).max()))
+    print("%s [%d x %d] x %d columns, %s kernel: max error %.2e of max|y|" % (name, M, K, N, "exact" if exact else "folded-scale", err / np.abs(want).max()))
     if exact:
         assert err <= 2e-5 * np.abs(y).max() + 1e-6
     else:
