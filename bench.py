@@ -209,11 +209,11 @@ def tp_parity(world: int, rank: int, local_rank: int, dist, batch: int = 8) -> d
 
     if os.path.join(ROOT, "tests") not in sys.path:
         sys.path.insert(0, os.path.join(ROOT, "tests"))
-    from helpers import NoisyOracle, oracle_decoder_step
+    from helpers import NoisyOracle, oracle_decoder_step, oracle_prefill
     from oracle.bindings import Oracle
     from tensorlisp_b200.graph import align256
     from tensorlisp_b200.native import Native, NativeProgram, StateBlock
-    from tensorlisp_b200.programs import COLUMN_PARALLEL, ROW_PARALLEL, DecoderConfig, decoder_step, decoder_weights
+    from tensorlisp_b200.programs import COLUMN_PARALLEL, ROW_PARALLEL, DecoderConfig, decoder_step, decoder_weights, prefill_step
     from tensorlisp_b200._lib import check
 
     torch.cuda.set_device(local_rank)
@@ -314,6 +314,26 @@ def tp_parity(world: int, rank: int, local_rank: int, dist, batch: int = 8) -> d
     else:
         parts = [(logits, fin, token)]
     prog.free()
+    # ---- the prompt pass of the same sharded model: one prompt of 80 tokens (more than 64 columns, so the mul_mats are the
+    # folded-scale tensor-core GEMM and the attention the tcgen05 kernel; the 1.3 MB all-reduces go through NCCL)
+    p_tokens = 80
+    pg = prefill_step(cfg, 1, p_tokens, tp=world, write_cache=False)
+    pprog = NativeProgram.compile(native, pg.graph)
+    p_ids = rng.integers(0, cfg.vocab, p_tokens).astype(np.int32)
+    p_pos = np.arange(p_tokens, dtype=np.int32)
+    for i, a in enumerate([p_ids, p_pos, np.triu(np.full((p_tokens, p_tokens), -np.inf, np.float16), 1), np.array([p_tokens - 1], np.int32)]):
+        pprog.set_input(i, a)
+    if dist is not None:
+        dist.barrier()
+    pprog.run()
+    p_logits = pprog.read(pg.logits).reshape(1, cfg.vocab // world)
+    if dist is not None:
+        p_parts = [None] * world
+        dist.all_gather_object(p_parts, p_logits)
+        dist.barrier()
+    else:
+        p_parts = [p_logits]
+    pprog.free()
     native.close()
     if rank != 0:
         return {}
@@ -333,7 +353,15 @@ def tp_parity(world: int, rank: int, local_rank: int, dist, batch: int = 8) -> d
     from tensorlisp_b200.programs import combine_argmax
     tok = combine_argmax(local_best[0], local_best[1], cfg.vocab // world)
     top2 = np.sort(want, axis=1)[:, -2:]
-    return {"model": "2 layers at the benchmark's width (d_model 4096, 32/8 heads, FFN 14336), vocabulary 2048, %d sequences, contexts %s"
+    # the prompt pass against the oracle, with the oracle's envelope under the folded-scale kernel's own error
+    p_full = np.concatenate(p_parts, axis=1)
+    p_want = oracle_prefill(oracle, cfg, full_specs, full_host, p_ids, p_pos, 1, p_tokens)
+    p_noisy = oracle_prefill(NoisyOracle(oracle, 7e-5, 0, of_max=True), cfg, full_specs, full_host, p_ids, p_pos, 1, p_tokens)
+    p_err, p_env = float(np.abs(p_full - p_want).max()), float(np.abs(p_noisy - p_want).max())
+    prompt = {"tokens": p_tokens, "logits_max_abs_err": p_err, "oracle_noise_envelope_7e-5_of_max": p_env,
+              "within_envelope": bool(p_err <= max(1e-2, 1.5 * p_env)), "top1_equal": bool(p_full.argmax() == p_want.argmax())}
+    return {"prompt_pass": prompt,
+            "model": "2 layers at the benchmark's width (d_model 4096, 32/8 heads, FFN 14336), vocabulary 2048, %d sequences, contexts %s"
                      % (B, ctx_before.tolist()),
             "tp": world, "allreduce": path, "checked_against": "CPU oracle on the unsharded weights",
             "logits_max_abs_err": err, "logits_max_rel_err": err / float(np.abs(want).max()),

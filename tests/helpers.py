@@ -104,3 +104,46 @@ def oracle_decoder_step(oracle, cfg, specs, weights, ids, pos, ks, vs):
         x = x + lin(p + "ffn_down", m)
     x = oracle.rms_norm(x, cfg.eps, W["output_norm"][1])
     return lin("output", x)
+
+
+# ------------------------------------------------------------------ oracle-side prompt pass
+def causal_attention(q, k16, v16, n_seqs, n_tokens, heads, kvh, hd):
+    """q f32 [T, heads, hd], k16 / v16 f16 [T, kvh, hd] -> f32 [T, heads*hd], prompts independent."""
+    out = np.zeros((n_seqs * n_tokens, heads, hd), np.float32)
+    grp = heads // kvh
+    mask = np.triu(np.full((n_tokens, n_tokens), -np.inf, np.float32), 1)
+    for s in range(n_seqs):
+        r = slice(s * n_tokens, (s + 1) * n_tokens)
+        for h in range(heads):
+            kk = k16[r, h // grp].astype(np.float32)
+            vv = v16[r, h // grp].astype(np.float32)
+            sc = q[r, h] @ kk.T / np.float32(np.sqrt(hd)) + mask
+            p = np.exp(sc - sc.max(axis=1, keepdims=True))
+            out[r, h] = (p / p.sum(axis=1, keepdims=True)) @ vv
+    return out.reshape(n_seqs * n_tokens, heads * hd)
+
+
+def oracle_prefill(oracle, cfg, specs, weights, ids, pos, n_seqs, n_tokens):
+    W = {s.name: (s, w) for s, w in zip(specs, weights)}
+    T = len(ids)
+    hd, heads, kvh = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
+
+    def lin(name, x):
+        s, w = W[name]
+        return oracle.mul_mat(s.ty, w, s.ne[0], np.ascontiguousarray(x, np.float32))
+
+    s, w = W["token_embd"]
+    x = oracle.get_rows(s.ty, w, cfg.d_model, ids)
+    for l in range(cfg.n_layers):
+        p = "blk.%d." % l
+        h = oracle.rms_norm(x, cfg.eps, W[p + "attn_norm"][1])
+        q, k, v = lin(p + "wq", h), lin(p + "wk", h), lin(p + "wv", h)
+        q = oracle.rope(q.reshape(T, heads, hd), pos, hd, 2, cfg.rope_theta)
+        k = oracle.rope(k.reshape(T, kvh, hd), pos, hd, 2, cfg.rope_theta)
+        a = causal_attention(q, k.astype(np.float16), v.reshape(T, kvh, hd).astype(np.float16), n_seqs, n_tokens, heads, kvh, hd)
+        x = x + lin(p + "wo", a)
+        h = oracle.rms_norm(x, cfg.eps, W[p + "ffn_norm"][1])
+        x = x + lin(p + "ffn_down", oracle.silu_mul(lin(p + "ffn_gate", h), lin(p + "ffn_up", h)))
+    last = np.arange(n_seqs) * n_tokens + n_tokens - 1
+    x = oracle.rms_norm(np.ascontiguousarray(x[last]), cfg.eps, W["output_norm"][1])
+    return lin("output", x)

@@ -51,3 +51,7 @@ def test_two_ranks_against_the_oracle(path):
     assert out["ranks_hold_identical_final_norm"], out
     if out["smallest_top1_margin_of_the_oracle"] > 2 * out["logits_max_abs_err"]:
         assert out["top1_equal"] == out["rows"], out
+    # the prompt pass of the same sharded model (80 tokens: folded-scale tensor-core mul_mats, tcgen05 attention, NCCL
+    # all-reduces of 1.3 MB) against the oracle, judged by the oracle's envelope under that kernel's own error
+    pp = out["prompt_pass"]
+    assert pp["logits_max_abs_err"] <= max(1e-2, 1.5 * pp["oracle_noise_envelope_7e-5_of_max"]), pp
