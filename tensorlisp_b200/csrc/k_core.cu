@@ -518,7 +518,33 @@ __global__ void k_argmax(TView a, const uint8_t *x, int32_t *out) {
     const float *xr = reinterpret_cast<const float *>(x + row * a.nb[1]);
     float mx = -CUDART_INF_F;
     int idx = 0;
-    for (int64_t i = threadIdx.x; i < a.ne[0]; i += blockDim.x) {
+    // a row of logits is half a megabyte read by one CTA: 16-byte loads, several in flight per thread (a thread still
+    // meets its elements in rising index order, so ">=" keeps the last of equal maxima)
+    const int64_t n4 = ((reinterpret_cast<uintptr_t>(xr) & 15) == 0) ? a.ne[0] / 4 : 0;
+    const float4 *x4 = reinterpret_cast<const float4 *>(xr);
+    int64_t i4 = threadIdx.x;
+    for (; i4 + 3 * (int64_t)blockDim.x < n4; i4 += 4 * (int64_t)blockDim.x) {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) v[u] = x4[i4 + u * (int64_t)blockDim.x];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int base = (int)(4 * (i4 + u * (int64_t)blockDim.x));
+            if (v[u].x >= mx) { mx = v[u].x; idx = base; }
+            if (v[u].y >= mx) { mx = v[u].y; idx = base + 1; }
+            if (v[u].z >= mx) { mx = v[u].z; idx = base + 2; }
+            if (v[u].w >= mx) { mx = v[u].w; idx = base + 3; }
+        }
+    }
+    for (; i4 < n4; i4 += blockDim.x) {
+        const float4 v = x4[i4];
+        const int base = (int)(4 * i4);
+        if (v.x >= mx) { mx = v.x; idx = base; }
+        if (v.y >= mx) { mx = v.y; idx = base + 1; }
+        if (v.z >= mx) { mx = v.z; idx = base + 2; }
+        if (v.w >= mx) { mx = v.w; idx = base + 3; }
+    }
+    for (int64_t i = 4 * n4 + threadIdx.x; i < a.ne[0]; i += blockDim.x) {   // the tail, or everything of an unaligned row
         const float v = xr[i];
         if (v >= mx) { mx = v; idx = (int)i; }
     }
@@ -539,7 +565,7 @@ __global__ void k_argmax(TView a, const uint8_t *x, int32_t *out) {
 cudaError_t launch_argmax(const TView &a, const void *x, int32_t *out, cudaStream_t st) {
     const int64_t rows = a.ne[1] * a.ne[2] * a.ne[3];
     if (rows == 0) return cudaSuccess;
-    k_argmax<<<(unsigned)rows, 256, 0, st>>>(a, (const uint8_t *)x, out);
+    k_argmax<<<(unsigned)rows, a.ne[0] >= 16384 ? 1024 : 256, 0, st>>>(a, (const uint8_t *)x, out);
     return cudaGetLastError();
 }
 

@@ -159,13 +159,23 @@ __global__ void __launch_bounds__(RQ_THREADS) k_row_quant_q8k(RowQuantArgs p) {
         return;
     }
     float scale = 1.f;
+    float v[8];
+    bool have = false;   // v already holds this warp's block (met while the whole row was read for the norm)
     if (p.mode == RQ_NORM) {
+        // thread t reads elements t*8.. of every 2048-element stretch in turn: in stretch blockIdx.y those are the very
+        // values of the block this warp quantizes below, so they are kept instead of being read a second time
         float ss = 0.f;
-        for (int64_t k0 = (int64_t)threadIdx.x * 8; k0 < K; k0 += RQ_THREADS * 8) {
+        int it = 0;
+        for (int64_t k0 = (int64_t)threadIdx.x * 8; k0 < K; k0 += RQ_THREADS * 8, it++) {
             float x[8];
             rq_load8(p, n, k0, x);
 #pragma unroll
             for (int e = 0; e < 8; e++) ss = __fadd_rn(ss, __fmul_rn(x[e], x[e]));
+            if (it == (int)blockIdx.y) {
+                have = true;
+#pragma unroll
+                for (int e = 0; e < 8; e++) v[e] = x[e];
+            }
         }
 #pragma unroll
         for (int s = 16; s > 0; s >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, s));
@@ -179,8 +189,7 @@ __global__ void __launch_bounds__(RQ_THREADS) k_row_quant_q8k(RowQuantArgs p) {
     if (sb >= nblk) return;
     // ---- this warp's block: lane holds 8 consecutive values
     const int64_t k0 = (int64_t)sb * 256 + lane * 8;
-    float v[8];
-    rq_load8(p, n, k0, v);
+    if (!have) rq_load8(p, n, k0, v);
     if (p.mode != RQ_GLU && p.mode != RQ_F16 && p.b && p.sum_out) {   // the sum is the new residual stream
         *reinterpret_cast<float4 *>(p.sum_out + n * p.ld_sum + k0) = make_float4(v[0], v[1], v[2], v[3]);
         *reinterpret_cast<float4 *>(p.sum_out + n * p.ld_sum + k0 + 4) = make_float4(v[4], v[5], v[6], v[7]);
