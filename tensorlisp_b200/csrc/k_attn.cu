@@ -22,6 +22,7 @@
 
 #include "kernels.h"
 #include "pdl.cuh"
+#include "rowquant.cuh"
 #include "tlb_internal.h"
 
 namespace tlb {
@@ -66,6 +67,10 @@ struct PagedParams {
     uint32_t pool_blocks;  // pages in each pool; 0x80000000 when this launch does not know (block ids are then only checked for sign)
     int *err;              // device error word, or null: set to TLB_ERR_INDEX when a length or a block id was out of range
     float scale_log2;      // softmax scale * log2(e)
+    // fuse_rq: the f16 output row is also quantized to Q8_K (and packed for the tensor-core mul_mat) right here, as the
+    // row quantizer in RQ_F16 mode would do in a launch of its own; only without a context split (n_chunks == 1)
+    int fuse_rq;
+    RowQuantArgs rq;
 };
 // A context length beyond the cap is cut to the cap; a CTA that meets a block id outside the pools leaves without
 // touching them; either way the error word tells the host that the result is not to be used.
@@ -334,11 +339,25 @@ __global__ void __launch_bounds__(PA_WARPS * 32) k_paged_attn(PagedParams p) {
         }
         const int head = head0 + row;
         if (p.n_chunks == 1) {
-            p.out[((size_t)seq * p.heads + head) * HS + d] = __float2half_rn(l > 0.f ? a / l : 0.f);
+            const __half o16 = __float2half_rn(l > 0.f ? a / l : 0.f);
+            p.out[((size_t)seq * p.heads + head) * HS + d] = o16;
+            if (p.fuse_rq) acc[(size_t)PA_WARPS * 16 * HS + idx] = __half2float(o16);   // behind the warps' partial outputs
         } else {
             float *pp = p.partial + (((size_t)seq * p.heads + head) * p.n_chunks + chunk) * (HS + 2);
             pp[2 + d] = a;
             if (d == 0) { pp[0] = m; pp[1] = l; }
+        }
+    }
+    if (p.fuse_rq && p.n_chunks == 1) {
+        // the CTA's heads are nrows * HS consecutive elements of the token's row: whole 256-value Q8_K blocks, one per warp
+        __syncthreads();
+        const float *rowv = acc + (size_t)PA_WARPS * 16 * HS;
+        const int nblk = (int)(p.rq.K / 256), blk0 = head0 * HS / 256;
+        for (int w = warp; w < nrows * HS / 256; w += PA_WARPS) {
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; e++) v[e] = rowv[w * 256 + lane * 8 + e];
+            rq_quant_block(p.rq, seq, blk0 + w, nblk, lane, v);
         }
     }
 }
@@ -366,9 +385,15 @@ __global__ void __launch_bounds__(128) k_paged_reduce(PagedParams p) {
 }
 
 // ---------------------------------------------------------------- host side
+// the heads of a CTA make whole 256-value blocks of the output row, at a block boundary
+bool paged_quant_fusable(const PagedGeom &g) {
+    const int group = g.heads / g.kv_heads;
+    return (g.hs == 128 && group % 2 == 0 && (group <= 16 || group % 16 == 0)) || (g.hs == 256 && (group <= 16 || group % 16 == 0));
+}
+
 static size_t pa_smem(int hs) {
     const size_t ring = (size_t)PA_WARPS * PA_STAGES * 2 * PA_TILE * hs * 2;
-    const size_t merge = (size_t)PA_WARPS * 16 * (2 + hs) * 4;
+    const size_t merge = (size_t)PA_WARPS * 16 * (2 + hs) * 4 + (size_t)16 * hs * 4;   // + the output row of the fused quantizer
     return ring > merge ? ring : merge;
 }
 
@@ -428,7 +453,7 @@ static cudaError_t launch_pa(const PagedGeom &g, const PagedParams &p, cudaStrea
 
 cudaError_t launch_paged_attention(const PagedGeom &g, const void *q, const void *kpool, const void *vpool,
                                    const int32_t *tables, const int32_t *lens, void *out, void *scratch,
-                                   int64_t pool_blocks, int *err, cudaStream_t st) {
+                                   int64_t pool_blocks, int *err, cudaStream_t st, const RowQuantArgs *rq) {
     if (g.seqs == 0 || g.heads == 0) return cudaSuccess;
     PagedParams p;
     p.q = (const __half *)q;
@@ -451,6 +476,13 @@ cudaError_t launch_paged_attention(const PagedGeom &g, const void *q, const void
     p.ctx_cap = (int)std::min<int64_t>(g.max_ctx, (int64_t)g.max_blocks * g.block_size);
     p.pool_blocks = pool_blocks > 0 && pool_blocks < 0x80000000ll ? (uint32_t)pool_blocks : 0x80000000u;
     p.err = err;
+    p.fuse_rq = 0;
+    p.rq = RowQuantArgs{};
+    if (rq) {
+        if (g.n_chunks != 1 || !paged_quant_fusable(g)) return cudaErrorInvalidValue;
+        p.fuse_rq = 1;
+        p.rq = *rq;
+    }
     p.scale_log2 = g.scale * 1.4426950408889634f;
     switch (g.hs) {
         case 64: return launch_pa<64>(g, p, st);

@@ -213,9 +213,13 @@ struct PagedGeom {
 void paged_plan(PagedGeom &g, int sm_count);
 uint64_t paged_scratch_bytes(const PagedGeom &g);
 bool paged_supported(const PagedGeom &g);
+// rq: also quantize the output rows to Q8_K (RQ_F16 semantics of the row quantizer; needs n_chunks == 1 and
+// paged_quant_fusable(g)); null: only the f16 output
+struct RowQuantArgs;
+bool paged_quant_fusable(const PagedGeom &g);
 cudaError_t launch_paged_attention(const PagedGeom &g, const void *q, const void *kpool, const void *vpool,
                                    const int32_t *tables, const int32_t *lens, void *out, void *scratch,
-                                   int64_t pool_blocks, int *err, cudaStream_t st);
+                                   int64_t pool_blocks, int *err, cudaStream_t st, const RowQuantArgs *rq = nullptr);
 // pool_slots: block_size * pages of each pool; a slot at or beyond it is skipped and reported through err
 cudaError_t launch_cache_write(int tokens, int kv_heads, int hs, int block_size, const void *key, const void *value,
                                void *kpool, void *vpool, const int64_t *slots, int64_t pool_slots, int *err, cudaStream_t st);

@@ -639,9 +639,29 @@ void lower_custom(L &l) {
         ps.off = sc < 0 ? 0 : (uint64_t)sc;
         const Place pq = l.place(q), pk = l.place(kc), pv = l.place(vc), pt = l.place(tables), pl = l.place(lens), pd = l.place(l.id);
         const int64_t pool_blocks = std::min(l.T(kc).nelements(), l.T(vc).nelements()) / ((int64_t)pg.kv_heads * pg.block_size * pg.hs);
+        // src[9]: the Q8_K quantization of the output rows that fuse_attn_quant folded into this launch
+        const int32_t qid = t.src[9];
+        RowQuantArgs rq{};
+        Place prq;
+        if (qid >= 0) {
+            if (pg.n_chunks != 1 || !paged_quant_fusable(pg)) throw std::string("the attention plan changed after its quantizer was folded in");
+            rq.mode = RQ_F16;
+            rq.K = (int64_t)pg.hs * pg.heads;
+            rq.N = pg.seqs;
+            const ActLayout al = act_layout(ACT_Q8_K, rq.K, rq.N);
+            rq.qs_off = al.qs_off;
+            rq.d_off = al.d_off;
+            rq.bsum_off = al.bsum_off;
+            rq.npad = l.T(qid).op_params[1];
+            rq.blob_off = al.bytes;
+            rq.blob_bytes = rq.npad > 0 ? mmq_tc_plan(rq.K, 128, rq.N, 148).blob_unit : 0;
+            prq = l.place(qid);
+        }
         l.push([=](const RunCtx &r) {
+            RowQuantArgs a = rq;
+            if (qid >= 0) a.out = r.at(prq);
             return launch_paged_attention(pg, r.at(pq), r.at(pk), r.at(pv), (const int32_t *)r.at(pt), (const int32_t *)r.at(pl),
-                                          r.at(pd), r.at(ps), pool_blocks, r.err, r.stream);
+                                          r.at(pd), r.at(ps), pool_blocks, r.err, r.stream, qid >= 0 ? &a : nullptr);
         });
     } else if (u.kind == 2) {
         const int32_t key = l.src(0), value = l.src(1), kc = l.src(2), vc = l.src(3), slots = l.src(4);
@@ -1001,6 +1021,7 @@ void lower_node(const LowerCtx &c, int32_t id, int pos, std::vector<Dispatch> &o
 void fuse_row_producers(Graph &g);
 void fuse_rope_cache(Graph &g);
 void fuse_mul_mat_groups(Graph &g);
+void fuse_attn_quant(Graph &g);
 // Readers of every root (views of a tensor count for the root), as fuse.rs:56-63 requires.
 void rewrite_graph(Graph &g) {
     const size_t nt0 = g.tensors.size();
@@ -1146,8 +1167,45 @@ void rewrite_graph(Graph &g) {
     }
     g.nodes.swap(nodes);
     if (enabled("ROW_QUANT")) fuse_row_producers(g);
+    if (enabled("ROW_QUANT") && enabled("ATTN_QUANT")) fuse_attn_quant(g);
     if (enabled("ROPE_KV_WRITE")) fuse_rope_cache(g);
     if (enabled("MUL_MAT_GROUP")) fuse_mul_mat_groups(g);
+}
+
+// The f16 output of paged attention, cast and quantized for the output projection (a ROW_QUANT node in RQ_F16 mode right
+// behind the attention): the attention kernel quantizes its rows itself when it runs without a context split (one
+// launch less per layer). The ROW_QUANT node leaves the node list; its tensor becomes src[9] of the attention node, which
+// also makes the planner keep it alive from that position on.
+void fuse_attn_quant(Graph &g) {
+    const size_t nn = g.nodes.size();
+    std::vector<int> pos_of(g.tensors.size(), -1);
+    for (size_t i = 0; i < nn; i++) pos_of[g.nodes[i]] = (int)i;
+    std::vector<char> dead(nn, 0);
+    for (size_t qi = 0; qi < nn; qi++) {
+        const int32_t qid = g.nodes[qi];
+        const Tensor &Q = g.tensors[qid];
+        if (Q.op != "ROW_QUANT" || Q.op_params[2] != RQ_F16 || Q.op_params[0] != ACT_Q8_K || Q.src[0] < 0 || Q.src[5] < 0) continue;
+        const int32_t src = Q.src[0], root = g.root(src);
+        const int ap = pos_of[root];
+        if (ap < 0 || ap >= (int)qi) continue;
+        Tensor &A = g.tensors[root];
+        if (A.op != "CUSTOM" || paged_ud(A).kind != 1 || A.src[9] >= 0) continue;
+        bool only_views = true;
+        for (int i = ap + 1; i < (int)qi; i++) only_views = only_views && g.tensors[g.nodes[i]].is_view_op();
+        if (!only_views) continue;
+        // the quantizer reads the whole output as rows of heads * head size, one per sequence
+        const Tensor &S = g.tensors[src], &shape = g.tensors[Q.src[5]];
+        if (S.ty != TLB_TYPE_F16 || !S.is_contiguous() || S.view_offs != 0 || S.nelements() != A.nelements()) continue;
+        if (shape.ne[0] != A.ne[0] * A.ne[1] || shape.nrows() != A.ne[2]) continue;
+        PagedGeom pg{};
+        if (!paged_geom(g, A, 148, pg) || pg.n_chunks != 1 || !paged_quant_fusable(pg)) continue;
+        A.src[9] = qid;
+        dead[qi] = 1;
+    }
+    std::vector<int32_t> out;
+    for (size_t i = 0; i < nn; i++)
+        if (!dead[i]) out.push_back(g.nodes[i]);
+    g.nodes.swap(out);
 }
 
 // Fold the producer of a quantized activation into its QUANT_ACT node (k_fused.cu): RMS_NORM_MUL

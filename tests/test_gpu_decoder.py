@@ -198,3 +198,40 @@ def _decode_step_case(oracle, cfg, ctx_before, max_ctx, noise_seeds):
     assert np.array_equal(out["logits"].argmax(axis=1)[decided], want.argmax(axis=1)[decided])
     m.close()
 
+
+
+def test_attention_quantizes_its_own_output(oracle):
+    """Without a context split the paged-attention kernel also quantizes its f16 output rows to Q8_K for the output
+    projection (the ROW_QUANT node behind it is folded in: one launch less per layer). TL_NATIVE_NOFUSE=ATTN_QUANT keeps
+    the separate launch; both programs must give the same bits."""
+    import os
+    cfg = DecoderConfig(n_layers=2, d_model=4096, n_heads=32, n_kv_heads=8, head_dim=128, d_ffn=14336, vocab=2048)
+    B, max_ctx, bs = 32, 64, cfg.block_size
+    rng = np.random.default_rng(21)
+    max_blocks = max_ctx // bs
+    pool_blocks = B * max_blocks
+    ids = rng.integers(0, cfg.vocab, B).astype(np.int32)
+    pos = rng.integers(0, max_ctx - 1, B).astype(np.int32)
+    lens = pos + 1
+    tables = rng.permutation(pool_blocks).astype(np.int32).reshape(B, max_blocks)
+    slots = np.array([tables[b, pos[b] // bs] * bs + pos[b] % bs for b in range(B)], np.int64)
+    dg = decoder_step(cfg, B, max_ctx, pool_blocks)
+    weights = make_decoder_weights(oracle, dg.weights, seed=3)
+    pools = [(rng.standard_normal((pool_blocks, cfg.n_kv_heads, bs, cfg.head_dim)) * 0.5).astype(np.float16) for _ in range(2 * cfg.n_layers)]
+    got, counts = [], []
+    for separate in (False, True):
+        if separate:
+            os.environ["TL_NATIVE_NOFUSE"] = "ATTN_QUANT"
+        try:
+            m = Model(dg.graph, weights, dg.state_bytes, [("logits", dg.logits)])
+        finally:
+            os.environ.pop("TL_NATIVE_NOFUSE", None)
+        for i, pl in enumerate(pools):
+            m.native.state.write(m.native.state_offsets[i], pl)
+        (logits,) = m.run(ids, pos, tables, lens, slots.view(np.int32))
+        got.append(logits.copy())
+        counts.append(m.program.kernel_count())
+        m.close()
+    assert np.array_equal(got[0], got[1])
+    assert np.isfinite(got[0]).all() and np.abs(got[0]).max() > 0
+    assert counts[1] - counts[0] == cfg.n_layers, counts
