@@ -11,8 +11,10 @@
 //   3. k_fa_tc: a CTA owns 128 queries of one (head, batch). Tensor memory holds two score accumulators S (128 columns
 //      each), the output accumulator O (128 columns) and two P operands (f16, 64 columns each). One warp copies tiles,
 //      one issues MMAs (S = Q K^T: 8 x 128x128x16 from shared memory; O += P V: 8 x 128x128x16 with P read from tensor
-//      memory), four warps own one query row per thread: they pull a row of S out of tensor memory, take maximum, exp2
-//      and sum without any shuffle, and put P back. S is double buffered, so the tensor core works on the next tile's
+//      memory), eight warps do the softmax, two threads per query row with 64 score columns each: they pull their half
+//      of the row out of tensor memory, agree on the row's maximum through shared memory, take exp2 and their part of
+//      the sum, and put P back (one thread per row spent 3500-4000 cycles per key tile on its own serial instruction
+//      stream and the tensor-memory round trips; splitting the row halves that). S is double buffered, so the tensor core works on the next tile's
 //      scores while the exponentials of this one are taken. The running maximum that the exponents refer to is only
 //      moved when a row's maximum has grown by more than 2^8 (the factor cancels in the final division; P stays far
 //      inside the f16 range), so O in tensor memory is rescaled rarely instead of once per tile.
@@ -30,8 +32,8 @@ namespace tlb {
 namespace fat {
 constexpr int T = 128;                    // queries per CTA, keys per tile, head size
 constexpr int TILE_BYTES = T * T * 2;     // 32 KB
-constexpr int THREADS = 256;              // warp 0 copies, warp 1 issues MMAs, warps 2-3 idle, warps 4-7 softmax
-constexpr int SM_WARP0 = 4;
+constexpr int THREADS = 384;              // warp 0 copies, warp 1 issues MMAs, warps 2-3 idle, warps 4-11 softmax
+constexpr int SM_WARP0 = 4, SM_WARPS = 8; // two threads per query row: warps 4-7 take score columns 0-63, warps 8-11 columns 64-127
 constexpr uint32_t S_COL0 = 0, O_COL0 = 256, P_COL0 = 384;
 constexpr float RESCALE_STEP = 8.f;       // in the base-2 domain
 
@@ -155,6 +157,7 @@ __global__ void __launch_bounds__(fat::THREADS, 1) k_fa_tc(FaTcParams p) {
     __shared__ uint64_t bar_q, bar_k[2], bar_v[2], bar_kfree[2], bar_vfree[2], bar_s[2], bar_sfree[2], bar_p[2], bar_pv;
     __shared__ uint32_t tmem_base_s;
     __shared__ int s_fail, n_live_s;
+    __shared__ float pair_x[2][fat::T];   // what the two threads of a row tell each other: the maximum of their half, at the end their sum
     __shared__ uint16_t live_kt[512];   // key tiles that are not skipped, with their flag in the top bits
     volatile int *fail = &s_fail;
 
@@ -170,8 +173,8 @@ __global__ void __launch_bounds__(fat::THREADS, 1) k_fa_tc(FaTcParams p) {
             mbar_init(&bar_kfree[i], 1);
             mbar_init(&bar_vfree[i], 1);
             mbar_init(&bar_s[i], 1);
-            mbar_init(&bar_sfree[i], 4);
-            mbar_init(&bar_p[i], 4);
+            mbar_init(&bar_sfree[i], fat::SM_WARPS);
+            mbar_init(&bar_p[i], fat::SM_WARPS);
         }
         mbar_init(&bar_pv, 1);
         s_fail = 0;
@@ -257,10 +260,12 @@ __global__ void __launch_bounds__(fat::THREADS, 1) k_fa_tc(FaTcParams p) {
             }
         }
     } else if (warp >= fat::SM_WARP0) {
-        // ---- softmax: one query row per thread
-        const int quad = warp & 3;
+        // ---- softmax: two threads per query row (64 score columns each); the pair shares a lane quadrant and meets at
+        // a named barrier of its own (64 threads) to agree on the row's maximum
+        const int quad = warp & 3, half = (warp - fat::SM_WARP0) >> 2;
         const int row = quad * 32 + lane, qr = qt * T + row;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+        auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory"); };
         const __half *mrow = nullptr;
         if (p.mask)
             mrow = reinterpret_cast<const __half *>(p.mask + (int64_t)(h % p.m_ne2) * p.m.nb[2] + (int64_t)(b % p.m_ne3) * p.m.nb[3] +
@@ -269,30 +274,30 @@ __global__ void __launch_bounds__(fat::THREADS, 1) k_fa_tc(FaTcParams p) {
         bool have_ref = false;   // m_ref is the maximum the exponents refer to; unset until the row has seen a finite score
         for (int j = 0; j < n_live; j++) {
             const int s = j & 1, kt = live_kt[j] & 0xfff, flag = live_kt[j] >> 12;
+            const int key0 = kt * T + half * 64;
             mbar_wait_nap(&bar_s[s], (j >> 1) & 1, fail, 0);
             tc_fence_after();
-            float x[T];
-#pragma unroll
-            for (int c = 0; c < 4; c++) fat::tmem_ld32(lane_base + fat::S_COL0 + (uint32_t)(s * T + c * 32), reinterpret_cast<uint32_t *>(x) + c * 32);
+            float x[64];
+            fat::tmem_ld32(lane_base + fat::S_COL0 + (uint32_t)(s * T + half * 64), reinterpret_cast<uint32_t *>(x));
+            fat::tmem_ld32(lane_base + fat::S_COL0 + (uint32_t)(s * T + half * 64 + 32), reinterpret_cast<uint32_t *>(x) + 32);
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_sfree[s]);
             // scores in the base-2 domain
 #pragma unroll
-            for (int i = 0; i < T; i++) x[i] *= p.scale_log2;
+            for (int i = 0; i < 64; i++) x[i] *= p.scale_log2;
             if (flag & 2) {
-                const uint4 *mv = reinterpret_cast<const uint4 *>(mrow + kt * T);
-                const bool full = kt * T + T <= p.nkv;
+                const bool full = key0 + 64 <= p.nkv;
 #pragma unroll
-                for (int c = 0; c < 16; c++) {
+                for (int c = 0; c < 8; c++) {
                     uint4 v = make_uint4(0, 0, 0, 0);
                     if (full) {
-                        v = mv[c];
+                        v = *reinterpret_cast<const uint4 *>(mrow + key0 + c * 8);
                     } else {
                         __half t[8];
 #pragma unroll
-                        for (int e = 0; e < 8; e++) t[e] = kt * T + c * 8 + e < p.nkv ? mrow[kt * T + c * 8 + e] : __ushort_as_half(0);
+                        for (int e = 0; e < 8; e++) t[e] = key0 + c * 8 + e < p.nkv ? mrow[key0 + c * 8 + e] : __ushort_as_half(0);
                         v = *reinterpret_cast<const uint4 *>(t);
                     }
                     const __half2 *h2 = reinterpret_cast<const __half2 *>(&v);
@@ -306,13 +311,18 @@ __global__ void __launch_bounds__(fat::THREADS, 1) k_fa_tc(FaTcParams p) {
             }
             if (flag & 4) {
 #pragma unroll
-                for (int i = 0; i < T; i++)
-                    if (kt * T + i >= p.nkv) x[i] = -CUDART_INF_F;
+                for (int i = 0; i < 64; i++)
+                    if (key0 + i >= p.nkv) x[i] = -CUDART_INF_F;
             }
             float mx = x[0];
 #pragma unroll
-            for (int i = 1; i < T; i++) mx = fmaxf(mx, x[i]);
-            // the reference maximum moves only when this row's maximum has outgrown it by more than the step
+            for (int i = 1; i < 64; i++) mx = fmaxf(mx, x[i]);
+            pair_x[half][row] = mx;
+            pair_sync();
+            mx = fmaxf(mx, pair_x[half ^ 1][row]);
+            pair_sync();   // both have read before either writes the next tile's value
+            // the reference maximum moves only when this row's maximum has outgrown it by more than the step (the two
+            // threads of a row see the same numbers and take the same decisions)
             float alpha = 1.f;
             if (!have_ref) {
                 if (mx != -CUDART_INF_F) {
@@ -324,50 +334,53 @@ __global__ void __launch_bounds__(fat::THREADS, 1) k_fa_tc(FaTcParams p) {
                 m_ref = mx;
             }
             if (__any_sync(0xffffffffu, alpha != 1.f)) {
-                // O of the tiles before has to be complete before it is scaled (j > 0 here: alpha is 1 on the first tile)
+                // O of the tiles before has to be complete before it is scaled (j > 0 here: alpha is 1 on the first tile);
+                // each thread scales its half of the row's output columns
                 mbar_wait_nap(&bar_pv, (j - 1) & 1, fail, 0);
                 tc_fence_after();
 #pragma unroll 1
-                for (int c = 0; c < 4; c++) {
+                for (int c = 0; c < 2; c++) {
                     uint32_t o[32];
-                    fat::tmem_ld32(lane_base + fat::O_COL0 + (uint32_t)(c * 32), o);
+                    fat::tmem_ld32(lane_base + fat::O_COL0 + (uint32_t)(half * 64 + c * 32), o);
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                    fat::tmem_st32(lane_base + fat::O_COL0 + (uint32_t)(c * 32), o);
+                    fat::tmem_st32(lane_base + fat::O_COL0 + (uint32_t)(half * 64 + c * 32), o);
                 }
                 tmem_st_wait();
                 l *= alpha;
             }
-            // P = exp2(x - m_ref) as f16 pairs; the row sum in f32
-            uint32_t pk[T / 2];
+            // P = exp2(x - m_ref) as f16 pairs; this thread's part of the row sum in f32
+            uint32_t pk[32];
             float sum = 0.f;
 #pragma unroll
-            for (int i = 0; i < T; i += 2) {
+            for (int i = 0; i < 64; i += 2) {
                 const float e0 = fat::ex2(x[i] - m_ref), e1 = fat::ex2(x[i + 1] - m_ref);
                 sum += e0 + e1;
                 pk[i / 2] = fat::pack_h2(e0, e1);
             }
             l += sum;
-            fat::tmem_st32(lane_base + fat::P_COL0 + (uint32_t)(s * 64), pk);
-            fat::tmem_st32(lane_base + fat::P_COL0 + (uint32_t)(s * 64 + 32), pk + 32);
+            fat::tmem_st32(lane_base + fat::P_COL0 + (uint32_t)(s * 64 + half * 32), pk);
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_p[s]);
         }
-        // ---- O / l -> out [D, nh, nq, nb]
+        // ---- O / l -> out [D, nh, nq, nb]: the row sum is the two threads' parts together, each writes its 64 columns
+        pair_x[half][row] = l;
+        pair_sync();
+        l += pair_x[half ^ 1][row];
         if (n_live > 0) {
             mbar_wait_nap(&bar_pv, (n_live - 1) & 1, fail, 0);
             tc_fence_after();
         }
         const float inv = l > 0.f ? 1.f / l : 0.f;
-        float *dst = p.out + (((int64_t)b * p.nq + qr) * p.nh + h) * T;
+        float *dst = p.out + (((int64_t)b * p.nq + qr) * p.nh + h) * T + half * 64;
 #pragma unroll 1
-        for (int c = 0; c < 4; c++) {
+        for (int c = 0; c < 2; c++) {
             uint32_t o[32];
             if (n_live > 0) {
-                fat::tmem_ld32(lane_base + fat::O_COL0 + (uint32_t)(c * 32), o);
+                fat::tmem_ld32(lane_base + fat::O_COL0 + (uint32_t)(half * 64 + c * 32), o);
                 tmem_ld_wait();
             } else {
 #pragma unroll
