@@ -35,6 +35,10 @@ CONTEXT = 2048
 METRIC = "decode tok/s (8B-shape Q4_K, batch 32)"
 
 
+WORKLOAD = ("benchmark config 4: Llama-3-8B shape, 32 layers, Q4_K weights (Q8_0 embed/output), "
+            "batch 32 decode step at context 2048")
+
+
 def measured_peaks() -> tuple[float, str]:
     """HBM GB/s roofline denominator: the driver-measured copy bandwidth when present."""
     try:
@@ -491,8 +495,7 @@ def run_ours(args) -> dict:
         "metric": METRIC, "value": BATCH / (ms_dev * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_dev, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int8 codes: f16 / int8 tcgen05 mma and dp4a, f32 scales and accumulate", "data": "synthetic",
-        "config": {"workload": "benchmark config 4: Llama-3-8B shape, 32 layers, Q4_K weights (Q8_0 embed/output), "
-                               "batch 32 decode step at context 2048, paged f16 KV (16-token pages)",
+        "config": {"workload": WORKLOAD, "kv": "paged f16 KV (16-token pages)",
                    "parallelism": "tp%d" % world, **({"allreduce": allreduce} if world > 1 else {}), "l2": "inputs larger than L2: %.2f GB weights + %.2f GB KV read per step per GPU"
                                                         % (ab["weights"] / 1e9, ab["kv"] / 1e9)},
         "e2e": {"value": BATCH / (ms_e2e * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": BATCH * 4,
@@ -810,13 +813,41 @@ def run_kernel(args) -> dict:
 
 
 # ---------------------------------------------------------------------------------- reference arm (CPU)
+def host_memory_available() -> int:
+    """Bytes this process can still take: MemAvailable of /proc/meminfo, cut to what the control group's
+    memory limit leaves (0 when neither can be read)."""
+    avail = 0
+    try:
+        with open("/proc/meminfo") as f:
+            for line in f:
+                if line.startswith("MemAvailable:"):
+                    avail = int(line.split()[1]) * 1024
+    except OSError:
+        return 0
+    for limit_file, usage_file in (("/sys/fs/cgroup/memory.max", "/sys/fs/cgroup/memory.current"),
+                                   ("/sys/fs/cgroup/memory/memory.limit_in_bytes", "/sys/fs/cgroup/memory/memory.usage_in_bytes")):
+        try:
+            limit = open(limit_file).read().strip()
+            if limit != "max":
+                avail = min(avail, max(int(limit) - int(open(usage_file).read().strip()), 0))
+        except (OSError, ValueError):
+            pass
+    return avail
+
+
+FULL_STEP_HOST_BYTES = 15.5e9      # 4.5 GB of weights + 8.6 GB of dense f16 K/V + 1.1 GB of tables + intermediates
+
+
 def cpu_reference_step(cfg, time_limit_s: float = 20.0, steps: int = 1, warmup: int = 0) -> dict:
-    """The reference's own ggml CPU backend (the build of oracle/_ref that fits this host's CPU) on a
-    bounded sample of the decode step: ONE decoder layer at batch 32 / context 2048 (dense f16 K/V,
-    because ggml has no CPU paged attention; FLASH_ATTN_EXT reads the same bytes) plus the output
-    projection, all host threads. The full step is 32 x layer + output + small ops, so
-    tok/s = 32 / (32 * t_layer + t_output). Weight VALUES do not affect CPU time: 256 quantized rows
-    are tiled to the full row count instead of quantizing 8e9 values on the host."""
+    """The reference's own ggml CPU backend (the build of oracle/_ref that fits this host's CPU), all host
+    threads, on the whole decode step of the benchmark: embedding lookup, 32 decoder layers at batch 32 /
+    context 2048 (each with its own weights and its own dense f16 K/V cache, the new key and value written
+    into the cache before the attention: ggml has no CPU paged attention, FLASH_ATTN_EXT over a dense cache
+    reads the same bytes), final norm, output projection, argmax. One graph, one compute call per step.
+    Weight VALUES do not affect CPU time: 256 quantized rows are tiled to the full row count of every matrix
+    instead of quantizing 8e9 values on the host, and the layers' caches hold the same random values.
+    A host with less than ~24 GB available gets the bounded sample instead (one layer + output projection,
+    step = 32 x layer + output) and the result says so."""
     from oracle.bindings import F16, F32, I32, Q4_K, Q8_0, Ref, best_ref_variant
 
     variant = best_ref_variant()
@@ -826,63 +857,100 @@ def cpu_reference_step(cfg, time_limit_s: float = 20.0, steps: int = 1, warmup: 
     threads = os.cpu_count() or 1
     rng = np.random.default_rng(0)
     d, hd, heads, kvh, ffn = cfg.d_model, cfg.head_dim, cfg.n_heads, cfg.n_kv_heads, cfg.d_ffn
+    avail = host_memory_available()
+    full = avail >= FULL_STEP_HOST_BYTES * 1.5
+    bases = {}
 
-    def tiled(ty, k, rows):
-        base = ref.quantize(ty, (rng.standard_normal((256, k)) * 0.02).astype(np.float32))
-        return np.tile(base, ((rows + 255) // 256, 1))[:rows]
+    def weight(g, ty, k, rows):
+        if (ty, k) not in bases:
+            bases[(ty, k)] = ref.quantize(ty, (rng.standard_normal((256, k)) * 0.02).astype(np.float32))
+        t = g.tensor(ty, [k, rows])
+        g.write_repeated(t, bases[(ty, k)])
+        return t
 
-    def layer_graph():
-        g = ref.graph(int(2.5e9), threads)
-        x = g.tensor(F32, [d, BATCH], data=rng.standard_normal((BATCH, d)).astype(np.float32))
-        pos = g.tensor(I32, [BATCH], data=np.full(BATCH, CONTEXT - 1, np.int32))
-        wn = g.tensor(F32, [d], data=np.ones(d, np.float32))
-        W = {n: g.tensor(Q4_K, [k, m], data=tiled(Q4_K, k, m)) for n, k, m in
+    kv_values = rng.standard_normal((BATCH, kvh, CONTEXT, hd)).astype(np.float16)
+    rp = dict(ints=[hd, 2, 0], floats=[cfg.rope_theta, 1.0, 0.0, 1.0, 32.0, 1.0])
+
+    def layer(g, x, pos, wn, effects):
+        """One decoder layer on x [d, BATCH]; appends the cache writes to `effects`."""
+        W = {n: weight(g, Q4_K, k, m) for n, k, m in
              (("wq", d, heads * hd), ("wk", d, kvh * hd), ("wv", d, kvh * hd), ("wo", heads * hd, d),
               ("gate", d, ffn), ("up", d, ffn), ("down", ffn, d))}
-        K = g.tensor(F16, [hd, CONTEXT, kvh, BATCH], data=rng.standard_normal((BATCH, kvh, CONTEXT, hd)).astype(np.float16))
-        V = g.tensor(F16, [hd, CONTEXT, kvh, BATCH], data=rng.standard_normal((BATCH, kvh, CONTEXT, hd)).astype(np.float16))
+        K = g.tensor(F16, [hd, CONTEXT, kvh, BATCH], data=kv_values)
+        V = g.tensor(F16, [hd, CONTEXT, kvh, BATCH], data=kv_values)
         h = g.op("mul", [g.op("rms_norm", [x], floats=[cfg.eps]), wn])
         q = g.op("mul_mat", [W["wq"], h])
         k = g.op("mul_mat", [W["wk"], h])
         v = g.op("mul_mat", [W["wv"], h])
-        rp = dict(ints=[hd, 2, 0], floats=[cfg.rope_theta, 1.0, 0.0, 1.0, 32.0, 1.0])
         q = g.op("rope_ext", [g.op("reshape", [q], ints=[hd, heads, BATCH, 1]), pos, None], **rp)
         k = g.op("rope_ext", [g.op("reshape", [k], ints=[hd, kvh, BATCH, 1]), pos, None], **rp)
+        # the step's own key and value go to the last position of every sequence's cache
+        last = [hd, 1, kvh, BATCH, hd * 2, hd * CONTEXT * 2, hd * CONTEXT * kvh * 2, (CONTEXT - 1) * hd * 2]
+        effects.append(g.op("cpy", [g.op("reshape", [k], ints=[hd, 1, kvh, BATCH]), g.op("view", [K], ints=last)]))
+        effects.append(g.op("cpy", [g.op("reshape", [v], ints=[hd, 1, kvh, BATCH]), g.op("view", [V], ints=last)]))
         q4 = g.op("reshape", [q], ints=[hd, 1, heads, BATCH])      # one query per sequence
         a = g.op("flash_attn_ext", [q4, K, V, None], floats=[1.0 / float(np.sqrt(hd)), 0.0, 0.0])
         a = g.op("reshape", [a], ints=[hd * heads, BATCH, 1, 1])
         x1 = g.op("add", [x, g.op("mul_mat", [W["wo"], a])])
         h2 = g.op("mul", [g.op("rms_norm", [x1], floats=[cfg.eps]), wn])
         m = g.op("mul", [g.op("unary", [g.op("mul_mat", [W["gate"], h2])], ints=[10]), g.op("mul_mat", [W["up"], h2])])
-        out = g.op("add", [x1, g.op("mul_mat", [W["down"], m])])
-        return g, [out, k, v]
-
-    def head_graph():
-        g = ref.graph(int(1.2e9), threads)
-        x = g.tensor(F32, [d, BATCH], data=rng.standard_normal((BATCH, d)).astype(np.float32))
-        w = g.tensor(Q8_0, [d, cfg.vocab], data=tiled(Q8_0, d, cfg.vocab))
-        y = g.op("mul_mat", [w, x])
-        return g, [g.op("argmax", [y])]
+        return g.op("add", [x1, g.op("mul_mat", [W["down"], m])])
 
     t0 = time.time()
-    gl, outs_l = layer_graph()
-    gh, outs_h = head_graph()
-    for _ in range(max(warmup, 1)):
-        gl.compute(outs_l)
-        gh.compute(outs_h)
-    t_layer, t_head, n = [], [], 0
-    while n < max(steps, 1) or (time.time() - t0 < time_limit_s and n < 5):
-        t_layer.append(gl.compute(outs_l))
-        t_head.append(gh.compute(outs_h))
-        n += 1
-    tl, th = float(np.median(t_layer)), float(np.median(t_head))
-    ms_step = cfg.n_layers * tl + th
-    gl.close()
-    gh.close()
+    if full:
+        g = ref.graph(int(FULL_STEP_HOST_BYTES), threads)
+        ids = g.tensor(I32, [BATCH], data=rng.integers(0, cfg.vocab, BATCH).astype(np.int32))
+        pos = g.tensor(I32, [BATCH], data=np.full(BATCH, CONTEXT - 1, np.int32))
+        wn = g.tensor(F32, [d], data=np.ones(d, np.float32))
+        x = g.op("get_rows", [weight(g, Q8_0, d, cfg.vocab), ids])
+        effects = []
+        for _ in range(cfg.n_layers):
+            x = layer(g, x, pos, wn, effects)
+        h = g.op("mul", [g.op("rms_norm", [x], floats=[cfg.eps]), wn])
+        y = g.op("mul_mat", [weight(g, Q8_0, d, cfg.vocab), h])
+        # the cache writes come first in the output list: ggml orders the graph by first use, so each layer's
+        # writes land in front of that layer's attention
+        outs = effects + [g.op("argmax", [y])]
+        setup_s = time.time() - t0
+        for _ in range(max(warmup, 1)):
+            g.compute(outs)
+        t_step, t1 = [], time.time()
+        while len(t_step) < max(steps, 1) or (time.time() - t1 < time_limit_s and len(t_step) < 5):
+            t_step.append(g.compute(outs))
+        g.close()
+        ms_step = float(np.median(t_step))
+        sample = ("the whole step in one ggml graph: embedding lookup, %d layers (own weights and dense f16 K/V each, "
+                  "cache write included), final norm, output projection, argmax; batch %d, context %d; %d timed steps, "
+                  "median; %.0f s to lay out %.1f GB of host tensors (not timed)"
+                  % (cfg.n_layers, BATCH, CONTEXT, len(t_step), setup_s, FULL_STEP_HOST_BYTES / 1e9))
+    else:
+        gl = ref.graph(int(2.5e9), threads)
+        x = gl.tensor(F32, [d, BATCH], data=rng.standard_normal((BATCH, d)).astype(np.float32))
+        pos = gl.tensor(I32, [BATCH], data=np.full(BATCH, CONTEXT - 1, np.int32))
+        wn = gl.tensor(F32, [d], data=np.ones(d, np.float32))
+        effects = []
+        outs_l = [layer(gl, x, pos, wn, effects)]
+        outs_l = effects + outs_l
+        gh = ref.graph(int(1.2e9), threads)
+        xh = gh.tensor(F32, [d, BATCH], data=rng.standard_normal((BATCH, d)).astype(np.float32))
+        outs_h = [gh.op("argmax", [gh.op("mul_mat", [weight(gh, Q8_0, d, cfg.vocab), xh])])]
+        for _ in range(max(warmup, 1)):
+            gl.compute(outs_l)
+            gh.compute(outs_h)
+        t_layer, t_head, t1 = [], [], time.time()
+        while len(t_layer) < max(steps, 1) or (time.time() - t1 < time_limit_s and len(t_layer) < 5):
+            t_layer.append(gl.compute(outs_l))
+            t_head.append(gh.compute(outs_h))
+        tl, th = float(np.median(t_layer)), float(np.median(t_head))
+        ms_step = cfg.n_layers * tl + th
+        gl.close()
+        gh.close()
+        sample = ("BOUNDED SAMPLE, the host has %.1f GB available and the whole step needs %.1f GB: 1 of %d layers (%.1f ms) + "
+                  "output projection (%.1f ms), batch %d, context %d, dense f16 K/V; step time = %d*layer + output; %d timed repeats"
+                  % (avail / 1e9, FULL_STEP_HOST_BYTES * 1.5 / 1e9, cfg.n_layers, tl, th, BATCH, CONTEXT, cfg.n_layers, len(t_layer)))
     return {"value": BATCH / (ms_step * 1e-3), "unit": "tok/s", "cores": threads, "kind": "reference",
-            "ms_per_step": ms_step, "build": "ggml CPU backend of the reference, flags %s" % ref.build_flags(),
-            "sample": "1 of 32 layers (%.1f ms) + output projection (%.1f ms), batch 32, context 2048, dense f16 K/V; "
-                      "step time = 32*layer + output; %d timed repeats" % (tl, th, n)}
+            "ms_per_step": ms_step, "whole_step": full,
+            "build": "ggml CPU backend of the reference, flags %s" % ref.build_flags(), "sample": sample}
 
 
 def run_reference(args) -> dict:
@@ -898,7 +966,8 @@ def run_reference(args) -> dict:
     return {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "tok/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["ms_per_step"], "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int8 dot, f32 accumulate (ggml CPU)", "data": "synthetic",
-            "config": {"workload": "benchmark config 4 (bounded sample, see cpu_baseline.sample)", "parallelism": "cpu"},
+            "config": {"workload": WORKLOAD if cb["whole_step"] else WORKLOAD + " (bounded sample, see cpu_baseline.sample)",
+                       "kv": "dense f16 KV per layer (ggml has no CPU paged attention)", "parallelism": "cpu"},
             "cpu_baseline": cb, "gpu_launches": 0,
             "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
 

@@ -307,6 +307,13 @@ class RefGraph:
         assert data.nbytes == n, (data.nbytes, n)
         C.memmove(self.L.tlref_data(self.h, t), data.ctypes.data, n)
 
+    def write_repeated(self, t: int, data: np.ndarray) -> None:
+        """Fills the tensor with `data` repeated end to end (the last copy cut short)."""
+        data = np.ascontiguousarray(data)
+        n, base = int(self.L.tlref_nbytes(self.h, t)), self.L.tlref_data(self.h, t)
+        for off in range(0, n, data.nbytes):
+            C.memmove(base + off, data.ctypes.data, min(data.nbytes, n - off))
+
     def read(self, t: int, dtype=np.float32) -> np.ndarray:
         n = int(self.L.tlref_nbytes(self.h, t))
         buf = np.empty(n, np.uint8)
