@@ -186,8 +186,11 @@ tlb_status tlb_program_profile(tlb_program *prog, tlb_buffer *const *weights, ui
 
 /* ------------------------------------------------------------------ quantizers
  * DType::from_f32 (crates/tensorlisp/src/dtype.rs:98-124) -> ggml_quantize_chunk: f32 rows to
- * Q8_0 / Q4_0 / Q4_K blocks (also F16), bit-exact with the reference's build. Host pointers; the
- * rows are quantized on the GPU. n_per_row must be a multiple of the block size (32 / 256). */
+ * Q4_0 / Q4_1 / Q5_0 / Q5_1 / Q8_0 / Q2_K / Q3_K / Q4_K / Q5_K / Q6_K blocks (also F16 and BF16),
+ * bit-exact with the reference's build (the quantize targets of dtype.rs:28-33 that need no
+ * importance matrix, except IQ4_NL, IQ4_XS, TQ1_0, TQ2_0 and MXFP4: TLB_UNSUPPORTED by name).
+ * Host pointers; the rows are quantized on the GPU. n_per_row must be a multiple of the block
+ * size (32 / 256). */
 tlb_status tlb_quantize_rows(tlb_device *dev, uint32_t type, const float *src, int64_t rows, int64_t n_per_row, void *out);
 /* Same on device-resident data (src and out are device pointers), enqueued on the device stream. */
 tlb_status tlb_quantize_rows_device(tlb_device *dev, uint32_t type, const void *src, int64_t rows, int64_t n_per_row, void *out);

@@ -18,7 +18,7 @@ import numpy as np
 HERE = Path(__file__).resolve().parent
 
 F32, F16, Q4_0, Q8_0, Q4_K, I32, I64 = 0, 1, 2, 8, 12, 26, 27
-Q4_1, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K, Q6_K = 3, 6, 7, 10, 11, 13, 14   # decoded (dequantize / get_rows / exact-dequant mul_mat) only
+Q4_1, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K, Q6_K, BF16 = 3, 6, 7, 10, 11, 13, 14, 30   # quantized and decoded; mul_mat through exact dequantization
 
 _p = C.c_void_p
 _i64 = C.c_int64

@@ -2,6 +2,7 @@
  * build has no FMA contraction and the Q4_K scale search is sensitive to it). */
 #include "oracle.h"
 
+#include <float.h>
 #include <math.h>
 #include <stdlib.h>
 #include <string.h>
@@ -68,12 +69,20 @@ typedef struct { uint16_t d; uint8_t qs[16]; } blk_q4_0;                       /
 typedef struct { uint16_t d; int8_t qs[32]; } blk_q8_0;                        /* 34 B / 32  */
 typedef struct { uint16_t d, dmin; uint8_t scales[12]; uint8_t qs[128]; } blk_q4_K; /* 144 B / 256 */
 typedef struct { float d; int8_t qs[256]; int16_t bsums[16]; } blk_q8_K;       /* 292 B / 256 */
+typedef struct { uint16_t d, m; uint8_t qs[16]; } blk_q4_1;                    /* 20 B / 32  */
+typedef struct { uint16_t d; uint8_t qh[4]; uint8_t qs[16]; } blk_q5_0;        /* 22 B / 32  */
+typedef struct { uint16_t d, m; uint8_t qh[4]; uint8_t qs[16]; } blk_q5_1;     /* 24 B / 32  */
+typedef struct { uint8_t scales[16]; uint8_t qs[64]; uint16_t d, dmin; } blk_q2_K;                  /* 84 B / 256  */
+typedef struct { uint8_t hmask[32]; uint8_t qs[64]; uint8_t scales[12]; uint16_t d; } blk_q3_K;     /* 110 B / 256 */
+typedef struct { uint16_t d, dmin; uint8_t scales[12]; uint8_t qh[32]; uint8_t qs[128]; } blk_q5_K; /* 176 B / 256 */
+typedef struct { uint8_t ql[128]; uint8_t qh[64]; int8_t scales[16]; uint16_t d; } blk_q6_K;        /* 210 B / 256 */
 #pragma pack(pop)
 
 int64_t orc_row_size(int type, int64_t ne0) {
     switch (type) {
         case ORC_F32: return ne0 * 4;
         case ORC_F16: return ne0 * 2;
+        case ORC_BF16: return ne0 * 2;
         case ORC_Q4_0: return ne0 / 32 * 18;
         case ORC_Q8_0: return ne0 / 32 * 34;
         case ORC_Q4_K: return ne0 / 256 * 144;
@@ -134,10 +143,12 @@ void orc_quantize_row_q4_0(const float *x, void *vy, int64_t k) {
     }
 }
 
-/* ggml-quants.c:799-878, called with n=32, nmax=15, rmin=-1, rdelta=0.1, nstep=20, use_mad=false */
-static float search_scale_min(const float *x, const float *w, uint8_t *L, float *the_min, uint8_t *Laux) {
-    const int n = 32, nmax = 15, nstep = 20;
-    const float rmin = -1.f, rdelta = 0.1f;
+/* ggml-quants.c:799-878 (make_qkx2_quants): weighted least-squares search of (scale, min) for codes 0..nmax.
+ * Q4_K calls it with n=32, nmax=15, rmin=-1, nstep=20, squared error; Q5_K with nmax=31, rmin=-0.5, nstep=15;
+ * Q2_K with n=16, nmax=3, rmin=-0.5, nstep=15 and the absolute error (use_mad). rdelta is 0.1 everywhere. */
+static float search_scale_min(int n, int nmax, const float *x, const float *w, uint8_t *L, float *the_min, uint8_t *Laux,
+                              float rmin, int nstep, int use_mad) {
+    const float rdelta = 0.1f;
     float min = x[0], max = x[0];
     float sum_w = w[0];
     float sum_x = sum_w * x[0];
@@ -161,7 +172,7 @@ static float search_scale_min(const float *x, const float *w, uint8_t *L, float 
         l = l < 0 ? 0 : (l > nmax ? nmax : l);
         L[i] = (uint8_t)l;
         float diff = scale * L[i] + min - x[i];
-        diff = diff * diff;
+        diff = use_mad ? fabsf(diff) : diff * diff;
         best += w[i] * diff;
     }
     for (int is = 0; is <= nstep; is++) {
@@ -186,11 +197,11 @@ static float search_scale_min(const float *x, const float *w, uint8_t *L, float 
             float err = 0;
             for (int i = 0; i < n; i++) {
                 float diff = this_scale * Laux[i] + this_min - x[i];
-                diff = diff * diff;
+                diff = use_mad ? fabsf(diff) : diff * diff;
                 err += w[i] * diff;
             }
             if (err < best) {
-                memcpy(L, Laux, n);
+                memcpy(L, Laux, (size_t)n);
                 best = err;
                 scale = this_scale;
                 min = this_min;
@@ -225,7 +236,7 @@ void orc_quantize_row_q4_K(const float *x, void *vy, int64_t k) {
             for (int l = 0; l < 32; l++) sum_x2 += xs[l] * xs[l];
             float av_x = sqrtf(sum_x2 / 32);
             for (int l = 0; l < 32; l++) weights[l] = av_x + fabsf(xs[l]);
-            scales[j] = search_scale_min(xs, weights, L + 32 * j, &mins[j], Laux);
+            scales[j] = search_scale_min(32, 15, xs, weights, L + 32 * j, &mins[j], Laux, -1.f, 20, 0);
             if (scales[j] > max_scale) max_scale = scales[j];
             if (mins[j] > max_min) max_min = mins[j];
         }
@@ -297,6 +308,381 @@ void orc_quantize_row_q8_K(const float *x, void *vy, int64_t k) {
  * result only differs if the stale bsums*0 were NaN/inf, which int16 cannot be. Byte comparisons
  * of Q8_K in tests exclude the bsums of such blocks. */
 
+/* ggml-quants.c:150-185: d = (max - min) / 15, m = min, codes (int8)((x - min) / d + 0.5) capped at 15 */
+void orc_quantize_row_q4_1(const float *x, void *vy, int64_t k) {
+    blk_q4_1 *y = (blk_q4_1 *)vy;
+    for (int64_t b = 0; b < k / 32; b++) {
+        const float *xb = x + b * 32;
+        float min = FLT_MAX, max = -FLT_MAX;
+        for (int j = 0; j < 32; j++) {
+            if (xb[j] < min) min = xb[j];
+            if (xb[j] > max) max = xb[j];
+        }
+        const float d = (max - min) / 15;
+        const float id = d ? 1.0f / d : 0.0f;
+        y[b].d = orc_f32_to_f16(d);
+        y[b].m = orc_f32_to_f16(min);
+        for (int j = 0; j < 16; j++) {
+            const float x0 = (xb[j] - min) * id, x1 = (xb[16 + j] - min) * id;
+            const int a = (int8_t)(x0 + 0.5f), c = (int8_t)(x1 + 0.5f);
+            const uint8_t lo = (uint8_t)(a > 15 ? 15 : a), hi = (uint8_t)(c > 15 ? 15 : c);
+            y[b].qs[j] = (uint8_t)(lo | (hi << 4));
+        }
+    }
+}
+
+/* ggml-quants.c:187-229: d = (signed value of largest magnitude) / -16; the fifth bit of element e is bit e of qh */
+void orc_quantize_row_q5_0(const float *x, void *vy, int64_t k) {
+    blk_q5_0 *y = (blk_q5_0 *)vy;
+    for (int64_t b = 0; b < k / 32; b++) {
+        const float *xb = x + b * 32;
+        float amax = 0.0f, max = 0.0f;
+        for (int j = 0; j < 32; j++)
+            if (amax < fabsf(xb[j])) { amax = fabsf(xb[j]); max = xb[j]; }
+        const float d = max / -16;
+        const float id = d ? 1.0f / d : 0.0f;
+        y[b].d = orc_f32_to_f16(d);
+        uint32_t qh = 0;
+        for (int j = 0; j < 16; j++) {
+            const float x0 = xb[j] * id, x1 = xb[16 + j] * id;
+            const int a = (int8_t)(x0 + 16.5f), c = (int8_t)(x1 + 16.5f);
+            const uint8_t lo = (uint8_t)(a > 31 ? 31 : a), hi = (uint8_t)(c > 31 ? 31 : c);
+            y[b].qs[j] = (uint8_t)((lo & 0x0F) | ((hi & 0x0F) << 4));
+            qh |= (uint32_t)((lo & 0x10u) >> 4) << j;
+            qh |= (uint32_t)((hi & 0x10u) >> 4) << (j + 16);
+        }
+        memcpy(y[b].qh, &qh, 4);
+    }
+}
+
+/* ggml-quants.c:231-273: d = (max - min) / 31, m = min, codes (uint8)((x - min) / d + 0.5), no cap */
+void orc_quantize_row_q5_1(const float *x, void *vy, int64_t k) {
+    blk_q5_1 *y = (blk_q5_1 *)vy;
+    for (int64_t b = 0; b < k / 32; b++) {
+        const float *xb = x + b * 32;
+        float min = FLT_MAX, max = -FLT_MAX;
+        for (int j = 0; j < 32; j++) {
+            if (xb[j] < min) min = xb[j];
+            if (xb[j] > max) max = xb[j];
+        }
+        const float d = (max - min) / 31;
+        const float id = d ? 1.0f / d : 0.0f;
+        y[b].d = orc_f32_to_f16(d);
+        y[b].m = orc_f32_to_f16(min);
+        uint32_t qh = 0;
+        for (int j = 0; j < 16; j++) {
+            const float x0 = (xb[j] - min) * id, x1 = (xb[16 + j] - min) * id;
+            const uint8_t lo = (uint8_t)(x0 + 0.5f), hi = (uint8_t)(x1 + 0.5f);
+            y[b].qs[j] = (uint8_t)((lo & 0x0F) | ((hi & 0x0F) << 4));
+            qh |= (uint32_t)((lo & 0x10u) >> 4) << j;
+            qh |= (uint32_t)((hi & 0x10u) >> 4) << (j + 16);
+        }
+        memcpy(y[b].qh, &qh, 4);
+    }
+}
+
+/* ggml-quants.c:891-958: 16 groups of 16 with 4-bit scale and 4-bit min each (one byte), 2-bit codes */
+void orc_quantize_row_q2_K(const float *x, void *vy, int64_t k) {
+    blk_q2_K *y = (blk_q2_K *)vy;
+    uint8_t L[256], Laux[16];
+    float weights[16], mins[16], scales[16];
+    for (int64_t b = 0; b < k / 256; b++, x += 256) {
+        float max_scale = 0, max_min = 0;
+        for (int j = 0; j < 16; j++) {
+            for (int l = 0; l < 16; l++) weights[l] = fabsf(x[16 * j + l]);
+            scales[j] = search_scale_min(16, 3, x + 16 * j, weights, L + 16 * j, &mins[j], Laux, -0.5f, 15, 1);
+            if (scales[j] > max_scale) max_scale = scales[j];
+            if (mins[j] > max_min) max_min = mins[j];
+        }
+        if (max_scale > 0) {
+            const float iscale = 15.f / max_scale;
+            for (int j = 0; j < 16; j++) y[b].scales[j] = (uint8_t)near_int(iscale * scales[j]);
+            y[b].d = orc_f32_to_f16(max_scale / 15.f);
+        } else {
+            memset(y[b].scales, 0, 16);
+            y[b].d = orc_f32_to_f16(0.f);
+        }
+        if (max_min > 0) {
+            const float iscale = 15.f / max_min;
+            for (int j = 0; j < 16; j++) y[b].scales[j] |= (uint8_t)(near_int(iscale * mins[j]) << 4);
+            y[b].dmin = orc_f32_to_f16(max_min / 15.f);
+        } else {
+            y[b].dmin = orc_f32_to_f16(0.f);
+        }
+        for (int j = 0; j < 16; j++) {
+            const float d = orc_f16_to_f32(y[b].d) * (y[b].scales[j] & 0xF);
+            if (!d) continue;
+            const float dm = orc_f16_to_f32(y[b].dmin) * (y[b].scales[j] >> 4);
+            for (int i = 0; i < 16; i++) {
+                int l = near_int((x[16 * j + i] + dm) / d);
+                L[16 * j + i] = (uint8_t)(l < 0 ? 0 : (l > 3 ? 3 : l));
+            }
+        }
+        for (int j = 0; j < 256; j += 128)
+            for (int l = 0; l < 32; l++)
+                y[b].qs[j / 4 + l] = (uint8_t)(L[j + l] | (L[j + l + 32] << 2) | (L[j + l + 64] << 4) | (L[j + l + 96] << 6));
+    }
+}
+
+/* ggml-quants.c:697-754 (make_q3_quants, do_rmse): codes -nmax..nmax-1 for weights x^2, then up to five passes that move
+ * one code at a time when that raises (sum w x l)^2 / (sum w l^2); returns the least-squares scale, codes stored + nmax */
+static float search_scale_refine(int n, int nmax, const float *x, int8_t *L) {
+    float max = 0, amax = 0;
+    for (int i = 0; i < n; i++) {
+        float ax = fabsf(x[i]);
+        if (ax > amax) { amax = ax; max = x[i]; }
+    }
+    if (amax < 1e-15f) {
+        memset(L, 0, (size_t)n);
+        return 0.f;
+    }
+    const float iscale = -nmax / max;
+    float sumlx = 0, suml2 = 0;
+    for (int i = 0; i < n; i++) {
+        int l = near_int(iscale * x[i]);
+        l = l < -nmax ? -nmax : (l > nmax - 1 ? nmax - 1 : l);
+        L[i] = (int8_t)l;
+        const float w = x[i] * x[i];
+        sumlx += w * x[i] * l;
+        suml2 += w * l * l;
+    }
+    for (int itry = 0; itry < 5; itry++) {
+        int changed = 0;
+        for (int i = 0; i < n; i++) {
+            const float w = x[i] * x[i];
+            float slx = sumlx - w * x[i] * L[i];
+            if (slx > 0) {
+                float sl2 = suml2 - w * L[i] * L[i];
+                int nl = near_int(x[i] * sl2 / slx);
+                nl = nl < -nmax ? -nmax : (nl > nmax - 1 ? nmax - 1 : nl);
+                if (nl != L[i]) {
+                    slx += w * x[i] * nl;
+                    sl2 += w * nl * nl;
+                    if (sl2 > 0 && slx * slx * suml2 > sumlx * sumlx * sl2) {
+                        L[i] = (int8_t)nl;
+                        sumlx = slx;
+                        suml2 = sl2;
+                        changed++;
+                    }
+                }
+            }
+        }
+        if (!changed) break;
+    }
+    for (int i = 0; i < n; i++) L[i] = (int8_t)(L[i] + nmax);
+    return suml2 > 0.0f ? sumlx / suml2 : 0.0f;
+}
+
+/* ggml-quants.c:1229-1303: 16 groups of 16, 6-bit signed group scales against d = max_scale / -32, 3-bit codes whose
+ * high bit goes to hmask (bit j/32 of byte j%32) */
+void orc_quantize_row_q3_K(const float *x, void *vy, int64_t k) {
+    blk_q3_K *y = (blk_q3_K *)vy;
+    int8_t L[256];
+    float scales[16];
+    for (int64_t b = 0; b < k / 256; b++, x += 256) {
+        float max_scale = 0, amax = 0;
+        for (int j = 0; j < 16; j++) {
+            scales[j] = search_scale_refine(16, 4, x + 16 * j, L + 16 * j);
+            const float a = fabsf(scales[j]);
+            if (a > amax) { amax = a; max_scale = scales[j]; }
+        }
+        memset(y[b].scales, 0, 12);
+        if (max_scale) {
+            const float iscale = -32.f / max_scale;
+            for (int j = 0; j < 16; j++) {
+                int8_t l = (int8_t)near_int(iscale * scales[j]);
+                l = (int8_t)((l < -32 ? -32 : (l > 31 ? 31 : l)) + 32);
+                if (j < 8) y[b].scales[j] = (uint8_t)(l & 0xF);
+                else y[b].scales[j - 8] |= (uint8_t)((l & 0xF) << 4);
+                l >>= 4;
+                y[b].scales[j % 4 + 8] |= (uint8_t)(l << (2 * (j / 4)));
+            }
+            y[b].d = orc_f32_to_f16(1 / iscale);
+        } else {
+            y[b].d = orc_f32_to_f16(0.f);
+        }
+        for (int j = 0; j < 16; j++) {
+            int8_t sc = (int8_t)(j < 8 ? y[b].scales[j] & 0xF : y[b].scales[j - 8] >> 4);
+            sc = (int8_t)((sc | (((y[b].scales[8 + j % 4] >> (2 * (j / 4))) & 3) << 4)) - 32);
+            const float d = orc_f16_to_f32(y[b].d) * sc;
+            if (!d) continue;
+            for (int i = 0; i < 16; i++) {
+                int l = near_int(x[16 * j + i] / d);
+                l = l < -4 ? -4 : (l > 3 ? 3 : l);
+                L[16 * j + i] = (int8_t)(l + 4);
+            }
+        }
+        memset(y[b].hmask, 0, 32);
+        for (int j = 0; j < 256; j++)
+            if (L[j] > 3) {
+                y[b].hmask[j % 32] |= (uint8_t)(1 << (j / 32));
+                L[j] = (int8_t)(L[j] - 4);
+            }
+        for (int j = 0; j < 256; j += 128)
+            for (int l = 0; l < 32; l++)
+                y[b].qs[j / 4 + l] = (uint8_t)(L[j + l] | (L[j + l + 32] << 2) | (L[j + l + 64] << 4) | (L[j + l + 96] << 6));
+    }
+}
+
+/* ggml-quants.c:1644-1727: Q4_K's scheme with 5-bit codes (search with nmax 31, rmin -0.5, 15 steps); bit 2c / 2c+1 of
+ * qh[j] is the fifth bit of element 64c + j / 64c + 32 + j */
+void orc_quantize_row_q5_K(const float *x, void *vy, int64_t k) {
+    blk_q5_K *y = (blk_q5_K *)vy;
+    uint8_t L[256], Laux[32];
+    float weights[32], mins[8], scales[8];
+    for (int64_t b = 0; b < k / 256; b++, x += 256) {
+        float max_scale = 0, max_min = 0;
+        for (int j = 0; j < 8; j++) {
+            const float *xs = x + 32 * j;
+            float sum_x2 = 0;
+            for (int l = 0; l < 32; l++) sum_x2 += xs[l] * xs[l];
+            const float av_x = sqrtf(sum_x2 / 32);
+            for (int l = 0; l < 32; l++) weights[l] = av_x + fabsf(xs[l]);
+            scales[j] = search_scale_min(32, 31, xs, weights, L + 32 * j, &mins[j], Laux, -0.5f, 15, 0);
+            if (scales[j] > max_scale) max_scale = scales[j];
+            if (mins[j] > max_min) max_min = mins[j];
+        }
+        const float inv_scale = max_scale > 0 ? 63.f / max_scale : 0.f;
+        const float inv_min = max_min > 0 ? 63.f / max_min : 0.f;
+        memset(y[b].scales, 0, 12);
+        for (int j = 0; j < 8; j++) {
+            uint8_t ls = (uint8_t)near_int(inv_scale * scales[j]);
+            uint8_t lm = (uint8_t)near_int(inv_min * mins[j]);
+            if (ls > 63) ls = 63;
+            if (lm > 63) lm = 63;
+            if (j < 4) {
+                y[b].scales[j] = ls;
+                y[b].scales[j + 4] = lm;
+            } else {
+                y[b].scales[j + 4] = (uint8_t)((ls & 0xF) | ((lm & 0xF) << 4));
+                y[b].scales[j - 4] |= (uint8_t)((ls >> 4) << 6);
+                y[b].scales[j] |= (uint8_t)((lm >> 4) << 6);
+            }
+        }
+        y[b].d = orc_f32_to_f16(max_scale / 63.f);
+        y[b].dmin = orc_f32_to_f16(max_min / 63.f);
+        for (int j = 0; j < 8; j++) {
+            uint8_t sc, m;
+            scale_min_k4(j, y[b].scales, &sc, &m);
+            const float d = orc_f16_to_f32(y[b].d) * sc;
+            if (!d) continue;
+            const float dm = orc_f16_to_f32(y[b].dmin) * m;
+            for (int i = 0; i < 32; i++) {
+                int l = near_int((x[32 * j + i] + dm) / d);
+                L[32 * j + i] = (uint8_t)(l < 0 ? 0 : (l > 31 ? 31 : l));
+            }
+        }
+        memset(y[b].qh, 0, 32);
+        uint8_t *ql = y[b].qs;
+        for (int n = 0, c = 0; n < 256; n += 64, c++, ql += 32)
+            for (int j = 0; j < 32; j++) {
+                int l1 = L[n + j], l2 = L[n + j + 32];
+                if (l1 > 15) { l1 -= 16; y[b].qh[j] |= (uint8_t)(1 << (2 * c)); }
+                if (l2 > 15) { l2 -= 16; y[b].qh[j] |= (uint8_t)(2 << (2 * c)); }
+                ql[j] = (uint8_t)(l1 | (l2 << 4));
+            }
+    }
+}
+
+/* ggml-quants.c:628-695 (make_qx_quants with rmse_type 1, no external weights): codes -nmax..nmax-1 stored + nmax, weights
+ * x^2, the scale tried at 18 more values around -nmax / (value of largest magnitude) */
+static float search_scale_sym(int n, int nmax, const float *x, int8_t *L) {
+    float max = 0, amax = 0;
+    for (int i = 0; i < n; i++) {
+        float ax = fabsf(x[i]);
+        if (ax > amax) { amax = ax; max = x[i]; }
+    }
+    if (amax < 1e-15f) {
+        memset(L, 0, (size_t)n);
+        return 0.f;
+    }
+    float iscale = -nmax / max;
+    float sumlx = 0, suml2 = 0;
+    for (int i = 0; i < n; i++) {
+        int l = near_int(iscale * x[i]);
+        l = l < -nmax ? -nmax : (l > nmax - 1 ? nmax - 1 : l);
+        L[i] = (int8_t)(l + nmax);
+        const float w = x[i] * x[i];
+        sumlx += w * x[i] * l;
+        suml2 += w * l * l;
+    }
+    float scale = suml2 ? sumlx / suml2 : 0.0f;
+    float best = scale * sumlx;
+    for (int is = -9; is <= 9; is++) {
+        if (is == 0) continue;
+        iscale = -(nmax + 0.1f * is) / max;
+        sumlx = suml2 = 0;
+        for (int i = 0; i < n; i++) {
+            int l = near_int(iscale * x[i]);
+            l = l < -nmax ? -nmax : (l > nmax - 1 ? nmax - 1 : l);
+            const float w = x[i] * x[i];
+            sumlx += w * x[i] * l;
+            suml2 += w * l * l;
+        }
+        if (suml2 > 0 && sumlx * sumlx > best * suml2) {
+            for (int i = 0; i < n; i++) {
+                int l = near_int(iscale * x[i]);
+                l = l < -nmax ? -nmax : (l > nmax - 1 ? nmax - 1 : l);
+                L[i] = (int8_t)(nmax + l);
+            }
+            scale = sumlx / suml2;
+            best = scale * sumlx;
+        }
+    }
+    return scale;
+}
+
+/* ggml-quants.c:1869-1937: 16 groups of 16, int8 group scales against d = max_scale / -128, 6-bit codes split into
+ * ql (low nibbles) and qh (high two bits) */
+void orc_quantize_row_q6_K(const float *x, void *vy, int64_t k) {
+    blk_q6_K *y = (blk_q6_K *)vy;
+    int8_t L[256];
+    float scales[16];
+    for (int64_t b = 0; b < k / 256; b++, x += 256) {
+        float max_scale = 0, max_abs_scale = 0;
+        for (int j = 0; j < 16; j++) {
+            scales[j] = search_scale_sym(16, 32, x + 16 * j, L + 16 * j);
+            const float a = fabsf(scales[j]);
+            if (a > max_abs_scale) { max_abs_scale = a; max_scale = scales[j]; }
+        }
+        if (max_abs_scale < 1e-15f) {
+            memset(&y[b], 0, sizeof(blk_q6_K));
+            continue;
+        }
+        const float iscale = -128.f / max_scale;
+        y[b].d = orc_f32_to_f16(1 / iscale);
+        for (int j = 0; j < 16; j++) {
+            const int l = near_int(iscale * scales[j]);
+            y[b].scales[j] = (int8_t)(l > 127 ? 127 : l);
+        }
+        for (int j = 0; j < 16; j++) {
+            const float d = orc_f16_to_f32(y[b].d) * y[b].scales[j];
+            if (!d) continue;
+            for (int i = 0; i < 16; i++) {
+                int l = near_int(x[16 * j + i] / d);
+                l = l < -32 ? -32 : (l > 31 ? 31 : l);
+                L[16 * j + i] = (int8_t)(l + 32);
+            }
+        }
+        uint8_t *ql = y[b].ql, *qh = y[b].qh;
+        for (int j = 0; j < 256; j += 128, ql += 64, qh += 32)
+            for (int l = 0; l < 32; l++) {
+                const uint8_t q1 = L[j + l] & 0xF, q2 = L[j + l + 32] & 0xF, q3 = L[j + l + 64] & 0xF, q4 = L[j + l + 96] & 0xF;
+                ql[l] = (uint8_t)(q1 | (q3 << 4));
+                ql[l + 32] = (uint8_t)(q2 | (q4 << 4));
+                qh[l] = (uint8_t)((L[j + l] >> 4) | ((L[j + l + 32] >> 4) << 2) | ((L[j + l + 64] >> 4) << 4) | ((L[j + l + 96] >> 4) << 6));
+            }
+    }
+}
+
+/* ggml-impl.h ggml_compute_fp32_to_bf16: round to nearest even on the upper 16 bits, NaN kept quiet */
+static uint16_t f32_to_bf16(float f) {
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    if ((u & 0x7fffffff) > 0x7f800000) return (uint16_t)((u >> 16) | 64);
+    return (uint16_t)((u + (0x7fff + ((u >> 16) & 1))) >> 16);
+}
+
 int orc_quantize_rows(int type, const float *src, int64_t nrows, int64_t n, void *dst) {
     int64_t rs = orc_row_size(type, n);
     if (rs < 0) return -1;
@@ -307,6 +693,14 @@ int orc_quantize_rows(int type, const float *src, int64_t nrows, int64_t n, void
             case ORC_Q8_0: orc_quantize_row_q8_0(s, o, n); break;
             case ORC_Q4_0: orc_quantize_row_q4_0(s, o, n); break;
             case ORC_Q4_K: orc_quantize_row_q4_K(s, o, n); break;
+            case ORC_Q4_1: orc_quantize_row_q4_1(s, o, n); break;
+            case ORC_Q5_0: orc_quantize_row_q5_0(s, o, n); break;
+            case ORC_Q5_1: orc_quantize_row_q5_1(s, o, n); break;
+            case ORC_Q2_K: orc_quantize_row_q2_K(s, o, n); break;
+            case ORC_Q3_K: orc_quantize_row_q3_K(s, o, n); break;
+            case ORC_Q5_K: orc_quantize_row_q5_K(s, o, n); break;
+            case ORC_Q6_K: orc_quantize_row_q6_K(s, o, n); break;
+            case ORC_BF16: for (int64_t i = 0; i < n; i++) ((uint16_t *)o)[i] = f32_to_bf16(s[i]); break;
             case ORC_F16: for (int64_t i = 0; i < n; i++) ((uint16_t *)o)[i] = orc_f32_to_f16(s[i]); break;
             case ORC_F32: memcpy(o, s, (size_t)n * 4); break;
             default: return -1;

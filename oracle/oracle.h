@@ -16,7 +16,7 @@ extern "C" {
 #endif
 
 enum { ORC_F32 = 0, ORC_F16 = 1, ORC_Q4_0 = 2, ORC_Q4_1 = 3, ORC_Q5_0 = 6, ORC_Q5_1 = 7, ORC_Q8_0 = 8, ORC_Q2_K = 10, ORC_Q3_K = 11, ORC_Q4_K = 12,
-       ORC_Q5_K = 13, ORC_Q6_K = 14 };
+       ORC_Q5_K = 13, ORC_Q6_K = 14, ORC_BF16 = 30 };
 
 uint16_t orc_f32_to_f16(float f);
 float    orc_f16_to_f32(uint16_t h);
@@ -29,6 +29,13 @@ void orc_quantize_row_q8_0(const float *x, void *y, int64_t k); /* ggml-quants.c
 void orc_quantize_row_q4_0(const float *x, void *y, int64_t k); /* ggml-quants.c:113-148  */
 void orc_quantize_row_q4_K(const float *x, void *y, int64_t k); /* ggml-quants.c:1457-1527 */
 void orc_quantize_row_q8_K(const float *x, void *y, int64_t k); /* ggml-quants.c:2768-2805 */
+void orc_quantize_row_q4_1(const float *x, void *y, int64_t k); /* ggml-quants.c:150-185   */
+void orc_quantize_row_q5_0(const float *x, void *y, int64_t k); /* ggml-quants.c:187-229   */
+void orc_quantize_row_q5_1(const float *x, void *y, int64_t k); /* ggml-quants.c:231-273   */
+void orc_quantize_row_q2_K(const float *x, void *y, int64_t k); /* ggml-quants.c:891-958   */
+void orc_quantize_row_q3_K(const float *x, void *y, int64_t k); /* ggml-quants.c:1229-1303 */
+void orc_quantize_row_q5_K(const float *x, void *y, int64_t k); /* ggml-quants.c:1644-1727 */
+void orc_quantize_row_q6_K(const float *x, void *y, int64_t k); /* ggml-quants.c:1869-1937 */
 int  orc_quantize_rows(int type, const float *src, int64_t nrows, int64_t n_per_row, void *dst);
 int  orc_dequantize_row(int type, const void *src, float *dst, int64_t k);
 

@@ -848,7 +848,10 @@ tlb_status tlb_selftest_wait_runs_out(tlb_device *dev, uint32_t limit, uint32_t 
 tlb_status tlb_quantize_rows_device(tlb_device *dev, uint32_t type, const void *src, int64_t rows, int64_t n_per_row, void *out) {
     if (!dev) return fail(TLB_INVALID, "null device");
     const TypeTraits *tr = type_traits(type);
-    if (!tr || !(type == TLB_TYPE_Q8_0 || type == TLB_TYPE_Q4_0 || type == TLB_TYPE_Q4_K || type == TLB_TYPE_F16))
+    const bool have = type == TLB_TYPE_Q8_0 || type == TLB_TYPE_Q4_0 || type == TLB_TYPE_Q4_K || type == TLB_TYPE_F16 || type == TLB_TYPE_BF16 ||
+                      type == TLB_TYPE_Q4_1 || type == TLB_TYPE_Q5_0 || type == TLB_TYPE_Q5_1 || type == TLB_TYPE_Q2_K || type == TLB_TYPE_Q3_K ||
+                      type == TLB_TYPE_Q5_K || type == TLB_TYPE_Q6_K;
+    if (!tr || !have)
         return fail(TLB_UNSUPPORTED, std::string("quantizing to ggml type ") + (tr ? tr->name : "?") + " is not implemented");
     if (rows < 0 || n_per_row < 0 || n_per_row % tr->blck != 0)
         return fail(TLB_INVALID, "row length " + std::to_string(n_per_row) + " is not a multiple of the block size " + std::to_string(tr->blck));

@@ -281,7 +281,7 @@ def quantize_rows(native: Native, ty: int, x: np.ndarray) -> np.ndarray:
     """DType::from_f32 (crates/tensorlisp/src/dtype.rs:98-124): f32 [rows, n] -> blocks [rows, row bytes]."""
     x = np.ascontiguousarray(x, np.float32)
     rows, n = x.shape
-    name, blck, size = TYPE_TRAITS[ty]
+    name, blck, size = TYPE_TRAITS.get(ty, ("?", 1, 0))      # an unknown type is refused by name by the library
     out = np.zeros((rows, size * n // blck if n % blck == 0 else 0), np.uint8)
     check(native.L.tlb_quantize_rows(native.dev, ty, x.ctypes.data_as(C.c_void_p), rows, n,
                                      out.ctypes.data_as(C.c_void_p)))

@@ -5,12 +5,14 @@ import os
 import numpy as np
 import pytest
 
-from oracle.bindings import Q4_0, Q4_K, Q8_0
+from oracle.bindings import BF16, Q2_K, Q3_K, Q4_0, Q4_1, Q4_K, Q5_0, Q5_1, Q5_K, Q6_K, Q8_0
 from tensorlisp_b200.native import TlbError, quantize_rows
 
 pytestmark = pytest.mark.gpu
 G = np.load(os.path.join(os.path.dirname(__file__), "golden", "golden.npz"))
+DEC = np.load(os.path.join(os.path.dirname(__file__), "golden", "golden_decoders.npz"))
 TYPES = [(Q8_0, "q8_0"), (Q4_0, "q4_0"), (Q4_K, "q4_K")]
+MORE = [(Q4_1, "q4_1"), (Q5_0, "q5_0"), (Q5_1, "q5_1"), (Q2_K, "q2_K"), (Q3_K, "q3_K"), (Q5_K, "q5_K"), (Q6_K, "q6_K")]
 
 
 @pytest.mark.parametrize("ty,name", TYPES)
@@ -19,14 +21,29 @@ def test_golden_bytes(native, ty, name):
     assert np.array_equal(got, G["quant_" + name])
 
 
-@pytest.mark.parametrize("ty,name", TYPES)
+@pytest.mark.parametrize("ty,name", MORE)
+def test_golden_bytes_of_the_other_block_types(native, ty, name):
+    """The reference's own bytes (ggml_quantize_chunk) for seeded random rows and edge-case rows: all-zero and constant
+    blocks, an outlier, tiny and huge magnitudes."""
+    got = quantize_rows(native, ty, DEC["x"])
+    assert np.array_equal(got, DEC["quant_" + name])
+
+
+@pytest.mark.parametrize("ty,name", TYPES + MORE + [(BF16, "bf16")])
 @pytest.mark.parametrize("shape,scale,seed", [((64, 4096), 0.02, 0), ((8, 14336), 0.02, 3), ((33, 256), 1.0, 4), ((5, 1024), 50.0, 5)])
 def test_against_oracle(native, oracle, ty, name, shape, scale, seed):
     rng = np.random.default_rng(seed)
     x = (rng.standard_normal(shape) * scale).astype(np.float32)
     x[0, :256] = 0.0          # an all-zero super-block
     x[-1, :32] = 0.25         # a constant block
-    assert np.array_equal(quantize_rows(native, ty, x), oracle.quantize(ty, x))
+    x[1, :256] = np.abs(x[1, :256])        # all positive: the block minimum clamps to zero in the K-quants
+    x[2, 5] = 3e3 * scale     # an outlier
+    x[3, :16] = 1e-20         # a group below the all-zero threshold of the K-quant searches
+    x[4, 32:64] = np.where(np.arange(32) % 2 == 0, 0.0, -0.0)   # zeros of both signs (first minimum / maximum wins)
+    got, want = quantize_rows(native, ty, x), oracle.quantize(ty, x)
+    if ty == BF16:
+        got, want = got.view(np.uint8), want.view(np.uint8)
+    assert np.array_equal(got.reshape(want.shape), want)
 
 
 def test_config1_matrix_q8_0_bit_exact(native, oracle):
@@ -58,7 +75,7 @@ def test_empty_and_bad_rows(native):
         quantize_rows(native, Q4_K, np.zeros((2, 100), np.float32))
     assert "multiple of the block size" in str(e.value)
     with pytest.raises(TlbError) as e:
-        quantize_rows(native, 14, np.zeros((2, 256), np.float32))  # q6_K is not implemented
+        quantize_rows(native, 20, np.zeros((2, 256), np.float32))  # iq4_nl is not implemented
     assert "not implemented" in str(e.value)
 
 

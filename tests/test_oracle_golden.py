@@ -80,6 +80,8 @@ def test_decoders_of_the_other_block_types(oracle, ty, name):
     q = DEC["quant_" + name]
     assert q.shape[1] == oracle.row_size(ty, 512)
     assert np.array_equal(oracle.dequantize(ty, q, 512).view(np.uint32), DEC["dequant_" + name].view(np.uint32))
+    # and the oracle's quantizer gives the reference's bytes for the same rows
+    assert np.array_equal(oracle.quantize(ty, DEC["x"]), q)
     # the values are what the type can hold of x: a few percent of the row scale at most (2- and 3-bit types are coarse)
     x, y = DEC["x"], DEC["dequant_" + name]
     assert np.abs(x - y).max() <= 0.5 * np.abs(x).max()

@@ -3,16 +3,25 @@
 import numpy as np
 import pytest
 
-from oracle.bindings import F32, Q4_0, Q4_K, Q8_0
+from oracle.bindings import BF16, F32, Q2_K, Q3_K, Q4_0, Q4_1, Q4_K, Q5_0, Q5_1, Q5_K, Q6_K, Q8_0
 
 TYPES = [(Q8_0, "q8_0"), (Q4_0, "q4_0"), (Q4_K, "q4_K")]
+ALL_TARGETS = TYPES + [(Q4_1, "q4_1"), (Q5_0, "q5_0"), (Q5_1, "q5_1"), (Q2_K, "q2_K"), (Q3_K, "q3_K"), (Q5_K, "q5_K"), (Q6_K, "q6_K"),
+                       (BF16, "bf16")]
 
 
-@pytest.mark.parametrize("ty,name", TYPES)
-@pytest.mark.parametrize("n", [4096, 14336])
-def test_quantizers_match_reference(oracle, ref, ty, name, n):
+@pytest.mark.parametrize("ty,name", ALL_TARGETS)
+@pytest.mark.parametrize("n,scale", [(4096, 0.02), (14336, 0.02), (1024, 30.0)])
+def test_quantizers_match_reference(oracle, ref, ty, name, n, scale):
     rng = np.random.default_rng(0)
-    x = (rng.standard_normal((16, n)) * 0.02).astype(np.float32)
+    x = (rng.standard_normal((16, n)) * scale).astype(np.float32)
+    x[0, :256] = 0.0            # an all-zero super-block
+    x[1, :32] = 0.25            # a constant block
+    x[2, 256:512] = np.abs(x[2, 256:512])       # all positive: the minimum clamps to zero
+    x[3, 7] = 1e4 * scale       # an outlier
+    x[4, :16] = 1e-20           # below the all-zero threshold of the K-quant group search
+    x[5, 32:64] = np.where(np.arange(32) % 2 == 0, 0.0, -0.0)     # zeros of both signs
+    x[6, 32:64] = np.where(np.arange(32) % 2 == 0, -0.0, 0.0)
     assert np.array_equal(oracle.quantize(ty, x), ref.quantize(ty, x))
 
 
