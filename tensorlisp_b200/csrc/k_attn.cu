@@ -63,6 +63,7 @@ struct PagedParams {
     __half *out;           // [seqs][heads][HS]
     float *partial;        // [seqs][heads][n_chunks][HS + 2]  (max, sum, O) when n_chunks > 1
     int heads, kv_heads, group, groups_per_kv, block_size, block_shift, max_blocks, chunk_tokens, n_chunks;
+    int hs;                // head size (the tensor-core kernel has it as a template argument)
     int ctx_cap;           // min(maximum context, max_blocks * block_size): no length from the caller reaches past a table row
     uint32_t pool_blocks;  // pages in each pool; 0x80000000 when this launch does not know (block ids are then only checked for sign)
     int *err;              // device error word, or null: set to TLB_ERR_INDEX when a length or a block id was out of range
@@ -384,6 +385,120 @@ __global__ void __launch_bounds__(128) k_paged_reduce(PagedParams p) {
     }
 }
 
+// ---------------------------------------------------------------- any other head size
+// The head sizes of the reference's list (crates/kernels/src/cuda/paged_attn.rs:24: 64 80 96 112 128 192 256 512) that
+// the tensor-core kernel above does not take, and any other multiple of 8 up to 512: one CTA per (sequence, query
+// head), a warp per token in turn, a lane per 16-byte chunk of the row (C chunks per lane), f32 dot product, online
+// softmax and accumulation per warp, the warps merged through shared memory. No context split. Not a tuned kernel:
+// a query head re-reads its KV head's pages (from L2 within a group).
+template <int C>
+__global__ void __launch_bounds__(PA_WARPS * 32) k_paged_attn_any(PagedParams p) {
+    griddep_launch();
+    griddep_wait();
+    __shared__ float ml[PA_WARPS][2];
+    __shared__ float accs[PA_WARPS][512];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int head = blockIdx.y, seq = blockIdx.z, kvh = head / p.group;
+    const int hs = p.hs, chunks = hs >> 3;
+    const int ctx = paged_ctx(p, seq);
+    const int32_t *table = p.tables + (size_t)seq * p.max_blocks;
+    {
+        bool bad = false;
+        if (ctx > 0)
+            for (int b = (int)threadIdx.x; b <= ((ctx - 1) >> p.block_shift); b += PA_WARPS * 32)
+                bad |= (uint32_t)table[b] >= p.pool_blocks;
+        if (__syncthreads_or(bad)) {
+            if (threadIdx.x == 0 && p.err) atomicExch(p.err, TLB_ERR_INDEX);
+            return;
+        }
+    }
+    float qf[C][8], acc[C][8];
+    const __half *q0 = p.q + ((size_t)seq * p.heads + head) * hs;
+#pragma unroll
+    for (int c = 0; c < C; c++) {
+        const int ch = lane + 32 * c;
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if (ch < chunks) raw = *reinterpret_cast<const uint4 *>(q0 + ch * 8);
+        const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const float2 f = __half22float2(h[e]);
+            qf[c][2 * e] = f.x;
+            qf[c][2 * e + 1] = f.y;
+            acc[c][2 * e] = acc[c][2 * e + 1] = 0.f;
+        }
+    }
+    float m_run = -CUDART_INF_F, l_run = 0.f;
+    const size_t page_stride = (size_t)p.block_size * hs;
+    for (int tok = warp; tok < ctx; tok += PA_WARPS) {
+        const int blk = table[tok >> p.block_shift];
+        const size_t off = ((size_t)blk * p.kv_heads + kvh) * page_stride + (size_t)(tok & (p.block_size - 1)) * hs;
+        uint4 vraw[C];
+        float dot = 0.f;
+#pragma unroll
+        for (int c = 0; c < C; c++) {
+            const int ch = lane + 32 * c;
+            uint4 kraw = make_uint4(0, 0, 0, 0);
+            vraw[c] = make_uint4(0, 0, 0, 0);
+            if (ch < chunks) {
+                kraw = *reinterpret_cast<const uint4 *>(p.kpool + off + ch * 8);
+                vraw[c] = *reinterpret_cast<const uint4 *>(p.vpool + off + ch * 8);
+            }
+            const __half2 *h = reinterpret_cast<const __half2 *>(&kraw);
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float2 f = __half22float2(h[e]);
+                dot = fmaf(qf[c][2 * e], f.x, dot);
+                dot = fmaf(qf[c][2 * e + 1], f.y, dot);
+            }
+        }
+#pragma unroll
+        for (int sh = 16; sh > 0; sh >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, sh);
+        const float sc = dot * p.scale_log2;
+        const float m_new = fmaxf(m_run, sc);
+        const float corr = exp2f(m_run - m_new), pw = exp2f(sc - m_new);
+        m_run = m_new;
+        l_run = l_run * corr + pw;
+#pragma unroll
+        for (int c = 0; c < C; c++) {
+            const __half2 *h = reinterpret_cast<const __half2 *>(&vraw[c]);
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float2 f = __half22float2(h[e]);
+                acc[c][2 * e] = fmaf(pw, f.x, acc[c][2 * e] * corr);
+                acc[c][2 * e + 1] = fmaf(pw, f.y, acc[c][2 * e + 1] * corr);
+            }
+        }
+    }
+    if (lane == 0) {
+        ml[warp][0] = m_run;
+        ml[warp][1] = l_run;
+    }
+#pragma unroll
+    for (int c = 0; c < C; c++) {
+        const int ch = lane + 32 * c;
+        if (ch < chunks) {
+#pragma unroll
+            for (int e = 0; e < 8; e++) accs[warp][ch * 8 + e] = acc[c][e];
+        }
+    }
+    __syncthreads();
+    float m = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < PA_WARPS; w++) m = fmaxf(m, ml[w][0]);
+    const float mu = m == -CUDART_INF_F ? 0.f : m;
+    for (int d = threadIdx.x; d < hs; d += PA_WARPS * 32) {
+        float l = 0.f, a = 0.f;
+#pragma unroll
+        for (int w = 0; w < PA_WARPS; w++) {
+            const float f = exp2f(ml[w][0] - mu);
+            l += ml[w][1] * f;
+            a += accs[w][d] * f;
+        }
+        p.out[((size_t)seq * p.heads + head) * hs + d] = __float2half_rn(l > 0.f ? a / l : 0.f);
+    }
+}
+
 // ---------------------------------------------------------------- host side
 // the heads of a CTA make whole 256-value blocks of the output row, at a block boundary
 bool paged_quant_fusable(const PagedGeom &g) {
@@ -403,8 +518,10 @@ void attn_configure() {
     cudaFuncSetAttribute(k_paged_attn<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pa_smem(256));
 }
 
+static bool pa_tensor_core_hs(int hs) { return hs == 64 || hs == 128 || hs == 256; }
+
 bool paged_supported(const PagedGeom &g) {
-    if (!(g.hs == 64 || g.hs == 128 || g.hs == 256)) return false;
+    if (g.hs < 8 || g.hs > 512 || g.hs % 8 != 0) return false;
     if (g.kv_heads < 1 || g.heads % g.kv_heads != 0) return false;
     if (g.block_size < 1 || g.max_blocks < 1 || (g.block_size & (g.block_size - 1)) != 0) return false;
     return true;
@@ -416,6 +533,11 @@ bool paged_supported(const PagedGeom &g) {
 // as 110 tokens and splitting as much as 100: the context is split only as far as it takes to fill
 // the machine, and the split count minimises that model.
 void paged_plan(PagedGeom &g, int sm_count) {
+    if (!pa_tensor_core_hs(g.hs)) {   // the kernel for the other head sizes takes a whole context per CTA
+        g.chunk_tokens = (int)std::max<int64_t>(64, (g.max_ctx + 63) / 64 * 64);
+        g.n_chunks = 1;
+        return;
+    }
     const int group = g.heads / g.kv_heads;
     const int64_t base = (int64_t)g.seqs * g.kv_heads * ((group + 15) / 16);
     const int64_t per_sm = std::max<int64_t>(1, std::min<int64_t>(3, (227 * 1024) / ((int64_t)pa_smem(g.hs) + 1024)));
@@ -473,6 +595,7 @@ cudaError_t launch_paged_attention(const PagedGeom &g, const void *q, const void
     p.max_blocks = g.max_blocks;
     p.chunk_tokens = g.chunk_tokens;
     p.n_chunks = g.n_chunks;
+    p.hs = g.hs;
     p.ctx_cap = (int)std::min<int64_t>(g.max_ctx, (int64_t)g.max_blocks * g.block_size);
     p.pool_blocks = pool_blocks > 0 && pool_blocks < 0x80000000ll ? (uint32_t)pool_blocks : 0x80000000u;
     p.err = err;
@@ -488,8 +611,12 @@ cudaError_t launch_paged_attention(const PagedGeom &g, const void *q, const void
         case 64: return launch_pa<64>(g, p, st);
         case 128: return launch_pa<128>(g, p, st);
         case 256: return launch_pa<256>(g, p, st);
-        default: return cudaErrorInvalidValue;
+        default: break;
     }
+    if (!paged_supported(g) || g.n_chunks != 1) return cudaErrorInvalidValue;
+    const dim3 grid(1, (unsigned)g.heads, (unsigned)g.seqs);
+    if (g.hs <= 256) return launch_pdl(k_paged_attn_any<1>, grid, dim3(PA_WARPS * 32), 0, st, p);
+    return launch_pdl(k_paged_attn_any<2>, grid, dim3(PA_WARPS * 32), 0, st, p);
 }
 
 // cache write: key/value f16 [kv_heads*hs, tokens] -> pools at slot = block*block_size + offset

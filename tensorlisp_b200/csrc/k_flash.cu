@@ -258,9 +258,140 @@ __global__ void __launch_bounds__(D) k_flash_merge(FlashArgs p, const float *__r
     out[(((int64_t)b * p.nq + q) * p.nh + h) * D + d] = l > 0.f ? a / l : 0.f;
 }
 
+// ---------------------------------------------------------------- any other head size
+// Head sizes other than 64 / 128, up to 512, keys and values of different sizes included (the reference takes any value
+// head size up to 512, crates/kernels/src/cuda/lower.rs:594-596; its tests run 72, 80, 96, 112 and 256,
+// crates/tensorlisp/tests/native.rs:283-346): one CTA per (query, stretch of keys, head, batch) as in the reference's
+// fa_main / fa_split, a warp per key in turn, lane i holding elements i, i + 32, ... of the rows; f32 dot product,
+// online softmax and accumulation per warp, the warps merged through shared memory. With an f16 cache the query is
+// rounded to f16 first, as the CPU backend does. Not a tuned kernel.
+constexpr int FA_ANY_MAX = 512, FA_ANY_PER_LANE = FA_ANY_MAX / 32;
+
+template <bool KF32, bool VF32>
+__global__ void __launch_bounds__(FA_WARPS * 32) k_flash_attn_any(FlashArgs p, const uint8_t *__restrict__ q, const uint8_t *__restrict__ k,
+                                                                  const uint8_t *__restrict__ v, const uint8_t *__restrict__ mask,
+                                                                  float *__restrict__ out, float *__restrict__ partial) {
+    griddep_launch();
+    griddep_wait();
+    __shared__ float ml[FA_WARPS][2];
+    __shared__ float accs[FA_WARPS][FA_ANY_MAX];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int part = blockIdx.x % p.parts, qi = blockIdx.x / p.parts;
+    const int h = blockIdx.y, b = blockIdx.z, hk = h / (p.nh / p.nhkv);
+    const int k_begin = part * p.part_len, k_end = min(p.nkv, k_begin + p.part_len);
+    const int D = p.d, DV = p.dv;
+    float qf[FA_ANY_PER_LANE], acc[FA_ANY_PER_LANE];
+    {
+        const float *qr = reinterpret_cast<const float *>(q + (int64_t)qi * p.q.nb[1] + (int64_t)h * p.q.nb[2] + (int64_t)b * p.q.nb[3]);
+#pragma unroll
+        for (int j = 0; j < FA_ANY_PER_LANE; j++) {
+            const int e = lane + 32 * j;
+            float x = e < D ? qr[e] : 0.f;
+            if (!KF32) x = __half2float(__float2half_rn(x));
+            qf[j] = x;
+            acc[j] = 0.f;
+        }
+    }
+    const uint8_t *kb = k + (int64_t)hk * p.k.nb[2] + (int64_t)b * p.k.nb[3];
+    const uint8_t *vb = v + (int64_t)hk * p.v.nb[2] + (int64_t)b * p.v.nb[3];
+    const __half *mr = mask ? reinterpret_cast<const __half *>(mask + (int64_t)(h % p.m_ne2) * p.m.nb[2] + (int64_t)(b % p.m_ne3) * p.m.nb[3] +
+                                                               (int64_t)qi * p.m.nb[1])
+                            : nullptr;
+    const float LOG2E = 1.4426950408889634f;
+    float slope = 1.f;
+    if (p.max_bias > 0.f) slope = h < p.n_head_log2 ? powf(p.m0, (float)(h + 1)) : powf(p.m1, (float)(2 * (h - p.n_head_log2) + 1));
+    float m_run = -CUDART_INF_F, l_run = 0.f;
+    for (int key = k_begin + warp; key < k_end; key += FA_WARPS) {
+        float mv = 0.f;
+        if (mr) {
+            const __half mh = mr[key];
+            if (__half_as_ushort(mh) == 0xfc00) continue;   // a key masked with -inf takes no part
+            mv = slope * __half2float(mh);
+        }
+        const uint8_t *kr = kb + (int64_t)key * p.k.nb[1];
+        float dot = 0.f;
+#pragma unroll
+        for (int j = 0; j < FA_ANY_PER_LANE; j++) {
+            const int e = lane + 32 * j;
+            if (32 * j < D && e < D)
+                dot = fmaf(qf[j], KF32 ? reinterpret_cast<const float *>(kr)[e] : __half2float(reinterpret_cast<const __half *>(kr)[e]), dot);
+        }
+#pragma unroll
+        for (int sh = 16; sh > 0; sh >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, sh);
+        float x = dot * p.scale;
+        if (p.softcap != 0.f) x = p.softcap * tanhf(x);
+        x = (x + mv) * LOG2E;
+        if (x == -CUDART_INF_F) continue;
+        const float m_new = fmaxf(m_run, x);
+        const float corr = exp2f(m_run - m_new), pw = exp2f(x - m_new);
+        m_run = m_new;
+        l_run = l_run * corr + pw;
+        const uint8_t *vr = vb + (int64_t)key * p.v.nb[1];
+#pragma unroll
+        for (int j = 0; j < FA_ANY_PER_LANE; j++) {
+            const int e = lane + 32 * j;
+            if (32 * j < DV && e < DV)
+                acc[j] = fmaf(pw, VF32 ? reinterpret_cast<const float *>(vr)[e] : __half2float(reinterpret_cast<const __half *>(vr)[e]), acc[j] * corr);
+        }
+    }
+    if (lane == 0) {
+        ml[warp][0] = m_run;
+        ml[warp][1] = l_run;
+    }
+#pragma unroll
+    for (int j = 0; j < FA_ANY_PER_LANE; j++) {
+        const int e = lane + 32 * j;
+        if (e < DV) accs[warp][e] = acc[j];
+    }
+    __syncthreads();
+    float m = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < FA_WARPS; w++) m = fmaxf(m, ml[w][0]);
+    const float ref = m == -CUDART_INF_F ? 0.f : m;
+    float f[FA_WARPS], l = 0.f;
+#pragma unroll
+    for (int w = 0; w < FA_WARPS; w++) {
+        f[w] = exp2f(ml[w][0] - ref);   // a warp that saw no live key has m = -inf: weight 0
+        l += ml[w][1] * f[w];
+    }
+    float *pp = p.parts > 1 ? partial + ((((int64_t)b * p.nh + h) * p.nq + qi) * p.parts + part) * (DV + 2) : nullptr;
+    float *o = out + (((int64_t)b * p.nq + qi) * p.nh + h) * DV;
+    if (pp && threadIdx.x == 0) {
+        pp[0] = m;
+        pp[1] = l;
+    }
+    for (int d = threadIdx.x; d < DV; d += FA_WARPS * 32) {
+        float a = 0.f;
+#pragma unroll
+        for (int w = 0; w < FA_WARPS; w++) a += accs[w][d] * f[w];
+        if (pp) pp[2 + d] = a;
+        else o[d] = l > 0.f ? a / l : 0.f;
+    }
+}
+
+// merges the stretches of a split for any value head size: one CTA per (query, head, batch)
+__global__ void __launch_bounds__(128) k_flash_merge_any(FlashArgs p, const float *__restrict__ partial, float *__restrict__ out) {
+    griddep_launch();
+    griddep_wait();
+    const int q = blockIdx.x, h = blockIdx.y, b = blockIdx.z, DV = p.dv;
+    const float *pp = partial + (((int64_t)b * p.nh + h) * p.nq + q) * p.parts * (DV + 2);
+    float m = -CUDART_INF_F;
+    for (int c = 0; c < p.parts; c++) m = fmaxf(m, pp[(int64_t)c * (DV + 2)]);
+    const float ref = m == -CUDART_INF_F ? 0.f : m;
+    float l = 0.f;
+    for (int c = 0; c < p.parts; c++) l += pp[(int64_t)c * (DV + 2) + 1] * exp2f(pp[(int64_t)c * (DV + 2)] - ref);
+    for (int d = threadIdx.x; d < DV; d += 128) {
+        float a = 0.f;
+        for (int c = 0; c < p.parts; c++) a += pp[(int64_t)c * (DV + 2) + 2 + d] * exp2f(pp[(int64_t)c * (DV + 2)] - ref);
+        out[(((int64_t)b * p.nq + q) * p.nh + h) * DV + d] = l > 0.f ? a / l : 0.f;
+    }
+}
+
 }  // namespace
 
-bool flash_supported(int64_t d, int64_t dv) { return d == dv && (d == 64 || d == 128); }
+static bool fa_tensor_core_size(int64_t d, int64_t dv) { return d == dv && (d == 64 || d == 128); }
+bool flash_supported(int64_t d, int64_t dv) { return d >= 1 && dv >= 1 && d <= FA_ANY_MAX && dv <= FA_ANY_MAX; }
+bool flash_rows_need_alignment(int64_t d, int64_t dv) { return fa_tensor_core_size(d, dv); }
 
 // Split-KV for few queries over a long dense cache (the reference's rule, crates/kernels/src/cuda/lower.rs:764-779, on
 // this kernel's 64-key tiles): without it a one-query node runs heads x batch CTAs whatever the length of the cache.
@@ -268,7 +399,9 @@ void flash_split_plan(FlashArgs &p, int sm_count) {
     p.part_len = p.nkv > 0 ? p.nkv : 1;
     p.parts = 1;
     const char *e = getenv("TL_NATIVE_FA");
-    if (p.nq > FA_QT || p.nkv < 256 || (e && std::string(e) == "plain")) return;
+    const bool tc = fa_tensor_core_size(p.d, p.dv);
+    // the other head sizes run one query per CTA, like the reference: its rule as it stands (one query, 256 keys or more)
+    if (p.nq > (tc ? FA_QT : 1) || p.nkv < 256 || (e && std::string(e) == "plain")) return;
     const int64_t blocks = (int64_t)p.nh * p.nb;
     const int64_t want = ((int64_t)p.nkv * blocks + 4 * (int64_t)sm_count - 1) / (4 * (int64_t)sm_count);
     const int64_t part_len = std::max<int64_t>(FA_KT, (want + FA_KT - 1) / FA_KT * FA_KT);
@@ -279,7 +412,7 @@ void flash_split_plan(FlashArgs &p, int sm_count) {
     }
 }
 uint64_t flash_split_scratch_bytes(const FlashArgs &p) {
-    return p.parts > 1 ? (uint64_t)p.nb * p.nh * p.nq * p.parts * (p.d + 2) * 4 : 0;
+    return p.parts > 1 ? (uint64_t)p.nb * p.nh * p.nq * p.parts * (p.dv + 2) * 4 : 0;
 }
 
 template <int D>
@@ -301,7 +434,20 @@ cudaError_t launch_flash_attn(const FlashArgs &p, const void *q, const void *k, 
                               cudaStream_t st) {
     if (p.nq == 0 || p.nh == 0 || p.nb == 0) return cudaSuccess;
     if (p.parts < 1 || (p.parts > 1 && !scratch)) return cudaErrorInvalidValue;
-    return p.d == 64 ? launch_fa<64>(p, q, k, v, mask, out, (float *)scratch, st) : launch_fa<128>(p, q, k, v, mask, out, (float *)scratch, st);
+    if (fa_tensor_core_size(p.d, p.dv))
+        return p.d == 64 ? launch_fa<64>(p, q, k, v, mask, out, (float *)scratch, st) : launch_fa<128>(p, q, k, v, mask, out, (float *)scratch, st);
+    if (!flash_supported(p.d, p.dv)) return cudaErrorInvalidValue;
+    const dim3 grid((unsigned)(p.nq * p.parts), (unsigned)p.nh, (unsigned)p.nb), block(FA_WARPS * 32);
+    const uint8_t *q8 = (const uint8_t *)q, *k8 = (const uint8_t *)k, *v8 = (const uint8_t *)v, *m8 = (const uint8_t *)mask;
+    float *partial = (float *)scratch;
+    cudaError_t e;
+    if (p.k_f32 && p.v_f32) e = launch_pdl(k_flash_attn_any<true, true>, grid, block, 0, st, p, q8, k8, v8, m8, out, partial);
+    else if (p.k_f32) e = launch_pdl(k_flash_attn_any<true, false>, grid, block, 0, st, p, q8, k8, v8, m8, out, partial);
+    else if (p.v_f32) e = launch_pdl(k_flash_attn_any<false, true>, grid, block, 0, st, p, q8, k8, v8, m8, out, partial);
+    else e = launch_pdl(k_flash_attn_any<false, false>, grid, block, 0, st, p, q8, k8, v8, m8, out, partial);
+    if (e == cudaSuccess && p.parts > 1)
+        e = launch_pdl(k_flash_merge_any, dim3((unsigned)p.nq, (unsigned)p.nh, (unsigned)p.nb), dim3(128), 0, st, p, (const float *)partial, out);
+    return e;
 }
 
 }  // namespace tlb

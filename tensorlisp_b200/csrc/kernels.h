@@ -175,7 +175,7 @@ cudaError_t launch_pad(const PadArgs &p, const void *a, void *d, cudaStream_t st
 // FLASH_ATTN_EXT (dense): q f32 [d, nq, nh, nb], k / v f16 or f32 [d, nkv, nhkv, nb], optional f16 mask
 struct FlashArgs {
     TView q, k, v, m;
-    int nq, nkv, nh, nhkv, nb, d, m_ne2, m_ne3, n_head_log2;
+    int nq, nkv, nh, nhkv, nb, d, dv, m_ne2, m_ne3, n_head_log2;   // d: head size of queries and keys, dv: of values
     float scale, softcap, max_bias, m0, m1;   // scale already divided by softcap when that is set
     bool k_f32, v_f32;
     // split-KV (few queries over a long cache): the keys are cut into `parts` stretches of part_len, every stretch is a
@@ -183,6 +183,8 @@ struct FlashArgs {
     int part_len, parts;
 };
 bool flash_supported(int64_t d, int64_t dv);
+// 64 / 128 run on the tensor cores from 16-byte copies: their rows must start on 16-byte boundaries
+bool flash_rows_need_alignment(int64_t d, int64_t dv);
 // fills p.part_len / p.parts (parts = 1: no split) for a device of sm_count SMs; bytes of scratch the split needs
 void flash_split_plan(FlashArgs &p, int sm_count);
 uint64_t flash_split_scratch_bytes(const FlashArgs &p);

@@ -695,10 +695,11 @@ static const char *flash_args(const Graph &g, const Tensor &t, FlashArgs &p) {
     auto f16_or_f32 = [](const Tensor &x) { return (x.ty == TLB_TYPE_F16 && x.nb[0] == 2) || (x.ty == TLB_TYPE_F32 && x.nb[0] == 4); };
     if (tq.ty != TLB_TYPE_F32 || tq.nb[0] != 4 || t.ty != TLB_TYPE_F32) return "queries and result must be f32";
     if (!f16_or_f32(tk) || !f16_or_f32(tv)) return "keys and values must be dense f16 or f32 rows";
-    if (!flash_supported(tq.ne[0], tv.ne[0]) || tk.ne[0] != tq.ne[0]) return "head size must be 64 or 128, the same for keys and values";
+    if (!flash_supported(tq.ne[0], tv.ne[0]) || tk.ne[0] != tq.ne[0]) return "head sizes above 512, or keys of another size than the queries";
     if (tk.ne[1] != tv.ne[1] || tk.ne[2] != tv.ne[2] || tk.ne[2] == 0 || tq.ne[2] % tk.ne[2] != 0 || tk.ne[3] != tq.ne[3] || tv.ne[3] != tq.ne[3])
         return "inconsistent shapes";
-    if (tk.nb[1] % 16 || tv.nb[1] % 16 || tk.nb[2] % 16 || tv.nb[2] % 16 || tk.nb[3] % 16 || tv.nb[3] % 16 || tq.nb[1] % 8 || tq.nb[2] % 8 || tq.nb[3] % 8)
+    if (flash_rows_need_alignment(tq.ne[0], tv.ne[0]) &&
+        (tk.nb[1] % 16 || tv.nb[1] % 16 || tk.nb[2] % 16 || tv.nb[2] % 16 || tk.nb[3] % 16 || tv.nb[3] % 16 || tq.nb[1] % 8 || tq.nb[2] % 8 || tq.nb[3] % 8))
         return "rows must start on 16-byte boundaries";
     if (t.ne[0] != tv.ne[0] || t.ne[1] != tq.ne[2] || t.ne[2] != tq.ne[1] || t.ne[3] != tq.ne[3] || !t.is_contiguous())
         return "the result must be a contiguous [dv, heads, queries, batch] tensor";
@@ -707,6 +708,7 @@ static const char *flash_args(const Graph &g, const Tensor &t, FlashArgs &p) {
     p.k = view_of(tk);
     p.v = view_of(tv);
     p.d = (int)tq.ne[0];
+    p.dv = (int)tv.ne[0];
     p.nq = (int)tq.ne[1];
     p.nh = (int)tq.ne[2];
     p.nb = (int)tq.ne[3];

@@ -113,6 +113,54 @@ def test_flash_attn_against_ggml(ref):
     close(got, want, TOL)
 
 
+OTHER_SIZES = [
+    # d, dv, nq, nkv, nh, nhkv, nb, kv type: the shapes of the reference's own tests (crates/tensorlisp/tests/native.rs:283-346:
+    # head sizes 256, 72, 80, 96, 112; one query over a long cache, query counts around 16, key counts around the tiles)
+    (256, 256, 1, 1000, 4, 1, 1, G.F16), (256, 256, 1, 100, 4, 1, 1, G.F16), (256, 256, 5, 60, 4, 1, 1, G.F16), (256, 256, 40, 70, 4, 1, 1, G.F32),
+    (72, 72, 16, 1, 4, 2, 2, G.F16), (72, 72, 17, 17, 4, 2, 2, G.F32), (72, 72, 100, 300, 4, 2, 2, G.F16), (80, 80, 33, 129, 4, 2, 2, G.F16),
+    (96, 96, 20, 5000, 4, 2, 2, G.F16), (112, 112, 50, 33, 4, 2, 2, G.F16),
+    # values of another size than keys, the largest size, and a size that is no multiple of 8
+    (192, 128, 7, 90, 4, 2, 1, G.F16), (512, 512, 3, 77, 2, 1, 1, G.F16), (100, 60, 9, 40, 2, 2, 1, G.F32),
+]
+
+
+@pytest.mark.parametrize("case", OTHER_SIZES, ids=[str(c[:7]) for c in OTHER_SIZES])
+def test_other_head_sizes(case):
+    """Head sizes other than 64 / 128 (one CTA per query, as in the reference). The padding mask has holes inside the valid
+    range and hides the last quarter of the keys, as the reference's tests do; for one query over 256 keys or more the keys
+    are split into stretches and merged."""
+    d, dv, nq, nkv, nh, nhkv, nb, kv_ty = case
+    rng = np.random.default_rng(d + nq + nkv)
+    kdt = np.float16 if kv_ty == G.F16 else np.float32
+    q = rng.standard_normal((nb, nh, nq, d)).astype(np.float32)
+    k = rng.standard_normal((nb, nhkv, nkv, d)).astype(kdt)
+    v = rng.standard_normal((nb, nhkv, nkv, dv)).astype(kdt)
+    nq_pad = (nq + 31) // 32 * 32
+    valid = np.zeros(nkv, bool)
+    valid[[j for j in range(max(1, nkv * 3 // 4)) if j % 3 != 1 or nkv < 3]] = True
+    mask = np.ascontiguousarray(np.broadcast_to(np.where(valid, np.float16(0), np.float16(-np.inf)), (1, 1, nq_pad, nkv)))
+    scale = 1.0 / np.sqrt(d)
+    g = G.Graph()
+    tq = g.input(G.F32, [d, nq, nh, nb], "q")
+    tk = g.input(kv_ty, [d, nkv, nhkv, nb], "k")
+    tv = g.input(kv_ty, [dv, nkv, nhkv, nb], "v")
+    tm = g.input(G.F16, [nkv, nq_pad, 1, 1], "mask")
+    g.output(g.flash_attn_ext(tq, tk, tv, tm, scale, 0.0, 0.0, "attn"))
+    m = Model(g)
+    (got,) = m.run(q, k, v, mask)
+    m.close()
+    got = got.reshape(nb, nq, nh, dv)
+    qq = (q.astype(np.float16) if kv_ty == G.F16 else q).astype(np.float64)     # an f16 cache rounds the query to f16
+    want = np.zeros((nb, nq, nh, dv))
+    for b in range(nb):
+        for h in range(nh):
+            hk = h // (nh // nhkv)
+            sc = qq[b, h] @ k[b, hk].astype(np.float64).T * scale + mask[0, 0, :nq].astype(np.float64)
+            pr = np.exp(sc - sc.max(axis=1, keepdims=True))
+            want[b, :, h] = (pr / pr.sum(axis=1, keepdims=True)) @ v[b, hk].astype(np.float64)
+    close(got, want.astype(np.float32), TOL)
+
+
 def test_sinks_are_reported_by_name():
     from tensorlisp_b200._lib import TlbError
     g = G.Graph()

@@ -73,7 +73,10 @@ def paged_case(oracle, seqs, heads, kvh, hs, bs, ctxs, seed=0, shuffle=True, ski
     return got.reshape(seqs, heads, hs), want32
 
 
-@pytest.mark.parametrize("hs,kvh,heads,bs", [(64, 1, 4, 16), (128, 2, 8, 8), (256, 1, 2, 16), (128, 8, 32, 16), (128, 2, 2, 32), (64, 1, 20, 16)])
+@pytest.mark.parametrize("hs,kvh,heads,bs", [(64, 1, 4, 16), (128, 2, 8, 8), (256, 1, 2, 16), (128, 8, 32, 16), (128, 2, 2, 32), (64, 1, 20, 16),
+                                             # the other head sizes of the reference's list (paged_attn.rs:24), (512, 1, 32) being the
+                                             # case of its own test (native.rs:355)
+                                             (512, 1, 4, 32), (80, 2, 4, 16), (96, 1, 3, 8), (112, 1, 2, 16), (192, 2, 4, 32)])
 def test_paged_matches_dense(oracle, hs, kvh, heads, bs):
     got, want = paged_case(oracle, 4, heads, kvh, hs, bs, [1, 17, 64, 150], seed=hs + bs)
     close(got, want, 1e-3)
@@ -83,6 +86,13 @@ def test_paged_matches_dense(oracle, hs, kvh, heads, bs):
 def test_block_sizes_outside_the_scheme_layer(oracle, bs):
     """Pages of fewer than 8 tokens take the copy path with a table lookup per row; pages longer than a tile span tiles."""
     got, want = paged_case(oracle, 3, 8, 2, 128, bs, [5, 70, 131], seed=bs)
+    close(got, want, 1e-3)
+
+
+def test_head_size_512_ragged_lengths(oracle):
+    """The kernel for the head sizes outside 64 / 128 / 256 takes a whole context per CTA: an empty sequence, lengths
+    that leave some warps without a token, a context of a thousand tokens, grouped heads."""
+    got, want = paged_case(oracle, 5, 4, 2, 512, 16, [0, 1, 3, 1025, 700], seed=5)
     close(got, want, 1e-3)
 
 
