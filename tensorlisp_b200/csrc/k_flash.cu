@@ -18,6 +18,7 @@
 #include <cuda_fp16.h>
 #include <math_constants.h>
 
+#include "dequant.cuh"
 #include "kernels.h"
 #include "pdl.cuh"
 
@@ -267,7 +268,15 @@ __global__ void __launch_bounds__(D) k_flash_merge(FlashArgs p, const float *__r
 // rounded to f16 first, as the CPU backend does. Not a tuned kernel.
 constexpr int FA_ANY_MAX = 512, FA_ANY_PER_LANE = FA_ANY_MAX / 32;
 
-template <bool KF32, bool VF32>
+// element e of a key or value row: MODE 0 = f16, 1 = f32, 2 = any other type the executor decodes (bf16 and the block types)
+template <int MODE>
+__device__ __forceinline__ float fa_any_elem(const uint8_t *row, uint32_t ty, int e) {
+    if (MODE == 0) return __half2float(reinterpret_cast<const __half *>(row)[e]);
+    if (MODE == 1) return reinterpret_cast<const float *>(row)[e];
+    return is_quant(ty) ? dq_elem(row, ty, e) : ld_elem(row + (int64_t)e * 2, ty);   // the only other plain type here is bf16
+}
+
+template <int KM, int VM>
 __global__ void __launch_bounds__(FA_WARPS * 32) k_flash_attn_any(FlashArgs p, const uint8_t *__restrict__ q, const uint8_t *__restrict__ k,
                                                                   const uint8_t *__restrict__ v, const uint8_t *__restrict__ mask,
                                                                   float *__restrict__ out, float *__restrict__ partial) {
@@ -287,7 +296,7 @@ __global__ void __launch_bounds__(FA_WARPS * 32) k_flash_attn_any(FlashArgs p, c
         for (int j = 0; j < FA_ANY_PER_LANE; j++) {
             const int e = lane + 32 * j;
             float x = e < D ? qr[e] : 0.f;
-            if (!KF32) x = __half2float(__float2half_rn(x));
+            if (KM == 0) x = __half2float(__float2half_rn(x));
             qf[j] = x;
             acc[j] = 0.f;
         }
@@ -314,7 +323,7 @@ __global__ void __launch_bounds__(FA_WARPS * 32) k_flash_attn_any(FlashArgs p, c
         for (int j = 0; j < FA_ANY_PER_LANE; j++) {
             const int e = lane + 32 * j;
             if (32 * j < D && e < D)
-                dot = fmaf(qf[j], KF32 ? reinterpret_cast<const float *>(kr)[e] : __half2float(reinterpret_cast<const __half *>(kr)[e]), dot);
+                dot = fmaf(qf[j], fa_any_elem<KM>(kr, p.k_ty, e), dot);
         }
 #pragma unroll
         for (int sh = 16; sh > 0; sh >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, sh);
@@ -331,7 +340,7 @@ __global__ void __launch_bounds__(FA_WARPS * 32) k_flash_attn_any(FlashArgs p, c
         for (int j = 0; j < FA_ANY_PER_LANE; j++) {
             const int e = lane + 32 * j;
             if (32 * j < DV && e < DV)
-                acc[j] = fmaf(pw, VF32 ? reinterpret_cast<const float *>(vr)[e] : __half2float(reinterpret_cast<const __half *>(vr)[e]), acc[j] * corr);
+                acc[j] = fmaf(pw, fa_any_elem<VM>(vr, p.v_ty, e), acc[j] * corr);
         }
     }
     if (lane == 0) {
@@ -390,6 +399,9 @@ __global__ void __launch_bounds__(128) k_flash_merge_any(FlashArgs p, const floa
 }  // namespace
 
 static bool fa_tensor_core_size(int64_t d, int64_t dv) { return d == dv && (d == 64 || d == 128); }
+static bool fa_tensor_core(const FlashArgs &p) {
+    return fa_tensor_core_size(p.d, p.dv) && (p.k_ty == TLB_TYPE_F16 || p.k_ty == TLB_TYPE_F32) && (p.v_ty == TLB_TYPE_F16 || p.v_ty == TLB_TYPE_F32);
+}
 bool flash_supported(int64_t d, int64_t dv) { return d >= 1 && dv >= 1 && d <= FA_ANY_MAX && dv <= FA_ANY_MAX; }
 bool flash_rows_need_alignment(int64_t d, int64_t dv) { return fa_tensor_core_size(d, dv); }
 
@@ -399,7 +411,7 @@ void flash_split_plan(FlashArgs &p, int sm_count) {
     p.part_len = p.nkv > 0 ? p.nkv : 1;
     p.parts = 1;
     const char *e = getenv("TL_NATIVE_FA");
-    const bool tc = fa_tensor_core_size(p.d, p.dv);
+    const bool tc = fa_tensor_core(p);
     // the other head sizes run one query per CTA, like the reference: its rule as it stands (one query, 256 keys or more)
     if (p.nq > (tc ? FA_QT : 1) || p.nkv < 256 || (e && std::string(e) == "plain")) return;
     const int64_t blocks = (int64_t)p.nh * p.nb;
@@ -434,17 +446,19 @@ cudaError_t launch_flash_attn(const FlashArgs &p, const void *q, const void *k, 
                               cudaStream_t st) {
     if (p.nq == 0 || p.nh == 0 || p.nb == 0) return cudaSuccess;
     if (p.parts < 1 || (p.parts > 1 && !scratch)) return cudaErrorInvalidValue;
-    if (fa_tensor_core_size(p.d, p.dv))
+    if (fa_tensor_core(p))
         return p.d == 64 ? launch_fa<64>(p, q, k, v, mask, out, (float *)scratch, st) : launch_fa<128>(p, q, k, v, mask, out, (float *)scratch, st);
     if (!flash_supported(p.d, p.dv)) return cudaErrorInvalidValue;
     const dim3 grid((unsigned)(p.nq * p.parts), (unsigned)p.nh, (unsigned)p.nb), block(FA_WARPS * 32);
     const uint8_t *q8 = (const uint8_t *)q, *k8 = (const uint8_t *)k, *v8 = (const uint8_t *)v, *m8 = (const uint8_t *)mask;
     float *partial = (float *)scratch;
     cudaError_t e;
-    if (p.k_f32 && p.v_f32) e = launch_pdl(k_flash_attn_any<true, true>, grid, block, 0, st, p, q8, k8, v8, m8, out, partial);
-    else if (p.k_f32) e = launch_pdl(k_flash_attn_any<true, false>, grid, block, 0, st, p, q8, k8, v8, m8, out, partial);
-    else if (p.v_f32) e = launch_pdl(k_flash_attn_any<false, true>, grid, block, 0, st, p, q8, k8, v8, m8, out, partial);
-    else e = launch_pdl(k_flash_attn_any<false, false>, grid, block, 0, st, p, q8, k8, v8, m8, out, partial);
+    const auto plain = [](uint32_t ty) { return ty == TLB_TYPE_F16 || ty == TLB_TYPE_F32; };
+    if (!plain(p.k_ty) || !plain(p.v_ty)) e = launch_pdl(k_flash_attn_any<2, 2>, grid, block, 0, st, p, q8, k8, v8, m8, out, partial);
+    else if (p.k_f32 && p.v_f32) e = launch_pdl(k_flash_attn_any<1, 1>, grid, block, 0, st, p, q8, k8, v8, m8, out, partial);
+    else if (p.k_f32) e = launch_pdl(k_flash_attn_any<1, 0>, grid, block, 0, st, p, q8, k8, v8, m8, out, partial);
+    else if (p.v_f32) e = launch_pdl(k_flash_attn_any<0, 1>, grid, block, 0, st, p, q8, k8, v8, m8, out, partial);
+    else e = launch_pdl(k_flash_attn_any<0, 0>, grid, block, 0, st, p, q8, k8, v8, m8, out, partial);
     if (e == cudaSuccess && p.parts > 1)
         e = launch_pdl(k_flash_merge_any, dim3((unsigned)p.nq, (unsigned)p.nh, (unsigned)p.nb), dim3(128), 0, st, p, (const float *)partial, out);
     return e;

@@ -406,7 +406,7 @@ void flash_tc_configure() { cudaFuncSetAttribute(k_fa_tc, cudaFuncAttributeMaxDy
 
 bool flash_tc_supported(const FlashArgs &p, bool has_mask) {
     if (getenv("TLB_NO_FLASH_TC") || !tc_available()) return false;
-    if (p.d != fat::T || p.dv != fat::T || p.k_f32 || p.v_f32 || p.softcap != 0.f || p.max_bias != 0.f) return false;
+    if (p.d != fat::T || p.dv != fat::T || p.k_ty != TLB_TYPE_F16 || p.v_ty != TLB_TYPE_F16 || p.softcap != 0.f || p.max_bias != 0.f) return false;
     if (p.nq < 64 || p.nkv < 1 || (p.nkv + fat::T - 1) / fat::T > 512 || p.nh % p.nhkv != 0) return false;
     if (p.q.nb[1] % 16 || p.q.nb[2] % 16 || p.q.nb[3] % 16) return false;
     if (has_mask && (p.m.nb[1] % 16 || p.m.nb[2] % 16 || p.m.nb[3] % 16)) return false;

@@ -178,6 +178,7 @@ struct FlashArgs {
     int nq, nkv, nh, nhkv, nb, d, dv, m_ne2, m_ne3, n_head_log2;   // d: head size of queries and keys, dv: of values
     float scale, softcap, max_bias, m0, m1;   // scale already divided by softcap when that is set
     bool k_f32, v_f32;
+    uint32_t k_ty, v_ty;   // ggml types of keys and values: f16 / f32 everywhere, bf16 and the block types on the one-query-per-CTA kernel
     // split-KV (few queries over a long cache): the keys are cut into `parts` stretches of part_len, every stretch is a
     // CTA of its own that leaves (maximum, sum, unnormalised output) in scratch, and a second launch merges them
     int part_len, parts;

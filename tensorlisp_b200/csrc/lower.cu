@@ -692,13 +692,19 @@ static const char *flash_args(const Graph &g, const Tensor &t, FlashArgs &p) {
     const int32_t m = t.src[3];
     if (t.src[4] >= 0) return "attention sinks are not supported";
     const Tensor &tq = g.tensors[t.src[0]], &tk = g.tensors[t.src[1]], &tv = g.tensors[t.src[2]];
-    auto f16_or_f32 = [](const Tensor &x) { return (x.ty == TLB_TYPE_F16 && x.nb[0] == 2) || (x.ty == TLB_TYPE_F32 && x.nb[0] == 4); };
+    // f16 / f32 rows, or (on the one-query-per-CTA kernel) bf16 and the block types the executor decodes: whole rows
+    auto rows_ok = [](const Tensor &x) {
+        const TypeTraits *tr = type_traits(x.ty);
+        const bool known = x.ty == TLB_TYPE_F16 || x.ty == TLB_TYPE_F32 || x.ty == TLB_TYPE_BF16 || (tr && tr->blck > 1);
+        return known && tr && x.nb[0] == (uint64_t)tr->size && x.ne[0] % tr->blck == 0;
+    };
+    const bool tc_types = (tk.ty == TLB_TYPE_F16 || tk.ty == TLB_TYPE_F32) && (tv.ty == TLB_TYPE_F16 || tv.ty == TLB_TYPE_F32);
     if (tq.ty != TLB_TYPE_F32 || tq.nb[0] != 4 || t.ty != TLB_TYPE_F32) return "queries and result must be f32";
-    if (!f16_or_f32(tk) || !f16_or_f32(tv)) return "keys and values must be dense f16 or f32 rows";
+    if (!rows_ok(tk) || !rows_ok(tv)) return "keys and values must be rows of f32, f16, bf16 or a block-quantized type";
     if (!flash_supported(tq.ne[0], tv.ne[0]) || tk.ne[0] != tq.ne[0]) return "head sizes above 512, or keys of another size than the queries";
     if (tk.ne[1] != tv.ne[1] || tk.ne[2] != tv.ne[2] || tk.ne[2] == 0 || tq.ne[2] % tk.ne[2] != 0 || tk.ne[3] != tq.ne[3] || tv.ne[3] != tq.ne[3])
         return "inconsistent shapes";
-    if (flash_rows_need_alignment(tq.ne[0], tv.ne[0]) &&
+    if (tc_types && flash_rows_need_alignment(tq.ne[0], tv.ne[0]) &&
         (tk.nb[1] % 16 || tv.nb[1] % 16 || tk.nb[2] % 16 || tv.nb[2] % 16 || tk.nb[3] % 16 || tv.nb[3] % 16 || tq.nb[1] % 8 || tq.nb[2] % 8 || tq.nb[3] % 8))
         return "rows must start on 16-byte boundaries";
     if (t.ne[0] != tv.ne[0] || t.ne[1] != tq.ne[2] || t.ne[2] != tq.ne[1] || t.ne[3] != tq.ne[3] || !t.is_contiguous())
@@ -716,6 +722,8 @@ static const char *flash_args(const Graph &g, const Tensor &t, FlashArgs &p) {
     p.nhkv = (int)tk.ne[2];
     p.k_f32 = tk.ty == TLB_TYPE_F32;
     p.v_f32 = tv.ty == TLB_TYPE_F32;
+    p.k_ty = tk.ty;
+    p.v_ty = tv.ty;
     p.scale = t.param_f32(0);
     p.max_bias = t.param_f32(1);
     p.softcap = t.param_f32(2);

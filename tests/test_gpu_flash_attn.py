@@ -161,6 +161,36 @@ def test_other_head_sizes(case):
     close(got, want.astype(np.float32), TOL)
 
 
+@pytest.mark.parametrize("name,ty,d", [("q8_0", G.Q8_0, 128), ("q4_0", G.Q4_0, 64), ("q5_1", G.Q5_1, 96), ("q4_K", G.Q4_K, 256), ("q6_K", G.Q6_K, 256),
+                                       ("bf16", G.BF16, 128)])
+def test_quantized_and_bf16_keys_and_values(oracle, name, ty, d):
+    """The reference's lowering takes keys and values of every type it can decode (crates/kernels/src/cuda/lower.rs:587-589):
+    a cache held as bf16 or as quantized blocks is decoded element by element, the query stays f32. Closed form on the
+    decoded values."""
+    nq, nkv, nh, nhkv, nb = 5, 70, 4, 2, 1
+    rng = np.random.default_rng(d + ty)
+    q = rng.standard_normal((nb, nh, nq, d)).astype(np.float32)
+    k = rng.standard_normal((nb * nhkv * nkv, d)).astype(np.float32)
+    v = rng.standard_normal((nb * nhkv * nkv, d)).astype(np.float32)
+    kq, vq = oracle.quantize(ty, k), oracle.quantize(ty, v)
+    if ty == G.BF16:
+        dec = lambda b: (b.view(np.uint16).astype(np.uint32) << 16).view(np.float32).reshape(-1, d)
+    else:
+        dec = lambda b: oracle.dequantize(ty, b, d).reshape(-1, d)
+    kd, vd = dec(kq).reshape(nb, nhkv, nkv, d), dec(vq).reshape(nb, nhkv, nkv, d)
+    scale = 1.0 / np.sqrt(d)
+    g = G.Graph()
+    tk = g.weight(ty, [d, nkv, nhkv, nb], "k")
+    tv = g.weight(ty, [d, nkv, nhkv, nb], "v")
+    tq = g.input(G.F32, [d, nq, nh, nb], "q")
+    g.output(g.flash_attn_ext(tq, tk, tv, None, scale, 0.0, 0.0, "attn"))
+    m = Model(g, [kq, vq])
+    (got,) = m.run(q)
+    m.close()
+    want = closed_form(q, kd, vd, None, scale)
+    close(got.reshape(nb, nq, nh, d), want, TOL)
+
+
 def test_sinks_are_reported_by_name():
     from tensorlisp_b200._lib import TlbError
     g = G.Graph()
