@@ -17,6 +17,7 @@
 
 #include "kernels.h"
 #include "dequant.cuh"
+#include "pdl.cuh"
 
 namespace tlb {
 
@@ -237,6 +238,9 @@ k_gemv_stream(const uint8_t *__restrict__ W, int row_bytes, int64_t M, int K, co
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint64_t full[GEMV_STAGES], empty[GEMV_STAGES];
     __shared__ float partial[2][GEMV_CW][NC];
+    // The weights do not depend on the kernel before this one: the producer streams them without waiting for it.
+    // The consumers wait before they touch the activations or write a result.
+    griddep_launch();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wpr = 1 << wpr_log;
     const int rows_per_pass = GEMV_CW >> wpr_log;
@@ -278,6 +282,7 @@ k_gemv_stream(const uint8_t *__restrict__ W, int row_bytes, int64_t M, int K, co
     }
 
     // ---- consumers
+    griddep_wait();
     aq += (int64_t)n0 * K;
     if (TYPE == TLB_TYPE_Q4_K) {
         // int8 codes of this pass's columns -> shared memory, in the lane order of row_q4_K
@@ -397,12 +402,13 @@ static cudaError_t launch_gemv_t(const void *W, int64_t K, int64_t M, const ActL
     const int8_t *aq = (const int8_t *)(ab + a.qs_off);
     const float *ad = (const float *)(ab + a.d_off);
     const int16_t *bs = (const int16_t *)(ab + a.bsum_off);
-    for (int n0 = 0; n0 < a.N;) {
+    cudaError_t e = cudaSuccess;
+    for (int n0 = 0; n0 < a.N && e == cudaSuccess;) {
         const int nc = (int)std::min<int64_t>(nc_max, a.N - n0);
         const size_t smem = (size_t)GEMV_STAGES * stage_stride + (size_t)nc * act_stride;
 #define GO(NCV)                                                                                                        \
-    k_gemv_stream<TYPE, NCV><<<grid, GEMV_THREADS, smem, st>>>((const uint8_t *)W, (int)rb, M, (int)K, aq, ad, bs, y, ldy, \
-                                                              n0, rows_per_tile, wpr_log, stage_stride, act_stride, err)
+    e = launch_pdl(k_gemv_stream<TYPE, NCV>, dim3((unsigned)grid), dim3(GEMV_THREADS), smem, st, (const uint8_t *)W, (int)rb, M, (int)K, aq, ad, bs, \
+                   y, ldy, n0, rows_per_tile, wpr_log, stage_stride, act_stride, err)
         switch (nc) {
             case 1: GO(1); break;
             case 2: GO(2); break;
@@ -412,7 +418,7 @@ static cudaError_t launch_gemv_t(const void *W, int64_t K, int64_t M, const ActL
 #undef GO
         n0 += nc;
     }
-    return cudaGetLastError();
+    return e;
 }
 
 cudaError_t launch_gemv(uint32_t type, const void *W, int64_t K, int64_t M, const ActLayout &a, const void *act,
