@@ -118,6 +118,7 @@ int tlref_op(tlref_ctx * c, const char * op, const int * src, int nsrc, const in
     else if (o == "log")       r = ggml_log(g, S(0));
     else if (o == "clamp")     r = ggml_clamp(g, S(0), F(0), F(1));
     else if (o == "leaky_relu") r = ggml_leaky_relu(g, S(0), F(0), false);
+    else if (o == "fill")      r = ggml_fill(g, S(0), F(0));
     else if (o == "rope_ext")  r = ggml_rope_ext(g, S(0), S(1), S(2), (int)I(0), (int)I(1), (int)I(2),
                                                  F(0), F(1), F(2), F(3), F(4), F(5));
     else if (o == "soft_max_ext") r = ggml_soft_max_ext(g, S(0), S(1), F(0), F(1));

@@ -212,6 +212,21 @@ class Graph:
     def sqrt(self, a, name=""):
         return self._node(self._dup(a), "SQRT", [a], name=name)
 
+    def sin(self, a, name=""):
+        return self._node(self._dup(a), "SIN", [a], name=name)
+
+    def cos(self, a, name=""):
+        return self._node(self._dup(a), "COS", [a], name=name)
+
+    def log(self, a, name=""):
+        return self._node(self._dup(a), "LOG", [a], name=name)
+
+    def leaky_relu(self, a, negative_slope: float, name=""):  # ggml_leaky_relu (not in place)
+        return self._node(self._dup(a), "LEAKY_RELU", [a], {0: f32_bits(negative_slope)}, name)
+
+    def fill(self, a, c: float, name=""):  # ggml_fill (ggml.c:5294-5317): a tensor shaped like a, every element c
+        return self._node(self._dup(a), "FILL", [a], {0: f32_bits(c)}, name)
+
     def clamp(self, a, lo: float, hi: float, name=""):
         # ggml_clamp is in place: the result is a view of a
         return self._node(self._view(a), "CLAMP", [a], {0: f32_bits(lo), 1: f32_bits(hi)}, name)
@@ -322,6 +337,17 @@ class Graph:
     def sum_rows(self, a: int, name: str = "") -> int:
         A = self.tensors[a]
         return self._node(self._new(A.ty, [1, A.ne[1], A.ne[2], A.ne[3]]), "SUM_ROWS", [a], name=name)
+
+    def mean(self, a: int, name: str = "") -> int:  # ggml_mean (ggml.c:2522-2532): f32 whatever the source type
+        A = self.tensors[a]
+        return self._node(self._new(F32, [1, A.ne[1], A.ne[2], A.ne[3]]), "MEAN", [a], name=name)
+
+    def arange(self, start: float, stop: float, step: float, name: str = "") -> int:  # ggml_arange (ggml.c:5380-5398)
+        import math
+        assert stop > start
+        # the count is taken in f32, as ggml takes it
+        steps = int(math.ceil(float(np.float32(np.float32(stop) - np.float32(start)) / np.float32(step))))
+        return self._node(self._new(F32, [steps]), "ARANGE", [], {0: f32_bits(start), 1: f32_bits(stop), 2: f32_bits(step)}, name)
 
     # ------------------------------------------------------------------ image ops (shape rules of ggml.c)
     @staticmethod

@@ -129,6 +129,27 @@ def test_argmax_ties_pick_the_last_index():
     m.close()
 
 
+@pytest.mark.parametrize("n", [100, 16384, 20000, 20001, 262144])
+def test_argmax_of_long_rows(n):
+    """The rows of the reference's own long-row test (crates/tensorlisp/tests/native.rs:416-436): the same maximum at three
+    places of a row, the maximum in the last element, noise. The native CUDA executor and ggml's CPU backend keep the
+    LAST of equal maxima (crates/kernels/src/cuda/native/core.cu:456-460). 20001 makes every second row start off a 16-byte
+    boundary."""
+    rng = np.random.default_rng(n)
+    x = rng.standard_normal((3, n)).astype(np.float32)
+    for j in (n // 3, n // 2 + 1, n - 1):
+        x[0, j] = 5.0
+    x[1, n - 1] = 9.0
+    g = G.Graph()
+    tx = g.input(G.F32, [n, 3])
+    g.output(g.argmax(tx))
+    m = Model(g)
+    (got,) = m.run(x)
+    m.close()
+    want = np.array([n - 1 - int(np.argmax(x[r, ::-1])) for r in range(3)], np.int32)
+    assert np.array_equal(np.asarray(got).reshape(-1), want)
+
+
 def test_masked_soft_max():
     rng = np.random.default_rng(3)
     x = rng.standard_normal((2, 5, 64)).astype(np.float32)       # [heads, rows, n]

@@ -163,6 +163,49 @@ def image_ops_program(b):
     return out
 
 
+def elementwise_program(b):
+    """The element-wise, normalisation, reduction and shape ops of the executor's table (crates/kernels/src/cuda/lower.rs:177-213),
+    each with ggml's own constructor beside it: what the reference's test `elementwise_norms_and_reductions` runs
+    (crates/tensorlisp/tests/native.rs:109-153) and the rest of the unary table. Returns (name, node pair) list."""
+    x = b.leaf("input", G.F32, [24, 7, 3], "x")
+    y = b.leaf("input", G.F32, [24, 7, 3], "y")
+    row = b.leaf("input", G.F32, [24, 1, 3], "row")     # broadcasts over dimension 1
+    out = []
+    out.append(("norm", b.op("norm", "norm", [x], (1e-6,), floats=[1e-6])))
+    out.append(("rms_norm", b.op("rms_norm", "rms_norm", [x], (1e-5,), floats=[1e-5])))
+    for name, code in G.UNARY_OPS.items():
+        if name != "xielu":
+            out.append(("unary " + name, b.op("unary", "unary", [x], (name,), ints=[code])))
+    out.append(("scale", b.op("scale", "scale", [x], (0.5, 3.0), floats=[0.5, 3.0])))
+    sq = b.op("sqr", "sqr", [x])
+    out.append(("sqr", sq))
+    out.append(("sqrt", b.op("sqrt", "sqrt", [sq])))
+    out.append(("log", b.op("log", "log", [b.op("scale", "scale", [sq], (1.0, 0.1), floats=[1.0, 0.1])])))
+    out.append(("sin", b.op("sin", "sin", [x])))
+    out.append(("cos", b.op("cos", "cos", [y])))
+    out.append(("leaky_relu", b.op("leaky_relu", "leaky_relu", [x], (0.1,), floats=[0.1])))
+    out.append(("fill", b.op("fill", "fill", [x], (2.5,), floats=[2.5])))
+    # clamp works in place: it gets a copy of its own to change
+    out.append(("clamp", b.op("clamp", "clamp", [b.op("scale", "scale", [x], (1.0, 0.0), floats=[1.0, 0.0])], (-0.5, 0.7), floats=[-0.5, 0.7])))
+    ey = b.op("scale", "scale", [b.op("unary", "unary", [y], ("exp",), ints=[G.UNARY_OPS["exp"]])], (1.0, 2.0), floats=[1.0, 2.0])
+    out.append(("arith", b.op("div", "div", [b.op("sub", "sub", [b.op("mul", "mul", [x, y]), sq]), ey])))
+    out.append(("add broadcast", b.op("add", "add", [x, row])))
+    out.append(("mul broadcast", b.op("mul", "mul", [x, row])))
+    out.append(("sum_rows", b.op("sum_rows", "sum_rows", [x])))
+    out.append(("mean", b.op("mean", "mean", [x])))
+    out.append(("repeat", b.op("repeat", "repeat", [row, x])))
+    for dim in (0, 1, 2):
+        out.append(("concat %d" % dim, b.op("concat", "concat", [x, y], (dim,), ints=[dim])))
+    out.append(("arange", b.op("arange", "arange", [], (1.0, 10.0, 1.5), floats=[1.0, 10.0, 1.5])))
+    return out
+
+
+def test_elementwise_op_ir_matches_ggml(ref):
+    g, rg, pairs = build_both(ref, elementwise_program)
+    compare(g, rg, pairs)
+    rg.close()
+
+
 def test_image_op_ir_matches_ggml(ref):
     g, rg, pairs = build_both(ref, image_ops_program)
     compare(g, rg, pairs)
