@@ -273,7 +273,9 @@ __device__ __forceinline__ void rope_cs(const RopeArgs &p, int64_t pr, float pos
     if (p.ext_factor != 0.0f) {
         const float yv = ((float)pr - p.corr0) / fmaxf(0.001f, p.corr1 - p.corr0);
         const float ramp_mix = (1.f - fminf(1.f, fmaxf(0.f, yv))) * p.ext_factor;
-        th = theta_interp * (1.f - ramp_mix) + theta_extrap * ramp_mix;
+        // two rounded products and a rounded sum, as the CPU build computes it: at position 4096 one unit in the last
+        // place of the angle is 5e-4 rad, so a fused multiply-add here shows in the fourth digit of the result
+        th = __fadd_rn(__fmul_rn(theta_interp, 1.f - ramp_mix), __fmul_rn(theta_extrap, ramp_mix));
         mscale *= 1.0f + 0.1f * logf(1.0f / p.freq_scale);
     }
     cs = cosf(th) * mscale;

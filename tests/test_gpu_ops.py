@@ -102,6 +102,44 @@ def test_rope(mode, name, nd, base):
     m.close()
 
 
+ROPE_VARIANTS = [
+    # head, heads, tokens, n_dims, mode, n_ctx_orig, base, freq_scale, ext_factor, attn_factor, beta_fast, beta_slow, freq factors
+    (8, 2, 3, 8, 2, 0, 100.0, 0.5, 0.0, 1.0, 32.0, 1.0, False),       # attn:rope 'base 100.0 'scale 0.5 (native.rs:256)
+    (8, 2, 3, 8, 0, 0, 100.0, 1.0, 0.0, 1.0, 0.0, 0.0, False),        # ggml-rope-ext ... 8 0 0 100.0 1.0 0.0 1.0 0.0 0.0 (native.rs:257)
+    (128, 4, 6, 128, 2, 0, 500000.0, 1.0, 0.0, 1.0, 32.0, 1.0, True),  # per-frequency factors (the scaled-rope models)
+    (128, 4, 6, 64, 0, 0, 10000.0, 1.0, 0.0, 1.0, 32.0, 1.0, True),
+    (128, 4, 6, 128, 2, 4096, 10000.0, 0.25, 1.0, 1.0, 32.0, 1.0, False),   # YaRN: interpolated and extrapolated angles mixed by a ramp
+    (64, 2, 5, 64, 0, 2048, 10000.0, 0.5, 0.7, 1.3, 16.0, 2.0, False),
+]
+
+
+@pytest.mark.parametrize("v", ROPE_VARIANTS, ids=[str(v[:9]) for v in ROPE_VARIANTS])
+def test_rope_variants_against_ggml(ref, v):
+    """Frequency scale, per-frequency factors and the YaRN ramp against ggml's CPU rope on the same inputs (the reference's
+    own test runs the first two at 1e-5, crates/tensorlisp/tests/native.rs:252-275)."""
+    hd, heads, tokens, nd, mode, nctx, base, fs, ext, attn, bf, bs, with_ff = v
+    rng = np.random.default_rng(hd + nd + mode)
+    x = rng.standard_normal((tokens, heads, hd)).astype(np.float32)
+    pos = np.array([0, 3, 7, 100, 4095, 8191][:tokens], np.int32)
+    ff = (1.0 + 7.0 * rng.random(nd // 2)).astype(np.float32)
+    rg = ref.graph(16 << 20, 1)
+    rx, rp = rg.tensor(G.F32, [hd, heads, tokens], "x", x), rg.tensor(G.I32, [tokens], "pos", pos)
+    rf = rg.tensor(G.F32, [nd // 2], "ff", ff) if with_ff else None
+    ry = rg.op("rope_ext", [rx, rp, rf], ints=[nd, mode, nctx], floats=[base, fs, ext, attn, bf, bs])
+    rg.compute([ry])
+    want = rg.read(ry).reshape(tokens, heads, hd).copy()
+    rg.close()
+    g = G.Graph()
+    tx = g.input(G.F32, [hd, heads, tokens], "x")
+    tp = g.input(G.I32, [tokens], "pos")
+    tf = g.input(G.F32, [nd // 2], "ff") if with_ff else None
+    g.output(g.rope_ext(tx, tp, tf, nd, mode, nctx, base, fs, ext, attn, bf, bs))
+    m = Model(g)
+    (got,) = m.run(*([x, pos, ff] if with_ff else [x, pos]))
+    m.close()
+    close(got.reshape(tokens, heads, hd), want, 1e-5)
+
+
 def test_soft_max_scale_argmax_add():
     x = GOLD["row_x"]
     g = G.Graph()
