@@ -65,3 +65,69 @@ def test_elementwise_ops_match_ggml(ref):
     prog_gpu.free()
     n.close()
     rg.close()
+
+
+def indexing_inputs(g, pairs, rng):
+    """Seeded inputs for indexing_program: masks with -inf holes (never a whole row), ids inside the tables, distinct
+    destination rows per SET_ROWS column."""
+    data = {}
+    for a, _ in pairs:
+        T = g.tensors[a]
+        if T.storage_kind != G.INPUT:
+            continue
+        shape = T.ne[::-1]
+        if T.name in ("mask16", "mask32"):
+            m = rng.standard_normal(shape).astype(np.float32)
+            m[rng.random(shape) < 0.3] = -np.inf
+            m[..., 0] = 0.0
+            v = m.astype(np.float16 if T.ty == G.F16 else np.float32)
+        elif T.name == "table_i32":
+            v = rng.integers(-1000, 1000, shape).astype(np.int32)
+        elif T.name in ("ids1", "ids2"):
+            v = rng.integers(0, 11, shape).astype(np.int32)
+        elif T.name in ("at64", "at32"):
+            v = np.stack([rng.permutation(11)[:4] for _ in range(int(np.prod(shape[:-1])))]).reshape(shape)
+            v = v.astype(np.int64 if T.ty == G.I64 else np.int32)
+        else:
+            v = (rng.standard_normal(shape) * 2.0).astype(np.float16 if T.ty == G.F16 else np.float32)
+        data[a] = v
+    return data
+
+
+def np_type(ty):
+    return {G.F16: np.float16, G.I32: np.int32, G.I64: np.int64}.get(ty, np.float32)
+
+
+def test_indexing_ops_match_ggml(ref):
+    from test_graph_ir import indexing_program
+    named = []
+
+    def prog(b):
+        named.extend(indexing_program(b))
+
+    g, rg, pairs = build_both(ref, prog)
+    data = indexing_inputs(g, pairs, np.random.default_rng(12))
+    theirs = dict(pairs)
+    for a, v in data.items():
+        rg.write(theirs[a], v)
+    for _, (a, _) in named:
+        g.output(a)
+    rg.compute([b for _, (_, b) in named])
+    n = Native.load([])
+    n.alloc_states([])
+    prog_gpu = NativeProgram.compile(n, g, [(name, a) for name, (a, _) in named])
+    for a, v in data.items():
+        prog_gpu.set_input(g.tensors[a].storage_index, v)
+    prog_gpu.run()
+    got = dict(prog_gpu.outputs())
+    for name, (a, b) in named:
+        want = rg.read(b, np_type(g.tensors[a].ty)).astype(np.float32)
+        have = np.asarray(got[name], np.float32).reshape(want.shape)
+        if name.startswith("soft_max"):
+            err = close(have, want, 1e-5)
+            print("%s: max error %.2e of max|want|" % (name, err / max(np.abs(want).max(), 1e-30)))
+        else:
+            assert np.array_equal(have, want), name
+    prog_gpu.free()
+    n.close()
+    rg.close()

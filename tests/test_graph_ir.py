@@ -200,6 +200,47 @@ def elementwise_program(b):
     return out
 
 
+def indexing_program(b):
+    """SOFT_MAX with f16 and f32 masks, per-head masks and ALiBi slopes; GET_ROWS from f32 / f16 / i32 tables with batched
+    ids; SET_ROWS into f32 and f16 destinations with i64 and i32 ids broadcast over the batch; copies of permuted and
+    transposed sources. Returns (name, node pair) list."""
+    out = []
+    s = b.leaf("input", G.F32, [40, 9, 6, 2], "scores")                 # [keys, queries, heads, batch]
+    m16 = b.leaf("input", G.F16, [40, 32, 1, 1], "mask16")             # one mask for all heads, padded rows
+    m32 = b.leaf("input", G.F32, [40, 9, 6, 1], "mask32")              # a mask per head
+    out.append(("soft_max plain", b.op("soft_max_ext", "soft_max_ext", [s, None], (0.7, 0.0), floats=[0.7, 0.0])))
+    out.append(("soft_max f16 mask", b.op("soft_max_ext", "soft_max_ext", [s, m16], (0.3, 0.0), floats=[0.3, 0.0])))
+    out.append(("soft_max f32 mask per head", b.op("soft_max_ext", "soft_max_ext", [s, m32], (1.0, 0.0), floats=[1.0, 0.0])))
+    out.append(("soft_max alibi", b.op("soft_max_ext", "soft_max_ext", [s, m16], (0.5, 8.0), floats=[0.5, 8.0])))
+    t32 = b.leaf("input", G.F32, [16, 11, 3], "table32")
+    t16 = b.leaf("input", G.F16, [16, 11, 3], "table16")
+    ti = b.leaf("input", G.I32, [16, 11], "table_i32")
+    ids2 = b.leaf("input", G.I32, [5, 3], "ids2")                       # one list of ids per batch entry of the table
+    ids1 = b.leaf("input", G.I32, [4], "ids1")
+    out.append(("get_rows f32 batched", b.op("get_rows", "get_rows", [t32, ids2])))
+    out.append(("get_rows f16 batched", b.op("get_rows", "get_rows", [t16, ids2])))
+    out.append(("get_rows i32", b.op("get_rows", "get_rows", [ti, ids1])))
+    rows = b.leaf("input", G.F32, [16, 4, 3], "rows")
+    at64 = b.leaf("input", G.I64, [4, 1], "at64")                       # the same rows of every batch entry
+    at32 = b.leaf("input", G.I32, [4, 3], "at32")
+    d32 = b.op("scale", "scale", [t32], (1.0, 0.0), floats=[1.0, 0.0])   # destinations that the node may write
+    d16 = b.op("cast", "cast", [t32], (G.F16,), ints=[G.F16])
+    w32 = b.op("set_rows", "set_rows", [d32, rows, at64])
+    w16 = b.op("set_rows", "set_rows", [d16, rows, at32])
+    out.append(("set_rows f32", b.op("scale", "scale", [w32], (1.0, 0.0), floats=[1.0, 0.0])))
+    out.append(("set_rows f16", b.op("cast", "cast", [w16], (G.F32,), ints=[G.F32])))
+    out.append(("cont permuted", b.op("cont", "cont", [b.op("permute", "permute", [s], (2, 0, 1, 3), ints=[2, 0, 1, 3])])))
+    out.append(("cont transposed f16", b.op("cont", "cont", [b.op("transpose", "transpose", [t16])])))
+    out.append(("cast permuted", b.op("cast", "cast", [b.op("permute", "permute", [t32], (1, 0, 2, 3), ints=[1, 0, 2, 3])], (G.F16,), ints=[G.F16])))
+    return out
+
+
+def test_indexing_op_ir_matches_ggml(ref):
+    g, rg, pairs = build_both(ref, indexing_program)
+    compare(g, rg, pairs)
+    rg.close()
+
+
 def test_elementwise_op_ir_matches_ggml(ref):
     g, rg, pairs = build_both(ref, elementwise_program)
     compare(g, rg, pairs)
