@@ -131,3 +131,82 @@ def test_indexing_ops_match_ggml(ref):
     prog_gpu.free()
     n.close()
     rg.close()
+
+
+def test_glu_variants_match_ggml(ref):
+    """GLU in every form the executor takes (REGLU, GEGLU, SWIGLU, GEGLU_ERF, GEGLU_QUICK; one tensor cut in halves, straight
+    and swapped, or two tensors) against ggml's CPU operator. GEGLU and GEGLU_QUICK read an f16 table on the CPU: those are
+    held to the table's precision against ggml and to 1e-5 against the closed form."""
+    from scipy.special import erf
+    rng = np.random.default_rng(13)
+    n, rows = 96, 7
+    xu = (rng.standard_normal((rows, 2 * n)) * 2).astype(np.float32)
+    a, u = np.ascontiguousarray(xu[:, :n]), np.ascontiguousarray(xu[:, n:])
+    act = {
+        "reglu": lambda x: np.maximum(x, 0),
+        "geglu": lambda x: 0.5 * x * (1 + np.tanh(math.sqrt(2 / math.pi) * x * (1 + 0.044715 * x * x))),
+        "swiglu": lambda x: x / (1 + np.exp(-x)),
+        "geglu_erf": lambda x: 0.5 * x * (1 + erf(x / math.sqrt(2))),
+        "geglu_quick": lambda x: x / (1 + np.exp(-1.702 * x)),
+    }
+    g, rg = G.Graph(), ref.graph(16 << 20, 1)
+    t_xu, t_a, t_u = g.input(G.F32, [2 * n, rows], "xu"), g.input(G.F32, [n, rows], "a"), g.input(G.F32, [n, rows], "u")
+    r_xu, r_a, r_u = rg.tensor(G.F32, [2 * n, rows], "xu", xu), rg.tensor(G.F32, [n, rows], "a", a), rg.tensor(G.F32, [n, rows], "u", u)
+    cases = []
+    for name, code in G.GLU_OPS.items():
+        if name == "swiglu_oai":
+            continue
+        for form in ("halves", "swapped", "split"):
+            if form == "split":
+                ours, theirs = g.glu(t_a, name, b=t_u), rg.op("glu_split", [r_a, r_u], ints=[code])
+                want64 = act[name](a.astype(np.float64)) * u
+            else:
+                sw = form == "swapped"
+                ours, theirs = g.glu(t_xu, name, swapped=sw), rg.op("glu", [r_xu], ints=[code, int(sw)])
+                want64 = act[name](u.astype(np.float64)) * a if sw else act[name](a.astype(np.float64)) * u
+            g.output(ours)
+            cases.append(("%s %s" % (name, form), ours, theirs, want64))
+    rg.compute([c[2] for c in cases])
+    n_dev = Native.load([])
+    n_dev.alloc_states([])
+    prog = NativeProgram.compile(n_dev, g, [(c[0], c[1]) for c in cases])
+    for i, v in enumerate((xu, a, u)):
+        prog.set_input(i, v)
+    prog.run()
+    got = dict(prog.outputs())
+    for name, _, theirs, want64 in cases:
+        want = rg.read(theirs).reshape(rows, n)
+        have = np.asarray(got[name], np.float32).reshape(rows, n)
+        if name.startswith(("geglu ", "geglu_quick")):
+            close(have, want, 2e-3)
+        else:
+            close(have, want, 1e-5)
+        close(have, want64.astype(np.float32), 1e-5)
+    prog.free()
+    n_dev.close()
+    rg.close()
+
+
+def test_copy_into_state_accumulates_in_graph_order():
+    """cpy(add(state, x), state) followed by a read of the state, as the reference's `state_and_set_rows_persist_between_runs`
+    does (crates/tensorlisp/tests/native.rs:437-468): the read comes after the write in graph order and sees the new sum; the
+    sum survives runs and goes back to zero with reset_state."""
+    from helpers import Model
+    g = G.Graph()
+    st = g.state(G.F32, [4], "sum")
+    x = g.input(G.F32, [4], "x")
+    g.cpy(g.add(st, x), st)
+    g.output(g.scale(st, 1.0))
+    m = Model(g, state_bytes=[16])
+    rng = np.random.default_rng(14)
+    total = np.zeros(4, np.float32)
+    for _ in range(3):
+        v = rng.standard_normal(4).astype(np.float32)
+        total = total + v
+        (got,) = m.run(v)
+        assert np.array_equal(np.asarray(got, np.float32).reshape(4), total)
+    m.native.reset_state()
+    v = rng.standard_normal(4).astype(np.float32)
+    (got,) = m.run(v)
+    assert np.array_equal(np.asarray(got, np.float32).reshape(4), v)
+    m.close()
