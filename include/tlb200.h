@@ -117,6 +117,15 @@ tlb_status tlb_state_fork(tlb_buffer *src, tlb_buffer **copy);
  * KV heads). Bounds-checked; a page that is written may not be read or written by another pair. Waits. */
 tlb_status tlb_state_copy_blocks(tlb_buffer *state, uint64_t k_pool_offset, uint64_t v_pool_offset, uint64_t pool_blocks,
                                  uint64_t bytes_per_block, const int64_t *pairs, uint32_t n_pairs);
+/* gather_kv_cache (crates/kernels/src/cuda/paged_attn.rs:450-509, shaders/gather_kv_cache_kernel.cu): the cached keys and
+ * values of `seqs` sequences, read page by page through their block tables (`tables`: seqs x max_blocks block numbers,
+ * `lens`: tokens per sequence; host memory), as dense f16 rows [token][kv_head][head_size] in host memory, one sequence
+ * after another -- what exporting or inspecting a session's cache needs. The pools start at the given byte offsets of the
+ * state block and hold `pool_blocks` pages of `block_size` tokens. Lengths and block numbers are checked on the host
+ * before anything is launched. Waits. */
+tlb_status tlb_state_gather_kv(tlb_buffer *state, uint64_t k_pool_offset, uint64_t v_pool_offset, uint64_t pool_blocks,
+                               uint32_t kv_heads, uint32_t head_size, uint32_t block_size, const int32_t *tables,
+                               uint32_t max_blocks, const int32_t *lens, uint32_t seqs, void *k_out, void *v_out);
 /* Buffer::write_at / read_range (cuda/mod.rs:79-120): bounds-checked blocking copies. */
 tlb_status tlb_buffer_write(tlb_buffer *b, uint64_t offset, const void *host, uint64_t n);
 tlb_status tlb_buffer_read(tlb_buffer *b, uint64_t offset, void *host, uint64_t n);

@@ -77,6 +77,7 @@ SYMBOLS = {
     "tlb_state_zero": (C.c_int, [_P]),
     "tlb_state_fork": (C.c_int, [_P, C.POINTER(_P)]),
     "tlb_state_copy_blocks": (C.c_int, [_P, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, _P, C.c_uint32]),
+    "tlb_state_gather_kv": (C.c_int, [_P, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint32, _P, C.c_uint32, _P, C.c_uint32, _P, _P]),
     "tlb_buffer_write": (C.c_int, [_P, C.c_uint64, _P, C.c_uint64]),
     "tlb_buffer_read": (C.c_int, [_P, C.c_uint64, _P, C.c_uint64]),
     "tlb_buffer_size": (C.c_uint64, [_P]),

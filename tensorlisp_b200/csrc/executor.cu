@@ -387,6 +387,64 @@ tlb_status tlb_state_copy_blocks(tlb_buffer *state, uint64_t k_pool_offset, uint
     return TLB_OK;
 }
 
+// gather_kv_cache of the reference (crates/kernels/src/cuda/paged_attn.rs:450-509): the cached keys and values of some
+// sequences, read page by page through their block tables, as dense f16 rows in host memory.
+tlb_status tlb_state_gather_kv(tlb_buffer *state, uint64_t k_pool_offset, uint64_t v_pool_offset, uint64_t pool_blocks, uint32_t kv_heads,
+                               uint32_t head_size, uint32_t block_size, const int32_t *tables, uint32_t max_blocks, const int32_t *lens,
+                               uint32_t seqs, void *k_out, void *v_out) {
+    if (!state || ((!tables || !lens) && seqs)) return fail(TLB_INVALID, "tlb_state_gather_kv: bad arguments");
+    if (kv_heads == 0 || head_size == 0 || head_size % 8 || block_size == 0 || k_pool_offset % 16 || v_pool_offset % 16)
+        return fail(TLB_INVALID, "tlb_state_gather_kv: the head size must be a multiple of 8, the block size at least 1, the pools 16-byte aligned");
+    const uint64_t token_bytes = (uint64_t)kv_heads * head_size * 2, pool_bytes = pool_blocks * block_size * token_bytes;
+    if (k_pool_offset > state->size || pool_bytes > state->size - k_pool_offset || v_pool_offset > state->size || pool_bytes > state->size - v_pool_offset)
+        return fail(TLB_INVALID, "tlb_state_gather_kv: a pool of " + std::to_string(pool_bytes) + " bytes does not fit the state block of " + std::to_string(state->size));
+    std::vector<int64_t> first(seqs + 1, 0);   // first output row of each sequence
+    int64_t longest = 0;
+    for (uint32_t s = 0; s < seqs; s++) {
+        const int64_t n = lens[s];
+        if (n < 0 || (uint64_t)n > (uint64_t)max_blocks * block_size)
+            return fail(TLB_INVALID, "tlb_state_gather_kv: sequence " + std::to_string(s) + " has length " + std::to_string(n) + ", its table covers " +
+                                         std::to_string((uint64_t)max_blocks * block_size));
+        for (int64_t b = 0; b < (n + block_size - 1) / block_size; b++) {
+            const int64_t blk = tables[(size_t)s * max_blocks + b];
+            if (blk < 0 || (uint64_t)blk >= pool_blocks)
+                return fail(TLB_INVALID, "tlb_state_gather_kv: block " + std::to_string(blk) + " of sequence " + std::to_string(s) + " is outside a pool of " +
+                                             std::to_string(pool_blocks) + " blocks");
+        }
+        first[s + 1] = first[s] + n;
+        longest = std::max(longest, n);
+    }
+    const uint64_t out_bytes = (uint64_t)first[seqs] * token_bytes;
+    if (out_bytes == 0) return TLB_OK;
+    if (!k_out || !v_out) return fail(TLB_INVALID, "tlb_state_gather_kv: null output");
+    cudaSetDevice(state->dev->ordinal);
+    cudaStream_t st = state->dev->stream;
+    const size_t tab_bytes = (size_t)seqs * max_blocks * 4, len_bytes = (size_t)seqs * 4, first_bytes = (size_t)(seqs + 1) * 8;
+    char *dev_mem = nullptr;   // tables | lens | first rows | keys | values, each 256-byte aligned
+    auto up = [](size_t n) { return (n + 255) / 256 * 256; };
+    const size_t o_len = up(tab_bytes), o_first = o_len + up(len_bytes), o_k = o_first + up(first_bytes), o_v = o_k + up(out_bytes), total = o_v + up(out_bytes);
+    if (cudaMalloc(&dev_mem, total) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(TLB_ALLOC, "buffer allocation of " + std::to_string(total) + " bytes failed");
+    }
+    cudaError_t e = cudaMemcpyAsync(dev_mem, tables, tab_bytes, cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dev_mem + o_len, lens, len_bytes, cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dev_mem + o_first, first.data(), first_bytes, cudaMemcpyHostToDevice, st);
+    for (int which = 0; which < 2 && e == cudaSuccess; which++)
+        e = launch_paged_gather((int)seqs, (int)kv_heads, (int)head_size, (int)block_size, (int)max_blocks,
+                                (char *)state->ptr + (which ? v_pool_offset : k_pool_offset), (const int32_t *)dev_mem, (const int32_t *)(dev_mem + o_len),
+                                (const int64_t *)(dev_mem + o_first), dev_mem + (which ? o_v : o_k), (int)longest, st);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(k_out, dev_mem + o_k, out_bytes, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(v_out, dev_mem + o_v, out_bytes, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    cudaFree(dev_mem);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(TLB_EXECUTION, "gathering cached keys and values failed: " + cuda_msg(e));
+    }
+    return TLB_OK;
+}
+
 tlb_status tlb_buffer_write(tlb_buffer *b, uint64_t offset, const void *host, uint64_t n) {
     if (!b || (!host && n)) return fail(TLB_INVALID, "tlb_buffer_write: bad arguments");
     if (offset > b->size || n > b->size - offset)

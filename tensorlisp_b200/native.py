@@ -54,6 +54,21 @@ class StateBlock:
         m = np.ascontiguousarray(pairs, np.int64).reshape(-1, 2)
         check(_lib.lib().tlb_state_copy_blocks(self.h, k_pool_offset, v_pool_offset, pool_blocks, bytes_per_block, m.ctypes.data_as(C.c_void_p), len(m)))
 
+    def gather_kv(self, k_pool_offset: int, v_pool_offset: int, pool_blocks: int, kv_heads: int, head_size: int, block_size: int,
+                  tables, lens):
+        """gather_kv_cache (cuda/paged_attn.rs:450-509): the cached keys and values of the sequences as dense f16 arrays
+        [tokens of all sequences, kv_heads, head_size], sequence after sequence."""
+        t = np.ascontiguousarray(tables, np.int32)
+        n = np.ascontiguousarray(lens, np.int32)
+        t = t.reshape(len(n), -1) if len(n) else t.reshape(0, 1)
+        total = int(n.sum())
+        k = np.zeros((total, kv_heads, head_size), np.float16)
+        v = np.zeros((total, kv_heads, head_size), np.float16)
+        check(_lib.lib().tlb_state_gather_kv(self.h, k_pool_offset, v_pool_offset, pool_blocks, kv_heads, head_size, block_size,
+                                             t.ctypes.data_as(C.c_void_p), t.shape[1], n.ctypes.data_as(C.c_void_p), len(n),
+                                             k.ctypes.data_as(C.c_void_p), v.ctypes.data_as(C.c_void_p)))
+        return k, v
+
     def copy_device(self, offset: int, device_ptr: int, nbytes: int) -> None:
         """Device-to-device copy into the buffer (for data that is already in HBM)."""
         check(_lib.lib().tlb_buffer_copy_device(self.h, offset, C.c_void_p(device_ptr), nbytes))

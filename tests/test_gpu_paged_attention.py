@@ -96,6 +96,47 @@ def test_head_size_512_ragged_lengths(oracle):
     close(got, want, 1e-3)
 
 
+def test_gather_returns_what_the_cache_write_stored():
+    """gather_kv_cache of the reference's paged-attention module (crates/kernels/src/cuda/paged_attn.rs:450-509; its own
+    check: crates/kernels/tests/paged_attn_cuda.rs:140-170): tokens written through the cache-write node into shuffled
+    pages come back, sequence after sequence, exactly as they went in. Lengths and block numbers outside the tables or
+    the pool are refused before anything is launched."""
+    from tensorlisp_b200._lib import TlbError
+    rng = np.random.default_rng(21)
+    kvh, hs, bs, lens = 2, 128, 16, np.array([37, 0, 16, 5], np.int32)
+    max_blocks = 3
+    n_blocks = 9
+    perm = rng.permutation(n_blocks)
+    tables = np.zeros((len(lens), max_blocks), np.int32)
+    nxt = 0
+    for s, c in enumerate(lens):
+        nb = (c + bs - 1) // bs
+        tables[s, :nb] = perm[nxt:nxt + nb]
+        nxt += nb
+    tokens = int(lens.sum())
+    key = rng.standard_normal((tokens, kvh * hs)).astype(np.float16)
+    val = rng.standard_normal((tokens, kvh * hs)).astype(np.float16)
+    slots = np.concatenate([tables[s, np.arange(c) // bs] * bs + np.arange(c) % bs for s, c in enumerate(lens)]).astype(np.int64)
+    pool_elems = n_blocks * kvh * bs * hs
+    g = G.Graph()
+    kc = g.state(G.F16, [pool_elems], "pk")
+    vc = g.state(G.F16, [pool_elems], "pv")
+    tk = g.input(G.F32, [hs * kvh, tokens], "k")
+    tv = g.input(G.F32, [hs * kvh, tokens], "v")
+    ts = g.input(G.I32, [2 * tokens], "slots")
+    g.output(g.cast(g.paged_cache_write(g.cast(tk, G.F16), g.cast(tv, G.F16), kc, vc, ts, bs, kvh), G.F32))
+    m = Model(g, state_bytes=[pool_elems * 2, pool_elems * 2])
+    m.run(key.astype(np.float32), val.astype(np.float32), slots.view(np.int32))
+    ko, vo = m.native.state_offsets
+    k, v = m.native.state.gather_kv(ko, vo, n_blocks, kvh, hs, bs, tables, lens)
+    assert np.array_equal(k.reshape(tokens, kvh * hs), key) and np.array_equal(v.reshape(tokens, kvh * hs), val)
+    for bad_tables, bad_lens in ((tables, np.array([49, 0, 16, 5], np.int32)), (np.where(tables == perm[0], n_blocks, tables), lens),
+                                 (np.where(tables == perm[0], -1, tables), lens), (tables, np.array([37, -1, 16, 5], np.int32))):
+        with pytest.raises(TlbError):
+            m.native.state.gather_kv(ko, vo, n_blocks, kvh, hs, bs, bad_tables, bad_lens)
+    m.close()
+
+
 def test_reversed_tables_and_negative_slots(oracle):
     got, want = paged_case(oracle, 3, 8, 2, 128, 16, [33, 5, 100], seed=1, shuffle=False, skip_some=True)
     close(got, want, 1e-3)
