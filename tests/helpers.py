@@ -147,3 +147,28 @@ def oracle_prefill(oracle, cfg, specs, weights, ids, pos, n_seqs, n_tokens):
     last = np.arange(n_seqs) * n_tokens + n_tokens - 1
     x = oracle.rms_norm(np.ascontiguousarray(x[last]), cfg.eps, W["output_norm"][1])
     return lin("output", x)
+
+
+def varied_rows(seed: int, n: int = 1024) -> np.ndarray:
+    """Rows of very different character for the row quantizers: normal at scales from 1e-6 to 1e4, uniform, heavy-tailed,
+    sparse, one-sided, constant, alternating signs, a ramp, blocks of zeros inside noise, values at f16's limits."""
+    r = np.random.default_rng(seed)
+    rows = []
+    for scale in (1e-6, 1e-3, 0.02, 1.0, 37.0, 1e4):
+        rows.append(r.standard_normal(n) * scale)
+    rows.append(r.uniform(-1, 1, n))
+    rows.append(r.standard_cauchy(n).clip(-1e4, 1e4))
+    rows.append(r.standard_normal(n) * (r.random(n) < 0.05))
+    rows.append(np.abs(r.standard_normal(n)))
+    rows.append(-np.abs(r.standard_normal(n)) - 3.0)
+    rows.append(np.full(n, -0.75))
+    rows.append(np.where(np.arange(n) % 2 == 0, 1.0, -1.0) * r.random(n))
+    rows.append(np.linspace(-5, 5, n))
+    z = r.standard_normal(n)
+    z[64:128] = 0.0
+    z[256:512] = 0.0
+    rows.append(z)
+    rows.append(r.choice([65504.0, -65504.0, 6e-8, -6e-8, 1.0], n))
+    rows.append(r.standard_normal(n) * np.exp(r.uniform(-8, 8, n)))
+    rows.append(np.round(r.standard_normal(n) * 3))         # many exact ties
+    return np.asarray(rows, np.float32)

@@ -46,6 +46,18 @@ def test_against_oracle(native, oracle, ty, name, shape, scale, seed):
     assert np.array_equal(got.reshape(want.shape), want)
 
 
+@pytest.mark.parametrize("ty,name", TYPES + MORE + [(BF16, "bf16")])
+def test_varied_rows(native, oracle, ty, name):
+    """Rows of very different character (scales from 1e-6 to 1e4, heavy tails, sparse, one-sided, constant, ramps, zero
+    blocks inside noise, f16's limits, many exact ties): the bytes must still be the oracle's, which the CPU suite holds
+    against the reference's own quantizers on the same rows."""
+    from helpers import varied_rows
+    for seed in (0, 1, 2):
+        x = varied_rows(seed)
+        got, want = quantize_rows(native, ty, x), oracle.quantize(ty, x)
+        assert np.array_equal(got.view(np.uint8).reshape(want.shape), want), (name, seed)
+
+
 def test_config1_matrix_q8_0_bit_exact(native, oracle):
     """benchmark config 1: 4096x4096 N(0, 0.02) seed 0 -> Q8_0."""
     x = (np.random.default_rng(0).standard_normal((4096, 4096)) * 0.02).astype(np.float32)

@@ -25,6 +25,14 @@ def test_quantizers_match_reference(oracle, ref, ty, name, n, scale):
     assert np.array_equal(oracle.quantize(ty, x), ref.quantize(ty, x))
 
 
+@pytest.mark.parametrize("ty,name", ALL_TARGETS)
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_quantizers_match_reference_on_varied_rows(oracle, ref, ty, name, seed):
+    from helpers import varied_rows
+    x = varied_rows(seed)
+    assert np.array_equal(oracle.quantize(ty, x), ref.quantize(ty, x))
+
+
 def test_activation_quantizers_match_reference(oracle, ref):
     rng = np.random.default_rng(1)
     x = rng.standard_normal((16, 4096)).astype(np.float32)
