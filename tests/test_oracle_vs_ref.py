@@ -67,3 +67,14 @@ def test_decoders_match_reference(oracle, ref, ty):
     x = (rng.standard_normal((12, 4096)) * 0.05).astype(np.float32)
     q = ref.quantize(ty, x)
     assert np.array_equal(oracle.dequantize(ty, q, 4096).view(np.uint32), ref.dequantize(ty, q, 4096).view(np.uint32))
+
+
+@pytest.mark.parametrize("ty,name", [t for t in ALL_TARGETS if t[1] != "bf16"])
+def test_decoders_match_reference_on_varied_rows(oracle, ref, ty, name):
+    """Every block type's decoder on the bytes the reference's quantizer gives for rows of very different character: the
+    oracle's values must be ggml's, bit for bit."""
+    from helpers import varied_rows
+    x = varied_rows(3)
+    q = ref.quantize(ty, x)
+    mine, theirs = oracle.dequantize(ty, q, x.shape[1]), ref.dequantize(ty, q, x.shape[1])
+    assert np.array_equal(mine.view(np.uint32), theirs.view(np.uint32))
