@@ -347,3 +347,186 @@ def quantize_file(native, src_path: str, dst_path: str, ty: int, graphs=None, in
     out.write(dst_path)
     src.close()
     return report
+
+
+# ------------------------------------------------------------------ `tl convert`
+# safetensors dtype -> (numpy dtype, bytes per element)
+_ST_TYPES = {"F64": (np.float64, 8), "F32": (np.float32, 4), "F16": (np.float16, 2), "BF16": (np.uint16, 2), "I64": (np.int64, 8),
+             "I32": (np.int32, 4), "I16": (np.int16, 2), "I8": (np.int8, 1), "U32": (np.uint32, 4), "U16": (np.uint16, 2), "U8": (np.uint8, 1),
+             "BOOL": (np.uint8, 1)}
+_ST_FLOAT = ("F64", "F32", "F16", "BF16")
+
+
+def read_safetensors_header(path: str):
+    """(entries, data start): every tensor of a .safetensors file as {name, dtype, shape, start, end} in file order of
+    their data, offsets relative to the data section (the format: u64 header length, JSON header, data)."""
+    import json
+    with open(path, "rb") as f:
+        (n,) = struct.unpack("<Q", f.read(8))
+        header = json.loads(f.read(n).decode("utf-8"))
+    entries = [{"name": k, "dtype": v["dtype"], "shape": [int(d) for d in v["shape"]], "start": int(v["data_offsets"][0]),
+                "end": int(v["data_offsets"][1])} for k, v in header.items() if k != "__metadata__"]
+    entries.sort(key=lambda e: e["start"])
+    return entries, 8 + n
+
+
+def parse_type(name: str) -> int:
+    from . import graph as G
+    for ty, (n, _, _) in G.TYPE_TRAITS.items():
+        if n.lower() == name.lower():
+            return ty
+    raise GgufError("unknown type %r" % name)
+
+
+def convert_target(dtype: str):
+    """--dtype of `tl convert` (crates/tensorlisp-cli/src/convert.rs:227-237): ("keep", None), ("float", type) or
+    ("quant", type)."""
+    from . import graph as G
+    if dtype == "keep":
+        return ("keep", None)
+    if dtype in ("f32", "f16", "bf16"):
+        return ("float", parse_type(dtype))
+    try:
+        ty = parse_type(dtype)
+    except GgufError:
+        ty = None
+    if ty is None or G.TYPE_TRAITS[ty][1] == 1:
+        raise GgufError("unknown --dtype %r (expected keep, f32, f16, bf16 or a quantized type such as q8_0, q4_0, q4_K)" % dtype)
+    return ("quant", ty)
+
+
+def stored_type(st_dtype: str, ndim: int, target, quant_ok: bool):
+    """The type a safetensors tensor is stored as (convert.rs:129-149): with anything but f32, 1-D float tensors stay f32;
+    a quantized target applies where `quant_ok`, other matrices become f16; integers become i8 / i16 / i32."""
+    from . import graph as G
+    kind, ty = target
+
+    def float_type(native: int) -> int:
+        if kind == "keep":
+            return native
+        if kind == "float":
+            return G.F32 if ndim <= 1 and ty != G.F32 else ty
+        if ndim <= 1:
+            return G.F32
+        return ty if quant_ok else G.F16
+
+    if st_dtype in ("F32", "F64"):
+        return float_type(G.F32)
+    if st_dtype == "F16":
+        return float_type(G.F16)
+    if st_dtype == "BF16":
+        return float_type(G.BF16)
+    if st_dtype == "I8":
+        return G.I8
+    if st_dtype == "I16":
+        return G.I16
+    if st_dtype in ("I32", "I64", "U32", "U16", "U8", "BOOL"):
+        return G.I32
+    return None
+
+
+def _split_assignment(s: str):
+    if "=" not in s:
+        raise GgufError("expected NAME=VALUE, got %r" % s)
+    k, v = s.split("=", 1)
+    return k, v
+
+
+def convert_name(name: str, strip_prefix=(), replace_prefix=(), rename=()) -> str:
+    """convert.rs:217-224: the first matching prefix is stripped, then the first matching prefix replaced, then an exact
+    rename applied."""
+    stripped = next((name[len(p):] for p in strip_prefix if name.startswith(p)), name)
+    replaced = next((new + stripped[len(old):] for old, new in replace_prefix if stripped.startswith(old)), stripped)
+    return next((new for old, new in rename if old == replaced), replaced)
+
+
+def convert_plan(entries, dtype: str = "keep", types=(), no_quant=(), min_elements: int = 1024, include=(), exclude=(),
+                 strip_prefix=(), replace_prefix=(), rename=(), offset=()):
+    """What `tl convert` does with every tensor, decided before any data is read (convert.rs:271-302): a list of
+    {name, new_name, dtype, shape, stored, offset} for the converted tensors and the list of skipped names."""
+    from . import graph as G
+    target = convert_target(dtype)
+    type_rules = [(g, parse_type(t)) for g, t in map(_split_assignment, types)]
+    offsets = [(g, float(v)) for g, v in map(_split_assignment, offset)]
+    renames = [_split_assignment(r) for r in rename]
+    prefixes = [_split_assignment(r) for r in replace_prefix]
+    plan, skipped = [], []
+    for e in entries:
+        name, st, shape = e["name"], e["dtype"], e["shape"]
+        if (include and not any(glob_match(g, name) for g in include)) or any(glob_match(g, name) for g in exclude):
+            skipped.append(name)
+            continue
+        is_float = st in _ST_FLOAT
+        elements = int(np.prod(shape, dtype=np.int64)) if shape else 1
+        quant_ok = False
+        if target[0] == "quant":
+            blck = G.TYPE_TRAITS[target[1]][1]
+            quant_ok = (is_float and elements >= min_elements and bool(shape) and shape[-1] % blck == 0
+                        and not any(glob_match(g, name) for g in no_quant))
+        stored = stored_type(st, len(shape), target, quant_ok)
+        if stored is None:
+            raise GgufError("tensor %s: unsupported safetensors dtype %s" % (name, st))
+        if is_float:
+            stored = next((ty for g, ty in type_rules if glob_match(g, name)), stored)
+        row = shape[-1] if shape else 1
+        if row % G.TYPE_TRAITS[stored][1] != 0:
+            raise GgufError("tensor %s: rows of %d values do not fit the blocks of %s" % (name, row, G.TYPE_TRAITS[stored][0]))
+        if st in _ST_TYPES and e["end"] - e["start"] != elements * _ST_TYPES[st][1]:
+            raise GgufError("tensor %s: %d bytes of data do not match shape %s" % (name, e["end"] - e["start"], shape))
+        off = next((v for g, v in offsets if glob_match(g, name)), None)
+        if off is not None and not is_float:
+            raise GgufError("--offset matches %s, which is not a float tensor" % name)
+        plan.append({"name": name, "new_name": convert_name(name, strip_prefix, prefixes, renames), "dtype": st, "shape": list(shape),
+                     "stored": stored, "offset": off, "start": e["start"], "end": e["end"]})
+    return plan, skipped
+
+
+def convert_safetensors(native, inputs, dst_path: str, dtype: str = "keep", program: str | None = None, assets=(), meta=(), **rules):
+    """`tl convert` (crates/tensorlisp-cli/src/convert.rs:226-330) for local .safetensors files, with float tensors encoded
+    ON THE GPU (`tlb_quantize_rows`: f16, bf16 and every block type it takes; bit-exact with the reference's
+    DType::from_f32). `rules` are convert_plan's keyword arguments. Tensors keep the order of the files. Returns the report:
+    one dict per tensor (name, new_name, from, to, shape, bytes) plus the skipped names."""
+    from . import graph as G
+    from .native import quantize_rows
+
+    out = GgufWriter()
+    if program is not None:
+        out.set_program(program)
+    for m in meta:
+        k, v = _split_assignment(m)
+        out.set_str(k, v)
+    for name, data in assets:
+        out.set_asset(name, data)
+    report, all_skipped = [], []
+    for path in ([inputs] if isinstance(inputs, str) else list(inputs)):
+        entries, data0 = read_safetensors_header(path)
+        plan, skipped = convert_plan(entries, dtype, **rules)
+        all_skipped += skipped
+        raw = np.memmap(path, np.uint8, "r", offset=data0) if plan else None
+        for p in plan:
+            st, stored, shape = p["dtype"], p["stored"], p["shape"]
+            npdt, _ = _ST_TYPES[st]
+            src = np.frombuffer(raw[p["start"]:p["end"]], npdt)
+            row = shape[-1] if shape else 1
+            native_same = (st, stored) in (("F32", G.F32), ("F16", G.F16), ("BF16", G.BF16), ("I8", G.I8), ("I16", G.I16), ("I32", G.I32))
+            if native_same and p["offset"] is None:
+                data = src
+            elif st in _ST_FLOAT:
+                if st == "BF16":
+                    vals = (src.astype(np.uint32) << 16).view(np.float32)
+                else:
+                    vals = src.astype(np.float32)
+                if p["offset"] is not None:
+                    vals = vals + np.float32(p["offset"])
+                data = vals if stored == G.F32 else quantize_rows(native, stored, np.ascontiguousarray(vals.reshape(-1, max(row, 1))))
+            else:
+                wide = src.astype(np.int64)
+                if wide.size and (wide.min() < -2 ** 31 or wide.max() >= 2 ** 31):
+                    raise GgufError("tensor %s: a value does not fit in i32" % p["name"])
+                data = wide.astype(np.int32)
+            ne = list(reversed(shape)) if shape else [1]
+            out.add_tensor(p["new_name"], stored, ne, np.ascontiguousarray(data))
+            report.append({"name": p["name"], "new_name": p["new_name"], "from": st.lower(), "to": G.TYPE_TRAITS[stored][0], "shape": shape,
+                           "bytes": int(np.ascontiguousarray(data).nbytes)})
+    out.write(dst_path)
+    return {"tensors": report, "skipped": all_skipped}

@@ -172,3 +172,25 @@ def varied_rows(seed: int, n: int = 1024) -> np.ndarray:
     rows.append(r.standard_normal(n) * np.exp(r.uniform(-8, 8, n)))
     rows.append(np.round(r.standard_normal(n) * 3))         # many exact ties
     return np.asarray(rows, np.float32)
+
+
+def write_safetensors(path, tensors) -> None:
+    """A .safetensors file from {name: array}; bf16 tensors are given as ("BF16", uint16 array)."""
+    import json
+    import struct
+    names = {np.dtype(np.float64): "F64", np.dtype(np.float32): "F32", np.dtype(np.float16): "F16", np.dtype(np.int64): "I64",
+             np.dtype(np.int32): "I32", np.dtype(np.int16): "I16", np.dtype(np.int8): "I8", np.dtype(np.uint8): "U8", np.dtype(np.bool_): "BOOL"}
+    header, blobs, off = {}, [], 0
+    for name, a in tensors.items():
+        if isinstance(a, tuple):
+            st, a = a
+        else:
+            st = names[a.dtype]
+        b = np.ascontiguousarray(a).tobytes()
+        header[name] = {"dtype": st, "shape": list(a.shape), "data_offsets": [off, off + len(b)]}
+        blobs.append(b)
+        off += len(b)
+    h = json.dumps(header).encode()
+    h += b" " * ((8 - len(h) % 8) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(h)) + h + b"".join(blobs))

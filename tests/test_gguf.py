@@ -110,3 +110,50 @@ def test_quantize_selection_rules():
     assert skip_reason(info("w", G.F32, [4096]), G.Q8_0, None, include_1d=True) is None
     assert skip_reason(info("w", G.F32, [100, 50]), G.Q4_K, None) == "row length 100 is not a multiple of the q4_K block size 256"
     assert glob_match("blk.*.attn_?", "blk.12.attn_q") and not glob_match("blk.*", "output") and glob_match("*", "")
+
+
+def test_convert_rules(tmp_path):
+    """The decisions of `tl convert` (crates/tensorlisp-cli/src/convert.rs:129-149, 217-224, 271-302), without a GPU: which
+    type every tensor is stored as, names, offsets, and the errors raised before any data is read."""
+    from helpers import write_safetensors
+    from tensorlisp_b200 import graph as G
+    from tensorlisp_b200.gguf import GgufError, convert_plan, read_safetensors_header
+    path = str(tmp_path / "m.safetensors")
+    write_safetensors(path, {
+        "model.embed.weight": np.zeros((64, 256), np.float32),
+        "model.layers.0.attn.weight": np.zeros((256, 256), np.float16),
+        "model.layers.0.norm.weight": np.zeros(256, np.float32),
+        "model.layers.0.small.weight": np.zeros((2, 256), np.float32),
+        "model.layers.0.ragged.weight": ("BF16", np.zeros((40, 100), np.uint16)),
+        "model.ids": np.arange(6, dtype=np.int64),
+        "model.mask": np.ones((2, 3), np.bool_),
+        "model.double": np.zeros((4, 32), np.float64),
+    })
+    entries, data0 = read_safetensors_header(path)
+    assert [e["name"] for e in entries][:2] == ["model.embed.weight", "model.layers.0.attn.weight"] and data0 % 8 == 0
+    by = lambda plan: {p["name"]: p for p in plan}
+    plan, skipped = convert_plan(entries, "q4_K", no_quant=["*embed*"], strip_prefix=["model."], replace_prefix=["layers.=blk."],
+                                 rename=["ids=token_ids"], exclude=["*mask"], offset=["*norm.weight=1"])
+    p = by(plan)
+    assert skipped == ["model.mask"]
+    assert p["model.embed.weight"]["stored"] == G.F16                       # --no-quant: f16 instead
+    assert p["model.layers.0.attn.weight"]["stored"] == G.Q4_K
+    assert p["model.layers.0.norm.weight"]["stored"] == G.F32 and p["model.layers.0.norm.weight"]["offset"] == 1.0   # 1-D stays f32
+    assert p["model.layers.0.small.weight"]["stored"] == G.F16              # fewer than --min-elements values
+    assert p["model.layers.0.ragged.weight"]["stored"] == G.F16             # rows of 100 do not fit blocks of 256
+    assert p["model.ids"]["stored"] == G.I32 and p["model.ids"]["new_name"] == "token_ids"
+    assert p["model.double"]["stored"] == G.F16                             # 128 values: below the minimum
+    assert p["model.layers.0.attn.weight"]["new_name"] == "blk.0.attn.weight"
+    keep = by(convert_plan(entries, "keep")[0])
+    assert keep["model.layers.0.attn.weight"]["stored"] == G.F16 and keep["model.layers.0.ragged.weight"]["stored"] == G.BF16
+    assert keep["model.double"]["stored"] == G.F32 and keep["model.mask"]["stored"] == G.I32
+    half = by(convert_plan(entries, "bf16")[0])
+    assert half["model.embed.weight"]["stored"] == G.BF16 and half["model.layers.0.norm.weight"]["stored"] == G.F32
+    mixed = by(convert_plan(entries, "q4_K", types=["*attn*=q8_0", "*norm*=f16"])[0])
+    assert mixed["model.layers.0.attn.weight"]["stored"] == G.Q8_0 and mixed["model.layers.0.norm.weight"]["stored"] == G.F16
+    with pytest.raises(GgufError):      # a type the rows do not fit is an error before any data is read
+        convert_plan(entries, "keep", types=["*ragged*=q4_K"])
+    with pytest.raises(GgufError):
+        convert_plan(entries, "keep", offset=["model.ids=1"])
+    with pytest.raises(GgufError):
+        convert_plan(entries, "q9_9")

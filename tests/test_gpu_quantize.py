@@ -154,3 +154,38 @@ def test_quantize_file_like_tl_quantize(native, oracle, tmp_path):
     assert f.tensors[i8].ty == G.Q4_K
     assert np.array_equal(f.tensor_bytes(i8), oracle.quantize(G.Q4_K, oracle.dequantize(G.Q8_0, w8, 1024)).reshape(-1))
     f.close()
+
+
+def test_convert_safetensors_like_tl_convert(native, oracle, tmp_path):
+    """`tl convert --dtype q4_K` on the GPU (crates/tensorlisp-cli/src/convert.rs): matrices become Q4_K (one, by a --type
+    rule, Q8_0), bit-exact with the oracle from the f32 values of their f32 / f16 / bf16 sources; the 1-D norm stays f32 and
+    takes its --offset; integers become i32; a small f64 matrix becomes f16; names are rewritten; program and metadata are
+    stored."""
+    from helpers import write_safetensors
+    from tensorlisp_b200 import graph as G
+    from tensorlisp_b200.gguf import GgufFile, convert_safetensors
+    rng = np.random.default_rng(9)
+    w = (rng.standard_normal((40, 1024)) * 0.02).astype(np.float32)
+    h = rng.standard_normal((8, 512)).astype(np.float16)
+    b = (rng.standard_normal((4, 256)).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    norm = rng.standard_normal(1024).astype(np.float32)
+    ids = np.array([3, 1, 4, 1, 5, 9], np.int64)
+    small = rng.standard_normal((4, 32))
+    src, dst = str(tmp_path / "m.safetensors"), str(tmp_path / "m.gguf")
+    write_safetensors(src, {"model.w": w, "model.f16m": h, "model.b": ("BF16", b), "model.norm.weight": norm, "model.ids": ids, "model.small": small})
+    rep = convert_safetensors(native, src, dst, "q4_K", program="(define (f x) x)", meta=["general.name=tiny"], strip_prefix=["model."],
+                              types=["*f16m*=q8_0"], offset=["*norm.weight=1"])
+    assert [t["to"] for t in rep["tensors"]] == ["q4_K", "q8_0", "q4_K", "f32", "i32", "f16"] and rep["skipped"] == []
+    f = GgufFile(dst)
+    got = {t.name: (t, f.tensor_bytes(i)) for i, t in enumerate(f.tensors)}
+    assert set(got) == {"w", "f16m", "b", "norm.weight", "ids", "small"}
+    assert got["w"][0].ty == G.Q4_K and got["w"][0].ne[:2] == [1024, 40]
+    assert np.array_equal(np.frombuffer(got["w"][1], np.uint8), oracle.quantize(Q4_K, w).reshape(-1))
+    assert np.array_equal(np.frombuffer(got["f16m"][1], np.uint8), oracle.quantize(Q8_0, h.astype(np.float32)).reshape(-1))
+    bf = (b.astype(np.uint32) << 16).view(np.float32)
+    assert np.array_equal(np.frombuffer(got["b"][1], np.uint8), oracle.quantize(Q4_K, bf).reshape(-1))
+    assert np.array_equal(np.frombuffer(got["norm.weight"][1], np.float32), norm + np.float32(1))
+    assert np.array_equal(np.frombuffer(got["ids"][1], np.int32), ids.astype(np.int32))
+    assert np.array_equal(np.frombuffer(got["small"][1], np.float16), small.astype(np.float32).astype(np.float16).reshape(-1))
+    assert f.program() == "(define (f x) x)" and f.kv["general.name"][1] == "tiny"
+    f.close()
