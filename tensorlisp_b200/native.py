@@ -12,9 +12,9 @@ import numpy as np
 
 from . import _lib
 from ._lib import TlbError, check
-from .graph import Graph, TYPE_TRAITS, align256
+from .graph import F32, I32, I64, INPUT, Graph, TYPE_TRAITS, align256
 
-__all__ = ["Native", "NativeProgram", "StateBlock", "TlbError", "quantize_rows", "row_size"]
+__all__ = ["EntryCache", "Native", "NativeProgram", "StateBlock", "TlbError", "quantize_rows", "row_size", "to_i32"]
 
 _NP_OF = {0: np.float32, 1: np.float16, 26: np.int32, 27: np.int64, 24: np.int8, 25: np.int16}
 
@@ -290,6 +290,69 @@ class NativeProgram:
             self.free()
         except Exception:
             pass
+
+
+def to_i32(name: str, values: np.ndarray) -> np.ndarray:
+    """An i32 input arrives as whole-number f32 values (crates/tensorlisp/src/model.rs:940-952); anything else is an
+    input error that names the input and the value."""
+    v = np.ascontiguousarray(values)
+    if v.dtype.kind in "iu":
+        return v.astype(np.int32)
+    f = v.astype(np.float32).reshape(-1)
+    bad = ~((f == np.trunc(f)) & (f >= np.float32(-2 ** 31)) & (f <= np.float32(2 ** 31 - 1)))     # NaN compares false
+    if bad.any():
+        raise ValueError("input %r is i32 but contains %s" % (name, f[np.argmax(bad)]))
+    return f.astype(np.int64).clip(-2 ** 31, 2 ** 31 - 1).astype(np.int32).reshape(v.shape)
+
+
+class EntryCache:
+    """Inner::run_native (crates/tensorlisp/src/model.rs:1038-1093): the programs of a model's entries, compiled per
+    combination of input shapes when first seen and replayed afterwards. An entry keeps at most eight programs; a ninth
+    shape drops the oldest (and frees it). `build(name, shapes)` returns the entry's Graph for those input shapes with
+    its outputs marked (the reference builds it by running the Scheme program); `compile` is NativeProgram.compile unless
+    a test passes its own."""
+
+    LIMIT = 8
+
+    def __init__(self, native, build, compile=None) -> None:
+        self.native, self.build = native, build
+        self.compile = compile or (lambda native, graph: NativeProgram.compile(native, graph))
+        self.programs: dict[str, list[tuple[tuple, object]]] = {}
+
+    def program(self, name: str, shapes: tuple):
+        lst = self.programs.setdefault(name, [])
+        for key, prog in lst:
+            if key == shapes:
+                return prog
+        prog = self.compile(self.native, self.build(name, shapes))
+        if len(lst) >= self.LIMIT:
+            _, oldest = lst.pop(0)
+            oldest.free()
+        lst.append((shapes, prog))
+        return prog
+
+    def run(self, name: str, inputs, state: StateBlock | None = None):
+        """inputs: arrays in the entry's input order. f32 goes in as it is; an input the graph declares i32 takes
+        whole-number values. Returns the outputs as (name, array) pairs."""
+        arrays = [np.asarray(a) for a in inputs]
+        prog = self.program(name, tuple(tuple(a.shape) for a in arrays))
+        declared = [t for t in prog.graph.tensors if t.storage_kind == INPUT]
+        declared.sort(key=lambda t: t.storage_index)
+        for i, a in enumerate(arrays):
+            t = declared[i] if i < len(declared) else None
+            if t is not None and t.ty in (I32, I64):
+                a = to_i32(t.name, a) if t.ty == I32 else to_i32(t.name, a).astype(np.int64)
+            elif t is not None and t.ty == F32:
+                a = np.ascontiguousarray(a, np.float32)
+            prog.set_input(i, a)
+        prog.run(state)
+        return prog.outputs()
+
+    def free(self) -> None:
+        for lst in self.programs.values():
+            for _, prog in lst:
+                prog.free()
+        self.programs = {}
 
 
 def quantize_rows(native: Native, ty: int, x: np.ndarray) -> np.ndarray:

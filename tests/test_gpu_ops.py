@@ -328,3 +328,38 @@ def test_copy_blocks_copies_pairs():
         with pytest.raises(TlbError):
             native.state.copy_blocks(ko, vo, nb, n * 4, bad)
     native.close()
+
+
+def test_entry_cache_compiles_per_shape_and_converts_i32_inputs():
+    """The caller side of the boundary (Inner::run_native, crates/tensorlisp/src/model.rs:1038-1093): an entry is compiled
+    for the shapes of its inputs when they are first seen and replayed afterwards; an i32 input arrives as whole-number f32
+    values."""
+    from tensorlisp_b200.native import EntryCache, Native
+    rng = np.random.default_rng(31)
+    table = rng.standard_normal((20, 64)).astype(np.float32)
+    built = []
+
+    def build(name, shapes):
+        built.append(shapes)
+        g = G.Graph()
+        w = g.weight(G.F32, [64, 20], "table")
+        ids = g.input(G.I32, [shapes[0][0]], "ids")
+        x = g.input(G.F32, [64, shapes[1][0]], "x")
+        g.output(g.get_rows(w, ids, "rows"))
+        g.output(g.mul_mat(w, x, "scores"))
+        return g
+
+    n = Native.load([table])
+    n.alloc_states([])
+    cache = EntryCache(n, build)
+    for n_ids, n_x in ((3, 2), (5, 2), (3, 2)):
+        ids = rng.integers(0, 20, n_ids).astype(np.float32)          # whole numbers as f32, as the caller passes them
+        x = rng.standard_normal((n_x, 64)).astype(np.float32)
+        out = dict(cache.run("lookup", [ids, x]))
+        assert np.array_equal(out["rows"].reshape(n_ids, 64), table[ids.astype(int)])
+        close(out["scores"].reshape(n_x, 20), x @ table.T, 1e-5)
+    assert built == [((3,), (2, 64)), ((5,), (2, 64))]               # the third call reused the first program
+    with pytest.raises(ValueError):
+        cache.run("lookup", [np.array([0.5, 1, 2], np.float32), np.zeros((2, 64), np.float32)])
+    cache.free()
+    n.close()
