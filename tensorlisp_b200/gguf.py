@@ -530,3 +530,23 @@ def convert_safetensors(native, inputs, dst_path: str, dtype: str = "keep", prog
                            "bytes": int(np.ascontiguousarray(data).nbytes)})
     out.write(dst_path)
     return {"tensors": report, "skipped": all_skipped}
+
+
+def pack_program(src_path: str, dst_path: str | None, program: str, assets=()) -> None:
+    """`tl pack` (crates/tensorlisp-cli/src/convert.rs:374-397): stores a program (and assets, replacing those of the same
+    name) in a GGUF file; every tensor and every other key is carried over. Writes to `dst_path`, or replaces the file.
+    The reference first checks that the program is valid by evaluating it; that needs its Scheme front end."""
+    import os
+    src = GgufFile(src_path)
+    out = GgufWriter(src.alignment)
+    out.copy_metadata(src)
+    out.set_program(program)
+    for name, data in assets:
+        out.set_asset(name, data)
+    for i, t in enumerate(src.tensors):
+        out.add_tensor(t.name, t.ty, t.ne, np.array(src.tensor_bytes(i)))
+    target = dst_path or src_path
+    tmp = target + ".tmp"
+    out.write(tmp)
+    src.close()
+    os.replace(tmp, target)

@@ -157,3 +157,29 @@ def test_convert_rules(tmp_path):
         convert_plan(entries, "keep", offset=["model.ids=1"])
     with pytest.raises(GgufError):
         convert_plan(entries, "q9_9")
+
+
+def test_pack_program_keeps_tensors_and_metadata(tmp_path):
+    """`tl pack`: the program and a replaced asset go in, tensors and the other keys stay byte for byte; with no output
+    path the file itself is replaced."""
+    from tensorlisp_b200 import graph as G
+    from tensorlisp_b200.gguf import GgufFile, GgufWriter, pack_program
+    path = str(tmp_path / "m.gguf")
+    w = np.arange(64, dtype=np.float32).reshape(4, 16)
+    out = GgufWriter()
+    out.set_str("general.name", "tiny")
+    out.set_asset("vocab", b"old")
+    out.set_asset("merges", b"m")
+    out.add_tensor("w", G.F32, [16, 4], w)
+    out.write(path)
+    pack_program(path, None, "(define (f x) x)", assets=[("vocab", b"new")])
+    f = GgufFile(path)
+    assert f.program() == "(define (f x) x)" and f.kv["general.name"][1] == "tiny"
+    assert dict(f.assets()) == {"vocab": b"new", "merges": b"m"}
+    assert np.array_equal(np.frombuffer(f.tensor_bytes(0), np.float32).reshape(4, 16), w)
+    f.close()
+    other = str(tmp_path / "n.gguf")
+    pack_program(path, other, "(define (g x) x)")
+    f = GgufFile(other)
+    assert f.program() == "(define (g x) x)" and dict(f.assets())["vocab"] == b"new"
+    f.close()
