@@ -111,6 +111,17 @@ class Native:
             check(n.L.tlb_buffer_write(h, off, w.ctypes.data_as(C.c_void_p), w.nbytes))
         return n
 
+    @classmethod
+    def load_gguf(cls, path: str, ordinal: int = 0):
+        """Model::load_with for the native device (crates/tensorlisp/src/model.rs:458-518 -> native_cuda.rs:44-82): every
+        tensor of a GGUF file becomes a weight, in file order, at a 256-byte aligned offset of the one weight buffer, read
+        from the file and copied tensor by tensor. Returns (native, file): `file.tensors[i]` describes weight i (name, type,
+        shape), `file.program()` is the stored program text; the caller closes both."""
+        from .gguf import GgufFile
+        f = GgufFile(path)
+        n = cls.load([f.tensor_bytes(i) for i in range(len(f.tensors))], ordinal)
+        return n, f
+
     # alloc_states (native_cuda.rs:85-98): one zeroed buffer for all state tensors
     def alloc_states(self, nbytes_per_state: list[int]) -> None:
         total = 0

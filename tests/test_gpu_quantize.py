@@ -189,3 +189,40 @@ def test_convert_safetensors_like_tl_convert(native, oracle, tmp_path):
     assert np.array_equal(np.frombuffer(got["small"][1], np.float16), small.astype(np.float32).astype(np.float16).reshape(-1))
     assert f.program() == "(define (f x) x)" and f.kv["general.name"][1] == "tiny"
     f.close()
+
+
+def test_a_converted_file_loads_and_runs(native, oracle, tmp_path):
+    """safetensors -> `tl convert --dtype q8_0` on the GPU -> GGUF on disk -> Native.load_gguf -> a program over the stored
+    weights: the embedding lookup returns the dequantized rows and the projection agrees with the oracle on the file's bytes."""
+    from helpers import close, write_safetensors
+    from tensorlisp_b200 import graph as G
+    from tensorlisp_b200.gguf import convert_safetensors
+    from tensorlisp_b200.native import Native, NativeProgram
+    rng = np.random.default_rng(10)
+    emb = (rng.standard_normal((50, 256)) * 0.1).astype(np.float32)
+    proj = (rng.standard_normal((96, 256)) * 0.02).astype(np.float32)
+    src, dst = str(tmp_path / "m.safetensors"), str(tmp_path / "m.gguf")
+    write_safetensors(src, {"embed.weight": emb, "proj.weight": proj})
+    convert_safetensors(native, src, dst, "q8_0", program="(define (f ids) ids)")
+    n, f = Native.load_gguf(dst)
+    assert [t.name for t in f.tensors] == ["embed.weight", "proj.weight"] and all(t.ty == G.Q8_0 for t in f.tensors)
+    n.alloc_states([])
+    g = G.Graph()
+    we = g.weight(G.Q8_0, [256, 50], "embed.weight")
+    wp = g.weight(G.Q8_0, [256, 96], "proj.weight")
+    ids = g.input(G.I32, [4], "ids")
+    rows = g.get_rows(we, ids, "rows")
+    g.output(rows)
+    g.output(g.mul_mat(wp, rows, "scores"))
+    prog = NativeProgram.compile(n, g)
+    which = np.array([7, 0, 49, 7], np.int32)
+    prog.set_input(0, which)
+    prog.run()
+    out = dict(prog.outputs())
+    eq, pq = oracle.quantize(Q8_0, emb), oracle.quantize(Q8_0, proj)
+    want_rows = oracle.dequantize(Q8_0, eq, 256).reshape(50, 256)[which]
+    assert np.array_equal(out["rows"].reshape(4, 256), want_rows)
+    close(out["scores"].reshape(4, 96), oracle.mul_mat(Q8_0, pq, 256, want_rows), 1e-3)
+    prog.free()
+    f.close()
+    n.close()
